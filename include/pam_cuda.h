@@ -1,0 +1,368 @@
+/*
+ * pam_cuda.h -- C ABI of the B200 (sm_100a) paged-KV attention library.
+ *
+ * Two groups of entry points:
+ *
+ *  pam_*   The C ABI the reference project exports from Swift
+ *          (Sources/PagedAttentionMetal/PagedAttentionCABI.swift:71-337), with
+ *          identical names, argument order, argument types and return
+ *          conventions.  Where the reference takes an MTLBuffer object pointer,
+ *          this library takes a raw pointer to the same bytes: either CUDA
+ *          device memory, or host memory (the reference's buffers are host
+ *          visible, CABI.swift:58-62); host pointers are staged through the
+ *          context's device arena inside the call.
+ *
+ *  pamc_*  What the Swift classes PagedAttentionEngine, KVCacheManager,
+ *          BatchKVCacheManager and ContinuousBatchingScheduler need beyond
+ *          that, one function per public method; each cites the method it
+ *          backs.
+ *
+ * Conventions (CABI.swift:18-37): int32 results are 0 on success and -1 on
+ * failure, with a message kept in the context and returned by
+ * pam_last_error() until the next call on that context; creators return NULL
+ * on failure.  Handles are opaque; every handle is safe to use from several
+ * threads (calls on one handle serialise).  Unless pamc_set_async() is on,
+ * every operation has completed on the GPU when its call returns
+ * (PagedAttentionEngine.swift:2008-2015).
+ *
+ * KV pools are [block][kv_head][block_size][head_dim] in HBM; FP8 pools carry
+ * float16 scales [block][kv_head].  Element types: see PAM_DTYPE_*.
+ */
+#ifndef PAM_CUDA_H
+#define PAM_CUDA_H
+
+#include <stdbool.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* PagedAttentionDataType (PagedAttentionTypes.swift:67-74); 3 is an addition. */
+enum {
+    PAM_DTYPE_F32 = 0,
+    PAM_DTYPE_F16 = 1,
+    PAM_DTYPE_FP8 = 2, /* e4m3 codes; queries, new K/V and outputs are float16 */
+    PAM_DTYPE_BF16 = 3
+};
+
+/* Error classes: PagedAttentionError (PagedAttentionTypes.swift:5-31) and
+ * KVCacheError (KVCacheManager.swift:6-11). */
+enum {
+    PAM_OK = 0,
+    PAM_ERR_DEVICE_INIT = 1,
+    PAM_ERR_INVALID_CONFIGURATION = 4,
+    PAM_ERR_BUFFER_TOO_SMALL = 5,
+    PAM_ERR_COMMAND_ENCODING = 6,
+    PAM_ERR_COMMAND_EXECUTION = 7,
+    PAM_ERR_UNSUPPORTED = 8,
+    PAM_ERR_RESOURCE_EXHAUSTED = 10,
+    PAM_ERR_INVALID_STATE = 12,
+    PAM_ERR_RECURRING = 13,
+    PAM_ERR_KV_OUT_OF_MEMORY = 20,
+    PAM_ERR_KV_SEQUENCE_NOT_FOUND = 21,
+    PAM_ERR_KV_SEQUENCE_EXISTS = 22,
+    PAM_ERR_KV_INVALID_REQUEST = 23,
+    PAM_ERR_NULL_HANDLE = 30
+};
+
+/* BlockEvictionPolicy (KVCacheManager.swift:13-17). */
+enum { PAM_POLICY_FIFO = 0, PAM_POLICY_LIFO = 1, PAM_POLICY_BEST_FIT = 2 };
+
+/* SequenceStatus (Scheduler.swift:5-10). */
+enum { PAM_SEQ_WAITING = 0, PAM_SEQ_RUNNING = 1, PAM_SEQ_PAUSED = 2, PAM_SEQ_COMPLETED = 3 };
+
+/* PagedAttentionStats.Operation (PagedAttentionTypes.swift:171-180).  The four
+ * prefill values name reference kernel variants; this library reports
+ * PAM_OP_PREFILL_MMA for its tensor-core prefill kernel and
+ * PAM_OP_PREFILL_TILED for the general one. */
+enum {
+    PAM_OP_NONE = 0,
+    PAM_OP_PREFILL_SINGLE_PASS = 1,
+    PAM_OP_PREFILL_MMA = 2,
+    PAM_OP_PREFILL_FLASH = 3,
+    PAM_OP_PREFILL_TILED = 4,
+    PAM_OP_DECODE = 5,
+    PAM_OP_APPEND = 6,
+    PAM_OP_BACKWARD = 7
+};
+
+/* ------------------------------------------------------------------------
+ * Reference C ABI (PagedAttentionCABI.swift)
+ * ---------------------------------------------------------------------- */
+
+/* CABI.swift:71-79.  Uses the current CUDA device. */
+void *pam_create_context(void);
+/* CABI.swift:81-85 */
+void pam_destroy_context(void *ctx);
+/* CABI.swift:87-90 */
+const char *pam_last_error(void *ctx);
+/* CABI.swift:92-132.  data_type: PAM_DTYPE_*; unknown values fail. */
+void *pam_create_cache(void *ctx, int32_t max_blocks, int32_t block_size, int32_t head_dim,
+                       int32_t num_kv_heads, int32_t data_type);
+/* CABI.swift:134-138 */
+void pam_destroy_cache(void *cache);
+/* CABI.swift:140-154 -> KVCacheManager.allocateSequence (KVCacheManager.swift:106-113) */
+int32_t pam_reserve_sequence(void *ctx, void *cache, int64_t sequence_id);
+/* CABI.swift:156-171 -> KVCacheManager.appendTokens without hashes (KVCacheManager.swift:115-174) */
+int32_t pam_append_tokens(void *ctx, void *cache, int64_t sequence_id, int32_t count);
+/* CABI.swift:173-179 -> KVCacheManager.freeSequence (KVCacheManager.swift:216-239) */
+void pam_free_sequence(void *cache, int64_t sequence_id);
+/* CABI.swift:181-185; -1 for a NULL cache */
+int32_t pam_available_blocks(void *cache);
+/* CABI.swift:187-201 */
+int32_t pam_sequence_length(void *ctx, void *cache, int64_t sequence_id);
+/* CABI.swift:203-244 -> PagedAttentionEngine.appendToCache (PagedAttentionEngine.swift:585-628).
+ * keys/values: [num_new_tokens][num_kv_heads][head_dim] in the cache's type
+ * (float16 for an FP8 cache). */
+int32_t pam_append_kv(void *ctx, void *cache, int64_t sequence_id, void *keys, void *values,
+                      int32_t token_offset, int32_t num_new_tokens, int32_t num_heads);
+/* CABI.swift:246-287 -> PagedAttentionEngine.prefill (PagedAttentionEngine.swift:405-418).
+ * q/out: [seq_len][num_heads][head_dim]. */
+int32_t pam_prefill(void *ctx, void *cache, int64_t sequence_id, void *q, void *out,
+                    int32_t seq_len, int32_t num_heads, bool causal);
+/* CABI.swift:289-337 -> PagedAttentionEngine.decode (PagedAttentionEngine.swift:533-546).
+ * q/out: [batch][num_heads][head_dim]. */
+int32_t pam_decode(void *ctx, void *cache, const int64_t *batch_ids, int32_t batch_size, void *q,
+                   void *out, int32_t num_heads);
+
+/* ------------------------------------------------------------------------
+ * Context / engine (PagedAttentionEngine.swift)
+ * ---------------------------------------------------------------------- */
+
+/* Number of CUDA devices; 0 when there is none (never fails). */
+int32_t pamc_device_count(void);
+/* PagedAttentionEngine.init (PagedAttentionEngine.swift:248-333) on a chosen device. */
+void *pamc_create_context_on(int32_t device);
+/* A context without a device: it carries the last error for calls on
+ * bookkeeping-only managers (pamc_cache_create_bookkeeping) and needs no GPU.
+ * Every operation that would launch a kernel fails on it. */
+void *pamc_create_host_context(void);
+/* Class of the last error on this context (PAM_ERR_*), PAM_OK if none. */
+int32_t pamc_last_error_code(void *ctx);
+/* Run on a caller-owned CUDA stream (a cudaStream_t); NULL restores the
+ * context's own stream. */
+int32_t pamc_set_stream(void *ctx, void *cuda_stream);
+/* 1: operations return after enqueueing; 0 (default): they wait for the GPU
+ * like the reference's commitAndWait (PagedAttentionEngine.swift:2008-2015). */
+int32_t pamc_set_async(void *ctx, int32_t enabled);
+/* Wait for everything enqueued on the context's stream. */
+int32_t pamc_synchronize(void *ctx);
+/* Engine properties (PagedAttentionEngine.swift:116-129). */
+int32_t pamc_set_max_retries(void *ctx, int32_t n);            /* maxRetries, default 3 */
+int32_t pamc_set_graceful_degradation(void *ctx, int32_t on);  /* enableGracefulDegradation, default 1 */
+int32_t pamc_set_split_threshold(void *ctx, int32_t tokens);   /* splitThreshold, default 1024 */
+int32_t pamc_set_default_window(void *ctx, int32_t tokens);    /* defaultWindowSize, default 0 */
+int32_t pamc_set_default_chunk(void *ctx, int32_t tokens);     /* defaultChunkSize, default 0 */
+/* Host-side fault injection for tests of the retry loop, circuit breaker and
+ * zero-fill path (PagedAttentionEngine.swift:375-414): the next n kernel
+ * launches of this context report failure without touching the GPU. */
+int32_t pamc_inject_launch_failures(void *ctx, int32_t n);
+/* Number of this library's kernels launched on the context since creation. */
+int64_t pamc_kernel_launches(void *ctx);
+
+/* PagedAttentionStats (PagedAttentionTypes.swift:169-207). */
+typedef struct PamStats {
+    int32_t operation; /* PAM_OP_* */
+    int32_t batch_size;
+    int32_t sequence_length;
+    int32_t num_blocks;
+    int64_t temporary_bytes;
+    int32_t used_split_pass;
+    double elapsed_ms;
+} PamStats;
+/* PagedAttentionEngine.lastStats (PagedAttentionEngine.swift:137-141). */
+int32_t pamc_last_stats(void *ctx, PamStats *out);
+
+/* recommendedMaxBlocks (PagedAttentionEngine.swift:201-217) with free device
+ * memory in place of recommendedMaxWorkingSetSize. */
+int64_t pamc_recommended_max_blocks(void *ctx, int32_t block_size, int32_t num_kv_heads,
+                                    int32_t head_dim, int32_t data_type, float memory_fraction,
+                                    int32_t layer_count);
+
+/* Plain device memory for callers without a CUDA runtime of their own (the
+ * Swift veneer's PagedBuffer).  kind: 0 host->device, 1 device->host,
+ * 2 device->device; copies are ordered on the context's stream and complete
+ * on return. */
+void *pamc_buffer_alloc(void *ctx, size_t bytes);
+void pamc_buffer_free(void *ctx, void *ptr);
+int32_t pamc_memcpy(void *ctx, void *dst, const void *src, size_t bytes, int32_t kind);
+
+/* ------------------------------------------------------------------------
+ * KV cache manager (KVCacheManager.swift)
+ * ---------------------------------------------------------------------- */
+
+/* A manager that keeps block tables, reference counts and the prefix cache
+ * but owns no pools (max_blocks, block_size only).  Multi-GPU callers take
+ * allocation decisions once on such a handle and replay them on each GPU;
+ * it needs no CUDA device. */
+void *pamc_cache_create_bookkeeping(int32_t max_blocks, int32_t block_size);
+
+/* KVCacheManager.appendTokens(toSequence:count:blockHashes:) (KVCacheManager.swift:115-174).
+ * hashes[i] belongs to the i-th block newly added by this call; a shared
+ * partial last block is copied on the GPU (K, V and FP8 scales) before the
+ * call returns (KVCacheManager.swift:134-140, 176-194). */
+int32_t pamc_cache_append_tokens(void *ctx, void *cache, int64_t sequence_id, int32_t count,
+                                 const uint64_t *hashes, int32_t num_hashes);
+/* KVCacheManager.ensureExclusiveAccess (KVCacheManager.swift:200-214) */
+int32_t pamc_cache_ensure_exclusive(void *ctx, void *cache, int64_t sequence_id,
+                                    int32_t logical_block);
+/* KVCacheManager.registerBlockHash (KVCacheManager.swift:196-198) */
+void pamc_cache_register_block_hash(void *cache, uint64_t hash, int32_t physical_block);
+/* KVCacheManager.getBlockTable (KVCacheManager.swift:299-303): copies up to
+ * capacity entries to out (host memory), returns the table length or -1. */
+int32_t pamc_cache_block_table(void *ctx, void *cache, int64_t sequence_id, int32_t *out,
+                               int32_t capacity);
+/* KVCacheManager.getNumBlocks (KVCacheManager.swift:335-339) */
+int32_t pamc_cache_num_blocks(void *ctx, void *cache, int64_t sequence_id);
+/* KVCacheManager.activeSequenceCount (KVCacheManager.swift:347-351) */
+int32_t pamc_cache_active_sequences(void *cache);
+/* KVCacheManager.evictionPolicy didSet (KVCacheManager.swift:65-67, 267-283) */
+int32_t pamc_cache_set_eviction_policy(void *cache, int32_t policy);
+
+/* KVCacheMemoryStats (KVCacheManager.swift:19-32). */
+typedef struct PamMemoryStats {
+    int64_t total_blocks, used_blocks, free_blocks, active_sequences;
+    int64_t total_memory_bytes, used_memory_bytes;
+    int64_t partially_filled_blocks;
+    float fragmentation_ratio;
+    int64_t prefix_cache_hits, prefix_cache_entries, shared_blocks;
+    int32_t eviction_policy;
+} PamMemoryStats;
+/* KVCacheManager.memoryStats (KVCacheManager.swift:353-378) */
+int32_t pamc_cache_memory_stats(void *cache, PamMemoryStats *out);
+
+/* kPoolBuffer / vPoolBuffer (KVCacheManager.swift:59-60) plus the FP8 scale
+ * arrays; device pointers, any out argument may be NULL. */
+int32_t pamc_cache_pools(void *cache, void **k_pool, void **v_pool, void **k_scale, void **v_scale,
+                         size_t *pool_bytes, size_t *scale_bytes);
+/* Copy-on-write pairs (src block, dst block) recorded since the last call, in
+ * order; returns how many were written to out (host, capacity pairs). */
+int32_t pamc_cache_drain_cow_log(void *cache, int32_t *out_pairs, int32_t capacity);
+
+/* BatchKVCacheManager.getBatchBlockTableBuffer / getSeqLengthsBuffer
+ * (KVCacheManager.swift:661-703) and the C ABI's BatchKVCacheView
+ * (CABI.swift:339-372): rows zero-padded to max_num_blocks.  tables
+ * [n][max_num_blocks] int32 and lens [n] uint32 may be device or host memory. */
+int32_t pamc_cache_batch_tables(void *ctx, void *cache, const int64_t *ids, int32_t n,
+                                int32_t max_num_blocks, int32_t *tables, uint32_t *lens);
+/* Slot of each token of a sequence (kernels.metal:1823-1827):
+ * table[(off+t)/bs]*bs + (off+t)%bs, written to out (host). */
+int32_t pamc_cache_slot_mapping(void *ctx, void *cache, int64_t sequence_id, int32_t token_offset,
+                                int32_t num_tokens, int64_t *out);
+
+/* ------------------------------------------------------------------------
+ * Operations (PagedAttentionEngine.swift), flat form
+ * ---------------------------------------------------------------------- */
+
+/* A buffer argument with its length, for the reference's bufferTooSmall checks
+ * (PagedAttentionEngine.swift:1994-1998).  ptr may be device or host memory. */
+typedef struct PamBuffer {
+    void *ptr;
+    size_t bytes;
+} PamBuffer;
+
+/* PagedLayerSpec (PagedAttentionTypes.swift:94-152). */
+typedef struct PamLayerSpec {
+    int32_t head_dim, num_heads, num_kv_heads, block_size, data_type, window_size;
+} PamLayerSpec;
+
+/* PagedKVAppendRequest (PagedAttentionTypes.swift:318-364). */
+typedef struct PamAppendRequest {
+    PamBuffer keys, values, k_pool, v_pool, block_table;
+    int32_t token_offset, num_new_tokens;
+    PamLayerSpec layer;
+    PamBuffer k_scale, v_scale; /* FP8 only: [block][kv_head] float16 */
+} PamAppendRequest;
+/* PagedAttentionEngine.appendToCache (PagedAttentionEngine.swift:585-628) */
+int32_t pamc_append_to_cache(void *ctx, const PamAppendRequest *request);
+
+/* Append by explicit slot mapping (one int64 slot per token, device or host):
+ * the scatter of kernels.metal:1804-1961 with the slot supplied by the caller
+ * instead of derived from one block table. */
+int32_t pamc_reshape_and_cache(void *ctx, void *cache, const void *keys, const void *values,
+                               const int64_t *slot_mapping, int32_t num_tokens);
+/* Block copies of copy-on-write (KVCacheManager.swift:176-194): K, V and FP8
+ * scale rows of src[i] to dst[i]; src/dst are host arrays. */
+int32_t pamc_copy_blocks(void *ctx, void *cache, const int32_t *src, const int32_t *dst, int32_t n);
+
+/* PagedAttentionDecodeRequest (PagedAttentionTypes.swift:259-315). */
+typedef struct PamDecodeRequest {
+    PamBuffer q, k_pool, v_pool, block_tables, seq_lengths, output;
+    int32_t batch_size, max_num_blocks;
+    PamLayerSpec layer;
+    PamBuffer k_scale, v_scale;
+} PamDecodeRequest;
+/* PagedAttentionEngine.decode (PagedAttentionEngine.swift:533-580) */
+int32_t pamc_decode(void *ctx, const PamDecodeRequest *request);
+
+/* PagedAttentionPrefillRequest (PagedAttentionTypes.swift:210-256) plus the row
+ * range of one chunk: rows [q_start, q_start+q_len) of a sequence whose cache
+ * holds seq_len tokens.  q/output hold q_len rows.  q_len = 0 means the whole
+ * sequence (q_start = 0, q_len = seq_len), the reference's call. */
+typedef struct PamPrefillRequest {
+    PamBuffer q, k_pool, v_pool, block_table, output;
+    int32_t seq_len;
+    PamLayerSpec layer;
+    int32_t causal;
+    PamBuffer k_scale, v_scale;
+    int32_t q_start, q_len;
+} PamPrefillRequest;
+/* PagedAttentionEngine.prefill (PagedAttentionEngine.swift:405-528); with
+ * chunk_size > 0 the rows are processed chunk by chunk like the reference's
+ * loop (PagedAttentionEngine.swift:740-756) but each row only once. */
+int32_t pamc_prefill(void *ctx, const PamPrefillRequest *request, int32_t chunk_size);
+
+/* One launch for the same chunk of several sequences that share one cache:
+ * sequence i contributes rows [q_start[i], q_start[i]+q_len[i]); q/output are
+ * the rows of all sequences back to back.  tables [n][max_num_blocks]. */
+typedef struct PamBatchPrefillRequest {
+    PamBuffer q, k_pool, v_pool, block_tables, output;
+    const int32_t *seq_lens, *q_starts, *q_lens; /* host arrays, n entries */
+    int32_t num_sequences, max_num_blocks;
+    PamLayerSpec layer;
+    int32_t causal;
+    PamBuffer k_scale, v_scale;
+} PamBatchPrefillRequest;
+int32_t pamc_prefill_batch(void *ctx, const PamBatchPrefillRequest *request);
+
+/* ------------------------------------------------------------------------
+ * Scheduler (Scheduler.swift)
+ * ---------------------------------------------------------------------- */
+
+/* ContinuousBatchingScheduler.init (Scheduler.swift:53-56) */
+void *pamc_sched_create(int32_t max_batch_size, int32_t max_sequences);
+void pamc_sched_destroy(void *sched);
+/* addRequest (Scheduler.swift:58-70): new id, or -1 when the table is full */
+int64_t pamc_sched_add_request(void *sched, int32_t prompt_token_count, int32_t max_new_tokens);
+/* completeSequence (Scheduler.swift:72-76) */
+void pamc_sched_complete(void *sched, int64_t id);
+/* step (Scheduler.swift:78-114): ids of the batch in order; returns the batch
+ * size (which may exceed capacity; only capacity ids are written). */
+int32_t pamc_sched_step(void *sched, int64_t *out_ids, int32_t capacity);
+/* markPrefilled / markDecoded / preemptSequence (Scheduler.swift:116-132) */
+void pamc_sched_mark_prefilled(void *sched, int64_t id);
+void pamc_sched_mark_decoded(void *sched, int64_t id);
+void pamc_sched_preempt(void *sched, int64_t id);
+/* handleMemoryPressure (Scheduler.swift:134-152).  available is evaluated
+ * before every preemption like the reference's autoclosure. */
+typedef int32_t (*pamc_available_fn)(void *user);
+int32_t pamc_sched_handle_memory_pressure(void *sched, int32_t required_blocks,
+                                          pamc_available_fn available, void *user,
+                                          int64_t *out_ids, int32_t capacity);
+/* waitingCount / runningCount / completedCount (Scheduler.swift:154-170), by status */
+int32_t pamc_sched_count(void *sched, int32_t status);
+/* totalSequencesProcessed (Scheduler.swift:172-176) */
+int32_t pamc_sched_total(void *sched);
+/* SchedulerSequence (Scheduler.swift:24-40) */
+typedef struct PamSchedSequence {
+    int64_t id;
+    int32_t status, num_generated_tokens, max_new_tokens, prompt_length, arrival_order;
+} PamSchedSequence;
+int32_t pamc_sched_get(void *sched, int64_t id, PamSchedSequence *out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PAM_CUDA_H */

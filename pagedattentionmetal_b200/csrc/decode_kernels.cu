@@ -1,0 +1,642 @@
+// Batched paged decode for pools laid out [block][kv_head][block_size][head_dim].
+//
+// Semantics: paged_decode_single / _f16 / _fp8 (kernels.metal:1417-1620): per
+// (sequence, query head) softmax(q.K^T / sqrt(dim)) V over tokens
+// [window_start, L) reached through the block table, window_start = L - W when
+// W > 0 and L > W (kernels.metal:1442), float32 accumulation.
+//
+// Two kernels:
+//
+//  * decodeSplitKernel -- the fast path (float16 / bfloat16 KV, head_dim 64 or
+//    128, block_size a multiple of 16, at most 16 query heads per KV head).
+//    Split-K flash decoding.  A CTA owns (sequence, kv_head, split); each of
+//    its warps runs its own cp.async ring over 16-token tiles (a 16-token run
+//    of one kv head is contiguous in the pool: 4 KB of K and 4 KB of V for
+//    dim 128) into XOR-swizzled shared memory, multiplies with mma.sync
+//    m16n8k16 (rows = the query heads of the GQA group, so every K/V byte is
+//    read from HBM once for the whole group), keeps an online softmax in
+//    registers, and the warps' partial (m, l, O) are merged through shared
+//    memory.  With more than one split per sequence the CTA writes its partial
+//    to a workspace and decodeMergeKernel combines the splits with a
+//    log-sum-exp reduction.  The kernel is bound by HBM bandwidth; the tensor
+//    cores only keep the arithmetic out of the way.
+//
+//  * decodeGeneralKernel -- any type (float32, FP8 with the reference's
+//    half-precision dequantisation chain, kernels.metal:553-562), any block
+//    size, head_dim up to 256.  One CTA per (sequence, kv_head), 16 tokens at a
+//    time.  Used where the fast path does not apply; not tuned.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <cmath>
+
+#include "kernels.h"
+
+namespace pam {
+namespace {
+
+constexpr int kTileTokens = 16;
+constexpr float kLog2e = 1.4426950408889634f;
+
+// ---------------------------------------------------------------- PTX helpers
+
+__device__ __forceinline__ uint32_t smemAddr(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void cpAsync16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src));
+}
+__device__ __forceinline__ void cpAsyncCommit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cpAsyncWait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+__device__ __forceinline__ void ldmatrixX4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrixX4Trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+
+template <typename T>
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1);
+template <>
+__device__ __forceinline__ void mma16816<__half>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <>
+__device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template <typename T>
+__device__ __forceinline__ T fromFloat(float v);
+template <>
+__device__ __forceinline__ __half fromFloat<__half>(float v) { return __float2half_rn(v); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 fromFloat<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <>
+__device__ __forceinline__ float fromFloat<float>(float v) { return v; }
+
+__device__ __forceinline__ float toFloat(float v) { return v; }
+__device__ __forceinline__ float toFloat(__half v) { return __half2float(v); }
+__device__ __forceinline__ float toFloat(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+// Split geometry shared by the decode and the merge kernel.
+struct SplitInfo {
+    int firstTile;   // first 16-token tile that holds a visible token
+    int numTiles;    // tiles from there to the end of the sequence
+    int windowStart; // first visible token
+};
+__device__ __forceinline__ SplitInfo splitInfo(uint32_t len, int window, int maxTokens) {
+    SplitInfo s;
+    uint32_t L = len < static_cast<uint32_t>(maxTokens) ? len : static_cast<uint32_t>(maxTokens);
+    s.windowStart = (window > 0 && len > static_cast<uint32_t>(window)) ? static_cast<int>(len) - window : 0;
+    if (s.windowStart > static_cast<int>(L)) s.windowStart = static_cast<int>(L);
+    s.firstTile = s.windowStart / kTileTokens;
+    s.numTiles = (static_cast<int>(L) + kTileTokens - 1) / kTileTokens - s.firstTile;
+    return s;
+}
+
+// ------------------------------------------------------------ fast split kernel
+
+template <typename T, int HD, int NW, int NS, bool UPPER>
+__global__ void __launch_bounds__(NW * 32)
+decodeSplitKernel(const T* __restrict__ q, const T* __restrict__ kPool, const T* __restrict__ vPool,
+                  const int32_t* __restrict__ tables, const uint32_t* __restrict__ lens,
+                  T* __restrict__ out, float* __restrict__ workspace, int heads, int kvHeads,
+                  int blockSize, int maxNumBlocks, int window, int chunkTiles, int maxSplits,
+                  float scaleLog2, int poolBlocks) {
+    constexpr int ROWB = HD * 2;                 // bytes per token row
+    constexpr int CPR = ROWB / 16;               // 16-byte chunks per row
+    constexpr int TILEB = kTileTokens * ROWB;    // bytes per K (or V) tile
+    constexpr int CHUNKS = TILEB / 16;
+    constexpr int KSTEPS = HD / 16;
+    constexpr int NT = HD / 8;                   // output n-tiles
+
+    extern __shared__ __align__(128) unsigned char smem[];
+
+    const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int G = heads / kvHeads;
+    const int r = lane >> 2, j = lane & 3;
+
+    const uint32_t len = lens[b];
+    const SplitInfo si = splitInfo(len, window, maxNumBlocks * blockSize);
+    const int numSplits = (si.numTiles + chunkTiles - 1) / chunkTiles;
+    if (si.numTiles <= 0) {
+        // Empty context (the reference divides 0 by 0 here): write zeros.
+        if (split == 0)
+            for (int i = threadIdx.x; i < G * HD; i += NW * 32)
+                out[(static_cast<int64_t>(b) * heads + kvh * G) * HD + i] = fromFloat<T>(0.f);
+        return;
+    }
+    if (split >= numSplits) return;
+
+    const int tileBegin = si.firstTile + split * chunkTiles;
+    const int tileEnd = min(tileBegin + chunkTiles, si.firstTile + si.numTiles);
+    // warp w takes tiles tileBegin + w, + NW, ...
+    const int myTiles = (tileEnd - tileBegin - warp + NW - 1) / NW;
+    const int tilesPerPage = blockSize / kTileTokens;
+    const int32_t* table = tables + static_cast<int64_t>(b) * maxNumBlocks;
+
+    unsigned char* ring = smem + static_cast<size_t>(warp) * NS * 2 * TILEB;
+    const uint32_t ringAddr = smemAddr(ring);
+
+    auto issue = [&](int it) {
+        const int tile = tileBegin + warp + it * NW;
+        const int page = tile / tilesPerPage, within = tile - page * tilesPerPage;
+        const int64_t blk = min(max(table[page], 0), poolBlocks - 1);   // never read outside the pool
+        const int64_t elemOff = ((blk * kvHeads + kvh) * blockSize + within * kTileTokens) * static_cast<int64_t>(HD);
+        const unsigned char* gk = reinterpret_cast<const unsigned char*>(kPool + elemOff);
+        const unsigned char* gv = reinterpret_cast<const unsigned char*>(vPool + elemOff);
+        const uint32_t sk = ringAddr + (it % NS) * 2 * TILEB, sv = sk + TILEB;
+#pragma unroll
+        for (int i = 0; i < CHUNKS / 32; ++i) {
+            const int idx = lane + 32 * i;
+            const int row = idx / CPR, c = idx % CPR;
+            const uint32_t dst = row * ROWB + ((c ^ (row & 7)) << 4);
+            cpAsync16(sk + dst, gk + idx * 16);
+            cpAsync16(sv + dst, gv + idx * 16);
+        }
+    };
+
+    // Query rows of this GQA group as A fragments (rows >= G are zero).
+    uint32_t qa[KSTEPS][4];
+    {
+        const T* qb = q + (static_cast<int64_t>(b) * heads + kvh * G) * HD;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+            const int d0 = ks * 16 + 2 * j;
+            qa[ks][0] = r < G ? *reinterpret_cast<const uint32_t*>(qb + r * HD + d0) : 0u;
+            qa[ks][2] = r < G ? *reinterpret_cast<const uint32_t*>(qb + r * HD + d0 + 8) : 0u;
+            if (UPPER) {
+                qa[ks][1] = r + 8 < G ? *reinterpret_cast<const uint32_t*>(qb + (r + 8) * HD + d0) : 0u;
+                qa[ks][3] = r + 8 < G ? *reinterpret_cast<const uint32_t*>(qb + (r + 8) * HD + d0 + 8) : 0u;
+            } else {
+                qa[ks][1] = 0u;
+                qa[ks][3] = 0u;
+            }
+        }
+    }
+
+    float o[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+#pragma unroll
+    for (int s = 0; s < NS; ++s) {
+        if (s < myTiles) issue(s);
+        cpAsyncCommit();
+    }
+
+    for (int it = 0; it < myTiles; ++it) {
+        cpAsyncWait<NS - 1>();
+        __syncwarp();
+        const int tile = tileBegin + warp + it * NW;
+        const int tokBase = tile * kTileTokens;
+        const uint32_t sk = ringAddr + (it % NS) * 2 * TILEB, sv = sk + TILEB;
+        const bool partial = tokBase < si.windowStart || tokBase + kTileTokens > static_cast<int>(len);
+        if (partial) {
+            // Rows outside [window_start, L) may hold anything; zero their V so
+            // that a zero probability times that row stays zero.
+            unsigned char* vt = ring + (it % NS) * 2 * TILEB + TILEB;
+            for (int idx = lane; idx < CHUNKS; idx += 32) {
+                const int row = idx / CPR;
+                const int tok = tokBase + row;
+                if (tok < si.windowStart || tok >= static_cast<int>(len))
+                    *reinterpret_cast<uint4*>(vt + idx * 16) = make_uint4(0u, 0u, 0u, 0u);
+            }
+            __syncwarp();
+        }
+
+        // S = Q K^T for the 16 tokens of the tile (two n-tiles of 8 tokens).
+        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+            const int mi = lane >> 3, rowIn = lane & 7;
+            const int row = 8 * (mi >> 1) + rowIn, chunk = 2 * ks + (mi & 1);
+            uint32_t kb[4];
+            ldmatrixX4(kb, sk + row * ROWB + ((chunk ^ (row & 7)) << 4));
+            mma16816<T>(s[0], qa[ks], kb[0], kb[1]);
+            mma16816<T>(s[1], qa[ks], kb[2], kb[3]);
+        }
+
+        // Online softmax in the log2 domain.
+        float tmax0 = -INFINITY, tmax1 = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int tok = tokBase + 8 * nt + 2 * j + e;
+                const bool ok = !partial || (tok >= si.windowStart && tok < static_cast<int>(len));
+                s[nt][e] = ok ? s[nt][e] * scaleLog2 : -INFINITY;
+                tmax0 = fmaxf(tmax0, s[nt][e]);
+                if (UPPER) {
+                    s[nt][e + 2] = ok ? s[nt][e + 2] * scaleLog2 : -INFINITY;
+                    tmax1 = fmaxf(tmax1, s[nt][e + 2]);
+                }
+            }
+        }
+        tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xFFFFFFFFu, tmax0, 1));
+        tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xFFFFFFFFu, tmax0, 2));
+        const float mn0 = fmaxf(m0, tmax0);
+        const float c0 = exp2f(m0 - mn0);          // m0 = -inf gives 0
+        m0 = mn0;
+        float c1 = 1.f;
+        if (UPPER) {
+            tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xFFFFFFFFu, tmax1, 1));
+            tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xFFFFFFFFu, tmax1, 2));
+            const float mn1 = fmaxf(m1, tmax1);
+            c1 = exp2f(m1 - mn1);
+            m1 = mn1;
+        }
+        uint32_t pa[4];
+        {
+            const float p00 = exp2f(s[0][0] - m0), p01 = exp2f(s[0][1] - m0);
+            const float p10 = exp2f(s[1][0] - m0), p11 = exp2f(s[1][1] - m0);
+            l0 = l0 * c0 + (p00 + p01 + p10 + p11);
+            pa[0] = pack2<T>(p00, p01);
+            pa[2] = pack2<T>(p10, p11);
+            if (UPPER) {
+                const float q00 = exp2f(s[0][2] - m1), q01 = exp2f(s[0][3] - m1);
+                const float q10 = exp2f(s[1][2] - m1), q11 = exp2f(s[1][3] - m1);
+                l1 = l1 * c1 + (q00 + q01 + q10 + q11);
+                pa[1] = pack2<T>(q00, q01);
+                pa[3] = pack2<T>(q10, q11);
+            } else {
+                pa[1] = 0u;
+                pa[3] = 0u;
+            }
+        }
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+            o[n][0] *= c0;
+            o[n][1] *= c0;
+            if (UPPER) {
+                o[n][2] *= c1;
+                o[n][3] *= c1;
+            }
+        }
+
+        // O += P V
+#pragma unroll
+        for (int cp = 0; cp < NT / 2; ++cp) {
+            const int mi = lane >> 3, rowIn = lane & 7;
+            const int row = (mi & 1) * 8 + rowIn, chunk = 2 * cp + (mi >> 1);
+            uint32_t vb[4];
+            ldmatrixX4Trans(vb, sv + row * ROWB + ((chunk ^ (row & 7)) << 4));
+            mma16816<T>(o[2 * cp], pa, vb[0], vb[1]);
+            mma16816<T>(o[2 * cp + 1], pa, vb[2], vb[3]);
+        }
+
+        __syncwarp();
+        if (it + NS < myTiles) issue(it + NS);
+        cpAsyncCommit();
+    }
+    cpAsyncWait<0>();
+
+    // Row sums live spread over the four lanes of a quad.
+    l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 1);
+    l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 2);
+    if (UPPER) {
+        l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, 1);
+        l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, 2);
+    }
+
+    // Merge the warps of the CTA through shared memory (the rings are idle now).
+    __syncthreads();
+    float* red = reinterpret_cast<float*>(smem);            // [NW][G][HD + 2]
+    constexpr int RS = HD + 2;
+    {
+        float* mine = red + static_cast<size_t>(warp) * G * RS;
+        if (r < G) {
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                mine[r * RS + 8 * n + 2 * j] = o[n][0];
+                mine[r * RS + 8 * n + 2 * j + 1] = o[n][1];
+            }
+            if (j == 0) { mine[r * RS + HD] = m0; mine[r * RS + HD + 1] = l0; }
+        }
+        if (UPPER && r + 8 < G) {
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                mine[(r + 8) * RS + 8 * n + 2 * j] = o[n][2];
+                mine[(r + 8) * RS + 8 * n + 2 * j + 1] = o[n][3];
+            }
+            if (j == 0) { mine[(r + 8) * RS + HD] = m1; mine[(r + 8) * RS + HD + 1] = l1; }
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * HD; idx += NW * 32) {
+        const int g = idx / HD, d = idx - g * HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) M = fmaxf(M, red[(w * G + g) * RS + HD]);
+        float acc = 0.f, lsum = 0.f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) {
+            const float wgt = exp2f(red[(w * G + g) * RS + HD] - M);   // idle warps: exp2(-inf) = 0
+            acc += wgt * red[(w * G + g) * RS + d];
+            lsum += wgt * red[(w * G + g) * RS + HD + 1];
+        }
+        const int head = kvh * G + g;
+        if (numSplits == 1) {
+            out[(static_cast<int64_t>(b) * heads + head) * HD + d] = fromFloat<T>(acc / lsum);
+        } else {
+            float* part = workspace + ((static_cast<int64_t>(b) * heads + head) * maxSplits + split) * RS;
+            part[d] = acc;
+            if (d == 0) { part[HD] = M; part[HD + 1] = lsum; }
+        }
+    }
+}
+
+// Combine the splits of one (sequence, head): out = sum_s 2^(m_s - M) O_s / sum_s 2^(m_s - M) l_s.
+template <typename T, int HD>
+__global__ void decodeMergeKernel(const float* __restrict__ workspace, const uint32_t* __restrict__ lens,
+                                  T* __restrict__ out, int heads, int blockSize, int maxNumBlocks,
+                                  int window, int chunkTiles, int maxSplits) {
+    constexpr int RS = HD + 2;
+    const int head = blockIdx.x, b = blockIdx.y;
+    const SplitInfo si = splitInfo(lens[b], window, maxNumBlocks * blockSize);
+    const int numSplits = (si.numTiles + chunkTiles - 1) / chunkTiles;
+    if (numSplits <= 1) return;                       // written by the decode kernel itself
+    const float* part = workspace + (static_cast<int64_t>(b) * heads + head) * maxSplits * RS;
+    float M = -INFINITY;
+    for (int s = 0; s < numSplits; ++s) M = fmaxf(M, part[s * RS + HD]);
+    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+        float acc = 0.f, lsum = 0.f;
+        for (int s = 0; s < numSplits; ++s) {
+            const float wgt = exp2f(part[s * RS + HD] - M);
+            acc += wgt * part[s * RS + d];
+            lsum += wgt * part[s * RS + HD + 1];
+        }
+        out[(static_cast<int64_t>(b) * heads + head) * HD + d] = fromFloat<T>(acc / lsum);
+    }
+}
+
+// ------------------------------------------------------------ general kernel
+
+// dequant_fp8 (kernels.metal:553-562): every product rounded to half.
+__device__ __forceinline__ float dequantE4m3(uint8_t v, __half scale) {
+    const int e = (v >> 3) & 0xF, m = v & 7;
+    if (e == 0 && m == 0) return 0.f;
+    const __half ss = (v & 0x80) ? __hneg(scale) : scale;
+    const __half frac = __float2half_rn(static_cast<float>(m) * 0.125f);
+    if (e == 0) return __half2float(__hmul(__hmul(ss, frac), __float2half_rn(0.015625f)));
+    const __half t = __hmul(ss, __hadd(__float2half_rn(1.0f), frac));
+    return __half2float(__hmul(t, __float2half_rn(exp2f(static_cast<float>(e - 7)))));
+}
+
+template <typename QT, typename KT>
+__global__ void __launch_bounds__(128)
+decodeGeneralKernel(const QT* __restrict__ q, const KT* __restrict__ kPool, const KT* __restrict__ vPool,
+                    const int32_t* __restrict__ tables, const uint32_t* __restrict__ lens,
+                    QT* __restrict__ out, const __half* __restrict__ kScale,
+                    const __half* __restrict__ vScale, int heads, int kvHeads, int headDim,
+                    int blockSize, int maxNumBlocks, int window, int poolBlocks) {
+    constexpr int TB = 16, GMAX = 8, DPT = 2;
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int kvh = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
+    const int G = heads / kvHeads, D = headDim;
+    float* sq = reinterpret_cast<float*>(smem);       // [GMAX][D]
+    float* sk = sq + GMAX * D;                        // [TB][D]
+    float* sv = sk + TB * D;                          // [TB][D]
+    float* ss = sv + TB * D;                          // [GMAX][TB]
+    float* sm = ss + GMAX * TB;                       // m, l, corr: [3][GMAX]
+    const uint32_t len = lens[b];
+    uint32_t L = len;
+    if (L > static_cast<uint32_t>(maxNumBlocks) * blockSize) L = static_cast<uint32_t>(maxNumBlocks) * blockSize;
+    const uint32_t ws = (window > 0 && len > static_cast<uint32_t>(window)) ? len - window : 0;
+    const float scale = 1.0f / sqrtf(static_cast<float>(D));          // kernels.metal:1441
+    const int32_t* table = tables + static_cast<int64_t>(b) * maxNumBlocks;
+
+    for (int g0 = 0; g0 < G; g0 += GMAX) {
+        const int gn = min(GMAX, G - g0);
+        __syncthreads();
+        for (int i = tid; i < gn * D; i += 128)
+            sq[i] = toFloat(q[(static_cast<int64_t>(b) * heads + kvh * G + g0) * D + i]);
+        if (tid < GMAX) { sm[tid] = -INFINITY; sm[GMAX + tid] = 0.f; sm[2 * GMAX + tid] = 0.f; }
+        float acc[GMAX][DPT];
+#pragma unroll
+        for (int g = 0; g < GMAX; ++g)
+#pragma unroll
+            for (int i = 0; i < DPT; ++i) acc[g][i] = 0.f;
+
+        for (uint32_t j0 = ws; j0 < L; j0 += TB) {
+            const int nt = static_cast<int>(min(static_cast<uint32_t>(TB), L - j0));
+            __syncthreads();
+            for (int i = tid; i < nt * D; i += 128) {
+                const int t = i / D, d = i - t * D;
+                const uint32_t tok = j0 + t;
+                const int64_t blk = min(max(table[tok / blockSize], 0), poolBlocks - 1);
+                const int64_t off = ((blk * kvHeads + kvh) * blockSize + tok % blockSize) * static_cast<int64_t>(D) + d;
+                if constexpr (sizeof(KT) == 1) {
+                    sk[i] = dequantE4m3(kPool[off], kScale[blk * kvHeads + kvh]);
+                    sv[i] = dequantE4m3(vPool[off], vScale[blk * kvHeads + kvh]);
+                } else {
+                    sk[i] = toFloat(kPool[off]);
+                    sv[i] = toFloat(vPool[off]);
+                }
+            }
+            __syncthreads();
+            for (int i = tid; i < gn * nt; i += 128) {
+                const int g = i / nt, t = i - g * nt;
+                float dot = 0.f;
+                for (int d = 0; d < D; ++d) dot += sq[g * D + d] * sk[t * D + d];
+                ss[g * TB + t] = dot * scale;
+            }
+            __syncthreads();
+            if (tid < gn) {
+                const int g = tid;
+                float m = sm[g], mx = m;
+                for (int t = 0; t < nt; ++t) mx = fmaxf(mx, ss[g * TB + t]);
+                const float corr = expf(m - mx);
+                float sum = 0.f;
+                for (int t = 0; t < nt; ++t) {
+                    const float p = expf(ss[g * TB + t] - mx);
+                    ss[g * TB + t] = p;
+                    sum += p;
+                }
+                sm[g] = mx;
+                sm[GMAX + g] = sm[GMAX + g] * corr + sum;
+                sm[2 * GMAX + g] = corr;
+            }
+            __syncthreads();
+#pragma unroll
+            for (int i = 0; i < DPT; ++i) {
+                const int d = tid + 128 * i;
+                if (d < D) {
+#pragma unroll
+                    for (int g = 0; g < GMAX; ++g) {
+                        if (g < gn) {
+                            float a = acc[g][i] * sm[2 * GMAX + g];
+                            for (int t = 0; t < nt; ++t) a += ss[g * TB + t] * sv[t * D + d];
+                            acc[g][i] = a;
+                        }
+                    }
+                }
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < DPT; ++i) {
+            const int d = tid + 128 * i;
+            if (d < D) {
+#pragma unroll
+                for (int g = 0; g < GMAX; ++g) {
+                    if (g < gn) {
+                        const float l = sm[GMAX + g];
+                        // An empty context is 0/0 in the reference; zeros here.
+                        const float v = l > 0.f ? acc[g][i] / l : 0.f;
+                        out[(static_cast<int64_t>(b) * heads + kvh * G + g0 + g) * D + d] = fromFloat<QT>(v);
+                    }
+                }
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------- launch plan
+
+struct SplitPlan {
+    bool fast;
+    int chunkTiles, maxSplits;
+};
+
+constexpr int kWarps = 4, kStages = 3;
+
+SplitPlan planSplits(const DecodeParams& p, int smCount) {
+    SplitPlan plan{false, 0, 1};
+    const int G = p.kvHeads > 0 ? p.heads / p.kvHeads : 0;
+    plan.fast = (p.dtype == kF16 || p.dtype == kBF16) && (p.headDim == 128 || p.headDim == 64) &&
+                p.blockSize % kTileTokens == 0 && G >= 1 && G <= 16;
+    if (!plan.fast) return plan;
+    int maxTokens = p.maxNumBlocks * p.blockSize;
+    if (p.maxContext > 0 && p.maxContext < maxTokens) maxTokens = p.maxContext;
+    if (p.window > 0 && p.window + kTileTokens < maxTokens) maxTokens = p.window + kTileTokens;
+    const int maxTiles = (maxTokens + kTileTokens - 1) / kTileTokens;
+    // Enough CTAs to fill the machine several times over, but no chunk shorter
+    // than two tiles per warp.
+    const int64_t pairs = static_cast<int64_t>(p.batch) * p.kvHeads;
+    const int64_t wantCtas = static_cast<int64_t>(smCount) * 8;
+    int chunk = 64 * kWarps / 4;                                 // 64 tiles = 1024 tokens
+    while (chunk > 2 * kWarps && pairs * ((maxTiles + chunk - 1) / chunk) < wantCtas) chunk /= 2;
+    plan.chunkTiles = chunk;
+    plan.maxSplits = (maxTiles + chunk - 1) / chunk;
+    if (plan.maxSplits < 1) plan.maxSplits = 1;
+    return plan;
+}
+
+template <typename T, int HD, bool UPPER>
+cudaError_t launchFast(const DecodeParams& p, const SplitPlan& plan, cudaStream_t stream, int* launches) {
+    constexpr int NW = kWarps, NS = kStages;
+    const int G = p.heads / p.kvHeads;
+    size_t ring = static_cast<size_t>(NW) * NS * 2 * kTileTokens * HD * 2;
+    size_t red = static_cast<size_t>(NW) * G * (HD + 2) * sizeof(float);
+    size_t smem = ring > red ? ring : red;
+    auto kernel = decodeSplitKernel<T, HD, NW, NS, UPPER>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+    dim3 grid(static_cast<unsigned>(plan.maxSplits), static_cast<unsigned>(p.kvHeads), static_cast<unsigned>(p.batch));
+    const float scaleLog2 = (1.0f / sqrtf(static_cast<float>(p.headDim))) * kLog2e;
+    kernel<<<grid, NW * 32, smem, stream>>>(static_cast<const T*>(p.q), static_cast<const T*>(p.kPool),
+                                            static_cast<const T*>(p.vPool), p.tables, p.lens,
+                                            static_cast<T*>(p.out), p.workspace, p.heads, p.kvHeads,
+                                            p.blockSize, p.maxNumBlocks, p.window, plan.chunkTiles,
+                                            plan.maxSplits, scaleLog2, p.poolBlocks);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    if (launches) *launches += 1;
+    if (plan.maxSplits > 1) {
+        dim3 mgrid(static_cast<unsigned>(p.heads), static_cast<unsigned>(p.batch));
+        decodeMergeKernel<T, HD><<<mgrid, HD, 0, stream>>>(p.workspace, p.lens, static_cast<T*>(p.out), p.heads,
+                                                          p.blockSize, p.maxNumBlocks, p.window,
+                                                          plan.chunkTiles, plan.maxSplits);
+        e = cudaGetLastError();
+        if (e == cudaSuccess && launches) *launches += 1;
+    }
+    return e;
+}
+
+template <typename T>
+cudaError_t launchFastT(const DecodeParams& p, const SplitPlan& plan, cudaStream_t stream, int* launches) {
+    const bool upper = p.heads / p.kvHeads > 8;
+    if (p.headDim == 128)
+        return upper ? launchFast<T, 128, true>(p, plan, stream, launches)
+                     : launchFast<T, 128, false>(p, plan, stream, launches);
+    return upper ? launchFast<T, 64, true>(p, plan, stream, launches)
+                 : launchFast<T, 64, false>(p, plan, stream, launches);
+}
+
+template <typename QT, typename KT>
+cudaError_t launchGeneral(const DecodeParams& p, cudaStream_t stream, int* launches) {
+    const size_t smem = (static_cast<size_t>(8 + 2 * 16) * p.headDim + 8 * 16 + 3 * 8) * sizeof(float);
+    auto kernel = decodeGeneralKernel<QT, KT>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+    dim3 grid(static_cast<unsigned>(p.kvHeads), static_cast<unsigned>(p.batch));
+    kernel<<<grid, 128, smem, stream>>>(static_cast<const QT*>(p.q), static_cast<const KT*>(p.kPool),
+                                        static_cast<const KT*>(p.vPool), p.tables, p.lens,
+                                        static_cast<QT*>(p.out), static_cast<const __half*>(p.kScale),
+                                        static_cast<const __half*>(p.vScale), p.heads, p.kvHeads,
+                                        p.headDim, p.blockSize, p.maxNumBlocks, p.window, p.poolBlocks);
+    if (launches) *launches += 1;
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+size_t decodeWorkspaceBytes(const DecodeParams& p, int smCount) {
+    const SplitPlan plan = planSplits(p, smCount);
+    if (!plan.fast || plan.maxSplits <= 1) return 0;
+    return static_cast<size_t>(p.batch) * p.heads * plan.maxSplits * (p.headDim + 2) * sizeof(float);
+}
+
+cudaError_t launchDecode(const DecodeParams& p, int smCount, cudaStream_t stream, int* launches) {
+    if (p.batch <= 0) return cudaSuccess;
+    if (p.headDim > 256 || p.poolBlocks <= 0) return cudaErrorInvalidValue;
+    const SplitPlan plan = planSplits(p, smCount);
+    if (plan.fast) {
+        if (plan.maxSplits > 1 &&
+            (!p.workspace || p.workspaceBytes < decodeWorkspaceBytes(p, smCount)))
+            return cudaErrorInvalidValue;
+        return p.dtype == kF16 ? launchFastT<__half>(p, plan, stream, launches)
+                               : launchFastT<__nv_bfloat16>(p, plan, stream, launches);
+    }
+    switch (p.dtype) {
+        case kF32: return launchGeneral<float, float>(p, stream, launches);
+        case kF16: return launchGeneral<__half, __half>(p, stream, launches);
+        case kBF16: return launchGeneral<__nv_bfloat16, __nv_bfloat16>(p, stream, launches);
+        case kFP8: return launchGeneral<__half, uint8_t>(p, stream, launches);
+    }
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace pam

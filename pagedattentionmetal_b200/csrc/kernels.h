@@ -1,0 +1,85 @@
+// Launchers of the CUDA kernels (sm_100a).  All pointers are device pointers;
+// every launcher enqueues on `stream` and returns the launch status without
+// synchronising.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+namespace pam {
+
+enum DType { kF32 = 0, kF16 = 1, kFP8 = 2, kBF16 = 3 };
+
+inline int elemBytes(int dtype) { return dtype == kF32 ? 4 : dtype == kFP8 ? 1 : 2; }
+// Type of queries, new K/V rows and outputs for a cache of type `dtype`.
+inline int ioBytes(int dtype) { return dtype == kF32 ? 4 : 2; }
+
+// Where the slot of token t comes from: an explicit list, or one block table
+// with a token offset (slot = table[(off+t)/bs]*bs + (off+t)%bs).
+struct SlotSource {
+    const int64_t* slots = nullptr;
+    const int32_t* table = nullptr;
+    int tokenOffset = 0;
+    int64_t numSlots = 0;   // slots of the pool; tokens whose slot lies outside are skipped
+};
+
+// ---- KV append and block copies (cache_kernels.cu) ----
+cudaError_t launchReshapeAndCache(const void* keys, const void* values, void* kPool, void* vPool,
+                                  SlotSource src, int numTokens, int kvHeads, int blockSize,
+                                  int headDim, int elemBytes, cudaStream_t stream, int* launches);
+// amaxScratch: [blocks][kvHeads][2] 64-bit words, zero when first used; epoch
+// must grow by one per call on the same scratch.
+cudaError_t launchReshapeAndCacheFp8(const void* keysF16, const void* valuesF16, void* kCodes,
+                                     void* vCodes, void* kScale, void* vScale, SlotSource src,
+                                     int numTokens, int kvHeads, int blockSize, int headDim,
+                                     unsigned long long* amaxScratch, uint32_t epoch,
+                                     cudaStream_t stream, int* launches);
+// pairs: [n][2] (src block, dst block).  scale pointers may be null.
+cudaError_t launchCopyBlocks(void* kPool, void* vPool, void* kScale, void* vScale,
+                             const int32_t* pairs, int n, size_t blockBytes, int kvHeads,
+                             cudaStream_t stream, int* launches);
+
+// ---- decode (decode_kernels.cu) ----
+struct DecodeParams {
+    const void* q;            // [batch][heads][dim], io type
+    const void* kPool;        // [block][kvHeads][blockSize][dim], storage type
+    const void* vPool;
+    const int32_t* tables;    // [batch][maxNumBlocks]
+    const uint32_t* lens;     // [batch]
+    void* out;                // [batch][heads][dim], io type
+    const void* kScale;       // FP8: [block][kvHeads] float16
+    const void* vScale;
+    int batch, heads, kvHeads, headDim, blockSize, maxNumBlocks, window, dtype;
+    int maxContext;           // upper bound of any length in `lens` (for split sizing)
+    int poolBlocks;           // blocks in the pools; table entries are clamped into [0, poolBlocks)
+    float* workspace;         // split-K partials, decodeWorkspaceBytes() bytes
+    size_t workspaceBytes;
+};
+// Bytes of split-K workspace the launch of `p` needs (0 when it runs unsplit).
+size_t decodeWorkspaceBytes(const DecodeParams& p, int smCount);
+cudaError_t launchDecode(const DecodeParams& p, int smCount, cudaStream_t stream, int* launches);
+
+// ---- prefill (prefill_kernels.cu) ----
+struct PrefillParams {
+    const void* q;            // rows of all sequences back to back, [rows][heads][dim]
+    const void* kPool;
+    const void* vPool;
+    const int32_t* tables;    // [numSeqs][maxNumBlocks]
+    void* out;
+    const void* kScale;
+    const void* vScale;
+    // per sequence (device arrays, numSeqs entries)
+    const int32_t* seqLens;       // tokens in the cache
+    const int32_t* qStarts;       // first row of this launch within the sequence
+    const int32_t* qLens;         // rows of this launch
+    const int32_t* qRowOffsets;   // first row of the sequence within q/out
+    const int32_t* windowStarts;  // first visible key
+    int numSeqs, maxQLen, heads, kvHeads, headDim, blockSize, maxNumBlocks, causal, dtype;
+    int poolBlocks;               // table entries are clamped into [0, poolBlocks)
+};
+cudaError_t launchPrefill(const PrefillParams& p, int smCount, cudaStream_t stream, int* launches,
+                          bool* usedTensorPath);
+
+}  // namespace pam

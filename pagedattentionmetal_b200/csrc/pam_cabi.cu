@@ -1,0 +1,1227 @@
+// Host side of the library: context (engine), KV cache handles and the C ABI
+// declared in include/pam_cuda.h.  Mirrors PagedAttentionEngine
+// (PagedAttentionEngine.swift), KVCacheManager (KVCacheManager.swift),
+// ContinuousBatchingScheduler (Scheduler.swift) and the reference's own C ABI
+// (PagedAttentionCABI.swift); each function cites what it follows.
+#include <cuda_runtime.h>
+#include <unistd.h>
+
+#include <algorithm>
+#include <chrono>
+#include <climits>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <unordered_set>
+#include <vector>
+
+#include "../../include/pam_cuda.h"
+#include "block_manager.h"
+#include "kernels.h"
+
+namespace {
+
+using pam::BlockManager;
+using pam::KVResult;
+using pam::KVStatus;
+
+constexpr size_t kUnknownBytes = static_cast<size_t>(-1);
+
+size_t alignUp(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Device memory handed out in bump fashion for the duration of one call:
+// staging copies of host arguments, block tables, split-K partials.
+class Arena {
+public:
+    ~Arena() { release(); }
+    void release() {
+        for (auto& c : chunks_) cudaFree(c.base);
+        chunks_.clear();
+    }
+    // Start of a call: fold several chunks into one of their total size.
+    void reset(cudaStream_t stream) {
+        if (chunks_.size() > 1) {
+            size_t total = 0;
+            for (auto& c : chunks_) total += c.cap;
+            cudaStreamSynchronize(stream);
+            release();
+            void* p = nullptr;
+            if (cudaMalloc(&p, total) == cudaSuccess) chunks_.push_back({p, total, 0});
+        }
+        for (auto& c : chunks_) c.used = 0;
+    }
+    void* take(size_t bytes) {
+        bytes = alignUp(std::max<size_t>(bytes, 1), 256);
+        for (auto& c : chunks_)
+            if (c.cap - c.used >= bytes) {
+                void* p = static_cast<char*>(c.base) + c.used;
+                c.used += bytes;
+                return p;
+            }
+        size_t cap = std::max(bytes, chunks_.empty() ? size_t(1) << 20 : chunks_.back().cap * 2);
+        void* p = nullptr;
+        if (cudaMalloc(&p, cap) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+        chunks_.push_back({p, cap, bytes});
+        return p;
+    }
+
+private:
+    struct Chunk { void* base; size_t cap, used; };
+    std::vector<Chunk> chunks_;
+};
+
+struct Context {
+    int device = 0, smCount = 148;
+    cudaStream_t ownStream = nullptr, stream = nullptr;
+    bool async = false;
+    std::mutex mu;            // serialises operations and guards the fields below
+    std::string lastError;
+    bool hasError = false;
+    int lastCode = PAM_OK;
+    // PagedAttentionEngine.swift:116-129
+    int maxRetries = 3, splitThreshold = 1024, defaultWindow = 0, defaultChunk = 0;
+    bool graceful = true;
+    int consecutiveFailures = 0, injectFailures = 0;
+    int64_t launches = 0;
+    PamStats stats{};
+    Arena arena;
+
+    int32_t fail(int code, const std::string& msg) {            // CABI.swift:18-30
+        lastError = msg;
+        hasError = true;
+        lastCode = code;
+        return -1;
+    }
+    void clearError() { hasError = false; lastCode = PAM_OK; lastError.clear(); }   // CABI.swift:32-37
+};
+
+struct Cache {
+    BlockManager mgr;
+    bool bookkeeping = false;
+    int device = 0, dtype = 0, headDim = 0, kvHeads = 0, blockSize = 0, maxBlocks = 0;
+    void *kPool = nullptr, *vPool = nullptr, *kScale = nullptr, *vScale = nullptr;
+    unsigned long long* amax = nullptr;    // FP8 append scratch, [block][kv_head][2]
+    uint32_t epoch = 0;
+    size_t poolBytes = 0, scaleBytes = 0;
+    std::mutex mu;
+    std::vector<std::pair<int32_t, int32_t>> cowLog;
+    Cache(int maxBlocks_, int blockSize_) : mgr(maxBlocks_, blockSize_), blockSize(blockSize_), maxBlocks(maxBlocks_) {}
+    ~Cache() {
+        if (bookkeeping) return;
+        cudaSetDevice(device);
+        cudaFree(kPool); cudaFree(vPool); cudaFree(kScale); cudaFree(vScale); cudaFree(amax);
+    }
+    size_t blockBytes() const { return static_cast<size_t>(blockSize) * kvHeads * headDim * pam::elemBytes(dtype); }
+};
+
+struct Sched {
+    pam::Scheduler s;
+    Sched(int b, int m) : s(b, m) {}
+};
+
+Context* asCtx(void* p) { return static_cast<Context*>(p); }
+Cache* asCache(void* p) { return static_cast<Cache*>(p); }
+
+bool isDevicePointer(const void* p) {
+    cudaPointerAttributes a{};
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return false; }
+    return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
+}
+
+// Operations that need the GPU fail like a missing device (PagedAttentionTypes.swift:36-37).
+int32_t noGpu(Context* c) {
+    return c->fail(PAM_ERR_DEVICE_INIT, "Metal device or command queue could not be initialized.");
+}
+
+int32_t kvFail(Context* c, const KVResult& r) {
+    switch (r.status) {
+        case KVStatus::outOfMemory: return c->fail(PAM_ERR_KV_OUT_OF_MEMORY, "KVCacheError.outOfMemory");
+        case KVStatus::sequenceNotFound: return c->fail(PAM_ERR_KV_SEQUENCE_NOT_FOUND, "KVCacheError.sequenceNotFound");
+        case KVStatus::sequenceAlreadyExists: return c->fail(PAM_ERR_KV_SEQUENCE_EXISTS, "KVCacheError.sequenceAlreadyExists");
+        case KVStatus::invalidRequest: return c->fail(PAM_ERR_KV_INVALID_REQUEST, "KVCacheError.invalidRequest(\"" + r.message + "\")");
+        default: return 0;
+    }
+}
+
+// PagedAttentionError.description (PagedAttentionTypes.swift:34-63)
+std::string invalidConfiguration(const std::string& m) { return "Invalid paged attention configuration: " + m; }
+std::string bufferTooSmall(const char* name, size_t expected, size_t actual) {
+    return std::string(name) + " buffer is too small: expected at least " + std::to_string(expected) +
+           " bytes, got " + std::to_string(actual) + ".";
+}
+std::string commandExecutionFailed(const std::string& m) { return "Metal command execution failed: " + m; }
+
+bool validDtype(int d) { return d >= 0 && d <= 3; }
+
+// PagedLayerSpec.validate (PagedAttentionTypes.swift:126-142)
+bool validateLayer(Context* c, const PamLayerSpec& l) {
+    const char* m = nullptr;
+    if (l.head_dim <= 0) m = "headDim must be positive.";
+    else if (l.num_heads <= 0) m = "numHeads must be positive.";
+    else if (l.num_kv_heads <= 0) m = "numKVHeads must be positive.";
+    else if (l.num_heads % l.num_kv_heads != 0) m = "numHeads must be divisible by numKVHeads for GQA/MQA mapping.";
+    else if (l.block_size <= 0) m = "blockSize must be positive.";
+    if (m) { c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration(m)); return false; }
+    if (!validDtype(l.data_type)) {                              // CABI.swift:64-69
+        c->fail(PAM_ERR_INVALID_CONFIGURATION,
+                invalidConfiguration("unknown dtype " + std::to_string(l.data_type) +
+                                     "; use 0 for float32 or 1 for float16"));
+        return false;
+    }
+    return true;
+}
+
+// requireBuffer (PagedAttentionEngine.swift:1994-1998)
+bool requireBuffer(Context* c, const PamBuffer& b, const char* name, size_t expected) {
+    if (b.bytes != kUnknownBytes && b.bytes < expected) {
+        c->fail(PAM_ERR_BUFFER_TOO_SMALL, bufferTooSmall(name, expected, b.bytes));
+        return false;
+    }
+    if (!b.ptr) {
+        c->fail(PAM_ERR_BUFFER_TOO_SMALL, bufferTooSmall(name, expected, 0));
+        return false;
+    }
+    return true;
+}
+
+size_t qBytesPerToken(const PamLayerSpec& l) {                  // PagedAttentionTypes.swift:149
+    return static_cast<size_t>(l.num_heads) * l.head_dim * pam::elemBytes(l.data_type);
+}
+size_t kvBytesPerToken(const PamLayerSpec& l) {                 // PagedAttentionTypes.swift:151
+    return static_cast<size_t>(l.num_kv_heads) * l.head_dim * pam::elemBytes(l.data_type);
+}
+// Actual size of query/output rows: FP8 caches take float16 queries.
+size_t ioBytesPerToken(const PamLayerSpec& l) {
+    return static_cast<size_t>(l.num_heads) * l.head_dim * pam::ioBytes(l.data_type);
+}
+
+// Blocks a pool buffer of known length holds (table entries are clamped to it).
+int poolBlocksOf(const PamBuffer& k, const PamBuffer& v, const PamLayerSpec& l) {
+    if (k.bytes == kUnknownBytes || v.bytes == kUnknownBytes) return INT32_MAX;
+    const size_t perBlock = std::max<size_t>(static_cast<size_t>(l.block_size) * kvBytesPerToken(l), 1);
+    return static_cast<int>(std::min<size_t>(std::min(k.bytes, v.bytes) / perBlock, INT32_MAX));
+}
+
+// Host arguments are copied into the arena; outputs are copied back by finish().
+class Stager {
+public:
+    explicit Stager(Context* c) : c_(c) {}
+    const void* in(const void* p, size_t bytes) {
+        if (!p || isDevicePointer(p)) return p;
+        void* d = c_->arena.take(bytes);
+        if (!d || cudaMemcpyAsync(d, p, bytes, cudaMemcpyHostToDevice, c_->stream) != cudaSuccess) { ok_ = false; return nullptr; }
+        return d;
+    }
+    void* out(void* p, size_t bytes) {
+        if (!p || isDevicePointer(p)) return p;
+        void* d = c_->arena.take(bytes);
+        if (!d) { ok_ = false; return nullptr; }
+        outs_.push_back({p, d, bytes});
+        return d;
+    }
+    // Upload a host array the library built itself (tables, lengths, ...).
+    void* upload(const void* host, size_t bytes) {
+        void* d = c_->arena.take(bytes);
+        if (!d || cudaMemcpyAsync(d, host, bytes, cudaMemcpyHostToDevice, c_->stream) != cudaSuccess) { ok_ = false; return nullptr; }
+        return d;
+    }
+    bool ok() const { return ok_; }
+    bool hasOutputs() const { return !outs_.empty(); }
+    cudaError_t copyBack() {
+        for (auto& o : outs_) {
+            cudaError_t e = cudaMemcpyAsync(o.host, o.dev, o.bytes, cudaMemcpyDeviceToHost, c_->stream);
+            if (e != cudaSuccess) return e;
+        }
+        return cudaSuccess;
+    }
+    void zeroOutputs(void* devOrHostOut, size_t bytes) {
+        if (!devOrHostOut) return;
+        if (isDevicePointer(devOrHostOut)) cudaMemsetAsync(devOrHostOut, 0, bytes, c_->stream);
+        else std::memset(devOrHostOut, 0, bytes);
+    }
+
+private:
+    struct Out { void* host; void* dev; size_t bytes; };
+    Context* c_;
+    std::vector<Out> outs_;
+    bool ok_ = true;
+};
+
+// withRetry (PagedAttentionEngine.swift:375-400): up to maxRetries attempts,
+// a back-off of 10 ms * 2^attempt from the second failure on, and a circuit
+// breaker after 2 * maxRetries consecutive failures.  `attempt` enqueues the
+// work and returns a CUDA status; host-injected failures stand in for it.
+template <class F>
+int32_t withRetry(Context* c, const char* operation, F attempt) {
+    std::string last = "no attempt made (maxRetries is 0)";
+    for (int i = 0; i < c->maxRetries; ++i) {
+        cudaError_t e;
+        if (c->injectFailures > 0) {
+            c->injectFailures -= 1;
+            e = cudaErrorLaunchFailure;
+            last = "injected launch failure";
+        } else {
+            e = attempt();
+            if (e == cudaSuccess && !c->async) e = cudaStreamSynchronize(c->stream);
+            if (e != cudaSuccess) { last = cudaGetErrorString(e); cudaGetLastError(); }
+        }
+        if (e == cudaSuccess) { c->consecutiveFailures = 0; return 0; }
+        c->consecutiveFailures += 1;
+        if (c->consecutiveFailures >= c->maxRetries * 2) {
+            return c->fail(PAM_ERR_RECURRING, "Recurring failure in '" + std::string(operation) + "' after " +
+                                                  std::to_string(c->consecutiveFailures) +
+                                                  " attempts \xE2\x80\x94 circuit breaker engaged.");
+        }
+        if (i > 0) usleep(static_cast<useconds_t>(0.01 * static_cast<double>(1 << i) * 1e6));
+    }
+    return c->fail(PAM_ERR_COMMAND_EXECUTION, commandExecutionFailed(last));
+}
+
+double nowMs() {
+    return std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now().time_since_epoch()).count();
+}
+
+struct DeviceGuard {
+    int prev = -1;
+    explicit DeviceGuard(int dev) {
+        if (dev < 0) return;
+        cudaGetDevice(&prev);
+        if (prev != dev) cudaSetDevice(dev);
+        else prev = -1;
+    }
+    ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
+};
+
+// ------------------------------------------------------------------ operations
+
+// Copy-on-write pairs recorded by the block manager: copy K, V and scales on
+// the GPU, one launch per run of pairs that do not feed one another.
+int32_t runCopies(Context* c, Cache* k, const std::vector<std::pair<int32_t, int32_t>>& pairs) {
+    if (pairs.empty() || k->bookkeeping) return 0;
+    size_t begin = 0;
+    while (begin < pairs.size()) {
+        std::unordered_set<int32_t> written;
+        size_t end = begin;
+        while (end < pairs.size() && !written.count(pairs[end].first) && !written.count(pairs[end].second)) {
+            written.insert(pairs[end].second);
+            ++end;
+        }
+        if (end == begin) end = begin + 1;
+        std::vector<int32_t> flat;
+        for (size_t i = begin; i < end; ++i) { flat.push_back(pairs[i].first); flat.push_back(pairs[i].second); }
+        const int n = static_cast<int>(end - begin);
+        int32_t rc = withRetry(c, "copyBlocks", [&]() -> cudaError_t {
+            Stager st(c);
+            const int32_t* dev = static_cast<const int32_t*>(st.upload(flat.data(), flat.size() * sizeof(int32_t)));
+            if (!st.ok()) return cudaErrorMemoryAllocation;
+            int launches = 0;
+            cudaError_t e = pam::launchCopyBlocks(k->kPool, k->vPool, k->kScale, k->vScale, dev, n, k->blockBytes(),
+                                                  k->kvHeads, c->stream, &launches);
+            c->launches += launches;
+            // the upload buffer is read by the kernel: the caller keeps `flat` alive until the sync below
+            if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+            return e;
+        });
+        if (rc != 0) return rc;
+        begin = end;
+    }
+    return 0;
+}
+
+int32_t appendImpl(Context* c, const PamAppendRequest& rq, Cache* cacheForScratch, const int64_t* hostSlots) {
+    // PagedAttentionEngine.swift:585-628; validateAppend :1935-1950
+    if (!validateLayer(c, rq.layer)) return -1;
+    if (rq.token_offset < 0) return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("tokenOffset must be non-negative."));
+    if (rq.num_new_tokens <= 0) return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("numNewTokens must be positive."));
+    const PamLayerSpec& l = rq.layer;
+    const int T = rq.num_new_tokens;
+    const size_t finalLen = static_cast<size_t>(rq.token_offset) + T;
+    const size_t numBlocks = (finalLen + l.block_size - 1) / l.block_size;
+    const size_t newBytes = static_cast<size_t>(T) * l.num_kv_heads * l.head_dim * pam::ioBytes(l.data_type);
+    if (!requireBuffer(c, rq.keys, "new keys", static_cast<size_t>(T) * kvBytesPerToken(l))) return -1;
+    if (!requireBuffer(c, rq.values, "new values", static_cast<size_t>(T) * kvBytesPerToken(l))) return -1;
+    if (!hostSlots && !requireBuffer(c, rq.block_table, "blockTable", numBlocks * sizeof(int32_t))) return -1;
+    if (!requireBuffer(c, rq.k_pool, "K pool", numBlocks * l.block_size * kvBytesPerToken(l))) return -1;
+    if (!requireBuffer(c, rq.v_pool, "V pool", numBlocks * l.block_size * kvBytesPerToken(l))) return -1;
+    const bool fp8 = l.data_type == PAM_DTYPE_FP8;
+    if (fp8 && (!rq.k_scale.ptr || !rq.v_scale.ptr || !cacheForScratch))
+        return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("FP8 append needs the cache's scale buffers."));
+    if (!isDevicePointer(rq.k_pool.ptr) || !isDevicePointer(rq.v_pool.ptr))
+        return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("KV pools must be device memory."));
+
+    // Slots outside the pool are skipped by the kernels; the pool size comes
+    // from the cache handle, else from the length given with the pool buffer.
+    int64_t poolSlots = INT64_MAX;
+    if (cacheForScratch) poolSlots = static_cast<int64_t>(cacheForScratch->maxBlocks) * cacheForScratch->blockSize;
+    else if (rq.k_pool.bytes != kUnknownBytes) poolSlots = static_cast<int64_t>(std::min(rq.k_pool.bytes, rq.v_pool.bytes) / std::max<size_t>(kvBytesPerToken(l), 1));
+    const double t0 = nowMs();
+    c->arena.reset(c->stream);
+    int32_t rc = withRetry(c, "appendToCacheFlat", [&]() -> cudaError_t {
+        Stager st(c);
+        const void* keys = st.in(rq.keys.ptr, newBytes);
+        const void* values = st.in(rq.values.ptr, newBytes);
+        pam::SlotSource src;
+        src.numSlots = poolSlots;
+        if (hostSlots) src.slots = static_cast<const int64_t*>(st.upload(hostSlots, sizeof(int64_t) * T));
+        else {
+            src.table = static_cast<const int32_t*>(st.in(rq.block_table.ptr, numBlocks * sizeof(int32_t)));
+            src.tokenOffset = rq.token_offset;
+        }
+        if (!st.ok()) return cudaErrorMemoryAllocation;
+        int launches = 0;
+        cudaError_t e;
+        if (fp8) {
+            Cache* k = cacheForScratch;
+            if (!k->amax) {
+                const size_t bytes = static_cast<size_t>(k->maxBlocks) * k->kvHeads * 2 * sizeof(unsigned long long);
+                e = cudaMalloc(reinterpret_cast<void**>(&k->amax), bytes);
+                if (e != cudaSuccess) return e;
+                e = cudaMemsetAsync(k->amax, 0, bytes, c->stream);
+                if (e != cudaSuccess) return e;
+                k->epoch = 0;
+            }
+            k->epoch += 1;
+            e = pam::launchReshapeAndCacheFp8(keys, values, rq.k_pool.ptr, rq.v_pool.ptr, rq.k_scale.ptr, rq.v_scale.ptr,
+                                              src, T, l.num_kv_heads, l.block_size, l.head_dim, k->amax, k->epoch,
+                                              c->stream, &launches);
+        } else {
+            e = pam::launchReshapeAndCache(keys, values, rq.k_pool.ptr, rq.v_pool.ptr, src, T, l.num_kv_heads,
+                                           l.block_size, l.head_dim, pam::elemBytes(l.data_type), c->stream, &launches);
+        }
+        c->launches += launches;
+        return e;
+    });
+    if (rc != 0) {
+        if (!c->graceful) return rc;                             // :588-596 swallows the error
+        c->clearError();
+    }
+    c->stats = PamStats{PAM_OP_APPEND, 1, T, static_cast<int32_t>(numBlocks), 0, 0, nowMs() - t0};   // :616-626
+    return 0;
+}
+
+int32_t decodeImpl(Context* c, const PamDecodeRequest& rq, int maxContext) {
+    // PagedAttentionEngine.swift:533-580; validateDecode :1916-1933
+    if (!validateLayer(c, rq.layer)) return -1;
+    if (rq.batch_size <= 0) return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("batchSize must be positive."));
+    if (rq.max_num_blocks <= 0) return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("maxNumBlocks must be positive."));
+    const PamLayerSpec& l = rq.layer;
+    const size_t B = static_cast<size_t>(rq.batch_size), NB = static_cast<size_t>(rq.max_num_blocks);
+    if (rq.block_tables.bytes != kUnknownBytes && NB > rq.block_tables.bytes / (B * sizeof(int32_t)))
+        return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("maxNumBlocks exceeds blockTables buffer capacity"));
+    if (!requireBuffer(c, rq.q, "Q", B * qBytesPerToken(l))) return -1;
+    if (!requireBuffer(c, rq.block_tables, "blockTables", B * NB * sizeof(int32_t))) return -1;
+    if (!requireBuffer(c, rq.seq_lengths, "seqLengths", B * sizeof(uint32_t))) return -1;
+    if (!requireBuffer(c, rq.output, "output", B * qBytesPerToken(l))) return -1;
+    if (!requireBuffer(c, rq.k_pool, "K pool", NB * l.block_size * kvBytesPerToken(l))) return -1;
+    if (!requireBuffer(c, rq.v_pool, "V pool", NB * l.block_size * kvBytesPerToken(l))) return -1;
+    if (l.data_type == PAM_DTYPE_FP8 && (!rq.k_scale.ptr || !rq.v_scale.ptr))
+        return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("FP8 decode needs kScaleBuffer and vScaleBuffer."));
+    if (l.head_dim > 256)
+        return c->fail(PAM_ERR_UNSUPPORTED, "Unsupported paged attention path: headDim above 256.");
+    if (!isDevicePointer(rq.k_pool.ptr) || !isDevicePointer(rq.v_pool.ptr))
+        return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("KV pools must be device memory."));
+
+    const int window = l.window_size > 0 ? l.window_size : c->defaultWindow;     // :1028
+    const size_t ioBytes = B * ioBytesPerToken(l);
+    const double t0 = nowMs();
+    c->arena.reset(c->stream);
+    size_t tempBytes = 0;
+    Stager st(c);
+    int32_t rc = withRetry(c, "decodeFlat", [&]() -> cudaError_t {
+        pam::DecodeParams p{};
+        p.q = st.in(rq.q.ptr, ioBytes);
+        p.kPool = rq.k_pool.ptr;
+        p.vPool = rq.v_pool.ptr;
+        p.tables = static_cast<const int32_t*>(st.in(rq.block_tables.ptr, B * NB * sizeof(int32_t)));
+        p.lens = static_cast<const uint32_t*>(st.in(rq.seq_lengths.ptr, B * sizeof(uint32_t)));
+        p.out = st.out(rq.output.ptr, ioBytes);
+        p.kScale = rq.k_scale.ptr;
+        p.vScale = rq.v_scale.ptr;
+        p.batch = rq.batch_size; p.heads = l.num_heads; p.kvHeads = l.num_kv_heads; p.headDim = l.head_dim;
+        p.blockSize = l.block_size; p.maxNumBlocks = rq.max_num_blocks; p.window = window; p.dtype = l.data_type;
+        p.maxContext = maxContext;
+        p.poolBlocks = poolBlocksOf(rq.k_pool, rq.v_pool, l);
+        tempBytes = pam::decodeWorkspaceBytes(p, c->smCount);
+        if (tempBytes) {
+            p.workspace = static_cast<float*>(c->arena.take(tempBytes));
+            p.workspaceBytes = tempBytes;
+            if (!p.workspace) return cudaErrorMemoryAllocation;
+        }
+        if (!st.ok()) return cudaErrorMemoryAllocation;
+        int launches = 0;
+        cudaError_t e = pam::launchDecode(p, c->smCount, c->stream, &launches);
+        c->launches += launches;
+        if (e == cudaSuccess) e = st.copyBack();
+        return e;
+    });
+    if (rc != 0) {
+        if (!c->graceful) return rc;
+        st.zeroOutputs(rq.output.ptr, rq.output.bytes != kUnknownBytes ? rq.output.bytes : ioBytes);   // :536-542
+        c->clearError();
+    }
+    if (c->async && st.hasOutputs()) cudaStreamSynchronize(c->stream);   // host results must be there on return
+    c->stats = PamStats{PAM_OP_DECODE, rq.batch_size, 0, rq.max_num_blocks, static_cast<int64_t>(tempBytes), 0, nowMs() - t0};   // :568-577
+    return 0;
+}
+
+struct PrefillSeq { int seqLen, qStart, qLen; };
+
+int32_t prefillImpl(Context* c, const PamLayerSpec& l, const PamBuffer& q, const PamBuffer& kPool, const PamBuffer& vPool,
+                    const PamBuffer& tables, const PamBuffer& output, const PamBuffer& kScale, const PamBuffer& vScale,
+                    const std::vector<PrefillSeq>& seqs, int maxNumBlocks, bool causal, const char* tableName) {
+    // PagedAttentionEngine.swift:405-528; validatePrefill :1897-1914
+    if (!validateLayer(c, l)) return -1;
+    int64_t totalRows = 0;
+    int maxQLen = 0, maxSeqLen = 0;
+    for (auto& s : seqs) {
+        if (s.seqLen <= 0) return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("seqLen must be positive."));
+        if (s.qStart < 0 || s.qLen <= 0 || s.qStart + s.qLen > s.seqLen)
+            return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("chunk rows must lie inside the sequence."));
+        totalRows += s.qLen;
+        maxQLen = std::max(maxQLen, s.qLen);
+        maxSeqLen = std::max(maxSeqLen, s.seqLen);
+    }
+    const size_t numBlocks = (static_cast<size_t>(maxSeqLen) + l.block_size - 1) / l.block_size;
+    if (static_cast<size_t>(maxNumBlocks) < numBlocks)
+        return c->fail(PAM_ERR_BUFFER_TOO_SMALL, bufferTooSmall(tableName, numBlocks * sizeof(int32_t), static_cast<size_t>(maxNumBlocks) * sizeof(int32_t)));
+    if (!requireBuffer(c, q, "Q", static_cast<size_t>(totalRows) * qBytesPerToken(l))) return -1;
+    if (!requireBuffer(c, tables, tableName, seqs.size() * static_cast<size_t>(maxNumBlocks) * sizeof(int32_t))) return -1;
+    if (!requireBuffer(c, output, "output", static_cast<size_t>(totalRows) * qBytesPerToken(l))) return -1;
+    if (!requireBuffer(c, kPool, "K pool", numBlocks * l.block_size * kvBytesPerToken(l))) return -1;
+    if (!requireBuffer(c, vPool, "V pool", numBlocks * l.block_size * kvBytesPerToken(l))) return -1;
+    if (l.data_type == PAM_DTYPE_FP8 && (!kScale.ptr || !vScale.ptr))
+        return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("FP8 prefill needs kScaleBuffer and vScaleBuffer."));
+    if (l.head_dim > 256)
+        return c->fail(PAM_ERR_UNSUPPORTED, "Unsupported paged attention path: headDim above 256.");
+    if (!isDevicePointer(kPool.ptr) || !isDevicePointer(vPool.ptr))
+        return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("KV pools must be device memory."));
+
+    const int window = l.window_size > 0 ? l.window_size : c->defaultWindow;     // :729
+    const int n = static_cast<int>(seqs.size());
+    std::vector<int32_t> meta(static_cast<size_t>(5) * n);
+    int32_t rowOff = 0;
+    for (int i = 0; i < n; ++i) {
+        meta[i] = seqs[i].seqLen;
+        meta[n + i] = seqs[i].qStart;
+        meta[2 * n + i] = seqs[i].qLen;
+        meta[3 * n + i] = rowOff;
+        meta[4 * n + i] = window > 0 ? std::max(0, seqs[i].seqLen - window) : 0;   // :802, one start for all rows
+        rowOff += seqs[i].qLen;
+    }
+    const size_t ioBytes = static_cast<size_t>(totalRows) * ioBytesPerToken(l);
+    const double t0 = nowMs();
+    c->arena.reset(c->stream);
+    bool tensorPath = false;
+    Stager st(c);
+    int32_t rc = withRetry(c, "prefill", [&]() -> cudaError_t {
+        pam::PrefillParams p{};
+        p.q = st.in(q.ptr, ioBytes);
+        p.kPool = kPool.ptr; p.vPool = vPool.ptr;
+        p.tables = static_cast<const int32_t*>(st.in(tables.ptr, static_cast<size_t>(n) * maxNumBlocks * sizeof(int32_t)));
+        p.out = st.out(output.ptr, ioBytes);
+        p.kScale = kScale.ptr; p.vScale = vScale.ptr;
+        const int32_t* dm = static_cast<const int32_t*>(st.upload(meta.data(), meta.size() * sizeof(int32_t)));
+        if (!st.ok()) return cudaErrorMemoryAllocation;
+        p.seqLens = dm; p.qStarts = dm + n; p.qLens = dm + 2 * n; p.qRowOffsets = dm + 3 * n; p.windowStarts = dm + 4 * n;
+        p.numSeqs = n; p.maxQLen = maxQLen; p.heads = l.num_heads; p.kvHeads = l.num_kv_heads; p.headDim = l.head_dim;
+        p.blockSize = l.block_size; p.maxNumBlocks = maxNumBlocks; p.causal = causal ? 1 : 0; p.dtype = l.data_type;
+        p.poolBlocks = poolBlocksOf(kPool, vPool, l);
+        int launches = 0;
+        cudaError_t e = pam::launchPrefill(p, c->smCount, c->stream, &launches, &tensorPath);
+        c->launches += launches;
+        if (e == cudaSuccess) e = st.copyBack();
+        // `meta` is read by an async copy from pageable memory, which the
+        // runtime stages before returning; nothing else outlives this scope.
+        return e;
+    });
+    if (rc != 0) {
+        if (!c->graceful) return rc;
+        st.zeroOutputs(output.ptr, output.bytes != kUnknownBytes ? output.bytes : ioBytes);       // :408-414
+        c->clearError();
+    }
+    if (c->async && st.hasOutputs()) cudaStreamSynchronize(c->stream);
+    c->stats = PamStats{tensorPath ? PAM_OP_PREFILL_MMA : PAM_OP_PREFILL_TILED, 1, maxSeqLen,
+                        static_cast<int32_t>(numBlocks), 0, tensorPath ? 0 : 1, nowMs() - t0};      // :511-527
+    return 0;
+}
+
+PamBuffer buf(const void* p, size_t bytes = kUnknownBytes) { return PamBuffer{const_cast<void*>(p), bytes}; }
+
+PamLayerSpec layerOf(const Cache* k, int numHeads) {
+    return PamLayerSpec{k->headDim, numHeads, k->kvHeads, k->blockSize, k->dtype, 0};
+}
+
+Cache* createCache(Context* c, int32_t maxBlocks, int32_t blockSize, int32_t headDim, int32_t kvHeads, int32_t dtype) {
+    Cache* k = new Cache(maxBlocks, blockSize);
+    k->device = c->device; k->dtype = dtype; k->headDim = headDim; k->kvHeads = kvHeads;
+    k->poolBytes = static_cast<size_t>(maxBlocks) * k->blockBytes();            // KVCacheManager.swift:91-92
+    cudaError_t e = cudaMalloc(&k->kPool, k->poolBytes);
+    if (e == cudaSuccess) e = cudaMalloc(&k->vPool, k->poolBytes);
+    if (e == cudaSuccess) e = cudaMemsetAsync(k->kPool, 0, k->poolBytes, c->stream);
+    if (e == cudaSuccess) e = cudaMemsetAsync(k->vPool, 0, k->poolBytes, c->stream);
+    if (e == cudaSuccess && dtype == PAM_DTYPE_FP8) {
+        k->scaleBytes = static_cast<size_t>(maxBlocks) * kvHeads * 2;
+        e = cudaMalloc(&k->kScale, k->scaleBytes);
+        if (e == cudaSuccess) e = cudaMalloc(&k->vScale, k->scaleBytes);
+        if (e == cudaSuccess) e = cudaMemsetAsync(k->kScale, 0, k->scaleBytes, c->stream);   // scales start at zero
+        if (e == cudaSuccess) e = cudaMemsetAsync(k->vScale, 0, k->scaleBytes, c->stream);
+    }
+    if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        c->fail(PAM_ERR_COMMAND_ENCODING, "Metal command encoding failed: Failed to allocate KV pool buffers");   // KVCacheManager.swift:96
+        delete k;
+        return nullptr;
+    }
+    return k;
+}
+
+}  // namespace
+
+// ======================================================================= C ABI
+
+extern "C" {
+
+int32_t pamc_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) { cudaGetLastError(); return 0; }
+    return n;
+}
+
+void* pamc_create_context_on(int32_t device) {
+    int n = pamc_device_count();
+    if (device < 0 || device >= n) return nullptr;                // deviceInitializationFailed
+    if (cudaSetDevice(device) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    Context* c = new Context();
+    c->device = device;
+    cudaDeviceProp prop{};
+    if (cudaGetDeviceProperties(&prop, device) == cudaSuccess) c->smCount = prop.multiProcessorCount;
+    if (cudaStreamCreateWithFlags(&c->ownStream, cudaStreamNonBlocking) != cudaSuccess) {
+        cudaGetLastError();
+        delete c;
+        return nullptr;
+    }
+    c->stream = c->ownStream;
+    return c;
+}
+
+void* pamc_create_host_context(void) {
+    Context* c = new Context();
+    c->device = -1;
+    return c;
+}
+
+void* pam_create_context(void) {
+    int dev = 0;
+    if (pamc_device_count() <= 0) return nullptr;
+    if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    return pamc_create_context_on(dev);
+}
+
+void pam_destroy_context(void* ctx) {
+    if (!ctx) return;
+    Context* c = asCtx(ctx);
+    if (c->device < 0) { delete c; return; }
+    cudaSetDevice(c->device);
+    cudaStreamSynchronize(c->stream);
+    c->arena.release();
+    if (c->ownStream) cudaStreamDestroy(c->ownStream);
+    delete c;
+}
+
+const char* pam_last_error(void* ctx) {
+    if (!ctx) return nullptr;
+    Context* c = asCtx(ctx);
+    return c->hasError ? c->lastError.c_str() : nullptr;
+}
+
+int32_t pamc_last_error_code(void* ctx) { return ctx ? asCtx(ctx)->lastCode : PAM_ERR_NULL_HANDLE; }
+
+void* pam_create_cache(void* ctx, int32_t max_blocks, int32_t block_size, int32_t head_dim, int32_t num_kv_heads,
+                       int32_t data_type) {
+    if (!ctx) return nullptr;
+    Context* c = asCtx(ctx);
+    std::lock_guard<std::mutex> g(c->mu);
+    DeviceGuard dg(c->device);
+    if (c->device < 0) { noGpu(c); return nullptr; }
+    PamLayerSpec l{head_dim, num_kv_heads, num_kv_heads, block_size, data_type, 0};   // CABI.swift:107-114
+    if (!validateLayer(c, l)) return nullptr;
+    if (max_blocks <= 0) { c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("maxBlocks must be positive")); return nullptr; }
+    Cache* k = createCache(c, max_blocks, block_size, head_dim, num_kv_heads, data_type);
+    if (k) c->clearError();
+    return k;
+}
+
+void* pamc_cache_create_bookkeeping(int32_t max_blocks, int32_t block_size) {
+    if (max_blocks <= 0 || block_size <= 0) return nullptr;
+    Cache* k = new Cache(max_blocks, block_size);
+    k->bookkeeping = true;
+    return k;
+}
+
+void pam_destroy_cache(void* cache) { delete asCache(cache); }
+
+int32_t pam_reserve_sequence(void* ctx, void* cache, int64_t id) {
+    if (!ctx || !cache) return -1;
+    Context* c = asCtx(ctx);
+    std::lock_guard<std::mutex> g(c->mu);
+    KVResult r = asCache(cache)->mgr.allocateSequence(id);
+    if (!r.ok()) return kvFail(c, r);
+    c->clearError();
+    return 0;
+}
+
+int32_t pamc_cache_append_tokens(void* ctx, void* cache, int64_t id, int32_t count, const uint64_t* hashes,
+                                 int32_t num_hashes) {
+    if (!ctx || !cache) return -1;
+    Context* c = asCtx(ctx);
+    Cache* k = asCache(cache);
+    std::lock_guard<std::mutex> g(c->mu);
+    std::vector<std::pair<int32_t, int32_t>> cow;
+    KVResult r = k->mgr.appendTokens(id, count, hashes, hashes ? num_hashes : 0, &cow);
+    {
+        std::lock_guard<std::mutex> gk(k->mu);
+        k->cowLog.insert(k->cowLog.end(), cow.begin(), cow.end());
+    }
+    if (!cow.empty() && !k->bookkeeping) {
+        DeviceGuard dg(c->device);
+        if (c->device < 0) return noGpu(c);
+        c->arena.reset(c->stream);
+        if (runCopies(c, k, cow) != 0) return -1;
+    }
+    if (!r.ok()) return kvFail(c, r);
+    c->clearError();
+    return 0;
+}
+
+int32_t pam_append_tokens(void* ctx, void* cache, int64_t id, int32_t count) {
+    return pamc_cache_append_tokens(ctx, cache, id, count, nullptr, 0);
+}
+
+int32_t pamc_cache_ensure_exclusive(void* ctx, void* cache, int64_t id, int32_t logical_block) {
+    if (!ctx || !cache) return -1;
+    Context* c = asCtx(ctx);
+    Cache* k = asCache(cache);
+    std::lock_guard<std::mutex> g(c->mu);
+    std::vector<std::pair<int32_t, int32_t>> cow;
+    KVResult r = k->mgr.ensureExclusiveAccess(id, logical_block, &cow);
+    {
+        std::lock_guard<std::mutex> gk(k->mu);
+        k->cowLog.insert(k->cowLog.end(), cow.begin(), cow.end());
+    }
+    if (!cow.empty() && !k->bookkeeping) {
+        DeviceGuard dg(c->device);
+        if (c->device < 0) return noGpu(c);
+        c->arena.reset(c->stream);
+        if (runCopies(c, k, cow) != 0) return -1;
+    }
+    if (!r.ok()) return kvFail(c, r);
+    c->clearError();
+    return 0;
+}
+
+void pamc_cache_register_block_hash(void* cache, uint64_t hash, int32_t physical_block) {
+    if (cache) asCache(cache)->mgr.registerBlockHash(hash, physical_block);
+}
+
+void pam_free_sequence(void* cache, int64_t id) {
+    if (cache) asCache(cache)->mgr.freeSequence(id);
+}
+
+int32_t pam_available_blocks(void* cache) { return cache ? asCache(cache)->mgr.availableBlocks() : -1; }
+
+int32_t pam_sequence_length(void* ctx, void* cache, int64_t id) {
+    if (!ctx || !cache) return -1;
+    Context* c = asCtx(ctx);
+    std::lock_guard<std::mutex> g(c->mu);
+    int64_t len = 0;
+    KVResult r = asCache(cache)->mgr.sequenceLength(id, &len);
+    if (!r.ok()) return kvFail(c, r);
+    c->clearError();
+    return static_cast<int32_t>(len);
+}
+
+int32_t pamc_cache_block_table(void* ctx, void* cache, int64_t id, int32_t* out, int32_t capacity) {
+    if (!ctx || !cache) return -1;
+    Context* c = asCtx(ctx);
+    std::lock_guard<std::mutex> g(c->mu);
+    std::vector<int32_t> t;
+    KVResult r = asCache(cache)->mgr.blockTable(id, &t);
+    if (!r.ok()) return kvFail(c, r);
+    if (out) for (int i = 0; i < capacity && i < static_cast<int>(t.size()); ++i) out[i] = t[static_cast<size_t>(i)];
+    c->clearError();
+    return static_cast<int32_t>(t.size());
+}
+
+int32_t pamc_cache_num_blocks(void* ctx, void* cache, int64_t id) {
+    return pamc_cache_block_table(ctx, cache, id, nullptr, 0);
+}
+
+int32_t pamc_cache_active_sequences(void* cache) { return cache ? asCache(cache)->mgr.activeSequences() : -1; }
+
+int32_t pamc_cache_set_eviction_policy(void* cache, int32_t policy) {
+    if (!cache || policy < 0 || policy > 2) return -1;
+    asCache(cache)->mgr.setPolicy(policy);
+    return 0;
+}
+
+int32_t pamc_cache_memory_stats(void* cache, PamMemoryStats* out) {
+    if (!cache || !out) return -1;
+    Cache* k = asCache(cache);
+    pam::MemoryStats s = k->mgr.stats();
+    const int64_t bytesPerBlock = k->bookkeeping ? 0 : static_cast<int64_t>(k->blockBytes()) * 2;   // KVCacheManager.swift:357
+    out->total_blocks = s.totalBlocks; out->used_blocks = s.usedBlocks; out->free_blocks = s.freeBlocks;
+    out->active_sequences = s.activeSequences;
+    out->total_memory_bytes = s.totalBlocks * bytesPerBlock; out->used_memory_bytes = s.usedBlocks * bytesPerBlock;
+    out->partially_filled_blocks = s.partiallyFilledBlocks; out->fragmentation_ratio = s.fragmentationRatio;
+    out->prefix_cache_hits = s.prefixCacheHits; out->prefix_cache_entries = s.prefixCacheEntries;
+    out->shared_blocks = s.sharedBlocks; out->eviction_policy = s.policy;
+    return 0;
+}
+
+int32_t pamc_cache_pools(void* cache, void** k_pool, void** v_pool, void** k_scale, void** v_scale,
+                         size_t* pool_bytes, size_t* scale_bytes) {
+    if (!cache) return -1;
+    Cache* k = asCache(cache);
+    if (k_pool) *k_pool = k->kPool;
+    if (v_pool) *v_pool = k->vPool;
+    if (k_scale) *k_scale = k->kScale;
+    if (v_scale) *v_scale = k->vScale;
+    if (pool_bytes) *pool_bytes = k->poolBytes;
+    if (scale_bytes) *scale_bytes = k->scaleBytes;
+    return 0;
+}
+
+int32_t pamc_cache_drain_cow_log(void* cache, int32_t* out_pairs, int32_t capacity) {
+    if (!cache) return -1;
+    Cache* k = asCache(cache);
+    std::lock_guard<std::mutex> g(k->mu);
+    int n = static_cast<int>(std::min<size_t>(k->cowLog.size(), static_cast<size_t>(std::max(capacity, 0))));
+    for (int i = 0; i < n; ++i) {
+        out_pairs[2 * i] = k->cowLog[static_cast<size_t>(i)].first;
+        out_pairs[2 * i + 1] = k->cowLog[static_cast<size_t>(i)].second;
+    }
+    k->cowLog.erase(k->cowLog.begin(), k->cowLog.begin() + n);
+    return n;
+}
+
+static int32_t buildBatchTables(Context* c, Cache* k, const int64_t* ids, int32_t n, int32_t maxNumBlocks,
+                                std::vector<int32_t>* tables, std::vector<uint32_t>* lens, int* maxLen) {
+    tables->assign(static_cast<size_t>(n) * maxNumBlocks, 0);   // zero padding, CABI.swift:360-363
+    lens->assign(static_cast<size_t>(n), 0);
+    if (maxLen) *maxLen = 0;
+    std::vector<int32_t> t;
+    for (int i = 0; i < n; ++i) {
+        KVResult r = k->mgr.blockTable(ids[i], &t);
+        if (!r.ok()) return kvFail(c, r);
+        if (static_cast<int>(t.size()) > maxNumBlocks)           // KVCacheManager.swift:675-677
+            return c->fail(PAM_ERR_KV_INVALID_REQUEST,
+                           "KVCacheError.invalidRequest(\"sequence " + std::to_string(ids[i]) + " requires " +
+                               std::to_string(t.size()) + " blocks, maxSequenceBlocks is " + std::to_string(maxNumBlocks) + "\")");
+        std::copy(t.begin(), t.end(), tables->begin() + static_cast<std::ptrdiff_t>(i) * maxNumBlocks);
+        int64_t len = 0;
+        k->mgr.sequenceLength(ids[i], &len);
+        (*lens)[static_cast<size_t>(i)] = static_cast<uint32_t>(len);
+        if (maxLen) *maxLen = std::max(*maxLen, static_cast<int>(len));
+    }
+    return 0;
+}
+
+int32_t pamc_cache_batch_tables(void* ctx, void* cache, const int64_t* ids, int32_t n, int32_t max_num_blocks,
+                                int32_t* tables, uint32_t* lens) {
+    if (!ctx || !cache || !ids || n < 0 || max_num_blocks <= 0) return -1;
+    Context* c = asCtx(ctx);
+    std::lock_guard<std::mutex> g(c->mu);
+    std::vector<int32_t> t;
+    std::vector<uint32_t> l;
+    if (buildBatchTables(c, asCache(cache), ids, n, max_num_blocks, &t, &l, nullptr) != 0) return -1;
+    DeviceGuard dg(c->device);
+    auto put = [&](void* dst, const void* src, size_t bytes) -> bool {
+        if (!dst || bytes == 0) return true;
+        if (c->device < 0 || !isDevicePointer(dst)) { std::memcpy(dst, src, bytes); return true; }
+        return cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, c->stream) == cudaSuccess &&
+               cudaStreamSynchronize(c->stream) == cudaSuccess;
+    };
+    if (!put(tables, t.data(), t.size() * sizeof(int32_t)) || !put(lens, l.data(), l.size() * sizeof(uint32_t)))
+        return c->fail(PAM_ERR_COMMAND_EXECUTION, commandExecutionFailed("copy of batch tables failed"));
+    c->clearError();
+    return 0;
+}
+
+int32_t pamc_cache_slot_mapping(void* ctx, void* cache, int64_t id, int32_t token_offset, int32_t num_tokens,
+                                int64_t* out) {
+    if (!ctx || !cache || !out) return -1;
+    Context* c = asCtx(ctx);
+    Cache* k = asCache(cache);
+    std::lock_guard<std::mutex> g(c->mu);
+    std::vector<int32_t> t;
+    KVResult r = k->mgr.blockTable(id, &t);
+    if (!r.ok()) return kvFail(c, r);
+    const int bs = k->blockSize;
+    if (token_offset < 0 || num_tokens < 0 ||
+        (static_cast<int64_t>(token_offset) + num_tokens + bs - 1) / bs > static_cast<int64_t>(t.size()))
+        return c->fail(PAM_ERR_KV_INVALID_REQUEST, "KVCacheError.invalidRequest(\"tokens lie outside the block table\")");
+    for (int i = 0; i < num_tokens; ++i) {
+        const int pos = token_offset + i;                         // kernels.metal:1823-1827
+        out[i] = static_cast<int64_t>(t[static_cast<size_t>(pos / bs)]) * bs + pos % bs;
+    }
+    c->clearError();
+    return 0;
+}
+
+// ------------------------------------------------------------------ engine knobs
+
+int32_t pamc_set_stream(void* ctx, void* cuda_stream) {
+    if (!ctx) return -1;
+    Context* c = asCtx(ctx);
+    std::lock_guard<std::mutex> g(c->mu);
+    if (c->device < 0) return noGpu(c);
+    cudaStreamSynchronize(c->stream);
+    c->stream = cuda_stream ? static_cast<cudaStream_t>(cuda_stream) : c->ownStream;
+    return 0;
+}
+int32_t pamc_set_async(void* ctx, int32_t enabled) { if (!ctx) return -1; asCtx(ctx)->async = enabled != 0; return 0; }
+int32_t pamc_synchronize(void* ctx) {
+    if (!ctx) return -1;
+    Context* c = asCtx(ctx);
+    DeviceGuard dg(c->device);
+    if (c->device < 0) return noGpu(c);
+    cudaError_t e = cudaStreamSynchronize(c->stream);
+    if (e != cudaSuccess) { cudaGetLastError(); return c->fail(PAM_ERR_COMMAND_EXECUTION, commandExecutionFailed(cudaGetErrorString(e))); }
+    return 0;
+}
+int32_t pamc_set_max_retries(void* ctx, int32_t n) { if (!ctx || n < 0) return -1; asCtx(ctx)->maxRetries = n; return 0; }
+int32_t pamc_set_graceful_degradation(void* ctx, int32_t on) { if (!ctx) return -1; asCtx(ctx)->graceful = on != 0; return 0; }
+int32_t pamc_set_split_threshold(void* ctx, int32_t t) { if (!ctx) return -1; asCtx(ctx)->splitThreshold = t; return 0; }
+int32_t pamc_set_default_window(void* ctx, int32_t t) { if (!ctx || t < 0) return -1; asCtx(ctx)->defaultWindow = t; return 0; }
+int32_t pamc_set_default_chunk(void* ctx, int32_t t) { if (!ctx || t < 0) return -1; asCtx(ctx)->defaultChunk = t; return 0; }
+int32_t pamc_inject_launch_failures(void* ctx, int32_t n) { if (!ctx || n < 0) return -1; asCtx(ctx)->injectFailures = n; return 0; }
+int64_t pamc_kernel_launches(void* ctx) { return ctx ? asCtx(ctx)->launches : -1; }
+
+int32_t pamc_last_stats(void* ctx, PamStats* out) {
+    if (!ctx || !out) return -1;
+    Context* c = asCtx(ctx);
+    std::lock_guard<std::mutex> g(c->mu);
+    *out = c->stats;
+    return 0;
+}
+
+int64_t pamc_recommended_max_blocks(void* ctx, int32_t block_size, int32_t num_kv_heads, int32_t head_dim,
+                                    int32_t data_type, float memory_fraction, int32_t layer_count) {
+    if (!ctx || !validDtype(data_type)) return -1;
+    Context* c = asCtx(ctx);
+    DeviceGuard dg(c->device);
+    if (c->device < 0) return noGpu(c);
+    size_t freeB = 0, totalB = 0;
+    if (cudaMemGetInfo(&freeB, &totalB) != cudaSuccess) { cudaGetLastError(); return -1; }
+    // PagedAttentionEngine.swift:201-217: fraction * budget / (bytes per block, K and V, all layers), at least 1
+    const double perBlock = static_cast<double>(block_size) * num_kv_heads * head_dim * pam::elemBytes(data_type) * 2.0 *
+                            std::max(layer_count, 1);
+    if (perBlock <= 0) return 1;
+    const int64_t n = static_cast<int64_t>(static_cast<double>(memory_fraction) * static_cast<double>(freeB) / perBlock);
+    return std::max<int64_t>(n, 1);
+}
+
+void* pamc_buffer_alloc(void* ctx, size_t bytes) {
+    if (!ctx) return nullptr;
+    Context* c = asCtx(ctx);
+    DeviceGuard dg(c->device);
+    if (c->device < 0) { noGpu(c); return nullptr; }
+    void* p = nullptr;
+    if (cudaMalloc(&p, std::max<size_t>(bytes, 1)) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    return p;
+}
+void pamc_buffer_free(void* ctx, void* ptr) {
+    if (!ctx || !ptr) return;
+    DeviceGuard dg(asCtx(ctx)->device);
+    cudaFree(ptr);
+}
+int32_t pamc_memcpy(void* ctx, void* dst, const void* src, size_t bytes, int32_t kind) {
+    if (!ctx) return -1;
+    Context* c = asCtx(ctx);
+    DeviceGuard dg(c->device);
+    if (c->device < 0) return noGpu(c);
+    cudaMemcpyKind k = kind == 0 ? cudaMemcpyHostToDevice : kind == 1 ? cudaMemcpyDeviceToHost : cudaMemcpyDeviceToDevice;
+    cudaError_t e = cudaMemcpyAsync(dst, src, bytes, k, c->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+    if (e != cudaSuccess) { cudaGetLastError(); return c->fail(PAM_ERR_COMMAND_EXECUTION, commandExecutionFailed(cudaGetErrorString(e))); }
+    return 0;
+}
+
+// ------------------------------------------------------------------ operations
+
+int32_t pamc_append_to_cache(void* ctx, const PamAppendRequest* request) {
+    if (!ctx || !request) return -1;
+    Context* c = asCtx(ctx);
+    std::lock_guard<std::mutex> g(c->mu);
+    DeviceGuard dg(c->device);
+    if (c->device < 0) return noGpu(c);
+    if (request->layer.data_type == PAM_DTYPE_FP8)
+        return c->fail(PAM_ERR_UNSUPPORTED, "Unsupported paged attention path: FP8 append goes through a cache handle (pam_append_kv or pamc_reshape_and_cache), which owns the absmax scratch.");
+    int32_t rc = appendImpl(c, *request, nullptr, nullptr);
+    if (rc == 0) c->clearError();
+    return rc;
+}
+
+int32_t pam_append_kv(void* ctx, void* cache, int64_t id, void* keys, void* values, int32_t token_offset,
+                      int32_t num_new_tokens, int32_t num_heads) {
+    if (!ctx || !cache || !keys || !values) return -1;           // CABI.swift:214-219
+    Context* c = asCtx(ctx);
+    Cache* k = asCache(cache);
+    std::lock_guard<std::mutex> g(c->mu);
+    DeviceGuard dg(c->device);
+    if (c->device < 0) return noGpu(c);
+    if (k->bookkeeping) return c->fail(PAM_ERR_INVALID_STATE, "Invalid engine state: cache has no pools");
+    std::vector<int32_t> table;
+    KVResult r = k->mgr.blockTable(id, &table);
+    if (!r.ok()) return kvFail(c, r);
+    PamAppendRequest rq{};
+    rq.keys = buf(keys); rq.values = buf(values);
+    rq.k_pool = buf(k->kPool, k->poolBytes); rq.v_pool = buf(k->vPool, k->poolBytes);
+    // getBlockTableBuffer pads an empty table to one entry (KVCacheManager.swift:310)
+    rq.block_table = buf(table.data(), std::max<size_t>(table.size(), 1) * sizeof(int32_t));
+    rq.token_offset = token_offset; rq.num_new_tokens = num_new_tokens;
+    rq.layer = layerOf(k, num_heads);
+    rq.k_scale = buf(k->kScale, k->scaleBytes); rq.v_scale = buf(k->vScale, k->scaleBytes);
+    // The table is known on the host: derive the slots here after the same checks.
+    std::vector<int64_t> slots;
+    if (token_offset >= 0 && num_new_tokens > 0) {
+        const size_t need = (static_cast<size_t>(token_offset) + num_new_tokens + k->blockSize - 1) / k->blockSize;
+        if (need * sizeof(int32_t) > rq.block_table.bytes)
+            return c->fail(PAM_ERR_BUFFER_TOO_SMALL, bufferTooSmall("blockTable", need * sizeof(int32_t), rq.block_table.bytes));
+        slots.resize(static_cast<size_t>(num_new_tokens));
+        for (int i = 0; i < num_new_tokens; ++i) {
+            const int pos = token_offset + i;
+            slots[static_cast<size_t>(i)] = static_cast<int64_t>(table[static_cast<size_t>(pos / k->blockSize)]) * k->blockSize + pos % k->blockSize;
+        }
+    }
+    int32_t rc = appendImpl(c, rq, k, slots.empty() ? nullptr : slots.data());
+    if (rc == 0) c->clearError();
+    return rc;
+}
+
+int32_t pamc_reshape_and_cache(void* ctx, void* cache, const void* keys, const void* values,
+                               const int64_t* slot_mapping, int32_t num_tokens) {
+    if (!ctx || !cache || !keys || !values || !slot_mapping) return -1;
+    Context* c = asCtx(ctx);
+    Cache* k = asCache(cache);
+    std::lock_guard<std::mutex> g(c->mu);
+    DeviceGuard dg(c->device);
+    if (c->device < 0) return noGpu(c);
+    if (k->bookkeeping) return c->fail(PAM_ERR_INVALID_STATE, "Invalid engine state: cache has no pools");
+    if (num_tokens <= 0) return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("numNewTokens must be positive."));
+    PamAppendRequest rq{};
+    rq.keys = buf(keys); rq.values = buf(values);
+    rq.k_pool = buf(k->kPool, k->poolBytes); rq.v_pool = buf(k->vPool, k->poolBytes);
+    rq.block_table = buf(nullptr, 0);
+    rq.token_offset = 0; rq.num_new_tokens = num_tokens;
+    rq.layer = layerOf(k, k->kvHeads);
+    rq.k_scale = buf(k->kScale, k->scaleBytes); rq.v_scale = buf(k->vScale, k->scaleBytes);
+    std::vector<int64_t> hostSlots;
+    const int64_t* slots = slot_mapping;
+    if (isDevicePointer(slot_mapping)) {
+        hostSlots.resize(static_cast<size_t>(num_tokens));
+        if (cudaMemcpyAsync(hostSlots.data(), slot_mapping, sizeof(int64_t) * num_tokens, cudaMemcpyDeviceToHost, c->stream) != cudaSuccess ||
+            cudaStreamSynchronize(c->stream) != cudaSuccess) {
+            cudaGetLastError();
+            return c->fail(PAM_ERR_COMMAND_EXECUTION, commandExecutionFailed("slot mapping copy failed"));
+        }
+        slots = hostSlots.data();
+    }
+    const int64_t poolSlots = static_cast<int64_t>(k->maxBlocks) * k->blockSize;
+    for (int i = 0; i < num_tokens; ++i)
+        if (slots[i] < 0 || slots[i] >= poolSlots)
+            return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("slot " + std::to_string(slots[i]) + " lies outside the pool"));
+    // appendImpl's pool lower bound is counted from token_offset + tokens; the
+    // slots were checked against the pool above, so keep that bound trivial.
+    rq.num_new_tokens = num_tokens;
+    PamAppendRequest small = rq;
+    small.k_pool.bytes = kUnknownBytes; small.v_pool.bytes = kUnknownBytes;
+    int32_t rc = appendImpl(c, small, k, slots);
+    if (rc == 0) c->clearError();
+    return rc;
+}
+
+int32_t pamc_copy_blocks(void* ctx, void* cache, const int32_t* src, const int32_t* dst, int32_t n) {
+    if (!ctx || !cache || (n > 0 && (!src || !dst))) return -1;
+    Context* c = asCtx(ctx);
+    Cache* k = asCache(cache);
+    std::lock_guard<std::mutex> g(c->mu);
+    DeviceGuard dg(c->device);
+    if (c->device < 0) return noGpu(c);
+    if (k->bookkeeping) return c->fail(PAM_ERR_INVALID_STATE, "Invalid engine state: cache has no pools");
+    std::vector<std::pair<int32_t, int32_t>> pairs;
+    for (int i = 0; i < n; ++i) {
+        if (src[i] < 0 || src[i] >= k->maxBlocks || dst[i] < 0 || dst[i] >= k->maxBlocks)
+            return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("block index outside the pool"));
+        pairs.emplace_back(src[i], dst[i]);
+    }
+    c->arena.reset(c->stream);
+    int32_t rc = runCopies(c, k, pairs);
+    if (rc == 0) c->clearError();
+    return rc;
+}
+
+int32_t pamc_decode(void* ctx, const PamDecodeRequest* request) {
+    if (!ctx || !request) return -1;
+    Context* c = asCtx(ctx);
+    std::lock_guard<std::mutex> g(c->mu);
+    DeviceGuard dg(c->device);
+    if (c->device < 0) return noGpu(c);
+    int32_t rc = decodeImpl(c, *request, 0);
+    if (rc == 0) c->clearError();
+    return rc;
+}
+
+int32_t pam_decode(void* ctx, void* cache, const int64_t* batch_ids, int32_t batch_size, void* q, void* out,
+                   int32_t num_heads) {
+    if (!ctx || !cache || !batch_ids || !q || !out) return -1;   // CABI.swift:299-305
+    Context* c = asCtx(ctx);
+    Cache* k = asCache(cache);
+    std::lock_guard<std::mutex> g(c->mu);
+    DeviceGuard dg(c->device);
+    if (c->device < 0) return noGpu(c);
+    if (k->bookkeeping) return c->fail(PAM_ERR_INVALID_STATE, "Invalid engine state: cache has no pools");
+    if (batch_size <= 0) return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("batchSize must be positive."));
+    int maxNumBlocks = 1;                                         // CABI.swift:308
+    std::vector<int32_t> t;
+    for (int i = 0; i < batch_size; ++i) {
+        KVResult r = k->mgr.blockTable(batch_ids[i], &t);
+        if (!r.ok()) return kvFail(c, r);
+        maxNumBlocks = std::max(maxNumBlocks, static_cast<int>(t.size()));
+    }
+    std::vector<int32_t> tables;
+    std::vector<uint32_t> lens;
+    int maxLen = 0;
+    if (buildBatchTables(c, k, batch_ids, batch_size, maxNumBlocks, &tables, &lens, &maxLen) != 0) return -1;
+    PamDecodeRequest rq{};
+    rq.q = buf(q); rq.output = buf(out);
+    rq.k_pool = buf(k->kPool, k->poolBytes); rq.v_pool = buf(k->vPool, k->poolBytes);
+    rq.block_tables = buf(tables.data(), tables.size() * sizeof(int32_t));
+    rq.seq_lengths = buf(lens.data(), lens.size() * sizeof(uint32_t));
+    rq.batch_size = batch_size; rq.max_num_blocks = maxNumBlocks;
+    rq.layer = layerOf(k, num_heads);
+    rq.k_scale = buf(k->kScale, k->scaleBytes); rq.v_scale = buf(k->vScale, k->scaleBytes);
+    // validateDecode's pool bound uses maxNumBlocks (a lower bound, PagedAttentionEngine.swift:1931)
+    int32_t rc = decodeImpl(c, rq, std::max(maxLen, 1));
+    if (rc == 0) {
+        // tables/lens are host vectors read by async copies: they must be consumed before they die
+        if (c->async) cudaStreamSynchronize(c->stream);
+        c->clearError();
+    }
+    return rc;
+}
+
+int32_t pamc_prefill(void* ctx, const PamPrefillRequest* request, int32_t chunk_size) {
+    if (!ctx || !request) return -1;
+    Context* c = asCtx(ctx);
+    std::lock_guard<std::mutex> g(c->mu);
+    DeviceGuard dg(c->device);
+    if (c->device < 0) return noGpu(c);
+    const PamPrefillRequest& rq = *request;
+    if (rq.seq_len <= 0) return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("seqLen must be positive."));
+    const int qLen = rq.q_len > 0 ? rq.q_len : rq.seq_len;
+    const int qStart = rq.q_len > 0 ? rq.q_start : 0;
+    const int chunk = chunk_size > 0 ? chunk_size : c->defaultChunk;            // PagedAttentionEngine.swift:730
+    const int maxNumBlocks = rq.block_table.bytes != kUnknownBytes
+                                 ? static_cast<int>(std::min<size_t>(rq.block_table.bytes / sizeof(int32_t), 1u << 30))
+                                 : (rq.seq_len + std::max(rq.layer.block_size, 1) - 1) / std::max(rq.layer.block_size, 1);
+    int32_t rc = 0;
+    if (chunk > 0 && qLen > chunk && validDtype(rq.layer.data_type) && rq.layer.num_heads > 0 && rq.layer.head_dim > 0) {
+        // PagedAttentionEngine.swift:740-756, each row computed once.
+        const size_t rowBytes = ioBytesPerToken(rq.layer);
+        for (int cs = 0; cs < qLen && rc == 0; cs += chunk) {
+            const int n = std::min(chunk, qLen - cs);
+            PamBuffer q = rq.q, o = rq.output;
+            q.ptr = static_cast<char*>(q.ptr) + static_cast<size_t>(cs) * rowBytes;
+            o.ptr = static_cast<char*>(o.ptr) + static_cast<size_t>(cs) * rowBytes;
+            if (q.bytes != kUnknownBytes) q.bytes = q.bytes > static_cast<size_t>(cs) * rowBytes ? q.bytes - static_cast<size_t>(cs) * rowBytes : 0;
+            if (o.bytes != kUnknownBytes) o.bytes = o.bytes > static_cast<size_t>(cs) * rowBytes ? o.bytes - static_cast<size_t>(cs) * rowBytes : 0;
+            rc = prefillImpl(c, rq.layer, q, rq.k_pool, rq.v_pool, rq.block_table, o, rq.k_scale, rq.v_scale,
+                             {PrefillSeq{rq.seq_len, qStart + cs, n}}, maxNumBlocks, rq.causal != 0, "blockTable");
+        }
+    } else {
+        rc = prefillImpl(c, rq.layer, rq.q, rq.k_pool, rq.v_pool, rq.block_table, rq.output, rq.k_scale, rq.v_scale,
+                         {PrefillSeq{rq.seq_len, qStart, qLen}}, maxNumBlocks, rq.causal != 0, "blockTable");
+    }
+    if (rc == 0) c->clearError();
+    return rc;
+}
+
+int32_t pamc_prefill_batch(void* ctx, const PamBatchPrefillRequest* request) {
+    if (!ctx || !request) return -1;
+    Context* c = asCtx(ctx);
+    std::lock_guard<std::mutex> g(c->mu);
+    DeviceGuard dg(c->device);
+    if (c->device < 0) return noGpu(c);
+    const PamBatchPrefillRequest& rq = *request;
+    if (rq.num_sequences <= 0 || !rq.seq_lens || !rq.q_starts || !rq.q_lens)
+        return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("batchSize must be positive."));
+    std::vector<PrefillSeq> seqs;
+    for (int i = 0; i < rq.num_sequences; ++i) seqs.push_back({rq.seq_lens[i], rq.q_starts[i], rq.q_lens[i]});
+    int32_t rc = prefillImpl(c, rq.layer, rq.q, rq.k_pool, rq.v_pool, rq.block_tables, rq.output, rq.k_scale, rq.v_scale,
+                             seqs, rq.max_num_blocks, rq.causal != 0, "blockTables");
+    if (rc == 0) c->clearError();
+    return rc;
+}
+
+int32_t pam_prefill(void* ctx, void* cache, int64_t id, void* q, void* out, int32_t seq_len, int32_t num_heads,
+                    bool causal) {
+    if (!ctx || !cache || !q || !out) return -1;                 // CABI.swift:257-262
+    Context* c = asCtx(ctx);
+    Cache* k = asCache(cache);
+    std::vector<int32_t> table;
+    {
+        std::lock_guard<std::mutex> g(c->mu);
+        if (k->bookkeeping) return c->fail(PAM_ERR_INVALID_STATE, "Invalid engine state: cache has no pools");
+        KVResult r = k->mgr.blockTable(id, &table);
+        if (!r.ok()) return kvFail(c, r);
+    }
+    if (table.empty()) table.push_back(0);                        // KVCacheManager.swift:310
+    PamPrefillRequest rq{};
+    rq.q = buf(q); rq.output = buf(out);
+    rq.k_pool = buf(k->kPool, k->poolBytes); rq.v_pool = buf(k->vPool, k->poolBytes);
+    rq.block_table = buf(table.data(), table.size() * sizeof(int32_t));
+    rq.seq_len = seq_len; rq.layer = layerOf(k, num_heads); rq.causal = causal ? 1 : 0;
+    rq.k_scale = buf(k->kScale, k->scaleBytes); rq.v_scale = buf(k->vScale, k->scaleBytes);
+    int32_t rc = pamc_prefill(ctx, &rq, 0);
+    if (rc == 0 && c->async) cudaStreamSynchronize(c->stream);    // `table` is read by an async copy
+    return rc;
+}
+
+// ------------------------------------------------------------------ scheduler
+
+void* pamc_sched_create(int32_t max_batch_size, int32_t max_sequences) { return new Sched(max_batch_size, max_sequences); }
+void pamc_sched_destroy(void* s) { delete static_cast<Sched*>(s); }
+int64_t pamc_sched_add_request(void* s, int32_t prompt, int32_t max_new) { return s ? static_cast<Sched*>(s)->s.addRequest(prompt, max_new) : -1; }
+void pamc_sched_complete(void* s, int64_t id) { if (s) static_cast<Sched*>(s)->s.complete(id); }
+int32_t pamc_sched_step(void* s, int64_t* out_ids, int32_t capacity) {
+    if (!s) return -1;
+    std::vector<int64_t> b = static_cast<Sched*>(s)->s.step();
+    for (int i = 0; i < capacity && i < static_cast<int>(b.size()); ++i) out_ids[i] = b[static_cast<size_t>(i)];
+    return static_cast<int32_t>(b.size());
+}
+void pamc_sched_mark_prefilled(void* s, int64_t id) { if (s) static_cast<Sched*>(s)->s.markPrefilled(id); }
+void pamc_sched_mark_decoded(void* s, int64_t id) { if (s) static_cast<Sched*>(s)->s.markDecoded(id); }
+void pamc_sched_preempt(void* s, int64_t id) { if (s) static_cast<Sched*>(s)->s.preempt(id); }
+int32_t pamc_sched_handle_memory_pressure(void* s, int32_t required_blocks, pamc_available_fn available, void* user,
+                                          int64_t* out_ids, int32_t capacity) {
+    if (!s || !available) return -1;
+    std::vector<int64_t> v = static_cast<Sched*>(s)->s.handleMemoryPressure(required_blocks, [&]() { return available(user); });
+    for (int i = 0; i < capacity && i < static_cast<int>(v.size()); ++i) out_ids[i] = v[static_cast<size_t>(i)];
+    return static_cast<int32_t>(v.size());
+}
+int32_t pamc_sched_count(void* s, int32_t status) { return s ? static_cast<Sched*>(s)->s.count(status) : -1; }
+int32_t pamc_sched_total(void* s) { return s ? static_cast<Sched*>(s)->s.total() : -1; }
+int32_t pamc_sched_get(void* s, int64_t id, PamSchedSequence* out) {
+    if (!s || !out) return -1;
+    pam::SchedulerSequence q;
+    if (!static_cast<Sched*>(s)->s.get(id, &q)) return -1;
+    out->id = q.id; out->status = q.status; out->num_generated_tokens = q.numGeneratedTokens;
+    out->max_new_tokens = q.maxNewTokens; out->prompt_length = q.promptLength; out->arrival_order = q.arrivalOrder;
+    return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,193 @@
+// Chunked causal / sliding-window prefill over paged KV laid out
+// [block][kv_head][block_size][head_dim].
+//
+// Semantics: paged_attention_tiled (kernels.metal:693-765) and the reference's
+// chunk loop (PagedAttentionEngine.swift:740-756): row i of a sequence attends
+// keys [window_start, S) of its paged cache, key j visible iff j <= i when
+// causal; scores are scaled by 1/sqrt(dim), accumulation is float32.  A launch
+// covers one chunk of rows [q_start, q_start + q_len) of each of several
+// sequences.  Rows that see no key (0/0 in the reference) are written as zeros.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <cmath>
+
+#include "kernels.h"
+
+namespace pam {
+namespace {
+
+__device__ __forceinline__ float toFloat(float v) { return v; }
+__device__ __forceinline__ float toFloat(__half v) { return __half2float(v); }
+__device__ __forceinline__ float toFloat(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T>
+__device__ __forceinline__ T fromFloat(float v);
+template <>
+__device__ __forceinline__ __half fromFloat<__half>(float v) { return __float2half_rn(v); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 fromFloat<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <>
+__device__ __forceinline__ float fromFloat<float>(float v) { return v; }
+
+// dequant_fp8 (kernels.metal:553-562): every product rounded to half.
+__device__ __forceinline__ float dequantE4m3(uint8_t v, __half scale) {
+    const int e = (v >> 3) & 0xF, m = v & 7;
+    if (e == 0 && m == 0) return 0.f;
+    const __half ss = (v & 0x80) ? __hneg(scale) : scale;
+    const __half frac = __float2half_rn(static_cast<float>(m) * 0.125f);
+    if (e == 0) return __half2float(__hmul(__hmul(ss, frac), __float2half_rn(0.015625f)));
+    const __half t = __hmul(ss, __hadd(__float2half_rn(1.0f), frac));
+    return __half2float(__hmul(t, __float2half_rn(exp2f(static_cast<float>(e - 7)))));
+}
+
+// General kernel: one CTA per (16-row tile, head, sequence), 16 keys at a time.
+// Works for every storage type, block size and head_dim up to 256; not tuned.
+template <typename QT, typename KT>
+__global__ void __launch_bounds__(128)
+prefillGeneralKernel(PrefillParams p) {
+    constexpr int QR = 16, TB = 16, DPT = 2;
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int tile = blockIdx.x, head = blockIdx.y, seq = blockIdx.z, tid = threadIdx.x;
+    const int D = p.headDim, G = p.heads / p.kvHeads, kvh = head / G;
+    const int qLen = p.qLens[seq];
+    if (tile * QR >= qLen) return;
+    const int qStart = p.qStarts[seq], seqLen = p.seqLens[seq], ws = p.windowStarts[seq];
+    const int64_t rowBase = p.qRowOffsets[seq] + tile * QR;
+    const int rows = min(QR, qLen - tile * QR);
+    const int firstRow = qStart + tile * QR;             // sequence position of local row 0
+
+    float* sq = reinterpret_cast<float*>(smem);          // [QR][D]
+    float* sk = sq + QR * D;                             // [TB][D]
+    float* sv = sk + TB * D;                             // [TB][D]
+    float* ss = sv + TB * D;                             // [QR][TB]
+    float* sm = ss + QR * TB;                            // m, l, corr: [3][QR]
+    const QT* q = static_cast<const QT*>(p.q);
+    const KT* kPool = static_cast<const KT*>(p.kPool);
+    const KT* vPool = static_cast<const KT*>(p.vPool);
+    const __half* kScale = static_cast<const __half*>(p.kScale);
+    const __half* vScale = static_cast<const __half*>(p.vScale);
+    QT* out = static_cast<QT*>(p.out);
+    const int32_t* table = p.tables + static_cast<int64_t>(seq) * p.maxNumBlocks;
+    const float scale = 1.0f / sqrtf(static_cast<float>(D));      // kernels.metal:719
+
+    for (int i = tid; i < rows * D; i += 128) {
+        const int r = i / D, d = i - r * D;
+        sq[i] = toFloat(q[((rowBase + r) * p.heads + head) * D + d]);
+    }
+    if (tid < QR) { sm[tid] = -INFINITY; sm[QR + tid] = 0.f; sm[2 * QR + tid] = 0.f; }
+    float acc[QR][DPT];
+#pragma unroll
+    for (int r = 0; r < QR; ++r)
+#pragma unroll
+        for (int i = 0; i < DPT; ++i) acc[r][i] = 0.f;
+
+    int keyEnd = seqLen;
+    if (p.causal) keyEnd = min(keyEnd, firstRow + rows);        // kernels.metal:745
+    for (int j0 = ws; j0 < keyEnd; j0 += TB) {
+        const int nt = min(TB, keyEnd - j0);
+        __syncthreads();
+        for (int i = tid; i < nt * D; i += 128) {
+            const int t = i / D, d = i - t * D;
+            const int tok = j0 + t;
+            const int64_t blk = min(max(table[tok / p.blockSize], 0), p.poolBlocks - 1);
+            const int64_t off = ((blk * p.kvHeads + kvh) * p.blockSize + tok % p.blockSize) * static_cast<int64_t>(D) + d;
+            if constexpr (sizeof(KT) == 1) {
+                sk[i] = dequantE4m3(kPool[off], kScale[blk * p.kvHeads + kvh]);
+                sv[i] = dequantE4m3(vPool[off], vScale[blk * p.kvHeads + kvh]);
+            } else {
+                sk[i] = toFloat(kPool[off]);
+                sv[i] = toFloat(vPool[off]);
+            }
+        }
+        __syncthreads();
+        for (int i = tid; i < rows * nt; i += 128) {
+            const int r = i / nt, t = i - r * nt;
+            float dot = 0.f;
+            for (int d = 0; d < D; ++d) dot += sq[r * D + d] * sk[t * D + d];
+            const bool visible = !p.causal || (j0 + t <= firstRow + r);
+            ss[r * TB + t] = visible ? dot * scale : -INFINITY;
+        }
+        __syncthreads();
+        if (tid < rows) {
+            const int r = tid;
+            float m = sm[r], mx = m;
+            for (int t = 0; t < nt; ++t) mx = fmaxf(mx, ss[r * TB + t]);
+            if (mx == -INFINITY) {
+                for (int t = 0; t < nt; ++t) ss[r * TB + t] = 0.f;
+                sm[2 * QR + r] = 1.f;
+            } else {
+                const float corr = expf(m - mx);
+                float sum = 0.f;
+                for (int t = 0; t < nt; ++t) {
+                    const float pr = expf(ss[r * TB + t] - mx);
+                    ss[r * TB + t] = pr;
+                    sum += pr;
+                }
+                sm[r] = mx;
+                sm[QR + r] = sm[QR + r] * corr + sum;
+                sm[2 * QR + r] = corr;
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < DPT; ++i) {
+            const int d = tid + 128 * i;
+            if (d < D) {
+#pragma unroll
+                for (int r = 0; r < QR; ++r) {
+                    if (r < rows) {
+                        float a = acc[r][i] * sm[2 * QR + r];
+                        for (int t = 0; t < nt; ++t) a += ss[r * TB + t] * sv[t * D + d];
+                        acc[r][i] = a;
+                    }
+                }
+            }
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+        const int d = tid + 128 * i;
+        if (d < D) {
+#pragma unroll
+            for (int r = 0; r < QR; ++r) {
+                if (r < rows) {
+                    const float l = sm[QR + r];
+                    out[((rowBase + r) * p.heads + head) * D + d] = fromFloat<QT>(l > 0.f ? acc[r][i] / l : 0.f);
+                }
+            }
+        }
+    }
+}
+
+template <typename QT, typename KT>
+cudaError_t launchGeneral(const PrefillParams& p, cudaStream_t stream, int* launches) {
+    const size_t smem = (static_cast<size_t>(16 + 2 * 16) * p.headDim + 16 * 16 + 3 * 16) * sizeof(float);
+    auto kernel = prefillGeneralKernel<QT, KT>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+    dim3 grid(static_cast<unsigned>((p.maxQLen + 15) / 16), static_cast<unsigned>(p.heads),
+              static_cast<unsigned>(p.numSeqs));
+    kernel<<<grid, 128, smem, stream>>>(p);
+    if (launches) *launches += 1;
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launchPrefill(const PrefillParams& p, int smCount, cudaStream_t stream, int* launches,
+                          bool* usedTensorPath) {
+    (void)smCount;
+    if (usedTensorPath) *usedTensorPath = false;
+    if (p.numSeqs <= 0 || p.maxQLen <= 0) return cudaSuccess;
+    if (p.headDim > 256 || p.poolBlocks <= 0) return cudaErrorInvalidValue;
+    switch (p.dtype) {
+        case kF32: return launchGeneral<float, float>(p, stream, launches);
+        case kF16: return launchGeneral<__half, __half>(p, stream, launches);
+        case kBF16: return launchGeneral<__nv_bfloat16, __nv_bfloat16>(p, stream, launches);
+        case kFP8: return launchGeneral<__half, uint8_t>(p, stream, launches);
+    }
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace pam

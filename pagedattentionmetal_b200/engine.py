@@ -1,0 +1,567 @@
+"""Python face of the library: PagedAttentionEngine, KVCacheManager,
+BatchKVCacheManager and ContinuousBatchingScheduler with the reference's method
+names and error behaviour, each a thin veneer over the C ABI (all logic and all
+kernels live in libpam_cuda.so; nothing here computes).
+
+Buffers may be numpy arrays (host memory; staged by the library inside the
+call, like the reference's host-visible MTLBuffers), ``DeviceBuffer`` objects,
+torch CUDA tensors, or raw device addresses.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Iterable, Optional, Sequence
+
+import numpy as np
+
+from . import _cabi
+from ._cabi import lib
+from .api_types import (BlockEvictionPolicy, KVCacheError, KVCacheMemoryStats, LogicalSequence,
+                        Operation, PagedAttentionDataType, PagedAttentionDecodeRequest,
+                        PagedAttentionError, PagedAttentionPrefillRequest, PagedAttentionStats,
+                        PagedKVAppendRequest, PagedLayerSpec, SchedulerSequence, SequenceStatus)
+
+
+def _raise(ctx) -> None:
+    code = lib.pamc_last_error_code(ctx)
+    msg = lib.pam_last_error(ctx)
+    text = msg.decode() if msg else "unknown error"
+    if 20 <= code < 30:
+        raise KVCacheError(code, text)
+    raise PagedAttentionError(code, text)
+
+
+def _check(ctx, rc: int) -> None:
+    if rc != 0:
+        _raise(ctx)
+
+
+def _layer(spec: PagedLayerSpec) -> _cabi.PamLayerSpec:
+    return _cabi.PamLayerSpec(spec.headDim, spec.numHeads, spec.numKVHeads, spec.blockSize,
+                              int(spec.dataType), spec.windowSize)
+
+
+class DeviceBuffer:
+    """Device memory owned by the library (stands where the reference has an
+    MTLBuffer): address + length, upload/download through the context."""
+
+    def __init__(self, engine: "PagedAttentionEngine", nbytes: int):
+        self._engine = engine
+        self.nbytes = int(nbytes)
+        self.ptr = lib.pamc_buffer_alloc(engine._ctx, self.nbytes)
+        if not self.ptr:
+            raise PagedAttentionError(10, f"GPU resource exhausted: cannot allocate {nbytes} bytes")
+
+    @property
+    def length(self) -> int:
+        return self.nbytes
+
+    def upload(self, array: np.ndarray, offset: int = 0) -> "DeviceBuffer":
+        a = np.ascontiguousarray(array)
+        assert offset + a.nbytes <= self.nbytes
+        _check(self._engine._ctx, lib.pamc_memcpy(self._engine._ctx, self.ptr + offset, a.ctypes.data, a.nbytes, 0))
+        return self
+
+    def download(self, dtype, shape, offset: int = 0) -> np.ndarray:
+        out = np.empty(shape, dtype=dtype)
+        assert offset + out.nbytes <= self.nbytes
+        _check(self._engine._ctx, lib.pamc_memcpy(self._engine._ctx, out.ctypes.data, self.ptr + offset, out.nbytes, 1))
+        return out
+
+    def free(self) -> None:
+        if self.ptr:
+            lib.pamc_buffer_free(self._engine._ctx, self.ptr)
+            self.ptr = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+def _buf(x) -> _cabi.PamBuffer:
+    if x is None:
+        return _cabi.PamBuffer(None, 0)
+    if isinstance(x, DeviceBuffer):
+        return _cabi.PamBuffer(x.ptr, x.nbytes)
+    return _cabi.buffer(x)
+
+
+class PagedAttentionEngine:
+    """PagedAttentionEngine (PagedAttentionEngine.swift:82): prefill, decode and
+    appendToCache over paged KV pools, with the reference's validation, retry,
+    graceful-degradation and statistics behaviour."""
+
+    def __init__(self, device: Optional[int] = None):
+        if lib.pamc_device_count() <= 0:
+            raise PagedAttentionError(1, "Metal device or command queue could not be initialized.")
+        self._ctx = lib.pamc_create_context_on(device) if device is not None else lib.pam_create_context()
+        if not self._ctx:
+            raise PagedAttentionError(1, "Metal device or command queue could not be initialized.")
+        self._splitThreshold, self._defaultWindowSize, self._defaultChunkSize = 1024, 0, 0
+        self._maxRetries, self._graceful = 3, True
+
+    def close(self) -> None:
+        if getattr(self, "_ctx", None):
+            lib.pam_destroy_context(self._ctx)
+            self._ctx = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- properties (PagedAttentionEngine.swift:116-129) --
+    splitThreshold = property(lambda s: s._splitThreshold)
+    defaultWindowSize = property(lambda s: s._defaultWindowSize)
+    defaultChunkSize = property(lambda s: s._defaultChunkSize)
+    maxRetries = property(lambda s: s._maxRetries)
+    enableGracefulDegradation = property(lambda s: s._graceful)
+
+    @splitThreshold.setter
+    def splitThreshold(self, v):
+        self._splitThreshold = int(v)
+        lib.pamc_set_split_threshold(self._ctx, int(v))
+
+    @defaultWindowSize.setter
+    def defaultWindowSize(self, v):
+        self._defaultWindowSize = int(v)
+        lib.pamc_set_default_window(self._ctx, int(v))
+
+    @defaultChunkSize.setter
+    def defaultChunkSize(self, v):
+        self._defaultChunkSize = int(v)
+        lib.pamc_set_default_chunk(self._ctx, int(v))
+
+    @maxRetries.setter
+    def maxRetries(self, v):
+        self._maxRetries = int(v)
+        lib.pamc_set_max_retries(self._ctx, int(v))
+
+    @enableGracefulDegradation.setter
+    def enableGracefulDegradation(self, v):
+        self._graceful = bool(v)
+        lib.pamc_set_graceful_degradation(self._ctx, 1 if v else 0)
+
+    @property
+    def lastStats(self) -> PagedAttentionStats:      # PagedAttentionEngine.swift:137-141
+        s = _cabi.PamStats()
+        lib.pamc_last_stats(self._ctx, C.byref(s))
+        return PagedAttentionStats(Operation(s.operation), s.batch_size, s.sequence_length, s.num_blocks,
+                                   s.temporary_bytes, bool(s.used_split_pass), s.elapsed_ms)
+
+    @property
+    def lastError(self) -> Optional[str]:            # PagedAttentionEngine.swift:144-148
+        m = lib.pam_last_error(self._ctx)
+        return m.decode() if m else None
+
+    @property
+    def kernelLaunches(self) -> int:
+        return int(lib.pamc_kernel_launches(self._ctx))
+
+    def recommendedMaxBlocks(self, blockSize, numKVHeads, headDim, dataType, memoryFraction=0.75, layerCount=1) -> int:
+        """PagedAttentionEngine.swift:201-217"""
+        return int(lib.pamc_recommended_max_blocks(self._ctx, blockSize, numKVHeads, headDim, int(dataType),
+                                                   memoryFraction, layerCount))
+
+    def makeBuffer(self, nbytes: int) -> DeviceBuffer:
+        return DeviceBuffer(self, nbytes)
+
+    def makeBufferFrom(self, array: np.ndarray) -> DeviceBuffer:
+        a = np.ascontiguousarray(array)
+        return DeviceBuffer(self, max(a.nbytes, 1)).upload(a) if a.nbytes else DeviceBuffer(self, 1)
+
+    def setStream(self, cuda_stream: Optional[int]) -> None:
+        _check(self._ctx, lib.pamc_set_stream(self._ctx, cuda_stream))
+
+    def setAsync(self, enabled: bool) -> None:
+        lib.pamc_set_async(self._ctx, 1 if enabled else 0)
+
+    def synchronize(self) -> None:
+        _check(self._ctx, lib.pamc_synchronize(self._ctx))
+
+    def injectLaunchFailures(self, n: int) -> None:
+        lib.pamc_inject_launch_failures(self._ctx, n)
+
+    # -- operations --
+    def prefill(self, request: PagedAttentionPrefillRequest, chunkSize: int = 0) -> None:
+        """PagedAttentionEngine.swift:405-418 (request form) and :713-768 (chunk loop)."""
+        r = _cabi.PamPrefillRequest(_buf(request.q), _buf(request.kPool), _buf(request.vPool),
+                                    _buf(request.blockTable), _buf(request.output), request.seqLen,
+                                    _layer(request.layer), 1 if request.causal else 0,
+                                    _buf(request.kScaleBuffer), _buf(request.vScaleBuffer),
+                                    request.qStart, request.qLen)
+        _check(self._ctx, lib.pamc_prefill(self._ctx, C.byref(r), chunkSize))
+
+    def prefillBatch(self, q, kPool, vPool, blockTables, output, seqLens: Sequence[int], qStarts: Sequence[int],
+                     qLens: Sequence[int], maxNumBlocks: int, layer: PagedLayerSpec, causal: bool = True,
+                     kScaleBuffer=None, vScaleBuffer=None) -> None:
+        """One launch for the same chunk of several sequences (no counterpart in
+        the reference, whose prefill takes one sequence per dispatch)."""
+        n = len(seqLens)
+        arr = lambda v: (C.c_int32 * n)(*[int(x) for x in v])
+        sl, qs, ql = arr(seqLens), arr(qStarts), arr(qLens)
+        r = _cabi.PamBatchPrefillRequest(_buf(q), _buf(kPool), _buf(vPool), _buf(blockTables), _buf(output),
+                                         sl, qs, ql, n, maxNumBlocks, _layer(layer), 1 if causal else 0,
+                                         _buf(kScaleBuffer), _buf(vScaleBuffer))
+        _check(self._ctx, lib.pamc_prefill_batch(self._ctx, C.byref(r)))
+
+    def decode(self, request: PagedAttentionDecodeRequest) -> None:
+        """PagedAttentionEngine.swift:533-546"""
+        r = _cabi.PamDecodeRequest(_buf(request.q), _buf(request.kPool), _buf(request.vPool),
+                                   _buf(request.blockTables), _buf(request.seqLengths), _buf(request.output),
+                                   request.batchSize, request.maxNumBlocks, _layer(request.layer),
+                                   _buf(request.kScaleBuffer), _buf(request.vScaleBuffer))
+        _check(self._ctx, lib.pamc_decode(self._ctx, C.byref(r)))
+
+    def appendToCache(self, request: PagedKVAppendRequest) -> None:
+        """PagedAttentionEngine.swift:585-597"""
+        r = _cabi.PamAppendRequest(_buf(request.keys), _buf(request.values), _buf(request.kPool),
+                                   _buf(request.vPool), _buf(request.blockTable), request.tokenOffset,
+                                   request.numNewTokens, _layer(request.layer), _buf(request.kScaleBuffer),
+                                   _buf(request.vScaleBuffer))
+        _check(self._ctx, lib.pamc_append_to_cache(self._ctx, C.byref(r)))
+
+    # -- cache-handle forms (the reference's C ABI, PagedAttentionCABI.swift:203-337) --
+    def appendKV(self, cache: "KVCacheManager", sequenceId: int, keys, values, tokenOffset: int,
+                 numNewTokens: int, numHeads: int) -> None:
+        _check(self._ctx, lib.pam_append_kv(self._ctx, cache._h, sequenceId, _cabi.address(keys),
+                                            _cabi.address(values), tokenOffset, numNewTokens, numHeads))
+
+    def prefillSequence(self, cache: "KVCacheManager", sequenceId: int, q, output, seqLen: int, numHeads: int,
+                        causal: bool = True) -> None:
+        _check(self._ctx, lib.pam_prefill(self._ctx, cache._h, sequenceId, _cabi.address(q),
+                                          _cabi.address(output), seqLen, numHeads, causal))
+
+    def decodeBatch(self, cache: "KVCacheManager", ids: Sequence[int], q, output, numHeads: int) -> None:
+        arr = (C.c_int64 * len(ids))(*[int(i) for i in ids])
+        _check(self._ctx, lib.pam_decode(self._ctx, cache._h, arr, len(ids), _cabi.address(q),
+                                         _cabi.address(output), numHeads))
+
+    def reshapeAndCache(self, cache: "KVCacheManager", keys, values, slotMapping, numTokens: int) -> None:
+        _check(self._ctx, lib.pamc_reshape_and_cache(self._ctx, cache._h, _cabi.address(keys),
+                                                     _cabi.address(values), _cabi.address(slotMapping), numTokens))
+
+    def copyBlocks(self, cache: "KVCacheManager", src: Iterable[int], dst: Iterable[int]) -> None:
+        s = np.ascontiguousarray(list(src), dtype=np.int32)
+        d = np.ascontiguousarray(list(dst), dtype=np.int32)
+        assert len(s) == len(d)
+        _check(self._ctx, lib.pamc_copy_blocks(self._ctx, cache._h, s.ctypes.data_as(C.POINTER(C.c_int32)),
+                                               d.ctypes.data_as(C.POINTER(C.c_int32)), len(s)))
+
+
+class KVCacheManager:
+    """KVCacheManager (KVCacheManager.swift:47-379).  With ``engine=None`` the
+    manager only keeps the books (no pools, no GPU)."""
+
+    def __init__(self, engine: Optional[PagedAttentionEngine], maxBlocks: int, blockSize: int = 16,
+                 headDim: int = 0, numKVHeads: int = 0,
+                 dataType: PagedAttentionDataType = PagedAttentionDataType.float16):
+        self.engine = engine
+        self.maxBlocks, self.blockSize, self.headDim, self.numKVHeads = maxBlocks, blockSize, headDim, numKVHeads
+        self.dataType = PagedAttentionDataType(dataType)
+        self._ownCtx = None
+        if engine is None:
+            self._h = lib.pamc_cache_create_bookkeeping(maxBlocks, blockSize)
+            if not self._h:
+                raise PagedAttentionError(4, "Invalid paged attention configuration: maxBlocks must be positive")
+            # errors of a manager without an engine are kept in a context-free holder
+            self._ctx = None
+        else:
+            self._ctx = engine._ctx
+            self._h = lib.pam_create_cache(self._ctx, maxBlocks, blockSize, headDim, numKVHeads, int(dataType))
+            if not self._h:
+                _raise(self._ctx)
+        self._policy = BlockEvictionPolicy.fifo
+
+    def _context(self):
+        if self._ctx is None:
+            raise PagedAttentionError(12, "Invalid engine state: this manager has no engine")
+        return self._ctx
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            lib.pam_destroy_cache(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # pools (KVCacheManager.swift:59-60)
+    def _pools(self):
+        k, v, ks, vs = C.c_void_p(), C.c_void_p(), C.c_void_p(), C.c_void_p()
+        pb, sb = C.c_size_t(), C.c_size_t()
+        lib.pamc_cache_pools(self._h, C.byref(k), C.byref(v), C.byref(ks), C.byref(vs), C.byref(pb), C.byref(sb))
+        return k.value, v.value, ks.value, vs.value, pb.value, sb.value
+
+    @property
+    def kPoolBuffer(self) -> _cabi.PamBuffer:
+        p = self._pools()
+        return _cabi.PamBuffer(p[0], p[4])
+
+    @property
+    def vPoolBuffer(self) -> _cabi.PamBuffer:
+        p = self._pools()
+        return _cabi.PamBuffer(p[1], p[4])
+
+    @property
+    def kScaleBuffer(self) -> Optional[_cabi.PamBuffer]:
+        p = self._pools()
+        return _cabi.PamBuffer(p[2], p[5]) if p[2] else None
+
+    @property
+    def vScaleBuffer(self) -> Optional[_cabi.PamBuffer]:
+        p = self._pools()
+        return _cabi.PamBuffer(p[3], p[5]) if p[3] else None
+
+    def readPools(self):
+        """Download K/V pools as arrays [blocks][kv_heads][block_size][head_dim]
+        (and FP8 scales [blocks][kv_heads] float16, else None)."""
+        k, v, ks, vs, pb, sb = self._pools()
+        dt = {0: np.float32, 1: np.float16, 2: np.uint8, 3: np.uint16}[int(self.dataType)]
+        shape = (self.maxBlocks, self.numKVHeads, self.blockSize, self.headDim)
+        ctx = self._context()
+        kp, vp = np.empty(shape, dtype=dt), np.empty(shape, dtype=dt)
+        _check(ctx, lib.pamc_memcpy(ctx, kp.ctypes.data, k, pb, 1))
+        _check(ctx, lib.pamc_memcpy(ctx, vp.ctypes.data, v, pb, 1))
+        ksc = vsc = None
+        if ks:
+            ksc = np.empty((self.maxBlocks, self.numKVHeads), dtype=np.float16)
+            vsc = np.empty((self.maxBlocks, self.numKVHeads), dtype=np.float16)
+            _check(ctx, lib.pamc_memcpy(ctx, ksc.ctypes.data, ks, sb, 1))
+            _check(ctx, lib.pamc_memcpy(ctx, vsc.ctypes.data, vs, sb, 1))
+        return kp, vp, ksc, vsc
+
+    # -- bookkeeping --
+    def _kv(self, rc: int):
+        if rc < 0:
+            if self._ctx is None:
+                raise KVCacheError(0, "KVCacheError")
+            _raise(self._ctx)
+        return rc
+
+    def _ctx_or_scratch(self):
+        if self._ctx is None:
+            if self._ownCtx is None:
+                self._ownCtx = _ErrorHolder()
+            return self._ownCtx.ctx
+        return self._ctx
+
+    def allocateSequence(self, id: int) -> None:                       # KVCacheManager.swift:106-113
+        ctx = self._ctx_or_scratch()
+        _check(ctx, lib.pam_reserve_sequence(ctx, self._h, id))
+
+    def appendTokens(self, toSequence: int, count: int, blockHashes: Optional[Sequence[int]] = None) -> None:
+        """KVCacheManager.swift:115-174"""
+        ctx = self._ctx_or_scratch()
+        if blockHashes is None:
+            _check(ctx, lib.pamc_cache_append_tokens(ctx, self._h, toSequence, count, None, 0))
+        else:
+            n = len(blockHashes)
+            arr = (C.c_uint64 * max(n, 1))(*[int(h) for h in blockHashes])
+            _check(ctx, lib.pamc_cache_append_tokens(ctx, self._h, toSequence, count, arr, n))
+
+    def registerBlockHash(self, hash: int, physicalBlock: int) -> None:   # KVCacheManager.swift:196-198
+        lib.pamc_cache_register_block_hash(self._h, hash, physicalBlock)
+
+    def ensureExclusiveAccess(self, sequenceId: int, logicalBlockIndex: int) -> None:   # :200-214
+        ctx = self._ctx_or_scratch()
+        _check(ctx, lib.pamc_cache_ensure_exclusive(ctx, self._h, sequenceId, logicalBlockIndex))
+
+    def freeSequence(self, id: int) -> None:                           # KVCacheManager.swift:216-239
+        lib.pam_free_sequence(self._h, id)
+
+    def getBlockTable(self, forSequence: int) -> list:                  # KVCacheManager.swift:299-303
+        ctx = self._ctx_or_scratch()
+        n = lib.pamc_cache_block_table(ctx, self._h, forSequence, None, 0)
+        if n < 0:
+            _raise(ctx)
+        out = (C.c_int32 * max(n, 1))()
+        lib.pamc_cache_block_table(ctx, self._h, forSequence, out, n)
+        return list(out[:n])
+
+    def getSequence(self, id: int) -> LogicalSequence:                  # KVCacheManager.swift:323-327
+        return LogicalSequence(id, self.getBlockTable(id), self.getSequenceLength(id))
+
+    def getSequenceLength(self, id: int) -> int:                        # KVCacheManager.swift:329-333
+        ctx = self._ctx_or_scratch()
+        n = lib.pam_sequence_length(ctx, self._h, id)
+        if n < 0:
+            _raise(ctx)
+        return n
+
+    def getNumBlocks(self, forSequence: int) -> int:                    # KVCacheManager.swift:335-339
+        ctx = self._ctx_or_scratch()
+        n = lib.pamc_cache_num_blocks(ctx, self._h, forSequence)
+        if n < 0:
+            _raise(ctx)
+        return n
+
+    @property
+    def availableBlocks(self) -> int:                                   # KVCacheManager.swift:341-345
+        return lib.pam_available_blocks(self._h)
+
+    @property
+    def activeSequenceCount(self) -> int:                               # KVCacheManager.swift:347-351
+        return lib.pamc_cache_active_sequences(self._h)
+
+    @property
+    def evictionPolicy(self) -> BlockEvictionPolicy:
+        return self._policy
+
+    @evictionPolicy.setter
+    def evictionPolicy(self, p) -> None:                                # KVCacheManager.swift:65-67
+        self._policy = BlockEvictionPolicy(p)
+        lib.pamc_cache_set_eviction_policy(self._h, int(self._policy))
+
+    def memoryStats(self) -> KVCacheMemoryStats:                        # KVCacheManager.swift:353-378
+        s = _cabi.PamMemoryStats()
+        lib.pamc_cache_memory_stats(self._h, C.byref(s))
+        return KVCacheMemoryStats(s.total_blocks, s.used_blocks, s.free_blocks, s.active_sequences,
+                                  s.total_memory_bytes, s.used_memory_bytes, s.partially_filled_blocks,
+                                  s.fragmentation_ratio, s.prefix_cache_hits, s.prefix_cache_entries,
+                                  s.shared_blocks, BlockEvictionPolicy(s.eviction_policy))
+
+    def drainCopyOnWriteLog(self) -> list:
+        out = (C.c_int32 * 2048)()
+        n = lib.pamc_cache_drain_cow_log(self._h, out, 1024)
+        return [(out[2 * i], out[2 * i + 1]) for i in range(n)]
+
+    def slotMapping(self, id: int, tokenOffset: int, numTokens: int) -> np.ndarray:
+        ctx = self._ctx_or_scratch()
+        out = np.empty(numTokens, dtype=np.int64)
+        _check(ctx, lib.pamc_cache_slot_mapping(ctx, self._h, id, tokenOffset, numTokens,
+                                                out.ctypes.data_as(C.POINTER(C.c_int64))))
+        return out
+
+    def batchTables(self, ids: Sequence[int], maxNumBlocks: int):
+        """Zero-padded [n][maxNumBlocks] int32 tables and [n] uint32 lengths
+        (KVCacheManager.swift:661-703), as host arrays."""
+        ctx = self._ctx_or_scratch()
+        n = len(ids)
+        tables = np.zeros((n, maxNumBlocks), dtype=np.int32)
+        lens = np.zeros(n, dtype=np.uint32)
+        arr = (C.c_int64 * max(n, 1))(*[int(i) for i in ids])
+        _check(ctx, lib.pamc_cache_batch_tables(ctx, self._h, arr, n, maxNumBlocks, tables.ctypes.data, lens.ctypes.data))
+        return tables, lens
+
+
+class _ErrorHolder:
+    """A manager without an engine still needs a place for its last error; the
+    C ABI keeps that in a context.  A host-only context needs no GPU."""
+
+    def __init__(self):
+        self.ctx = lib.pamc_create_host_context()
+
+    def __del__(self):
+        try:
+            if self.ctx:
+                lib.pam_destroy_context(self.ctx)
+                self.ctx = None
+        except Exception:
+            pass
+
+
+class BatchKVCacheManager(KVCacheManager):
+    """BatchKVCacheManager (KVCacheManager.swift:382-739): adds device slabs for
+    block tables and lengths that getBatchBlockTableBuffer/getSeqLengthsBuffer
+    overwrite on every call."""
+
+    def __init__(self, engine: PagedAttentionEngine, maxBatchSize: int, maxSequenceBlocks: int, maxBlocks: int,
+                 blockSize: int = 16, headDim: int = 0, numKVHeads: int = 0,
+                 dataType: PagedAttentionDataType = PagedAttentionDataType.float16):
+        super().__init__(engine, maxBlocks, blockSize, headDim, numKVHeads, dataType)
+        self.maxBatchSize, self.maxSequenceBlocks = maxBatchSize, maxSequenceBlocks
+        self.blockTablesSlab = engine.makeBuffer(maxBatchSize * maxSequenceBlocks * 4)   # KVCacheManager.swift:446
+        self.seqLengthsSlab = engine.makeBuffer(maxBatchSize * 4)
+
+    def getBatchBlockTableBuffer(self, forBatch: Sequence[int]) -> DeviceBuffer:   # KVCacheManager.swift:661-688
+        if len(forBatch) > self.maxBatchSize:
+            raise KVCacheError(20, "KVCacheError.outOfMemory")
+        n = len(forBatch)
+        arr = (C.c_int64 * max(n, 1))(*[int(i) for i in forBatch])
+        _check(self._ctx, lib.pamc_cache_batch_tables(self._ctx, self._h, arr, n, self.maxSequenceBlocks,
+                                                      self.blockTablesSlab.ptr, None))
+        return self.blockTablesSlab
+
+    def getSeqLengthsBuffer(self, forBatch: Sequence[int]) -> DeviceBuffer:        # KVCacheManager.swift:690-703
+        n = len(forBatch)
+        arr = (C.c_int64 * max(n, 1))(*[int(i) for i in forBatch])
+        _check(self._ctx, lib.pamc_cache_batch_tables(self._ctx, self._h, arr, n, self.maxSequenceBlocks,
+                                                      None, self.seqLengthsSlab.ptr))
+        return self.seqLengthsSlab
+
+
+class ContinuousBatchingScheduler:
+    """ContinuousBatchingScheduler (Scheduler.swift:42-177)."""
+
+    def __init__(self, maxBatchSize: int, maxSequences: int = 128):
+        self.maxBatchSize, self.maxSequences = maxBatchSize, maxSequences
+        self._h = lib.pamc_sched_create(maxBatchSize, maxSequences)
+
+    def __del__(self):
+        try:
+            if self._h:
+                lib.pamc_sched_destroy(self._h)
+                self._h = None
+        except Exception:
+            pass
+
+    def _get(self, id: int) -> Optional[SchedulerSequence]:
+        s = _cabi.PamSchedSequence()
+        if lib.pamc_sched_get(self._h, id, C.byref(s)) != 0:
+            return None
+        return SchedulerSequence(s.id, SequenceStatus(s.status), s.num_generated_tokens, s.max_new_tokens,
+                                 s.prompt_length, s.arrival_order)
+
+    def addRequest(self, promptTokenCount: int, maxNewTokens: int) -> int:          # Scheduler.swift:58-70
+        return int(lib.pamc_sched_add_request(self._h, promptTokenCount, maxNewTokens))
+
+    def completeSequence(self, id: int) -> None:                                    # Scheduler.swift:72-76
+        lib.pamc_sched_complete(self._h, id)
+
+    def step(self) -> list:                                                         # Scheduler.swift:78-114
+        cap = max(self.maxBatchSize, 1)
+        out = (C.c_int64 * cap)()
+        n = lib.pamc_sched_step(self._h, out, cap)
+        return [self._get(out[i]) for i in range(min(n, cap))]
+
+    def markPrefilled(self, id: int) -> None:                                       # Scheduler.swift:116-120
+        lib.pamc_sched_mark_prefilled(self._h, id)
+
+    def markDecoded(self, id: int) -> None:                                         # Scheduler.swift:122-126
+        lib.pamc_sched_mark_decoded(self._h, id)
+
+    def preemptSequence(self, id: int) -> None:                                     # Scheduler.swift:128-132
+        lib.pamc_sched_preempt(self._h, id)
+
+    def handleMemoryPressure(self, requiredBlocks: int, availableBlocks) -> list:   # Scheduler.swift:134-152
+        fn = _cabi.AVAILABLE_FN(lambda _user: int(availableBlocks()))
+        cap = max(self.maxSequences, 1)
+        out = (C.c_int64 * cap)()
+        n = lib.pamc_sched_handle_memory_pressure(self._h, requiredBlocks, fn, None, out, cap)
+        return [int(out[i]) for i in range(min(n, cap))]
+
+    def sequence(self, id: int) -> Optional[SchedulerSequence]:
+        return self._get(id)
+
+    @property
+    def waitingCount(self) -> int:                                                  # Scheduler.swift:154-158
+        return lib.pamc_sched_count(self._h, int(SequenceStatus.waiting))
+
+    @property
+    def runningCount(self) -> int:                                                  # Scheduler.swift:160-164
+        return lib.pamc_sched_count(self._h, int(SequenceStatus.running))
+
+    @property
+    def completedCount(self) -> int:                                                # Scheduler.swift:166-170
+        return lib.pamc_sched_count(self._h, int(SequenceStatus.completed))
+
+    @property
+    def totalSequencesProcessed(self) -> int:                                       # Scheduler.swift:172-176
+        return lib.pamc_sched_total(self._h)
