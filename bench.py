@@ -1,0 +1,363 @@
+"""Benchmark of the paged-KV hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Default workload `decode_c2`: large-batch paged decode with float16 KV -- 256
+sequences, context lengths uniform in [512, 8192], block size 16, head_dim 128,
+32 query / 8 KV heads, non-contiguous block tables, seeded synthetic N(0,1)
+data.  With N GPUs the KV heads are split into N groups, one per GPU; no
+collective runs on the attention path, so the total work is fixed (strong
+scaling).  A step is one decode of the whole batch (one new token per
+sequence); the metric is decode tokens per second of the whole job.
+
+Prints ONE JSON line: `value` is measured with every input resident in HBM
+(CUDA events around exactly K steps on the launching stream, max over ranks);
+`e2e` is the same step through the reference-shaped C-ABI call `pam_decode`
+with queries and outputs in pinned host memory, copies inside the timed
+region; `roofline` relates the decode kernel's algorithmic bytes to the
+measured HBM copy bandwidth; `cpu_baseline` is the C oracle (a restatement of
+the reference's CPU path) timed on this host's cores on a bounded sample.
+
+`--impl reference` times that CPU path alone (rank 0 only).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+SEED = 1002
+BATCH, LEN_LO, LEN_HI = 256, 512, 8192
+HEADS, KV_HEADS, HEAD_DIM, BLOCK = 32, 8, 128, 16
+SPARE_BLOCKS = 1024
+CPU_SAMPLE_SEQS = 32
+FALLBACK_HBM_GBS = 6650.0
+
+
+def workload_lengths():
+    rng = np.random.default_rng(SEED)
+    return rng.integers(LEN_LO, LEN_HI + 1, size=BATCH).astype(np.int64)
+
+
+def measured_hbm_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+def algorithmic_bytes(lens, heads, kv_heads):
+    """Bytes one decode step must move for `kv_heads` KV heads and `heads` query
+    heads: K and V of every context token once, queries, outputs, the touched
+    block-table entries and the lengths."""
+    kv = int(lens.sum()) * 2 * kv_heads * HEAD_DIM * 2
+    qo = 2 * len(lens) * heads * HEAD_DIM * 2
+    tables = int(((lens + BLOCK - 1) // BLOCK).sum()) * 4
+    return kv + qo + tables + len(lens) * 4
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.samples, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append(line.strip())
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            parts = [p.strip() for p in s.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------- CPU arm
+
+def cpu_sample_inputs(lens, n_seqs):
+    """K/V pools, tables, lengths and queries for the first n_seqs sequences of
+    the workload (same lengths, same shapes, N(0,1) float16)."""
+    from oracle import paged_oracle as po
+
+    sub = lens[:n_seqs]
+    nblk = (sub + BLOCK - 1) // BLOCK
+    n_pool = int(nblk.sum()) + 16
+    rng = np.random.default_rng(SEED + 1)
+    perm = rng.permutation(n_pool).astype(np.int32)
+    tables = np.zeros((n_seqs, int(nblk.max())), dtype=np.int32)
+    o = 0
+    for i in range(n_seqs):
+        tables[i, : nblk[i]] = perm[o: o + nblk[i]]
+        o += int(nblk[i])
+    shape = (n_pool, KV_HEADS, BLOCK, HEAD_DIM)
+    k_pool = rng.standard_normal(shape, dtype=np.float32).astype(np.float16)
+    v_pool = rng.standard_normal(shape, dtype=np.float32).astype(np.float16)
+    q = rng.standard_normal((n_seqs, HEADS, HEAD_DIM), dtype=np.float32).astype(np.float16)
+    return q, k_pool, v_pool, tables, sub.astype(np.uint32)
+
+
+def time_cpu_path(lens, steps, warmup, n_seqs=CPU_SAMPLE_SEQS):
+    """The reference's CPU path (its decode loop restated in C, OpenMP over
+    (sequence, kv head)) on all host cores; tokens/s over the sample."""
+    from oracle import c_oracle as co
+
+    q, k_pool, v_pool, tables, l = cpu_sample_inputs(lens, n_seqs)
+    cores = co.max_threads()
+    for _ in range(max(warmup, 1)):
+        co.decode(q, k_pool, v_pool, tables, l, KV_HEADS, BLOCK, 1)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        co.decode(q, k_pool, v_pool, tables, l, KV_HEADS, BLOCK, 1)
+    dt = (time.perf_counter() - t0) / steps
+    return {"value": n_seqs / dt, "unit": "tokens/s", "cores": cores, "kind": "port",
+            "sample": f"first {n_seqs} of {BATCH} sequences of the workload ({int(l.sum())} context tokens), "
+                      f"{steps} timed passes of {dt * 1e3:.1f} ms",
+            "ms_per_step_sample": dt * 1e3}
+
+
+def config_dict(n_gpus):
+    return {"workload": "decode_c2: batch 256, context U[512,8192], block 16, head_dim 128, 32 q / 8 kv heads, "
+                        "float16 KV, random non-contiguous block tables",
+            "seed": SEED, "sharding": f"kv-head groups over {n_gpus} GPU(s), no collective on the attention path",
+            "l2": "inputs larger than L2 (KV read per step per GPU exceeds 126 MB); no flush needed"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    lens = workload_lengths()
+    cb = time_cpu_path(lens, max(args.steps, 1), args.warmup)
+    line = {"impl": "reference", "metric": "paged decode tokens/s", "value": cb["value"], "unit": "tokens/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": cb["ms_per_step_sample"] * BATCH / CPU_SAMPLE_SEQS,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
+            "data": "synthetic", "config": config_dict(args.gpus), "cpu_baseline": cb,
+            "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+# --------------------------------------------------------------------- GPU arm
+
+def scramble_free_list(cache, n_blocks, rng):
+    """Make the allocator hand out blocks in a random order, as after a long
+    run of a server: take every block with one-block sequences, free them in a
+    random order (the fifo policy re-uses blocks in the order they were freed)."""
+    base = 1 << 40
+    for i in range(n_blocks):
+        cache.allocateSequence(base + i)
+        cache.appendTokens(base + i, 1)
+    for i in rng.permutation(n_blocks):
+        cache.freeSequence(base + int(i))
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    import pagedattentionmetal_b200 as pam
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run for --gpus > 1")
+    assert KV_HEADS % world == 0, "the KV heads must divide over the GPUs"
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = torch.device("cuda", local)
+    kvh = KV_HEADS // world
+    heads = HEADS // world
+    DT = pam.PagedAttentionDataType
+
+    lens = workload_lengths()
+    nblk = (lens + BLOCK - 1) // BLOCK
+    n_pool = int(nblk.sum()) + SPARE_BLOCKS
+    engine = pam.PagedAttentionEngine(local)
+    stream = torch.cuda.current_stream(dev)
+    engine.setStream(stream.cuda_stream)
+    cache = pam.KVCacheManager(engine, n_pool, BLOCK, HEAD_DIM, kvh, DT.float16)
+    scramble_free_list(cache, n_pool, np.random.default_rng(SEED + 2))
+    ids = list(range(BATCH))
+    gen = torch.Generator(device=dev)
+    for sid in ids:
+        L = int(lens[sid])
+        cache.allocateSequence(sid)
+        cache.appendTokens(sid, L)
+        gen.manual_seed(SEED * 1000 + sid)
+        # the full [L][KV_HEADS][D] tensor of the sequence, of which this GPU keeps its heads
+        kv = torch.randn((2, L, KV_HEADS, HEAD_DIM), generator=gen, device=dev, dtype=torch.float32)
+        kv = kv[:, :, rank * kvh:(rank + 1) * kvh, :].to(torch.float16).contiguous()
+        engine.appendKV(cache, sid, kv[0], kv[1], 0, L, heads)
+    gen.manual_seed(SEED * 1000 + 999983)
+    q_full = torch.randn((BATCH, HEADS, HEAD_DIM), generator=gen, device=dev, dtype=torch.float32).to(torch.float16)
+    q_dev = q_full[:, rank * heads:(rank + 1) * heads, :].contiguous()
+    out_dev = torch.empty_like(q_dev)
+    max_nb = int(nblk.max())
+    tables_h, lens_h = cache.batchTables(ids, max_nb)
+    assert np.array_equal(lens_h.astype(np.int64), lens)
+    tables_dev = torch.from_numpy(tables_h).to(dev)
+    lens_dev = torch.from_numpy(lens_h.view(np.int32)).to(dev)
+    layer = pam.PagedLayerSpec(HEAD_DIM, heads, kvh, BLOCK, DT.float16)
+    req = pam.PagedAttentionDecodeRequest(q_dev, cache.kPoolBuffer, cache.vPoolBuffer, tables_dev, lens_dev, out_dev,
+                                          BATCH, max_nb, layer)
+    q_pin = torch.empty((BATCH, heads, HEAD_DIM), dtype=torch.float16, pin_memory=True)
+    q_pin.copy_(q_dev)
+    out_pin = torch.empty_like(q_pin, pin_memory=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # correctness guard on two sequences against the oracle (rank 0, its own heads)
+    engine.decode(req)
+    if rank == 0:
+        from oracle import c_oracle as co
+        chk = [int(np.argmin(lens)), 3]
+        sub_tables, sub_lens = cache.batchTables(chk, max_nb)
+        # gather the pages of the two sequences into a small pool for the oracle
+        used = np.unique(np.concatenate([sub_tables[i, : (int(sub_lens[i]) + BLOCK - 1) // BLOCK] for i in range(2)]))
+        remap = {int(b): i for i, b in enumerate(used)}
+        pools = []
+        for pb in (cache.kPoolBuffer, cache.vPoolBuffer):
+            page_elems = kvh * BLOCK * HEAD_DIM
+            small = np.empty((len(used), kvh, BLOCK, HEAD_DIM), np.float16)
+            from pagedattentionmetal_b200._cabi import lib
+            for i, b in enumerate(used):
+                lib.pamc_memcpy(engine._ctx, small[i].ctypes.data, pb.ptr + int(b) * page_elems * 2, page_elems * 2, 1)
+            pools.append(small)
+        t2 = np.vectorize(lambda b: remap.get(int(b), 0))(sub_tables).astype(np.int32)
+        ref = co.decode(q_dev[chk].cpu().numpy(), pools[0], pools[1], t2, sub_lens, kvh, BLOCK, 1)
+        err = float(np.abs(out_dev[chk].float().cpu().numpy() - ref).max())
+        assert err <= 2e-3, f"decode differs from the oracle by {err}"
+
+    # ---- value: inputs resident in HBM, kernels only ----
+    engine.setAsync(True)
+    for _ in range(max(args.warmup, 3)):
+        engine.decode(req)
+    sampler = ClockSampler(local)
+    barrier()
+    sampler.start()
+    launches0 = engine.kernelLaunches
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        engine.decode(req)
+    e1.record(stream)
+    barrier()
+    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    ms_step = ms_total / args.steps
+    engine.setAsync(False)
+
+    # ---- e2e: the reference-shaped call with host buffers ----
+    for _ in range(max(args.warmup, 3)):
+        engine.decodeBatch(cache, ids, q_pin.data_ptr(), out_pin.data_ptr(), heads)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        engine.decodeBatch(cache, ids, q_pin.data_ptr(), out_pin.data_ptr(), heads)
+    barrier()
+    e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3) / args.steps
+    launches = engine.kernelLaunches - launches0
+    clocks = sampler.stop()
+    assert torch.equal(out_pin.to(dev), out_dev), "host-buffer path and device path disagree"
+
+    if rank == 0:
+        peak, peak_kind = measured_hbm_peak()
+        bytes_gpu = algorithmic_bytes(lens, heads, kvh)
+        achieved = bytes_gpu / (ms_step * 1e-3) / 1e9
+        cpu = time_cpu_path(lens, 2, 1) if world == 1 else None
+        io_bytes = BATCH * heads * HEAD_DIM * 2
+        line = {
+            "metric": "paged decode tokens/s", "value": BATCH / (ms_step * 1e-3), "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": config_dict(world),
+            "kv_read_gbs_total": achieved * world,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_source": f"{peak_kind} copy bandwidth", "per": "GPU",
+                         "kernel": "decodeSplitKernel (+ decodeMergeKernel, same timed step)",
+                         "algorithmic_bytes_per_launch": bytes_gpu, "traffic": None},
+            "e2e": {"value": BATCH / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": io_bytes + tables_h.nbytes + lens_h.nbytes, "d2h_bytes_per_step": io_bytes,
+                    "call": "pam_decode with pinned host q/out; block tables rebuilt and uploaded per call"},
+            "gpu_launches": int(launches), "clocks": clocks,
+        }
+        if cpu:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line))
+    cache.close()
+    engine.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,152 @@
+"""Paged decode on the GPU against the oracle and the golden vectors."""
+import os
+
+import numpy as np
+import pytest
+
+import pagedattentionmetal_b200 as pam
+from gpu_helpers import DT, TOL, DecodeCase, from_io, max_abs
+from oracle import paged_oracle as po
+from test_oracle import c0_inputs
+
+pytestmark = pytest.mark.gpu
+
+
+def _flat_decode_f32(engine, q, k_pool, v_pool, tables, lens, kvh, bs, window=0):
+    B, H, D = q.shape
+    out = np.zeros_like(q)
+    req = pam.PagedAttentionDecodeRequest(q, engine.makeBufferFrom(k_pool), engine.makeBufferFrom(v_pool), tables,
+                                          lens, out, B, tables.shape[1],
+                                          pam.PagedLayerSpec(D, H, kvh, bs, DT.float32, window))
+    engine.decode(req)
+    return out
+
+
+def test_golden_decode_small(engine, golden_dir):
+    g = np.load(os.path.join(golden_dir, "decode_small.npz"))
+    out = _flat_decode_f32(engine, g["q"], g["k_pool"], g["v_pool"], g["tables"], g["lens"], 2, 16)
+    assert max_abs(out, g["out"]) < 1e-4
+
+
+def test_golden_decode_c0(engine, golden_dir):
+    """The CPU-runnable benchmark configuration against the outputs of the
+    reference's numpy implementation: max-abs <= 2e-3."""
+    g = np.load(os.path.join(golden_dir, "decode_c0.npz"))
+    q, k_pool, v_pool, tables, lens = c0_inputs()
+    out = _flat_decode_f32(engine, q, k_pool, v_pool, tables, lens, 8, 16)
+    assert max_abs(out, g["out"]) <= 2e-3
+    assert engine.lastStats.operation == pam.Operation.decode and engine.lastStats.batchSize == 8
+
+
+@pytest.mark.parametrize("dtype", [DT.float16, DT.bfloat16])
+@pytest.mark.parametrize("heads,kv_heads,head_dim,block_size", [
+    (8, 2, 128, 16),      # GQA 4
+    (16, 2, 128, 16),     # GQA 8
+    (32, 2, 128, 16),     # GQA 16: both halves of the MMA tile
+    (2, 2, 128, 16),      # MHA
+    (6, 2, 128, 16),      # GQA 3
+    (8, 2, 64, 16),       # head_dim 64
+    (8, 2, 128, 32),      # two tiles per page
+    (24, 2, 64, 48),      # GQA 12, three tiles per page
+])
+def test_fast_decode_matches_oracle(engine, dtype, heads, kv_heads, head_dim, block_size):
+    case = DecodeCase(11, 7, 1, 333, heads, kv_heads, head_dim, block_size, dtype)
+    out = case.run(engine)
+    assert max_abs(out, case.oracle()) <= TOL[dtype]
+    assert np.isfinite(out).all()
+
+
+@pytest.mark.parametrize("dtype", [DT.float16, DT.bfloat16, DT.float8, DT.float32])
+@pytest.mark.parametrize("window", [1, 16, 17, 100, 4096])
+def test_sliding_window(engine, dtype, window):
+    case = DecodeCase(12, 5, 1, 400, 8, 2, 128, 16, dtype)
+    out = case.run(engine, window=window)
+    assert max_abs(out, case.oracle(window=window)) <= TOL[dtype]
+
+
+def test_split_k_many_splits(engine):
+    """Few sequences with long contexts: the plan cuts each into many splits
+    and the merge kernel combines them."""
+    case = DecodeCase(13, 2, 5000, 9000, 8, 2, 128, 16, DT.float16)
+    out = case.run(engine)
+    assert max_abs(out, case.oracle()) <= TOL[DT.float16]
+    assert engine.lastStats.temporaryBytes > 0
+    case = DecodeCase(14, 1, 3000, 3000, 16, 1, 128, 16, DT.bfloat16)
+    out = case.run(engine, window=1000)
+    assert max_abs(out, case.oracle(window=1000)) <= TOL[DT.bfloat16]
+
+
+@pytest.mark.parametrize("dtype,heads,kv_heads,head_dim,block_size", [
+    (DT.float8, 8, 2, 128, 16),
+    (DT.float8, 16, 2, 128, 16),
+    (DT.float8, 4, 4, 64, 8),
+    (DT.float32, 4, 2, 32, 4),
+    (DT.float32, 12, 4, 256, 16),
+    (DT.float16, 8, 2, 96, 16),       # head_dim outside the fast path
+    (DT.float16, 8, 2, 128, 8),       # block size outside the fast path
+    (DT.bfloat16, 40, 2, 128, 16),    # GQA 20: more heads per KV head than one MMA tile
+])
+def test_general_decode_matches_oracle(engine, dtype, heads, kv_heads, head_dim, block_size):
+    case = DecodeCase(15, 4, 1, 150, heads, kv_heads, head_dim, block_size, dtype)
+    out = case.run(engine)
+    assert max_abs(out, case.oracle()) <= TOL[dtype]
+
+
+def test_edge_lengths(engine):
+    """Length 0 (0/0 in the reference: zeros here), 1, exact tile and block
+    multiples, and a length larger than the table can hold (clamped like
+    kernels.metal:1451-1452)."""
+    for dtype in (DT.float16, DT.float32):
+        case = DecodeCase(16, 6, 1, 1, 8, 2, 128, 16, dtype, lens=[0, 1, 16, 17, 32, 48])
+        out = case.run(engine)
+        ref = case.oracle()
+        assert np.all(out[0] == 0)
+        assert max_abs(out[1:], ref[1:]) <= TOL[dtype]
+    case = DecodeCase(17, 2, 1, 1, 8, 2, 128, 16, DT.float16, lens=[40, 64])
+    case.tables = np.ascontiguousarray(case.tables[:, :3])          # room for 48 tokens only
+    out = case.run(engine)
+    assert max_abs(out, case.oracle()) <= TOL[DT.float16]
+
+
+def test_host_buffers_are_staged(engine):
+    case = DecodeCase(18, 4, 10, 200, 8, 2, 128, 16, DT.float16)
+    out = case.run(engine, host_io=True)
+    assert max_abs(out, case.oracle()) <= TOL[DT.float16]
+
+
+def test_reference_cabi_decode_end_to_end(engine):
+    """pam_reserve_sequence / pam_append_tokens / pam_append_kv / pam_decode with
+    host buffers, the call sequence of the reference's C ABI."""
+    rng = np.random.default_rng(19)
+    H, KVH, D, bs = 8, 2, 128, 16
+    cache = pam.KVCacheManager(engine, 64, bs, D, KVH, DT.float16)
+    lens = [37, 5, 80]
+    ks, vs = {}, {}
+    for sid, L in enumerate(lens):
+        cache.allocateSequence(sid)
+        cache.appendTokens(sid, L)
+        ks[sid] = rng.standard_normal((L, KVH, D)).astype(np.float16)
+        vs[sid] = rng.standard_normal((L, KVH, D)).astype(np.float16)
+        # append in two pieces to exercise token offsets
+        cut = L // 2
+        if cut:
+            engine.appendKV(cache, sid, ks[sid][:cut], vs[sid][:cut], 0, cut, H)
+        engine.appendKV(cache, sid, ks[sid][cut:], vs[sid][cut:], cut, L - cut, H)
+    q = rng.standard_normal((3, H, D)).astype(np.float16)
+    out = np.zeros_like(q)
+    engine.decodeBatch(cache, [2, 0, 1], q, out, H)
+    # oracle on its own pools, filled by its own scatter
+    kp = np.zeros((64, KVH, bs, D), np.float16)
+    vp = np.zeros_like(kp)
+    tabs = []
+    for sid, L in enumerate(lens):
+        t = cache.getBlockTable(sid)
+        tabs.append(t)
+        po.reshape_and_cache(kp, vp, ks[sid], vs[sid], po.slot_mapping(t, 0, L, bs), bs)
+    gk, gv, _, _ = cache.readPools()
+    assert np.array_equal(gk, kp) and np.array_equal(gv, vp)
+    tables, l = cache.batchTables([2, 0, 1], 5)
+    from oracle import c_oracle as co
+    ref = co.decode(q, kp, vp, tables, l, KVH, bs, 1)
+    assert max_abs(out.astype(np.float32), ref) <= TOL[DT.float16]
+    cache.close()

@@ -1,0 +1,183 @@
+"""Paged prefill (whole sequence, chunks, batches of chunks, windows, prefix
+sharing) on the GPU against the oracle and the golden vectors."""
+import os
+
+import numpy as np
+import pytest
+
+import pagedattentionmetal_b200 as pam
+from gpu_helpers import DT, TOL, from_io, io_numpy_dtype, max_abs, quantize_pool, to_storage
+from oracle import c_oracle as co
+from oracle import paged_oracle as po
+
+pytestmark = pytest.mark.gpu
+
+
+class PrefillCase:
+    def __init__(self, seed, seq_len, heads, kv_heads, head_dim, block_size, dtype, spare=2):
+        rng = np.random.default_rng(seed)
+        self.S, self.H, self.KVH, self.D, self.bs, self.dtype = seq_len, heads, kv_heads, head_dim, block_size, dtype
+        nb = (seq_len + block_size - 1) // block_size
+        self.n_pool = nb + spare
+        self.table = rng.permutation(self.n_pool)[:nb].astype(np.int32)
+        shape = (self.n_pool, kv_heads, block_size, head_dim)
+        k32, v32 = rng.standard_normal(shape, dtype=np.float32), rng.standard_normal(shape, dtype=np.float32)
+        self.k_scale = self.v_scale = None
+        if dtype == DT.float8:
+            self.k_pool, self.k_scale = quantize_pool(k32)
+            self.v_pool, self.v_scale = quantize_pool(v32)
+        else:
+            self.k_pool, self.v_pool = to_storage(k32, dtype), to_storage(v32, dtype)
+        self.q = to_storage(rng.standard_normal((seq_len, heads, head_dim), dtype=np.float32), dtype)
+
+    def layer(self, window=0):
+        return pam.PagedLayerSpec(self.D, self.H, self.KVH, self.bs, self.dtype, window)
+
+    def oracle(self, causal=True, window=0, q_start=0, q_len=None):
+        q_len = self.S - q_start if q_len is None else q_len
+        ws = max(0, self.S - window) if window > 0 else 0           # PagedAttentionEngine.swift:802
+        ks = None if self.k_scale is None else self.k_scale.view(np.uint16)
+        vs = None if self.v_scale is None else self.v_scale.view(np.uint16)
+        return co.prefill(self.q[q_start:q_start + q_len], self.k_pool, self.v_pool, self.table, self.S, self.KVH,
+                          self.bs, int(self.dtype), causal=causal, window_start=ws, q_start=q_start,
+                          k_scale=ks, v_scale=vs)
+
+    def run(self, engine, causal=True, window=0, q_start=0, q_len=0, chunk=0, host_io=False):
+        kp, vp = engine.makeBufferFrom(self.k_pool), engine.makeBufferFrom(self.v_pool)
+        ks = engine.makeBufferFrom(self.k_scale) if self.k_scale is not None else None
+        vs = engine.makeBufferFrom(self.v_scale) if self.v_scale is not None else None
+        rows = q_len if q_len else self.S
+        qh = np.ascontiguousarray(self.q[q_start:q_start + rows])
+        out_host = np.zeros(qh.shape, dtype=io_numpy_dtype(self.dtype))
+        if host_io:
+            q, out, table = qh, out_host, self.table
+        else:
+            q, out, table = engine.makeBufferFrom(qh), engine.makeBuffer(out_host.nbytes), engine.makeBufferFrom(self.table)
+        req = pam.PagedAttentionPrefillRequest(q, kp, vp, table, out, self.S, self.layer(window), causal, ks, vs,
+                                               q_start, q_len)
+        engine.prefill(req, chunk)
+        if not host_io:
+            out_host = out.download(out_host.dtype, out_host.shape)
+        return from_io(out_host, self.dtype)
+
+
+def test_golden_prefill_small(engine, golden_dir):
+    g = np.load(os.path.join(golden_dir, "prefill_small.npz"))
+    kp, vp = engine.makeBufferFrom(g["k_pool"]), engine.makeBufferFrom(g["v_pool"])
+    for causal, key in ((False, "out_full"), (True, "out_causal")):
+        out = np.zeros_like(g["q"])
+        engine.prefill(pam.PagedAttentionPrefillRequest(g["q"], kp, vp, g["table"], out, 40,
+                                                        pam.PagedLayerSpec(16, 4, 2, 8, DT.float32), causal))
+        assert max_abs(out, g[key]) < 1e-4
+
+
+@pytest.mark.parametrize("dtype", [DT.float16, DT.bfloat16, DT.float32, DT.float8])
+@pytest.mark.parametrize("causal", [True, False])
+def test_prefill_matches_oracle(engine, dtype, causal):
+    case = PrefillCase(31, 150, 8, 2, 128, 16, dtype)
+    out = case.run(engine, causal=causal)
+    assert max_abs(out, case.oracle(causal=causal)) <= TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", [DT.float16, DT.bfloat16])
+@pytest.mark.parametrize("seq_len,heads,kv_heads,head_dim,block_size", [
+    (1, 4, 2, 128, 16), (16, 4, 4, 128, 16), (129, 8, 2, 128, 16), (300, 16, 2, 128, 16),
+    (257, 8, 2, 64, 16), (200, 8, 2, 128, 32), (77, 6, 2, 96, 8),
+])
+def test_prefill_shapes(engine, dtype, seq_len, heads, kv_heads, head_dim, block_size):
+    case = PrefillCase(32, seq_len, heads, kv_heads, head_dim, block_size, dtype)
+    out = case.run(engine)
+    assert max_abs(out, case.oracle()) <= TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", [DT.float16, DT.bfloat16])
+def test_chunked_prefill_equals_full(engine, dtype):
+    """Rows of a chunk equal the same rows of a full prefill
+    (PagedAttentionEngine.swift:740-756), through q_start/q_len and through the
+    engine's chunk loop."""
+    case = PrefillCase(33, 400, 8, 2, 128, 16, dtype)
+    full = case.oracle()
+    for q_start, q_len in ((0, 128), (128, 128), (256, 144), (399, 1), (100, 37)):
+        out = case.run(engine, q_start=q_start, q_len=q_len)
+        assert max_abs(out, full[q_start:q_start + q_len]) <= TOL[dtype]
+    out = case.run(engine, chunk=128)
+    assert max_abs(out, full) <= TOL[dtype]
+    engine.defaultChunkSize = 96
+    out = case.run(engine, host_io=True)
+    engine.defaultChunkSize = 0
+    assert max_abs(out, full) <= TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", [DT.float16, DT.float8])
+@pytest.mark.parametrize("window", [16, 64, 256])
+def test_prefill_window(engine, dtype, window):
+    """One window start for all rows, max(0, S - W) (PagedAttentionEngine.swift:802);
+    causal rows before the window see no key and are don't-care (zeros here)."""
+    case = PrefillCase(34, 208, 8, 2, 128, 16, dtype)
+    ref = case.oracle(window=window)
+    out = case.run(engine, window=window)
+    ws = max(0, 208 - window)
+    assert max_abs(out[ws:], ref[ws:]) <= TOL[dtype]
+    assert np.all(out[:ws] == 0)
+    ref = case.oracle(causal=False, window=window)
+    out = case.run(engine, causal=False, window=window)
+    assert max_abs(out, ref) <= TOL[dtype]
+
+
+def test_batch_prefill_with_shared_prefix(engine):
+    """Several sequences sharing prefix pages (refcounted by the manager), one
+    chunk each in a single launch; every row equals the oracle's."""
+    rng = np.random.default_rng(35)
+    n_seq, prefix, total, chunk, H, KVH, D, bs = 4, 64, 160, 48, 8, 2, 128, 16
+    dtype = DT.bfloat16
+    cache = pam.KVCacheManager(engine, 64, bs, D, KVH, dtype)
+    shared_k = rng.standard_normal((prefix, KVH, D), dtype=np.float32)
+    shared_v = rng.standard_normal((prefix, KVH, D), dtype=np.float32)
+    ks, vs, qs = [], [], []
+    for s in range(n_seq):
+        k = np.concatenate([shared_k, rng.standard_normal((total - prefix, KVH, D), dtype=np.float32)])
+        v = np.concatenate([shared_v, rng.standard_normal((total - prefix, KVH, D), dtype=np.float32)])
+        ks.append(to_storage(k, dtype)); vs.append(to_storage(v, dtype))
+        qs.append(to_storage(rng.standard_normal((total, H, D), dtype=np.float32), dtype))
+        cache.allocateSequence(s)
+        cache.appendTokens(s, prefix, list(range(prefix // bs)))
+        if s == 0:
+            engine.appendKV(cache, 0, ks[0][:prefix], vs[0][:prefix], 0, prefix, H)       # written once
+        cache.appendTokens(s, total - prefix)
+        engine.appendKV(cache, s, ks[s][prefix:], vs[s][prefix:], prefix, total - prefix, H)
+    assert cache.memoryStats().sharedBlocks == prefix // bs
+    assert cache.memoryStats().prefixCacheHits == (n_seq - 1) * (prefix // bs)
+    tables, lens = cache.batchTables(list(range(n_seq)), total // bs)
+    gk, gv, _, _ = cache.readPools()
+    q_starts = [64, 96, 112, 64]
+    q_lens = [chunk, chunk, chunk, 17]
+    q_cat = np.concatenate([qs[s][q_starts[s]:q_starts[s] + q_lens[s]] for s in range(n_seq)])
+    out = np.zeros(q_cat.shape, dtype=np.uint16)
+    engine.prefillBatch(q_cat, cache.kPoolBuffer, cache.vPoolBuffer, tables, out, [total] * n_seq, q_starts, q_lens,
+                        total // bs, pam.PagedLayerSpec(D, H, KVH, bs, dtype))
+    o = 0
+    for s in range(n_seq):
+        ref = co.prefill(qs[s][q_starts[s]:q_starts[s] + q_lens[s]], gk, gv, tables[s], total, KVH, bs, int(dtype),
+                         q_start=q_starts[s])
+        assert max_abs(from_io(out[o:o + q_lens[s]], dtype), ref) <= TOL[dtype]
+        o += q_lens[s]
+    cache.close()
+
+
+def test_reference_cabi_prefill(engine):
+    rng = np.random.default_rng(36)
+    H, KVH, D, bs, S = 4, 2, 128, 16, 70
+    cache = pam.KVCacheManager(engine, 8, bs, D, KVH, DT.float16)
+    cache.allocateSequence(5)
+    cache.appendTokens(5, S)
+    k = rng.standard_normal((S, KVH, D)).astype(np.float16)
+    v = rng.standard_normal((S, KVH, D)).astype(np.float16)
+    q = rng.standard_normal((S, H, D)).astype(np.float16)
+    engine.appendKV(cache, 5, k, v, 0, S, H)
+    out = np.zeros_like(q)
+    engine.prefillSequence(cache, 5, q, out, S, H, True)
+    gk, gv, _, _ = cache.readPools()
+    ref = co.prefill(q, gk, gv, np.array(cache.getBlockTable(5), np.int32), S, KVH, bs, 1)
+    assert max_abs(out.astype(np.float32), ref) <= TOL[DT.float16]
+    assert engine.lastStats.sequenceLength == S and engine.lastStats.numBlocks == 5
+    cache.close()
