@@ -166,6 +166,8 @@ def buffer(ptr, nbytes=None) -> PamBuffer:
         return PamBuffer(None, 0)
     if hasattr(ptr, "ctypes") and hasattr(ptr, "nbytes"):          # numpy
         return PamBuffer(ptr.ctypes.data, ptr.nbytes if nbytes is None else nbytes)
+    if hasattr(ptr, "data_ptr") and hasattr(ptr, "nbytes") and not hasattr(ptr, "numel"):
+        return PamBuffer(ptr.data_ptr(), ptr.nbytes if nbytes is None else nbytes)
     if hasattr(ptr, "data_ptr"):                                   # torch
         n = ptr.numel() * ptr.element_size()
         return PamBuffer(ptr.data_ptr(), n if nbytes is None else nbytes)

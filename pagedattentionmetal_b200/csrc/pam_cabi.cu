@@ -330,7 +330,8 @@ int32_t runCopies(Context* c, Cache* k, const std::vector<std::pair<int32_t, int
     return 0;
 }
 
-int32_t appendImpl(Context* c, const PamAppendRequest& rq, Cache* cacheForScratch, const int64_t* hostSlots) {
+int32_t appendImpl(Context* c, const PamAppendRequest& rq, Cache* cacheForScratch, const int64_t* hostSlots,
+                   const int64_t* deviceSlots = nullptr) {
     // PagedAttentionEngine.swift:585-628; validateAppend :1935-1950
     if (!validateLayer(c, rq.layer)) return -1;
     if (rq.token_offset < 0) return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("tokenOffset must be non-negative."));
@@ -342,7 +343,7 @@ int32_t appendImpl(Context* c, const PamAppendRequest& rq, Cache* cacheForScratc
     const size_t newBytes = static_cast<size_t>(T) * l.num_kv_heads * l.head_dim * pam::ioBytes(l.data_type);
     if (!requireBuffer(c, rq.keys, "new keys", static_cast<size_t>(T) * kvBytesPerToken(l))) return -1;
     if (!requireBuffer(c, rq.values, "new values", static_cast<size_t>(T) * kvBytesPerToken(l))) return -1;
-    if (!hostSlots && !requireBuffer(c, rq.block_table, "blockTable", numBlocks * sizeof(int32_t))) return -1;
+    if (!hostSlots && !deviceSlots && !requireBuffer(c, rq.block_table, "blockTable", numBlocks * sizeof(int32_t))) return -1;
     if (!requireBuffer(c, rq.k_pool, "K pool", numBlocks * l.block_size * kvBytesPerToken(l))) return -1;
     if (!requireBuffer(c, rq.v_pool, "V pool", numBlocks * l.block_size * kvBytesPerToken(l))) return -1;
     const bool fp8 = l.data_type == PAM_DTYPE_FP8;
@@ -364,7 +365,8 @@ int32_t appendImpl(Context* c, const PamAppendRequest& rq, Cache* cacheForScratc
         const void* values = st.in(rq.values.ptr, newBytes);
         pam::SlotSource src;
         src.numSlots = poolSlots;
-        if (hostSlots) src.slots = static_cast<const int64_t*>(st.upload(hostSlots, sizeof(int64_t) * T));
+        if (deviceSlots) src.slots = deviceSlots;
+        else if (hostSlots) src.slots = static_cast<const int64_t*>(st.upload(hostSlots, sizeof(int64_t) * T));
         else {
             src.table = static_cast<const int32_t*>(st.in(rq.block_table.ptr, numBlocks * sizeof(int32_t)));
             src.tokenOffset = rq.token_offset;
@@ -1019,27 +1021,21 @@ int32_t pamc_reshape_and_cache(void* ctx, void* cache, const void* keys, const v
     rq.token_offset = 0; rq.num_new_tokens = num_tokens;
     rq.layer = layerOf(k, k->kvHeads);
     rq.k_scale = buf(k->kScale, k->scaleBytes); rq.v_scale = buf(k->vScale, k->scaleBytes);
-    std::vector<int64_t> hostSlots;
-    const int64_t* slots = slot_mapping;
-    if (isDevicePointer(slot_mapping)) {
-        hostSlots.resize(static_cast<size_t>(num_tokens));
-        if (cudaMemcpyAsync(hostSlots.data(), slot_mapping, sizeof(int64_t) * num_tokens, cudaMemcpyDeviceToHost, c->stream) != cudaSuccess ||
-            cudaStreamSynchronize(c->stream) != cudaSuccess) {
-            cudaGetLastError();
-            return c->fail(PAM_ERR_COMMAND_EXECUTION, commandExecutionFailed("slot mapping copy failed"));
-        }
-        slots = hostSlots.data();
+    // Host slot lists are checked here; device lists are checked by the kernel,
+    // which skips tokens whose slot lies outside the pool.
+    const bool onDevice = isDevicePointer(slot_mapping);
+    if (!onDevice) {
+        const int64_t poolSlots = static_cast<int64_t>(k->maxBlocks) * k->blockSize;
+        for (int i = 0; i < num_tokens; ++i)
+            if (slot_mapping[i] < 0 || slot_mapping[i] >= poolSlots)
+                return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("slot " + std::to_string(slot_mapping[i]) + " lies outside the pool"));
     }
-    const int64_t poolSlots = static_cast<int64_t>(k->maxBlocks) * k->blockSize;
-    for (int i = 0; i < num_tokens; ++i)
-        if (slots[i] < 0 || slots[i] >= poolSlots)
-            return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("slot " + std::to_string(slots[i]) + " lies outside the pool"));
     // appendImpl's pool lower bound is counted from token_offset + tokens; the
     // slots were checked against the pool above, so keep that bound trivial.
     rq.num_new_tokens = num_tokens;
     PamAppendRequest small = rq;
     small.k_pool.bytes = kUnknownBytes; small.v_pool.bytes = kUnknownBytes;
-    int32_t rc = appendImpl(c, small, k, slots);
+    int32_t rc = appendImpl(c, small, k, onDevice ? nullptr : slot_mapping, onDevice ? slot_mapping : nullptr);
     if (rc == 0) c->clearError();
     return rc;
 }

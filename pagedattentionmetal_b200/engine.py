@@ -56,6 +56,9 @@ class DeviceBuffer:
     def length(self) -> int:
         return self.nbytes
 
+    def data_ptr(self) -> int:
+        return self.ptr
+
     def upload(self, array: np.ndarray, offset: int = 0) -> "DeviceBuffer":
         a = np.ascontiguousarray(array)
         assert offset + a.nbytes <= self.nbytes

@@ -15,7 +15,8 @@ pytestmark = pytest.mark.gpu
 @pytest.mark.parametrize("kv_heads,head_dim,block_size", [(8, 128, 16), (2, 64, 4), (3, 20, 5)])
 def test_reshape_and_cache_bit_exact(engine, dtype, kv_heads, head_dim, block_size):
     rng = np.random.default_rng(21)
-    nblk, T = 50, 333
+    T = 333
+    nblk = T // block_size + 30
     cache = pam.KVCacheManager(engine, nblk, block_size, head_dim, kv_heads, dtype)
     k = to_storage(rng.standard_normal((T, kv_heads, head_dim), dtype=np.float32), dtype)
     v = to_storage(rng.standard_normal((T, kv_heads, head_dim), dtype=np.float32), dtype)
@@ -38,7 +39,8 @@ def test_fp8_append_bit_exact(engine, kv_heads, head_dim, block_size):
     """Codes and scales after three appends (fresh groups, groups that grow,
     groups whose absmax shrinks) equal the oracle's, bit for bit."""
     rng = np.random.default_rng(22)
-    nblk, T = 40, 400
+    T = 400
+    nblk = T // block_size + 15
     cache = pam.KVCacheManager(engine, nblk, block_size, head_dim, kv_heads, DT.float8)
     kc = np.zeros((nblk, kv_heads, block_size, head_dim), np.uint8)
     vc = np.zeros_like(kc)
@@ -86,7 +88,14 @@ def test_fp8_quantiser_all_halves(engine):
         co.reshape_and_cache_fp8(x, x[::-1].copy(), kc, vc, ks.view(np.uint16), vs.view(np.uint16), slots, 1)
         gk, gv, gks, gvs = cache.readPools()
         assert np.array_equal(gks, ks) and np.array_equal(gvs, vs)
-        assert np.array_equal(gk, kc) and np.array_equal(gv, vc)
+        # A group whose absmax is below 448 * 2^-25 gets the half scale 0; a zero
+        # in such a group is 0/0, which the reference leaves undefined
+        # (kernels.metal:565-566, clamp of a NaN).  Everything else must match.
+        xr = x[::-1]
+        defined_k = ~((ks[:, :, None, None] == 0) & (x.reshape(kc.shape) == 0))
+        defined_v = ~((vs[:, :, None, None] == 0) & (xr.reshape(vc.shape) == 0))
+        assert np.array_equal(gk[defined_k], kc[defined_k]) and np.array_equal(gv[defined_v], vc[defined_v])
+        assert defined_k.mean() > 0.99
         cache.close()
 
 

@@ -5,7 +5,7 @@ import numpy as np
 import pytest
 
 import pagedattentionmetal_b200 as pam
-from gpu_helpers import DT, TOL, DecodeCase, from_io, max_abs
+from gpu_helpers import DT, TOL, DecodeCase, assert_close, from_io, max_abs
 from oracle import paged_oracle as po
 from test_oracle import c0_inputs
 
@@ -52,7 +52,7 @@ def test_golden_decode_c0(engine, golden_dir):
 def test_fast_decode_matches_oracle(engine, dtype, heads, kv_heads, head_dim, block_size):
     case = DecodeCase(11, 7, 1, 333, heads, kv_heads, head_dim, block_size, dtype)
     out = case.run(engine)
-    assert max_abs(out, case.oracle()) <= TOL[dtype]
+    assert_close(out, case.oracle(), dtype)
     assert np.isfinite(out).all()
 
 
@@ -61,7 +61,7 @@ def test_fast_decode_matches_oracle(engine, dtype, heads, kv_heads, head_dim, bl
 def test_sliding_window(engine, dtype, window):
     case = DecodeCase(12, 5, 1, 400, 8, 2, 128, 16, dtype)
     out = case.run(engine, window=window)
-    assert max_abs(out, case.oracle(window=window)) <= TOL[dtype]
+    assert_close(out, case.oracle(window=window), dtype)
 
 
 def test_split_k_many_splits(engine):
@@ -69,11 +69,11 @@ def test_split_k_many_splits(engine):
     and the merge kernel combines them."""
     case = DecodeCase(13, 2, 5000, 9000, 8, 2, 128, 16, DT.float16)
     out = case.run(engine)
-    assert max_abs(out, case.oracle()) <= TOL[DT.float16]
+    assert_close(out, case.oracle(), DT.float16)
     assert engine.lastStats.temporaryBytes > 0
     case = DecodeCase(14, 1, 3000, 3000, 16, 1, 128, 16, DT.bfloat16)
     out = case.run(engine, window=1000)
-    assert max_abs(out, case.oracle(window=1000)) <= TOL[DT.bfloat16]
+    assert_close(out, case.oracle(window=1000), DT.bfloat16)
 
 
 @pytest.mark.parametrize("dtype,heads,kv_heads,head_dim,block_size", [
@@ -89,7 +89,7 @@ def test_split_k_many_splits(engine):
 def test_general_decode_matches_oracle(engine, dtype, heads, kv_heads, head_dim, block_size):
     case = DecodeCase(15, 4, 1, 150, heads, kv_heads, head_dim, block_size, dtype)
     out = case.run(engine)
-    assert max_abs(out, case.oracle()) <= TOL[dtype]
+    assert_close(out, case.oracle(), dtype)
 
 
 def test_edge_lengths(engine):
@@ -101,17 +101,17 @@ def test_edge_lengths(engine):
         out = case.run(engine)
         ref = case.oracle()
         assert np.all(out[0] == 0)
-        assert max_abs(out[1:], ref[1:]) <= TOL[dtype]
+        assert_close(out[1:], ref[1:], dtype)
     case = DecodeCase(17, 2, 1, 1, 8, 2, 128, 16, DT.float16, lens=[40, 64])
     case.tables = np.ascontiguousarray(case.tables[:, :3])          # room for 48 tokens only
     out = case.run(engine)
-    assert max_abs(out, case.oracle()) <= TOL[DT.float16]
+    assert_close(out, case.oracle(), DT.float16)
 
 
 def test_host_buffers_are_staged(engine):
     case = DecodeCase(18, 4, 10, 200, 8, 2, 128, 16, DT.float16)
     out = case.run(engine, host_io=True)
-    assert max_abs(out, case.oracle()) <= TOL[DT.float16]
+    assert_close(out, case.oracle(), DT.float16)
 
 
 def test_reference_cabi_decode_end_to_end(engine):
@@ -148,5 +148,5 @@ def test_reference_cabi_decode_end_to_end(engine):
     tables, l = cache.batchTables([2, 0, 1], 5)
     from oracle import c_oracle as co
     ref = co.decode(q, kp, vp, tables, l, KVH, bs, 1)
-    assert max_abs(out.astype(np.float32), ref) <= TOL[DT.float16]
+    assert_close(out.astype(np.float32), ref, DT.float16)
     cache.close()

@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 
 import pagedattentionmetal_b200 as pam
-from gpu_helpers import DT, TOL, from_io, io_numpy_dtype, max_abs, quantize_pool, to_storage
+from gpu_helpers import DT, TOL, assert_close, from_io, io_numpy_dtype, max_abs, quantize_pool, to_storage
 from oracle import c_oracle as co
 from oracle import paged_oracle as po
 
@@ -76,7 +76,7 @@ def test_golden_prefill_small(engine, golden_dir):
 def test_prefill_matches_oracle(engine, dtype, causal):
     case = PrefillCase(31, 150, 8, 2, 128, 16, dtype)
     out = case.run(engine, causal=causal)
-    assert max_abs(out, case.oracle(causal=causal)) <= TOL[dtype]
+    assert_close(out, case.oracle(causal=causal), dtype)
 
 
 @pytest.mark.parametrize("dtype", [DT.float16, DT.bfloat16])
@@ -87,7 +87,7 @@ def test_prefill_matches_oracle(engine, dtype, causal):
 def test_prefill_shapes(engine, dtype, seq_len, heads, kv_heads, head_dim, block_size):
     case = PrefillCase(32, seq_len, heads, kv_heads, head_dim, block_size, dtype)
     out = case.run(engine)
-    assert max_abs(out, case.oracle()) <= TOL[dtype]
+    assert_close(out, case.oracle(), dtype)
 
 
 @pytest.mark.parametrize("dtype", [DT.float16, DT.bfloat16])
@@ -99,13 +99,13 @@ def test_chunked_prefill_equals_full(engine, dtype):
     full = case.oracle()
     for q_start, q_len in ((0, 128), (128, 128), (256, 144), (399, 1), (100, 37)):
         out = case.run(engine, q_start=q_start, q_len=q_len)
-        assert max_abs(out, full[q_start:q_start + q_len]) <= TOL[dtype]
+        assert_close(out, full[q_start:q_start + q_len], dtype)
     out = case.run(engine, chunk=128)
-    assert max_abs(out, full) <= TOL[dtype]
+    assert_close(out, full, dtype)
     engine.defaultChunkSize = 96
     out = case.run(engine, host_io=True)
     engine.defaultChunkSize = 0
-    assert max_abs(out, full) <= TOL[dtype]
+    assert_close(out, full, dtype)
 
 
 @pytest.mark.parametrize("dtype", [DT.float16, DT.float8])
@@ -117,11 +117,11 @@ def test_prefill_window(engine, dtype, window):
     ref = case.oracle(window=window)
     out = case.run(engine, window=window)
     ws = max(0, 208 - window)
-    assert max_abs(out[ws:], ref[ws:]) <= TOL[dtype]
+    assert_close(out[ws:], ref[ws:], dtype)
     assert np.all(out[:ws] == 0)
     ref = case.oracle(causal=False, window=window)
     out = case.run(engine, causal=False, window=window)
-    assert max_abs(out, ref) <= TOL[dtype]
+    assert_close(out, ref, dtype)
 
 
 def test_batch_prefill_with_shared_prefix(engine):
@@ -159,7 +159,7 @@ def test_batch_prefill_with_shared_prefix(engine):
     for s in range(n_seq):
         ref = co.prefill(qs[s][q_starts[s]:q_starts[s] + q_lens[s]], gk, gv, tables[s], total, KVH, bs, int(dtype),
                          q_start=q_starts[s])
-        assert max_abs(from_io(out[o:o + q_lens[s]], dtype), ref) <= TOL[dtype]
+        assert_close(from_io(out[o:o + q_lens[s]], dtype), ref, dtype)
         o += q_lens[s]
     cache.close()
 
@@ -178,6 +178,6 @@ def test_reference_cabi_prefill(engine):
     engine.prefillSequence(cache, 5, q, out, S, H, True)
     gk, gv, _, _ = cache.readPools()
     ref = co.prefill(q, gk, gv, np.array(cache.getBlockTable(5), np.int32), S, KVH, bs, 1)
-    assert max_abs(out.astype(np.float32), ref) <= TOL[DT.float16]
+    assert_close(out.astype(np.float32), ref, DT.float16)
     assert engine.lastStats.sequenceLength == S and engine.lastStats.numBlocks == 5
     cache.close()
