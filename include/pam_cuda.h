@@ -297,6 +297,35 @@ typedef struct PamDecodeRequest {
 /* PagedAttentionEngine.decode (PagedAttentionEngine.swift:533-580) */
 int32_t pamc_decode(void *ctx, const PamDecodeRequest *request);
 
+/* Decode without any allocation.  No counterpart in the reference.
+ *
+ * For callers that must not allocate device memory while they run: code that
+ * is recording work to replay later, a serving loop that has handed all free
+ * memory to the KV pools, or a host that only ever gets pointers from another
+ * runtime's allocator and cannot reach cudaMalloc itself.  pamc_decode may grow
+ * the context's arena (for staged host buffers and for the split-K partial
+ * results); this entry point never does.  It calls no cudaMalloc, cudaFree or
+ * other allocating routine.
+ *
+ * Same request, checks, kernels and results as pamc_decode, with these limits:
+ *  - q, output, pools, block tables and lengths must all be device memory
+ *    (nothing is staged);
+ *  - the split-K partial results live in an 8 MiB array that is part of the
+ *    library image on every GPU that loads it (held until the process exits).
+ *    A request needs batch * heads * splits * (head_dim + 2) * 4 bytes of it,
+ *    where splits is what the library's split plan yields for the batch and
+ *    max_num_blocks; a request that needs more fails with
+ *    PAM_ERR_RESOURCE_EXHAUSTED and a message that states both numbers.
+ *  - The first call on each GPU looks up the array's device address (once per
+ *    device, with that device current).  Make that first call before starting
+ *    any stream capture.
+ *  - All calls on one GPU share the array and it keeps whatever the previous
+ *    call left there.  Nothing in it has to start at zero: every word a call
+ *    reads was written earlier by that same call.  Two such decodes that
+ *    overlap on one GPU (different streams or contexts) race on the array and
+ *    give wrong results; keep them ordered. */
+int32_t pamc_decode_noalloc(void *ctx, const PamDecodeRequest *request);
+
 /* PagedAttentionPrefillRequest (PagedAttentionTypes.swift:210-256) plus the row
  * range of one chunk: rows [q_start, q_start+q_len) of a sequence whose cache
  * holds seq_len tokens.  q/output hold q_len rows.  q_len = 0 means the whole

@@ -136,6 +136,7 @@ SIGNATURES = {
     "pamc_reshape_and_cache": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32]),
     "pamc_copy_blocks": (c_int32, [c_void_p, c_void_p, C.POINTER(c_int32), C.POINTER(c_int32), c_int32]),
     "pamc_decode": (c_int32, [c_void_p, C.POINTER(PamDecodeRequest)]),
+    "pamc_decode_noalloc": (c_int32, [c_void_p, C.POINTER(PamDecodeRequest)]),
     "pamc_prefill": (c_int32, [c_void_p, C.POINTER(PamPrefillRequest), c_int32]),
     "pamc_prefill_batch": (c_int32, [c_void_p, C.POINTER(PamBatchPrefillRequest)]),
     # scheduler

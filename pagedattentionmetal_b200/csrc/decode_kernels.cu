@@ -38,6 +38,12 @@ namespace {
 constexpr int kTileTokens = 16;
 constexpr float kLog2e = 1.4426950408889634f;
 
+// Split-K workspace for launchDecodeStatic(): device memory that belongs to the
+// library image itself, so that a decode can run without any allocation call.
+// Every GPU that loads the library holds these 8 MiB until the process exits.
+constexpr size_t kStaticScratchBytes = size_t(8) << 20;
+static __device__ __align__(256) float gStaticDecodeScratch[kStaticScratchBytes / sizeof(float)];
+
 // ---------------------------------------------------------------- PTX helpers
 
 __device__ __forceinline__ uint32_t smemAddr(const void* p) {
@@ -637,6 +643,30 @@ cudaError_t launchDecode(const DecodeParams& p, int smCount, cudaStream_t stream
         case kFP8: return launchGeneral<__half, uint8_t>(p, stream, launches);
     }
     return cudaErrorInvalidValue;
+}
+
+size_t decodeStaticScratchBytes() { return kStaticScratchBytes; }
+
+cudaError_t launchDecodeStatic(const DecodeParams& p, int smCount, cudaStream_t stream, int* launches) {
+    // In host code the array's name is only a handle; the kernels need its
+    // device address, which differs per GPU.  It is looked up once per device,
+    // with that device current (the caller has made it so).
+    static float* addressOnDevice[64] = {};
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (!addressOnDevice[dev]) {
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, gStaticDecodeScratch);
+        if (e != cudaSuccess) return e;
+        addressOnDevice[dev] = static_cast<float*>(ptr);
+    }
+    if (decodeWorkspaceBytes(p, smCount) > kStaticScratchBytes) return cudaErrorInvalidValue;
+    DecodeParams q = p;
+    q.workspace = addressOnDevice[dev];
+    q.workspaceBytes = kStaticScratchBytes;
+    return launchDecode(q, smCount, stream, launches);
 }
 
 }  // namespace pam

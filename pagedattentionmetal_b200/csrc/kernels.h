@@ -60,6 +60,13 @@ struct DecodeParams {
 // Bytes of split-K workspace the launch of `p` needs (0 when it runs unsplit).
 size_t decodeWorkspaceBytes(const DecodeParams& p, int smCount);
 cudaError_t launchDecode(const DecodeParams& p, int smCount, cudaStream_t stream, int* launches);
+// Same decode with the split-K workspace taken from a fixed array inside the
+// library (decodeStaticScratchBytes() bytes per GPU) instead of p.workspace.
+// Allocates nothing; fails with cudaErrorInvalidValue when the launch would
+// need more workspace than the array holds.  The current device must be the
+// one the pointers in `p` live on.
+size_t decodeStaticScratchBytes();
+cudaError_t launchDecodeStatic(const DecodeParams& p, int smCount, cudaStream_t stream, int* launches);
 
 // ---- prefill (prefill_kernels.cu) ----
 struct PrefillParams {

@@ -468,6 +468,66 @@ int32_t decodeImpl(Context* c, const PamDecodeRequest& rq, int maxContext) {
     return 0;
 }
 
+// Decode for callers that may not allocate: same checks and kernels as
+// decodeImpl, but nothing is staged (every buffer must already be device
+// memory), the context's arena is left alone, and split-K partials go to the
+// library's fixed scratch array.
+int32_t decodeNoAllocImpl(Context* c, const PamDecodeRequest& rq) {
+    if (!validateLayer(c, rq.layer)) return -1;
+    if (rq.batch_size <= 0) return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("batchSize must be positive."));
+    if (rq.max_num_blocks <= 0) return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("maxNumBlocks must be positive."));
+    const PamLayerSpec& l = rq.layer;
+    const size_t B = static_cast<size_t>(rq.batch_size), NB = static_cast<size_t>(rq.max_num_blocks);
+    if (rq.block_tables.bytes != kUnknownBytes && NB > rq.block_tables.bytes / (B * sizeof(int32_t)))
+        return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("maxNumBlocks exceeds blockTables buffer capacity"));
+    if (!requireBuffer(c, rq.q, "Q", B * qBytesPerToken(l))) return -1;
+    if (!requireBuffer(c, rq.block_tables, "blockTables", B * NB * sizeof(int32_t))) return -1;
+    if (!requireBuffer(c, rq.seq_lengths, "seqLengths", B * sizeof(uint32_t))) return -1;
+    if (!requireBuffer(c, rq.output, "output", B * qBytesPerToken(l))) return -1;
+    if (!requireBuffer(c, rq.k_pool, "K pool", NB * l.block_size * kvBytesPerToken(l))) return -1;
+    if (!requireBuffer(c, rq.v_pool, "V pool", NB * l.block_size * kvBytesPerToken(l))) return -1;
+    if (l.data_type == PAM_DTYPE_FP8 && (!rq.k_scale.ptr || !rq.v_scale.ptr))
+        return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("FP8 decode needs kScaleBuffer and vScaleBuffer."));
+    if (l.head_dim > 256)
+        return c->fail(PAM_ERR_UNSUPPORTED, "Unsupported paged attention path: headDim above 256.");
+    const void* mustBeDevice[] = {rq.q.ptr, rq.k_pool.ptr, rq.v_pool.ptr, rq.block_tables.ptr, rq.seq_lengths.ptr, rq.output.ptr};
+    for (const void* p : mustBeDevice)
+        if (!isDevicePointer(p))
+            return c->fail(PAM_ERR_INVALID_CONFIGURATION,
+                           invalidConfiguration("the no-allocation decode takes device memory only: a host buffer would need a staging allocation."));
+    pam::DecodeParams p{};
+    p.q = rq.q.ptr; p.kPool = rq.k_pool.ptr; p.vPool = rq.v_pool.ptr;
+    p.tables = static_cast<const int32_t*>(rq.block_tables.ptr);
+    p.lens = static_cast<const uint32_t*>(rq.seq_lengths.ptr);
+    p.out = rq.output.ptr; p.kScale = rq.k_scale.ptr; p.vScale = rq.v_scale.ptr;
+    p.batch = rq.batch_size; p.heads = l.num_heads; p.kvHeads = l.num_kv_heads; p.headDim = l.head_dim;
+    p.blockSize = l.block_size; p.maxNumBlocks = rq.max_num_blocks;
+    p.window = l.window_size > 0 ? l.window_size : c->defaultWindow;
+    p.dtype = l.data_type; p.maxContext = 0;
+    p.poolBlocks = poolBlocksOf(rq.k_pool, rq.v_pool, l);
+    const size_t need = pam::decodeWorkspaceBytes(p, c->smCount);
+    if (need > pam::decodeStaticScratchBytes())
+        return c->fail(PAM_ERR_RESOURCE_EXHAUSTED,
+                       "GPU resource exhausted: this decode needs " + std::to_string(need) +
+                           " bytes of split-K scratch, the built-in scratch holds " +
+                           std::to_string(pam::decodeStaticScratchBytes()) +
+                           "; use pamc_decode, or a smaller batch, fewer heads or shorter tables.");
+    const double t0 = nowMs();
+    int32_t rc = withRetry(c, "decodeFlat", [&]() -> cudaError_t {
+        int launches = 0;
+        cudaError_t e = pam::launchDecodeStatic(p, c->smCount, c->stream, &launches);
+        c->launches += launches;
+        return e;
+    });
+    if (rc != 0) {
+        if (!c->graceful) return rc;
+        cudaMemsetAsync(rq.output.ptr, 0, rq.output.bytes != kUnknownBytes ? rq.output.bytes : B * ioBytesPerToken(l), c->stream);
+        c->clearError();
+    }
+    c->stats = PamStats{PAM_OP_DECODE, rq.batch_size, 0, rq.max_num_blocks, static_cast<int64_t>(need), 0, nowMs() - t0};
+    return 0;
+}
+
 struct PrefillSeq { int seqLen, qStart, qLen; };
 
 int32_t prefillImpl(Context* c, const PamLayerSpec& l, const PamBuffer& q, const PamBuffer& kPool, const PamBuffer& vPool,
@@ -1067,6 +1127,17 @@ int32_t pamc_decode(void* ctx, const PamDecodeRequest* request) {
     DeviceGuard dg(c->device);
     if (c->device < 0) return noGpu(c);
     int32_t rc = decodeImpl(c, *request, 0);
+    if (rc == 0) c->clearError();
+    return rc;
+}
+
+int32_t pamc_decode_noalloc(void* ctx, const PamDecodeRequest* request) {
+    if (!ctx || !request) return -1;
+    Context* c = asCtx(ctx);
+    std::lock_guard<std::mutex> g(c->mu);
+    DeviceGuard dg(c->device);
+    if (c->device < 0) return noGpu(c);
+    int32_t rc = decodeNoAllocImpl(c, *request);
     if (rc == 0) c->clearError();
     return rc;
 }

@@ -219,6 +219,16 @@ class PagedAttentionEngine:
                                    _buf(request.kScaleBuffer), _buf(request.vScaleBuffer))
         _check(self._ctx, lib.pamc_decode(self._ctx, C.byref(r)))
 
+    def decodeNoAlloc(self, request: PagedAttentionDecodeRequest) -> None:
+        """The same decode for callers that must not allocate device memory
+        (see pamc_decode_noalloc in include/pam_cuda.h): device buffers only,
+        split-K partials in the library's fixed 8 MiB scratch array."""
+        r = _cabi.PamDecodeRequest(_buf(request.q), _buf(request.kPool), _buf(request.vPool),
+                                   _buf(request.blockTables), _buf(request.seqLengths), _buf(request.output),
+                                   request.batchSize, request.maxNumBlocks, _layer(request.layer),
+                                   _buf(request.kScaleBuffer), _buf(request.vScaleBuffer))
+        _check(self._ctx, lib.pamc_decode_noalloc(self._ctx, C.byref(r)))
+
     def appendToCache(self, request: PagedKVAppendRequest) -> None:
         """PagedAttentionEngine.swift:585-597"""
         r = _cabi.PamAppendRequest(_buf(request.keys), _buf(request.values), _buf(request.kPool),

@@ -1,0 +1,78 @@
+"""pamc_decode_noalloc: the decode for callers that must not allocate device
+memory (work being recorded for replay, a server that gave all free memory to
+the KV pools, a host that only receives pointers from another allocator).
+
+It must give what pamc_decode gives.  Both run the same kernels on the same
+split plan, so the outputs are compared bit for bit as well as within the
+tolerance of the other decode tests, on two calls in a row that share the
+library's fixed scratch array (the second with other data and another shape,
+so stale partial results of the first would show).  Collected last on purpose.
+"""
+import numpy as np
+import pytest
+
+import pagedattentionmetal_b200 as pam
+from gpu_helpers import DT, DecodeCase, assert_close, from_io, io_numpy_dtype
+
+pytestmark = pytest.mark.gpu
+
+
+def _device_request(engine, case, window=0):
+    out = engine.makeBuffer(case.q.nbytes)
+    req = pam.PagedAttentionDecodeRequest(
+        engine.makeBufferFrom(case.q), engine.makeBufferFrom(case.k_pool), engine.makeBufferFrom(case.v_pool),
+        engine.makeBufferFrom(case.tables), engine.makeBufferFrom(case.lens), out, len(case.lens),
+        case.tables.shape[1], case.layer(window))
+    return req, out
+
+
+def _download(out, case):
+    return out.download(io_numpy_dtype(case.dtype), case.q.shape)
+
+
+def test_noalloc_decode_matches_decode_on_two_calls_in_a_row():
+    engine = pam.PagedAttentionEngine()
+    # few long sequences: the plan splits each context, so the scratch array is really used
+    cases = [DecodeCase(51, 3, 3000, 6000, 8, 2, 128, 16, DT.float16),
+             DecodeCase(52, 2, 2000, 5000, 16, 2, 128, 16, DT.bfloat16)]
+    for case in cases:
+        req, out = _device_request(engine, case)
+        engine.decode(req)
+        assert engine.lastStats.temporaryBytes > 0, "the case must need split-K scratch"
+        expected = _download(out, case)
+        req2, out2 = _device_request(engine, case)
+        engine.decodeNoAlloc(req2)
+        assert 0 < engine.lastStats.temporaryBytes <= 8 << 20
+        got = _download(out2, case)
+        assert np.array_equal(got.view(np.uint16), expected.view(np.uint16))
+        assert_close(from_io(got, case.dtype), from_io(expected, case.dtype), case.dtype)
+        assert_close(from_io(got, case.dtype), case.oracle(), case.dtype)
+    # a windowed call through the same array
+    req3, out3 = _device_request(engine, cases[0], window=1500)
+    engine.decodeNoAlloc(req3)
+    assert_close(from_io(_download(out3, cases[0]), DT.float16), cases[0].oracle(window=1500), DT.float16)
+    engine.close()
+
+
+def test_noalloc_decode_rejects_what_it_cannot_hold():
+    engine = pam.PagedAttentionEngine()
+    engine.enableGracefulDegradation = False
+    # 64 sequences x 32 heads x 8 splits x 130 floats > 8 MiB; rejected before any launch,
+    # so a small pool that only satisfies the argument checks is enough
+    B, H, KVH, D, bs, max_nb = 64, 32, 8, 128, 16, 512
+    pool = engine.makeBuffer(max_nb * bs * KVH * D * 2)
+    q = engine.makeBuffer(B * H * D * 2)
+    out = engine.makeBuffer(B * H * D * 2)
+    tables = engine.makeBufferFrom(np.zeros((B, max_nb), np.int32))
+    lens = engine.makeBufferFrom(np.full(B, max_nb * bs, np.uint32))
+    layer = pam.PagedLayerSpec(D, H, KVH, bs, DT.float16)
+    with pytest.raises(pam.PagedAttentionError) as e:
+        engine.decodeNoAlloc(pam.PagedAttentionDecodeRequest(q, pool, pool, tables, lens, out, B, max_nb, layer))
+    assert e.value.case == "resourceExhausted"
+    assert str(8 << 20) in str(e.value) and "pamc_decode" in str(e.value)
+    # host buffers would need staging memory: refused as well
+    with pytest.raises(pam.PagedAttentionError) as e:
+        engine.decodeNoAlloc(pam.PagedAttentionDecodeRequest(np.zeros((1, H, D), np.float16), pool, pool, tables, lens,
+                                                             out, 1, max_nb, layer))
+    assert "device memory only" in str(e.value)
+    engine.close()
