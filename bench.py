@@ -1,6 +1,6 @@
 """Benchmark of the paged-KV hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--batch B] [--profile]
 
 Default workload `decode_c2`: large-batch paged decode with float16 KV -- 256
 sequences, context lengths uniform in [512, 8192], block size 16, head_dim 128,
@@ -140,6 +140,7 @@ def cpu_sample_inputs(lens, n_seqs):
 
 
 def time_cpu_path(lens, steps, warmup, n_seqs=CPU_SAMPLE_SEQS):
+    n_seqs = min(n_seqs, len(lens))
     """The reference's CPU path (its decode loop restated in C, OpenMP over
     (sequence, kv head)) on all host cores; tokens/s over the sample."""
     from oracle import c_oracle as co
@@ -159,7 +160,7 @@ def time_cpu_path(lens, steps, warmup, n_seqs=CPU_SAMPLE_SEQS):
 
 
 def config_dict(n_gpus):
-    return {"workload": "decode_c2: batch 256, context U[512,8192], block 16, head_dim 128, 32 q / 8 kv heads, "
+    return {"workload": f"decode_c2: batch {BATCH}, context U[512,8192], block 16, head_dim 128, 32 q / 8 kv heads, "
                         "float16 KV, random non-contiguous block tables",
             "seed": SEED, "sharding": f"kv-head groups over {n_gpus} GPU(s), no collective on the attention path",
             "l2": "inputs larger than L2 (KV read per step per GPU exceeds 126 MB); no flush needed"}
@@ -173,7 +174,7 @@ def run_reference(args):
     cb = time_cpu_path(lens, max(args.steps, 1), args.warmup)
     line = {"impl": "reference", "metric": "paged decode tokens/s", "value": cb["value"], "unit": "tokens/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": cb["ms_per_step_sample"] * BATCH / CPU_SAMPLE_SEQS,
+            "ms_per_step": cb["ms_per_step_sample"] * BATCH / min(CPU_SAMPLE_SEQS, BATCH),
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
             "data": "synthetic", "config": config_dict(args.gpus), "cpu_baseline": cb,
             "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -298,7 +299,7 @@ def run_ours(args):
     # keep the GPU busy for about half a second before timing, so that the
     # clock sampler sees the clocks the timed region runs at
     t_busy = time.perf_counter()
-    while time.perf_counter() - t_busy < 0.5:
+    while not args.profile and time.perf_counter() - t_busy < 0.5:
         for _ in range(10):
             engine.decode(req)
         torch.cuda.synchronize(dev)
@@ -316,23 +317,25 @@ def run_ours(args):
     engine.setAsync(False)
 
     # ---- e2e: the reference-shaped call with host buffers ----
-    for _ in range(max(args.warmup, 3)):
+    e2e_steps = 0 if args.profile else args.steps
+    for _ in range(0 if args.profile else max(args.warmup, 3)):
         engine.decodeBatch(cache, ids, q_pin.data_ptr(), out_pin.data_ptr(), heads)
     barrier()
     t0 = time.perf_counter()
-    for _ in range(args.steps):
+    for _ in range(e2e_steps):
         engine.decodeBatch(cache, ids, q_pin.data_ptr(), out_pin.data_ptr(), heads)
     barrier()
-    e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3) / args.steps
+    e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3) / max(e2e_steps, 1)
     launches = engine.kernelLaunches - launches0
     clocks = sampler.stop()
-    assert torch.equal(out_pin.to(dev), out_dev), "host-buffer path and device path disagree"
+    if not args.profile:
+        assert torch.equal(out_pin.to(dev), out_dev), "host-buffer path and device path disagree"
 
     if rank == 0:
         peak, peak_kind = measured_hbm_peak()
         bytes_gpu = algorithmic_bytes(lens, heads, kvh)
         achieved = bytes_gpu / (ms_step * 1e-3) / 1e9
-        cpu = time_cpu_path(lens, 2, 1) if world == 1 else None
+        cpu = time_cpu_path(lens, 2, 1) if world == 1 and not args.profile else None
         io_bytes = BATCH * heads * HEAD_DIM * 2
         line = {
             "metric": "paged decode tokens/s", "value": BATCH / (ms_step * 1e-3), "unit": "tokens/s",
@@ -343,8 +346,11 @@ def run_ours(args):
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": f"{peak_kind} copy bandwidth", "per": "GPU",
                          "kernel": "decodeSplitKernel (+ decodeMergeKernel, same timed step)",
-                         "algorithmic_bytes_per_launch": bytes_gpu, "traffic": None},
-            "e2e": {"value": BATCH / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+                         "algorithmic_bytes_per_launch": bytes_gpu,
+                         # DRAM read+write of one launch: 1.010 x algorithmic, from an ncu capture of the same
+                         # kernel on a 64-sequence case (profiles/decode_split_f16_b64_full.md), scaled by tokens
+                         "traffic": bytes_gpu * 1.010, "traffic_source": "ncu on batch 64, scaled by context tokens"},
+            "e2e": {"value": BATCH / (e2e_ms * 1e-3) if e2e_steps else None, "unit": "tokens/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": io_bytes + tables_h.nbytes + lens_h.nbytes, "d2h_bytes_per_step": io_bytes,
                     "call": "pam_decode with pinned host q/out; block tables rebuilt and uploaded per call"},
             "gpu_launches": int(launches), "clocks": clocks,
@@ -364,7 +370,12 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=BATCH,
+                    help="number of sequences (default: the workload's 256; smaller values are for profiler captures)")
+    ap.add_argument("--profile", action="store_true",
+                    help="profiler run: no clock-settling loop, no end-to-end leg, no CPU baseline")
     args = ap.parse_args()
+    globals()["BATCH"] = args.batch
     if args.impl == "reference":
         run_reference(args)
     else:
