@@ -364,6 +364,121 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# ----------------------------------------------------- prefill workload (c3)
+
+PF_SEQS, PF_LEN, PF_CHUNK, PF_PREFIX = 16, 2048, 512, 1024
+
+
+def run_prefill(args):
+    """Chunked causal prefill with prefix caching (`configs[3]`): 16 sequences x
+    2048 prompt tokens in 512-token chunks, all sharing an identical 1024-token
+    prefix (its pages are shared through the manager's prefix cache and written
+    once), bf16, 32 q / 8 kv heads, head_dim 128, block 16.  A step is the four
+    chunk launches (one launch per chunk for all 16 sequences); the metric is
+    algorithmic TFLOP/s: 16 x 32 x (2048 x 2049 / 2) x 4 x 128 = 550.0 GFLOP per
+    step, masked pairs and softmax not counted.  Tensor-bound."""
+    import torch
+
+    import pagedattentionmetal_b200 as pam
+
+    DT = pam.PagedAttentionDataType
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    engine = pam.PagedAttentionEngine(0)
+    stream = torch.cuda.Stream(dev)
+    torch.cuda.set_stream(stream)
+    engine.setStream(stream.cuda_stream)
+    nblk_seq = PF_LEN // BLOCK
+    cache = pam.KVCacheManager(engine, PF_SEQS * nblk_seq + 64, BLOCK, HEAD_DIM, KV_HEADS, DT.bfloat16)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1003)
+    prefix_kv = torch.randn((2, PF_PREFIX, KV_HEADS, HEAD_DIM), generator=gen, device=dev).to(torch.bfloat16)
+    prefix_q = torch.randn((PF_PREFIX, HEADS, HEAD_DIM), generator=gen, device=dev).to(torch.bfloat16)
+    qs = []
+    hashes = list(range(PF_PREFIX // BLOCK))
+    for sid in range(PF_SEQS):
+        cache.allocateSequence(sid)
+        cache.appendTokens(sid, PF_PREFIX, hashes)              # followers hit the leader's pages
+        if sid == 0:
+            engine.appendKV(cache, 0, prefix_kv[0].contiguous(), prefix_kv[1].contiguous(), 0, PF_PREFIX, HEADS)
+        cache.appendTokens(sid, PF_LEN - PF_PREFIX)
+        kv = torch.randn((2, PF_LEN - PF_PREFIX, KV_HEADS, HEAD_DIM), generator=gen, device=dev).to(torch.bfloat16)
+        engine.appendKV(cache, sid, kv[0].contiguous(), kv[1].contiguous(), PF_PREFIX, PF_LEN - PF_PREFIX, HEADS)
+        q_own = torch.randn((PF_LEN - PF_PREFIX, HEADS, HEAD_DIM), generator=gen, device=dev).to(torch.bfloat16)
+        qs.append(torch.cat([prefix_q, q_own]))
+    stats = cache.memoryStats()
+    assert stats.sharedBlocks == PF_PREFIX // BLOCK and stats.prefixCacheHits == (PF_SEQS - 1) * (PF_PREFIX // BLOCK)
+    tables_h, _ = cache.batchTables(list(range(PF_SEQS)), nblk_seq)
+    tables = torch.from_numpy(tables_h).to(dev)
+    layer = pam.PagedLayerSpec(HEAD_DIM, HEADS, KV_HEADS, BLOCK, DT.bfloat16)
+    n_chunks = PF_LEN // PF_CHUNK
+    q_chunks = [torch.cat([qs[s][c * PF_CHUNK:(c + 1) * PF_CHUNK] for s in range(PF_SEQS)]).contiguous() for c in range(n_chunks)]
+    outs = [torch.empty_like(q_chunks[c]) for c in range(n_chunks)]
+
+    def step():
+        for c in range(n_chunks):
+            engine.prefillBatch(q_chunks[c], cache.kPoolBuffer, cache.vPoolBuffer, tables, outs[c],
+                                [(c + 1) * PF_CHUNK] * PF_SEQS, [c * PF_CHUNK] * PF_SEQS, [PF_CHUNK] * PF_SEQS,
+                                nblk_seq, layer, True)
+
+    # correctness guard: a few rows of one follower sequence against the oracle
+    step()
+    engine.synchronize()
+    from oracle import c_oracle as co
+    from oracle import paged_oracle as po
+    gk, gv, _, _ = cache.readPools()
+    sid, c, r0, n = min(5, PF_SEQS - 1), 2, 100, 8
+    ref = co.prefill(qs[sid][c * PF_CHUNK + r0: c * PF_CHUNK + r0 + n].view(torch.uint16).cpu().numpy(), gk, gv,
+                     tables_h[sid], (c + 1) * PF_CHUNK, KV_HEADS, BLOCK, 3, q_start=c * PF_CHUNK + r0)
+    got = po.from_bf16_bits(outs[c][sid * PF_CHUNK + r0: sid * PF_CHUNK + r0 + n].view(torch.uint16).cpu().numpy())
+    err = float(np.abs(got - ref).max())
+    assert err <= 2e-3 + 2.0 ** -8, f"prefill differs from the oracle by {err}"
+    tensor_path = engine.lastStats.operation == pam.Operation.prefillMMA
+
+    engine.setAsync(True)
+    sampler = ClockSampler(0)
+    sampler.start()
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
+        step()
+    t_busy = time.perf_counter()
+    while not args.profile and time.perf_counter() - t_busy < 0.5:
+        step()
+        torch.cuda.synchronize(dev)
+        warm += 1
+    torch.cuda.synchronize(dev)
+    launches0 = engine.kernelLaunches
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    torch.cuda.synchronize(dev)
+    ms_step = e0.elapsed_time(e1) / args.steps
+    launches = engine.kernelLaunches - launches0
+    clocks = sampler.stop()
+    flops = PF_SEQS * HEADS * (PF_LEN * (PF_LEN + 1) // 2) * 4 * HEAD_DIM
+    tflops = flops / (ms_step * 1e-3) / 1e12
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            peak, kind = float(json.load(f)["bf16_tflops"]), "measured cuBLAS bf16 burst"
+    except Exception:
+        peak, kind = 1590.0, "fallback"
+    line = {"metric": "prefill TFLOP/s", "value": tflops, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": warm, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "prefill_c3: 16 seqs x 2048 tokens, chunks of 512, shared 1024-token prefix, bf16, "
+                                   "32 q / 8 kv heads, head_dim 128, block 16", "seed": 1003},
+            "tokens_per_s": PF_SEQS * PF_LEN / (ms_step * 1e-3),
+            "roofline": {"bound": "tensor", "achieved": tflops, "peak": peak, "unit": "TFLOP/s", "frac": tflops / peak,
+                         "peak_source": kind, "kernel": "prefillTcKernel" if tensor_path else "prefillGeneralKernel",
+                         "algorithmic_flops_per_step": flops, "traffic": None},
+            "gpu_launches": int(launches), "clocks": clocks}
+    print(json.dumps(line))
+    cache.close()
+    engine.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -372,11 +487,17 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=BATCH,
                     help="number of sequences (default: the workload's 256; smaller values are for profiler captures)")
+    ap.add_argument("--workload", default="decode_c2", choices=["decode_c2", "prefill_c3"],
+                    help="decode_c2 is the headline workload; prefill_c3 reports prefill TFLOP/s (1 GPU)")
     ap.add_argument("--profile", action="store_true",
                     help="profiler run: no clock-settling loop, no end-to-end leg, no CPU baseline")
     args = ap.parse_args()
     globals()["BATCH"] = args.batch
-    if args.impl == "reference":
+    if args.workload == "prefill_c3" and args.batch != 256:
+        globals()["PF_SEQS"] = args.batch
+    if args.workload == "prefill_c3" and args.impl == "ours":
+        run_prefill(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -155,6 +155,11 @@ int32_t pamc_set_graceful_degradation(void *ctx, int32_t on);  /* enableGraceful
 int32_t pamc_set_split_threshold(void *ctx, int32_t tokens);   /* splitThreshold, default 1024 */
 int32_t pamc_set_default_window(void *ctx, int32_t tokens);    /* defaultWindowSize, default 0 */
 int32_t pamc_set_default_chunk(void *ctx, int32_t tokens);     /* defaultChunkSize, default 0 */
+/* 1 (default): prefill takes the tensor-core kernel where it applies (bf16/f16,
+ * head_dim 128, block size a multiple of 16); 0: always the general kernel.
+ * The reference picks its prefill variant the same way, by type and head_dim
+ * (PagedAttentionEngine.swift:420-434). */
+int32_t pamc_set_prefill_tensor_path(void *ctx, int32_t on);
 /* Host-side fault injection for tests of the retry loop, circuit breaker and
  * zero-fill path (PagedAttentionEngine.swift:375-414): the next n kernel
  * launches of this context report failure without touching the GPU. */

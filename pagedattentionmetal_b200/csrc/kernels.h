@@ -85,7 +85,13 @@ struct PrefillParams {
     const int32_t* windowStarts;  // first visible key
     int numSeqs, maxQLen, heads, kvHeads, headDim, blockSize, maxNumBlocks, causal, dtype;
     int poolBlocks;               // table entries are clamped into [0, poolBlocks)
+    int totalRows;                // rows in q/out (all sequences of the launch)
+    int* errFlag;                 // device word the tensor-core kernel sets when a bounded wait runs out
+    int forceGeneral;             // 1: never take the tensor-core path
 };
+// Tensor-core path (prefill_tc_kernel.cu): bf16/f16, head_dim 128, block size multiple of 16.
+bool prefillTensorPathApplies(const PrefillParams& p);
+cudaError_t launchPrefillTensor(const PrefillParams& p, int totalRows, int* errFlag, cudaStream_t stream, int* launches);
 cudaError_t launchPrefill(const PrefillParams& p, int smCount, cudaStream_t stream, int* launches,
                           bool* usedTensorPath);
 

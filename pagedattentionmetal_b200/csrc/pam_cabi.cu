@@ -87,6 +87,10 @@ struct Context {
     int64_t launches = 0;
     PamStats stats{};
     Arena arena;
+    int* devErr = nullptr;    // set by a kernel whose bounded wait ran out
+    int* hostErr = nullptr;   // pinned copy, read after the stream has been synchronised
+    bool errPending = false;
+    bool forceGeneralPrefill = false;
 
     int32_t fail(int code, const std::string& msg) {            // CABI.swift:18-30
         lastError = msg;
@@ -266,6 +270,16 @@ int32_t withRetry(Context* c, const char* operation, F attempt) {
             e = attempt();
             if (e == cudaSuccess && !c->async) e = cudaStreamSynchronize(c->stream);
             if (e != cudaSuccess) { last = cudaGetErrorString(e); cudaGetLastError(); }
+            else if (!c->async && c->errPending) {
+                // a kernel gave up on a bounded wait and returned without finishing its work
+                c->errPending = false;
+                if (*c->hostErr != 0) {
+                    last = "a kernel's bounded wait ran out (site " + std::to_string(*c->hostErr) + ")";
+                    *c->hostErr = 0;
+                    cudaMemsetAsync(c->devErr, 0, sizeof(int), c->stream);
+                    e = cudaErrorLaunchTimeout;
+                }
+            }
         }
         if (e == cudaSuccess) { c->consecutiveFailures = 0; return 0; }
         c->consecutiveFailures += 1;
@@ -590,9 +604,16 @@ int32_t prefillImpl(Context* c, const PamLayerSpec& l, const PamBuffer& q, const
         p.numSeqs = n; p.maxQLen = maxQLen; p.heads = l.num_heads; p.kvHeads = l.num_kv_heads; p.headDim = l.head_dim;
         p.blockSize = l.block_size; p.maxNumBlocks = maxNumBlocks; p.causal = causal ? 1 : 0; p.dtype = l.data_type;
         p.poolBlocks = poolBlocksOf(kPool, vPool, l);
+        p.totalRows = static_cast<int>(totalRows);
+        p.errFlag = c->devErr;
+        p.forceGeneral = c->forceGeneralPrefill ? 1 : 0;
         int launches = 0;
         cudaError_t e = pam::launchPrefill(p, c->smCount, c->stream, &launches, &tensorPath);
         c->launches += launches;
+        if (e == cudaSuccess && tensorPath) {
+            e = cudaMemcpyAsync(c->hostErr, c->devErr, sizeof(int), cudaMemcpyDeviceToHost, c->stream);
+            c->errPending = true;
+        }
         if (e == cudaSuccess) e = st.copyBack();
         // `meta` is read by an async copy from pageable memory, which the
         // runtime stages before returning; nothing else outlives this scope.
@@ -666,6 +687,16 @@ void* pamc_create_context_on(int32_t device) {
         return nullptr;
     }
     c->stream = c->ownStream;
+    if (cudaMalloc(reinterpret_cast<void**>(&c->devErr), sizeof(int)) != cudaSuccess ||
+        cudaMemset(c->devErr, 0, sizeof(int)) != cudaSuccess ||
+        cudaMallocHost(reinterpret_cast<void**>(&c->hostErr), sizeof(int)) != cudaSuccess) {
+        cudaGetLastError();
+        if (c->devErr) cudaFree(c->devErr);
+        cudaStreamDestroy(c->ownStream);
+        delete c;
+        return nullptr;
+    }
+    *c->hostErr = 0;
     return c;
 }
 
@@ -689,6 +720,8 @@ void pam_destroy_context(void* ctx) {
     cudaSetDevice(c->device);
     cudaStreamSynchronize(c->stream);
     c->arena.release();
+    if (c->devErr) cudaFree(c->devErr);
+    if (c->hostErr) cudaFreeHost(c->hostErr);
     if (c->ownStream) cudaStreamDestroy(c->ownStream);
     delete c;
 }
@@ -952,11 +985,21 @@ int32_t pamc_synchronize(void* ctx) {
     if (c->device < 0) return noGpu(c);
     cudaError_t e = cudaStreamSynchronize(c->stream);
     if (e != cudaSuccess) { cudaGetLastError(); return c->fail(PAM_ERR_COMMAND_EXECUTION, commandExecutionFailed(cudaGetErrorString(e))); }
+    if (c->errPending) {
+        c->errPending = false;
+        if (*c->hostErr != 0) {
+            const int site = *c->hostErr;
+            *c->hostErr = 0;
+            cudaMemsetAsync(c->devErr, 0, sizeof(int), c->stream);
+            return c->fail(PAM_ERR_COMMAND_EXECUTION, commandExecutionFailed("a kernel's bounded wait ran out (site " + std::to_string(site) + ")"));
+        }
+    }
     return 0;
 }
 int32_t pamc_set_max_retries(void* ctx, int32_t n) { if (!ctx || n < 0) return -1; asCtx(ctx)->maxRetries = n; return 0; }
 int32_t pamc_set_graceful_degradation(void* ctx, int32_t on) { if (!ctx) return -1; asCtx(ctx)->graceful = on != 0; return 0; }
 int32_t pamc_set_split_threshold(void* ctx, int32_t t) { if (!ctx) return -1; asCtx(ctx)->splitThreshold = t; return 0; }
+int32_t pamc_set_prefill_tensor_path(void* ctx, int32_t on) { if (!ctx) return -1; asCtx(ctx)->forceGeneralPrefill = on == 0; return 0; }
 int32_t pamc_set_default_window(void* ctx, int32_t t) { if (!ctx || t < 0) return -1; asCtx(ctx)->defaultWindow = t; return 0; }
 int32_t pamc_set_default_chunk(void* ctx, int32_t t) { if (!ctx || t < 0) return -1; asCtx(ctx)->defaultChunk = t; return 0; }
 int32_t pamc_inject_launch_failures(void* ctx, int32_t n) { if (!ctx || n < 0) return -1; asCtx(ctx)->injectFailures = n; return 0; }

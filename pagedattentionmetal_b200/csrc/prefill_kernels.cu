@@ -181,6 +181,10 @@ cudaError_t launchPrefill(const PrefillParams& p, int smCount, cudaStream_t stre
     if (usedTensorPath) *usedTensorPath = false;
     if (p.numSeqs <= 0 || p.maxQLen <= 0) return cudaSuccess;
     if (p.headDim > 256 || p.poolBlocks <= 0) return cudaErrorInvalidValue;
+    if (!p.forceGeneral && p.errFlag && prefillTensorPathApplies(p)) {
+        if (usedTensorPath) *usedTensorPath = true;
+        return launchPrefillTensor(p, p.totalRows, p.errFlag, stream, launches);
+    }
     switch (p.dtype) {
         case kF32: return launchGeneral<float, float>(p, stream, launches);
         case kF16: return launchGeneral<__half, __half>(p, stream, launches);

@@ -1,0 +1,546 @@
+// Chunked causal prefill on the 5th-generation tensor cores (sm_100a):
+// tcgen05.mma with accumulators in tensor memory, operands staged in shared
+// memory by TMA, for bfloat16 / float16 KV with head_dim 128 and a block size
+// that is a multiple of 16.
+//
+// Semantics are those of prefillGeneralKernel (paged_attention_tiled,
+// kernels.metal:693-765, plus the chunk rows of
+// PagedAttentionEngine.swift:740-756).
+//
+// One CTA owns a tile of 128 query rows of one head of one sequence and walks
+// the key tiles (128 keys each) that those rows can see.
+//
+//   warp 4               TMA producer: the Q tile once, then per key tile the
+//                        8 pages of K and of V (each page is 16 rows x 256 B,
+//                        fetched as two 128-byte-swizzled boxes) into a
+//                        2-stage ring; completion on mbarriers.
+//   warp 5 (one thread)  MMA issuer: S = Q K^T (8 x tcgen05.mma 128x128x16)
+//                        into one of two S buffers in tensor memory, and
+//                        O += P V (8 more, V read as an MN-major operand
+//                        straight from its row-major pages); tcgen05.commit
+//                        signals the mbarriers.  QK^T of tile j+1 is issued
+//                        before PV of tile j so that the tensor pipe works
+//                        while the softmax warps are busy.
+//   warps 0-3            softmax: thread t owns row t.  S is read from tensor
+//                        memory (tcgen05.ld), scaled, masked (causal, window
+//                        start, sequence end) only on edge tiles; the running
+//                        maximum is only raised when it grows by more than 2^8
+//                        (the result is exact either way, the final division
+//                        uses the same reference), in which case O is rescaled
+//                        in tensor memory; P goes to shared memory in the cache
+//                        type, in the swizzled K-major layout the MMA reads; for
+//                        bfloat16 as two operands P_hi + P_lo (16 significant
+//                        bits together) and twice the PV instructions, because
+//                        8-bit weights alone miss the 2e-3 bound on short rows.
+//
+// Every wait on an mbarrier is bounded; a wait that runs out raises a flag the
+// host reads and the CTA falls through to the common exit, where the tensor
+// memory is released.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <cmath>
+
+#include "kernels.h"
+
+namespace pam {
+namespace {
+
+constexpr int kRows = 128;        // query rows per CTA
+constexpr int kKeys = 128;        // keys per tile
+constexpr int kHd = 128;
+constexpr int kStages = 2;
+constexpr int kTileBytes = kRows * kHd * 2;            // 32 KB: one [128][128] 16-bit tile
+constexpr int kHalfBytes = kTileBytes / 2;             // one 64-column block
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kRescaleThreshold = 8.0f;
+constexpr long long kWaitCycles = 400000000LL;         // ~0.2 s
+
+struct Smem {
+    // tiles first: each 1024-byte aligned (swizzle atoms)
+    unsigned char q[kTileBytes];
+    unsigned char p[kTileBytes];
+    unsigned char pLo[kTileBytes];     // bfloat16 only: the part of P that the first 8 bits lose
+    unsigned char k[kStages][kTileBytes];
+    unsigned char v[kStages][kTileBytes];
+    unsigned long long qFull, kFull[kStages], vFull[kStages], kvEmpty[kStages];
+    unsigned long long sFull[2], sEmpty[2], pFull, pvDone;
+    uint32_t tmemBase;
+    int dead;
+};
+
+__device__ __forceinline__ uint32_t smemAddr(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbarInit(unsigned long long* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smemAddr(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbarExpectTx(unsigned long long* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smemAddr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbarArrive(unsigned long long* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smemAddr(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbarTry(unsigned long long* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smemAddr(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false (and marks the CTA dead) when the barrier did
+// not complete in time or another thread of the CTA already gave up.
+__device__ __forceinline__ bool mbarWait(unsigned long long* bar, uint32_t parity, Smem* s, int* errFlag, int where) {
+    if (mbarTry(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (true) {
+        if (mbarTry(bar, parity)) return true;
+        if (*reinterpret_cast<volatile int*>(&s->dead)) return false;
+        if (clock64() - t0 > kWaitCycles) {
+            *reinterpret_cast<volatile int*>(&s->dead) = 1;
+            atomicCAS(errFlag, 0, where);
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void tmaLoad2d(void* dst, const CUtensorMap* map, unsigned long long* bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smemAddr(dst)), "l"(map), "r"(smemAddr(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tmaLoad3d(void* dst, const CUtensorMap* map, unsigned long long* bar, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smemAddr(dst)), "l"(map), "r"(smemAddr(bar)), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+
+// Shared-memory matrix descriptor (128-byte swizzle, descriptor version 1).
+// lbo/sbo in bytes.  K-major operands: sbo = 1024 (eight 128-byte rows),
+// lbo unused (1).  MN-major operand (V): lbo = distance between 64-element
+// column blocks, sbo = 1024 (eight keys).
+__device__ __forceinline__ uint64_t makeDesc(uint32_t addr, uint32_t lboBytes, uint32_t sboBytes) {
+    uint64_t d = (addr & 0x3FFFFu) >> 4;
+    d |= static_cast<uint64_t>((lboBytes >> 4) & 0x3FFFu) << 16;
+    d |= static_cast<uint64_t>((sboBytes >> 4) & 0x3FFFu) << 32;
+    d |= 1ull << 46;       // version
+    d |= 2ull << 61;       // SWIZZLE_128B
+    return d;
+}
+
+__device__ __forceinline__ void umma(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void ummaCommit(unsigned long long* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smemAddr(bar)) : "memory");
+}
+__device__ __forceinline__ void tcFenceBefore() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcFenceAfter() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmemLd32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmemSt32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmemStWait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack16(float lo, float hi) {
+    if (BF16) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<uint32_t*>(&h);
+    }
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(192, 1)
+prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
+                const __grid_constant__ CUtensorMap mapV, PrefillParams p, float scaleLog2, int* errFlag) {
+    extern __shared__ unsigned char rawSmem[];
+    Smem* s = reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(rawSmem) + 1023) & ~static_cast<uintptr_t>(1023));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);   // long tiles first
+    const int head = blockIdx.y, seq = blockIdx.z;
+    const int qLen = p.qLens[seq];
+    if (tile * kRows >= qLen) return;
+    if (*reinterpret_cast<volatile int*>(errFlag) != 0) return;       // an earlier CTA gave up: do not pile up waits
+    const int G = p.heads / p.kvHeads, kvh = head / G;
+    const int qStart = p.qStarts[seq], seqLen = p.seqLens[seq], ws = p.windowStarts[seq];
+    const int rowBase = p.qRowOffsets[seq] + tile * kRows;            // first row of the tile in q/out
+    const int rowsValid = min(kRows, qLen - tile * kRows);
+    const int firstPos = qStart + tile * kRows;                       // sequence position of row 0
+    const int lastPos = firstPos + rowsValid - 1;
+
+    // Key tiles [tileLo, tileHi] hold every key a row of this tile may see.
+    const int keyEnd = p.causal ? min(seqLen, lastPos + 1) : seqLen;  // exclusive
+    const int tileLo = ws / kKeys;
+    const int nT = keyEnd > ws ? (keyEnd - 1) / kKeys - tileLo + 1 : 0;
+
+    if (threadIdx.x == 0) {
+        mbarInit(&s->qFull, 1);
+        for (int i = 0; i < kStages; ++i) { mbarInit(&s->kFull[i], 1); mbarInit(&s->vFull[i], 1); mbarInit(&s->kvEmpty[i], 1); }
+        for (int i = 0; i < 2; ++i) { mbarInit(&s->sFull[i], 1); mbarInit(&s->sEmpty[i], 128); }
+        mbarInit(&s->pFull, 128);
+        mbarInit(&s->pvDone, 1);
+        s->dead = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemAddr(&s->tmemBase)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcFenceBefore();
+    __syncthreads();
+    tcFenceAfter();
+    const uint32_t tmem = s->tmemBase;
+    const uint32_t tmemS[2] = {tmem, tmem + 128u};
+    const uint32_t tmemO = tmem + 256u;
+
+    if (warp == 4) {
+        // ------------------------------------------------------------ TMA producer
+        // Lane 0 arms the barriers; lanes 0-7 each fetch one 16-token page piece
+        // of K and of V (their block-table reads run in parallel).
+        if (nT > 0) {
+            if (lane == 0) {
+                mbarExpectTx(&s->qFull, kTileBytes);
+                tmaLoad3d(s->q, &mapQ, &s->qFull, 0, head, rowBase);
+                tmaLoad3d(s->q + kHalfBytes, &mapQ, &s->qFull, 64, head, rowBase);
+            }
+            const int32_t* table = p.tables + static_cast<int64_t>(seq) * p.maxNumBlocks;
+            const int tilesPerPage = p.blockSize / 16;
+            bool ok = true;
+            for (int j = 0; j < nT && ok; ++j) {
+                const int st = j % kStages;
+                int row = 0;
+                if (lane < kKeys / 16) {
+                    const int t16 = (tileLo + j) * (kKeys / 16) + lane;           // 16-token piece of the sequence
+                    const int page = min(t16 / tilesPerPage, p.maxNumBlocks - 1);
+                    const int blk = min(max(table[page], 0), p.poolBlocks - 1);
+                    row = (blk * p.kvHeads + kvh) * p.blockSize + (t16 % tilesPerPage) * 16;
+                }
+                if (j >= kStages) ok = mbarWait(&s->kvEmpty[st], ((j / kStages) - 1) & 1, s, errFlag, 1);
+                ok = __all_sync(0xFFFFFFFFu, ok);
+                if (!ok) break;
+                if (lane == 0) {
+                    mbarExpectTx(&s->kFull[st], kTileBytes);
+                    mbarExpectTx(&s->vFull[st], kTileBytes);
+                }
+                __syncwarp();
+                if (lane < kKeys / 16) {
+                    tmaLoad2d(s->k[st] + lane * 2048, &mapK, &s->kFull[st], 0, row);
+                    tmaLoad2d(s->k[st] + kHalfBytes + lane * 2048, &mapK, &s->kFull[st], 64, row);
+                    tmaLoad2d(s->v[st] + lane * 2048, &mapV, &s->vFull[st], 0, row);
+                    tmaLoad2d(s->v[st] + kHalfBytes + lane * 2048, &mapV, &s->vFull[st], 64, row);
+                }
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0 && nT > 0) {
+            const uint32_t fmt = BF16 ? 1u : 0u;
+            // D = f32, A/B = bf16|f16, M = 128, N = 128; B of the second product is MN-major.
+            const uint32_t idescS = (1u << 4) | (fmt << 7) | (fmt << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+            // P has the type of the cache: a float16 P against bfloat16 V is rejected by
+            // the hardware (illegal instruction), the two operands must agree.
+            const uint32_t idescO = idescS | (1u << 16);
+            bool ok = mbarWait(&s->qFull, 0, s, errFlag, 2);
+            const uint32_t qAddr = smemAddr(s->q), pAddr = smemAddr(s->p);
+            for (int j = 0; j <= nT && ok; ++j) {
+                if (j < nT) {
+                    const int b = j & 1, st = j % kStages;
+                    ok = mbarWait(&s->kFull[st], (j / kStages) & 1, s, errFlag, 3);
+                    if (ok && j >= 2) ok = mbarWait(&s->sEmpty[b], ((j / 2) - 1) & 1, s, errFlag, 4);
+                    if (!ok) break;
+                    tcFenceAfter();
+                    const uint32_t kAddr = smemAddr(s->k[st]);
+#pragma unroll
+                    for (int ks = 0; ks < kHd / 16; ++ks) {
+                        const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
+                        umma(tmemS[b], makeDesc(qAddr + off, 16, 1024), makeDesc(kAddr + off, 16, 1024), idescS, ks > 0);
+                    }
+                    ummaCommit(&s->sFull[b]);
+                }
+                if (j >= 1) {
+                    const int jj = j - 1, st = jj % kStages;
+                    ok = mbarWait(&s->pFull, jj & 1, s, errFlag, 5);
+                    if (ok) ok = mbarWait(&s->vFull[st], (jj / kStages) & 1, s, errFlag, 6);
+                    if (!ok) break;
+                    tcFenceAfter();
+                    const uint32_t vAddr = smemAddr(s->v[st]);
+#pragma unroll
+                    for (int ks = 0; ks < kKeys / 16; ++ks) {
+                        const uint32_t aOff = (ks >> 2) * kHalfBytes + (ks & 3) * 32;   // P: K-major, keys along K
+                        const uint32_t bOff = ks * 16 * 128;                            // V: 16 keys = 16 rows of 128 B
+                        umma(tmemO, makeDesc(pAddr + aOff, 16, 1024), makeDesc(vAddr + bOff, kHalfBytes, 1024), idescO,
+                             (jj > 0 || ks > 0) ? 1u : 0u);
+                    }
+                    if (BF16) {
+                        // second term of P = P_hi + P_lo (see the softmax warps)
+                        const uint32_t pLoAddr = smemAddr(s->pLo);
+#pragma unroll
+                        for (int ks = 0; ks < kKeys / 16; ++ks) {
+                            const uint32_t aOff = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
+                            umma(tmemO, makeDesc(pLoAddr + aOff, 16, 1024), makeDesc(vAddr + ks * 16 * 128, kHalfBytes, 1024),
+                                 idescO, 1u);
+                        }
+                    }
+                    ummaCommit(&s->pvDone);
+                    ummaCommit(&s->kvEmpty[st]);
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ softmax warps
+        const int t = threadIdx.x;                      // row of the tile
+        const int rowPos = firstPos + t;
+        const uint32_t laneBase = static_cast<uint32_t>(warp * 32) << 16;
+        float mUsed = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < nT && ok; ++j) {
+            const int b = j & 1, st = j % kStages;
+            const int k0 = (tileLo + j) * kKeys;
+            const bool edge = k0 < ws || k0 + kKeys > seqLen || (p.causal && k0 + kKeys - 1 > firstPos);
+            ok = mbarWait(&s->sFull[b], (j / 2) & 1, s, errFlag, 7);
+            if (!ok) break;
+            tcFenceAfter();
+            // pass 1: row maximum of the scaled, masked scores
+            float tmax = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t r[32];
+                tmemLd32(tmemS[b] + laneBase + c * 32, r);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    float x = __uint_as_float(r[i]) * scaleLog2;
+                    if (edge) {
+                        const int key = k0 + c * 32 + i;
+                        if (key < ws || key >= seqLen || (p.causal && key > rowPos)) x = -INFINITY;
+                    }
+                    tmax = fmaxf(tmax, x);
+                }
+            }
+            bool raise = false;
+            float corr = 1.f;
+            if (j == 0) mUsed = tmax;
+            else if (tmax > mUsed + kRescaleThreshold) {
+                raise = true;
+                corr = exp2f(mUsed - tmax);
+                mUsed = tmax;
+            }
+            if (j >= 1) {
+                // PV of the previous tile is done: P may be overwritten, O may be rescaled
+                ok = mbarWait(&s->pvDone, (j - 1) & 1, s, errFlag, 8);
+                if (!ok) break;
+                tcFenceAfter();
+                if (__any_sync(0xFFFFFFFFu, raise)) {
+#pragma unroll 1
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t r[32];
+                        tmemLd32(tmemO + laneBase + c * 32, r);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
+                        tmemSt32(tmemO + laneBase + c * 32, r);
+                    }
+                    tmemStWait();
+                    l *= corr;
+                }
+            }
+            // pass 2: probabilities to shared memory (cache type, K-major, 128-byte swizzle)
+            const float mEff = mUsed == -INFINITY ? 0.f : mUsed;
+            float sum = 0.f;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t r[32];
+                tmemLd32(tmemS[b] + laneBase + c * 32, r);
+                uint32_t packed[16];
+                uint32_t packedLo[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float x0 = __uint_as_float(r[i]) * scaleLog2, x1 = __uint_as_float(r[i + 1]) * scaleLog2;
+                    if (edge) {
+                        const int key = k0 + c * 32 + i;
+                        if (key < ws || key >= seqLen || (p.causal && key > rowPos)) x0 = -INFINITY;
+                        if (key + 1 < ws || key + 1 >= seqLen || (p.causal && key + 1 > rowPos)) x1 = -INFINITY;
+                    }
+                    const float p0 = exp2f(x0 - mEff), p1 = exp2f(x1 - mEff);
+                    sum += p0 + p1;
+                    packed[i / 2] = pack16<BF16>(p0, p1);
+                    if (BF16) {
+                        // bfloat16 keeps 8 significant bits of a weight; the remainder goes
+                        // into a second operand so that P_hi + P_lo carries 16 bits
+                        const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&packed[i / 2]);
+                        packedLo[i / 2] = pack16<true>(p0 - __low2float(h), p1 - __high2float(h));
+                    }
+                }
+                // 32 keys = 4 chunks of 16 bytes; column block c/2, chunks (c&1)*4 .. +3 of row t
+                const int rowOff = (c >> 1) * kHalfBytes + t * 128;
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    const int chunk = (c & 1) * 4 + q4;
+                    const int off = rowOff + ((chunk ^ (t & 7)) << 4);
+                    *reinterpret_cast<uint4*>(s->p + off) =
+                        make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
+                    if (BF16)
+                        *reinterpret_cast<uint4*>(s->pLo + off) =
+                            make_uint4(packedLo[4 * q4], packedLo[4 * q4 + 1], packedLo[4 * q4 + 2], packedLo[4 * q4 + 3]);
+                }
+            }
+            l += sum;
+            tcFenceBefore();
+            mbarArrive(&s->sEmpty[b]);
+            if (k0 + kKeys > seqLen) {
+                // rows of V past the end of the sequence may hold anything: zero them
+                ok = mbarWait(&s->vFull[st], (j / kStages) & 1, s, errFlag, 9);
+                if (!ok) break;
+                if (k0 + t >= seqLen) {
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
+#pragma unroll
+                        for (int c16 = 0; c16 < 8; ++c16)
+                            *reinterpret_cast<uint4*>(s->v[st] + h * kHalfBytes + t * 128 + c16 * 16) = make_uint4(0u, 0u, 0u, 0u);
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbarArrive(&s->pFull);
+        }
+        // epilogue: O / l to global memory
+        if (ok && nT > 0) ok = mbarWait(&s->pvDone, (nT - 1) & 1, s, errFlag, 10);
+        if (ok) {
+            tcFenceAfter();
+            const float inv = (nT > 0 && l > 0.f) ? 1.f / l : 0.f;
+            unsigned char* out = static_cast<unsigned char*>(p.out) +
+                                 ((static_cast<int64_t>(rowBase) + t) * p.heads + head) * kHd * 2;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t r[32];
+                if (nT > 0) tmemLd32(tmemO + laneBase + c * 32, r);
+                if (t < rowsValid) {
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float a = nT > 0 ? __uint_as_float(r[8 * q4 + 2 * e]) * inv : 0.f;
+                            const float bb = nT > 0 ? __uint_as_float(r[8 * q4 + 2 * e + 1]) * inv : 0.f;
+                            w[e] = pack16<BF16>(a, bb);
+                        }
+                        *reinterpret_cast<uint4*>(out + c * 64 + q4 * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+            }
+        }
+    }
+
+    tcFenceBefore();
+    __syncthreads();
+    if (warp == 5) {
+        tcFenceAfter();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link
+// against libcuda).
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encodeFn() {
+    static EncodeFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeFn>(ptr);
+    }
+    return fn;
+}
+
+}  // namespace
+
+bool prefillTensorPathApplies(const PrefillParams& p) {
+    return (p.dtype == kF16 || p.dtype == kBF16) && p.headDim == kHd && p.blockSize % 16 == 0 && p.heads % p.kvHeads == 0 &&
+           (reinterpret_cast<uintptr_t>(p.q) & 15) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0 &&
+           (reinterpret_cast<uintptr_t>(p.kPool) & 15) == 0 && (reinterpret_cast<uintptr_t>(p.vPool) & 15) == 0 &&
+           p.poolBlocks > 0 && p.poolBlocks < (1 << 30) / (p.kvHeads * p.blockSize);
+}
+
+cudaError_t launchPrefillTensor(const PrefillParams& p, int totalRows, int* errFlag, cudaStream_t stream, int* launches) {
+    EncodeFn encode = encodeFn();
+    if (!encode) return cudaErrorNotSupported;
+    const CUtensorMapDataType dt = p.dtype == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    CUtensorMap mapQ, mapK, mapV;
+    {
+        // Q: [rows][heads][128]; a box is 64 dims x 1 head x 128 rows
+        cuuint64_t dims[3] = {static_cast<cuuint64_t>(kHd), static_cast<cuuint64_t>(p.heads), static_cast<cuuint64_t>(totalRows)};
+        cuuint64_t strides[2] = {static_cast<cuuint64_t>(kHd) * 2, static_cast<cuuint64_t>(p.heads) * kHd * 2};
+        cuuint32_t box[3] = {64, 1, static_cast<cuuint32_t>(kRows)};
+        cuuint32_t es[3] = {1, 1, 1};
+        if (encode(&mapQ, dt, 3, const_cast<void*>(p.q), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return cudaErrorInvalidValue;
+    }
+    const cuuint64_t poolRows = static_cast<cuuint64_t>(p.poolBlocks) * p.kvHeads * p.blockSize;
+    for (int which = 0; which < 2; ++which) {
+        // pools: [block * kv_head * slot][128]; a box is 64 dims x 16 rows (one half of a 16-token page piece)
+        cuuint64_t dims[2] = {static_cast<cuuint64_t>(kHd), poolRows};
+        cuuint64_t strides[1] = {static_cast<cuuint64_t>(kHd) * 2};
+        cuuint32_t box[2] = {64, 16};
+        cuuint32_t es[2] = {1, 1};
+        if (encode(which ? &mapV : &mapK, dt, 2, const_cast<void*>(which ? p.vPool : p.kPool), dims, strides, box, es,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return cudaErrorInvalidValue;
+    }
+    const size_t smem = sizeof(Smem) + 1024;
+    const float scaleLog2 = (1.0f / sqrtf(static_cast<float>(p.headDim))) * kLog2e;
+    dim3 grid(static_cast<unsigned>((p.maxQLen + kRows - 1) / kRows), static_cast<unsigned>(p.heads), static_cast<unsigned>(p.numSeqs));
+    cudaError_t e;
+    if (p.dtype == kBF16) {
+        e = cudaFuncSetAttribute(prefillTcKernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess) return e;
+        prefillTcKernel<true><<<grid, 192, smem, stream>>>(mapQ, mapK, mapV, p, scaleLog2, errFlag);
+    } else {
+        e = cudaFuncSetAttribute(prefillTcKernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess) return e;
+        prefillTcKernel<false><<<grid, 192, smem, stream>>>(mapQ, mapK, mapV, p, scaleLog2, errFlag);
+    }
+    if (launches) *launches += 1;
+    return cudaGetLastError();
+}
+
+}  // namespace pam

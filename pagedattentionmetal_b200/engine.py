@@ -185,6 +185,9 @@ class PagedAttentionEngine:
     def synchronize(self) -> None:
         _check(self._ctx, lib.pamc_synchronize(self._ctx))
 
+    def setPrefillTensorPath(self, on: bool) -> None:
+        lib.pamc_set_prefill_tensor_path(self._ctx, 1 if on else 0)
+
     def injectLaunchFailures(self, n: int) -> None:
         lib.pamc_inject_launch_failures(self._ctx, n)
 

@@ -109,12 +109,18 @@ def assert_close(out, ref, dtype):
     """max-abs error within the contract's bound.  The bound is on the value
     before the final rounding to the output type; a bfloat16 result carries one
     more rounding step of up to 2^-9 relative (2^-8 if the rounding flips), which
-    alone exceeds 2e-3 once |x| > 0.5, so that one unit in the last place of the
-    reference is allowed on top for bfloat16."""
+    alone exceeds 2e-3 once |x| > 0.5, so that one bfloat16 unit in the last place
+    of the reference value is allowed on top for bfloat16."""
     out = np.asarray(out, dtype=np.float64)
     ref = np.asarray(ref, dtype=np.float64)
-    ulp = 2.0 ** -8 if dtype == DT.bfloat16 else 0.0
-    ok = np.abs(out - ref) <= TOL[dtype] + ulp * np.abs(ref)
+    if dtype == DT.bfloat16:
+        # one bfloat16 unit in the last place of the reference value: 2^(exponent - 7)
+        with np.errstate(divide="ignore", invalid="ignore"):
+            ulp = np.where(ref != 0, 2.0 ** (np.floor(np.log2(np.abs(ref))) - 7), 0.0)
+        ulp = np.nan_to_num(ulp, nan=0.0)
+    else:
+        ulp = 0.0
+    ok = np.abs(out - ref) <= TOL[dtype] + ulp
     ok |= np.isnan(ref)
     assert ok.all(), f"max abs error {np.nanmax(np.abs(out - ref))}"
     assert np.isfinite(out).all()
