@@ -10,18 +10,20 @@
 // One CTA owns a tile of 128 query rows of one head of one sequence and walks
 // the key tiles (128 keys each) that those rows can see.
 //
-//   warp 4               TMA producer: the Q tile once, then per key tile the
+//   warp 8               TMA producer: the Q tile once, then per key tile the
 //                        8 pages of K and of V (each page is 16 rows x 256 B,
 //                        fetched as two 128-byte-swizzled boxes) into a
 //                        2-stage ring; completion on mbarriers.
-//   warp 5 (one thread)  MMA issuer: S = Q K^T (8 x tcgen05.mma 128x128x16)
+//   warp 9 (one thread)  MMA issuer: S = Q K^T (8 x tcgen05.mma 128x128x16)
 //                        into one of two S buffers in tensor memory, and
 //                        O += P V (8 more, V read as an MN-major operand
 //                        straight from its row-major pages); tcgen05.commit
 //                        signals the mbarriers.  QK^T of tile j+1 is issued
 //                        before PV of tile j so that the tensor pipe works
 //                        while the softmax warps are busy.
-//   warps 0-3            softmax: thread t owns row t.  S is read from tensor
+//   warps 0-7            softmax: two warpgroups, each owning half of the key
+//                        columns of every row (two warps per scheduler hide
+//                        each other's latencies).  S is read from tensor
 //                        memory (tcgen05.ld), scaled, masked (causal, window
 //                        start, sequence end) only on edge tiles; the running
 //                        maximum is only raised when it grows by more than 2^8
@@ -57,15 +59,18 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;
 constexpr long long kWaitCycles = 400000000LL;         // ~0.2 s
 
-struct Smem {
+template <bool BF16>
+struct SmemT {
     // tiles first: each 1024-byte aligned (swizzle atoms)
     unsigned char q[kTileBytes];
     unsigned char p[kTileBytes];
-    unsigned char pLo[kTileBytes];     // bfloat16 only: the part of P that the first 8 bits lose
+    unsigned char pLo[BF16 ? kTileBytes : 1024];   // bfloat16 only: the part of P that the first 8 bits lose
     unsigned char k[kStages][kTileBytes];
     unsigned char v[kStages][kTileBytes];
     unsigned long long qFull, kFull[kStages], vFull[kStages], kvEmpty[kStages];
-    unsigned long long sFull[2], sEmpty[2], pFull, pvDone;
+    unsigned long long sFull[2], sEmpty[2], pFull, pvDone, maxReady[2], sumReady;
+    float rowMax[2][2][kRows];     // [S buffer][column half][row]; the buffer the last tile does not
+                                   // use carries the row sums of the epilogue
     uint32_t tmemBase;
     int dead;
 };
@@ -95,14 +100,14 @@ __device__ __forceinline__ bool mbarTry(unsigned long long* bar, uint32_t parity
 }
 // Bounded wait.  Returns false (and marks the CTA dead) when the barrier did
 // not complete in time or another thread of the CTA already gave up.
-__device__ __forceinline__ bool mbarWait(unsigned long long* bar, uint32_t parity, Smem* s, int* errFlag, int where) {
+__device__ __forceinline__ bool mbarWait(unsigned long long* bar, uint32_t parity, int* dead, int* errFlag, int where) {
     if (mbarTry(bar, parity)) return true;
     const long long t0 = clock64();
     while (true) {
         if (mbarTry(bar, parity)) return true;
-        if (*reinterpret_cast<volatile int*>(&s->dead)) return false;
+        if (*reinterpret_cast<volatile int*>(dead)) return false;
         if (clock64() - t0 > kWaitCycles) {
-            *reinterpret_cast<volatile int*>(&s->dead) = 1;
+            *reinterpret_cast<volatile int*>(dead) = 1;
             atomicCAS(errFlag, 0, where);
             return false;
         }
@@ -184,12 +189,29 @@ __device__ __forceinline__ uint32_t pack16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
+__device__ __forceinline__ float ex2Approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+constexpr int kSoftmaxThreads = 256;                   // two warpgroups, each takes half of the key columns
+constexpr int kThreads = kSoftmaxThreads + 64;         // + producer warp + MMA warp
+constexpr int kProducerWarp = 8, kMmaWarp = 9;
+
 template <bool BF16>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(kThreads, 1)
 prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                 const __grid_constant__ CUtensorMap mapV, PrefillParams p, float scaleLog2, int* errFlag) {
-    extern __shared__ unsigned char rawSmem[];
-    Smem* s = reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(rawSmem) + 1023) & ~static_cast<uintptr_t>(1023));
+    // Dynamic shared memory starts on a 1024-byte boundary (the swizzle atoms
+    // need that); if it ever does not, give up cleanly instead of computing garbage.
+    extern __shared__ __align__(1024) unsigned char rawSmem[];
+    using Smem = SmemT<BF16>;
+    Smem* s = reinterpret_cast<Smem*>(rawSmem);
+    if ((smemAddr(rawSmem) & 1023u) != 0) {
+        if (threadIdx.x == 0) atomicCAS(errFlag, 0, 20);
+        return;
+    }
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);   // long tiles first
@@ -204,7 +226,7 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     const int firstPos = qStart + tile * kRows;                       // sequence position of row 0
     const int lastPos = firstPos + rowsValid - 1;
 
-    // Key tiles [tileLo, tileHi] hold every key a row of this tile may see.
+    // Key tiles tileLo .. tileLo + nT - 1 hold every key a row of this tile may see.
     const int keyEnd = p.causal ? min(seqLen, lastPos + 1) : seqLen;  // exclusive
     const int tileLo = ws / kKeys;
     const int nT = keyEnd > ws ? (keyEnd - 1) / kKeys - tileLo + 1 : 0;
@@ -212,13 +234,18 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     if (threadIdx.x == 0) {
         mbarInit(&s->qFull, 1);
         for (int i = 0; i < kStages; ++i) { mbarInit(&s->kFull[i], 1); mbarInit(&s->vFull[i], 1); mbarInit(&s->kvEmpty[i], 1); }
-        for (int i = 0; i < 2; ++i) { mbarInit(&s->sFull[i], 1); mbarInit(&s->sEmpty[i], 128); }
-        mbarInit(&s->pFull, 128);
+        for (int i = 0; i < 2; ++i) {
+            mbarInit(&s->sFull[i], 1);
+            mbarInit(&s->sEmpty[i], kSoftmaxThreads);
+            mbarInit(&s->maxReady[i], kSoftmaxThreads);
+        }
+        mbarInit(&s->pFull, kSoftmaxThreads);
         mbarInit(&s->pvDone, 1);
+        mbarInit(&s->sumReady, kSoftmaxThreads);
         s->dead = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 5) {
+    if (warp == kMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemAddr(&s->tmemBase)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -229,7 +256,7 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     const uint32_t tmemS[2] = {tmem, tmem + 128u};
     const uint32_t tmemO = tmem + 256u;
 
-    if (warp == 4) {
+    if (warp == kProducerWarp) {
         // ------------------------------------------------------------ TMA producer
         // Lane 0 arms the barriers; lanes 0-7 each fetch one 16-token page piece
         // of K and of V (their block-table reads run in parallel).
@@ -251,7 +278,7 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                     const int blk = min(max(table[page], 0), p.poolBlocks - 1);
                     row = (blk * p.kvHeads + kvh) * p.blockSize + (t16 % tilesPerPage) * 16;
                 }
-                if (j >= kStages) ok = mbarWait(&s->kvEmpty[st], ((j / kStages) - 1) & 1, s, errFlag, 1);
+                if (j >= kStages) ok = mbarWait(&s->kvEmpty[st], ((j / kStages) - 1) & 1, &s->dead, errFlag, 1);
                 ok = __all_sync(0xFFFFFFFFu, ok);
                 if (!ok) break;
                 if (lane == 0) {
@@ -267,7 +294,7 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 }
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == kMmaWarp) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0 && nT > 0) {
             const uint32_t fmt = BF16 ? 1u : 0u;
@@ -276,13 +303,13 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             // P has the type of the cache: a float16 P against bfloat16 V is rejected by
             // the hardware (illegal instruction), the two operands must agree.
             const uint32_t idescO = idescS | (1u << 16);
-            bool ok = mbarWait(&s->qFull, 0, s, errFlag, 2);
+            bool ok = mbarWait(&s->qFull, 0, &s->dead, errFlag, 2);
             const uint32_t qAddr = smemAddr(s->q), pAddr = smemAddr(s->p);
             for (int j = 0; j <= nT && ok; ++j) {
                 if (j < nT) {
                     const int b = j & 1, st = j % kStages;
-                    ok = mbarWait(&s->kFull[st], (j / kStages) & 1, s, errFlag, 3);
-                    if (ok && j >= 2) ok = mbarWait(&s->sEmpty[b], ((j / 2) - 1) & 1, s, errFlag, 4);
+                    ok = mbarWait(&s->kFull[st], (j / kStages) & 1, &s->dead, errFlag, 3);
+                    if (ok && j >= 2) ok = mbarWait(&s->sEmpty[b], ((j / 2) - 1) & 1, &s->dead, errFlag, 4);
                     if (!ok) break;
                     tcFenceAfter();
                     const uint32_t kAddr = smemAddr(s->k[st]);
@@ -295,8 +322,8 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 }
                 if (j >= 1) {
                     const int jj = j - 1, st = jj % kStages;
-                    ok = mbarWait(&s->pFull, jj & 1, s, errFlag, 5);
-                    if (ok) ok = mbarWait(&s->vFull[st], (jj / kStages) & 1, s, errFlag, 6);
+                    ok = mbarWait(&s->pFull, jj & 1, &s->dead, errFlag, 5);
+                    if (ok) ok = mbarWait(&s->vFull[st], (jj / kStages) & 1, &s->dead, errFlag, 6);
                     if (!ok) break;
                     tcFenceAfter();
                     const uint32_t vAddr = smemAddr(s->v[st]);
@@ -324,93 +351,114 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         }
     } else {
         // ------------------------------------------------------------ softmax warps
-        const int t = threadIdx.x;                      // row of the tile
+        // Thread (t, h): row t of the tile, key columns [64h, 64h + 64) of every
+        // key tile and output columns [64h, 64h + 64).  The two halves of a row
+        // exchange their maxima (and, at the end, their sums) through shared
+        // memory and a bounded mbarrier wait.
+        const int t = threadIdx.x & 127, h = threadIdx.x >> 7;
         const int rowPos = firstPos + t;
-        const uint32_t laneBase = static_cast<uint32_t>(warp * 32) << 16;
+        const uint32_t laneBase = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const uint32_t colBase = static_cast<uint32_t>(h * 64);
         float mUsed = -INFINITY, l = 0.f;
         bool ok = true;
         for (int j = 0; j < nT && ok; ++j) {
             const int b = j & 1, st = j % kStages;
             const int k0 = (tileLo + j) * kKeys;
+            const int kh = k0 + h * 64;                                     // first key of this thread's columns
             const bool edge = k0 < ws || k0 + kKeys > seqLen || (p.causal && k0 + kKeys - 1 > firstPos);
-            ok = mbarWait(&s->sFull[b], (j / 2) & 1, s, errFlag, 7);
+            ok = mbarWait(&s->sFull[b], (j / 2) & 1, &s->dead, errFlag, 7);
             if (!ok) break;
             tcFenceAfter();
-            // pass 1: row maximum of the scaled, masked scores
-            float tmax = -INFINITY;
+            // pass 1: maximum of the raw scores of this half row (the scale is positive)
+            float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {
                 uint32_t r[32];
-                tmemLd32(tmemS[b] + laneBase + c * 32, r);
+                tmemLd32(tmemS[b] + laneBase + colBase + c * 32, r);
+                if (!edge) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float x = __uint_as_float(r[i]) * scaleLog2;
-                    if (edge) {
-                        const int key = k0 + c * 32 + i;
-                        if (key < ws || key >= seqLen || (p.causal && key > rowPos)) x = -INFINITY;
+                    for (int i = 0; i < 32; i += 4) {
+                        m4[0] = fmaxf(m4[0], __uint_as_float(r[i]));
+                        m4[1] = fmaxf(m4[1], __uint_as_float(r[i + 1]));
+                        m4[2] = fmaxf(m4[2], __uint_as_float(r[i + 2]));
+                        m4[3] = fmaxf(m4[3], __uint_as_float(r[i + 3]));
                     }
-                    tmax = fmaxf(tmax, x);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int key = kh + c * 32 + i;
+                        const bool vis = key >= ws && key < seqLen && (!p.causal || key <= rowPos);
+                        m4[i & 3] = fmaxf(m4[i & 3], vis ? __uint_as_float(r[i]) : -INFINITY);
+                    }
                 }
             }
+            float tmax = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * scaleLog2;
+            s->rowMax[b][h][t] = tmax;
+            mbarArrive(&s->maxReady[b]);
+            ok = mbarWait(&s->maxReady[b], (j / 2) & 1, &s->dead, errFlag, 11);
+            if (!ok) break;
+            tmax = fmaxf(tmax, s->rowMax[b][h ^ 1][t]);
             bool raise = false;
             float corr = 1.f;
             if (j == 0) mUsed = tmax;
             else if (tmax > mUsed + kRescaleThreshold) {
                 raise = true;
-                corr = exp2f(mUsed - tmax);
+                corr = ex2Approx(mUsed - tmax);
                 mUsed = tmax;
             }
             if (j >= 1) {
                 // PV of the previous tile is done: P may be overwritten, O may be rescaled
-                ok = mbarWait(&s->pvDone, (j - 1) & 1, s, errFlag, 8);
+                ok = mbarWait(&s->pvDone, (j - 1) & 1, &s->dead, errFlag, 8);
                 if (!ok) break;
                 tcFenceAfter();
                 if (__any_sync(0xFFFFFFFFu, raise)) {
 #pragma unroll 1
-                    for (int c = 0; c < 4; ++c) {
+                    for (int c = 0; c < 2; ++c) {
                         uint32_t r[32];
-                        tmemLd32(tmemO + laneBase + c * 32, r);
+                        tmemLd32(tmemO + laneBase + colBase + c * 32, r);
 #pragma unroll
                         for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
-                        tmemSt32(tmemO + laneBase + c * 32, r);
+                        tmemSt32(tmemO + laneBase + colBase + c * 32, r);
                     }
                     tmemStWait();
                     l *= corr;
                 }
             }
-            // pass 2: probabilities to shared memory (cache type, K-major, 128-byte swizzle)
-            const float mEff = mUsed == -INFINITY ? 0.f : mUsed;
-            float sum = 0.f;
+            // pass 2: weights to shared memory (cache type, K-major, 128-byte swizzle);
+            // this thread's 64 keys are exactly column block h of the P tile
+            const float negM = mUsed == -INFINITY ? 0.f : -mUsed;
+            float s4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {
                 uint32_t r[32];
-                tmemLd32(tmemS[b] + laneBase + c * 32, r);
+                tmemLd32(tmemS[b] + laneBase + colBase + c * 32, r);
                 uint32_t packed[16];
                 uint32_t packedLo[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    float x0 = __uint_as_float(r[i]) * scaleLog2, x1 = __uint_as_float(r[i + 1]) * scaleLog2;
+                    float x0 = fmaf(__uint_as_float(r[i]), scaleLog2, negM);
+                    float x1 = fmaf(__uint_as_float(r[i + 1]), scaleLog2, negM);
                     if (edge) {
-                        const int key = k0 + c * 32 + i;
-                        if (key < ws || key >= seqLen || (p.causal && key > rowPos)) x0 = -INFINITY;
-                        if (key + 1 < ws || key + 1 >= seqLen || (p.causal && key + 1 > rowPos)) x1 = -INFINITY;
+                        const int key = kh + c * 32 + i;
+                        if (!(key >= ws && key < seqLen && (!p.causal || key <= rowPos))) x0 = -INFINITY;
+                        if (!(key + 1 >= ws && key + 1 < seqLen && (!p.causal || key + 1 <= rowPos))) x1 = -INFINITY;
                     }
-                    const float p0 = exp2f(x0 - mEff), p1 = exp2f(x1 - mEff);
-                    sum += p0 + p1;
+                    const float p0 = ex2Approx(x0), p1 = ex2Approx(x1);
+                    s4[(i >> 1) & 3] += p0 + p1;
                     packed[i / 2] = pack16<BF16>(p0, p1);
                     if (BF16) {
                         // bfloat16 keeps 8 significant bits of a weight; the remainder goes
                         // into a second operand so that P_hi + P_lo carries 16 bits
-                        const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&packed[i / 2]);
-                        packedLo[i / 2] = pack16<true>(p0 - __low2float(h), p1 - __high2float(h));
+                        const float h0 = __uint_as_float(packed[i / 2] << 16);
+                        const float h1 = __uint_as_float(packed[i / 2] & 0xFFFF0000u);
+                        packedLo[i / 2] = pack16<true>(p0 - h0, p1 - h1);
                     }
                 }
-                // 32 keys = 4 chunks of 16 bytes; column block c/2, chunks (c&1)*4 .. +3 of row t
-                const int rowOff = (c >> 1) * kHalfBytes + t * 128;
+                // 32 keys = 4 chunks of 16 bytes: chunks c*4 .. c*4+3 of row t in column block h
+                const int rowOff = h * kHalfBytes + t * 128;
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
-                    const int chunk = (c & 1) * 4 + q4;
-                    const int off = rowOff + ((chunk ^ (t & 7)) << 4);
+                    const int off = rowOff + (((c * 4 + q4) ^ (t & 7)) << 4);
                     *reinterpret_cast<uint4*>(s->p + off) =
                         make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
                     if (BF16)
@@ -418,35 +466,39 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                             make_uint4(packedLo[4 * q4], packedLo[4 * q4 + 1], packedLo[4 * q4 + 2], packedLo[4 * q4 + 3]);
                 }
             }
-            l += sum;
+            l += (s4[0] + s4[1]) + (s4[2] + s4[3]);
             tcFenceBefore();
             mbarArrive(&s->sEmpty[b]);
             if (k0 + kKeys > seqLen) {
                 // rows of V past the end of the sequence may hold anything: zero them
-                ok = mbarWait(&s->vFull[st], (j / kStages) & 1, s, errFlag, 9);
+                ok = mbarWait(&s->vFull[st], (j / kStages) & 1, &s->dead, errFlag, 9);
                 if (!ok) break;
                 if (k0 + t >= seqLen) {
 #pragma unroll
-                    for (int h = 0; h < 2; ++h)
-#pragma unroll
-                        for (int c16 = 0; c16 < 8; ++c16)
-                            *reinterpret_cast<uint4*>(s->v[st] + h * kHalfBytes + t * 128 + c16 * 16) = make_uint4(0u, 0u, 0u, 0u);
+                    for (int c16 = 0; c16 < 8; ++c16)
+                        *reinterpret_cast<uint4*>(s->v[st] + h * kHalfBytes + t * 128 + c16 * 16) = make_uint4(0u, 0u, 0u, 0u);
                 }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             mbarArrive(&s->pFull);
         }
         // epilogue: O / l to global memory
-        if (ok && nT > 0) ok = mbarWait(&s->pvDone, (nT - 1) & 1, s, errFlag, 10);
+        if (ok) {
+            s->rowMax[nT & 1][h][t] = l;
+            mbarArrive(&s->sumReady);
+            ok = mbarWait(&s->sumReady, 0, &s->dead, errFlag, 12);
+        }
+        if (ok && nT > 0) ok = mbarWait(&s->pvDone, (nT - 1) & 1, &s->dead, errFlag, 10);
         if (ok) {
             tcFenceAfter();
-            const float inv = (nT > 0 && l > 0.f) ? 1.f / l : 0.f;
+            const float lt = l + s->rowMax[nT & 1][h ^ 1][t];
+            const float inv = (nT > 0 && lt > 0.f) ? 1.f / lt : 0.f;
             unsigned char* out = static_cast<unsigned char*>(p.out) +
-                                 ((static_cast<int64_t>(rowBase) + t) * p.heads + head) * kHd * 2;
+                                 ((static_cast<int64_t>(rowBase) + t) * p.heads + head) * kHd * 2 + h * 128;
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {
                 uint32_t r[32];
-                if (nT > 0) tmemLd32(tmemO + laneBase + c * 32, r);
+                if (nT > 0) tmemLd32(tmemO + laneBase + colBase + c * 32, r);
                 if (t < rowsValid) {
 #pragma unroll
                     for (int q4 = 0; q4 < 4; ++q4) {
@@ -466,7 +518,7 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
 
     tcFenceBefore();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == kMmaWarp) {
         tcFenceAfter();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
     }
@@ -526,18 +578,18 @@ cudaError_t launchPrefillTensor(const PrefillParams& p, int totalRows, int* errF
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return cudaErrorInvalidValue;
     }
-    const size_t smem = sizeof(Smem) + 1024;
+    const size_t smem = p.dtype == kBF16 ? sizeof(SmemT<true>) : sizeof(SmemT<false>);
     const float scaleLog2 = (1.0f / sqrtf(static_cast<float>(p.headDim))) * kLog2e;
     dim3 grid(static_cast<unsigned>((p.maxQLen + kRows - 1) / kRows), static_cast<unsigned>(p.heads), static_cast<unsigned>(p.numSeqs));
     cudaError_t e;
     if (p.dtype == kBF16) {
         e = cudaFuncSetAttribute(prefillTcKernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (e != cudaSuccess) return e;
-        prefillTcKernel<true><<<grid, 192, smem, stream>>>(mapQ, mapK, mapV, p, scaleLog2, errFlag);
+        prefillTcKernel<true><<<grid, kThreads, smem, stream>>>(mapQ, mapK, mapV, p, scaleLog2, errFlag);
     } else {
         e = cudaFuncSetAttribute(prefillTcKernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (e != cudaSuccess) return e;
-        prefillTcKernel<false><<<grid, 192, smem, stream>>>(mapQ, mapK, mapV, p, scaleLog2, errFlag);
+        prefillTcKernel<false><<<grid, kThreads, smem, stream>>>(mapQ, mapK, mapV, p, scaleLog2, errFlag);
     }
     if (launches) *launches += 1;
     return cudaGetLastError();
