@@ -59,18 +59,13 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;
 constexpr long long kWaitCycles = 400000000LL;         // ~0.2 s
 
-template <bool BF16>
-struct SmemT {
+struct Smem {
     // tiles first: each 1024-byte aligned (swizzle atoms)
-    unsigned char q[kTileBytes];
-    unsigned char p[kTileBytes];
-    unsigned char pLo[BF16 ? kTileBytes : 1024];   // bfloat16 only: the part of P that the first 8 bits lose
+    unsigned char q[2][kTileBytes];            // two query tiles of 128 rows each
     unsigned char k[kStages][kTileBytes];
     unsigned char v[kStages][kTileBytes];
     unsigned long long qFull, kFull[kStages], vFull[kStages], kvEmpty[kStages];
-    unsigned long long sFull[2], sEmpty[2], pFull, pvDone, maxReady[2], sumReady;
-    float rowMax[2][2][kRows];     // [S buffer][column half][row]; the buffer the last tile does not
-                                   // use carries the row sums of the epilogue
+    unsigned long long sFull[2], pFull[2], pvDone[2];   // per query tile
     uint32_t tmemBase;
     int dead;
 };
@@ -148,6 +143,16 @@ __device__ __forceinline__ void umma(uint32_t tmemD, uint64_t descA, uint64_t de
         ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate), "r"(0u)
         : "memory");
 }
+// Same with the A operand read from tensor memory (row = lane, two 16-bit
+// elements of K per 32-bit column).
+__device__ __forceinline__ void ummaTs(uint32_t tmemD, uint32_t tmemA, uint64_t descB, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmemD), "r"(tmemA), "l"(descB), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
 __device__ __forceinline__ void ummaCommit(unsigned long long* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smemAddr(bar)) : "memory");
 }
@@ -195,9 +200,18 @@ __device__ __forceinline__ float ex2Approx(float x) {
     return y;
 }
 
-constexpr int kSoftmaxThreads = 256;                   // two warpgroups, each takes half of the key columns
+constexpr int kSoftmaxThreads = 256;                   // one warpgroup per query tile
 constexpr int kThreads = kSoftmaxThreads + 64;         // + producer warp + MMA warp
 constexpr int kProducerWarp = 8, kMmaWarp = 9;
+constexpr int kCtaRows = 2 * kRows;                    // query rows per CTA
+
+// Per query tile (slot x = 0, 1) of the CTA.
+struct SlotInfo {
+    int rowBase;     // first row of the tile in q/out
+    int rowsValid;   // rows of the tile that exist (<= 0: the tile is absent)
+    int firstPos;    // sequence position of row 0
+    int nT;          // key tiles this tile's rows can see (from tileLo on)
+};
 
 template <bool BF16>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -206,7 +220,6 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     // Dynamic shared memory starts on a 1024-byte boundary (the swizzle atoms
     // need that); if it ever does not, give up cleanly instead of computing garbage.
     extern __shared__ __align__(1024) unsigned char rawSmem[];
-    using Smem = SmemT<BF16>;
     Smem* s = reinterpret_cast<Smem*>(rawSmem);
     if ((smemAddr(rawSmem) & 1023u) != 0) {
         if (threadIdx.x == 0) atomicCAS(errFlag, 0, 20);
@@ -214,34 +227,36 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     }
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);   // long tiles first
+    const int pairIdx = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);   // long tiles first
     const int head = blockIdx.y, seq = blockIdx.z;
     const int qLen = p.qLens[seq];
-    if (tile * kRows >= qLen) return;
+    if (pairIdx * kCtaRows >= qLen) return;
     if (*reinterpret_cast<volatile int*>(errFlag) != 0) return;       // an earlier CTA gave up: do not pile up waits
     const int G = p.heads / p.kvHeads, kvh = head / G;
     const int qStart = p.qStarts[seq], seqLen = p.seqLens[seq], ws = p.windowStarts[seq];
-    const int rowBase = p.qRowOffsets[seq] + tile * kRows;            // first row of the tile in q/out
-    const int rowsValid = min(kRows, qLen - tile * kRows);
-    const int firstPos = qStart + tile * kRows;                       // sequence position of row 0
-    const int lastPos = firstPos + rowsValid - 1;
-
-    // Key tiles tileLo .. tileLo + nT - 1 hold every key a row of this tile may see.
-    const int keyEnd = p.causal ? min(seqLen, lastPos + 1) : seqLen;  // exclusive
     const int tileLo = ws / kKeys;
-    const int nT = keyEnd > ws ? (keyEnd - 1) / kKeys - tileLo + 1 : 0;
+
+    SlotInfo slot[2];
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+        const int tile = pairIdx * 2 + x;
+        slot[x].rowBase = p.qRowOffsets[seq] + tile * kRows;
+        slot[x].rowsValid = min(kRows, qLen - tile * kRows);
+        slot[x].firstPos = qStart + tile * kRows;
+        const int lastPos = slot[x].firstPos + slot[x].rowsValid - 1;
+        const int keyEnd = p.causal ? min(seqLen, lastPos + 1) : seqLen;                   // exclusive
+        slot[x].nT = (slot[x].rowsValid > 0 && keyEnd > ws) ? (keyEnd - 1) / kKeys - tileLo + 1 : 0;
+    }
+    const int nTmax = max(slot[0].nT, slot[1].nT);
 
     if (threadIdx.x == 0) {
         mbarInit(&s->qFull, 1);
         for (int i = 0; i < kStages; ++i) { mbarInit(&s->kFull[i], 1); mbarInit(&s->vFull[i], 1); mbarInit(&s->kvEmpty[i], 1); }
-        for (int i = 0; i < 2; ++i) {
-            mbarInit(&s->sFull[i], 1);
-            mbarInit(&s->sEmpty[i], kSoftmaxThreads);
-            mbarInit(&s->maxReady[i], kSoftmaxThreads);
+        for (int x = 0; x < 2; ++x) {
+            mbarInit(&s->sFull[x], 1);
+            mbarInit(&s->pFull[x], kRows);
+            mbarInit(&s->pvDone[x], 1);
         }
-        mbarInit(&s->pFull, kSoftmaxThreads);
-        mbarInit(&s->pvDone, 1);
-        mbarInit(&s->sumReady, kSoftmaxThreads);
         s->dead = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -253,23 +268,29 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     __syncthreads();
     tcFenceAfter();
     const uint32_t tmem = s->tmemBase;
-    const uint32_t tmemS[2] = {tmem, tmem + 128u};
-    const uint32_t tmemO = tmem + 256u;
+    // per query tile: S (aliased by P once the scores are consumed) and O
+    const uint32_t tmemS[2] = {tmem, tmem + 256u};
+    const uint32_t tmemO[2] = {tmem + 128u, tmem + 384u};
 
     if (warp == kProducerWarp) {
         // ------------------------------------------------------------ TMA producer
         // Lane 0 arms the barriers; lanes 0-7 each fetch one 16-token page piece
         // of K and of V (their block-table reads run in parallel).
-        if (nT > 0) {
+        if (nTmax > 0) {
             if (lane == 0) {
-                mbarExpectTx(&s->qFull, kTileBytes);
-                tmaLoad3d(s->q, &mapQ, &s->qFull, 0, head, rowBase);
-                tmaLoad3d(s->q + kHalfBytes, &mapQ, &s->qFull, 64, head, rowBase);
+                mbarExpectTx(&s->qFull, slot[1].nT > 0 ? 2 * kTileBytes : kTileBytes);
+#pragma unroll
+                for (int x = 0; x < 2; ++x) {
+                    if (x == 0 || slot[1].nT > 0) {
+                        tmaLoad3d(s->q[x], &mapQ, &s->qFull, 0, head, slot[x].rowBase);
+                        tmaLoad3d(s->q[x] + kHalfBytes, &mapQ, &s->qFull, 64, head, slot[x].rowBase);
+                    }
+                }
             }
             const int32_t* table = p.tables + static_cast<int64_t>(seq) * p.maxNumBlocks;
             const int tilesPerPage = p.blockSize / 16;
             bool ok = true;
-            for (int j = 0; j < nT && ok; ++j) {
+            for (int j = 0; j < nTmax && ok; ++j) {
                 const int st = j % kStages;
                 int row = 0;
                 if (lane < kKeys / 16) {
@@ -296,85 +317,95 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         }
     } else if (warp == kMmaWarp) {
         // ------------------------------------------------------------ MMA issuer
-        if (lane == 0 && nT > 0) {
+        // Tensor-core instructions of one thread execute in issue order, so S of
+        // tile j+1 (written over P of tile j) needs no wait on PV of tile j.
+        if (lane == 0 && nTmax > 0) {
             const uint32_t fmt = BF16 ? 1u : 0u;
             // D = f32, A/B = bf16|f16, M = 128, N = 128; B of the second product is MN-major.
             const uint32_t idescS = (1u << 4) | (fmt << 7) | (fmt << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
             // P has the type of the cache: a float16 P against bfloat16 V is rejected by
             // the hardware (illegal instruction), the two operands must agree.
             const uint32_t idescO = idescS | (1u << 16);
-            bool ok = mbarWait(&s->qFull, 0, &s->dead, errFlag, 2);
-            const uint32_t qAddr = smemAddr(s->q), pAddr = smemAddr(s->p);
-            for (int j = 0; j <= nT && ok; ++j) {
-                if (j < nT) {
-                    const int b = j & 1, st = j % kStages;
-                    ok = mbarWait(&s->kFull[st], (j / kStages) & 1, &s->dead, errFlag, 3);
-                    if (ok && j >= 2) ok = mbarWait(&s->sEmpty[b], ((j / 2) - 1) & 1, &s->dead, errFlag, 4);
-                    if (!ok) break;
-                    tcFenceAfter();
-                    const uint32_t kAddr = smemAddr(s->k[st]);
+            auto issueQK = [&](int x, int st) {
+                const uint32_t qAddr = smemAddr(s->q[x]), kAddr = smemAddr(s->k[st]);
 #pragma unroll
-                    for (int ks = 0; ks < kHd / 16; ++ks) {
-                        const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
-                        umma(tmemS[b], makeDesc(qAddr + off, 16, 1024), makeDesc(kAddr + off, 16, 1024), idescS, ks > 0);
-                    }
-                    ummaCommit(&s->sFull[b]);
+                for (int ks = 0; ks < kHd / 16; ++ks) {
+                    const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
+                    umma(tmemS[x], makeDesc(qAddr + off, 16, 1024), makeDesc(kAddr + off, 16, 1024), idescS, ks > 0);
                 }
-                if (j >= 1) {
-                    const int jj = j - 1, st = jj % kStages;
-                    ok = mbarWait(&s->pFull, jj & 1, &s->dead, errFlag, 5);
-                    if (ok) ok = mbarWait(&s->vFull[st], (jj / kStages) & 1, &s->dead, errFlag, 6);
-                    if (!ok) break;
-                    tcFenceAfter();
-                    const uint32_t vAddr = smemAddr(s->v[st]);
-#pragma unroll
-                    for (int ks = 0; ks < kKeys / 16; ++ks) {
-                        const uint32_t aOff = (ks >> 2) * kHalfBytes + (ks & 3) * 32;   // P: K-major, keys along K
-                        const uint32_t bOff = ks * 16 * 128;                            // V: 16 keys = 16 rows of 128 B
-                        umma(tmemO, makeDesc(pAddr + aOff, 16, 1024), makeDesc(vAddr + bOff, kHalfBytes, 1024), idescO,
-                             (jj > 0 || ks > 0) ? 1u : 0u);
-                    }
-                    if (BF16) {
-                        // second term of P = P_hi + P_lo (see the softmax warps)
-                        const uint32_t pLoAddr = smemAddr(s->pLo);
+                ummaCommit(&s->sFull[x]);
+            };
+            bool ok = mbarWait(&s->qFull, 0, &s->dead, errFlag, 2);
+            if (ok) ok = mbarWait(&s->kFull[0], 0, &s->dead, errFlag, 3);
+            if (ok) {
+                tcFenceAfter();
+                for (int x = 0; x < 2; ++x)
+                    if (slot[x].nT > 0) issueQK(x, 0);
+            }
+            for (int j = 0; j < nTmax && ok; ++j) {
+                const int st = j % kStages;
+                bool vReady = false, kNextReady = false;
+                for (int x = 0; x < 2 && ok; ++x) {
+                    if (j < slot[x].nT) {
+                        ok = mbarWait(&s->pFull[x], j & 1, &s->dead, errFlag, 5);
+                        if (ok && !vReady) { ok = mbarWait(&s->vFull[st], (j / kStages) & 1, &s->dead, errFlag, 6); vReady = true; }
+                        if (!ok) break;
+                        tcFenceAfter();
+                        const uint32_t vAddr = smemAddr(s->v[st]);
+                        // P of keys 32c .. 32c+31 sits in columns 32c .. 32c+15 (and, for bfloat16,
+                        // its low-order part in columns 32c+16 .. 32c+31) of the S region
 #pragma unroll
                         for (int ks = 0; ks < kKeys / 16; ++ks) {
-                            const uint32_t aOff = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
-                            umma(tmemO, makeDesc(pLoAddr + aOff, 16, 1024), makeDesc(vAddr + ks * 16 * 128, kHalfBytes, 1024),
-                                 idescO, 1u);
+                            const uint32_t pCol = tmemS[x] + 32u * (ks >> 1) + 8u * (ks & 1);
+                            ummaTs(tmemO[x], pCol, makeDesc(vAddr + ks * 16 * 128, kHalfBytes, 1024), idescO,
+                                   (j > 0 || ks > 0) ? 1u : 0u);
                         }
+                        if (BF16) {
+#pragma unroll
+                            for (int ks = 0; ks < kKeys / 16; ++ks) {
+                                const uint32_t pCol = tmemS[x] + 32u * (ks >> 1) + 8u * (ks & 1) + 16u;
+                                ummaTs(tmemO[x], pCol, makeDesc(vAddr + ks * 16 * 128, kHalfBytes, 1024), idescO, 1u);
+                            }
+                        }
+                        ummaCommit(&s->pvDone[x]);
                     }
-                    ummaCommit(&s->pvDone);
-                    ummaCommit(&s->kvEmpty[st]);
+                    if (j + 1 < slot[x].nT) {
+                        if (!kNextReady) {
+                            ok = mbarWait(&s->kFull[(j + 1) % kStages], ((j + 1) / kStages) & 1, &s->dead, errFlag, 3);
+                            kNextReady = true;
+                            if (!ok) break;
+                            tcFenceAfter();
+                        }
+                        issueQK(x, (j + 1) % kStages);
+                    }
                 }
+                if (ok) ummaCommit(&s->kvEmpty[st]);      // every instruction that reads stage st has been issued
             }
         }
     } else {
         // ------------------------------------------------------------ softmax warps
-        // Thread (t, h): row t of the tile, key columns [64h, 64h + 64) of every
-        // key tile and output columns [64h, 64h + 64).  The two halves of a row
-        // exchange their maxima (and, at the end, their sums) through shared
-        // memory and a bounded mbarrier wait.
-        const int t = threadIdx.x & 127, h = threadIdx.x >> 7;
-        const int rowPos = firstPos + t;
+        // Warpgroup x works on query tile x; thread t of it owns row t.
+        const int x = threadIdx.x >> 7, t = threadIdx.x & 127;
+        const SlotInfo me = slot[x];
+        const int rowPos = me.firstPos + t;
         const uint32_t laneBase = static_cast<uint32_t>((warp & 3) * 32) << 16;
-        const uint32_t colBase = static_cast<uint32_t>(h * 64);
+        const uint32_t sBase = tmemS[x] + laneBase, oBase = tmemO[x] + laneBase;
         float mUsed = -INFINITY, l = 0.f;
         bool ok = true;
-        for (int j = 0; j < nT && ok; ++j) {
-            const int b = j & 1, st = j % kStages;
+        for (int j = 0; j < me.nT && ok; ++j) {
+            const int st = j % kStages;
             const int k0 = (tileLo + j) * kKeys;
-            const int kh = k0 + h * 64;                                     // first key of this thread's columns
-            const bool edge = k0 < ws || k0 + kKeys > seqLen || (p.causal && k0 + kKeys - 1 > firstPos);
-            ok = mbarWait(&s->sFull[b], (j / 2) & 1, &s->dead, errFlag, 7);
+            const bool edge = k0 < ws || k0 + kKeys > seqLen || (p.causal && k0 + kKeys - 1 > me.firstPos);
+            // S of tile j is complete; so is every earlier instruction, PV of tile j-1 included
+            ok = mbarWait(&s->sFull[x], j & 1, &s->dead, errFlag, 7);
             if (!ok) break;
             tcFenceAfter();
-            // pass 1: maximum of the raw scores of this half row (the scale is positive)
+            // pass 1: maximum of the raw scores of the row (the scale is positive)
             float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll 1
-            for (int c = 0; c < 2; ++c) {
+            for (int c = 0; c < 4; ++c) {
                 uint32_t r[32];
-                tmemLd32(tmemS[b] + laneBase + colBase + c * 32, r);
+                tmemLd32(sBase + c * 32, r);
                 if (!edge) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 4) {
@@ -386,18 +417,13 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 } else {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
-                        const int key = kh + c * 32 + i;
+                        const int key = k0 + c * 32 + i;
                         const bool vis = key >= ws && key < seqLen && (!p.causal || key <= rowPos);
                         m4[i & 3] = fmaxf(m4[i & 3], vis ? __uint_as_float(r[i]) : -INFINITY);
                     }
                 }
             }
-            float tmax = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * scaleLog2;
-            s->rowMax[b][h][t] = tmax;
-            mbarArrive(&s->maxReady[b]);
-            ok = mbarWait(&s->maxReady[b], (j / 2) & 1, &s->dead, errFlag, 11);
-            if (!ok) break;
-            tmax = fmaxf(tmax, s->rowMax[b][h ^ 1][t]);
+            const float tmax = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * scaleLog2;
             bool raise = false;
             float corr = 1.f;
             if (j == 0) mUsed = tmax;
@@ -406,110 +432,92 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 corr = ex2Approx(mUsed - tmax);
                 mUsed = tmax;
             }
-            if (j >= 1) {
-                // PV of the previous tile is done: P may be overwritten, O may be rescaled
-                ok = mbarWait(&s->pvDone, (j - 1) & 1, &s->dead, errFlag, 8);
-                if (!ok) break;
-                tcFenceAfter();
-                if (__any_sync(0xFFFFFFFFu, raise)) {
+            if (j >= 1 && __any_sync(0xFFFFFFFFu, raise)) {
 #pragma unroll 1
-                    for (int c = 0; c < 2; ++c) {
-                        uint32_t r[32];
-                        tmemLd32(tmemO + laneBase + colBase + c * 32, r);
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t r[32];
+                    tmemLd32(oBase + c * 32, r);
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
-                        tmemSt32(tmemO + laneBase + colBase + c * 32, r);
-                    }
-                    tmemStWait();
-                    l *= corr;
+                    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
+                    tmemSt32(oBase + c * 32, r);
                 }
+                l *= corr;
             }
-            // pass 2: weights to shared memory (cache type, K-major, 128-byte swizzle);
-            // this thread's 64 keys are exactly column block h of the P tile
+            // pass 2: the weights replace the scores in tensor memory, 32 keys at a time:
+            // 16 columns of packed pairs (plus 16 columns of their low-order parts for bfloat16)
             const float negM = mUsed == -INFINITY ? 0.f : -mUsed;
             float s4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 1
-            for (int c = 0; c < 2; ++c) {
+            for (int c = 0; c < 4; ++c) {
                 uint32_t r[32];
-                tmemLd32(tmemS[b] + laneBase + colBase + c * 32, r);
-                uint32_t packed[16];
-                uint32_t packedLo[16];
+                tmemLd32(sBase + c * 32, r);
+                uint32_t w[32];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
                     float x0 = fmaf(__uint_as_float(r[i]), scaleLog2, negM);
                     float x1 = fmaf(__uint_as_float(r[i + 1]), scaleLog2, negM);
                     if (edge) {
-                        const int key = kh + c * 32 + i;
+                        const int key = k0 + c * 32 + i;
                         if (!(key >= ws && key < seqLen && (!p.causal || key <= rowPos))) x0 = -INFINITY;
                         if (!(key + 1 >= ws && key + 1 < seqLen && (!p.causal || key + 1 <= rowPos))) x1 = -INFINITY;
                     }
                     const float p0 = ex2Approx(x0), p1 = ex2Approx(x1);
                     s4[(i >> 1) & 3] += p0 + p1;
-                    packed[i / 2] = pack16<BF16>(p0, p1);
+                    w[i / 2] = pack16<BF16>(p0, p1);
                     if (BF16) {
                         // bfloat16 keeps 8 significant bits of a weight; the remainder goes
                         // into a second operand so that P_hi + P_lo carries 16 bits
-                        const float h0 = __uint_as_float(packed[i / 2] << 16);
-                        const float h1 = __uint_as_float(packed[i / 2] & 0xFFFF0000u);
-                        packedLo[i / 2] = pack16<true>(p0 - h0, p1 - h1);
+                        const float h0 = __uint_as_float(w[i / 2] << 16);
+                        const float h1 = __uint_as_float(w[i / 2] & 0xFFFF0000u);
+                        w[16 + i / 2] = pack16<true>(p0 - h0, p1 - h1);
+                    } else {
+                        w[16 + i / 2] = 0u;
                     }
                 }
-                // 32 keys = 4 chunks of 16 bytes: chunks c*4 .. c*4+3 of row t in column block h
-                const int rowOff = h * kHalfBytes + t * 128;
-#pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    const int off = rowOff + (((c * 4 + q4) ^ (t & 7)) << 4);
-                    *reinterpret_cast<uint4*>(s->p + off) =
-                        make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
-                    if (BF16)
-                        *reinterpret_cast<uint4*>(s->pLo + off) =
-                            make_uint4(packedLo[4 * q4], packedLo[4 * q4 + 1], packedLo[4 * q4 + 2], packedLo[4 * q4 + 3]);
-                }
+                tmemSt32(sBase + c * 32, w);
             }
+            tmemStWait();
             l += (s4[0] + s4[1]) + (s4[2] + s4[3]);
-            tcFenceBefore();
-            mbarArrive(&s->sEmpty[b]);
-            if (k0 + kKeys > seqLen) {
-                // rows of V past the end of the sequence may hold anything: zero them
+            // The lowest-numbered query tile that uses this key tile clears the rows of V
+            // past the end of the sequence (they may hold anything); the MMA thread
+            // takes the query tiles in that order.
+            if (k0 + kKeys > seqLen && (x == 0 || j >= slot[0].nT)) {
                 ok = mbarWait(&s->vFull[st], (j / kStages) & 1, &s->dead, errFlag, 9);
                 if (!ok) break;
                 if (k0 + t >= seqLen) {
 #pragma unroll
-                    for (int c16 = 0; c16 < 8; ++c16)
-                        *reinterpret_cast<uint4*>(s->v[st] + h * kHalfBytes + t * 128 + c16 * 16) = make_uint4(0u, 0u, 0u, 0u);
+                    for (int hh = 0; hh < 2; ++hh)
+#pragma unroll
+                        for (int c16 = 0; c16 < 8; ++c16)
+                            *reinterpret_cast<uint4*>(s->v[st] + hh * kHalfBytes + t * 128 + c16 * 16) = make_uint4(0u, 0u, 0u, 0u);
                 }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbarArrive(&s->pFull);
+            tcFenceBefore();
+            mbarArrive(&s->pFull[x]);
         }
         // epilogue: O / l to global memory
-        if (ok) {
-            s->rowMax[nT & 1][h][t] = l;
-            mbarArrive(&s->sumReady);
-            ok = mbarWait(&s->sumReady, 0, &s->dead, errFlag, 12);
-        }
-        if (ok && nT > 0) ok = mbarWait(&s->pvDone, (nT - 1) & 1, &s->dead, errFlag, 10);
-        if (ok) {
+        if (ok && me.nT > 0) ok = mbarWait(&s->pvDone[x], (me.nT - 1) & 1, &s->dead, errFlag, 10);
+        if (ok && me.rowsValid > 0) {
             tcFenceAfter();
-            const float lt = l + s->rowMax[nT & 1][h ^ 1][t];
-            const float inv = (nT > 0 && lt > 0.f) ? 1.f / lt : 0.f;
+            const float inv = (me.nT > 0 && l > 0.f) ? 1.f / l : 0.f;
             unsigned char* out = static_cast<unsigned char*>(p.out) +
-                                 ((static_cast<int64_t>(rowBase) + t) * p.heads + head) * kHd * 2 + h * 128;
+                                 ((static_cast<int64_t>(me.rowBase) + t) * p.heads + head) * kHd * 2;
 #pragma unroll 1
-            for (int c = 0; c < 2; ++c) {
+            for (int c = 0; c < 4; ++c) {
                 uint32_t r[32];
-                if (nT > 0) tmemLd32(tmemO + laneBase + colBase + c * 32, r);
-                if (t < rowsValid) {
+                if (me.nT > 0) tmemLd32(oBase + c * 32, r);
+                if (t < me.rowsValid) {
 #pragma unroll
                     for (int q4 = 0; q4 < 4; ++q4) {
-                        uint32_t w[4];
+                        uint32_t wv[4];
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            const float a = nT > 0 ? __uint_as_float(r[8 * q4 + 2 * e]) * inv : 0.f;
-                            const float bb = nT > 0 ? __uint_as_float(r[8 * q4 + 2 * e + 1]) * inv : 0.f;
-                            w[e] = pack16<BF16>(a, bb);
+                            const float a = me.nT > 0 ? __uint_as_float(r[8 * q4 + 2 * e]) * inv : 0.f;
+                            const float bb = me.nT > 0 ? __uint_as_float(r[8 * q4 + 2 * e + 1]) * inv : 0.f;
+                            wv[e] = pack16<BF16>(a, bb);
                         }
-                        *reinterpret_cast<uint4*>(out + c * 64 + q4 * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+                        *reinterpret_cast<uint4*>(out + c * 64 + q4 * 16) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
                     }
                 }
             }
@@ -578,9 +586,9 @@ cudaError_t launchPrefillTensor(const PrefillParams& p, int totalRows, int* errF
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return cudaErrorInvalidValue;
     }
-    const size_t smem = p.dtype == kBF16 ? sizeof(SmemT<true>) : sizeof(SmemT<false>);
+    const size_t smem = sizeof(Smem);
     const float scaleLog2 = (1.0f / sqrtf(static_cast<float>(p.headDim))) * kLog2e;
-    dim3 grid(static_cast<unsigned>((p.maxQLen + kRows - 1) / kRows), static_cast<unsigned>(p.heads), static_cast<unsigned>(p.numSeqs));
+    dim3 grid(static_cast<unsigned>((p.maxQLen + kCtaRows - 1) / kCtaRows), static_cast<unsigned>(p.heads), static_cast<unsigned>(p.numSeqs));
     cudaError_t e;
     if (p.dtype == kBF16) {
         e = cudaFuncSetAttribute(prefillTcKernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
