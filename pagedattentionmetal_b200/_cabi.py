@@ -9,7 +9,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libpam_cuda.so")
+# PAM_CUDA_LIBRARY selects another build of the same library (an instrumented one, say).
+LIB_PATH = os.environ.get("PAM_CUDA_LIBRARY") or os.path.join(_HERE, "libpam_cuda.so")
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(

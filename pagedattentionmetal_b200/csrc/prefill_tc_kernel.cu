@@ -7,33 +7,38 @@
 // kernels.metal:693-765, plus the chunk rows of
 // PagedAttentionEngine.swift:740-756).
 //
-// One CTA owns a tile of 128 query rows of one head of one sequence and walks
-// the key tiles (128 keys each) that those rows can see.
+// One CTA owns 256 query rows of one head of one sequence, as two query tiles
+// of 128 rows, and walks the key tiles (128 keys each) those rows can see.
+// Both query tiles use the same K/V tiles in shared memory.  Tensor memory
+// (512 columns) holds, per query tile, S (128 columns, overwritten in place by
+// the weights P) and the accumulator O (128 columns).
 //
-//   warp 8               TMA producer: the Q tile once, then per key tile the
-//                        8 pages of K and of V (each page is 16 rows x 256 B,
-//                        fetched as two 128-byte-swizzled boxes) into a
-//                        2-stage ring; completion on mbarriers.
-//   warp 9 (one thread)  MMA issuer: S = Q K^T (8 x tcgen05.mma 128x128x16)
-//                        into one of two S buffers in tensor memory, and
-//                        O += P V (8 more, V read as an MN-major operand
+//   warp 16              TMA producer: the two Q tiles once, then per key tile
+//                        the 8 pages of K and of V (each page is 16 rows x
+//                        256 B, fetched as two 128-byte-swizzled boxes, one
+//                        page per lane) into a 2-stage ring; completion on
+//                        mbarriers.
+//   warp 17 (one thread) MMA issuer: S = Q K^T (8 x tcgen05.mma 128x128x16,
+//                        both operands from shared memory) and O += P V (P
+//                        read from tensor memory, V as an MN-major operand
 //                        straight from its row-major pages); tcgen05.commit
-//                        signals the mbarriers.  QK^T of tile j+1 is issued
-//                        before PV of tile j so that the tensor pipe works
-//                        while the softmax warps are busy.
-//   warps 0-7            softmax: two warpgroups, each owning half of the key
-//                        columns of every row (two warps per scheduler hide
-//                        each other's latencies).  S is read from tensor
-//                        memory (tcgen05.ld), scaled, masked (causal, window
-//                        start, sequence end) only on edge tiles; the running
-//                        maximum is only raised when it grows by more than 2^8
-//                        (the result is exact either way, the final division
-//                        uses the same reference), in which case O is rescaled
-//                        in tensor memory; P goes to shared memory in the cache
-//                        type, in the swizzled K-major layout the MMA reads; for
-//                        bfloat16 as two operands P_hi + P_lo (16 significant
-//                        bits together) and twice the PV instructions, because
-//                        8-bit weights alone miss the 2e-3 bound on short rows.
+//                        signals the mbarriers.  The two query tiles alternate,
+//                        so that the tensor pipe works on one while the
+//                        softmax warps work on the other.
+//   warps 0-15           softmax, eight warps per query tile: thread (t, h)
+//                        owns row t and the key columns [64h, 64h+64).  S is
+//                        read from tensor memory (tcgen05.ld), scaled, masked
+//                        (causal, window start, sequence end) only on edge
+//                        tiles; the two halves of a row exchange their maxima
+//                        through shared memory.  The running maximum is only
+//                        raised when it grows by more than 2^8 (the result is
+//                        exact either way, the final division uses the same
+//                        reference), in which case O is rescaled in tensor
+//                        memory.  The weights go back to tensor memory in the
+//                        cache type (tcgen05.st); for bfloat16 as two operands
+//                        P_hi + P_lo (16 significant bits together) and twice
+//                        the PV instructions, because 8-bit weights alone miss
+//                        the 2e-3 bound on short rows.
 //
 // Every wait on an mbarrier is bounded; a wait that runs out raises a flag the
 // host reads and the CTA falls through to the common exit, where the tensor
@@ -59,6 +64,21 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;
 constexpr long long kWaitCycles = 400000000LL;         // ~0.2 s
 
+#ifdef PAM_PREFILL_TRACE
+// Instrumented build only: CTA (0,0,0) keeps clock stamps [role][tile][event] in
+// shared memory (no global traffic while it runs) and dumps them at the end.
+constexpr int kTraceRoles = 4, kTraceTiles = 32, kTraceEvents = 12;
+__device__ long long gTrace[kTraceRoles * kTraceTiles * kTraceEvents];
+#define TRACE(role, tile, event)                                                                        \
+    do {                                                                                                \
+        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (threadIdx.x & 31) == 0 &&         \
+            (role) < kTraceRoles && (tile) < kTraceTiles)                                               \
+            s->trace[((role) * kTraceTiles + (tile)) * kTraceEvents + (event)] = clock64();             \
+    } while (0)
+#else
+#define TRACE(role, tile, event)
+#endif
+
 struct Smem {
     // tiles first: each 1024-byte aligned (swizzle atoms)
     unsigned char q[2][kTileBytes];            // two query tiles of 128 rows each
@@ -66,8 +86,13 @@ struct Smem {
     unsigned char v[kStages][kTileBytes];
     unsigned long long qFull, kFull[kStages], vFull[kStages], kvEmpty[kStages];
     unsigned long long sFull[2], pFull[2], pvDone[2];   // per query tile
+    unsigned long long maxReady[2][2], sumReady[2];     // exchange between the two halves of a row
+    float rowMax[2][2][2][kRows];                       // [query tile][parity][column half][row]
     uint32_t tmemBase;
     int dead;
+#ifdef PAM_PREFILL_TRACE
+    long long trace[kTraceRoles * kTraceTiles * kTraceEvents];
+#endif
 };
 
 __device__ __forceinline__ uint32_t smemAddr(const void* p) {
@@ -93,13 +118,27 @@ __device__ __forceinline__ bool mbarTry(unsigned long long* bar, uint32_t parity
         : "memory");
     return ok != 0;
 }
+// The same with a suspend-time hint: the warp sleeps in hardware until the
+// phase completes or about that many nanoseconds have passed, instead of
+// spinning through issue slots that the working warps need.
+__device__ __forceinline__ bool mbarTrySleep(unsigned long long* bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smemAddr(bar)), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait.  Returns false (and marks the CTA dead) when the barrier did
 // not complete in time or another thread of the CTA already gave up.
 __device__ __forceinline__ bool mbarWait(unsigned long long* bar, uint32_t parity, int* dead, int* errFlag, int where) {
     if (mbarTry(bar, parity)) return true;
     const long long t0 = clock64();
     while (true) {
-        if (mbarTry(bar, parity)) return true;
+        if (mbarTrySleep(bar, parity, 20000u)) return true;
         if (*reinterpret_cast<volatile int*>(dead)) return false;
         if (clock64() - t0 > kWaitCycles) {
             *reinterpret_cast<volatile int*>(dead) = 1;
@@ -132,6 +171,19 @@ __device__ __forceinline__ uint64_t makeDesc(uint32_t addr, uint32_t lboBytes, u
     d |= static_cast<uint64_t>((sboBytes >> 4) & 0x3FFFu) << 32;
     d |= 1ull << 46;       // version
     d |= 2ull << 61;       // SWIZZLE_128B
+    return d;
+}
+
+// The two halves of a descriptor: the high word is the same for every tile of a
+// layout, the low word is the start address (in 16-byte units) plus the LBO
+// field, so that stepping through a tile is one integer add on the low word.
+__device__ __forceinline__ uint32_t descHi(uint32_t sboBytes) { return ((sboBytes >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29); }
+__device__ __forceinline__ uint32_t descLo(uint32_t addr, uint32_t lboBytes) {
+    return ((addr & 0x3FFFFu) >> 4) | (((lboBytes >> 4) & 0x3FFFu) << 16);
+}
+__device__ __forceinline__ uint64_t desc64(uint32_t lo, uint32_t hi) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
     return d;
 }
 
@@ -171,6 +223,19 @@ __device__ __forceinline__ void tmemLd32(uint32_t taddr, uint32_t (&r)[32]) {
         : "r"(taddr));
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+// The same load without the wait, to keep several loads in flight.
+__device__ __forceinline__ void tmemLd32NoWait(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmemLdWait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmemSt32(uint32_t taddr, const uint32_t (&r)[32]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -200,9 +265,64 @@ __device__ __forceinline__ float ex2Approx(float x) {
     return y;
 }
 
-constexpr int kSoftmaxThreads = 256;                   // one warpgroup per query tile
+// Visibility of key `key` for the row at sequence position `rowPos`.
+struct MaskInfo {
+    int ws, seqLen, rowPos, causal;
+    __device__ __forceinline__ bool visible(int key) const {
+        return key >= ws && key < seqLen && (!causal || key <= rowPos);
+    }
+};
+
+// Maximum of 64 raw scores (two loaded chunks); EDGE tiles mask invisible keys.
+template <bool EDGE>
+__device__ __forceinline__ float halfRowMax(const uint32_t (&r0)[32], const uint32_t (&r1)[32], const MaskInfo& mk, int firstKey) {
+    float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        float a = __uint_as_float(r0[i]), b = __uint_as_float(r1[i]);
+        if (EDGE) {
+            if (!mk.visible(firstKey + i)) a = -INFINITY;
+            if (!mk.visible(firstKey + 32 + i)) b = -INFINITY;
+        }
+        m4[i & 3] = fmaxf(m4[i & 3], fmaxf(a, b));
+    }
+    return fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+}
+
+// 32 scores -> 16 packed weight pairs (w[0..15]) and, for bfloat16, the 16 pairs
+// of their low-order parts (w[16..31]); returns the sum of the weights.
+template <bool BF16, bool EDGE>
+__device__ __forceinline__ float weights32(const uint32_t (&r)[32], uint32_t (&w)[32], float scaleLog2, float negM,
+                                           const MaskInfo& mk, int firstKey) {
+    float s4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+        float x0 = fmaf(__uint_as_float(r[i]), scaleLog2, negM);
+        float x1 = fmaf(__uint_as_float(r[i + 1]), scaleLog2, negM);
+        if (EDGE) {
+            if (!mk.visible(firstKey + i)) x0 = -INFINITY;
+            if (!mk.visible(firstKey + i + 1)) x1 = -INFINITY;
+        }
+        const float p0 = ex2Approx(x0), p1 = ex2Approx(x1);
+        s4[(i >> 1) & 3] += p0 + p1;
+        w[i / 2] = pack16<BF16>(p0, p1);
+        if (BF16) {
+            // bfloat16 keeps 8 significant bits of a weight; the remainder goes into a
+            // second operand so that P_hi + P_lo carries 16 bits
+            const float h0 = __uint_as_float(w[i / 2] << 16);
+            const float h1 = __uint_as_float(w[i / 2] & 0xFFFF0000u);
+            w[16 + i / 2] = pack16<true>(p0 - h0, p1 - h1);
+        } else {
+            w[16 + i / 2] = 0u;
+        }
+    }
+    return (s4[0] + s4[1]) + (s4[2] + s4[3]);
+}
+
+constexpr int kSlotThreads = 256;                      // softmax threads per query tile: two per row
+constexpr int kSoftmaxThreads = 2 * kSlotThreads;
 constexpr int kThreads = kSoftmaxThreads + 64;         // + producer warp + MMA warp
-constexpr int kProducerWarp = 8, kMmaWarp = 9;
+constexpr int kProducerWarp = 16, kMmaWarp = 17;
 constexpr int kCtaRows = 2 * kRows;                    // query rows per CTA
 
 // Per query tile (slot x = 0, 1) of the CTA.
@@ -254,8 +374,11 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         for (int i = 0; i < kStages; ++i) { mbarInit(&s->kFull[i], 1); mbarInit(&s->vFull[i], 1); mbarInit(&s->kvEmpty[i], 1); }
         for (int x = 0; x < 2; ++x) {
             mbarInit(&s->sFull[x], 1);
-            mbarInit(&s->pFull[x], kRows);
+            mbarInit(&s->pFull[x], kSlotThreads);
             mbarInit(&s->pvDone[x], 1);
+            mbarInit(&s->maxReady[x][0], kSlotThreads);
+            mbarInit(&s->maxReady[x][1], kSlotThreads);
+            mbarInit(&s->sumReady[x], kSlotThreads);
         }
         s->dead = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -326,12 +449,15 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             // P has the type of the cache: a float16 P against bfloat16 V is rejected by
             // the hardware (illegal instruction), the two operands must agree.
             const uint32_t idescO = idescS | (1u << 16);
+            const uint32_t hiK = descHi(1024);                      // K-major tiles and the MN-major V tile share it
+            const uint32_t qLo[2] = {descLo(smemAddr(s->q[0]), 16), descLo(smemAddr(s->q[1]), 16)};
+            const uint32_t kLo[kStages] = {descLo(smemAddr(s->k[0]), 16), descLo(smemAddr(s->k[1]), 16)};
+            const uint32_t vLo[kStages] = {descLo(smemAddr(s->v[0]), kHalfBytes), descLo(smemAddr(s->v[1]), kHalfBytes)};
             auto issueQK = [&](int x, int st) {
-                const uint32_t qAddr = smemAddr(s->q[x]), kAddr = smemAddr(s->k[st]);
 #pragma unroll
                 for (int ks = 0; ks < kHd / 16; ++ks) {
-                    const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
-                    umma(tmemS[x], makeDesc(qAddr + off, 16, 1024), makeDesc(kAddr + off, 16, 1024), idescS, ks > 0);
+                    const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
+                    umma(tmemS[x], desc64(qLo[x] + off, hiK), desc64(kLo[st] + off, hiK), idescS, ks > 0);
                 }
                 ummaCommit(&s->sFull[x]);
             };
@@ -347,27 +473,28 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 bool vReady = false, kNextReady = false;
                 for (int x = 0; x < 2 && ok; ++x) {
                     if (j < slot[x].nT) {
+                        TRACE(2 + x, j, 0);
                         ok = mbarWait(&s->pFull[x], j & 1, &s->dead, errFlag, 5);
+                        TRACE(2 + x, j, 1);
                         if (ok && !vReady) { ok = mbarWait(&s->vFull[st], (j / kStages) & 1, &s->dead, errFlag, 6); vReady = true; }
                         if (!ok) break;
                         tcFenceAfter();
-                        const uint32_t vAddr = smemAddr(s->v[st]);
                         // P of keys 32c .. 32c+31 sits in columns 32c .. 32c+15 (and, for bfloat16,
                         // its low-order part in columns 32c+16 .. 32c+31) of the S region
 #pragma unroll
                         for (int ks = 0; ks < kKeys / 16; ++ks) {
                             const uint32_t pCol = tmemS[x] + 32u * (ks >> 1) + 8u * (ks & 1);
-                            ummaTs(tmemO[x], pCol, makeDesc(vAddr + ks * 16 * 128, kHalfBytes, 1024), idescO,
-                                   (j > 0 || ks > 0) ? 1u : 0u);
+                            ummaTs(tmemO[x], pCol, desc64(vLo[st] + ks * 128, hiK), idescO, (j > 0 || ks > 0) ? 1u : 0u);
                         }
                         if (BF16) {
 #pragma unroll
                             for (int ks = 0; ks < kKeys / 16; ++ks) {
                                 const uint32_t pCol = tmemS[x] + 32u * (ks >> 1) + 8u * (ks & 1) + 16u;
-                                ummaTs(tmemO[x], pCol, makeDesc(vAddr + ks * 16 * 128, kHalfBytes, 1024), idescO, 1u);
+                                ummaTs(tmemO[x], pCol, desc64(vLo[st] + ks * 128, hiK), idescO, 1u);
                             }
                         }
                         ummaCommit(&s->pvDone[x]);
+                        TRACE(2 + x, j, 2);
                     }
                     if (j + 1 < slot[x].nT) {
                         if (!kNextReady) {
@@ -377,6 +504,7 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                             tcFenceAfter();
                         }
                         issueQK(x, (j + 1) % kStages);
+                        TRACE(2 + x, j, 3);
                     }
                 }
                 if (ok) ummaCommit(&s->kvEmpty[st]);      // every instruction that reads stage st has been issued
@@ -384,46 +512,47 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         }
     } else {
         // ------------------------------------------------------------ softmax warps
-        // Warpgroup x works on query tile x; thread t of it owns row t.
-        const int x = threadIdx.x >> 7, t = threadIdx.x & 127;
+        // Eight warps per query tile x.  Thread (t, h) owns row t and the key
+        // columns [64h, 64h + 64) of every key tile, and the output columns
+        // [64h, 64h + 64).  Four warps per scheduler cover each other's latencies;
+        // the two halves of a row exchange their maxima (and at the end their
+        // sums) through shared memory and a bounded mbarrier wait.
+        const int x = warp >> 3, h = (warp >> 2) & 1, t = (warp & 3) * 32 + lane;
         const SlotInfo me = slot[x];
         const int rowPos = me.firstPos + t;
         const uint32_t laneBase = static_cast<uint32_t>((warp & 3) * 32) << 16;
-        const uint32_t sBase = tmemS[x] + laneBase, oBase = tmemO[x] + laneBase;
+        const uint32_t sBase = tmemS[x] + laneBase + 64u * h, oBase = tmemO[x] + laneBase + 64u * h;
         float mUsed = -INFINITY, l = 0.f;
         bool ok = true;
         for (int j = 0; j < me.nT && ok; ++j) {
             const int st = j % kStages;
             const int k0 = (tileLo + j) * kKeys;
+            const int kh = k0 + 64 * h;                                     // first key of this thread's columns
             const bool edge = k0 < ws || k0 + kKeys > seqLen || (p.causal && k0 + kKeys - 1 > me.firstPos);
             // S of tile j is complete; so is every earlier instruction, PV of tile j-1 included
+            TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), j, 0);
             ok = mbarWait(&s->sFull[x], j & 1, &s->dead, errFlag, 7);
             if (!ok) break;
             tcFenceAfter();
-            // pass 1: maximum of the raw scores of the row (the scale is positive)
-            float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t r[32];
-                tmemLd32(sBase + c * 32, r);
-                if (!edge) {
-#pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        m4[0] = fmaxf(m4[0], __uint_as_float(r[i]));
-                        m4[1] = fmaxf(m4[1], __uint_as_float(r[i + 1]));
-                        m4[2] = fmaxf(m4[2], __uint_as_float(r[i + 2]));
-                        m4[3] = fmaxf(m4[3], __uint_as_float(r[i + 3]));
-                    }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int key = k0 + c * 32 + i;
-                        const bool vis = key >= ws && key < seqLen && (!p.causal || key <= rowPos);
-                        m4[i & 3] = fmaxf(m4[i & 3], vis ? __uint_as_float(r[i]) : -INFINITY);
-                    }
-                }
+            TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), j, 1);
+            // maximum of the raw scores of this half row (the scale is positive)
+            const MaskInfo mk{ws, seqLen, rowPos, p.causal};
+            float tmax;
+            {
+                uint32_t r0[32], r1[32];
+                tmemLd32NoWait(sBase, r0);
+                tmemLd32NoWait(sBase + 32, r1);
+                tmemLdWait();
+                TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), j, 4);
+                tmax = (edge ? halfRowMax<true>(r0, r1, mk, kh) : halfRowMax<false>(r0, r1, mk, kh)) * scaleLog2;
             }
-            const float tmax = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * scaleLog2;
+            s->rowMax[x][j & 1][h][t] = tmax;
+            mbarArrive(&s->maxReady[x][j & 1]);
+            TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), j, 5);
+            ok = mbarWait(&s->maxReady[x][j & 1], (j >> 1) & 1, &s->dead, errFlag, 11);
+            if (!ok) break;
+            tmax = fmaxf(tmax, s->rowMax[x][j & 1][h ^ 1][t]);
+            TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), j, 2);
             bool raise = false;
             float corr = 1.f;
             if (j == 0) mUsed = tmax;
@@ -434,50 +563,33 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             }
             if (j >= 1 && __any_sync(0xFFFFFFFFu, raise)) {
 #pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t r[32];
-                    tmemLd32(oBase + c * 32, r);
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t o[32];
+                    tmemLd32(oBase + c * 32, o);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
-                    tmemSt32(oBase + c * 32, r);
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+                    tmemSt32(oBase + c * 32, o);
                 }
                 l *= corr;
             }
-            // pass 2: the weights replace the scores in tensor memory, 32 keys at a time:
-            // 16 columns of packed pairs (plus 16 columns of their low-order parts for bfloat16)
+            // the weights replace the scores in tensor memory, 32 keys at a time: 16 columns of
+            // packed pairs (plus 16 columns of their low-order parts for bfloat16)
             const float negM = mUsed == -INFINITY ? 0.f : -mUsed;
-            float s4[4] = {0.f, 0.f, 0.f, 0.f};
+            float sum = 0.f;
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {
                 uint32_t r[32];
                 tmemLd32(sBase + c * 32, r);
+                TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), j, 6 + c);
                 uint32_t w[32];
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float x0 = fmaf(__uint_as_float(r[i]), scaleLog2, negM);
-                    float x1 = fmaf(__uint_as_float(r[i + 1]), scaleLog2, negM);
-                    if (edge) {
-                        const int key = k0 + c * 32 + i;
-                        if (!(key >= ws && key < seqLen && (!p.causal || key <= rowPos))) x0 = -INFINITY;
-                        if (!(key + 1 >= ws && key + 1 < seqLen && (!p.causal || key + 1 <= rowPos))) x1 = -INFINITY;
-                    }
-                    const float p0 = ex2Approx(x0), p1 = ex2Approx(x1);
-                    s4[(i >> 1) & 3] += p0 + p1;
-                    w[i / 2] = pack16<BF16>(p0, p1);
-                    if (BF16) {
-                        // bfloat16 keeps 8 significant bits of a weight; the remainder goes
-                        // into a second operand so that P_hi + P_lo carries 16 bits
-                        const float h0 = __uint_as_float(w[i / 2] << 16);
-                        const float h1 = __uint_as_float(w[i / 2] & 0xFFFF0000u);
-                        w[16 + i / 2] = pack16<true>(p0 - h0, p1 - h1);
-                    } else {
-                        w[16 + i / 2] = 0u;
-                    }
-                }
+                sum += edge ? weights32<BF16, true>(r, w, scaleLog2, negM, mk, kh + c * 32)
+                            : weights32<BF16, false>(r, w, scaleLog2, negM, mk, kh + c * 32);
                 tmemSt32(sBase + c * 32, w);
+                TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), j, 8 + c);
             }
             tmemStWait();
-            l += (s4[0] + s4[1]) + (s4[2] + s4[3]);
+            TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), j, 10);
+            l += sum;
             // The lowest-numbered query tile that uses this key tile clears the rows of V
             // past the end of the sequence (they may hold anything); the MMA thread
             // takes the query tiles in that order.
@@ -486,35 +598,40 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 if (!ok) break;
                 if (k0 + t >= seqLen) {
 #pragma unroll
-                    for (int hh = 0; hh < 2; ++hh)
-#pragma unroll
-                        for (int c16 = 0; c16 < 8; ++c16)
-                            *reinterpret_cast<uint4*>(s->v[st] + hh * kHalfBytes + t * 128 + c16 * 16) = make_uint4(0u, 0u, 0u, 0u);
+                    for (int c16 = 0; c16 < 8; ++c16)
+                        *reinterpret_cast<uint4*>(s->v[st] + h * kHalfBytes + t * 128 + c16 * 16) = make_uint4(0u, 0u, 0u, 0u);
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             }
             tcFenceBefore();
             mbarArrive(&s->pFull[x]);
+            TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), j, 3);
         }
         // epilogue: O / l to global memory
+        if (ok) {
+            s->rowMax[x][me.nT & 1][h][t] = l;       // the buffer the last tile did not use
+            mbarArrive(&s->sumReady[x]);
+            ok = mbarWait(&s->sumReady[x], 0, &s->dead, errFlag, 12);
+        }
         if (ok && me.nT > 0) ok = mbarWait(&s->pvDone[x], (me.nT - 1) & 1, &s->dead, errFlag, 10);
         if (ok && me.rowsValid > 0) {
             tcFenceAfter();
-            const float inv = (me.nT > 0 && l > 0.f) ? 1.f / l : 0.f;
+            const float lt = l + s->rowMax[x][me.nT & 1][h ^ 1][t];
+            const float inv = (me.nT > 0 && lt > 0.f) ? 1.f / lt : 0.f;
             unsigned char* out = static_cast<unsigned char*>(p.out) +
-                                 ((static_cast<int64_t>(me.rowBase) + t) * p.heads + head) * kHd * 2;
+                                 ((static_cast<int64_t>(me.rowBase) + t) * p.heads + head) * kHd * 2 + h * 128;
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t r[32];
-                if (me.nT > 0) tmemLd32(oBase + c * 32, r);
+            for (int c = 0; c < 2; ++c) {
+                uint32_t o[32];
+                if (me.nT > 0) tmemLd32(oBase + c * 32, o);
                 if (t < me.rowsValid) {
 #pragma unroll
                     for (int q4 = 0; q4 < 4; ++q4) {
                         uint32_t wv[4];
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            const float a = me.nT > 0 ? __uint_as_float(r[8 * q4 + 2 * e]) * inv : 0.f;
-                            const float bb = me.nT > 0 ? __uint_as_float(r[8 * q4 + 2 * e + 1]) * inv : 0.f;
+                            const float a = me.nT > 0 ? __uint_as_float(o[8 * q4 + 2 * e]) * inv : 0.f;
+                            const float bb = me.nT > 0 ? __uint_as_float(o[8 * q4 + 2 * e + 1]) * inv : 0.f;
                             wv[e] = pack16<BF16>(a, bb);
                         }
                         *reinterpret_cast<uint4*>(out + c * 64 + q4 * 16) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
@@ -526,6 +643,10 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
 
     tcFenceBefore();
     __syncthreads();
+#ifdef PAM_PREFILL_TRACE
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0)
+        for (int i = threadIdx.x; i < kTraceRoles * kTraceTiles * kTraceEvents; i += kThreads) gTrace[i] = s->trace[i];
+#endif
     if (warp == kMmaWarp) {
         tcFenceAfter();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
@@ -604,3 +725,11 @@ cudaError_t launchPrefillTensor(const PrefillParams& p, int totalRows, int* errF
 }
 
 }  // namespace pam
+
+#ifdef PAM_PREFILL_TRACE
+extern "C" int pamc_debug_trace_read(long long* out) {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, pam::gTrace, sizeof(long long) * pam::kTraceRoles * pam::kTraceTiles * pam::kTraceEvents);
+    return pam::kTraceRoles * pam::kTraceTiles * pam::kTraceEvents;
+}
+#endif
