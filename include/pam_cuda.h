@@ -160,6 +160,13 @@ int32_t pamc_set_default_chunk(void *ctx, int32_t tokens);     /* defaultChunkSi
  * The reference picks its prefill variant the same way, by type and head_dim
  * (PagedAttentionEngine.swift:420-434). */
 int32_t pamc_set_prefill_tensor_path(void *ctx, int32_t on);
+/* bfloat16 tensor-core prefill: how the softmax weights are carried into the
+ * second product.  0: one bfloat16 operand (8 significant bits, what bfloat16
+ * attention kernels usually do); 1 (default): two operands, 16 bits, on query
+ * tiles whose rows see fewer than 256 keys, where 8 bits can miss the 2e-3
+ * bound; 2: two operands everywhere (about 1.5x the tensor work).  No
+ * counterpart in the reference, which has no bfloat16. */
+int32_t pamc_set_prefill_exact_weights(void *ctx, int32_t mode);
 /* Host-side fault injection for tests of the retry loop, circuit breaker and
  * zero-fill path (PagedAttentionEngine.swift:375-414): the next n kernel
  * launches of this context report failure without touching the GPU. */

@@ -111,6 +111,7 @@ SIGNATURES = {
     "pamc_set_default_window": (c_int32, [c_void_p, c_int32]),
     "pamc_set_default_chunk": (c_int32, [c_void_p, c_int32]),
     "pamc_set_prefill_tensor_path": (c_int32, [c_void_p, c_int32]),
+    "pamc_set_prefill_exact_weights": (c_int32, [c_void_p, c_int32]),
     "pamc_inject_launch_failures": (c_int32, [c_void_p, c_int32]),
     "pamc_kernel_launches": (c_int64, [c_void_p]),
     "pamc_last_stats": (c_int32, [c_void_p, C.POINTER(PamStats)]),

@@ -88,6 +88,7 @@ struct PrefillParams {
     int totalRows;                // rows in q/out (all sequences of the launch)
     int* errFlag;                 // device word the tensor-core kernel sets when a bounded wait runs out
     int forceGeneral;             // 1: never take the tensor-core path
+    int exactWeights;             // bfloat16 tensor path: 0 = 8-bit weights, 1 = 16-bit on short rows, 2 = 16-bit always
 };
 // Tensor-core path (prefill_tc_kernel.cu): bf16/f16, head_dim 128, block size multiple of 16.
 bool prefillTensorPathApplies(const PrefillParams& p);

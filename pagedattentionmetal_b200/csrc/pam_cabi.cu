@@ -91,6 +91,7 @@ struct Context {
     int* hostErr = nullptr;   // pinned copy, read after the stream has been synchronised
     bool errPending = false;
     bool forceGeneralPrefill = false;
+    int exactWeights = 1;
 
     int32_t fail(int code, const std::string& msg) {            // CABI.swift:18-30
         lastError = msg;
@@ -607,6 +608,7 @@ int32_t prefillImpl(Context* c, const PamLayerSpec& l, const PamBuffer& q, const
         p.totalRows = static_cast<int>(totalRows);
         p.errFlag = c->devErr;
         p.forceGeneral = c->forceGeneralPrefill ? 1 : 0;
+        p.exactWeights = c->exactWeights;
         int launches = 0;
         cudaError_t e = pam::launchPrefill(p, c->smCount, c->stream, &launches, &tensorPath);
         c->launches += launches;
@@ -1000,6 +1002,7 @@ int32_t pamc_set_max_retries(void* ctx, int32_t n) { if (!ctx || n < 0) return -
 int32_t pamc_set_graceful_degradation(void* ctx, int32_t on) { if (!ctx) return -1; asCtx(ctx)->graceful = on != 0; return 0; }
 int32_t pamc_set_split_threshold(void* ctx, int32_t t) { if (!ctx) return -1; asCtx(ctx)->splitThreshold = t; return 0; }
 int32_t pamc_set_prefill_tensor_path(void* ctx, int32_t on) { if (!ctx) return -1; asCtx(ctx)->forceGeneralPrefill = on == 0; return 0; }
+int32_t pamc_set_prefill_exact_weights(void* ctx, int32_t mode) { if (!ctx || mode < 0 || mode > 2) return -1; asCtx(ctx)->exactWeights = mode; return 0; }
 int32_t pamc_set_default_window(void* ctx, int32_t t) { if (!ctx || t < 0) return -1; asCtx(ctx)->defaultWindow = t; return 0; }
 int32_t pamc_set_default_chunk(void* ctx, int32_t t) { if (!ctx || t < 0) return -1; asCtx(ctx)->defaultChunk = t; return 0; }
 int32_t pamc_inject_launch_failures(void* ctx, int32_t n) { if (!ctx || n < 0) return -1; asCtx(ctx)->injectFailures = n; return 0; }

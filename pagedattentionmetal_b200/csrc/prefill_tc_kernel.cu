@@ -62,6 +62,7 @@ constexpr int kTileBytes = kRows * kHd * 2;            // 32 KB: one [128][128] 
 constexpr int kHalfBytes = kTileBytes / 2;             // one 64-column block
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;
+constexpr int kShortRowKeys = 256;
 constexpr long long kWaitCycles = 400000000LL;         // ~0.2 s
 
 #ifdef PAM_PREFILL_TRACE
@@ -247,6 +248,14 @@ __device__ __forceinline__ void tmemSt32(uint32_t taddr, const uint32_t (&r)[32]
           "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
+__device__ __forceinline__ void tmemSt16(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
 __device__ __forceinline__ void tmemStWait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 template <bool BF16>
@@ -289,9 +298,9 @@ __device__ __forceinline__ float halfRowMax(const uint32_t (&r0)[32], const uint
     return fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
 }
 
-// 32 scores -> 16 packed weight pairs (w[0..15]) and, for bfloat16, the 16 pairs
-// of their low-order parts (w[16..31]); returns the sum of the weights.
-template <bool BF16, bool EDGE>
+// 32 scores -> 16 packed weight pairs (w[0..15]) and, with LO (bfloat16 only),
+// the 16 pairs of their low-order parts (w[16..31]); returns the sum of the weights.
+template <bool BF16, bool LO, bool EDGE>
 __device__ __forceinline__ float weights32(const uint32_t (&r)[32], uint32_t (&w)[32], float scaleLog2, float negM,
                                            const MaskInfo& mk, int firstKey) {
     float s4[4] = {0.f, 0.f, 0.f, 0.f};
@@ -306,14 +315,12 @@ __device__ __forceinline__ float weights32(const uint32_t (&r)[32], uint32_t (&w
         const float p0 = ex2Approx(x0), p1 = ex2Approx(x1);
         s4[(i >> 1) & 3] += p0 + p1;
         w[i / 2] = pack16<BF16>(p0, p1);
-        if (BF16) {
+        if (LO) {
             // bfloat16 keeps 8 significant bits of a weight; the remainder goes into a
             // second operand so that P_hi + P_lo carries 16 bits
             const float h0 = __uint_as_float(w[i / 2] << 16);
             const float h1 = __uint_as_float(w[i / 2] & 0xFFFF0000u);
             w[16 + i / 2] = pack16<true>(p0 - h0, p1 - h1);
-        } else {
-            w[16 + i / 2] = 0u;
         }
     }
     return (s4[0] + s4[1]) + (s4[2] + s4[3]);
@@ -331,6 +338,7 @@ struct SlotInfo {
     int rowsValid;   // rows of the tile that exist (<= 0: the tile is absent)
     int firstPos;    // sequence position of row 0
     int nT;          // key tiles this tile's rows can see (from tileLo on)
+    int useLo;       // bfloat16: weights as P_hi + P_lo (see below)
 };
 
 template <bool BF16>
@@ -366,6 +374,13 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         const int lastPos = slot[x].firstPos + slot[x].rowsValid - 1;
         const int keyEnd = p.causal ? min(seqLen, lastPos + 1) : seqLen;                   // exclusive
         slot[x].nT = (slot[x].rowsValid > 0 && keyEnd > ws) ? (keyEnd - 1) / kKeys - tileLo + 1 : 0;
+        // Fewest keys any row of the tile sees.  A bfloat16 weight keeps 8 significant bits;
+        // on a row with few keys (large weights) that alone can cost more than 2e-3 on
+        // unit-variance values, so such tiles carry the weights as two bfloat16 operands
+        // (16 bits).  Rows with hundreds of keys have weights small enough for 8 bits,
+        // as in every bfloat16 attention kernel.  exactWeights: 0 never, 1 short rows, 2 always.
+        const int fewest = p.causal ? slot[x].firstPos + 1 - ws : seqLen - ws;
+        slot[x].useLo = BF16 && (p.exactWeights == 2 || (p.exactWeights == 1 && fewest < kShortRowKeys));
     }
     const int nTmax = max(slot[0].nT, slot[1].nT);
 
@@ -486,7 +501,7 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                             const uint32_t pCol = tmemS[x] + 32u * (ks >> 1) + 8u * (ks & 1);
                             ummaTs(tmemO[x], pCol, desc64(vLo[st] + ks * 128, hiK), idescO, (j > 0 || ks > 0) ? 1u : 0u);
                         }
-                        if (BF16) {
+                        if (BF16 && slot[x].useLo) {
 #pragma unroll
                             for (int ks = 0; ks < kKeys / 16; ++ks) {
                                 const uint32_t pCol = tmemS[x] + 32u * (ks >> 1) + 8u * (ks & 1) + 16u;
@@ -582,9 +597,15 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 tmemLd32(sBase + c * 32, r);
                 TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), j, 6 + c);
                 uint32_t w[32];
-                sum += edge ? weights32<BF16, true>(r, w, scaleLog2, negM, mk, kh + c * 32)
-                            : weights32<BF16, false>(r, w, scaleLog2, negM, mk, kh + c * 32);
-                tmemSt32(sBase + c * 32, w);
+                if (BF16 && me.useLo) {
+                    sum += edge ? weights32<BF16, true, true>(r, w, scaleLog2, negM, mk, kh + c * 32)
+                                : weights32<BF16, true, false>(r, w, scaleLog2, negM, mk, kh + c * 32);
+                    tmemSt32(sBase + c * 32, w);
+                } else {
+                    sum += edge ? weights32<BF16, false, true>(r, w, scaleLog2, negM, mk, kh + c * 32)
+                                : weights32<BF16, false, false>(r, w, scaleLog2, negM, mk, kh + c * 32);
+                    tmemSt16(sBase + c * 32, w);
+                }
                 TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), j, 8 + c);
             }
             tmemStWait();

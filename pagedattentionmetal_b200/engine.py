@@ -188,6 +188,10 @@ class PagedAttentionEngine:
     def setPrefillTensorPath(self, on: bool) -> None:
         lib.pamc_set_prefill_tensor_path(self._ctx, 1 if on else 0)
 
+    def setPrefillExactWeights(self, mode: int) -> None:
+        """0 / 1 / 2, see pamc_set_prefill_exact_weights."""
+        lib.pamc_set_prefill_exact_weights(self._ctx, mode)
+
     def injectLaunchFailures(self, n: int) -> None:
         lib.pamc_inject_launch_failures(self._ctx, n)
 
