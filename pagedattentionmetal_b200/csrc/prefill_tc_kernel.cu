@@ -384,6 +384,7 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     }
     const int nTmax = max(slot[0].nT, slot[1].nT);
 
+    TRACE(0, 31, 0);                                   // CTA start (instrumented build)
     if (threadIdx.x == 0) {
         mbarInit(&s->qFull, 1);
         for (int i = 0; i < kStages; ++i) { mbarInit(&s->kFull[i], 1); mbarInit(&s->vFull[i], 1); mbarInit(&s->kvEmpty[i], 1); }
@@ -406,6 +407,7 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     __syncthreads();
     tcFenceAfter();
     const uint32_t tmem = s->tmemBase;
+    TRACE(0, 31, 1);                                   // barriers and tensor memory ready
     // per query tile: S (aliased by P once the scores are consumed) and O
     const uint32_t tmemS[2] = {tmem, tmem + 256u};
     const uint32_t tmemO[2] = {tmem + 128u, tmem + 384u};
@@ -635,6 +637,7 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             ok = mbarWait(&s->sumReady[x], 0, &s->dead, errFlag, 12);
         }
         if (ok && me.nT > 0) ok = mbarWait(&s->pvDone[x], (me.nT - 1) & 1, &s->dead, errFlag, 10);
+        TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), 31, 2);   // last PV done
         if (ok && me.rowsValid > 0) {
             tcFenceAfter();
             const float lt = l + s->rowMax[x][me.nT & 1][h ^ 1][t];
@@ -662,6 +665,7 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         }
     }
 
+    TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), 31, 3);       // output stored
     tcFenceBefore();
     __syncthreads();
 #ifdef PAM_PREFILL_TRACE
