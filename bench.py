@@ -146,12 +146,13 @@ def time_cpu_path(lens, steps, warmup, n_seqs=CPU_SAMPLE_SEQS):
     from oracle import c_oracle as co
 
     q, k_pool, v_pool, tables, l = cpu_sample_inputs(lens, n_seqs)
-    cores = co.max_threads()
+    # all host cores this process may run on (a launcher may have set OMP_NUM_THREADS=1)
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
     for _ in range(max(warmup, 1)):
-        co.decode(q, k_pool, v_pool, tables, l, KV_HEADS, BLOCK, 1)
+        co.decode(q, k_pool, v_pool, tables, l, KV_HEADS, BLOCK, 1, nthreads=cores)
     t0 = time.perf_counter()
     for _ in range(steps):
-        co.decode(q, k_pool, v_pool, tables, l, KV_HEADS, BLOCK, 1)
+        co.decode(q, k_pool, v_pool, tables, l, KV_HEADS, BLOCK, 1, nthreads=cores)
     dt = (time.perf_counter() - t0) / steps
     return {"value": n_seqs / dt, "unit": "tokens/s", "cores": cores, "kind": "port",
             "sample": f"first {n_seqs} of {BATCH} sequences of the workload ({int(l.sum())} context tokens), "
