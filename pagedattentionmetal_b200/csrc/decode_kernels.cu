@@ -383,6 +383,308 @@ decodeSplitKernel(const T* __restrict__ q, const T* __restrict__ kPool, const T*
     }
 }
 
+// ------------------------------------------------------------ FP8 split kernel
+
+// Two e4m3 codes (low 16 bits of `v`) to two float16 values; exact, every e4m3
+// value is a float16 value.
+__device__ __forceinline__ uint32_t e4m3x2ToHalf2(uint32_t v) {
+    uint32_t r;
+    asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %1;\n\tcvt.rn.f16x2.e4m3x2 %0, lo;\n\t}" : "=r"(r) : "r"(v));
+    return r;
+}
+__device__ __forceinline__ uint32_t e4m3x2HiToHalf2(uint32_t v) {
+    uint32_t r;
+    asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %1;\n\tcvt.rn.f16x2.e4m3x2 %0, hi;\n\t}" : "=r"(r) : "r"(v));
+    return r;
+}
+
+// The fast path for FP8 e4m3 KV (head_dim 128, block size a multiple of 16,
+// float16 queries and outputs).  Same structure as decodeSplitKernel; a
+// 16-token tile is 2 KB of K codes and 2 KB of V codes.  Codes become float16
+// in registers (exactly) and feed mma.sync.m16n8k16.f16; the group scales
+// [block][kv_head] are applied outside the products: K's on the scores, V's on
+// the weights (relative to the scale of the warp's first tile, so that the
+// weights stay in float16's normal range).  The fragments are loaded with
+// 16-byte shared-memory reads: the K-dimension of QK^T and the N-dimension of
+// PV are permuted so that every thread reads contiguous codes, which no result
+// depends on.
+template <int NW, int NS, bool UPPER>
+__global__ void __launch_bounds__(NW * 32)
+decodeSplitFp8Kernel(const __half* __restrict__ q, const uint8_t* __restrict__ kPool, const uint8_t* __restrict__ vPool,
+                     const __half* __restrict__ kScale, const __half* __restrict__ vScale,
+                     const int32_t* __restrict__ tables, const uint32_t* __restrict__ lens,
+                     __half* __restrict__ out, float* __restrict__ workspace, int heads, int kvHeads,
+                     int blockSize, int maxNumBlocks, int window, int chunkTiles, int maxSplits,
+                     float scaleLog2, int poolBlocks) {
+    constexpr int HD = 128;
+    constexpr int ROWB = HD;                     // bytes per token row
+    constexpr int TILEB = kTileTokens * ROWB;    // 2 KB per K (or V) tile
+    constexpr int CHUNKS = TILEB / 16;           // 128 16-byte chunks
+    constexpr int STAGEB = 2 * TILEB + 16;       // + the two group scales of the tile
+    constexpr int KSTEPS = HD / 16;
+    constexpr int NT = HD / 8;
+
+    extern __shared__ __align__(128) unsigned char smem[];
+
+    const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int G = heads / kvHeads;
+    const int r = lane >> 2, j = lane & 3;
+
+    const uint32_t len = lens[b];
+    const SplitInfo si = splitInfo(len, window, maxNumBlocks * blockSize);
+    const int numSplits = (si.numTiles + chunkTiles - 1) / chunkTiles;
+    if (si.numTiles <= 0) {
+        if (split == 0)
+            for (int i = threadIdx.x; i < G * HD; i += NW * 32)
+                out[(static_cast<int64_t>(b) * heads + kvh * G) * HD + i] = __float2half_rn(0.f);
+        return;
+    }
+    if (split >= numSplits) return;
+
+    const int tileBegin = si.firstTile + split * chunkTiles;
+    const int tileEnd = min(tileBegin + chunkTiles, si.firstTile + si.numTiles);
+    const int myTiles = (tileEnd - tileBegin - warp + NW - 1) / NW;
+    const int tilesPerPage = blockSize / kTileTokens;
+    const int32_t* table = tables + static_cast<int64_t>(b) * maxNumBlocks;
+
+    unsigned char* ring = smem + static_cast<size_t>(warp) * NS * STAGEB;
+    const uint32_t ringAddr = smemAddr(ring);
+
+    auto issue = [&](int it) {
+        const int tile = tileBegin + warp + it * NW;
+        const int page = tile / tilesPerPage, within = tile - page * tilesPerPage;
+        const int64_t blk = min(max(table[page], 0), poolBlocks - 1);
+        const int64_t off = ((blk * kvHeads + kvh) * blockSize + within * kTileTokens) * static_cast<int64_t>(HD);
+        const unsigned char* gk = kPool + off;
+        const unsigned char* gv = vPool + off;
+        const uint32_t sk = ringAddr + (it % NS) * STAGEB, sv = sk + TILEB;
+#pragma unroll
+        for (int i = 0; i < CHUNKS / 32; ++i) {
+            const int idx = lane + 32 * i;
+            const int row = idx >> 3, c = idx & 7;
+            const uint32_t dst = row * ROWB + ((c ^ (row & 7)) << 4);
+            cpAsync16(sk + dst, gk + idx * 16);
+            cpAsync16(sv + dst, gv + idx * 16);
+        }
+        if (lane == 0) {
+            __half* sc = reinterpret_cast<__half*>(ring + (it % NS) * STAGEB + 2 * TILEB);
+            sc[0] = kScale[blk * kvHeads + kvh];
+            sc[1] = vScale[blk * kvHeads + kvh];
+        }
+    };
+
+    // Query rows as A fragments with the permuted K order: step ks of thread
+    // (r, j) covers dims 32j + 4ks + {0,1} (first half) and + {2,3} (second half).
+    uint32_t qa[KSTEPS][4];
+    {
+        const __half* qb = q + (static_cast<int64_t>(b) * heads + kvh * G) * HD;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+            const int d0 = 32 * j + 4 * ks;
+            uint2 lo = make_uint2(0u, 0u), hi = make_uint2(0u, 0u);
+            if (r < G) lo = *reinterpret_cast<const uint2*>(qb + r * HD + d0);
+            if (UPPER && r + 8 < G) hi = *reinterpret_cast<const uint2*>(qb + (r + 8) * HD + d0);
+            qa[ks][0] = lo.x; qa[ks][2] = lo.y;
+            qa[ks][1] = hi.x; qa[ks][3] = hi.y;
+        }
+    }
+
+    float o[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    float vRef = 0.f, invVRef = 0.f;             // V scale of the warp's first tile
+
+#pragma unroll
+    for (int s = 0; s < NS; ++s) {
+        if (s < myTiles) issue(s);
+        cpAsyncCommit();
+    }
+
+    for (int it = 0; it < myTiles; ++it) {
+        cpAsyncWait<NS - 1>();
+        __syncwarp();
+        const int tile = tileBegin + warp + it * NW;
+        const int tokBase = tile * kTileTokens;
+        unsigned char* stage = ring + (it % NS) * STAGEB;
+        const uint32_t sk = ringAddr + (it % NS) * STAGEB, sv = sk + TILEB;
+        const __half* sc = reinterpret_cast<const __half*>(stage + 2 * TILEB);
+        const float ks_ = __half2float(sc[0]), vs_ = __half2float(sc[1]);
+        if (it == 0) { vRef = vs_ > 0.f ? vs_ : 1.f; invVRef = 1.f / vRef; }
+        const bool partial = tokBase < si.windowStart || tokBase + kTileTokens > static_cast<int>(len);
+        if (partial) {
+            // rows outside [window_start, L): zero codes, so that a zero weight times that row is zero
+            unsigned char* vt = stage + TILEB;
+            for (int idx = lane; idx < CHUNKS; idx += 32) {
+                const int tok = tokBase + (idx >> 3);
+                if (tok < si.windowStart || tok >= static_cast<int>(len))
+                    *reinterpret_cast<uint4*>(vt + idx * 16) = make_uint4(0u, 0u, 0u, 0u);
+            }
+            __syncwarp();
+        }
+
+        // S = Q K^T on the codes; the group scale and 1/sqrt(d) follow.
+        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            const int row = 8 * nt + r;
+            const uint4 w0 = *reinterpret_cast<const uint4*>(stage + row * ROWB + (((2 * j) ^ (row & 7)) << 4));
+            const uint4 w1 = *reinterpret_cast<const uint4*>(stage + row * ROWB + (((2 * j + 1) ^ (row & 7)) << 4));
+            const uint32_t w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ++ks)
+                mma16816<__half>(s[nt], qa[ks], e4m3x2ToHalf2(w[ks]), e4m3x2HiToHalf2(w[ks]));
+        }
+        (void)sk;
+
+        const float sScale = ks_ * scaleLog2;
+        float tmax0 = -INFINITY, tmax1 = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int tok = tokBase + 8 * nt + 2 * j + e;
+                const bool ok = !partial || (tok >= si.windowStart && tok < static_cast<int>(len));
+                s[nt][e] = ok ? s[nt][e] * sScale : -INFINITY;
+                tmax0 = fmaxf(tmax0, s[nt][e]);
+                if (UPPER) {
+                    s[nt][e + 2] = ok ? s[nt][e + 2] * sScale : -INFINITY;
+                    tmax1 = fmaxf(tmax1, s[nt][e + 2]);
+                }
+            }
+        }
+        tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xFFFFFFFFu, tmax0, 1));
+        tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xFFFFFFFFu, tmax0, 2));
+        const float mn0 = fmaxf(m0, tmax0);
+        const float c0 = exp2f(m0 - mn0);
+        m0 = mn0;
+        float c1 = 1.f;
+        if (UPPER) {
+            tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xFFFFFFFFu, tmax1, 1));
+            tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xFFFFFFFFu, tmax1, 2));
+            const float mn1 = fmaxf(m1, tmax1);
+            c1 = exp2f(m1 - mn1);
+            m1 = mn1;
+        }
+        // weights; those that enter the product carry V's group scale relative to vRef
+        const float vw = vs_ * invVRef;
+        uint32_t pa[4];
+        {
+            const float p00 = exp2f(s[0][0] - m0), p01 = exp2f(s[0][1] - m0);
+            const float p10 = exp2f(s[1][0] - m0), p11 = exp2f(s[1][1] - m0);
+            l0 = l0 * c0 + (p00 + p01 + p10 + p11);
+            pa[0] = pack2<__half>(p00 * vw, p01 * vw);
+            pa[2] = pack2<__half>(p10 * vw, p11 * vw);
+            if (UPPER) {
+                const float q00 = exp2f(s[0][2] - m1), q01 = exp2f(s[0][3] - m1);
+                const float q10 = exp2f(s[1][2] - m1), q11 = exp2f(s[1][3] - m1);
+                l1 = l1 * c1 + (q00 + q01 + q10 + q11);
+                pa[1] = pack2<__half>(q00 * vw, q01 * vw);
+                pa[3] = pack2<__half>(q10 * vw, q11 * vw);
+            } else {
+                pa[1] = 0u;
+                pa[3] = 0u;
+            }
+        }
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+            o[n][0] *= c0;
+            o[n][1] *= c0;
+            if (UPPER) {
+                o[n][2] *= c1;
+                o[n][3] *= c1;
+            }
+        }
+
+        // O += P V.  Thread (r, j) reads chunk r (dims 16r .. 16r+15) of the token rows
+        // 2j, 2j+1, 2j+8, 2j+9; n-tile c takes byte c of each: output column n of
+        // n-tile c is dim 16n + c.
+        {
+            const unsigned char* vt = stage + TILEB;
+            uint4 x[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int row = 2 * j + (i & 1) + 8 * (i >> 1);
+                x[i] = *reinterpret_cast<const uint4*>(vt + row * ROWB + ((r ^ (row & 7)) << 4));
+            }
+            const uint32_t* x0 = reinterpret_cast<const uint32_t*>(&x[0]);
+            const uint32_t* x1 = reinterpret_cast<const uint32_t*>(&x[1]);
+            const uint32_t* x2 = reinterpret_cast<const uint32_t*>(&x[2]);
+            const uint32_t* x3 = reinterpret_cast<const uint32_t*>(&x[3]);
+#pragma unroll
+            for (int wi = 0; wi < 4; ++wi) {
+                const uint32_t a01 = __byte_perm(x0[wi], x1[wi], 0x5140);   // bytes 0,1 of both tokens, interleaved
+                const uint32_t a23 = __byte_perm(x0[wi], x1[wi], 0x7362);
+                const uint32_t b01 = __byte_perm(x2[wi], x3[wi], 0x5140);
+                const uint32_t b23 = __byte_perm(x2[wi], x3[wi], 0x7362);
+                mma16816<__half>(o[4 * wi + 0], pa, e4m3x2ToHalf2(a01), e4m3x2ToHalf2(b01));
+                mma16816<__half>(o[4 * wi + 1], pa, e4m3x2HiToHalf2(a01), e4m3x2HiToHalf2(b01));
+                mma16816<__half>(o[4 * wi + 2], pa, e4m3x2ToHalf2(a23), e4m3x2ToHalf2(b23));
+                mma16816<__half>(o[4 * wi + 3], pa, e4m3x2HiToHalf2(a23), e4m3x2HiToHalf2(b23));
+            }
+        }
+        (void)sv;
+
+        __syncwarp();
+        if (it + NS < myTiles) issue(it + NS);
+        cpAsyncCommit();
+    }
+    cpAsyncWait<0>();
+
+    l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 1);
+    l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 2);
+    if (UPPER) {
+        l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, 1);
+        l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, 2);
+    }
+
+    __syncthreads();
+    float* red = reinterpret_cast<float*>(smem);            // [NW][G][HD + 2]
+    constexpr int RS = HD + 2;
+    {
+        float* mine = red + static_cast<size_t>(warp) * G * RS;
+        if (r < G) {
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                mine[r * RS + 16 * (2 * j) + n] = o[n][0] * vRef;
+                mine[r * RS + 16 * (2 * j + 1) + n] = o[n][1] * vRef;
+            }
+            if (j == 0) { mine[r * RS + HD] = m0; mine[r * RS + HD + 1] = l0; }
+        }
+        if (UPPER && r + 8 < G) {
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                mine[(r + 8) * RS + 16 * (2 * j) + n] = o[n][2] * vRef;
+                mine[(r + 8) * RS + 16 * (2 * j + 1) + n] = o[n][3] * vRef;
+            }
+            if (j == 0) { mine[(r + 8) * RS + HD] = m1; mine[(r + 8) * RS + HD + 1] = l1; }
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * HD; idx += NW * 32) {
+        const int g = idx / HD, d = idx - g * HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) M = fmaxf(M, red[(w * G + g) * RS + HD]);
+        float acc = 0.f, lsum = 0.f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) {
+            const float wgt = exp2f(red[(w * G + g) * RS + HD] - M);
+            acc += wgt * red[(w * G + g) * RS + d];
+            lsum += wgt * red[(w * G + g) * RS + HD + 1];
+        }
+        const int head = kvh * G + g;
+        if (numSplits == 1) {
+            out[(static_cast<int64_t>(b) * heads + head) * HD + d] = __float2half_rn(acc / lsum);
+        } else {
+            float* part = workspace + ((static_cast<int64_t>(b) * heads + head) * maxSplits + split) * RS;
+            part[d] = acc;
+            if (d == 0) { part[HD] = M; part[HD + 1] = lsum; }
+        }
+    }
+}
+
 // Combine the splits of one (sequence, head): out = sum_s 2^(m_s - M) O_s / sum_s 2^(m_s - M) l_s.
 template <typename T, int HD>
 __global__ void decodeMergeKernel(const float* __restrict__ workspace, const uint32_t* __restrict__ lens,
@@ -541,8 +843,10 @@ constexpr int kWarps = 4, kStages = 3;
 SplitPlan planSplits(const DecodeParams& p, int smCount) {
     SplitPlan plan{false, 0, 1};
     const int G = p.kvHeads > 0 ? p.heads / p.kvHeads : 0;
-    plan.fast = (p.dtype == kF16 || p.dtype == kBF16) && (p.headDim == 128 || p.headDim == 64) &&
-                p.blockSize % kTileTokens == 0 && G >= 1 && G <= 16;
+    plan.fast = ((p.dtype == kF16 || p.dtype == kBF16) && (p.headDim == 128 || p.headDim == 64) &&
+                 p.blockSize % kTileTokens == 0 && G >= 1 && G <= 16) ||
+                (p.dtype == kFP8 && p.headDim == 128 && p.blockSize % kTileTokens == 0 && G >= 1 && G <= 16 &&
+                 p.kScale && p.vScale);
     if (!plan.fast) return plan;
     int maxTokens = p.maxNumBlocks * p.blockSize;
     if (p.maxContext > 0 && p.maxContext < maxTokens) maxTokens = p.maxContext;
@@ -591,6 +895,38 @@ cudaError_t launchFast(const DecodeParams& p, const SplitPlan& plan, cudaStream_
     return e;
 }
 
+template <bool UPPER>
+cudaError_t launchFastFp8(const DecodeParams& p, const SplitPlan& plan, cudaStream_t stream, int* launches) {
+    constexpr int NW = kWarps, NS = 4, HD = 128;
+    const int G = p.heads / p.kvHeads;
+    size_t ring = static_cast<size_t>(NW) * NS * (2 * kTileTokens * HD + 16);
+    size_t red = static_cast<size_t>(NW) * G * (HD + 2) * sizeof(float);
+    size_t smem = ring > red ? ring : red;
+    auto kernel = decodeSplitFp8Kernel<NW, NS, UPPER>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+    dim3 grid(static_cast<unsigned>(plan.maxSplits), static_cast<unsigned>(p.kvHeads), static_cast<unsigned>(p.batch));
+    const float scaleLog2 = (1.0f / sqrtf(static_cast<float>(p.headDim))) * kLog2e;
+    kernel<<<grid, NW * 32, smem, stream>>>(static_cast<const __half*>(p.q), static_cast<const uint8_t*>(p.kPool),
+                                            static_cast<const uint8_t*>(p.vPool), static_cast<const __half*>(p.kScale),
+                                            static_cast<const __half*>(p.vScale), p.tables, p.lens,
+                                            static_cast<__half*>(p.out), p.workspace, p.heads, p.kvHeads, p.blockSize,
+                                            p.maxNumBlocks, p.window, plan.chunkTiles, plan.maxSplits, scaleLog2,
+                                            p.poolBlocks);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    if (launches) *launches += 1;
+    if (plan.maxSplits > 1) {
+        dim3 mgrid(static_cast<unsigned>(p.heads), static_cast<unsigned>(p.batch));
+        decodeMergeKernel<__half, HD><<<mgrid, HD, 0, stream>>>(p.workspace, p.lens, static_cast<__half*>(p.out), p.heads,
+                                                               p.blockSize, p.maxNumBlocks, p.window, plan.chunkTiles,
+                                                               plan.maxSplits);
+        e = cudaGetLastError();
+        if (e == cudaSuccess && launches) *launches += 1;
+    }
+    return e;
+}
+
 template <typename T>
 cudaError_t launchFastT(const DecodeParams& p, const SplitPlan& plan, cudaStream_t stream, int* launches) {
     const bool upper = p.heads / p.kvHeads > 8;
@@ -633,6 +969,9 @@ cudaError_t launchDecode(const DecodeParams& p, int smCount, cudaStream_t stream
         if (plan.maxSplits > 1 &&
             (!p.workspace || p.workspaceBytes < decodeWorkspaceBytes(p, smCount)))
             return cudaErrorInvalidValue;
+        if (p.dtype == kFP8)
+            return p.heads / p.kvHeads > 8 ? launchFastFp8<true>(p, plan, stream, launches)
+                                           : launchFastFp8<false>(p, plan, stream, launches);
         return p.dtype == kF16 ? launchFastT<__half>(p, plan, stream, launches)
                                : launchFastT<__nv_bfloat16>(p, plan, stream, launches);
     }

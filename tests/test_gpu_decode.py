@@ -92,6 +92,20 @@ def test_general_decode_matches_oracle(engine, dtype, heads, kv_heads, head_dim,
     assert_close(out, case.oracle(), dtype)
 
 
+@pytest.mark.parametrize("heads,kv_heads,block_size", [(8, 2, 16), (16, 2, 16), (32, 2, 32), (2, 2, 16), (64, 8, 16)])
+def test_fp8_fast_decode_matches_oracle(engine, heads, kv_heads, block_size):
+    """FP8 KV through the tensor-core split-K kernel (head_dim 128), against the
+    oracle's half-precision dequantisation chain: max-abs <= 1e-2."""
+    case = DecodeCase(20, 6, 1, 400, heads, kv_heads, 128, block_size, DT.float8)
+    out = case.run(engine)
+    assert_close(out, case.oracle(), DT.float8)
+    # long contexts, several splits, sliding window
+    case = DecodeCase(21, 2, 3000, 7000, heads, kv_heads, 128, block_size, DT.float8)
+    out = case.run(engine, window=2048)
+    assert_close(out, case.oracle(window=2048), DT.float8)
+    assert engine.lastStats.temporaryBytes > 0
+
+
 def test_edge_lengths(engine):
     """Length 0 (0/0 in the reference: zeros here), 1, exact tile and block
     multiples, and a length larger than the table can hold (clamped like
