@@ -276,9 +276,12 @@ __device__ __forceinline__ float ex2Approx(float x) {
 
 // Visibility of key `key` for the row at sequence position `rowPos`.
 struct MaskInfo {
-    int ws, seqLen, rowPos, causal;
+    int lo, hi;      // keys [lo, hi) are visible to the row
+    __device__ __forceinline__ MaskInfo(int ws, int seqLen, int rowPos, int causal)
+        : lo(ws), hi(causal ? min(seqLen, rowPos + 1) : seqLen) {}
+    // key = firstKey + i with i a compile-time constant in the callers' unrolled loops
     __device__ __forceinline__ bool visible(int key) const {
-        return key >= ws && key < seqLen && (!causal || key <= rowPos);
+        return static_cast<unsigned>(key - lo) < static_cast<unsigned>(max(hi - lo, 0));
     }
 };
 
@@ -384,6 +387,11 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     }
     const int nTmax = max(slot[0].nT, slot[1].nT);
 
+    if (threadIdx.x == kProducerWarp * 32) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&mapQ) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&mapK) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&mapV) : "memory");
+    }
     TRACE(0, 31, 0);                                   // CTA start (instrumented build)
     if (threadIdx.x == 0) {
         mbarInit(&s->qFull, 1);
@@ -553,7 +561,7 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             tcFenceAfter();
             TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), j, 1);
             // maximum of the raw scores of this half row (the scale is positive)
-            const MaskInfo mk{ws, seqLen, rowPos, p.causal};
+            const MaskInfo mk(ws, seqLen, rowPos, p.causal);
             float tmax;
             {
                 uint32_t r0[32], r1[32];
@@ -642,24 +650,37 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             tcFenceAfter();
             const float lt = l + s->rowMax[x][me.nT & 1][h ^ 1][t];
             const float inv = (me.nT > 0 && lt > 0.f) ? 1.f / lt : 0.f;
-            unsigned char* out = static_cast<unsigned char*>(p.out) +
-                                 ((static_cast<int64_t>(me.rowBase) + t) * p.heads + head) * kHd * 2 + h * 128;
+            // The Q tile of this query tile is no longer read: stage this warp's 32 rows x
+            // 128 bytes there (16-byte chunks XOR-swizzled by row), then write them out four
+            // rows per instruction, 128 contiguous bytes per row.
+            unsigned char* stage = s->q[x];
 #pragma unroll 1
             for (int c = 0; c < 2; ++c) {
                 uint32_t o[32];
                 if (me.nT > 0) tmemLd32(oBase + c * 32, o);
-                if (t < me.rowsValid) {
 #pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) {
-                        uint32_t wv[4];
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    uint32_t wv[4];
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const float a = me.nT > 0 ? __uint_as_float(o[8 * q4 + 2 * e]) * inv : 0.f;
-                            const float bb = me.nT > 0 ? __uint_as_float(o[8 * q4 + 2 * e + 1]) * inv : 0.f;
-                            wv[e] = pack16<BF16>(a, bb);
-                        }
-                        *reinterpret_cast<uint4*>(out + c * 64 + q4 * 16) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+                    for (int e = 0; e < 4; ++e) {
+                        const float a = me.nT > 0 ? __uint_as_float(o[8 * q4 + 2 * e]) * inv : 0.f;
+                        const float bb = me.nT > 0 ? __uint_as_float(o[8 * q4 + 2 * e + 1]) * inv : 0.f;
+                        wv[e] = pack16<BF16>(a, bb);
                     }
+                    *reinterpret_cast<uint4*>(stage + t * 256 + h * 128 + (((c * 4 + q4) ^ (t & 7)) << 4)) =
+                        make_uint4(wv[0], wv[1], wv[2], wv[3]);
+                }
+            }
+            __syncwarp();
+            const int rowLo = (warp & 3) * 32;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int row = rowLo + 4 * i + (lane >> 3), chunk = lane & 7;
+                if (row < me.rowsValid) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(stage + row * 256 + h * 128 + ((chunk ^ (row & 7)) << 4));
+                    unsigned char* out = static_cast<unsigned char*>(p.out) +
+                                         ((static_cast<int64_t>(me.rowBase) + row) * p.heads + head) * kHd * 2 + h * 128;
+                    *reinterpret_cast<uint4*>(out + chunk * 16) = v;
                 }
             }
         }
