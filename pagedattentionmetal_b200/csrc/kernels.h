@@ -69,6 +69,7 @@ size_t decodeStaticScratchBytes();
 cudaError_t launchDecodeStatic(const DecodeParams& p, int smCount, cudaStream_t stream, int* launches);
 
 // ---- prefill (prefill_kernels.cu) ----
+constexpr int kPrefillInlineSeqs = 32;
 struct PrefillParams {
     const void* q;            // rows of all sequences back to back, [rows][heads][dim]
     const void* kPool;
@@ -88,11 +89,25 @@ struct PrefillParams {
     int totalRows;                // rows in q/out (all sequences of the launch)
     int* errFlag;                 // device word the tensor-core kernel sets when a bounded wait runs out
     int forceGeneral;             // 1: never take the tensor-core path
+    // Up to kPrefillInlineSeqs sequences travel inside the kernel parameters
+    // (no upload before the launch): rows seqLens, qStarts, qLens, qRowOffsets,
+    // windowStarts; the pointers above are then unused.
+    int inlineMeta;
+    int32_t meta[5][kPrefillInlineSeqs];
     int exactWeights;             // bfloat16 tensor path: 0 = 8-bit weights, 1 = 16-bit on short rows, 2 = 16-bit always
 };
 // Tensor-core path (prefill_tc_kernel.cu): bf16/f16, head_dim 128, block size multiple of 16.
 bool prefillTensorPathApplies(const PrefillParams& p);
 cudaError_t launchPrefillTensor(const PrefillParams& p, int totalRows, int* errFlag, cudaStream_t stream, int* launches);
+#ifdef __CUDACC__
+// Per-sequence fields, from the inline table or from the device arrays.
+__device__ __forceinline__ int prefillMeta(const PrefillParams& p, int which, int seq) {
+    if (p.inlineMeta) return p.meta[which][seq];
+    const int32_t* const ptr = which == 0 ? p.seqLens : which == 1 ? p.qStarts : which == 2 ? p.qLens
+                               : which == 3 ? p.qRowOffsets : p.windowStarts;
+    return ptr[seq];
+}
+#endif
 cudaError_t launchPrefill(const PrefillParams& p, int smCount, cudaStream_t stream, int* launches,
                           bool* usedTensorPath);
 

@@ -599,9 +599,16 @@ int32_t prefillImpl(Context* c, const PamLayerSpec& l, const PamBuffer& q, const
         p.tables = static_cast<const int32_t*>(st.in(tables.ptr, static_cast<size_t>(n) * maxNumBlocks * sizeof(int32_t)));
         p.out = st.out(output.ptr, ioBytes);
         p.kScale = kScale.ptr; p.vScale = vScale.ptr;
-        const int32_t* dm = static_cast<const int32_t*>(st.upload(meta.data(), meta.size() * sizeof(int32_t)));
+        if (n <= pam::kPrefillInlineSeqs) {
+            p.inlineMeta = 1;
+            for (int w = 0; w < 5; ++w)
+                for (int i = 0; i < n; ++i) p.meta[w][i] = meta[static_cast<size_t>(w) * n + i];
+        } else {
+            const int32_t* dm = static_cast<const int32_t*>(st.upload(meta.data(), meta.size() * sizeof(int32_t)));
+            if (!st.ok()) return cudaErrorMemoryAllocation;
+            p.seqLens = dm; p.qStarts = dm + n; p.qLens = dm + 2 * n; p.qRowOffsets = dm + 3 * n; p.windowStarts = dm + 4 * n;
+        }
         if (!st.ok()) return cudaErrorMemoryAllocation;
-        p.seqLens = dm; p.qStarts = dm + n; p.qLens = dm + 2 * n; p.qRowOffsets = dm + 3 * n; p.windowStarts = dm + 4 * n;
         p.numSeqs = n; p.maxQLen = maxQLen; p.heads = l.num_heads; p.kvHeads = l.num_kv_heads; p.headDim = l.head_dim;
         p.blockSize = l.block_size; p.maxNumBlocks = maxNumBlocks; p.causal = causal ? 1 : 0; p.dtype = l.data_type;
         p.poolBlocks = poolBlocksOf(kPool, vPool, l);
@@ -613,7 +620,8 @@ int32_t prefillImpl(Context* c, const PamLayerSpec& l, const PamBuffer& q, const
         cudaError_t e = pam::launchPrefill(p, c->smCount, c->stream, &launches, &tensorPath);
         c->launches += launches;
         if (e == cudaSuccess && tensorPath) {
-            e = cudaMemcpyAsync(c->hostErr, c->devErr, sizeof(int), cudaMemcpyDeviceToHost, c->stream);
+            // the flag is fetched now when the call waits for the GPU anyway, else by pamc_synchronize
+            if (!c->async) e = cudaMemcpyAsync(c->hostErr, c->devErr, sizeof(int), cudaMemcpyDeviceToHost, c->stream);
             c->errPending = true;
         }
         if (e == cudaSuccess) e = st.copyBack();
@@ -985,7 +993,9 @@ int32_t pamc_synchronize(void* ctx) {
     Context* c = asCtx(ctx);
     DeviceGuard dg(c->device);
     if (c->device < 0) return noGpu(c);
-    cudaError_t e = cudaStreamSynchronize(c->stream);
+    cudaError_t e = cudaSuccess;
+    if (c->errPending) e = cudaMemcpyAsync(c->hostErr, c->devErr, sizeof(int), cudaMemcpyDeviceToHost, c->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
     if (e != cudaSuccess) { cudaGetLastError(); return c->fail(PAM_ERR_COMMAND_EXECUTION, commandExecutionFailed(cudaGetErrorString(e))); }
     if (c->errPending) {
         c->errPending = false;

@@ -44,15 +44,15 @@ __device__ __forceinline__ float dequantE4m3(uint8_t v, __half scale) {
 // Works for every storage type, block size and head_dim up to 256; not tuned.
 template <typename QT, typename KT>
 __global__ void __launch_bounds__(128)
-prefillGeneralKernel(PrefillParams p) {
+prefillGeneralKernel(const __grid_constant__ PrefillParams p) {
     constexpr int QR = 16, TB = 16, DPT = 2;
     extern __shared__ __align__(16) unsigned char smem[];
     const int tile = blockIdx.x, head = blockIdx.y, seq = blockIdx.z, tid = threadIdx.x;
     const int D = p.headDim, G = p.heads / p.kvHeads, kvh = head / G;
-    const int qLen = p.qLens[seq];
+    const int qLen = prefillMeta(p, 2, seq);
     if (tile * QR >= qLen) return;
-    const int qStart = p.qStarts[seq], seqLen = p.seqLens[seq], ws = p.windowStarts[seq];
-    const int64_t rowBase = p.qRowOffsets[seq] + tile * QR;
+    const int qStart = prefillMeta(p, 1, seq), seqLen = prefillMeta(p, 0, seq), ws = prefillMeta(p, 4, seq);
+    const int64_t rowBase = prefillMeta(p, 3, seq) + tile * QR;
     const int rows = min(QR, qLen - tile * QR);
     const int firstRow = qStart + tile * QR;             // sequence position of local row 0
 

@@ -347,7 +347,8 @@ struct SlotInfo {
 template <bool BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
-                const __grid_constant__ CUtensorMap mapV, PrefillParams p, float scaleLog2, int* errFlag) {
+                const __grid_constant__ CUtensorMap mapV, const __grid_constant__ PrefillParams p, float scaleLog2,
+                int* errFlag) {
     // Dynamic shared memory starts on a 1024-byte boundary (the swizzle atoms
     // need that); if it ever does not, give up cleanly instead of computing garbage.
     extern __shared__ __align__(1024) unsigned char rawSmem[];
@@ -360,18 +361,18 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int pairIdx = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);   // long tiles first
     const int head = blockIdx.y, seq = blockIdx.z;
-    const int qLen = p.qLens[seq];
+    const int qLen = prefillMeta(p, 2, seq);
     if (pairIdx * kCtaRows >= qLen) return;
     if (*reinterpret_cast<volatile int*>(errFlag) != 0) return;       // an earlier CTA gave up: do not pile up waits
     const int G = p.heads / p.kvHeads, kvh = head / G;
-    const int qStart = p.qStarts[seq], seqLen = p.seqLens[seq], ws = p.windowStarts[seq];
+    const int qStart = prefillMeta(p, 1, seq), seqLen = prefillMeta(p, 0, seq), ws = prefillMeta(p, 4, seq);
     const int tileLo = ws / kKeys;
 
     SlotInfo slot[2];
 #pragma unroll
     for (int x = 0; x < 2; ++x) {
         const int tile = pairIdx * 2 + x;
-        slot[x].rowBase = p.qRowOffsets[seq] + tile * kRows;
+        slot[x].rowBase = prefillMeta(p, 3, seq) + tile * kRows;
         slot[x].rowsValid = min(kRows, qLen - tile * kRows);
         slot[x].firstPos = qStart + tile * kRows;
         const int lastPos = slot[x].firstPos + slot[x].rowsValid - 1;
