@@ -341,6 +341,7 @@ struct SlotInfo {
     int rowsValid;   // rows of the tile that exist (<= 0: the tile is absent)
     int firstPos;    // sequence position of row 0
     int nT;          // key tiles this tile's rows can see (from tileLo on)
+    int head;        // query head of the tile
     int useLo;       // bfloat16: weights as P_hi + P_lo (see below)
 };
 
@@ -359,19 +360,26 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     }
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int pairIdx = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);   // long tiles first
-    const int head = blockIdx.y, seq = blockIdx.z;
+    // The two query tiles of a CTA: with an even number of query heads per KV head, the same
+    // 128 rows of two neighbouring heads (same keys, same masks: the two tiles stay in step);
+    // otherwise 256 consecutive rows of one head.
+    const int G = p.heads / p.kvHeads;
+    const bool pairHeads = (G & 1) == 0;
+    const int unitIdx = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);   // long tiles first
+    const int seq = blockIdx.z;
     const int qLen = prefillMeta(p, 2, seq);
-    if (pairIdx * kCtaRows >= qLen) return;
+    if (unitIdx * (pairHeads ? kRows : kCtaRows) >= qLen) return;
     if (*reinterpret_cast<volatile int*>(errFlag) != 0) return;       // an earlier CTA gave up: do not pile up waits
-    const int G = p.heads / p.kvHeads, kvh = head / G;
+    const int head0 = pairHeads ? 2 * static_cast<int>(blockIdx.y) : static_cast<int>(blockIdx.y);
+    const int kvh = head0 / G;
     const int qStart = prefillMeta(p, 1, seq), seqLen = prefillMeta(p, 0, seq), ws = prefillMeta(p, 4, seq);
     const int tileLo = ws / kKeys;
 
     SlotInfo slot[2];
 #pragma unroll
     for (int x = 0; x < 2; ++x) {
-        const int tile = pairIdx * 2 + x;
+        const int tile = pairHeads ? unitIdx : unitIdx * 2 + x;
+        slot[x].head = pairHeads ? head0 + x : head0;
         slot[x].rowBase = prefillMeta(p, 3, seq) + tile * kRows;
         slot[x].rowsValid = min(kRows, qLen - tile * kRows);
         slot[x].firstPos = qStart + tile * kRows;
@@ -431,8 +439,8 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
 #pragma unroll
                 for (int x = 0; x < 2; ++x) {
                     if (x == 0 || slot[1].nT > 0) {
-                        tmaLoad3d(s->q[x], &mapQ, &s->qFull, 0, head, slot[x].rowBase);
-                        tmaLoad3d(s->q[x] + kHalfBytes, &mapQ, &s->qFull, 64, head, slot[x].rowBase);
+                        tmaLoad3d(s->q[x], &mapQ, &s->qFull, 0, slot[x].head, slot[x].rowBase);
+                        tmaLoad3d(s->q[x] + kHalfBytes, &mapQ, &s->qFull, 64, slot[x].head, slot[x].rowBase);
                     }
                 }
             }
@@ -680,7 +688,7 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 if (row < me.rowsValid) {
                     const uint4 v = *reinterpret_cast<const uint4*>(stage + row * 256 + h * 128 + ((chunk ^ (row & 7)) << 4));
                     unsigned char* out = static_cast<unsigned char*>(p.out) +
-                                         ((static_cast<int64_t>(me.rowBase) + row) * p.heads + head) * kHd * 2 + h * 128;
+                                         ((static_cast<int64_t>(me.rowBase) + row) * p.heads + me.head) * kHd * 2 + h * 128;
                     *reinterpret_cast<uint4*>(out + chunk * 16) = v;
                 }
             }
@@ -756,7 +764,10 @@ cudaError_t launchPrefillTensor(const PrefillParams& p, int totalRows, int* errF
     }
     const size_t smem = sizeof(Smem);
     const float scaleLog2 = (1.0f / sqrtf(static_cast<float>(p.headDim))) * kLog2e;
-    dim3 grid(static_cast<unsigned>((p.maxQLen + kCtaRows - 1) / kCtaRows), static_cast<unsigned>(p.heads), static_cast<unsigned>(p.numSeqs));
+    const bool pairHeads = ((p.heads / p.kvHeads) & 1) == 0;
+    const int unitRows = pairHeads ? kRows : kCtaRows;
+    dim3 grid(static_cast<unsigned>((p.maxQLen + unitRows - 1) / unitRows),
+              static_cast<unsigned>(pairHeads ? p.heads / 2 : p.heads), static_cast<unsigned>(p.numSeqs));
     cudaError_t e;
     if (p.dtype == kBF16) {
         e = cudaFuncSetAttribute(prefillTcKernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));

@@ -82,7 +82,7 @@ def test_prefill_matches_oracle(engine, dtype, causal):
 @pytest.mark.parametrize("dtype", [DT.float16, DT.bfloat16])
 @pytest.mark.parametrize("seq_len,heads,kv_heads,head_dim,block_size", [
     (1, 4, 2, 128, 16), (16, 4, 4, 128, 16), (129, 8, 2, 128, 16), (300, 16, 2, 128, 16),
-    (257, 8, 2, 64, 16), (200, 8, 2, 128, 32), (77, 6, 2, 96, 8),
+    (257, 8, 2, 64, 16), (200, 8, 2, 128, 32), (77, 6, 2, 96, 8), (300, 6, 2, 128, 16), (600, 3, 3, 128, 16),
 ])
 def test_prefill_shapes(engine, dtype, seq_len, heads, kv_heads, head_dim, block_size):
     case = PrefillCase(32, seq_len, heads, kv_heads, head_dim, block_size, dtype)
