@@ -7,38 +7,36 @@
 // kernels.metal:693-765, plus the chunk rows of
 // PagedAttentionEngine.swift:740-756).
 //
-// One CTA owns 256 query rows of one head of one sequence, as two query tiles
-// of 128 rows, and walks the key tiles (128 keys each) those rows can see.
-// Both query tiles use the same K/V tiles in shared memory.  Tensor memory
-// (512 columns) holds, per query tile, S (128 columns, overwritten in place by
-// the weights P) and the accumulator O (128 columns).
+// One CTA owns 128 query rows of one head of one sequence and walks the key
+// tiles (128 keys each) those rows can see.  Tensor memory holds two S buffers
+// (128 columns each, overwritten in place by the weights P) and the
+// accumulator O (128 columns): while the softmax warps turn S of tile j into P,
+// the tensor pipe finishes P V of tile j-1 and Q K^T of tile j+1.
 //
-//   warp 16              TMA producer: the two Q tiles once, then per key tile
-//                        the 8 pages of K and of V (each page is 16 rows x
-//                        256 B, fetched as two 128-byte-swizzled boxes, one
-//                        page per lane) into a 2-stage ring; completion on
-//                        mbarriers.
-//   warp 17 (one thread) MMA issuer: S = Q K^T (8 x tcgen05.mma 128x128x16,
-//                        both operands from shared memory) and O += P V (P
-//                        read from tensor memory, V as an MN-major operand
-//                        straight from its row-major pages); tcgen05.commit
-//                        signals the mbarriers.  The two query tiles alternate,
-//                        so that the tensor pipe works on one while the
-//                        softmax warps work on the other.
-//   warps 0-15           softmax, eight warps per query tile: thread (t, h)
-//                        owns row t and the key columns [64h, 64h+64).  S is
-//                        read from tensor memory (tcgen05.ld), scaled, masked
-//                        (causal, window start, sequence end) only on edge
-//                        tiles; the two halves of a row exchange their maxima
-//                        through shared memory.  The running maximum is only
-//                        raised when it grows by more than 2^8 (the result is
-//                        exact either way, the final division uses the same
-//                        reference), in which case O is rescaled in tensor
-//                        memory.  The weights go back to tensor memory in the
-//                        cache type (tcgen05.st); for bfloat16 as two operands
-//                        P_hi + P_lo (16 significant bits together) and twice
-//                        the PV instructions, because 8-bit weights alone miss
-//                        the 2e-3 bound on short rows.
+//   warp 16              TMA producer of Q (once) and of K: per key tile 8
+//                        pages (each 16 rows x 256 B, fetched as two
+//                        128-byte-swizzled boxes, one page per lane) into a
+//                        3-stage ring; completion on mbarriers.
+//   warp 17              TMA producer of V, 2-stage ring.
+//   warp 18 (one thread) MMA issuer: S = Q K^T (8 x tcgen05.mma 128x128x16,
+//                        both operands from shared memory) two tiles ahead,
+//                        and O += P V (P read from tensor memory, V as an
+//                        MN-major operand straight from its row-major pages);
+//                        tcgen05.commit signals the mbarriers.
+//   warps 0-15           softmax: four threads per row, thread (t, c) owns row t
+//                        and key columns [32c, 32c+32).  S is read from tensor
+//                        memory (tcgen05.ld), scaled, masked (causal, window
+//                        start, sequence end) only on edge tiles; the four
+//                        parts of a row exchange their maxima through shared
+//                        memory.  The running maximum is only raised when it
+//                        grows by more than 2^8 (the result is exact either
+//                        way, the final division uses the same reference), in
+//                        which case O is rescaled in tensor memory.  The
+//                        weights go back to tensor memory in the cache type
+//                        (tcgen05.st); for bfloat16, on rows that see few keys,
+//                        as two operands P_hi + P_lo (16 significant bits
+//                        together) and twice the PV instructions, because 8-bit
+//                        weights alone miss the 2e-3 bound there.
 //
 // Every wait on an mbarrier is bounded; a wait that runs out raises a flag the
 // host reads and the CTA falls through to the common exit, where the tensor
@@ -57,7 +55,7 @@ namespace {
 constexpr int kRows = 128;        // query rows per CTA
 constexpr int kKeys = 128;        // keys per tile
 constexpr int kHd = 128;
-constexpr int kStages = 2;
+constexpr int kKStages = 3, kVStages = 2;
 constexpr int kTileBytes = kRows * kHd * 2;            // 32 KB: one [128][128] 16-bit tile
 constexpr int kHalfBytes = kTileBytes / 2;             // one 64-column block
 constexpr float kLog2e = 1.4426950408889634f;
@@ -82,13 +80,13 @@ __device__ long long gTrace[kTraceRoles * kTraceTiles * kTraceEvents];
 
 struct Smem {
     // tiles first: each 1024-byte aligned (swizzle atoms)
-    unsigned char q[2][kTileBytes];            // two query tiles of 128 rows each
-    unsigned char k[kStages][kTileBytes];
-    unsigned char v[kStages][kTileBytes];
-    unsigned long long qFull, kFull[kStages], vFull[kStages], kvEmpty[kStages];
-    unsigned long long sFull[2], pFull[2], pvDone[2];   // per query tile
-    unsigned long long maxReady[2][2], sumReady[2];     // exchange between the two halves of a row
-    float rowMax[2][2][2][kRows];                       // [query tile][parity][column half][row]
+    unsigned char q[kTileBytes];               // the query tile; reused to stage the output
+    unsigned char k[kKStages][kTileBytes];
+    unsigned char v[kVStages][kTileBytes];
+    unsigned long long qFull, kFull[kKStages], kEmpty[kKStages], vFull[kVStages], vEmpty[kVStages];
+    unsigned long long sFull[2], pFull, pvDone;
+    unsigned long long maxReady[2], sumReady;  // exchange between the four parts of a row
+    float rowMax[2][4][kRows];                 // [parity][column quarter][row]
     uint32_t tmemBase;
     int dead;
 #ifdef PAM_PREFILL_TRACE
@@ -285,6 +283,19 @@ struct MaskInfo {
     }
 };
 
+// Maximum of 32 raw scores; EDGE tiles mask invisible keys.
+template <bool EDGE>
+__device__ __forceinline__ float quarterRowMax(const uint32_t (&r)[32], const MaskInfo& mk, int firstKey) {
+    float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        float a = __uint_as_float(r[i]);
+        if (EDGE && !mk.visible(firstKey + i)) a = -INFINITY;
+        m4[i & 3] = fmaxf(m4[i & 3], a);
+    }
+    return fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+}
+
 // Maximum of 64 raw scores (two loaded chunks); EDGE tiles mask invisible keys.
 template <bool EDGE>
 __device__ __forceinline__ float halfRowMax(const uint32_t (&r0)[32], const uint32_t (&r1)[32], const MaskInfo& mk, int firstKey) {
@@ -329,21 +340,9 @@ __device__ __forceinline__ float weights32(const uint32_t (&r)[32], uint32_t (&w
     return (s4[0] + s4[1]) + (s4[2] + s4[3]);
 }
 
-constexpr int kSlotThreads = 256;                      // softmax threads per query tile: two per row
-constexpr int kSoftmaxThreads = 2 * kSlotThreads;
-constexpr int kThreads = kSoftmaxThreads + 64;         // + producer warp + MMA warp
-constexpr int kProducerWarp = 16, kMmaWarp = 17;
-constexpr int kCtaRows = 2 * kRows;                    // query rows per CTA
-
-// Per query tile (slot x = 0, 1) of the CTA.
-struct SlotInfo {
-    int rowBase;     // first row of the tile in q/out
-    int rowsValid;   // rows of the tile that exist (<= 0: the tile is absent)
-    int firstPos;    // sequence position of row 0
-    int nT;          // key tiles this tile's rows can see (from tileLo on)
-    int head;        // query head of the tile
-    int useLo;       // bfloat16: weights as P_hi + P_lo (see below)
-};
+constexpr int kSoftmaxThreads = 512;                   // four threads per row
+constexpr int kKProducerWarp = 16, kVProducerWarp = 17, kMmaWarp = 18;
+constexpr int kThreads = kSoftmaxThreads + 96;
 
 template <bool BF16>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -360,43 +359,30 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     }
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // The two query tiles of a CTA: with an even number of query heads per KV head, the same
-    // 128 rows of two neighbouring heads (same keys, same masks: the two tiles stay in step);
-    // otherwise 256 consecutive rows of one head.
-    const int G = p.heads / p.kvHeads;
-    const bool pairHeads = (G & 1) == 0;
-    const int unitIdx = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);   // long tiles first
-    const int seq = blockIdx.z;
+    const int tile = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);   // long tiles first
+    const int head = blockIdx.y, seq = blockIdx.z;
     const int qLen = prefillMeta(p, 2, seq);
-    if (unitIdx * (pairHeads ? kRows : kCtaRows) >= qLen) return;
+    if (tile * kRows >= qLen) return;
     if (*reinterpret_cast<volatile int*>(errFlag) != 0) return;       // an earlier CTA gave up: do not pile up waits
-    const int head0 = pairHeads ? 2 * static_cast<int>(blockIdx.y) : static_cast<int>(blockIdx.y);
-    const int kvh = head0 / G;
+    const int G = p.heads / p.kvHeads, kvh = head / G;
     const int qStart = prefillMeta(p, 1, seq), seqLen = prefillMeta(p, 0, seq), ws = prefillMeta(p, 4, seq);
+    const int rowBase = prefillMeta(p, 3, seq) + tile * kRows;        // first row of the tile in q/out
+    const int rowsValid = min(kRows, qLen - tile * kRows);
+    const int firstPos = qStart + tile * kRows;                       // sequence position of row 0
+    const int lastPos = firstPos + rowsValid - 1;
+    // Key tiles tileLo .. tileLo + nT - 1 hold every key a row of this tile may see.
+    const int keyEnd = p.causal ? min(seqLen, lastPos + 1) : seqLen;  // exclusive
     const int tileLo = ws / kKeys;
+    const int nT = keyEnd > ws ? (keyEnd - 1) / kKeys - tileLo + 1 : 0;
+    // Fewest keys any row of the tile sees.  A bfloat16 weight keeps 8 significant bits; on a
+    // row with few keys (large weights) that alone can cost more than 2e-3 on unit-variance
+    // values, so such tiles carry the weights as two bfloat16 operands (16 bits).  Rows with
+    // hundreds of keys have weights small enough for 8 bits, as in every bfloat16 attention
+    // kernel.  exactWeights: 0 never, 1 short rows, 2 always.
+    const int fewest = p.causal ? firstPos + 1 - ws : seqLen - ws;
+    const bool useLo = BF16 && (p.exactWeights == 2 || (p.exactWeights == 1 && fewest < kShortRowKeys));
 
-    SlotInfo slot[2];
-#pragma unroll
-    for (int x = 0; x < 2; ++x) {
-        const int tile = pairHeads ? unitIdx : unitIdx * 2 + x;
-        slot[x].head = pairHeads ? head0 + x : head0;
-        slot[x].rowBase = prefillMeta(p, 3, seq) + tile * kRows;
-        slot[x].rowsValid = min(kRows, qLen - tile * kRows);
-        slot[x].firstPos = qStart + tile * kRows;
-        const int lastPos = slot[x].firstPos + slot[x].rowsValid - 1;
-        const int keyEnd = p.causal ? min(seqLen, lastPos + 1) : seqLen;                   // exclusive
-        slot[x].nT = (slot[x].rowsValid > 0 && keyEnd > ws) ? (keyEnd - 1) / kKeys - tileLo + 1 : 0;
-        // Fewest keys any row of the tile sees.  A bfloat16 weight keeps 8 significant bits;
-        // on a row with few keys (large weights) that alone can cost more than 2e-3 on
-        // unit-variance values, so such tiles carry the weights as two bfloat16 operands
-        // (16 bits).  Rows with hundreds of keys have weights small enough for 8 bits,
-        // as in every bfloat16 attention kernel.  exactWeights: 0 never, 1 short rows, 2 always.
-        const int fewest = p.causal ? slot[x].firstPos + 1 - ws : seqLen - ws;
-        slot[x].useLo = BF16 && (p.exactWeights == 2 || (p.exactWeights == 1 && fewest < kShortRowKeys));
-    }
-    const int nTmax = max(slot[0].nT, slot[1].nT);
-
-    if (threadIdx.x == kProducerWarp * 32) {
+    if (threadIdx.x == kKProducerWarp * 32) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(&mapQ) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&mapK) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&mapV) : "memory");
@@ -404,15 +390,12 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     TRACE(0, 31, 0);                                   // CTA start (instrumented build)
     if (threadIdx.x == 0) {
         mbarInit(&s->qFull, 1);
-        for (int i = 0; i < kStages; ++i) { mbarInit(&s->kFull[i], 1); mbarInit(&s->vFull[i], 1); mbarInit(&s->kvEmpty[i], 1); }
-        for (int x = 0; x < 2; ++x) {
-            mbarInit(&s->sFull[x], 1);
-            mbarInit(&s->pFull[x], kSlotThreads);
-            mbarInit(&s->pvDone[x], 1);
-            mbarInit(&s->maxReady[x][0], kSlotThreads);
-            mbarInit(&s->maxReady[x][1], kSlotThreads);
-            mbarInit(&s->sumReady[x], kSlotThreads);
-        }
+        for (int i = 0; i < kKStages; ++i) { mbarInit(&s->kFull[i], 1); mbarInit(&s->kEmpty[i], 1); }
+        for (int i = 0; i < kVStages; ++i) { mbarInit(&s->vFull[i], 1); mbarInit(&s->vEmpty[i], 1); }
+        for (int i = 0; i < 2; ++i) { mbarInit(&s->sFull[i], 1); mbarInit(&s->maxReady[i], kSoftmaxThreads); }
+        mbarInit(&s->pFull, kSoftmaxThreads);
+        mbarInit(&s->pvDone, 1);
+        mbarInit(&s->sumReady, kSoftmaxThreads);
         s->dead = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -425,58 +408,64 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     tcFenceAfter();
     const uint32_t tmem = s->tmemBase;
     TRACE(0, 31, 1);                                   // barriers and tensor memory ready
-    // per query tile: S (aliased by P once the scores are consumed) and O
-    const uint32_t tmemS[2] = {tmem, tmem + 256u};
-    const uint32_t tmemO[2] = {tmem + 128u, tmem + 384u};
+    const uint32_t tmemS[2] = {tmem, tmem + 128u};
+    const uint32_t tmemO = tmem + 256u;
 
-    if (warp == kProducerWarp) {
-        // ------------------------------------------------------------ TMA producer
-        // Lane 0 arms the barriers; lanes 0-7 each fetch one 16-token page piece
-        // of K and of V (their block-table reads run in parallel).
-        if (nTmax > 0) {
+    // Row of the pool (block * kv_heads * block_size space) of the 16-token piece `lane`
+    // of key tile j; lanes 0-7 of a producer warp fetch one piece each.
+    const int32_t* table = p.tables + static_cast<int64_t>(seq) * p.maxNumBlocks;
+    const int tilesPerPage = p.blockSize / 16;
+    auto pieceRow = [&](int j) {
+        const int t16 = (tileLo + j) * (kKeys / 16) + lane;
+        const int page = min(t16 / tilesPerPage, p.maxNumBlocks - 1);
+        const int blk = min(max(table[page], 0), p.poolBlocks - 1);
+        return (blk * p.kvHeads + kvh) * p.blockSize + (t16 % tilesPerPage) * 16;
+    };
+
+    if (warp == kKProducerWarp) {
+        // ------------------------------------------------------------ Q and K producer
+        if (nT > 0) {
             if (lane == 0) {
-                mbarExpectTx(&s->qFull, slot[1].nT > 0 ? 2 * kTileBytes : kTileBytes);
-#pragma unroll
-                for (int x = 0; x < 2; ++x) {
-                    if (x == 0 || slot[1].nT > 0) {
-                        tmaLoad3d(s->q[x], &mapQ, &s->qFull, 0, slot[x].head, slot[x].rowBase);
-                        tmaLoad3d(s->q[x] + kHalfBytes, &mapQ, &s->qFull, 64, slot[x].head, slot[x].rowBase);
-                    }
-                }
+                mbarExpectTx(&s->qFull, kTileBytes);
+                tmaLoad3d(s->q, &mapQ, &s->qFull, 0, head, rowBase);
+                tmaLoad3d(s->q + kHalfBytes, &mapQ, &s->qFull, 64, head, rowBase);
             }
-            const int32_t* table = p.tables + static_cast<int64_t>(seq) * p.maxNumBlocks;
-            const int tilesPerPage = p.blockSize / 16;
             bool ok = true;
-            for (int j = 0; j < nTmax && ok; ++j) {
-                const int st = j % kStages;
-                int row = 0;
-                if (lane < kKeys / 16) {
-                    const int t16 = (tileLo + j) * (kKeys / 16) + lane;           // 16-token piece of the sequence
-                    const int page = min(t16 / tilesPerPage, p.maxNumBlocks - 1);
-                    const int blk = min(max(table[page], 0), p.poolBlocks - 1);
-                    row = (blk * p.kvHeads + kvh) * p.blockSize + (t16 % tilesPerPage) * 16;
-                }
-                if (j >= kStages) ok = mbarWait(&s->kvEmpty[st], ((j / kStages) - 1) & 1, &s->dead, errFlag, 1);
+            for (int j = 0; j < nT && ok; ++j) {
+                const int st = j % kKStages;
+                const int row = lane < kKeys / 16 ? pieceRow(j) : 0;
+                if (j >= kKStages) ok = mbarWait(&s->kEmpty[st], ((j / kKStages) - 1) & 1, &s->dead, errFlag, 1);
                 ok = __all_sync(0xFFFFFFFFu, ok);
                 if (!ok) break;
-                if (lane == 0) {
-                    mbarExpectTx(&s->kFull[st], kTileBytes);
-                    mbarExpectTx(&s->vFull[st], kTileBytes);
-                }
+                if (lane == 0) mbarExpectTx(&s->kFull[st], kTileBytes);
                 __syncwarp();
                 if (lane < kKeys / 16) {
                     tmaLoad2d(s->k[st] + lane * 2048, &mapK, &s->kFull[st], 0, row);
                     tmaLoad2d(s->k[st] + kHalfBytes + lane * 2048, &mapK, &s->kFull[st], 64, row);
-                    tmaLoad2d(s->v[st] + lane * 2048, &mapV, &s->vFull[st], 0, row);
-                    tmaLoad2d(s->v[st] + kHalfBytes + lane * 2048, &mapV, &s->vFull[st], 64, row);
                 }
+            }
+        }
+    } else if (warp == kVProducerWarp) {
+        // ------------------------------------------------------------ V producer
+        bool ok = true;
+        for (int j = 0; j < nT && ok; ++j) {
+            const int st = j % kVStages;
+            const int row = lane < kKeys / 16 ? pieceRow(j) : 0;
+            if (j >= kVStages) ok = mbarWait(&s->vEmpty[st], ((j / kVStages) - 1) & 1, &s->dead, errFlag, 13);
+            ok = __all_sync(0xFFFFFFFFu, ok);
+            if (!ok) break;
+            if (lane == 0) mbarExpectTx(&s->vFull[st], kTileBytes);
+            __syncwarp();
+            if (lane < kKeys / 16) {
+                tmaLoad2d(s->v[st] + lane * 2048, &mapV, &s->vFull[st], 0, row);
+                tmaLoad2d(s->v[st] + kHalfBytes + lane * 2048, &mapV, &s->vFull[st], 64, row);
             }
         }
     } else if (warp == kMmaWarp) {
         // ------------------------------------------------------------ MMA issuer
-        // Tensor-core instructions of one thread execute in issue order, so S of
-        // tile j+1 (written over P of tile j) needs no wait on PV of tile j.
-        if (lane == 0 && nTmax > 0) {
+        // Tensor-core instructions of one thread execute in issue order: S of tile j+2 is
+        // written over P of tile j right behind P V of tile j without a wait in between.
+        if (lane == 0 && nT > 0) {
             const uint32_t fmt = BF16 ? 1u : 0u;
             // D = f32, A/B = bf16|f16, M = 128, N = 128; B of the second product is MN-major.
             const uint32_t idescS = (1u << 4) | (fmt << 7) | (fmt << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
@@ -484,108 +473,88 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             // the hardware (illegal instruction), the two operands must agree.
             const uint32_t idescO = idescS | (1u << 16);
             const uint32_t hiK = descHi(1024);                      // K-major tiles and the MN-major V tile share it
-            const uint32_t qLo[2] = {descLo(smemAddr(s->q[0]), 16), descLo(smemAddr(s->q[1]), 16)};
-            const uint32_t kLo[kStages] = {descLo(smemAddr(s->k[0]), 16), descLo(smemAddr(s->k[1]), 16)};
-            const uint32_t vLo[kStages] = {descLo(smemAddr(s->v[0]), kHalfBytes), descLo(smemAddr(s->v[1]), kHalfBytes)};
-            auto issueQK = [&](int x, int st) {
+            const uint32_t qLo = descLo(smemAddr(s->q), 16);
+            bool ok = mbarWait(&s->qFull, 0, &s->dead, errFlag, 2);
+            auto issueQK = [&](int j) {
+                const int st = j % kKStages;
+                ok = mbarWait(&s->kFull[st], (j / kKStages) & 1, &s->dead, errFlag, 3);
+                if (!ok) return;
+                tcFenceAfter();
+                const uint32_t kLo = descLo(smemAddr(s->k[st]), 16);
 #pragma unroll
                 for (int ks = 0; ks < kHd / 16; ++ks) {
                     const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
-                    umma(tmemS[x], desc64(qLo[x] + off, hiK), desc64(kLo[st] + off, hiK), idescS, ks > 0);
+                    umma(tmemS[j & 1], desc64(qLo + off, hiK), desc64(kLo + off, hiK), idescS, ks > 0);
                 }
-                ummaCommit(&s->sFull[x]);
+                ummaCommit(&s->sFull[j & 1]);
+                ummaCommit(&s->kEmpty[st]);
+                TRACE(2, j, 3);
             };
-            bool ok = mbarWait(&s->qFull, 0, &s->dead, errFlag, 2);
-            if (ok) ok = mbarWait(&s->kFull[0], 0, &s->dead, errFlag, 3);
-            if (ok) {
+            if (ok) issueQK(0);
+            if (ok && nT > 1) issueQK(1);
+            for (int j = 0; j < nT && ok; ++j) {
+                const int st = j % kVStages;
+                TRACE(2, j, 0);
+                ok = mbarWait(&s->pFull, j & 1, &s->dead, errFlag, 5);
+                if (ok) ok = mbarWait(&s->vFull[st], (j / kVStages) & 1, &s->dead, errFlag, 6);
+                if (!ok) break;
                 tcFenceAfter();
-                for (int x = 0; x < 2; ++x)
-                    if (slot[x].nT > 0) issueQK(x, 0);
-            }
-            for (int j = 0; j < nTmax && ok; ++j) {
-                const int st = j % kStages;
-                bool vReady = false, kNextReady = false;
-                for (int x = 0; x < 2 && ok; ++x) {
-                    if (j < slot[x].nT) {
-                        TRACE(2 + x, j, 0);
-                        ok = mbarWait(&s->pFull[x], j & 1, &s->dead, errFlag, 5);
-                        TRACE(2 + x, j, 1);
-                        if (ok && !vReady) { ok = mbarWait(&s->vFull[st], (j / kStages) & 1, &s->dead, errFlag, 6); vReady = true; }
-                        if (!ok) break;
-                        tcFenceAfter();
-                        // P of keys 32c .. 32c+31 sits in columns 32c .. 32c+15 (and, for bfloat16,
-                        // its low-order part in columns 32c+16 .. 32c+31) of the S region
+                TRACE(2, j, 1);
+                const uint32_t vLo = descLo(smemAddr(s->v[st]), kHalfBytes);
+                // P of keys 32c .. 32c+31 sits in columns 32c .. 32c+15 (and, with the low-order
+                // pass, its remainder in columns 32c+16 .. 32c+31) of the S buffer
 #pragma unroll
-                        for (int ks = 0; ks < kKeys / 16; ++ks) {
-                            const uint32_t pCol = tmemS[x] + 32u * (ks >> 1) + 8u * (ks & 1);
-                            ummaTs(tmemO[x], pCol, desc64(vLo[st] + ks * 128, hiK), idescO, (j > 0 || ks > 0) ? 1u : 0u);
-                        }
-                        if (BF16 && slot[x].useLo) {
+                for (int ks = 0; ks < kKeys / 16; ++ks) {
+                    const uint32_t pCol = tmemS[j & 1] + 32u * (ks >> 1) + 8u * (ks & 1);
+                    ummaTs(tmemO, pCol, desc64(vLo + ks * 128, hiK), idescO, (j > 0 || ks > 0) ? 1u : 0u);
+                }
+                if (useLo) {
 #pragma unroll
-                            for (int ks = 0; ks < kKeys / 16; ++ks) {
-                                const uint32_t pCol = tmemS[x] + 32u * (ks >> 1) + 8u * (ks & 1) + 16u;
-                                ummaTs(tmemO[x], pCol, desc64(vLo[st] + ks * 128, hiK), idescO, 1u);
-                            }
-                        }
-                        ummaCommit(&s->pvDone[x]);
-                        TRACE(2 + x, j, 2);
-                    }
-                    if (j + 1 < slot[x].nT) {
-                        if (!kNextReady) {
-                            ok = mbarWait(&s->kFull[(j + 1) % kStages], ((j + 1) / kStages) & 1, &s->dead, errFlag, 3);
-                            kNextReady = true;
-                            if (!ok) break;
-                            tcFenceAfter();
-                        }
-                        issueQK(x, (j + 1) % kStages);
-                        TRACE(2 + x, j, 3);
+                    for (int ks = 0; ks < kKeys / 16; ++ks) {
+                        const uint32_t pCol = tmemS[j & 1] + 32u * (ks >> 1) + 8u * (ks & 1) + 16u;
+                        ummaTs(tmemO, pCol, desc64(vLo + ks * 128, hiK), idescO, 1u);
                     }
                 }
-                if (ok) ummaCommit(&s->kvEmpty[st]);      // every instruction that reads stage st has been issued
+                ummaCommit(&s->pvDone);
+                ummaCommit(&s->vEmpty[st]);
+                TRACE(2, j, 2);
+                if (j + 2 < nT) issueQK(j + 2);
             }
         }
     } else {
         // ------------------------------------------------------------ softmax warps
-        // Eight warps per query tile x.  Thread (t, h) owns row t and the key
-        // columns [64h, 64h + 64) of every key tile, and the output columns
-        // [64h, 64h + 64).  Four warps per scheduler cover each other's latencies;
-        // the two halves of a row exchange their maxima (and at the end their
-        // sums) through shared memory and a bounded mbarrier wait.
-        const int x = warp >> 3, h = (warp >> 2) & 1, t = (warp & 3) * 32 + lane;
-        const SlotInfo me = slot[x];
-        const int rowPos = me.firstPos + t;
+        // Thread (t, cq): row t, key columns [32cq, 32cq + 32) of every key tile and output
+        // columns [32cq, 32cq + 32).  Warps w, w+4, w+8, w+12 share the tensor-memory lanes
+        // 32(w&3) .. +31 (a warp may only touch the lane quarter of its index modulo 4).
+        const int cq = warp >> 2, t = (warp & 3) * 32 + lane;
+        const int rowPos = firstPos + t;
         const uint32_t laneBase = static_cast<uint32_t>((warp & 3) * 32) << 16;
-        const uint32_t sBase = tmemS[x] + laneBase + 64u * h, oBase = tmemO[x] + laneBase + 64u * h;
+        const uint32_t oBase = tmemO + laneBase + 32u * cq;
+        const MaskInfo mk(ws, seqLen, rowPos, p.causal);
         float mUsed = -INFINITY, l = 0.f;
         bool ok = true;
-        for (int j = 0; j < me.nT && ok; ++j) {
-            const int st = j % kStages;
+        for (int j = 0; j < nT && ok; ++j) {
+            const int b = j & 1;
             const int k0 = (tileLo + j) * kKeys;
-            const int kh = k0 + 64 * h;                                     // first key of this thread's columns
-            const bool edge = k0 < ws || k0 + kKeys > seqLen || (p.causal && k0 + kKeys - 1 > me.firstPos);
-            // S of tile j is complete; so is every earlier instruction, PV of tile j-1 included
+            const int kq = k0 + 32 * cq;                                    // first key of this thread's columns
+            const uint32_t sBase = tmemS[b] + laneBase + 32u * cq;
+            const bool edge = k0 < ws || k0 + kKeys > seqLen || (p.causal && k0 + kKeys - 1 > firstPos);
             TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), j, 0);
-            ok = mbarWait(&s->sFull[x], j & 1, &s->dead, errFlag, 7);
+            ok = mbarWait(&s->sFull[b], (j >> 1) & 1, &s->dead, errFlag, 7);
             if (!ok) break;
             tcFenceAfter();
             TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), j, 1);
-            // maximum of the raw scores of this half row (the scale is positive)
-            const MaskInfo mk(ws, seqLen, rowPos, p.causal);
-            float tmax;
-            {
-                uint32_t r0[32], r1[32];
-                tmemLd32NoWait(sBase, r0);
-                tmemLd32NoWait(sBase + 32, r1);
-                tmemLdWait();
-                TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), j, 4);
-                tmax = (edge ? halfRowMax<true>(r0, r1, mk, kh) : halfRowMax<false>(r0, r1, mk, kh)) * scaleLog2;
-            }
-            s->rowMax[x][j & 1][h][t] = tmax;
-            mbarArrive(&s->maxReady[x][j & 1]);
+            uint32_t r[32];
+            tmemLd32(sBase, r);
+            TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), j, 4);
+            // maximum of the raw scores of this quarter row (the scale is positive)
+            float tmax = (edge ? quarterRowMax<true>(r, mk, kq) : quarterRowMax<false>(r, mk, kq)) * scaleLog2;
+            s->rowMax[b][cq][t] = tmax;
+            mbarArrive(&s->maxReady[b]);
             TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), j, 5);
-            ok = mbarWait(&s->maxReady[x][j & 1], (j >> 1) & 1, &s->dead, errFlag, 11);
+            ok = mbarWait(&s->maxReady[b], (j >> 1) & 1, &s->dead, errFlag, 11);
             if (!ok) break;
-            tmax = fmaxf(tmax, s->rowMax[x][j & 1][h ^ 1][t]);
+            tmax = fmaxf(fmaxf(s->rowMax[b][0][t], s->rowMax[b][1][t]), fmaxf(s->rowMax[b][2][t], s->rowMax[b][3][t]));
             TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), j, 2);
             bool raise = false;
             float corr = 1.f;
@@ -596,99 +565,88 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 mUsed = tmax;
             }
             if (j >= 1 && __any_sync(0xFFFFFFFFu, raise)) {
-#pragma unroll 1
-                for (int c = 0; c < 2; ++c) {
-                    uint32_t o[32];
-                    tmemLd32(oBase + c * 32, o);
+                // O is still being added to by P V of tile j-1: wait for it, then rescale
+                ok = mbarWait(&s->pvDone, (j - 1) & 1, &s->dead, errFlag, 8);
+                if (!ok) break;
+                tcFenceAfter();
+                uint32_t o[32];
+                tmemLd32(oBase, o);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
-                    tmemSt32(oBase + c * 32, o);
-                }
+                for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+                tmemSt32(oBase, o);
                 l *= corr;
             }
-            // the weights replace the scores in tensor memory, 32 keys at a time: 16 columns of
-            // packed pairs (plus 16 columns of their low-order parts for bfloat16)
+            // the weights replace the scores in tensor memory: 16 columns of packed pairs
+            // (plus 16 columns of their low-order parts where the tile needs 16-bit weights)
             const float negM = mUsed == -INFINITY ? 0.f : -mUsed;
-            float sum = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < 2; ++c) {
-                uint32_t r[32];
-                tmemLd32(sBase + c * 32, r);
-                TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), j, 6 + c);
-                uint32_t w[32];
-                if (BF16 && me.useLo) {
-                    sum += edge ? weights32<BF16, true, true>(r, w, scaleLog2, negM, mk, kh + c * 32)
-                                : weights32<BF16, true, false>(r, w, scaleLog2, negM, mk, kh + c * 32);
-                    tmemSt32(sBase + c * 32, w);
-                } else {
-                    sum += edge ? weights32<BF16, false, true>(r, w, scaleLog2, negM, mk, kh + c * 32)
-                                : weights32<BF16, false, false>(r, w, scaleLog2, negM, mk, kh + c * 32);
-                    tmemSt16(sBase + c * 32, w);
-                }
-                TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), j, 8 + c);
+            uint32_t w[32];
+            if (useLo) {
+                l += edge ? weights32<BF16, true, true>(r, w, scaleLog2, negM, mk, kq)
+                          : weights32<BF16, true, false>(r, w, scaleLog2, negM, mk, kq);
+                tmemSt32(sBase, w);
+            } else {
+                l += edge ? weights32<BF16, false, true>(r, w, scaleLog2, negM, mk, kq)
+                          : weights32<BF16, false, false>(r, w, scaleLog2, negM, mk, kq);
+                tmemSt16(sBase, w);
             }
             tmemStWait();
             TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), j, 10);
-            l += sum;
-            // The lowest-numbered query tile that uses this key tile clears the rows of V
-            // past the end of the sequence (they may hold anything); the MMA thread
-            // takes the query tiles in that order.
-            if (k0 + kKeys > seqLen && (x == 0 || j >= slot[0].nT)) {
-                ok = mbarWait(&s->vFull[st], (j / kStages) & 1, &s->dead, errFlag, 9);
+            if (k0 + kKeys > seqLen) {
+                // rows of V past the end of the sequence may hold anything: zero them
+                const int st = j % kVStages;
+                ok = mbarWait(&s->vFull[st], (j / kVStages) & 1, &s->dead, errFlag, 9);
                 if (!ok) break;
                 if (k0 + t >= seqLen) {
 #pragma unroll
-                    for (int c16 = 0; c16 < 8; ++c16)
-                        *reinterpret_cast<uint4*>(s->v[st] + h * kHalfBytes + t * 128 + c16 * 16) = make_uint4(0u, 0u, 0u, 0u);
+                    for (int c16 = 0; c16 < 4; ++c16)
+                        *reinterpret_cast<uint4*>(s->v[st] + (cq >> 1) * kHalfBytes + t * 128 + ((cq & 1) * 4 + c16) * 16) =
+                            make_uint4(0u, 0u, 0u, 0u);
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             }
             tcFenceBefore();
-            mbarArrive(&s->pFull[x]);
+            mbarArrive(&s->pFull);
             TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), j, 3);
         }
         // epilogue: O / l to global memory
         if (ok) {
-            s->rowMax[x][me.nT & 1][h][t] = l;       // the buffer the last tile did not use
-            mbarArrive(&s->sumReady[x]);
-            ok = mbarWait(&s->sumReady[x], 0, &s->dead, errFlag, 12);
+            s->rowMax[nT & 1][cq][t] = l;            // the buffer the last tile did not use
+            mbarArrive(&s->sumReady);
+            ok = mbarWait(&s->sumReady, 0, &s->dead, errFlag, 12);
         }
-        if (ok && me.nT > 0) ok = mbarWait(&s->pvDone[x], (me.nT - 1) & 1, &s->dead, errFlag, 10);
+        if (ok && nT > 0) ok = mbarWait(&s->pvDone, (nT - 1) & 1, &s->dead, errFlag, 10);
         TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), 31, 2);   // last PV done
-        if (ok && me.rowsValid > 0) {
+        if (ok) {
             tcFenceAfter();
-            const float lt = l + s->rowMax[x][me.nT & 1][h ^ 1][t];
-            const float inv = (me.nT > 0 && lt > 0.f) ? 1.f / lt : 0.f;
-            // The Q tile of this query tile is no longer read: stage this warp's 32 rows x
-            // 128 bytes there (16-byte chunks XOR-swizzled by row), then write them out four
-            // rows per instruction, 128 contiguous bytes per row.
-            unsigned char* stage = s->q[x];
-#pragma unroll 1
-            for (int c = 0; c < 2; ++c) {
-                uint32_t o[32];
-                if (me.nT > 0) tmemLd32(oBase + c * 32, o);
+            const float lt = (s->rowMax[nT & 1][0][t] + s->rowMax[nT & 1][1][t]) + (s->rowMax[nT & 1][2][t] + s->rowMax[nT & 1][3][t]);
+            const float inv = (nT > 0 && lt > 0.f) ? 1.f / lt : 0.f;
+            // The Q tile is no longer read: stage this warp's 32 rows x 64 bytes there (16-byte
+            // chunks XOR-swizzled by row), then write them out eight rows per instruction,
+            // 64 contiguous bytes per row.
+            unsigned char* stage = s->q;
+            uint32_t o[32];
+            if (nT > 0) tmemLd32(oBase, o);
 #pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    uint32_t wv[4];
+            for (int q4 = 0; q4 < 4; ++q4) {
+                uint32_t wv[4];
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float a = me.nT > 0 ? __uint_as_float(o[8 * q4 + 2 * e]) * inv : 0.f;
-                        const float bb = me.nT > 0 ? __uint_as_float(o[8 * q4 + 2 * e + 1]) * inv : 0.f;
-                        wv[e] = pack16<BF16>(a, bb);
-                    }
-                    *reinterpret_cast<uint4*>(stage + t * 256 + h * 128 + (((c * 4 + q4) ^ (t & 7)) << 4)) =
-                        make_uint4(wv[0], wv[1], wv[2], wv[3]);
+                for (int e = 0; e < 4; ++e) {
+                    const float a = nT > 0 ? __uint_as_float(o[8 * q4 + 2 * e]) * inv : 0.f;
+                    const float bb = nT > 0 ? __uint_as_float(o[8 * q4 + 2 * e + 1]) * inv : 0.f;
+                    wv[e] = pack16<BF16>(a, bb);
                 }
+                *reinterpret_cast<uint4*>(stage + t * 256 + (((cq * 4 + q4) ^ (t & 7)) << 4)) =
+                    make_uint4(wv[0], wv[1], wv[2], wv[3]);
             }
             __syncwarp();
             const int rowLo = (warp & 3) * 32;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int row = rowLo + 4 * i + (lane >> 3), chunk = lane & 7;
-                if (row < me.rowsValid) {
-                    const uint4 v = *reinterpret_cast<const uint4*>(stage + row * 256 + h * 128 + ((chunk ^ (row & 7)) << 4));
+            for (int i = 0; i < 4; ++i) {
+                const int row = rowLo + 8 * i + (lane >> 2), chunk = cq * 4 + (lane & 3);
+                if (row < rowsValid) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(stage + row * 256 + ((chunk ^ (row & 7)) << 4));
                     unsigned char* out = static_cast<unsigned char*>(p.out) +
-                                         ((static_cast<int64_t>(me.rowBase) + row) * p.heads + me.head) * kHd * 2 + h * 128;
+                                         ((static_cast<int64_t>(rowBase) + row) * p.heads + head) * kHd * 2;
                     *reinterpret_cast<uint4*>(out + chunk * 16) = v;
                 }
             }
@@ -764,10 +722,7 @@ cudaError_t launchPrefillTensor(const PrefillParams& p, int totalRows, int* errF
     }
     const size_t smem = sizeof(Smem);
     const float scaleLog2 = (1.0f / sqrtf(static_cast<float>(p.headDim))) * kLog2e;
-    const bool pairHeads = ((p.heads / p.kvHeads) & 1) == 0;
-    const int unitRows = pairHeads ? kRows : kCtaRows;
-    dim3 grid(static_cast<unsigned>((p.maxQLen + unitRows - 1) / unitRows),
-              static_cast<unsigned>(pairHeads ? p.heads / 2 : p.heads), static_cast<unsigned>(p.numSeqs));
+    dim3 grid(static_cast<unsigned>((p.maxQLen + kRows - 1) / kRows), static_cast<unsigned>(p.heads), static_cast<unsigned>(p.numSeqs));
     cudaError_t e;
     if (p.dtype == kBF16) {
         e = cudaFuncSetAttribute(prefillTcKernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
