@@ -7,22 +7,25 @@
 // kernels.metal:693-765, plus the chunk rows of
 // PagedAttentionEngine.swift:740-756).
 //
-// One CTA owns 128 query rows of one head of one sequence and walks the key
-// tiles (128 keys each) those rows can see.  Tensor memory holds two S buffers
-// (128 columns each, overwritten in place by the weights P) and the
-// accumulator O (128 columns): while the softmax warps turn S of tile j into P,
-// the tensor pipe finishes P V of tile j-1 and Q K^T of tile j+1.
+// The kernel is persistent: one CTA per multiprocessor walks the work items
+// (128 query rows of one head of one sequence) round robin, longest items
+// first.  An item walks the key tiles (128 keys each) its rows can see.
+// Tensor memory holds two S buffers (128 columns each, overwritten in place by
+// the weights P) and two accumulators O (128 columns each, alternating between
+// items): while the softmax warps turn S of tile g into P, the tensor pipe
+// finishes P V of tile g-1 and Q K^T of tile g+1, across item boundaries.
 //
-//   warp 16              TMA producer of Q (once) and of K: per key tile 8
-//                        pages (each 16 rows x 256 B, fetched as two
-//                        128-byte-swizzled boxes, one page per lane) into a
-//                        3-stage ring; completion on mbarriers.
-//   warp 17              TMA producer of V, 2-stage ring.
+//   warp 16              TMA producer of Q (two buffers, one per item in flight)
+//                        and of K: per key tile 8 pages (each 16 rows x 256 B,
+//                        fetched as two 128-byte-swizzled boxes, one page per
+//                        lane) into a ring; completion on mbarriers.
+//   warp 17              TMA producer of V, its own ring.
 //   warp 18 (one thread) MMA issuer: S = Q K^T (8 x tcgen05.mma 128x128x16,
 //                        both operands from shared memory) two tiles ahead,
 //                        and O += P V (P read from tensor memory, V as an
 //                        MN-major operand straight from its row-major pages);
 //                        tcgen05.commit signals the mbarriers.
+//   warp 19 (one thread) TMA store of the finished rows of an item.
 //   warps 0-15           softmax: four threads per row, thread (t, c) owns row t
 //                        and key columns [32c, 32c+32).  S is read from tensor
 //                        memory (tcgen05.ld), scaled, masked (causal, window
@@ -36,7 +39,10 @@
 //                        (tcgen05.st); for bfloat16, on rows that see few keys,
 //                        as two operands P_hi + P_lo (16 significant bits
 //                        together) and twice the PV instructions, because 8-bit
-//                        weights alone miss the 2e-3 bound there.
+//                        weights alone miss the 2e-3 bound there.  O / l of an
+//                        item is written into its (by then idle) query buffer
+//                        one key tile late, behind the first tile of the next
+//                        item, in the layout of a TMA box.
 //
 // Every wait on an mbarrier is bounded; a wait that runs out raises a flag the
 // host reads and the CTA falls through to the common exit, where the tensor
@@ -55,7 +61,7 @@ namespace {
 constexpr int kRows = 128;        // query rows per CTA
 constexpr int kKeys = 128;        // keys per tile
 constexpr int kHd = 128;
-constexpr int kKStages = 3, kVStages = 2;
+constexpr int kKStages = 2, kVStages = 2;
 constexpr int kTileBytes = kRows * kHd * 2;            // 32 KB: one [128][128] 16-bit tile
 constexpr int kHalfBytes = kTileBytes / 2;             // one 64-column block
 constexpr float kLog2e = 1.4426950408889634f;
@@ -70,7 +76,7 @@ constexpr int kTraceRoles = 4, kTraceTiles = 32, kTraceEvents = 12;
 __device__ long long gTrace[kTraceRoles * kTraceTiles * kTraceEvents];
 #define TRACE(role, tile, event)                                                                        \
     do {                                                                                                \
-        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (threadIdx.x & 31) == 0 &&         \
+        if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 &&                                               \
             (role) < kTraceRoles && (tile) < kTraceTiles)                                               \
             s->trace[((role) * kTraceTiles + (tile)) * kTraceEvents + (event)] = clock64();             \
     } while (0)
@@ -80,13 +86,14 @@ __device__ long long gTrace[kTraceRoles * kTraceTiles * kTraceEvents];
 
 struct Smem {
     // tiles first: each 1024-byte aligned (swizzle atoms)
-    unsigned char q[kTileBytes];               // the query tile; reused to stage the output
+    unsigned char q[2][kTileBytes];            // query tiles of two items in flight; each doubles as output staging
     unsigned char k[kKStages][kTileBytes];
     unsigned char v[kVStages][kTileBytes];
-    unsigned long long qFull, kFull[kKStages], kEmpty[kKStages], vFull[kVStages], vEmpty[kVStages];
-    unsigned long long sFull[2], pFull, pvDone;
+    unsigned long long qFull[2], qEmpty[2], kFull[kKStages], kEmpty[kKStages], vFull[kVStages], vEmpty[kVStages];
+    unsigned long long sFull[2], pFull, pvDone, oEmpty[2], oStaged[2];
     unsigned long long maxReady[2], sumReady;  // exchange between the four parts of a row
-    float rowMax[2][4][kRows];                 // [parity][column quarter][row]
+    float rowMax[2][4][kRows];                 // [tile parity][column quarter][row]
+    float rowSum[2][4][kRows];                 // [item parity][column quarter][row]
     uint32_t tmemBase;
     int dead;
 #ifdef PAM_PREFILL_TRACE
@@ -158,6 +165,12 @@ __device__ __forceinline__ void tmaLoad3d(void* dst, const CUtensorMap* map, uns
         "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
         ::"r"(smemAddr(dst)), "l"(map), "r"(smemAddr(bar)), "r"(x), "r"(y), "r"(z)
         : "memory");
+}
+
+__device__ __forceinline__ void tmaStore3d(const CUtensorMap* map, const void* src, int x, int y, int z) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 ::"l"(map), "r"(smemAddr(src)), "r"(x), "r"(y), "r"(z)
+                 : "memory");
 }
 
 // Shared-memory matrix descriptor (128-byte swizzle, descriptor version 1).
@@ -341,14 +354,94 @@ __device__ __forceinline__ float weights32(const uint32_t (&r)[32], uint32_t (&w
 }
 
 constexpr int kSoftmaxThreads = 512;                   // four threads per row
-constexpr int kKProducerWarp = 16, kVProducerWarp = 17, kMmaWarp = 18;
-constexpr int kThreads = kSoftmaxThreads + 96;
+constexpr int kSoftmaxWarps = kSoftmaxThreads / 32;
+constexpr int kKProducerWarp = 16, kVProducerWarp = 17, kMmaWarp = 18, kStoreWarp = 19;
+constexpr int kThreads = kSoftmaxThreads + 128;
+
+// One unit of work: 128 query rows of one head of one sequence.
+struct Item {
+    int head, seq, kvh;
+    int nT, tileLo;          // key tiles tileLo .. tileLo + nT - 1 hold every key a row may see
+    int rowBase, rowsValid;  // first row in q/out, rows that exist
+    int firstPos;            // sequence position of row 0
+    int seqLen, ws;
+    bool useLo;
+    const int32_t* table;
+};
+
+// Work item `w` of the launch.  Items are numbered tile-major with the last (longest)
+// query tiles first and the head running fastest, so that the CTAs working side by side
+// share the keys of one KV head through L2 and the short items fill the end of the launch.
+// Returns false when the sequence has no rows in that tile.
+__device__ __forceinline__ bool loadItem(const PrefillParams& p, int w, int numTiles, Item& it) {
+    const int per = p.numSeqs * p.heads;
+    const int tile = numTiles - 1 - w / per;
+    const int rem = w % per;
+    it.seq = rem / p.heads;
+    it.head = rem % p.heads;
+    const int qLen = prefillMeta(p, 2, it.seq);
+    if (tile * kRows >= qLen) return false;
+    it.kvh = it.head / (p.heads / p.kvHeads);
+    const int qStart = prefillMeta(p, 1, it.seq);
+    it.seqLen = prefillMeta(p, 0, it.seq);
+    it.ws = prefillMeta(p, 4, it.seq);
+    it.rowBase = prefillMeta(p, 3, it.seq) + tile * kRows;
+    it.rowsValid = min(kRows, qLen - tile * kRows);
+    it.firstPos = qStart + tile * kRows;
+    const int lastPos = it.firstPos + it.rowsValid - 1;
+    const int keyEnd = p.causal ? min(it.seqLen, lastPos + 1) : it.seqLen;  // exclusive
+    it.tileLo = it.ws / kKeys;
+    it.nT = keyEnd > it.ws ? (keyEnd - 1) / kKeys - it.tileLo + 1 : 0;
+    // Fewest keys any row of the tile sees.  A bfloat16 weight keeps 8 significant bits; on a
+    // row with few keys (large weights) that alone can cost more than 2e-3 on unit-variance
+    // values, so such tiles carry the weights as two bfloat16 operands (16 bits).  Rows with
+    // hundreds of keys have weights small enough for 8 bits, as in every bfloat16 attention
+    // kernel.  exactWeights: 0 never, 1 short rows, 2 always.
+    const int fewest = p.causal ? it.firstPos + 1 - it.ws : it.seqLen - it.ws;
+    it.useLo = p.exactWeights == 2 || (p.exactWeights == 1 && fewest < kShortRowKeys);
+    it.table = p.tables + static_cast<int64_t>(it.seq) * p.maxNumBlocks;
+    return true;
+}
+
+// Position of a role in the CTA's stream of key tiles: item w, tile j of it, g tiles and
+// n items (with keys) done before.  Every role walks the same stream, so g and n give the
+// stage and the phase parity of every barrier without any communication.
+struct Cursor {
+    int w, j, g, n;
+    bool valid;
+    Item it;
+    __device__ __forceinline__ void seek(const PrefillParams& p, int total, int numTiles) {
+        valid = false;
+        while (w < total) {
+            if (loadItem(p, w, numTiles, it) && it.nT > 0) {
+                valid = true;
+                return;
+            }
+            w += gridDim.x;
+        }
+    }
+    __device__ __forceinline__ void init(const PrefillParams& p, int total, int numTiles) {
+        w = blockIdx.x;
+        j = g = n = 0;
+        seek(p, total, numTiles);
+    }
+    __device__ __forceinline__ void nextTile(const PrefillParams& p, int total, int numTiles) {
+        ++j;
+        ++g;
+        if (j == it.nT) {
+            j = 0;
+            ++n;
+            w += gridDim.x;
+            seek(p, total, numTiles);
+        }
+    }
+};
 
 template <bool BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
-                const __grid_constant__ CUtensorMap mapV, const __grid_constant__ PrefillParams p, float scaleLog2,
-                int* errFlag) {
+                const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapO,
+                const __grid_constant__ PrefillParams p, float scaleLog2, int* errFlag) {
     // Dynamic shared memory starts on a 1024-byte boundary (the swizzle atoms
     // need that); if it ever does not, give up cleanly instead of computing garbage.
     extern __shared__ __align__(1024) unsigned char rawSmem[];
@@ -359,44 +452,32 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     }
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);   // long tiles first
-    const int head = blockIdx.y, seq = blockIdx.z;
-    const int qLen = prefillMeta(p, 2, seq);
-    if (tile * kRows >= qLen) return;
-    if (*reinterpret_cast<volatile int*>(errFlag) != 0) return;       // an earlier CTA gave up: do not pile up waits
-    const int G = p.heads / p.kvHeads, kvh = head / G;
-    const int qStart = prefillMeta(p, 1, seq), seqLen = prefillMeta(p, 0, seq), ws = prefillMeta(p, 4, seq);
-    const int rowBase = prefillMeta(p, 3, seq) + tile * kRows;        // first row of the tile in q/out
-    const int rowsValid = min(kRows, qLen - tile * kRows);
-    const int firstPos = qStart + tile * kRows;                       // sequence position of row 0
-    const int lastPos = firstPos + rowsValid - 1;
-    // Key tiles tileLo .. tileLo + nT - 1 hold every key a row of this tile may see.
-    const int keyEnd = p.causal ? min(seqLen, lastPos + 1) : seqLen;  // exclusive
-    const int tileLo = ws / kKeys;
-    const int nT = keyEnd > ws ? (keyEnd - 1) / kKeys - tileLo + 1 : 0;
-    // Fewest keys any row of the tile sees.  A bfloat16 weight keeps 8 significant bits; on a
-    // row with few keys (large weights) that alone can cost more than 2e-3 on unit-variance
-    // values, so such tiles carry the weights as two bfloat16 operands (16 bits).  Rows with
-    // hundreds of keys have weights small enough for 8 bits, as in every bfloat16 attention
-    // kernel.  exactWeights: 0 never, 1 short rows, 2 always.
-    const int fewest = p.causal ? firstPos + 1 - ws : seqLen - ws;
-    const bool useLo = BF16 && (p.exactWeights == 2 || (p.exactWeights == 1 && fewest < kShortRowKeys));
+    const int numTiles = (p.maxQLen + kRows - 1) / kRows;
+    const int total = numTiles * p.numSeqs * p.heads;
 
     if (threadIdx.x == kKProducerWarp * 32) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(&mapQ) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&mapK) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&mapV) : "memory");
     }
+    if (threadIdx.x == kVProducerWarp * 32) asm volatile("prefetch.tensormap [%0];" ::"l"(&mapV) : "memory");
+    if (threadIdx.x == kStoreWarp * 32) asm volatile("prefetch.tensormap [%0];" ::"l"(&mapO) : "memory");
     TRACE(0, 31, 0);                                   // CTA start (instrumented build)
     if (threadIdx.x == 0) {
-        mbarInit(&s->qFull, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbarInit(&s->qFull[i], 1);
+            mbarInit(&s->qEmpty[i], 1);
+            mbarInit(&s->oEmpty[i], kSoftmaxWarps);
+            mbarInit(&s->oStaged[i], kSoftmaxWarps);
+            mbarInit(&s->sFull[i], 1);
+            mbarInit(&s->maxReady[i], kSoftmaxThreads);
+        }
         for (int i = 0; i < kKStages; ++i) { mbarInit(&s->kFull[i], 1); mbarInit(&s->kEmpty[i], 1); }
         for (int i = 0; i < kVStages; ++i) { mbarInit(&s->vFull[i], 1); mbarInit(&s->vEmpty[i], 1); }
-        for (int i = 0; i < 2; ++i) { mbarInit(&s->sFull[i], 1); mbarInit(&s->maxReady[i], kSoftmaxThreads); }
         mbarInit(&s->pFull, kSoftmaxThreads);
         mbarInit(&s->pvDone, 1);
         mbarInit(&s->sumReady, kSoftmaxThreads);
-        s->dead = 0;
+        // an earlier CTA gave up: do not pile up waits
+        s->dead = *reinterpret_cast<volatile int*>(errFlag) != 0 ? 1 : 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == kMmaWarp) {
@@ -408,50 +489,63 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     tcFenceAfter();
     const uint32_t tmem = s->tmemBase;
     TRACE(0, 31, 1);                                   // barriers and tensor memory ready
-    const uint32_t tmemS[2] = {tmem, tmem + 128u};
-    const uint32_t tmemO = tmem + 256u;
+    // tensor memory columns: S buffers at 0 and 128, accumulators at 256 and 384
+    auto tmemS = [&](int b) { return tmem + 128u * static_cast<uint32_t>(b); };
+    auto tmemO = [&](int b) { return tmem + 256u + 128u * static_cast<uint32_t>(b); };
+    const bool live = *reinterpret_cast<volatile int*>(&s->dead) == 0;
 
     // Row of the pool (block * kv_heads * block_size space) of the 16-token piece `lane`
-    // of key tile j; lanes 0-7 of a producer warp fetch one piece each.
-    const int32_t* table = p.tables + static_cast<int64_t>(seq) * p.maxNumBlocks;
+    // of key tile j of an item; lanes 0-7 of a producer warp fetch one piece each.
     const int tilesPerPage = p.blockSize / 16;
-    auto pieceRow = [&](int j) {
-        const int t16 = (tileLo + j) * (kKeys / 16) + lane;
+    auto pieceRow = [&](const Item& it, int j) {
+        const int t16 = (it.tileLo + j) * (kKeys / 16) + lane;
         const int page = min(t16 / tilesPerPage, p.maxNumBlocks - 1);
-        const int blk = min(max(table[page], 0), p.poolBlocks - 1);
-        return (blk * p.kvHeads + kvh) * p.blockSize + (t16 % tilesPerPage) * 16;
+        const int blk = min(max(it.table[page], 0), p.poolBlocks - 1);
+        return (blk * p.kvHeads + it.kvh) * p.blockSize + (t16 % tilesPerPage) * 16;
     };
 
-    if (warp == kKProducerWarp) {
+    if (!live) {
+        // nothing: fall through to the common exit
+    } else if (warp == kKProducerWarp) {
         // ------------------------------------------------------------ Q and K producer
-        if (nT > 0) {
-            if (lane == 0) {
-                mbarExpectTx(&s->qFull, kTileBytes);
-                tmaLoad3d(s->q, &mapQ, &s->qFull, 0, head, rowBase);
-                tmaLoad3d(s->q + kHalfBytes, &mapQ, &s->qFull, 64, head, rowBase);
-            }
-            bool ok = true;
-            for (int j = 0; j < nT && ok; ++j) {
-                const int st = j % kKStages;
-                const int row = lane < kKeys / 16 ? pieceRow(j) : 0;
-                if (j >= kKStages) ok = mbarWait(&s->kEmpty[st], ((j / kKStages) - 1) & 1, &s->dead, errFlag, 1);
+        Cursor c;
+        c.init(p, total, numTiles);
+        bool ok = true;
+        while (c.valid && ok) {
+            if (c.j == 0) {
+                // the query tile of item n goes into buffer n & 1 once the output of item n - 2 left it
+                const int qb = c.n & 1;
+                if (c.n >= 2) ok = mbarWait(&s->qEmpty[qb], ((c.n >> 1) - 1) & 1, &s->dead, errFlag, 14);
                 ok = __all_sync(0xFFFFFFFFu, ok);
                 if (!ok) break;
-                if (lane == 0) mbarExpectTx(&s->kFull[st], kTileBytes);
-                __syncwarp();
-                if (lane < kKeys / 16) {
-                    tmaLoad2d(s->k[st] + lane * 2048, &mapK, &s->kFull[st], 0, row);
-                    tmaLoad2d(s->k[st] + kHalfBytes + lane * 2048, &mapK, &s->kFull[st], 64, row);
+                if (lane == 0) {
+                    mbarExpectTx(&s->qFull[qb], kTileBytes);
+                    tmaLoad3d(s->q[qb], &mapQ, &s->qFull[qb], 0, c.it.head, c.it.rowBase);
+                    tmaLoad3d(s->q[qb] + kHalfBytes, &mapQ, &s->qFull[qb], 64, c.it.head, c.it.rowBase);
                 }
             }
+            const int st = c.g % kKStages;
+            const int row = lane < kKeys / 16 ? pieceRow(c.it, c.j) : 0;
+            if (c.g >= kKStages) ok = mbarWait(&s->kEmpty[st], ((c.g / kKStages) - 1) & 1, &s->dead, errFlag, 1);
+            ok = __all_sync(0xFFFFFFFFu, ok);
+            if (!ok) break;
+            if (lane == 0) mbarExpectTx(&s->kFull[st], kTileBytes);
+            __syncwarp();
+            if (lane < kKeys / 16) {
+                tmaLoad2d(s->k[st] + lane * 2048, &mapK, &s->kFull[st], 0, row);
+                tmaLoad2d(s->k[st] + kHalfBytes + lane * 2048, &mapK, &s->kFull[st], 64, row);
+            }
+            c.nextTile(p, total, numTiles);
         }
     } else if (warp == kVProducerWarp) {
         // ------------------------------------------------------------ V producer
+        Cursor c;
+        c.init(p, total, numTiles);
         bool ok = true;
-        for (int j = 0; j < nT && ok; ++j) {
-            const int st = j % kVStages;
-            const int row = lane < kKeys / 16 ? pieceRow(j) : 0;
-            if (j >= kVStages) ok = mbarWait(&s->vEmpty[st], ((j / kVStages) - 1) & 1, &s->dead, errFlag, 13);
+        while (c.valid && ok) {
+            const int st = c.g % kVStages;
+            const int row = lane < kKeys / 16 ? pieceRow(c.it, c.j) : 0;
+            if (c.g >= kVStages) ok = mbarWait(&s->vEmpty[st], ((c.g / kVStages) - 1) & 1, &s->dead, errFlag, 13);
             ok = __all_sync(0xFFFFFFFFu, ok);
             if (!ok) break;
             if (lane == 0) mbarExpectTx(&s->vFull[st], kTileBytes);
@@ -460,12 +554,15 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 tmaLoad2d(s->v[st] + lane * 2048, &mapV, &s->vFull[st], 0, row);
                 tmaLoad2d(s->v[st] + kHalfBytes + lane * 2048, &mapV, &s->vFull[st], 64, row);
             }
+            c.nextTile(p, total, numTiles);
         }
     } else if (warp == kMmaWarp) {
         // ------------------------------------------------------------ MMA issuer
-        // Tensor-core instructions of one thread execute in issue order: S of tile j+2 is
-        // written over P of tile j right behind P V of tile j without a wait in between.
-        if (lane == 0 && nT > 0) {
+        // Tensor-core instructions of one thread execute in issue order: S of tile g+2 is
+        // written over P of tile g right behind P V of tile g without a wait in between.
+        // The S products run two tiles ahead of the P V products, across item boundaries:
+        // while the softmax warps write out one item, S of the next is already there.
+        if (lane == 0) {
             const uint32_t fmt = BF16 ? 1u : 0u;
             // D = f32, A/B = bf16|f16, M = 128, N = 128; B of the second product is MN-major.
             const uint32_t idescS = (1u << 4) | (fmt << 7) | (fmt << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
@@ -473,191 +570,281 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             // the hardware (illegal instruction), the two operands must agree.
             const uint32_t idescO = idescS | (1u << 16);
             const uint32_t hiK = descHi(1024);                      // K-major tiles and the MN-major V tile share it
-            const uint32_t qLo = descLo(smemAddr(s->q), 16);
-            bool ok = mbarWait(&s->qFull, 0, &s->dead, errFlag, 2);
-            auto issueQK = [&](int j) {
-                const int st = j % kKStages;
-                ok = mbarWait(&s->kFull[st], (j / kKStages) & 1, &s->dead, errFlag, 3);
+            bool ok = true;
+            Cursor qk, pv;
+            qk.init(p, total, numTiles);
+            pv = qk;
+            auto issueQK = [&]() {
+                const int st = qk.g % kKStages, qb = qk.n & 1;
+                if (qk.j == 0) ok = mbarWait(&s->qFull[qb], (qk.n >> 1) & 1, &s->dead, errFlag, 2);
+                if (ok) ok = mbarWait(&s->kFull[st], (qk.g / kKStages) & 1, &s->dead, errFlag, 3);
                 if (!ok) return;
                 tcFenceAfter();
+                const uint32_t qLo = descLo(smemAddr(s->q[qb]), 16);
                 const uint32_t kLo = descLo(smemAddr(s->k[st]), 16);
 #pragma unroll
                 for (int ks = 0; ks < kHd / 16; ++ks) {
                     const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
-                    umma(tmemS[j & 1], desc64(qLo + off, hiK), desc64(kLo + off, hiK), idescS, ks > 0);
+                    umma(tmemS(qk.g & 1), desc64(qLo + off, hiK), desc64(kLo + off, hiK), idescS, ks > 0);
                 }
-                ummaCommit(&s->sFull[j & 1]);
+                ummaCommit(&s->sFull[qk.g & 1]);
                 ummaCommit(&s->kEmpty[st]);
-                TRACE(2, j, 3);
+                TRACE(2, qk.g, 3);
+                qk.nextTile(p, total, numTiles);
             };
-            if (ok) issueQK(0);
-            if (ok && nT > 1) issueQK(1);
-            for (int j = 0; j < nT && ok; ++j) {
-                const int st = j % kVStages;
-                TRACE(2, j, 0);
-                ok = mbarWait(&s->pFull, j & 1, &s->dead, errFlag, 5);
-                if (ok) ok = mbarWait(&s->vFull[st], (j / kVStages) & 1, &s->dead, errFlag, 6);
+            if (qk.valid) issueQK();
+            if (ok && qk.valid) issueQK();
+            while (pv.valid && ok) {
+                const int st = pv.g % kVStages, ob = pv.n & 1;
+                TRACE(2, pv.g, 0);
+                ok = mbarWait(&s->pFull, pv.g & 1, &s->dead, errFlag, 5);
+                if (ok) ok = mbarWait(&s->vFull[st], (pv.g / kVStages) & 1, &s->dead, errFlag, 6);
+                // the accumulator of item n is free once the output of item n - 2 was read from it
+                if (ok && pv.j == 0 && pv.n >= 2) ok = mbarWait(&s->oEmpty[ob], ((pv.n >> 1) - 1) & 1, &s->dead, errFlag, 15);
                 if (!ok) break;
                 tcFenceAfter();
-                TRACE(2, j, 1);
+                TRACE(2, pv.g, 1);
                 const uint32_t vLo = descLo(smemAddr(s->v[st]), kHalfBytes);
+                const uint32_t sCol = tmemS(pv.g & 1);
                 // P of keys 32c .. 32c+31 sits in columns 32c .. 32c+15 (and, with the low-order
                 // pass, its remainder in columns 32c+16 .. 32c+31) of the S buffer
 #pragma unroll
                 for (int ks = 0; ks < kKeys / 16; ++ks) {
-                    const uint32_t pCol = tmemS[j & 1] + 32u * (ks >> 1) + 8u * (ks & 1);
-                    ummaTs(tmemO, pCol, desc64(vLo + ks * 128, hiK), idescO, (j > 0 || ks > 0) ? 1u : 0u);
+                    const uint32_t pCol = sCol + 32u * (ks >> 1) + 8u * (ks & 1);
+                    ummaTs(tmemO(ob), pCol, desc64(vLo + ks * 128, hiK), idescO, (pv.j > 0 || ks > 0) ? 1u : 0u);
                 }
-                if (useLo) {
+                if (BF16 && pv.it.useLo) {
 #pragma unroll
                     for (int ks = 0; ks < kKeys / 16; ++ks) {
-                        const uint32_t pCol = tmemS[j & 1] + 32u * (ks >> 1) + 8u * (ks & 1) + 16u;
-                        ummaTs(tmemO, pCol, desc64(vLo + ks * 128, hiK), idescO, 1u);
+                        const uint32_t pCol = sCol + 32u * (ks >> 1) + 8u * (ks & 1) + 16u;
+                        ummaTs(tmemO(ob), pCol, desc64(vLo + ks * 128, hiK), idescO, 1u);
                     }
                 }
                 ummaCommit(&s->pvDone);
                 ummaCommit(&s->vEmpty[st]);
-                TRACE(2, j, 2);
-                if (j + 2 < nT) issueQK(j + 2);
+                TRACE(2, pv.g, 2);
+                pv.nextTile(p, total, numTiles);
+                if (qk.valid) issueQK();
             }
         }
+    } else if (warp == kStoreWarp) {
+        // ------------------------------------------------------------ output store
+        // The softmax warps leave the finished rows of item n in its query buffer, in the
+        // swizzled layout of a TMA box; one thread sends them to global memory and hands
+        // the buffer back to the producer once the copy has read it.  Tiles with fewer
+        // than 128 rows of this sequence were written by the softmax warps themselves (a
+        // box would run into the next sequence's rows).
+        int n = 0;
+        bool ok = true;
+        for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
+            Item it;
+            if (!loadItem(p, w, numTiles, it) || it.nT == 0) continue;
+            const int qb = n & 1;
+            ok = mbarWait(&s->oStaged[qb], (n >> 1) & 1, &s->dead, errFlag, 16);
+            ok = __all_sync(0xFFFFFFFFu, ok);
+            if (!ok) break;
+            if (lane == 0) {
+                if (it.rowsValid == kRows) {
+                    tmaStore3d(&mapO, s->q[qb], 0, it.head, it.rowBase);
+                    tmaStore3d(&mapO, s->q[qb] + kHalfBytes, 64, it.head, it.rowBase);
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                }
+                mbarArrive(&s->qEmpty[qb]);
+            }
+            ++n;
+        }
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     } else {
         // ------------------------------------------------------------ softmax warps
         // Thread (t, cq): row t, key columns [32cq, 32cq + 32) of every key tile and output
         // columns [32cq, 32cq + 32).  Warps w, w+4, w+8, w+12 share the tensor-memory lanes
         // 32(w&3) .. +31 (a warp may only touch the lane quarter of its index modulo 4).
         const int cq = warp >> 2, t = (warp & 3) * 32 + lane;
-        const int rowPos = firstPos + t;
         const uint32_t laneBase = static_cast<uint32_t>((warp & 3) * 32) << 16;
-        const uint32_t oBase = tmemO + laneBase + 32u * cq;
-        const MaskInfo mk(ws, seqLen, rowPos, p.causal);
-        float mUsed = -INFINITY, l = 0.f;
+        const int rowLo = (warp & 3) * 32;
+        int g = 0, n = 0;                               // key tiles and items (with keys) done so far
         bool ok = true;
-        for (int j = 0; j < nT && ok; ++j) {
-            const int b = j & 1;
-            const int k0 = (tileLo + j) * kKeys;
-            const int kq = k0 + 32 * cq;                                    // first key of this thread's columns
-            const uint32_t sBase = tmemS[b] + laneBase + 32u * cq;
-            const bool edge = k0 < ws || k0 + kKeys > seqLen || (p.causal && k0 + kKeys - 1 > firstPos);
-            TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), j, 0);
-            ok = mbarWait(&s->sFull[b], (j >> 1) & 1, &s->dead, errFlag, 7);
-            if (!ok) break;
+        // The output of an item is written one key tile late, behind the first tile of the next
+        // item: its last P V product has finished by then, and the tensor pipe has the next
+        // item's products to work on meanwhile.
+        bool pend = false;
+        int pendRowBase = 0, pendRowsValid = 0, pendHead = 0;
+        // O / l of item pn (whose last P V product is known to be complete) into its query
+        // buffer, in the layout of the two TMA boxes: [half][row][8 chunks of 16 bytes, chunk
+        // index XOR row % 8].
+        auto writeOut = [&](int pn, int rowBase, int rowsValid, int head) {
+            if (!mbarWait(&s->sumReady, pn & 1, &s->dead, errFlag, 12)) return false;
             tcFenceAfter();
-            TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), j, 1);
-            uint32_t r[32];
-            tmemLd32(sBase, r);
-            TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), j, 4);
-            // maximum of the raw scores of this quarter row (the scale is positive)
-            float tmax = (edge ? quarterRowMax<true>(r, mk, kq) : quarterRowMax<false>(r, mk, kq)) * scaleLog2;
-            s->rowMax[b][cq][t] = tmax;
-            mbarArrive(&s->maxReady[b]);
-            TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), j, 5);
-            ok = mbarWait(&s->maxReady[b], (j >> 1) & 1, &s->dead, errFlag, 11);
-            if (!ok) break;
-            tmax = fmaxf(fmaxf(s->rowMax[b][0][t], s->rowMax[b][1][t]), fmaxf(s->rowMax[b][2][t], s->rowMax[b][3][t]));
-            TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), j, 2);
-            bool raise = false;
-            float corr = 1.f;
-            if (j == 0) mUsed = tmax;
-            else if (tmax > mUsed + kRescaleThreshold) {
-                raise = true;
-                corr = ex2Approx(mUsed - tmax);
-                mUsed = tmax;
-            }
-            if (j >= 1 && __any_sync(0xFFFFFFFFu, raise)) {
-                // O is still being added to by P V of tile j-1: wait for it, then rescale
-                ok = mbarWait(&s->pvDone, (j - 1) & 1, &s->dead, errFlag, 8);
-                if (!ok) break;
-                tcFenceAfter();
-                uint32_t o[32];
-                tmemLd32(oBase, o);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
-                tmemSt32(oBase, o);
-                l *= corr;
-            }
-            // the weights replace the scores in tensor memory: 16 columns of packed pairs
-            // (plus 16 columns of their low-order parts where the tile needs 16-bit weights)
-            const float negM = mUsed == -INFINITY ? 0.f : -mUsed;
-            uint32_t w[32];
-            if (useLo) {
-                l += edge ? weights32<BF16, true, true>(r, w, scaleLog2, negM, mk, kq)
-                          : weights32<BF16, true, false>(r, w, scaleLog2, negM, mk, kq);
-                tmemSt32(sBase, w);
-            } else {
-                l += edge ? weights32<BF16, false, true>(r, w, scaleLog2, negM, mk, kq)
-                          : weights32<BF16, false, false>(r, w, scaleLog2, negM, mk, kq);
-                tmemSt16(sBase, w);
-            }
-            tmemStWait();
-            TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), j, 10);
-            if (k0 + kKeys > seqLen) {
-                // rows of V past the end of the sequence may hold anything: zero them
-                const int st = j % kVStages;
-                ok = mbarWait(&s->vFull[st], (j / kVStages) & 1, &s->dead, errFlag, 9);
-                if (!ok) break;
-                if (k0 + t >= seqLen) {
-#pragma unroll
-                    for (int c16 = 0; c16 < 4; ++c16)
-                        *reinterpret_cast<uint4*>(s->v[st] + (cq >> 1) * kHalfBytes + t * 128 + ((cq & 1) * 4 + c16) * 16) =
-                            make_uint4(0u, 0u, 0u, 0u);
-                }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            }
-            tcFenceBefore();
-            mbarArrive(&s->pFull);
-            TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), j, 3);
-        }
-        // epilogue: O / l to global memory
-        if (ok) {
-            s->rowMax[nT & 1][cq][t] = l;            // the buffer the last tile did not use
-            mbarArrive(&s->sumReady);
-            ok = mbarWait(&s->sumReady, 0, &s->dead, errFlag, 12);
-        }
-        if (ok && nT > 0) ok = mbarWait(&s->pvDone, (nT - 1) & 1, &s->dead, errFlag, 10);
-        TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), 31, 2);   // last PV done
-        if (ok) {
-            tcFenceAfter();
-            const float lt = (s->rowMax[nT & 1][0][t] + s->rowMax[nT & 1][1][t]) + (s->rowMax[nT & 1][2][t] + s->rowMax[nT & 1][3][t]);
-            const float inv = (nT > 0 && lt > 0.f) ? 1.f / lt : 0.f;
-            // The Q tile is no longer read: stage this warp's 32 rows x 64 bytes there (16-byte
-            // chunks XOR-swizzled by row), then write them out eight rows per instruction,
-            // 64 contiguous bytes per row.
-            unsigned char* stage = s->q;
+            const float lt = (s->rowSum[pn & 1][0][t] + s->rowSum[pn & 1][1][t]) + (s->rowSum[pn & 1][2][t] + s->rowSum[pn & 1][3][t]);
+            const float inv = lt > 0.f ? 1.f / lt : 0.f;
+            unsigned char* stage = s->q[pn & 1] + (cq >> 1) * kHalfBytes;
             uint32_t o[32];
-            if (nT > 0) tmemLd32(oBase, o);
+            tmemLd32(tmemO(pn & 1) + laneBase + 32u * cq, o);
+            tcFenceBefore();
 #pragma unroll
             for (int q4 = 0; q4 < 4; ++q4) {
                 uint32_t wv[4];
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float a = nT > 0 ? __uint_as_float(o[8 * q4 + 2 * e]) * inv : 0.f;
-                    const float bb = nT > 0 ? __uint_as_float(o[8 * q4 + 2 * e + 1]) * inv : 0.f;
-                    wv[e] = pack16<BF16>(a, bb);
-                }
-                *reinterpret_cast<uint4*>(stage + t * 256 + (((cq * 4 + q4) ^ (t & 7)) << 4)) =
+                for (int e = 0; e < 4; ++e)
+                    wv[e] = pack16<BF16>(__uint_as_float(o[8 * q4 + 2 * e]) * inv, __uint_as_float(o[8 * q4 + 2 * e + 1]) * inv);
+                *reinterpret_cast<uint4*>(stage + t * 128 + ((((cq & 1) * 4 + q4) ^ (t & 7)) << 4)) =
                     make_uint4(wv[0], wv[1], wv[2], wv[3]);
             }
-            __syncwarp();
-            const int rowLo = (warp & 3) * 32;
+            if (rowsValid < kRows) {
+                // ragged tile: this warp writes its own 32 rows x 64 bytes, eight rows per instruction
+                __syncwarp();
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int row = rowLo + 8 * i + (lane >> 2), chunk = cq * 4 + (lane & 3);
-                if (row < rowsValid) {
-                    const uint4 v = *reinterpret_cast<const uint4*>(stage + row * 256 + ((chunk ^ (row & 7)) << 4));
-                    unsigned char* out = static_cast<unsigned char*>(p.out) +
-                                         ((static_cast<int64_t>(rowBase) + row) * p.heads + head) * kHd * 2;
-                    *reinterpret_cast<uint4*>(out + chunk * 16) = v;
+                for (int i = 0; i < 4; ++i) {
+                    const int row = rowLo + 8 * i + (lane >> 2), chunk = (cq & 1) * 4 + (lane & 3);
+                    if (row < rowsValid) {
+                        const uint4 v = *reinterpret_cast<const uint4*>(stage + row * 128 + ((chunk ^ (row & 7)) << 4));
+                        unsigned char* out = static_cast<unsigned char*>(p.out) +
+                                             ((static_cast<int64_t>(rowBase) + row) * p.heads + head) * kHd * 2;
+                        *reinterpret_cast<uint4*>(out + (cq * 4 + (lane & 3)) * 16) = v;
+                    }
                 }
             }
+            // the buffer is next read (TMA store) and written (TMA load) by the asynchronous proxy
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+                mbarArrive(&s->oEmpty[pn & 1]);            // the accumulator may be overwritten
+                mbarArrive(&s->oStaged[pn & 1]);
+            }
+            return true;
+        };
+        for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
+            Item it;
+            if (!loadItem(p, w, numTiles, it)) continue;
+            if (it.nT == 0) {
+                // rows that see no key at all: zeros (no other role takes part)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int row = rowLo + 8 * i + (lane >> 2), chunk = cq * 4 + (lane & 3);
+                    if (row < it.rowsValid) {
+                        unsigned char* out = static_cast<unsigned char*>(p.out) +
+                                             ((static_cast<int64_t>(it.rowBase) + row) * p.heads + it.head) * kHd * 2;
+                        *reinterpret_cast<uint4*>(out + chunk * 16) = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                }
+                continue;
+            }
+            const uint32_t oBase = tmemO(n & 1) + laneBase + 32u * cq;
+            const MaskInfo mk(it.ws, it.seqLen, it.firstPos + t, p.causal);
+            const bool useLo = BF16 && it.useLo;
+            float mUsed = -INFINITY, l = 0.f;
+            for (int j = 0; j < it.nT && ok; ++j, ++g) {
+                const int b = g & 1;
+                const int k0 = (it.tileLo + j) * kKeys;
+                const int kq = k0 + 32 * cq;                                    // first key of this thread's columns
+                const uint32_t sBase = tmemS(b) + laneBase + 32u * cq;
+                const bool edge = k0 < it.ws || k0 + kKeys > it.seqLen || (p.causal && k0 + kKeys - 1 > it.firstPos);
+                TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), g, 0);
+                ok = mbarWait(&s->sFull[b], (g >> 1) & 1, &s->dead, errFlag, 7);
+                if (!ok) break;
+                tcFenceAfter();
+                TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), g, 1);
+                uint32_t r[32];
+                tmemLd32(sBase, r);
+                TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), g, 4);
+                // maximum of the raw scores of this quarter row (the scale is positive)
+                float tmax = (edge ? quarterRowMax<true>(r, mk, kq) : quarterRowMax<false>(r, mk, kq)) * scaleLog2;
+                s->rowMax[b][cq][t] = tmax;
+                mbarArrive(&s->maxReady[b]);
+                TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), g, 5);
+                ok = mbarWait(&s->maxReady[b], (g >> 1) & 1, &s->dead, errFlag, 11);
+                if (!ok) break;
+                tmax = fmaxf(fmaxf(s->rowMax[b][0][t], s->rowMax[b][1][t]), fmaxf(s->rowMax[b][2][t], s->rowMax[b][3][t]));
+                TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), g, 2);
+                bool raise = false;
+                float corr = 1.f;
+                if (j == 0) mUsed = tmax;
+                else if (tmax > mUsed + kRescaleThreshold) {
+                    raise = true;
+                    corr = ex2Approx(mUsed - tmax);
+                    mUsed = tmax;
+                }
+                if (j >= 1 && __any_sync(0xFFFFFFFFu, raise)) {
+                    // O is still being added to by P V of the tile before: wait for it, then rescale
+                    ok = mbarWait(&s->pvDone, (g - 1) & 1, &s->dead, errFlag, 8);
+                    if (!ok) break;
+                    tcFenceAfter();
+                    uint32_t o[32];
+                    tmemLd32(oBase, o);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+                    tmemSt32(oBase, o);
+                    l *= corr;
+                }
+                // the weights replace the scores in tensor memory: 16 columns of packed pairs
+                // (plus 16 columns of their low-order parts where the tile needs 16-bit weights)
+                const float negM = mUsed == -INFINITY ? 0.f : -mUsed;
+                TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), g, 7);
+                uint32_t wgt[32];
+                if (useLo) {
+                    l += edge ? weights32<BF16, true, true>(r, wgt, scaleLog2, negM, mk, kq)
+                              : weights32<BF16, true, false>(r, wgt, scaleLog2, negM, mk, kq);
+                    tmemSt32(sBase, wgt);
+                } else {
+                    l += edge ? weights32<BF16, false, true>(r, wgt, scaleLog2, negM, mk, kq)
+                              : weights32<BF16, false, false>(r, wgt, scaleLog2, negM, mk, kq);
+                    TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), g, 8);
+                    tmemSt16(sBase, wgt);
+                }
+                TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), g, 9);
+                tmemStWait();
+                TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), g, 10);
+                if (k0 + kKeys > it.seqLen) {
+                    // rows of V past the end of the sequence may hold anything: zero them
+                    const int st = g % kVStages;
+                    ok = mbarWait(&s->vFull[st], (g / kVStages) & 1, &s->dead, errFlag, 9);
+                    if (!ok) break;
+                    if (k0 + t >= it.seqLen) {
+#pragma unroll
+                        for (int c16 = 0; c16 < 4; ++c16)
+                            *reinterpret_cast<uint4*>(s->v[st] + (cq >> 1) * kHalfBytes + t * 128 + ((cq & 1) * 4 + c16) * 16) =
+                                make_uint4(0u, 0u, 0u, 0u);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                }
+                const bool flush = pend && j == 0;
+                // The last P V of the item before must be seen complete before this thread lets
+                // the next one start: the barrier's phase parity is only good for one step back.
+                if (flush) {
+                    ok = mbarWait(&s->pvDone, (g - 1) & 1, &s->dead, errFlag, 10);
+                    if (!ok) break;
+                }
+                tcFenceBefore();
+                mbarArrive(&s->pFull);
+                TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), g, 3);
+                if (flush) {
+                    pend = false;
+                    ok = writeOut(n - 1, pendRowBase, pendRowsValid, pendHead);
+                    TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), g, 6);
+                }
+            }
+            if (!ok) break;
+            // the four parts of a row add up their sums through shared memory (one buffer per
+            // item parity: a thread can be at most one item ahead of the slowest)
+            s->rowSum[n & 1][cq][t] = l;
+            mbarArrive(&s->sumReady);
+            pend = true;
+            pendRowBase = it.rowBase;
+            pendRowsValid = it.rowsValid;
+            pendHead = it.head;
+            ++n;
+        }
+        if (ok && pend) {
+            ok = mbarWait(&s->pvDone, (g - 1) & 1, &s->dead, errFlag, 10);
+            if (ok) writeOut(n - 1, pendRowBase, pendRowsValid, pendHead);
         }
     }
 
-    TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), 31, 3);       // output stored
     tcFenceBefore();
     __syncthreads();
 #ifdef PAM_PREFILL_TRACE
-    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0)
+    if (blockIdx.x == 0)
         for (int i = threadIdx.x; i < kTraceRoles * kTraceTiles * kTraceEvents; i += kThreads) gTrace[i] = s->trace[i];
 #endif
     if (warp == kMmaWarp) {
@@ -697,14 +884,14 @@ cudaError_t launchPrefillTensor(const PrefillParams& p, int totalRows, int* errF
     EncodeFn encode = encodeFn();
     if (!encode) return cudaErrorNotSupported;
     const CUtensorMapDataType dt = p.dtype == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    CUtensorMap mapQ, mapK, mapV;
-    {
-        // Q: [rows][heads][128]; a box is 64 dims x 1 head x 128 rows
+    CUtensorMap mapQ, mapK, mapV, mapO;
+    for (int which = 0; which < 2; ++which) {
+        // Q and the output: [rows][heads][128]; a box is 64 dims x 1 head x 128 rows
         cuuint64_t dims[3] = {static_cast<cuuint64_t>(kHd), static_cast<cuuint64_t>(p.heads), static_cast<cuuint64_t>(totalRows)};
         cuuint64_t strides[2] = {static_cast<cuuint64_t>(kHd) * 2, static_cast<cuuint64_t>(p.heads) * kHd * 2};
         cuuint32_t box[3] = {64, 1, static_cast<cuuint32_t>(kRows)};
         cuuint32_t es[3] = {1, 1, 1};
-        if (encode(&mapQ, dt, 3, const_cast<void*>(p.q), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+        if (encode(which ? &mapO : &mapQ, dt, 3, which ? p.out : const_cast<void*>(p.q), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return cudaErrorInvalidValue;
     }
@@ -722,16 +909,22 @@ cudaError_t launchPrefillTensor(const PrefillParams& p, int totalRows, int* errF
     }
     const size_t smem = sizeof(Smem);
     const float scaleLog2 = (1.0f / sqrtf(static_cast<float>(p.headDim))) * kLog2e;
-    dim3 grid(static_cast<unsigned>((p.maxQLen + kRows - 1) / kRows), static_cast<unsigned>(p.heads), static_cast<unsigned>(p.numSeqs));
-    cudaError_t e;
+    // One resident CTA per multiprocessor walks the work items round robin.
+    int dev = 0, sms = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return e;
+    const long long items = static_cast<long long>((p.maxQLen + kRows - 1) / kRows) * p.heads * p.numSeqs;
+    if (items <= 0 || items > 0x7FFFFFFF) return cudaErrorInvalidValue;
+    dim3 grid(static_cast<unsigned>(items < sms ? items : sms));
     if (p.dtype == kBF16) {
         e = cudaFuncSetAttribute(prefillTcKernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (e != cudaSuccess) return e;
-        prefillTcKernel<true><<<grid, kThreads, smem, stream>>>(mapQ, mapK, mapV, p, scaleLog2, errFlag);
+        prefillTcKernel<true><<<grid, kThreads, smem, stream>>>(mapQ, mapK, mapV, mapO, p, scaleLog2, errFlag);
     } else {
         e = cudaFuncSetAttribute(prefillTcKernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (e != cudaSuccess) return e;
-        prefillTcKernel<false><<<grid, kThreads, smem, stream>>>(mapQ, mapK, mapV, p, scaleLog2, errFlag);
+        prefillTcKernel<false><<<grid, kThreads, smem, stream>>>(mapQ, mapK, mapV, mapO, p, scaleLog2, errFlag);
     }
     if (launches) *launches += 1;
     return cudaGetLastError();
