@@ -313,6 +313,7 @@ def run_ours(args):
         engine.decode(req)
     e1.record(stream)
     barrier()
+    engine.synchronize()        # raises if a kernel of the timed region reported an error
     ms_total = max_over_ranks(e0.elapsed_time(e1))
     ms_step = ms_total / args.steps
     engine.setAsync(False)
@@ -455,6 +456,7 @@ def run_prefill(args):
         step()
     e1.record(stream)
     torch.cuda.synchronize(dev)
+    engine.synchronize()        # raises if a kernel of the timed region reported an error
     ms_step = e0.elapsed_time(e1) / args.steps
     launches = engine.kernelLaunches - launches0
     clocks = sampler.stop()
@@ -577,6 +579,7 @@ def run_decode_fp8(args):
         engine.decode(req)
     e1.record(stream)
     torch.cuda.synchronize(dev)
+    engine.synchronize()        # raises if a kernel of the timed region reported an error
     ms_step = e0.elapsed_time(e1) / args.steps
     launches = engine.kernelLaunches - launches0
     clocks = sampler.stop()

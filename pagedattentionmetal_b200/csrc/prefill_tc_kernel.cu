@@ -9,40 +9,41 @@
 //
 // The kernel is persistent: one CTA per multiprocessor walks the work items
 // (128 query rows of one head of one sequence) round robin, longest items
-// first.  An item walks the key tiles (128 keys each) its rows can see.
-// Tensor memory holds two S buffers (128 columns each, overwritten in place by
-// the weights P) and two accumulators O (128 columns each, alternating between
-// items): while the softmax warps turn S of tile g into P, the tensor pipe
-// finishes P V of tile g-1 and Q K^T of tile g+1, across item boundaries.
+// first.  An item walks the key tiles (128 keys each) its rows can see; the
+// tiles go alternately to two softmax groups, each with its own S buffer and
+// accumulator O in tensor memory (4 x 128 columns), so that one group turns S
+// into the weights P while the tensor pipe works for the other.  The two
+// accumulators are merged (log-sum-exp) when the item is written out.
 //
-//   warp 16              TMA producer of Q (two buffers, one per item in flight)
-//                        and of K: per key tile 8 pages (each 16 rows x 256 B,
-//                        fetched as two 128-byte-swizzled boxes, one page per
-//                        lane) into a ring; completion on mbarriers.
-//   warp 17              TMA producer of V, its own ring.
-//   warp 18 (one thread) MMA issuer: S = Q K^T (8 x tcgen05.mma 128x128x16,
-//                        both operands from shared memory) two tiles ahead,
-//                        and O += P V (P read from tensor memory, V as an
-//                        MN-major operand straight from its row-major pages);
-//                        tcgen05.commit signals the mbarriers.
-//   warp 19 (one thread) TMA store of the finished rows of an item.
-//   warps 0-15           softmax: four threads per row, thread (t, c) owns row t
-//                        and key columns [32c, 32c+32).  S is read from tensor
-//                        memory (tcgen05.ld), scaled, masked (causal, window
-//                        start, sequence end) only on edge tiles; the four
-//                        parts of a row exchange their maxima through shared
-//                        memory.  The running maximum is only raised when it
+//   warps 0-3, 4-7       softmax groups 0 and 1: thread t of a group owns query
+//                        row t, all 128 key columns of a tile, in registers (no
+//                        exchange between threads).  Scores are scaled, masked
+//                        (causal, window start, sequence end) only on edge
+//                        tiles.  The running maximum is only raised when it
 //                        grows by more than 2^8 (the result is exact either
 //                        way, the final division uses the same reference), in
 //                        which case O is rescaled in tensor memory.  The
-//                        weights go back to tensor memory in the cache type
-//                        (tcgen05.st); for bfloat16, on rows that see few keys,
-//                        as two operands P_hi + P_lo (16 significant bits
-//                        together) and twice the PV instructions, because 8-bit
-//                        weights alone miss the 2e-3 bound there.  O / l of an
-//                        item is written into its (by then idle) query buffer
-//                        one key tile late, behind the first tile of the next
-//                        item, in the layout of a TMA box.
+//                        weights go back to tensor memory over the scores, in
+//                        the cache type (tcgen05.st); for bfloat16, on rows that
+//                        see few keys, as two operands P_hi + P_lo (16
+//                        significant bits together) and twice the PV
+//                        instructions, because 8-bit weights alone miss the
+//                        2e-3 bound there.  The merged O / l of an item is
+//                        staged in its (by then idle) query buffer in the
+//                        layout of a TMA box.
+//   warp 8               TMA producer of Q (two buffers, one per item in flight)
+//                        and of K: per key tile 8 pages (each 16 rows x 256 B,
+//                        fetched as two 128-byte-swizzled boxes, one page per
+//                        lane) into a ring; completion on mbarriers.
+//   warp 9               TMA producer of V, its own ring.
+//   warp 10              MMA issuer (one elected lane): S = Q K^T (8 x
+//                        tcgen05.mma 128x128x16, both operands from shared
+//                        memory) and O += P V (P read from tensor memory, V as
+//                        an MN-major operand straight from its row-major
+//                        pages); tcgen05.commit signals the mbarriers.
+//   warp 11              TMA store of the finished rows of an item.
+//
+// The service warps hand registers to the softmax warps (setmaxnreg).
 //
 // Every wait on an mbarrier is bounded; a wait that runs out raises a flag the
 // host reads and the CTA falls through to the common exit, where the tensor
@@ -61,7 +62,7 @@ namespace {
 constexpr int kRows = 128;        // query rows per CTA
 constexpr int kKeys = 128;        // keys per tile
 constexpr int kHd = 128;
-constexpr int kKStages = 2, kVStages = 2;
+constexpr int kKStages = 3, kVStages = 2;
 constexpr int kTileBytes = kRows * kHd * 2;            // 32 KB: one [128][128] 16-bit tile
 constexpr int kHalfBytes = kTileBytes / 2;             // one 64-column block
 constexpr float kLog2e = 1.4426950408889634f;
@@ -70,15 +71,19 @@ constexpr int kShortRowKeys = 256;
 constexpr long long kWaitCycles = 400000000LL;         // ~0.2 s
 
 #ifdef PAM_PREFILL_TRACE
-// Instrumented build only: CTA (0,0,0) keeps clock stamps [role][tile][event] in
-// shared memory (no global traffic while it runs) and dumps them at the end.
+// Instrumented build only: CTA 0 leaves clock stamps [role][tile][event] in global memory.
 constexpr int kTraceRoles = 4, kTraceTiles = 32, kTraceEvents = 12;
 __device__ long long gTrace[kTraceRoles * kTraceTiles * kTraceEvents];
+__device__ unsigned long long gCtaTimes[4 * 256];      // start and end of every CTA: nanoseconds, then SM cycles
+__device__ __forceinline__ unsigned long long globalTimerNs() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 #define TRACE(role, tile, event)                                                                        \
     do {                                                                                                \
-        if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 &&                                               \
-            (role) < kTraceRoles && (tile) < kTraceTiles)                                               \
-            s->trace[((role) * kTraceTiles + (tile)) * kTraceEvents + (event)] = clock64();             \
+        if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (role) < kTraceRoles && (tile) < kTraceTiles) \
+            gTrace[((role) * kTraceTiles + (tile)) * kTraceEvents + (event)] = clock64();               \
     } while (0)
 #else
 #define TRACE(role, tile, event)
@@ -90,16 +95,15 @@ struct Smem {
     unsigned char k[kKStages][kTileBytes];
     unsigned char v[kVStages][kTileBytes];
     unsigned long long qFull[2], qEmpty[2], kFull[kKStages], kEmpty[kKStages], vFull[kVStages], vEmpty[kVStages];
-    unsigned long long sFull[2], pFull, pvDone, oEmpty[2], oStaged[2];
-    unsigned long long maxReady[2], sumReady;  // exchange between the four parts of a row
-    float rowMax[2][4][kRows];                 // [tile parity][column quarter][row]
-    float rowSum[2][4][kRows];                 // [item parity][column quarter][row]
+    unsigned long long sFull[2], pFull[2], pvDone[2];   // one of each per softmax group
+    unsigned long long oEmpty, oStaged[2];
+    unsigned long long stateReady, stateRead;  // the two softmax groups meet twice per item
+    float2 rowState[2][kRows];                 // [group][row]: reference maximum and sum of weights of an item
     uint32_t tmemBase;
     int dead;
-#ifdef PAM_PREFILL_TRACE
-    long long trace[kTraceRoles * kTraceTiles * kTraceEvents];
-#endif
 };
+
+static_assert(sizeof(Smem) <= 227 * 1024, "the CTA's shared memory must fit the 227 KB a block may opt into");
 
 __device__ __forceinline__ uint32_t smemAddr(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -217,6 +221,16 @@ __device__ __forceinline__ void ummaTs(uint32_t tmemD, uint32_t tmemA, uint64_t 
         ::"r"(tmemD), "r"(tmemA), "l"(descB), "r"(idesc), "r"(accumulate), "r"(0u)
         : "memory");
 }
+// True in exactly one lane of a converged warp.
+__device__ __forceinline__ bool electOne() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xFFFFFFFF;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
 __device__ __forceinline__ void ummaCommit(unsigned long long* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smemAddr(bar)) : "memory");
 }
@@ -267,6 +281,22 @@ __device__ __forceinline__ void tmemSt16(uint32_t taddr, const uint32_t (&r)[32]
           "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
         : "memory");
 }
+__device__ __forceinline__ uint32_t tmemLd1(uint32_t taddr) {
+    uint32_t v;
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(v) : "r"(taddr));
+    return v;
+}
+__device__ __forceinline__ void tmemSt1(uint32_t taddr, uint32_t v) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "r"(v) : "memory");
+}
+// A float as bfloat16 bits, rounded towards +infinity, and back.  Used for the reference
+// maximum of a row: any value at or a little above the true maximum serves, as long as the
+// four threads of the row use the same one.
+__device__ __forceinline__ unsigned short bf16Up(float x) {
+    const uint32_t b = __float_as_uint(x);
+    return static_cast<unsigned short>(((b >> 31) ? b : b + 0xFFFFu) >> 16);
+}
+__device__ __forceinline__ float bf16ToFloat(unsigned short h) { return __uint_as_float(static_cast<uint32_t>(h) << 16); }
 __device__ __forceinline__ void tmemStWait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 template <bool BF16>
@@ -285,62 +315,68 @@ __device__ __forceinline__ float ex2Approx(float x) {
     return y;
 }
 
-// Visibility of key `key` for the row at sequence position `rowPos`.
+// Keys [lo, hi) are visible to the row at sequence position `rowPos`.
 struct MaskInfo {
-    int lo, hi;      // keys [lo, hi) are visible to the row
+    int lo, hi;
     __device__ __forceinline__ MaskInfo(int ws, int seqLen, int rowPos, int causal)
         : lo(ws), hi(causal ? min(seqLen, rowPos + 1) : seqLen) {}
-    // key = firstKey + i with i a compile-time constant in the callers' unrolled loops
-    __device__ __forceinline__ bool visible(int key) const {
-        return static_cast<unsigned>(key - lo) < static_cast<unsigned>(max(hi - lo, 0));
-    }
 };
 
-// Maximum of 32 raw scores; EDGE tiles mask invisible keys.
-template <bool EDGE>
-__device__ __forceinline__ float quarterRowMax(const uint32_t (&r)[32], const MaskInfo& mk, int firstKey) {
-    float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+// Edge tiles only: the scores of invisible keys (key firstKey + i for score i) become -inf,
+// after which the tile goes through the same code as an inner tile.
+__device__ __forceinline__ void maskScores(uint32_t (&r)[32], const MaskInfo& mk, int firstKey) {
+    const int a = mk.lo - firstKey, b = mk.hi - firstKey;      // visible: a <= i < b
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-        float a = __uint_as_float(r[i]);
-        if (EDGE && !mk.visible(firstKey + i)) a = -INFINITY;
-        m4[i & 3] = fmaxf(m4[i & 3], a);
-    }
-    return fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+    for (int i = 0; i < 32; ++i)
+        if (i < a || i >= b) r[i] = 0xFF800000u;
 }
 
-// Maximum of 64 raw scores (two loaded chunks); EDGE tiles mask invisible keys.
-template <bool EDGE>
-__device__ __forceinline__ float halfRowMax(const uint32_t (&r0)[32], const uint32_t (&r1)[32], const MaskInfo& mk, int firstKey) {
-    float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-        float a = __uint_as_float(r0[i]), b = __uint_as_float(r1[i]);
-        if (EDGE) {
-            if (!mk.visible(firstKey + i)) a = -INFINITY;
-            if (!mk.visible(firstKey + 32 + i)) b = -INFINITY;
-        }
-        m4[i & 3] = fmaxf(m4[i & 3], fmaxf(a, b));
-    }
-    return fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+// Two float lanes in one 64-bit register pair (packed single-precision instructions).
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
+    unsigned long long v;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(lo), "f"(hi));
+    return v;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ unsigned long long add2(unsigned long long a, unsigned long long b) {
+    unsigned long long d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
 }
 
-// 32 scores -> 16 packed weight pairs (w[0..15]) and, with LO (bfloat16 only),
-// the 16 pairs of their low-order parts (w[16..31]); returns the sum of the weights.
-template <bool BF16, bool LO, bool EDGE>
-__device__ __forceinline__ float weights32(const uint32_t (&r)[32], uint32_t (&w)[32], float scaleLog2, float negM,
-                                           const MaskInfo& mk, int firstKey) {
-    float s4[4] = {0.f, 0.f, 0.f, 0.f};
+// Maximum of 32 raw scores (masked ones are -inf already).
+__device__ __forceinline__ float quarterRowMax(const uint32_t (&r)[32]) {
+    float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-    for (int i = 0; i < 32; i += 2) {
-        float x0 = fmaf(__uint_as_float(r[i]), scaleLog2, negM);
-        float x1 = fmaf(__uint_as_float(r[i + 1]), scaleLog2, negM);
-        if (EDGE) {
-            if (!mk.visible(firstKey + i)) x0 = -INFINITY;
-            if (!mk.visible(firstKey + i + 1)) x1 = -INFINITY;
-        }
+    for (int i = 0; i < 32; i += 2) m4[(i >> 1) & 3] = max3(m4[(i >> 1) & 3], __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+    return fmaxf(max3(m4[0], m4[1], m4[2]), m4[3]);
+}
+
+// Scores r[BEGIN .. END) of a thread's 32 -> packed weight pairs w[BEGIN/2 .. END/2) and,
+// with LO (bfloat16 only), the pairs of their low-order parts in w[16 + BEGIN/2 ..);
+// returns the sum of the weights.  Masked scores are -inf and give weight 0.
+template <bool BF16, bool LO, int BEGIN, int END>
+__device__ __forceinline__ float weightsRange(const uint32_t (&r)[32], uint32_t (&w)[32], float scaleLog2, float negM) {
+    const unsigned long long scale2 = pack2(scaleLog2, scaleLog2), negM2 = pack2(negM, negM);
+    unsigned long long acc[2] = {0ull, 0ull};
+#pragma unroll
+    for (int i = BEGIN; i < END; i += 2) {
+        float x0, x1;
+        unpack2(fma2(pack2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), scale2, negM2), x0, x1);
         const float p0 = ex2Approx(x0), p1 = ex2Approx(x1);
-        s4[(i >> 1) & 3] += p0 + p1;
+        acc[(i >> 1) & 1] = add2(acc[(i >> 1) & 1], pack2(p0, p1));
         w[i / 2] = pack16<BF16>(p0, p1);
         if (LO) {
             // bfloat16 keeps 8 significant bits of a weight; the remainder goes into a
@@ -350,13 +386,16 @@ __device__ __forceinline__ float weights32(const uint32_t (&r)[32], uint32_t (&w
             w[16 + i / 2] = pack16<true>(p0 - h0, p1 - h1);
         }
     }
-    return (s4[0] + s4[1]) + (s4[2] + s4[3]);
+    float s0, s1, s2, s3;
+    unpack2(acc[0], s0, s1);
+    unpack2(acc[1], s2, s3);
+    return (s0 + s1) + (s2 + s3);
 }
 
-constexpr int kSoftmaxThreads = 512;                   // four threads per row
-constexpr int kSoftmaxWarps = kSoftmaxThreads / 32;
-constexpr int kKProducerWarp = 16, kVProducerWarp = 17, kMmaWarp = 18, kStoreWarp = 19;
-constexpr int kThreads = kSoftmaxThreads + 128;
+constexpr int kGroupThreads = 128;                     // one thread per query row
+constexpr int kSoftmaxWarps = 8;                       // two groups of four warps
+constexpr int kKProducerWarp = 8, kVProducerWarp = 9, kMmaWarp = 10, kStoreWarp = 11;
+constexpr int kThreads = (kSoftmaxWarps + 4) * 32;
 
 // One unit of work: 128 query rows of one head of one sequence.
 struct Item {
@@ -428,12 +467,14 @@ struct Cursor {
     __device__ __forceinline__ void nextTile(const PrefillParams& p, int total, int numTiles) {
         ++j;
         ++g;
-        if (j == it.nT) {
-            j = 0;
-            ++n;
-            w += gridDim.x;
-            seek(p, total, numTiles);
-        }
+        if (j == it.nT) nextItem(p, total, numTiles);
+    }
+    // to the first tile of the next item with keys (g must already count the tiles left behind)
+    __device__ __forceinline__ void nextItem(const PrefillParams& p, int total, int numTiles) {
+        j = 0;
+        ++n;
+        w += gridDim.x;
+        seek(p, total, numTiles);
     }
 };
 
@@ -451,6 +492,12 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         return;
     }
 
+#ifdef PAM_PREFILL_TRACE
+    if (threadIdx.x == 0 && blockIdx.x < 256) {
+        gCtaTimes[4 * blockIdx.x] = globalTimerNs();
+        gCtaTimes[4 * blockIdx.x + 2] = clock64();
+    }
+#endif
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int numTiles = (p.maxQLen + kRows - 1) / kRows;
     const int total = numTiles * p.numSeqs * p.heads;
@@ -461,21 +508,20 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     }
     if (threadIdx.x == kVProducerWarp * 32) asm volatile("prefetch.tensormap [%0];" ::"l"(&mapV) : "memory");
     if (threadIdx.x == kStoreWarp * 32) asm volatile("prefetch.tensormap [%0];" ::"l"(&mapO) : "memory");
-    TRACE(0, 31, 0);                                   // CTA start (instrumented build)
     if (threadIdx.x == 0) {
         for (int i = 0; i < 2; ++i) {
             mbarInit(&s->qFull[i], 1);
             mbarInit(&s->qEmpty[i], 1);
-            mbarInit(&s->oEmpty[i], kSoftmaxWarps);
             mbarInit(&s->oStaged[i], kSoftmaxWarps);
             mbarInit(&s->sFull[i], 1);
-            mbarInit(&s->maxReady[i], kSoftmaxThreads);
+            mbarInit(&s->pFull[i], kGroupThreads);
+            mbarInit(&s->pvDone[i], 1);
         }
         for (int i = 0; i < kKStages; ++i) { mbarInit(&s->kFull[i], 1); mbarInit(&s->kEmpty[i], 1); }
         for (int i = 0; i < kVStages; ++i) { mbarInit(&s->vFull[i], 1); mbarInit(&s->vEmpty[i], 1); }
-        mbarInit(&s->pFull, kSoftmaxThreads);
-        mbarInit(&s->pvDone, 1);
-        mbarInit(&s->sumReady, kSoftmaxThreads);
+        mbarInit(&s->oEmpty, kSoftmaxWarps);
+        mbarInit(&s->stateReady, 2 * kGroupThreads);
+        mbarInit(&s->stateRead, 2 * kGroupThreads);
         // an earlier CTA gave up: do not pile up waits
         s->dead = *reinterpret_cast<volatile int*>(errFlag) != 0 ? 1 : 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -488,10 +534,9 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     __syncthreads();
     tcFenceAfter();
     const uint32_t tmem = s->tmemBase;
-    TRACE(0, 31, 1);                                   // barriers and tensor memory ready
-    // tensor memory columns: S buffers at 0 and 128, accumulators at 256 and 384
-    auto tmemS = [&](int b) { return tmem + 128u * static_cast<uint32_t>(b); };
-    auto tmemO = [&](int b) { return tmem + 256u + 128u * static_cast<uint32_t>(b); };
+    // tensor memory columns: S of group 0 and 1 at 0 and 128, their accumulators at 256 and 384
+    auto tmemS = [&](int grp) { return tmem + 128u * static_cast<uint32_t>(grp); };
+    auto tmemO = [&](int grp) { return tmem + 256u + 128u * static_cast<uint32_t>(grp); };
     const bool live = *reinterpret_cast<volatile int*>(&s->dead) == 0;
 
     // Row of the pool (block * kv_heads * block_size space) of the 16-token piece `lane`
@@ -504,10 +549,14 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         return (blk * p.kvHeads + it.kvh) * p.blockSize + (t16 % tilesPerPage) * 16;
     };
 
-    if (!live) {
-        // nothing: fall through to the common exit
-    } else if (warp == kKProducerWarp) {
+    // Registers move from the four service warps to the softmax warps, which hold a whole row
+    // of scores: first statement of every role's branch, the same value in all four warps of
+    // a warpgroup (the instruction is defined per warpgroup).  384 x 168 registers at launch;
+    // 128 threads give up 72 each, 256 threads take 32 each.
+    if (warp == kKProducerWarp) {
         // ------------------------------------------------------------ Q and K producer
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
+        if (!live) goto done;
         Cursor c;
         c.init(p, total, numTiles);
         bool ok = true;
@@ -539,6 +588,8 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         }
     } else if (warp == kVProducerWarp) {
         // ------------------------------------------------------------ V producer
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
+        if (!live) goto done;
         Cursor c;
         c.init(p, total, numTiles);
         bool ok = true;
@@ -558,73 +609,95 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         }
     } else if (warp == kMmaWarp) {
         // ------------------------------------------------------------ MMA issuer
-        // Tensor-core instructions of one thread execute in issue order: S of tile g+2 is
-        // written over P of tile g right behind P V of tile g without a wait in between.
-        // The S products run two tiles ahead of the P V products, across item boundaries:
-        // while the softmax warps write out one item, S of the next is already there.
-        if (lane == 0) {
-            const uint32_t fmt = BF16 ? 1u : 0u;
-            // D = f32, A/B = bf16|f16, M = 128, N = 128; B of the second product is MN-major.
-            const uint32_t idescS = (1u << 4) | (fmt << 7) | (fmt << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
-            // P has the type of the cache: a float16 P against bfloat16 V is rejected by
-            // the hardware (illegal instruction), the two operands must agree.
-            const uint32_t idescO = idescS | (1u << 16);
-            const uint32_t hiK = descHi(1024);                      // K-major tiles and the MN-major V tile share it
-            bool ok = true;
-            Cursor qk, pv;
-            qk.init(p, total, numTiles);
-            pv = qk;
-            auto issueQK = [&]() {
+        // Key tile j of an item belongs to softmax group j & 1, with its own S buffer and
+        // accumulator.  Tensor-core instructions execute in issue order: S of a group's next
+        // tile is written over its P right behind the P V product that read it.
+        // All 32 lanes walk the loop, so that the descriptor arithmetic is uniform across the
+        // warp (it then runs on the uniform datapath, where the tensor-core instructions take
+        // their operands from); one elected lane issues the tensor-core instructions.
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
+        if (!live) goto done;
+        const bool leader = electOne();
+        const uint32_t fmt = BF16 ? 1u : 0u;
+        // D = f32, A/B = bf16|f16, M = 128, N = 128; B of the second product is MN-major.
+        const uint32_t idescS = (1u << 4) | (fmt << 7) | (fmt << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+        // P has the type of the cache: a float16 P against bfloat16 V is rejected by
+        // the hardware (illegal instruction), the two operands must agree.
+        const uint32_t idescO = idescS | (1u << 16);
+        const uint32_t hiK = descHi(1024);                      // K-major tiles and the MN-major V tile share it
+        bool ok = true;
+        Cursor qk, pv;
+        qk.init(p, total, numTiles);
+        pv = qk;
+        int qkCnt0 = 0, qkCnt1 = 0, pvCnt0 = 0, pvCnt1 = 0;     // S products and P V products issued, per group
+        while (pv.valid && ok) {
+            // An S product needs its group's buffer back (the P V product of the group's tile
+            // before issued).  The query tile of a new item arrives only after the output of
+            // the item two before left its buffer, which takes P V products still to come: so
+            // the warp waits for it only when there is nothing else to issue.
+            const int gq = qk.j & 1;
+            const bool canQK = qk.valid && (gq ? qkCnt1 == pvCnt1 : qkCnt0 == pvCnt0);
+            bool takeQK = canQK && (qk.j != 0 || qk.g == pv.g);
+            if (canQK && !takeQK) takeQK = __all_sync(0xFFFFFFFFu, mbarTry(&s->qFull[qk.n & 1], (qk.n >> 1) & 1));
+            if (takeQK) {
                 const int st = qk.g % kKStages, qb = qk.n & 1;
                 if (qk.j == 0) ok = mbarWait(&s->qFull[qb], (qk.n >> 1) & 1, &s->dead, errFlag, 2);
                 if (ok) ok = mbarWait(&s->kFull[st], (qk.g / kKStages) & 1, &s->dead, errFlag, 3);
-                if (!ok) return;
+                ok = __all_sync(0xFFFFFFFFu, ok);
+                if (!ok) break;
                 tcFenceAfter();
                 const uint32_t qLo = descLo(smemAddr(s->q[qb]), 16);
                 const uint32_t kLo = descLo(smemAddr(s->k[st]), 16);
+                const uint32_t dS = tmemS(gq);
+                uint64_t dq[kHd / 16], dk[kHd / 16];
 #pragma unroll
                 for (int ks = 0; ks < kHd / 16; ++ks) {
                     const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
-                    umma(tmemS(qk.g & 1), desc64(qLo + off, hiK), desc64(kLo + off, hiK), idescS, ks > 0);
+                    dq[ks] = desc64(qLo + off, hiK);
+                    dk[ks] = desc64(kLo + off, hiK);
                 }
-                ummaCommit(&s->sFull[qk.g & 1]);
-                ummaCommit(&s->kEmpty[st]);
-                TRACE(2, qk.g, 3);
+                if (leader) {
+#pragma unroll
+                    for (int ks = 0; ks < kHd / 16; ++ks) umma(dS, dq[ks], dk[ks], idescS, ks > 0);
+                    ummaCommit(&s->sFull[gq]);
+                    ummaCommit(&s->kEmpty[st]);
+                }
+                __syncwarp();
+                if (gq) ++qkCnt1; else ++qkCnt0;
                 qk.nextTile(p, total, numTiles);
-            };
-            if (qk.valid) issueQK();
-            if (ok && qk.valid) issueQK();
-            while (pv.valid && ok) {
-                const int st = pv.g % kVStages, ob = pv.n & 1;
-                TRACE(2, pv.g, 0);
-                ok = mbarWait(&s->pFull, pv.g & 1, &s->dead, errFlag, 5);
+            } else {
+                const int st = pv.g % kVStages, gp = pv.j & 1;
+                ok = mbarWait(&s->pFull[gp], (gp ? pvCnt1 : pvCnt0) & 1, &s->dead, errFlag, 5);
                 if (ok) ok = mbarWait(&s->vFull[st], (pv.g / kVStages) & 1, &s->dead, errFlag, 6);
-                // the accumulator of item n is free once the output of item n - 2 was read from it
-                if (ok && pv.j == 0 && pv.n >= 2) ok = mbarWait(&s->oEmpty[ob], ((pv.n >> 1) - 1) & 1, &s->dead, errFlag, 15);
+                // the accumulators are free once the output of the item before was read from them
+                if (ok && pv.j < 2 && pv.n >= 1) ok = mbarWait(&s->oEmpty, (pv.n - 1) & 1, &s->dead, errFlag, 15);
+                ok = __all_sync(0xFFFFFFFFu, ok);
                 if (!ok) break;
                 tcFenceAfter();
-                TRACE(2, pv.g, 1);
                 const uint32_t vLo = descLo(smemAddr(s->v[st]), kHalfBytes);
-                const uint32_t sCol = tmemS(pv.g & 1);
-                // P of keys 32c .. 32c+31 sits in columns 32c .. 32c+15 (and, with the low-order
-                // pass, its remainder in columns 32c+16 .. 32c+31) of the S buffer
+                const uint32_t sCol = tmemS(gp), dO = tmemO(gp);
+                const uint32_t first = pv.j >= 2 ? 1u : 0u;
+                const bool lo = BF16 && pv.it.useLo;
+                uint64_t dv[kKeys / 16];
 #pragma unroll
-                for (int ks = 0; ks < kKeys / 16; ++ks) {
-                    const uint32_t pCol = sCol + 32u * (ks >> 1) + 8u * (ks & 1);
-                    ummaTs(tmemO(ob), pCol, desc64(vLo + ks * 128, hiK), idescO, (pv.j > 0 || ks > 0) ? 1u : 0u);
-                }
-                if (BF16 && pv.it.useLo) {
+                for (int ks = 0; ks < kKeys / 16; ++ks) dv[ks] = desc64(vLo + ks * 128, hiK);
+                if (leader) {
+                    // P of keys 32c .. 32c+31 sits in columns 32c .. 32c+15 (and, with the
+                    // low-order pass, its remainder in columns 32c+16 .. 32c+31) of the S buffer
 #pragma unroll
-                    for (int ks = 0; ks < kKeys / 16; ++ks) {
-                        const uint32_t pCol = sCol + 32u * (ks >> 1) + 8u * (ks & 1) + 16u;
-                        ummaTs(tmemO(ob), pCol, desc64(vLo + ks * 128, hiK), idescO, 1u);
+                    for (int ks = 0; ks < kKeys / 16; ++ks)
+                        ummaTs(dO, sCol + 32u * (ks >> 1) + 8u * (ks & 1), dv[ks], idescO, ks > 0 ? 1u : first);
+                    if (lo) {
+#pragma unroll
+                        for (int ks = 0; ks < kKeys / 16; ++ks)
+                            ummaTs(dO, sCol + 32u * (ks >> 1) + 8u * (ks & 1) + 16u, dv[ks], idescO, 1u);
                     }
+                    ummaCommit(&s->pvDone[gp]);
+                    ummaCommit(&s->vEmpty[st]);
                 }
-                ummaCommit(&s->pvDone);
-                ummaCommit(&s->vEmpty[st]);
-                TRACE(2, pv.g, 2);
+                __syncwarp();
+                if (gp) ++pvCnt1; else ++pvCnt0;
                 pv.nextTile(p, total, numTiles);
-                if (qk.valid) issueQK();
             }
         }
     } else if (warp == kStoreWarp) {
@@ -634,6 +707,8 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         // the buffer back to the producer once the copy has read it.  Tiles with fewer
         // than 128 rows of this sequence were written by the softmax warps themselves (a
         // box would run into the next sequence's rows).
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
+        if (!live) goto done;
         int n = 0;
         bool ok = true;
         for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
@@ -657,195 +732,198 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     } else {
         // ------------------------------------------------------------ softmax warps
-        // Thread (t, cq): row t, key columns [32cq, 32cq + 32) of every key tile and output
-        // columns [32cq, 32cq + 32).  Warps w, w+4, w+8, w+12 share the tensor-memory lanes
-        // 32(w&3) .. +31 (a warp may only touch the lane quarter of its index modulo 4).
-        const int cq = warp >> 2, t = (warp & 3) * 32 + lane;
+        // Two groups of 128 threads; group grp takes the key tiles j with j & 1 == grp of
+        // every item, thread t of a group owns query row t (all 128 key columns of a tile):
+        // no exchange between threads.  Each group keeps its own running maximum, sum and
+        // accumulator; the two are merged when the item is written out.  A tile is read
+        // from tensor memory twice, 32 columns at a time: once for the maximum, once for
+        // the weights.
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
+        if (!live) goto done;
+        const int grp = warp >> 2, t = (warp & 3) * 32 + lane;
         const uint32_t laneBase = static_cast<uint32_t>((warp & 3) * 32) << 16;
-        const int rowLo = (warp & 3) * 32;
-        int g = 0, n = 0;                               // key tiles and items (with keys) done so far
+        const uint32_t sAddr = tmemS(grp) + laneBase, oAddr = tmemO(grp) + laneBase;
         bool ok = true;
-        // The output of an item is written one key tile late, behind the first tile of the next
-        // item: its last P V product has finished by then, and the tensor pipe has the next
-        // item's products to work on meanwhile.
-        bool pend = false;
-        int pendRowBase = 0, pendRowsValid = 0, pendHead = 0;
-        // O / l of item pn (whose last P V product is known to be complete) into its query
-        // buffer, in the layout of the two TMA boxes: [half][row][8 chunks of 16 bytes, chunk
-        // index XOR row % 8].
-        auto writeOut = [&](int pn, int rowBase, int rowsValid, int head) {
-            if (!mbarWait(&s->sumReady, pn & 1, &s->dead, errFlag, 12)) return false;
-            tcFenceAfter();
-            const float lt = (s->rowSum[pn & 1][0][t] + s->rowSum[pn & 1][1][t]) + (s->rowSum[pn & 1][2][t] + s->rowSum[pn & 1][3][t]);
-            const float inv = lt > 0.f ? 1.f / lt : 0.f;
-            unsigned char* stage = s->q[pn & 1] + (cq >> 1) * kHalfBytes;
-            uint32_t o[32];
-            tmemLd32(tmemO(pn & 1) + laneBase + 32u * cq, o);
-            tcFenceBefore();
-#pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
-                uint32_t wv[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e)
-                    wv[e] = pack16<BF16>(__uint_as_float(o[8 * q4 + 2 * e]) * inv, __uint_as_float(o[8 * q4 + 2 * e + 1]) * inv);
-                *reinterpret_cast<uint4*>(stage + t * 128 + ((((cq & 1) * 4 + q4) ^ (t & 7)) << 4)) =
-                    make_uint4(wv[0], wv[1], wv[2], wv[3]);
-            }
-            if (rowsValid < kRows) {
-                // ragged tile: this warp writes its own 32 rows x 64 bytes, eight rows per instruction
-                __syncwarp();
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int row = rowLo + 8 * i + (lane >> 2), chunk = (cq & 1) * 4 + (lane & 3);
-                    if (row < rowsValid) {
-                        const uint4 v = *reinterpret_cast<const uint4*>(stage + row * 128 + ((chunk ^ (row & 7)) << 4));
-                        unsigned char* out = static_cast<unsigned char*>(p.out) +
-                                             ((static_cast<int64_t>(rowBase) + row) * p.heads + head) * kHd * 2;
-                        *reinterpret_cast<uint4*>(out + (cq * 4 + (lane & 3)) * 16) = v;
-                    }
-                }
-            }
-            // the buffer is next read (TMA store) and written (TMA load) by the asynchronous proxy
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) {
-                mbarArrive(&s->oEmpty[pn & 1]);            // the accumulator may be overwritten
-                mbarArrive(&s->oStaged[pn & 1]);
-            }
-            return true;
-        };
+        int k = 0;          // key tiles this group has done (phase of its barriers)
+        int g0 = 0;         // key tiles of the stream before the current item
+        int n = 0;          // items with keys before the current one
         for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
             Item it;
             if (!loadItem(p, w, numTiles, it)) continue;
             if (it.nT == 0) {
-                // rows that see no key at all: zeros (no other role takes part)
+                // rows that see no key at all: zeros (no other role takes part); each thread
+                // writes half of its row
+                if (t < it.rowsValid) {
+                    uint4* out = reinterpret_cast<uint4*>(static_cast<unsigned char*>(p.out) +
+                                                          ((static_cast<int64_t>(it.rowBase) + t) * p.heads + it.head) * kHd * 2 + grp * 128);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int row = rowLo + 8 * i + (lane >> 2), chunk = cq * 4 + (lane & 3);
-                    if (row < it.rowsValid) {
-                        unsigned char* out = static_cast<unsigned char*>(p.out) +
-                                             ((static_cast<int64_t>(it.rowBase) + row) * p.heads + it.head) * kHd * 2;
-                        *reinterpret_cast<uint4*>(out + chunk * 16) = make_uint4(0u, 0u, 0u, 0u);
-                    }
+                    for (int i = 0; i < 8; ++i) out[i] = make_uint4(0u, 0u, 0u, 0u);
                 }
                 continue;
             }
-            const uint32_t oBase = tmemO(n & 1) + laneBase + 32u * cq;
             const MaskInfo mk(it.ws, it.seqLen, it.firstPos + t, p.causal);
             const bool useLo = BF16 && it.useLo;
             float mUsed = -INFINITY, l = 0.f;
-            for (int j = 0; j < it.nT && ok; ++j, ++g) {
-                const int b = g & 1;
+            for (int j = grp; j < it.nT && ok; j += 2, ++k) {
                 const int k0 = (it.tileLo + j) * kKeys;
-                const int kq = k0 + 32 * cq;                                    // first key of this thread's columns
-                const uint32_t sBase = tmemS(b) + laneBase + 32u * cq;
                 const bool edge = k0 < it.ws || k0 + kKeys > it.seqLen || (p.causal && k0 + kKeys - 1 > it.firstPos);
-                TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), g, 0);
-                ok = mbarWait(&s->sFull[b], (g >> 1) & 1, &s->dead, errFlag, 7);
+                ok = mbarWait(&s->sFull[grp], k & 1, &s->dead, errFlag, 7);
                 if (!ok) break;
                 tcFenceAfter();
-                TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), g, 1);
-                uint32_t r[32];
-                tmemLd32(sBase, r);
-                TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), g, 4);
-                // maximum of the raw scores of this quarter row (the scale is positive)
-                float tmax = (edge ? quarterRowMax<true>(r, mk, kq) : quarterRowMax<false>(r, mk, kq)) * scaleLog2;
-                s->rowMax[b][cq][t] = tmax;
-                mbarArrive(&s->maxReady[b]);
-                TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), g, 5);
-                ok = mbarWait(&s->maxReady[b], (g >> 1) & 1, &s->dead, errFlag, 11);
-                if (!ok) break;
-                tmax = fmaxf(fmaxf(s->rowMax[b][0][t], s->rowMax[b][1][t]), fmaxf(s->rowMax[b][2][t], s->rowMax[b][3][t]));
-                TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), g, 2);
+                // ---- the whole row of scores into registers, then its maximum (the scale is positive)
+                uint32_t r0[32], r1[32], r2[32], r3[32];
+                tmemLd32NoWait(sAddr, r0);
+                tmemLd32NoWait(sAddr + 32u, r1);
+                tmemLd32NoWait(sAddr + 64u, r2);
+                tmemLd32NoWait(sAddr + 96u, r3);
+                tmemLdWait();
+                if (edge) {
+                    maskScores(r0, mk, k0);
+                    maskScores(r1, mk, k0 + 32);
+                    maskScores(r2, mk, k0 + 64);
+                    maskScores(r3, mk, k0 + 96);
+                }
+                const float tmax = fmaxf(fmaxf(quarterRowMax(r0), quarterRowMax(r1)), fmaxf(quarterRowMax(r2), quarterRowMax(r3))) * scaleLog2;
+                // The running maximum is only raised when it grows by more than 2^8: the result is
+                // exact either way, the final division uses the same reference.
                 bool raise = false;
                 float corr = 1.f;
-                if (j == 0) mUsed = tmax;
+                if (j < 2) mUsed = tmax;
                 else if (tmax > mUsed + kRescaleThreshold) {
                     raise = true;
                     corr = ex2Approx(mUsed - tmax);
                     mUsed = tmax;
                 }
-                if (j >= 1 && __any_sync(0xFFFFFFFFu, raise)) {
-                    // O is still being added to by P V of the tile before: wait for it, then rescale
-                    ok = mbarWait(&s->pvDone, (g - 1) & 1, &s->dead, errFlag, 8);
-                    if (!ok) break;
-                    tcFenceAfter();
-                    uint32_t o[32];
-                    tmemLd32(oBase, o);
+                if (j >= 2 && __any_sync(0xFFFFFFFFu, raise)) {
+                    // the group's accumulator is complete up to its tile before (seen at the end of
+                    // that tile, before this tile's S could be made)
+#pragma unroll 1
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t o[32];
+                        tmemLd32(oAddr + 32u * c, o);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
-                    tmemSt32(oBase, o);
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+                        tmemSt32(oAddr + 32u * c, o);
+                    }
+                    tmemStWait();
                     l *= corr;
                 }
-                // the weights replace the scores in tensor memory: 16 columns of packed pairs
-                // (plus 16 columns of their low-order parts where the tile needs 16-bit weights)
+                // ---- the weights replace the scores in tensor memory: per 32 keys 16 columns of
+                // packed pairs (plus 16 columns of their low-order parts where the item needs
+                // 16-bit weights)
                 const float negM = mUsed == -INFINITY ? 0.f : -mUsed;
-                TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), g, 7);
-                uint32_t wgt[32];
-                if (useLo) {
-                    l += edge ? weights32<BF16, true, true>(r, wgt, scaleLog2, negM, mk, kq)
-                              : weights32<BF16, true, false>(r, wgt, scaleLog2, negM, mk, kq);
-                    tmemSt32(sBase, wgt);
-                } else {
-                    l += edge ? weights32<BF16, false, true>(r, wgt, scaleLog2, negM, mk, kq)
-                              : weights32<BF16, false, false>(r, wgt, scaleLog2, negM, mk, kq);
-                    TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), g, 8);
-                    tmemSt16(sBase, wgt);
+                {
+                    uint32_t wgt[32];
+                    if (useLo) {
+                        l += weightsRange<BF16, true, 0, 32>(r0, wgt, scaleLog2, negM);
+                        tmemSt32(sAddr, wgt);
+                        l += weightsRange<BF16, true, 0, 32>(r1, wgt, scaleLog2, negM);
+                        tmemSt32(sAddr + 32u, wgt);
+                        l += weightsRange<BF16, true, 0, 32>(r2, wgt, scaleLog2, negM);
+                        tmemSt32(sAddr + 64u, wgt);
+                        l += weightsRange<BF16, true, 0, 32>(r3, wgt, scaleLog2, negM);
+                        tmemSt32(sAddr + 96u, wgt);
+                    } else {
+                        l += weightsRange<BF16, false, 0, 32>(r0, wgt, scaleLog2, negM);
+                        tmemSt16(sAddr, wgt);
+                        l += weightsRange<BF16, false, 0, 32>(r1, wgt, scaleLog2, negM);
+                        tmemSt16(sAddr + 32u, wgt);
+                        l += weightsRange<BF16, false, 0, 32>(r2, wgt, scaleLog2, negM);
+                        tmemSt16(sAddr + 64u, wgt);
+                        l += weightsRange<BF16, false, 0, 32>(r3, wgt, scaleLog2, negM);
+                        tmemSt16(sAddr + 96u, wgt);
+                    }
                 }
-                TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), g, 9);
                 tmemStWait();
-                TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), g, 10);
                 if (k0 + kKeys > it.seqLen) {
                     // rows of V past the end of the sequence may hold anything: zero them
-                    const int st = g % kVStages;
-                    ok = mbarWait(&s->vFull[st], (g / kVStages) & 1, &s->dead, errFlag, 9);
+                    const int gt = g0 + j, st = gt % kVStages;
+                    ok = mbarWait(&s->vFull[st], (gt / kVStages) & 1, &s->dead, errFlag, 9);
                     if (!ok) break;
                     if (k0 + t >= it.seqLen) {
 #pragma unroll
-                        for (int c16 = 0; c16 < 4; ++c16)
-                            *reinterpret_cast<uint4*>(s->v[st] + (cq >> 1) * kHalfBytes + t * 128 + ((cq & 1) * 4 + c16) * 16) =
+                        for (int c16 = 0; c16 < 16; ++c16)
+                            *reinterpret_cast<uint4*>(s->v[st] + (c16 >> 3) * kHalfBytes + t * 128 + (c16 & 7) * 16) =
                                 make_uint4(0u, 0u, 0u, 0u);
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 }
-                const bool flush = pend && j == 0;
-                // The last P V of the item before must be seen complete before this thread lets
-                // the next one start: the barrier's phase parity is only good for one step back.
-                if (flush) {
-                    ok = mbarWait(&s->pvDone, (g - 1) & 1, &s->dead, errFlag, 10);
-                    if (!ok) break;
-                }
                 tcFenceBefore();
-                mbarArrive(&s->pFull);
-                TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), g, 3);
-                if (flush) {
-                    pend = false;
-                    ok = writeOut(n - 1, pendRowBase, pendRowsValid, pendHead);
-                    TRACE((warp == 0 ? 0 : warp == 8 ? 1 : 99), g, 6);
-                }
+                mbarArrive(&s->pFull[grp]);
+                // Every thread sees every P V product of its group complete, in order: a wait on
+                // a phase parity is only good for one step back, and the next product cannot
+                // complete before this thread's next arrival.
+                ok = mbarWait(&s->pvDone[grp], k & 1, &s->dead, errFlag, 10);
             }
             if (!ok) break;
-            // the four parts of a row add up their sums through shared memory (one buffer per
-            // item parity: a thread can be at most one item ahead of the slowest)
-            s->rowSum[n & 1][cq][t] = l;
-            mbarArrive(&s->sumReady);
-            pend = true;
-            pendRowBase = it.rowBase;
-            pendRowsValid = it.rowsValid;
-            pendHead = it.head;
+            // ---- output of the item: (O_0 2^(m_0 - m) + O_1 2^(m_1 - m)) / (l_0 2^(m_0 - m) + l_1 2^(m_1 - m)).
+            // Thread t of group grp writes columns [64 grp, 64 grp + 64) of row t.
+            tcFenceAfter();
+            s->rowState[grp][t] = make_float2(mUsed, l);
+            mbarArrive(&s->stateReady);
+            ok = mbarWait(&s->stateReady, n & 1, &s->dead, errFlag, 17);
+            if (!ok) break;
+            const float2 other = s->rowState[grp ^ 1][t];
+            const float m = fmaxf(mUsed, other.x);
+            const float wMine = m == -INFINITY ? 0.f : ex2Approx(mUsed - m), wOther = m == -INFINITY ? 0.f : ex2Approx(other.x - m);
+            const float lt = l * wMine + other.y * wOther;
+            const float inv = lt > 0.f ? 1.f / lt : 0.f;
+            const float f0 = (grp == 0 ? wMine : wOther) * inv, f1 = (grp == 0 ? wOther : wMine) * inv;
+            const bool has1 = it.nT >= 2;                     // group 1 had a tile: its accumulator holds numbers
+            unsigned char* stage = s->q[n & 1] + grp * kHalfBytes + t * 128;
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                uint32_t o0[32], o1[32];
+                tmemLd32(tmemO(0) + laneBase + 64u * grp + 32u * c, o0);
+                if (has1) tmemLd32(tmemO(1) + laneBase + 64u * grp + 32u * c, o1);
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    uint32_t wv[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int i = 8 * q4 + 2 * e;
+                        float a = __uint_as_float(o0[i]) * f0, b = __uint_as_float(o0[i + 1]) * f0;
+                        if (has1) {
+                            a = fmaf(__uint_as_float(o1[i]), f1, a);
+                            b = fmaf(__uint_as_float(o1[i + 1]), f1, b);
+                        }
+                        wv[e] = pack16<BF16>(a, b);
+                    }
+                    *reinterpret_cast<uint4*>(stage + (((c * 4 + q4) ^ (t & 7)) << 4)) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+                }
+            }
+            tcFenceBefore();
+            __syncwarp();
+            if (lane == 0) mbarArrive(&s->oEmpty);                 // the accumulators may be overwritten
+            if (it.rowsValid < kRows) {
+                // ragged tile: this thread writes its own 128 bytes
+                if (t < it.rowsValid) {
+                    uint4* out = reinterpret_cast<uint4*>(static_cast<unsigned char*>(p.out) +
+                                                          ((static_cast<int64_t>(it.rowBase) + t) * p.heads + it.head) * kHd * 2 + grp * 128);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) out[i] = *reinterpret_cast<const uint4*>(stage + ((i ^ (t & 7)) << 4));
+                }
+            }
+            // the buffer is next read (TMA store) and written (TMA load) by the asynchronous proxy
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbarArrive(&s->oStaged[n & 1]);
+            // the other group must have read this group's row state before the next item overwrites it
+            mbarArrive(&s->stateRead);
+            ok = mbarWait(&s->stateRead, n & 1, &s->dead, errFlag, 18);
+            g0 += it.nT;
             ++n;
-        }
-        if (ok && pend) {
-            ok = mbarWait(&s->pvDone, (g - 1) & 1, &s->dead, errFlag, 10);
-            if (ok) writeOut(n - 1, pendRowBase, pendRowsValid, pendHead);
         }
     }
 
+done:
     tcFenceBefore();
     __syncthreads();
 #ifdef PAM_PREFILL_TRACE
-    if (blockIdx.x == 0)
-        for (int i = threadIdx.x; i < kTraceRoles * kTraceTiles * kTraceEvents; i += kThreads) gTrace[i] = s->trace[i];
+    if (threadIdx.x == 0 && blockIdx.x < 256) {
+        gCtaTimes[4 * blockIdx.x + 1] = globalTimerNs();
+        gCtaTimes[4 * blockIdx.x + 3] = clock64();
+    }
 #endif
     if (warp == kMmaWarp) {
         tcFenceAfter();
@@ -933,6 +1011,11 @@ cudaError_t launchPrefillTensor(const PrefillParams& p, int totalRows, int* errF
 }  // namespace pam
 
 #ifdef PAM_PREFILL_TRACE
+extern "C" int pamc_debug_cta_times(unsigned long long* out) {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, pam::gCtaTimes, sizeof(unsigned long long) * 1024);
+    return 1024;
+}
 extern "C" int pamc_debug_trace_read(long long* out) {
     cudaDeviceSynchronize();
     cudaMemcpyFromSymbol(out, pam::gTrace, sizeof(long long) * pam::kTraceRoles * pam::kTraceTiles * pam::kTraceEvents);
