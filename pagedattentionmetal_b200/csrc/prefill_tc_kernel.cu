@@ -8,40 +8,43 @@
 // PagedAttentionEngine.swift:740-756).
 //
 // The kernel is persistent: one CTA per multiprocessor walks the work items
-// (128 query rows of one head of one sequence) round robin, longest items
-// first.  An item walks the key tiles (128 keys each) its rows can see; the
-// tiles go alternately to two softmax groups, each with its own S buffer and
-// accumulator O in tensor memory (4 x 128 columns), so that one group turns S
-// into the weights P while the tensor pipe works for the other.  The two
-// accumulators are merged (log-sum-exp) when the item is written out.
+// round robin, longest items first.  An item is a pair of consecutive tiles of
+// 128 query rows of one head of one sequence; it walks the key tiles (128 keys
+// each) its rows can see, and every key and value tile is fetched once for
+// both query tiles.  Each query tile belongs to one of two softmax groups, with
+// its own S buffer and accumulator O in tensor memory (4 x 128 columns): while
+// one group turns its S into the weights P, the tensor pipe works for the
+// other.
 //
 //   warps 0-3, 4-7       softmax groups 0 and 1: thread t of a group owns query
-//                        row t, all 128 key columns of a tile, in registers (no
-//                        exchange between threads).  Scores are scaled, masked
-//                        (causal, window start, sequence end) only on edge
-//                        tiles.  The running maximum is only raised when it
-//                        grows by more than 2^8 (the result is exact either
-//                        way, the final division uses the same reference), in
-//                        which case O is rescaled in tensor memory.  The
-//                        weights go back to tensor memory over the scores, in
-//                        the cache type (tcgen05.st); for bfloat16, on rows that
-//                        see few keys, as two operands P_hi + P_lo (16
-//                        significant bits together) and twice the PV
-//                        instructions, because 8-bit weights alone miss the
-//                        2e-3 bound there.  The merged O / l of an item is
-//                        staged in its (by then idle) query buffer in the
-//                        layout of a TMA box.
-//   warp 8               TMA producer of Q (two buffers, one per item in flight)
-//                        and of K: per key tile 8 pages (each 16 rows x 256 B,
-//                        fetched as two 128-byte-swizzled boxes, one page per
-//                        lane) into a ring; completion on mbarriers.
+//                        row t of the group's tile, all 128 key columns of a key
+//                        tile, in registers (no exchange between threads).
+//                        Scores are scaled, masked (causal, window start,
+//                        sequence end) only on edge tiles.  The running maximum
+//                        is only raised when it grows by more than 2^8 (the
+//                        result is exact either way, the final division uses
+//                        the same reference), in which case O is rescaled in
+//                        tensor memory.  The weights go back to tensor memory
+//                        over the scores, in the cache type (tcgen05.st); for
+//                        bfloat16, on rows that see few keys, as two operands
+//                        P_hi + P_lo (16 significant bits together) and twice
+//                        the PV instructions, because 8-bit weights alone miss
+//                        the 2e-3 bound there.  Thread 0 of a group fetches the
+//                        group's next query tile by TMA during the last key
+//                        tile of the current one.  O / l goes to a staging
+//                        buffer in the layout of a TMA box, the groups taking
+//                        turns.
+//   warp 8               TMA producer of K: per key tile 8 pages (each 16 rows x
+//                        256 B, fetched as two 128-byte-swizzled boxes, one page
+//                        per lane) into a ring; completion on mbarriers.
 //   warp 9               TMA producer of V, its own ring.
-//   warp 10              MMA issuer (one elected lane): S = Q K^T (8 x
-//                        tcgen05.mma 128x128x16, both operands from shared
-//                        memory) and O += P V (P read from tensor memory, V as
-//                        an MN-major operand straight from its row-major
-//                        pages); tcgen05.commit signals the mbarriers.
-//   warp 11              TMA store of the finished rows of an item.
+//   warp 10              MMA issuer (one elected lane): for every key tile and
+//                        group, O += P V (P read from tensor memory, V as an
+//                        MN-major operand straight from its row-major pages)
+//                        and right behind it S = Q K^T of the group's next key
+//                        tile (8 x tcgen05.mma 128x128x16, both operands from
+//                        shared memory); tcgen05.commit signals the mbarriers.
+//   warp 11              TMA store of the staged rows.
 //
 // The service warps hand registers to the softmax warps (setmaxnreg).
 //
@@ -62,7 +65,7 @@ namespace {
 constexpr int kRows = 128;        // query rows per CTA
 constexpr int kKeys = 128;        // keys per tile
 constexpr int kHd = 128;
-constexpr int kKStages = 3, kVStages = 2;
+constexpr int kKStages = 2, kVStages = 2;
 constexpr int kTileBytes = kRows * kHd * 2;            // 32 KB: one [128][128] 16-bit tile
 constexpr int kHalfBytes = kTileBytes / 2;             // one 64-column block
 constexpr float kLog2e = 1.4426950408889634f;
@@ -91,14 +94,13 @@ __device__ __forceinline__ unsigned long long globalTimerNs() {
 
 struct Smem {
     // tiles first: each 1024-byte aligned (swizzle atoms)
-    unsigned char q[2][kTileBytes];            // query tiles of two items in flight; each doubles as output staging
+    unsigned char q[2][kTileBytes];            // the query tile of each softmax group
     unsigned char k[kKStages][kTileBytes];
     unsigned char v[kVStages][kTileBytes];
-    unsigned long long qFull[2], qEmpty[2], kFull[kKStages], kEmpty[kKStages], vFull[kVStages], vEmpty[kVStages];
-    unsigned long long sFull[2], pFull[2], pvDone[2];   // one of each per softmax group
-    unsigned long long oEmpty, oStaged[2];
-    unsigned long long stateReady, stateRead;  // the two softmax groups meet twice per item
-    float2 rowState[2][kRows];                 // [group][row]: reference maximum and sum of weights of an item
+    unsigned char stage[kTileBytes];           // finished rows of one group on their way out (TMA box layout)
+    unsigned long long qFull[2], kFull[kKStages], kEmpty[kKStages], vFull[kVStages], vEmpty[kVStages];
+    unsigned long long sFull[2], pFull[2], pvDone[2], oEmpty[2];   // one of each per softmax group
+    unsigned long long oStaged, stageFree[2];
     uint32_t tmemBase;
     int dead;
 };
@@ -326,9 +328,16 @@ struct MaskInfo {
 // after which the tile goes through the same code as an inner tile.
 __device__ __forceinline__ void maskScores(uint32_t (&r)[32], const MaskInfo& mk, int firstKey) {
     const int a = mk.lo - firstKey, b = mk.hi - firstKey;      // visible: a <= i < b
+    if (a <= 0) {
+        // the usual case (the causal diagonal, the end of the sequence): an upper bound only
 #pragma unroll
-    for (int i = 0; i < 32; ++i)
-        if (i < a || i >= b) r[i] = 0xFF800000u;
+        for (int i = 0; i < 32; ++i)
+            if (i >= b) r[i] = 0xFF800000u;
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            if (i < a || i >= b) r[i] = 0xFF800000u;
+    }
 }
 
 __device__ __forceinline__ float max3(float a, float b, float c) {
@@ -366,7 +375,10 @@ __device__ __forceinline__ float quarterRowMax(const uint32_t (&r)[32]) {
 
 // Scores r[BEGIN .. END) of a thread's 32 -> packed weight pairs w[BEGIN/2 .. END/2) and,
 // with LO (bfloat16 only), the pairs of their low-order parts in w[16 + BEGIN/2 ..);
-// returns the sum of the weights.  Masked scores are -inf and give weight 0.
+// returns the sum of the weights.  Masked scores are -inf and give weight 0.  (The loop is
+// kept to five instructions per pair: with one warp per group on each scheduler the
+// instruction count is what limits it; an integer-only pack and polynomial exponentials
+// for part of the pairs, which relieve the special-function pipe, both made it slower.)
 template <bool BF16, bool LO, int BEGIN, int END>
 __device__ __forceinline__ float weightsRange(const uint32_t (&r)[32], uint32_t (&w)[32], float scaleLog2, float negM) {
     const unsigned long long scale2 = pack2(scaleLog2, scaleLog2), negM2 = pack2(negM, negM);
@@ -397,84 +409,95 @@ constexpr int kSoftmaxWarps = 8;                       // two groups of four war
 constexpr int kKProducerWarp = 8, kVProducerWarp = 9, kMmaWarp = 10, kStoreWarp = 11;
 constexpr int kThreads = (kSoftmaxWarps + 4) * 32;
 
-// One unit of work: 128 query rows of one head of one sequence.
+// One unit of work: two consecutive tiles of 128 query rows of one head of one sequence.
+// Softmax group x owns tile x of the pair: its own query tile, S buffer and accumulator;
+// the key and value tiles are fetched once for both.
 struct Item {
     int head, seq, kvh;
-    int nT, tileLo;          // key tiles tileLo .. tileLo + nT - 1 hold every key a row may see
-    int rowBase, rowsValid;  // first row in q/out, rows that exist
-    int firstPos;            // sequence position of row 0
+    int tileLo, nT;              // key tiles tileLo .. tileLo + nT - 1 hold every key a row of the pair may see
+    int nTg[2];                  // ... a row of group x may see (0: the group has no rows, or they see nothing)
+    int rowBase[2], rowsValid[2];// first row in q/out, rows that exist
+    int firstPos[2];             // sequence position of a group's row 0
     int seqLen, ws;
-    bool useLo;
+    bool useLo[2];
     const int32_t* table;
 };
 
-// Work item `w` of the launch.  Items are numbered tile-major with the last (longest)
-// query tiles first and the head running fastest, so that the CTAs working side by side
-// share the keys of one KV head through L2 and the short items fill the end of the launch.
-// Returns false when the sequence has no rows in that tile.
-__device__ __forceinline__ bool loadItem(const PrefillParams& p, int w, int numTiles, Item& it) {
+// Work item `w` of the launch.  Items are numbered pair-major with the last (longest) pairs
+// first and the head running fastest, so that the CTAs working side by side share the keys
+// of one KV head through L2 and the short items fill the end of the launch.  Returns false
+// when the sequence has no rows in that pair.
+__device__ __forceinline__ bool loadItem(const PrefillParams& p, int w, int numPairs, Item& it) {
     const int per = p.numSeqs * p.heads;
-    const int tile = numTiles - 1 - w / per;
+    const int pair = numPairs - 1 - w / per;
     const int rem = w % per;
     it.seq = rem / p.heads;
     it.head = rem % p.heads;
     const int qLen = prefillMeta(p, 2, it.seq);
-    if (tile * kRows >= qLen) return false;
+    if (pair * 2 * kRows >= qLen) return false;
     it.kvh = it.head / (p.heads / p.kvHeads);
-    const int qStart = prefillMeta(p, 1, it.seq);
+    const int qStart = prefillMeta(p, 1, it.seq), rowOff = prefillMeta(p, 3, it.seq);
     it.seqLen = prefillMeta(p, 0, it.seq);
     it.ws = prefillMeta(p, 4, it.seq);
-    it.rowBase = prefillMeta(p, 3, it.seq) + tile * kRows;
-    it.rowsValid = min(kRows, qLen - tile * kRows);
-    it.firstPos = qStart + tile * kRows;
-    const int lastPos = it.firstPos + it.rowsValid - 1;
-    const int keyEnd = p.causal ? min(it.seqLen, lastPos + 1) : it.seqLen;  // exclusive
     it.tileLo = it.ws / kKeys;
-    it.nT = keyEnd > it.ws ? (keyEnd - 1) / kKeys - it.tileLo + 1 : 0;
-    // Fewest keys any row of the tile sees.  A bfloat16 weight keeps 8 significant bits; on a
-    // row with few keys (large weights) that alone can cost more than 2e-3 on unit-variance
-    // values, so such tiles carry the weights as two bfloat16 operands (16 bits).  Rows with
-    // hundreds of keys have weights small enough for 8 bits, as in every bfloat16 attention
-    // kernel.  exactWeights: 0 never, 1 short rows, 2 always.
-    const int fewest = p.causal ? it.firstPos + 1 - it.ws : it.seqLen - it.ws;
-    it.useLo = p.exactWeights == 2 || (p.exactWeights == 1 && fewest < kShortRowKeys);
+    it.nT = 0;
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+        const int first = (pair * 2 + x) * kRows;                 // first row of the tile within the launch's rows
+        const int rows = min(kRows, qLen - first);
+        it.rowsValid[x] = max(rows, 0);
+        it.rowBase[x] = rowOff + first;
+        it.firstPos[x] = qStart + first;
+        it.nTg[x] = 0;
+        it.useLo[x] = false;
+        if (rows > 0) {
+            const int lastPos = it.firstPos[x] + rows - 1;
+            const int keyEnd = p.causal ? min(it.seqLen, lastPos + 1) : it.seqLen;  // exclusive
+            it.nTg[x] = keyEnd > it.ws ? (keyEnd - 1) / kKeys - it.tileLo + 1 : 0;
+            // Fewest keys any row of the tile sees.  A bfloat16 weight keeps 8 significant bits;
+            // on a row with few keys (large weights) that alone can cost more than 2e-3 on
+            // unit-variance values, so such tiles carry the weights as two bfloat16 operands
+            // (16 bits).  Rows with hundreds of keys have weights small enough for 8 bits, as in
+            // every bfloat16 attention kernel.  exactWeights: 0 never, 1 short rows, 2 always.
+            const int fewest = p.causal ? it.firstPos[x] + 1 - it.ws : it.seqLen - it.ws;
+            it.useLo[x] = p.exactWeights == 2 || (p.exactWeights == 1 && fewest < kShortRowKeys);
+        }
+        it.nT = max(it.nT, it.nTg[x]);
+    }
     it.table = p.tables + static_cast<int64_t>(it.seq) * p.maxNumBlocks;
     return true;
 }
 
-// Position of a role in the CTA's stream of key tiles: item w, tile j of it, g tiles and
-// n items (with keys) done before.  Every role walks the same stream, so g and n give the
-// stage and the phase parity of every barrier without any communication.
+// Position of a role in the CTA's stream of key tiles: item w, tile j of it, g tiles done
+// before.  Every role walks the same stream, so g gives the stage and the phase parity of the
+// K and V rings without any communication.
 struct Cursor {
-    int w, j, g, n;
+    int w, j, g;
     bool valid;
     Item it;
-    __device__ __forceinline__ void seek(const PrefillParams& p, int total, int numTiles) {
+    __device__ __forceinline__ void seek(const PrefillParams& p, int total, int numPairs) {
         valid = false;
         while (w < total) {
-            if (loadItem(p, w, numTiles, it) && it.nT > 0) {
+            if (loadItem(p, w, numPairs, it) && it.nT > 0) {
                 valid = true;
                 return;
             }
             w += gridDim.x;
         }
     }
-    __device__ __forceinline__ void init(const PrefillParams& p, int total, int numTiles) {
+    __device__ __forceinline__ void init(const PrefillParams& p, int total, int numPairs) {
         w = blockIdx.x;
-        j = g = n = 0;
-        seek(p, total, numTiles);
+        j = g = 0;
+        seek(p, total, numPairs);
     }
-    __device__ __forceinline__ void nextTile(const PrefillParams& p, int total, int numTiles) {
+    __device__ __forceinline__ void nextTile(const PrefillParams& p, int total, int numPairs) {
         ++j;
         ++g;
-        if (j == it.nT) nextItem(p, total, numTiles);
-    }
-    // to the first tile of the next item with keys (g must already count the tiles left behind)
-    __device__ __forceinline__ void nextItem(const PrefillParams& p, int total, int numTiles) {
-        j = 0;
-        ++n;
-        w += gridDim.x;
-        seek(p, total, numTiles);
+        if (j == it.nT) {
+            j = 0;
+            w += gridDim.x;
+            seek(p, total, numPairs);
+        }
     }
 };
 
@@ -499,29 +522,26 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     }
 #endif
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int numTiles = (p.maxQLen + kRows - 1) / kRows;
-    const int total = numTiles * p.numSeqs * p.heads;
+    const int numPairs = ((p.maxQLen + kRows - 1) / kRows + 1) / 2;
+    const int total = numPairs * p.numSeqs * p.heads;
 
-    if (threadIdx.x == kKProducerWarp * 32) {
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&mapQ) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&mapK) : "memory");
-    }
+    if (threadIdx.x == kKProducerWarp * 32) asm volatile("prefetch.tensormap [%0];" ::"l"(&mapK) : "memory");
     if (threadIdx.x == kVProducerWarp * 32) asm volatile("prefetch.tensormap [%0];" ::"l"(&mapV) : "memory");
     if (threadIdx.x == kStoreWarp * 32) asm volatile("prefetch.tensormap [%0];" ::"l"(&mapO) : "memory");
+    if (threadIdx.x == 0 || threadIdx.x == kGroupThreads) asm volatile("prefetch.tensormap [%0];" ::"l"(&mapQ) : "memory");
     if (threadIdx.x == 0) {
         for (int i = 0; i < 2; ++i) {
             mbarInit(&s->qFull[i], 1);
-            mbarInit(&s->qEmpty[i], 1);
-            mbarInit(&s->oStaged[i], kSoftmaxWarps);
             mbarInit(&s->sFull[i], 1);
             mbarInit(&s->pFull[i], kGroupThreads);
             mbarInit(&s->pvDone[i], 1);
+            mbarInit(&s->oEmpty[i], kGroupThreads / 32);
         }
         for (int i = 0; i < kKStages; ++i) { mbarInit(&s->kFull[i], 1); mbarInit(&s->kEmpty[i], 1); }
         for (int i = 0; i < kVStages; ++i) { mbarInit(&s->vFull[i], 1); mbarInit(&s->vEmpty[i], 1); }
-        mbarInit(&s->oEmpty, kSoftmaxWarps);
-        mbarInit(&s->stateReady, 2 * kGroupThreads);
-        mbarInit(&s->stateRead, 2 * kGroupThreads);
+        mbarInit(&s->oStaged, kGroupThreads / 32);
+        mbarInit(&s->stageFree[0], 1);
+        mbarInit(&s->stageFree[1], 1);
         // an earlier CTA gave up: do not pile up waits
         s->dead = *reinterpret_cast<volatile int*>(errFlag) != 0 ? 1 : 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -552,27 +572,15 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     // Registers move from the four service warps to the softmax warps, which hold a whole row
     // of scores: first statement of every role's branch, the same value in all four warps of
     // a warpgroup (the instruction is defined per warpgroup).  384 x 168 registers at launch;
-    // 128 threads give up 72 each, 256 threads take 32 each.
+    // 128 threads give up 64 each, 256 threads take 32 each.
     if (warp == kKProducerWarp) {
-        // ------------------------------------------------------------ Q and K producer
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
+        // ------------------------------------------------------------ K producer
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
         if (!live) goto done;
         Cursor c;
-        c.init(p, total, numTiles);
+        c.init(p, total, numPairs);
         bool ok = true;
         while (c.valid && ok) {
-            if (c.j == 0) {
-                // the query tile of item n goes into buffer n & 1 once the output of item n - 2 left it
-                const int qb = c.n & 1;
-                if (c.n >= 2) ok = mbarWait(&s->qEmpty[qb], ((c.n >> 1) - 1) & 1, &s->dead, errFlag, 14);
-                ok = __all_sync(0xFFFFFFFFu, ok);
-                if (!ok) break;
-                if (lane == 0) {
-                    mbarExpectTx(&s->qFull[qb], kTileBytes);
-                    tmaLoad3d(s->q[qb], &mapQ, &s->qFull[qb], 0, c.it.head, c.it.rowBase);
-                    tmaLoad3d(s->q[qb] + kHalfBytes, &mapQ, &s->qFull[qb], 64, c.it.head, c.it.rowBase);
-                }
-            }
             const int st = c.g % kKStages;
             const int row = lane < kKeys / 16 ? pieceRow(c.it, c.j) : 0;
             if (c.g >= kKStages) ok = mbarWait(&s->kEmpty[st], ((c.g / kKStages) - 1) & 1, &s->dead, errFlag, 1);
@@ -584,14 +592,14 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 tmaLoad2d(s->k[st] + lane * 2048, &mapK, &s->kFull[st], 0, row);
                 tmaLoad2d(s->k[st] + kHalfBytes + lane * 2048, &mapK, &s->kFull[st], 64, row);
             }
-            c.nextTile(p, total, numTiles);
+            c.nextTile(p, total, numPairs);
         }
     } else if (warp == kVProducerWarp) {
         // ------------------------------------------------------------ V producer
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
         if (!live) goto done;
         Cursor c;
-        c.init(p, total, numTiles);
+        c.init(p, total, numPairs);
         bool ok = true;
         while (c.valid && ok) {
             const int st = c.g % kVStages;
@@ -605,17 +613,20 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 tmaLoad2d(s->v[st] + lane * 2048, &mapV, &s->vFull[st], 0, row);
                 tmaLoad2d(s->v[st] + kHalfBytes + lane * 2048, &mapV, &s->vFull[st], 64, row);
             }
-            c.nextTile(p, total, numTiles);
+            c.nextTile(p, total, numPairs);
         }
     } else if (warp == kMmaWarp) {
         // ------------------------------------------------------------ MMA issuer
-        // Key tile j of an item belongs to softmax group j & 1, with its own S buffer and
-        // accumulator.  Tensor-core instructions execute in issue order: S of a group's next
-        // tile is written over its P right behind the P V product that read it.
+        // For every key tile of the stream, for each group that takes part in it: O += P V
+        // once the group has released P, then right behind it S = Q K^T of the group's next
+        // tile (tensor-core instructions execute in issue order: S is written over P after
+        // the product that read it).  When the group's next tile is the first of the next
+        // item and at most two tiles ahead in the stream (so that the key ring can hold it),
+        // that S product is issued here as well; otherwise when the stream gets there.
         // All 32 lanes walk the loop, so that the descriptor arithmetic is uniform across the
         // warp (it then runs on the uniform datapath, where the tensor-core instructions take
         // their operands from); one elected lane issues the tensor-core instructions.
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
         if (!live) goto done;
         const bool leader = electOne();
         const uint32_t fmt = BF16 ? 1u : 0u;
@@ -626,58 +637,82 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         const uint32_t idescO = idescS | (1u << 16);
         const uint32_t hiK = descHi(1024);                      // K-major tiles and the MN-major V tile share it
         bool ok = true;
-        Cursor qk, pv;
-        qk.init(p, total, numTiles);
-        pv = qk;
-        int qkCnt0 = 0, qkCnt1 = 0, pvCnt0 = 0, pvCnt1 = 0;     // S products and P V products issued, per group
-        while (pv.valid && ok) {
-            // An S product needs its group's buffer back (the P V product of the group's tile
-            // before issued).  The query tile of a new item arrives only after the output of
-            // the item two before left its buffer, which takes P V products still to come: so
-            // the warp waits for it only when there is nothing else to issue.
-            const int gq = qk.j & 1;
-            const bool canQK = qk.valid && (gq ? qkCnt1 == pvCnt1 : qkCnt0 == pvCnt0);
-            bool takeQK = canQK && (qk.j != 0 || qk.g == pv.g);
-            if (canQK && !takeQK) takeQK = __all_sync(0xFFFFFFFFu, mbarTry(&s->qFull[qk.n & 1], (qk.n >> 1) & 1));
-            if (takeQK) {
-                const int st = qk.g % kKStages, qb = qk.n & 1;
-                if (qk.j == 0) ok = mbarWait(&s->qFull[qb], (qk.n >> 1) & 1, &s->dead, errFlag, 2);
-                if (ok) ok = mbarWait(&s->kFull[st], (qk.g / kKStages) & 1, &s->dead, errFlag, 3);
-                ok = __all_sync(0xFFFFFFFFu, ok);
-                if (!ok) break;
-                tcFenceAfter();
-                const uint32_t qLo = descLo(smemAddr(s->q[qb]), 16);
-                const uint32_t kLo = descLo(smemAddr(s->k[st]), 16);
-                const uint32_t dS = tmemS(gq);
-                uint64_t dq[kHd / 16], dk[kHd / 16];
+        Cursor c;
+        c.init(p, total, numPairs);
+        int steps0 = 0, steps1 = 0;          // group tiles done: phase of sFull, pFull, pvDone
+        int items0 = 0, items1 = 0;          // items a group took part in: phase of qFull, oEmpty
+        int qkOpen0 = 0, qkOpen1 = 0;        // per key stage: S products still to issue on the tile it holds
+        bool ahead0 = false, ahead1 = false; // the S product of the group's next tile is already issued
+        // S = Q_x K^T for tile j (global tile gTile) of item `it`
+        auto issueQK = [&](int x, const Item& it, int j, int gTile) {
+            const int st = gTile % kKStages;
+            if (j == 0) ok = mbarWait(&s->qFull[x], (x ? items1 : items0) & 1, &s->dead, errFlag, 2);
+            if (ok) ok = mbarWait(&s->kFull[st], (gTile / kKStages) & 1, &s->dead, errFlag, 3);
+            ok = __all_sync(0xFFFFFFFFu, ok);
+            if (!ok) return;
+            tcFenceAfter();
+            const uint32_t qLo = descLo(smemAddr(s->q[x]), 16);
+            const uint32_t kLo = descLo(smemAddr(s->k[st]), 16);
+            const uint32_t dS = tmemS(x);
+            uint64_t dq[kHd / 16], dk[kHd / 16];
 #pragma unroll
-                for (int ks = 0; ks < kHd / 16; ++ks) {
-                    const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
-                    dq[ks] = desc64(qLo + off, hiK);
-                    dk[ks] = desc64(kLo + off, hiK);
-                }
-                if (leader) {
+            for (int ks = 0; ks < kHd / 16; ++ks) {
+                const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
+                dq[ks] = desc64(qLo + off, hiK);
+                dk[ks] = desc64(kLo + off, hiK);
+            }
+            // the key stage goes back to its producer behind the last S product on it
+            int& open = st ? qkOpen1 : qkOpen0;
+            if (open == 0) open = (j < it.nTg[0] ? 1 : 0) + (j < it.nTg[1] ? 1 : 0);
+            --open;
+            if (leader) {
 #pragma unroll
-                    for (int ks = 0; ks < kHd / 16; ++ks) umma(dS, dq[ks], dk[ks], idescS, ks > 0);
-                    ummaCommit(&s->sFull[gq]);
-                    ummaCommit(&s->kEmpty[st]);
+                for (int ks = 0; ks < kHd / 16; ++ks) umma(dS, dq[ks], dk[ks], idescS, ks > 0);
+                ummaCommit(&s->sFull[x]);
+                if (open == 0) ummaCommit(&s->kEmpty[st]);
+            }
+            __syncwarp();
+            if (j == 0) { if (x) ++items1; else ++items0; }
+        };
+        while (c.valid && ok) {
+            // S products not issued ahead (start of the stream, or a group whose next item was
+            // too far away when it finished the one before)
+#pragma unroll
+            for (int x = 0; x < 2; ++x) {
+                bool& ahead = x ? ahead1 : ahead0;
+                if (c.j < c.it.nTg[x] && ok) {
+                    if (!ahead) issueQK(x, c.it, c.j, c.g);
+                    ahead = false;
                 }
-                __syncwarp();
-                if (gq) ++qkCnt1; else ++qkCnt0;
-                qk.nextTile(p, total, numTiles);
-            } else {
-                const int st = pv.g % kVStages, gp = pv.j & 1;
-                ok = mbarWait(&s->pFull[gp], (gp ? pvCnt1 : pvCnt0) & 1, &s->dead, errFlag, 5);
-                if (ok) ok = mbarWait(&s->vFull[st], (pv.g / kVStages) & 1, &s->dead, errFlag, 6);
-                // the accumulators are free once the output of the item before was read from them
-                if (ok && pv.j < 2 && pv.n >= 1) ok = mbarWait(&s->oEmpty, (pv.n - 1) & 1, &s->dead, errFlag, 15);
+            }
+            if (!ok) break;
+            const int st = c.g % kVStages;
+            // the next item of the stream, for the groups that finish this one here
+            Cursor nx = c;
+            const bool lastOfItem = c.j == c.it.nT - 1;
+            const bool endsHere0 = c.j == c.it.nTg[0] - 1, endsHere1 = c.j == c.it.nTg[1] - 1;
+            if (endsHere0 || endsHere1) {
+                nx.g = c.g + (c.it.nT - 1 - c.j);      // last tile of this item
+                nx.j = c.it.nT - 1;
+                nx.nextTile(p, total, numPairs);       // first tile of the next item (or the end)
+            }
+#pragma unroll
+            for (int x = 0; x < 2; ++x) {
+                if (!(c.j < c.it.nTg[x]) || !ok) continue;
+                int& steps = x ? steps1 : steps0;
+                ok = mbarWait(&s->pFull[x], steps & 1, &s->dead, errFlag, 5);
+                if (ok) ok = mbarWait(&s->vFull[st], (c.g / kVStages) & 1, &s->dead, errFlag, 6);
+                // the accumulator is free once the output of the group's item before was read from it
+                const int itemsX = x ? items1 : items0;
+                if (ok && c.j == 0 && itemsX >= 2) ok = mbarWait(&s->oEmpty[x], (itemsX - 2) & 1, &s->dead, errFlag, 15);
                 ok = __all_sync(0xFFFFFFFFu, ok);
                 if (!ok) break;
                 tcFenceAfter();
                 const uint32_t vLo = descLo(smemAddr(s->v[st]), kHalfBytes);
-                const uint32_t sCol = tmemS(gp), dO = tmemO(gp);
-                const uint32_t first = pv.j >= 2 ? 1u : 0u;
-                const bool lo = BF16 && pv.it.useLo;
+                const uint32_t sCol = tmemS(x), dO = tmemO(x);
+                const uint32_t first = c.j > 0 ? 1u : 0u;
+                const bool lo = BF16 && c.it.useLo[x];
+                const bool lastUser = x == 1 || !(c.j < c.it.nTg[1]);
                 uint64_t dv[kKeys / 16];
 #pragma unroll
                 for (int ks = 0; ks < kKeys / 16; ++ks) dv[ks] = desc64(vLo + ks * 128, hiK);
@@ -692,84 +727,143 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                         for (int ks = 0; ks < kKeys / 16; ++ks)
                             ummaTs(dO, sCol + 32u * (ks >> 1) + 8u * (ks & 1) + 16u, dv[ks], idescO, 1u);
                     }
-                    ummaCommit(&s->pvDone[gp]);
-                    ummaCommit(&s->vEmpty[st]);
+                    ummaCommit(&s->pvDone[x]);
+                    if (lastUser) ummaCommit(&s->vEmpty[st]);
                 }
                 __syncwarp();
-                if (gp) ++pvCnt1; else ++pvCnt0;
-                pv.nextTile(p, total, numTiles);
+                ++steps;
+                // the group's next S product
+                bool& ahead = x ? ahead1 : ahead0;
+                if (c.j + 1 < c.it.nTg[x]) {
+                    issueQK(x, c.it, c.j + 1, c.g + 1);
+                    ahead = true;
+                } else if (nx.valid && nx.it.nTg[x] > 0 && nx.g <= c.g + 2 &&
+                           __all_sync(0xFFFFFFFFu, mbarTry(&s->qFull[x], (x ? items1 : items0) & 1))) {
+                    // (only if the query tile is already there: the other group must not wait for it)
+                    issueQK(x, nx.it, 0, nx.g);
+                    ahead = true;
+                }
             }
+            (void)lastOfItem;
+            c.nextTile(p, total, numPairs);
         }
     } else if (warp == kStoreWarp) {
         // ------------------------------------------------------------ output store
-        // The softmax warps leave the finished rows of item n in its query buffer, in the
-        // swizzled layout of a TMA box; one thread sends them to global memory and hands
-        // the buffer back to the producer once the copy has read it.  Tiles with fewer
-        // than 128 rows of this sequence were written by the softmax warps themselves (a
-        // box would run into the next sequence's rows).
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
+        // The softmax groups leave the finished rows of a query tile in the staging buffer, in
+        // the swizzled layout of a TMA box, taking turns in stream order (group 0, then group 1
+        // of each item); one thread sends them to global memory and hands the buffer on once
+        // the copy has read it.  Tiles with fewer than 128 rows of the sequence are written by
+        // the softmax threads themselves (a box would run into the next sequence's rows) and
+        // take no turn.
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
         if (!live) goto done;
-        int n = 0;
+        int turn = 0;
         bool ok = true;
         for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
             Item it;
-            if (!loadItem(p, w, numTiles, it) || it.nT == 0) continue;
-            const int qb = n & 1;
-            ok = mbarWait(&s->oStaged[qb], (n >> 1) & 1, &s->dead, errFlag, 16);
-            ok = __all_sync(0xFFFFFFFFu, ok);
-            if (!ok) break;
-            if (lane == 0) {
-                if (it.rowsValid == kRows) {
-                    tmaStore3d(&mapO, s->q[qb], 0, it.head, it.rowBase);
-                    tmaStore3d(&mapO, s->q[qb] + kHalfBytes, 64, it.head, it.rowBase);
+            if (!loadItem(p, w, numPairs, it)) continue;
+#pragma unroll
+            for (int x = 0; x < 2; ++x) {
+                if (it.nTg[x] == 0 || it.rowsValid[x] < kRows || !ok) continue;
+                ok = mbarWait(&s->oStaged, turn & 1, &s->dead, errFlag, 16);
+                ok = __all_sync(0xFFFFFFFFu, ok);
+                if (!ok) break;
+                if (lane == 0) {
+                    tmaStore3d(&mapO, s->stage, 0, it.head, it.rowBase[x]);
+                    tmaStore3d(&mapO, s->stage + kHalfBytes, 64, it.head, it.rowBase[x]);
                     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                     asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                    mbarArrive(&s->stageFree[turn & 1]);
                 }
-                mbarArrive(&s->qEmpty[qb]);
+                ++turn;
             }
-            ++n;
         }
         if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     } else {
         // ------------------------------------------------------------ softmax warps
-        // Two groups of 128 threads; group grp takes the key tiles j with j & 1 == grp of
-        // every item, thread t of a group owns query row t (all 128 key columns of a tile):
-        // no exchange between threads.  Each group keeps its own running maximum, sum and
-        // accumulator; the two are merged when the item is written out.  A tile is read
-        // from tensor memory twice, 32 columns at a time: once for the maximum, once for
-        // the weights.
+        // Two groups of 128 threads; group x owns query tile x of every item, thread t of a
+        // group owns row t of it: all 128 key columns of a tile in registers, no exchange
+        // between threads.  While one group turns its S into P, the tensor pipe works for the
+        // other.
         asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
         if (!live) goto done;
-        const int grp = warp >> 2, t = (warp & 3) * 32 + lane;
+        const int x = warp >> 2, t = (warp & 3) * 32 + lane;
+        const bool loader = t == 0;                     // fetches the group's query tiles
         const uint32_t laneBase = static_cast<uint32_t>((warp & 3) * 32) << 16;
-        const uint32_t sAddr = tmemS(grp) + laneBase, oAddr = tmemO(grp) + laneBase;
+        const uint32_t sAddr = tmemS(x) + laneBase, oAddr = tmemO(x) + laneBase;
         bool ok = true;
-        int k = 0;          // key tiles this group has done (phase of its barriers)
+        int steps = 0;      // key tiles this group has done (phase of its barriers)
+        int items = 0;      // items this group has taken part in
         int g0 = 0;         // key tiles of the stream before the current item
-        int n = 0;          // items with keys before the current one
+        int turn = 0;       // staging turns of the stream before the current item
+        // the next query tile is brought into L2 an item early, so that its fetch during the
+        // last key tile of the item before it is short
+        auto prefetchQ = [&](const Item& it) {
+            const int rowBase = x ? it.rowBase[1] : it.rowBase[0];
+            asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(&mapQ), "r"(0), "r"(it.head), "r"(rowBase) : "memory");
+            asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(&mapQ), "r"(64), "r"(it.head), "r"(rowBase) : "memory");
+        };
+        auto loadQ = [&](const Item& it) {
+            const int rowBase = x ? it.rowBase[1] : it.rowBase[0];
+            mbarExpectTx(&s->qFull[x], kTileBytes);
+            tmaLoad3d(s->q[x], &mapQ, &s->qFull[x], 0, it.head, rowBase);
+            tmaLoad3d(s->q[x] + kHalfBytes, &mapQ, &s->qFull[x], 64, it.head, rowBase);
+        };
+        // the first item the group takes part in: its query tile is fetched right away
+        int wNext = blockIdx.x;
+        Item nextIt;
+        auto seekNext = [&]() {                          // first item at or after wNext in which the group has key tiles
+            while (wNext < total) {
+                if (loadItem(p, wNext, numPairs, nextIt) && (x ? nextIt.nTg[1] : nextIt.nTg[0]) > 0) return true;
+                wNext += gridDim.x;
+            }
+            return false;
+        };
+        bool haveNext = seekNext();
+        if (haveNext && loader) loadQ(nextIt);
         for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
             Item it;
-            if (!loadItem(p, w, numTiles, it)) continue;
-            if (it.nT == 0) {
-                // rows that see no key at all: zeros (no other role takes part); each thread
-                // writes half of its row
-                if (t < it.rowsValid) {
+            if (!loadItem(p, w, numPairs, it)) continue;
+            // staging turns of this item that come before this group's
+            const bool turn0 = it.nTg[0] > 0 && it.rowsValid[0] == kRows, turn1 = it.nTg[1] > 0 && it.rowsValid[1] == kRows;
+            const int myTurn = turn + (x == 1 && turn0 ? 1 : 0);
+            turn += (turn0 ? 1 : 0) + (turn1 ? 1 : 0);
+            const int gBase = g0;
+            g0 += it.nT;
+            // this group's half of the item
+            const int rowsValid = x ? it.rowsValid[1] : it.rowsValid[0], nT = x ? it.nTg[1] : it.nTg[0];
+            const int rowBase = x ? it.rowBase[1] : it.rowBase[0], firstPos = x ? it.firstPos[1] : it.firstPos[0];
+            if (rowsValid == 0) continue;
+            if (nT == 0) {
+                // rows that see no key at all: zeros (no other role takes part)
+                if (t < rowsValid) {
                     uint4* out = reinterpret_cast<uint4*>(static_cast<unsigned char*>(p.out) +
-                                                          ((static_cast<int64_t>(it.rowBase) + t) * p.heads + it.head) * kHd * 2 + grp * 128);
+                                                          ((static_cast<int64_t>(rowBase) + t) * p.heads + it.head) * kHd * 2);
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) out[i] = make_uint4(0u, 0u, 0u, 0u);
+                    for (int i = 0; i < 16; ++i) out[i] = make_uint4(0u, 0u, 0u, 0u);
                 }
                 continue;
             }
-            const MaskInfo mk(it.ws, it.seqLen, it.firstPos + t, p.causal);
-            const bool useLo = BF16 && it.useLo;
+            // the item after this one in which the group has key tiles (its query tile is
+            // fetched during this item's last key tile)
+            wNext = w + gridDim.x;
+            haveNext = seekNext();
+            if (haveNext && loader) prefetchQ(nextIt);
+            TRACE(((warp & 3) == 0 ? x : 99), items, 0);
+            const MaskInfo mk(it.ws, it.seqLen, firstPos + t, p.causal);
+            const bool useLo = BF16 && (x ? it.useLo[1] : it.useLo[0]);
             float mUsed = -INFINITY, l = 0.f;
-            for (int j = grp; j < it.nT && ok; j += 2, ++k) {
+            for (int j = 0; j < nT && ok; ++j, ++steps) {
                 const int k0 = (it.tileLo + j) * kKeys;
-                const bool edge = k0 < it.ws || k0 + kKeys > it.seqLen || (p.causal && k0 + kKeys - 1 > it.firstPos);
-                ok = mbarWait(&s->sFull[grp], k & 1, &s->dead, errFlag, 7);
+                const bool edge = k0 < it.ws || k0 + kKeys > it.seqLen || (p.causal && k0 + kKeys - 1 > firstPos);
+                ok = mbarWait(&s->sFull[x], steps & 1, &s->dead, errFlag, 7);
                 if (!ok) break;
                 tcFenceAfter();
+                if (j == 0) TRACE(((warp & 3) == 0 ? x : 99), items, 1);
+                if (j == 1) TRACE(((warp & 3) == 0 ? x : 99), items, 6);
+                if (j == nT - 1) TRACE(((warp & 3) == 0 ? x : 99), items, 7);
+                // S of the item's last tile is there, so its query tile is no longer read
+                if (j == nT - 1 && haveNext && loader) loadQ(nextIt);
                 // ---- the whole row of scores into registers, then its maximum (the scale is positive)
                 uint32_t r0[32], r1[32], r2[32], r3[32];
                 tmemLd32NoWait(sAddr, r0);
@@ -788,15 +882,15 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 // exact either way, the final division uses the same reference.
                 bool raise = false;
                 float corr = 1.f;
-                if (j < 2) mUsed = tmax;
+                if (j == 0) mUsed = tmax;
                 else if (tmax > mUsed + kRescaleThreshold) {
                     raise = true;
                     corr = ex2Approx(mUsed - tmax);
                     mUsed = tmax;
                 }
-                if (j >= 2 && __any_sync(0xFFFFFFFFu, raise)) {
-                    // the group's accumulator is complete up to its tile before (seen at the end of
-                    // that tile, before this tile's S could be made)
+                if (j >= 1 && __any_sync(0xFFFFFFFFu, raise)) {
+                    // The accumulator is complete up to the tile before: this tile's S product was
+                    // issued behind that P V product and has been seen complete.
 #pragma unroll 1
                     for (int c = 0; c < 4; ++c) {
                         uint32_t o[32];
@@ -809,7 +903,7 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                     l *= corr;
                 }
                 // ---- the weights replace the scores in tensor memory: per 32 keys 16 columns of
-                // packed pairs (plus 16 columns of their low-order parts where the item needs
+                // packed pairs (plus 16 columns of their low-order parts where the tile needs
                 // 16-bit weights)
                 const float negM = mUsed == -INFINITY ? 0.f : -mUsed;
                 {
@@ -836,8 +930,9 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 }
                 tmemStWait();
                 if (k0 + kKeys > it.seqLen) {
-                    // rows of V past the end of the sequence may hold anything: zero them
-                    const int gt = g0 + j, st = gt % kVStages;
+                    // rows of V past the end of the sequence may hold anything: zero them (both
+                    // groups may, with the same zeros)
+                    const int gt = gBase + j, st = gt % kVStages;
                     ok = mbarWait(&s->vFull[st], (gt / kVStages) & 1, &s->dead, errFlag, 9);
                     if (!ok) break;
                     if (k0 + t >= it.seqLen) {
@@ -849,70 +944,64 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 }
                 tcFenceBefore();
-                mbarArrive(&s->pFull[grp]);
-                // Every thread sees every P V product of its group complete, in order: a wait on
-                // a phase parity is only good for one step back, and the next product cannot
-                // complete before this thread's next arrival.
-                ok = mbarWait(&s->pvDone[grp], k & 1, &s->dead, errFlag, 10);
+                mbarArrive(&s->pFull[x]);
             }
             if (!ok) break;
-            // ---- output of the item: (O_0 2^(m_0 - m) + O_1 2^(m_1 - m)) / (l_0 2^(m_0 - m) + l_1 2^(m_1 - m)).
-            // Thread t of group grp writes columns [64 grp, 64 grp + 64) of row t.
-            tcFenceAfter();
-            s->rowState[grp][t] = make_float2(mUsed, l);
-            mbarArrive(&s->stateReady);
-            ok = mbarWait(&s->stateReady, n & 1, &s->dead, errFlag, 17);
+            TRACE(((warp & 3) == 0 ? x : 99), items, 2);
+            // ---- output of the tile: O / l.  The last P V product: the one before it is known
+            // complete (the last S product came behind it), so the phase parity is unambiguous.
+            ok = mbarWait(&s->pvDone[x], (steps - 1) & 1, &s->dead, errFlag, 10);
             if (!ok) break;
-            const float2 other = s->rowState[grp ^ 1][t];
-            const float m = fmaxf(mUsed, other.x);
-            const float wMine = m == -INFINITY ? 0.f : ex2Approx(mUsed - m), wOther = m == -INFINITY ? 0.f : ex2Approx(other.x - m);
-            const float lt = l * wMine + other.y * wOther;
-            const float inv = lt > 0.f ? 1.f / lt : 0.f;
-            const float f0 = (grp == 0 ? wMine : wOther) * inv, f1 = (grp == 0 ? wOther : wMine) * inv;
-            const bool has1 = it.nT >= 2;                     // group 1 had a tile: its accumulator holds numbers
-            unsigned char* stage = s->q[n & 1] + grp * kHalfBytes + t * 128;
+            tcFenceAfter();
+            TRACE(((warp & 3) == 0 ? x : 99), items, 3);
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            const bool full = rowsValid == kRows;
+            if (full && myTurn >= 1) {
+                // This group's turn at the staging buffer comes when the turn before it is
+                // complete.  (One barrier per turn parity; the turn three before is known
+                // complete, because the turn two before was staged before this group got here.)
+                ok = mbarWait(&s->stageFree[(myTurn - 1) & 1], ((myTurn - 1) >> 1) & 1, &s->dead, errFlag, 17);
+                if (!ok) break;
+            }
+            TRACE(((warp & 3) == 0 ? x : 99), items, 4);
+            unsigned char* out = static_cast<unsigned char*>(p.out) + ((static_cast<int64_t>(rowBase) + t) * p.heads + it.head) * kHd * 2;
+            {
+                uint32_t o0[32], o1[32], o2[32], o3[32];
+                tmemLd32NoWait(oAddr, o0);
+                tmemLd32NoWait(oAddr + 32u, o1);
+                tmemLd32NoWait(oAddr + 64u, o2);
+                tmemLd32NoWait(oAddr + 96u, o3);
+                tmemLdWait();
+                auto put = [&](const uint32_t (&o)[32], int c) {
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                uint32_t o0[32], o1[32];
-                tmemLd32(tmemO(0) + laneBase + 64u * grp + 32u * c, o0);
-                if (has1) tmemLd32(tmemO(1) + laneBase + 64u * grp + 32u * c, o1);
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        uint32_t wv[4];
 #pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    uint32_t wv[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int i = 8 * q4 + 2 * e;
-                        float a = __uint_as_float(o0[i]) * f0, b = __uint_as_float(o0[i + 1]) * f0;
-                        if (has1) {
-                            a = fmaf(__uint_as_float(o1[i]), f1, a);
-                            b = fmaf(__uint_as_float(o1[i + 1]), f1, b);
-                        }
-                        wv[e] = pack16<BF16>(a, b);
+                        for (int e = 0; e < 4; ++e)
+                            wv[e] = pack16<BF16>(__uint_as_float(o[8 * q4 + 2 * e]) * inv, __uint_as_float(o[8 * q4 + 2 * e + 1]) * inv);
+                        const int chunk = c * 4 + q4;          // 16-byte chunk of the 256-byte row
+                        if (full)
+                            *reinterpret_cast<uint4*>(s->stage + (chunk >> 3) * kHalfBytes + t * 128 + (((chunk & 7) ^ (t & 7)) << 4)) =
+                                make_uint4(wv[0], wv[1], wv[2], wv[3]);
+                        else if (t < rowsValid)
+                            *reinterpret_cast<uint4*>(out + chunk * 16) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
                     }
-                    *reinterpret_cast<uint4*>(stage + (((c * 4 + q4) ^ (t & 7)) << 4)) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
-                }
+                };
+                put(o0, 0);
+                put(o1, 1);
+                put(o2, 2);
+                put(o3, 3);
             }
             tcFenceBefore();
-            __syncwarp();
-            if (lane == 0) mbarArrive(&s->oEmpty);                 // the accumulators may be overwritten
-            if (it.rowsValid < kRows) {
-                // ragged tile: this thread writes its own 128 bytes
-                if (t < it.rowsValid) {
-                    uint4* out = reinterpret_cast<uint4*>(static_cast<unsigned char*>(p.out) +
-                                                          ((static_cast<int64_t>(it.rowBase) + t) * p.heads + it.head) * kHd * 2 + grp * 128);
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) out[i] = *reinterpret_cast<const uint4*>(stage + ((i ^ (t & 7)) << 4));
-                }
-            }
-            // the buffer is next read (TMA store) and written (TMA load) by the asynchronous proxy
+            // the buffer is next read (TMA store) by the asynchronous proxy
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbarArrive(&s->oStaged[n & 1]);
-            // the other group must have read this group's row state before the next item overwrites it
-            mbarArrive(&s->stateRead);
-            ok = mbarWait(&s->stateRead, n & 1, &s->dead, errFlag, 18);
-            g0 += it.nT;
-            ++n;
+            if (lane == 0) {
+                mbarArrive(&s->oEmpty[x]);                  // the accumulator may be overwritten
+                if (full) mbarArrive(&s->oStaged);
+            }
+            TRACE(((warp & 3) == 0 ? x : 99), items, 5);
+            ++items;
         }
     }
 
@@ -992,7 +1081,7 @@ cudaError_t launchPrefillTensor(const PrefillParams& p, int totalRows, int* errF
     cudaError_t e = cudaGetDevice(&dev);
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return e;
-    const long long items = static_cast<long long>((p.maxQLen + kRows - 1) / kRows) * p.heads * p.numSeqs;
+    const long long items = static_cast<long long>(((p.maxQLen + kRows - 1) / kRows + 1) / 2) * p.heads * p.numSeqs;
     if (items <= 0 || items > 0x7FFFFFFF) return cudaErrorInvalidValue;
     dim3 grid(static_cast<unsigned>(items < sms ? items : sms));
     if (p.dtype == kBF16) {
