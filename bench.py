@@ -529,7 +529,7 @@ def run_prefill(args):
 
 # ------------------------------------------- long-context FP8 decode (c4)
 
-C4_SEQS, C4_LO, C4_HI, C4_WINDOW, C4_HEADS = 64, 32768, 131072, 4096, 64
+C4_SEQS, C4_LO, C4_HI, C4_WINDOW, C4_HEADS, C4_CHUNK = 64, 32768, 131072, 4096, 64, 2048
 
 
 def run_decode_fp8(args):
@@ -556,7 +556,7 @@ def run_decode_fp8(args):
     n_seq = min(C4_SEQS, args.batch) if args.batch != 256 else C4_SEQS
     lens = rng.integers(C4_LO, C4_HI + 1, size=n_seq).astype(np.int64)
     nblk = (lens + BLOCK - 1) // BLOCK
-    cache = pam.KVCacheManager(engine, int(nblk.sum()) + 256, BLOCK, HEAD_DIM, KV_HEADS, DT.float8)
+    cache = pam.KVCacheManager(engine, int(nblk.sum()) + 256 + C4_CHUNK // BLOCK, BLOCK, HEAD_DIM, KV_HEADS, DT.float8)
     gen = torch.Generator(device=dev)
     visible = 0
     for sid in range(n_seq):
@@ -604,16 +604,68 @@ def run_decode_fp8(args):
     err = float(np.abs(out[sid:sid + 1].float().cpu().numpy() - ref).max())
     assert err <= 1e-2, f"FP8 decode differs from the oracle by {err}"
 
+    # ---- the waiting sequence of the whole step (`step_c4`): its first 2048-token chunk is
+    # appended (quantised to FP8) and prefilled in the same step as the 64 decodes
+    whole = args.workload == "step_c4"
+    step_tokens = n_seq
+    decode_only = lambda: engine.decode(req)
+    step = decode_only
+    if whole:
+        new_id = n_seq
+        sched = pam.ContinuousBatchingScheduler(n_seq + 1, n_seq + 1)
+        ids = [sched.addRequest(int(l), 1) for l in lens]
+        for q_s in sched.step():
+            sched.markPrefilled(q_s.id)
+        wid = sched.addRequest(8192, 1)
+        batch = [q_s.id for q_s in sched.step()]              # Scheduler.swift:78-114: waiting first, then running
+        assert batch == [wid] + ids and sched.waitingCount == 0, "scheduler batch order"
+        cache.allocateSequence(new_id)
+        cache.appendTokens(new_id, C4_CHUNK)
+        gen.manual_seed(1004 * 1000 + new_id)
+        kv_new = torch.randn((2, C4_CHUNK, KV_HEADS, HEAD_DIM), generator=gen, device=dev).to(torch.float16)
+        k_new, v_new = kv_new[0].contiguous(), kv_new[1].contiguous()
+        q_new = torch.randn((C4_CHUNK, C4_HEADS, HEAD_DIM), generator=gen, device=dev).to(torch.float16)
+        o_new = torch.empty_like(q_new)
+        t_new_h, _ = cache.batchTables([new_id], C4_CHUNK // BLOCK)
+        t_new = torch.from_numpy(t_new_h).to(dev)
+
+        def step():
+            engine.appendKV(cache, new_id, k_new, v_new, 0, C4_CHUNK, C4_HEADS)
+            engine.prefillBatch(q_new, cache.kPoolBuffer, cache.vPoolBuffer, t_new, o_new, [C4_CHUNK], [0], [C4_CHUNK],
+                                C4_CHUNK // BLOCK, layer, True, cache.kScaleBuffer, cache.vScaleBuffer)
+            engine.decode(req)
+
+        step()
+        engine.synchronize()
+        prefill_tensor = None
+        # correctness guard for the chunk: a few rows against the oracle on the quantised pages
+        used_n = t_new_h[0]
+        kc2 = np.zeros((len(used_n), KV_HEADS, BLOCK, HEAD_DIM), np.uint8)
+        vc2 = np.zeros_like(kc2)
+        ks2 = np.zeros((len(used_n), KV_HEADS), np.float16)
+        vs2 = np.zeros_like(ks2)
+        for i, b in enumerate(used_n):
+            lib.pamc_memcpy(engine._ctx, kc2[i].ctypes.data, kp + int(b) * page, page, 1)
+            lib.pamc_memcpy(engine._ctx, vc2[i].ctypes.data, vp + int(b) * page, page, 1)
+            lib.pamc_memcpy(engine._ctx, ks2[i].ctypes.data, ksp + int(b) * KV_HEADS * 2, KV_HEADS * 2, 1)
+            lib.pamc_memcpy(engine._ctx, vs2[i].ctypes.data, vsp + int(b) * KV_HEADS * 2, KV_HEADS * 2, 1)
+        r0, nr = C4_CHUNK - 8, 8
+        refp = co.prefill(q_new[r0:r0 + nr].cpu().numpy(), kc2, vc2, np.arange(len(used_n), dtype=np.int32), C4_CHUNK,
+                          KV_HEADS, BLOCK, 2, q_start=r0, k_scale=ks2.view(np.uint16), v_scale=vs2.view(np.uint16))
+        errp = float(np.abs(o_new[r0:r0 + nr].float().cpu().numpy() - refp).max())
+        assert errp <= 1e-2, f"FP8 prefill chunk differs from the oracle by {errp}"
+        step_tokens = n_seq + C4_CHUNK
+
     engine.setAsync(True)
     sampler = ClockSampler(0)
     sampler.start()
     warm = max(args.warmup, 3)
     for _ in range(warm):
-        engine.decode(req)
+        step()
     t_busy = time.perf_counter()
     while not args.profile and time.perf_counter() - t_busy < 0.5:
         for _ in range(10):
-            engine.decode(req)
+            step()
         torch.cuda.synchronize(dev)
         warm += 10
     torch.cuda.synchronize(dev)
@@ -621,29 +673,48 @@ def run_decode_fp8(args):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
     for _ in range(args.steps):
-        engine.decode(req)
+        step()
     e1.record(stream)
     torch.cuda.synchronize(dev)
     engine.synchronize()        # raises if a kernel of the timed region reported an error
     ms_step = e0.elapsed_time(e1) / args.steps
     launches = engine.kernelLaunches - launches0
+    ms_decode = ms_step
+    if whole:
+        # the decode launches alone, for the roofline of the HBM-bound kernel of the step
+        d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        d0.record(stream)
+        for _ in range(args.steps):
+            engine.decode(req)
+        d1.record(stream)
+        torch.cuda.synchronize(dev)
+        engine.synchronize()
+        ms_decode = d0.elapsed_time(d1) / args.steps
     clocks = sampler.stop()
     # visible tokens per sequence: tokens in blocks >= floor((L - W) / 16); K and V codes, scales, q, out, tables
     nvis = np.array([int(l) - ((int(l) - C4_WINDOW) // BLOCK) * BLOCK for l in lens])
     bytes_step = int(nvis.sum()) * 2 * KV_HEADS * HEAD_DIM + int(((nvis + BLOCK - 1) // BLOCK).sum()) * (KV_HEADS * 4 + 4) \
         + 2 * n_seq * C4_HEADS * HEAD_DIM * 2 + n_seq * 4
     peak, kind = measured_hbm_peak()
-    achieved = bytes_step / (ms_step * 1e-3) / 1e9
-    line = {"metric": "paged decode tokens/s", "value": n_seq / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": 1,
+    achieved = bytes_step / (ms_decode * 1e-3) / 1e9
+    line = {"metric": "step tokens/s" if whole else "paged decode tokens/s", "value": step_tokens / (ms_step * 1e-3),
+            "unit": "tokens/s", "n_gpus": 1,
             "steps": args.steps, "warmup": warm, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "fp8-e4m3 KV, f16 q/out", "data": "synthetic",
-            "config": {"workload": f"decode_c4: {n_seq} seqs, context U[32768,131072], window 4096, FP8 e4m3 KV with "
+            "config": {"workload": ("step_c4: one scheduler step = append + prefill of a 2048-token chunk of a new "
+                                    "sequence, and " if whole else "decode_c4: ") +
+                                   f"{n_seq} seqs, context U[32768,131072], window 4096, FP8 e4m3 KV with "
                                    "(block, kv_head) scales, 64 q / 8 kv heads, head_dim 128, block 16", "seed": 1004,
                        "l2": "window bytes per step (0.54 GB) exceed L2; contexts are resident, only the window is read"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": f"{kind} copy bandwidth", "kernel": "decodeSplitFp8Kernel (+ decodeMergeKernel)",
                          "algorithmic_bytes_per_launch": bytes_step, "traffic": None},
             "gpu_launches": int(launches), "clocks": clocks}
+    if whole:
+        pf_flops = C4_HEADS * (C4_CHUNK * (C4_CHUNK + 1) // 2) * 4 * HEAD_DIM
+        line["step_parts"] = {"decode_ms": ms_decode, "append_and_prefill_ms": ms_step - ms_decode,
+                              "prefill_chunk_gflop": pf_flops / 1e9,
+                              "prefill_path": "FP8 pages dequantised to float16 scratch, then prefillTcKernel"}
     print(json.dumps(line))
     cache.close()
     engine.close()
@@ -657,7 +728,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=BATCH,
                     help="number of sequences (default: the workload's 256; smaller values are for profiler captures)")
-    ap.add_argument("--workload", default="decode_c2", choices=["decode_c2", "prefill_c3", "decode_c4"],
+    ap.add_argument("--workload", default="decode_c2", choices=["decode_c2", "prefill_c3", "decode_c4", "step_c4"],
                     help="decode_c2 is the headline workload; prefill_c3 reports prefill TFLOP/s (1 GPU)")
     ap.add_argument("--profile", action="store_true",
                     help="profiler run: no clock-settling loop, no end-to-end leg, no CPU baseline")
@@ -667,7 +738,7 @@ def main():
         globals()["PF_SEQS"] = args.batch
     if args.workload == "prefill_c3" and args.impl == "ours":
         run_prefill(args)
-    elif args.workload == "decode_c4" and args.impl == "ours":
+    elif args.workload in ("decode_c4", "step_c4") and args.impl == "ours":
         run_decode_fp8(args)
     elif args.impl == "reference":
         run_reference(args)

@@ -110,5 +110,14 @@ __device__ __forceinline__ int prefillMeta(const PrefillParams& p, int which, in
 #endif
 cudaError_t launchPrefill(const PrefillParams& p, int smCount, cudaStream_t stream, int* launches,
                           bool* usedTensorPath);
+// FP8 KV on the tensor-core prefill path: the pages the launch can see (blocks
+// windowStart / blockSize .. ceil(seqLen / blockSize) of every sequence, at most
+// `maxCount` each) are dequantised to float16 with the reference's all-half chain
+// (kernels.metal:553-562) into scratch pools of numSeqs * maxCount blocks, and
+// `stagedTables` ([numSeqs][maxNumBlocks], zeroed by the caller) gets the scratch block
+// of every such table entry.  `meta` holds seqLens and windowStarts (numSeqs each).
+bool prefillFp8StagingApplies(const PrefillParams& p);
+cudaError_t launchFp8StagePages(const PrefillParams& p, const int32_t* seqLens, const int32_t* windowStarts, int maxCount,
+                                void* kOut, void* vOut, int32_t* stagedTables, cudaStream_t stream, int* launches);
 
 }  // namespace pam

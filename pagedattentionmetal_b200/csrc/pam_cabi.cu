@@ -617,6 +617,34 @@ int32_t prefillImpl(Context* c, const PamLayerSpec& l, const PamBuffer& q, const
         p.forceGeneral = c->forceGeneralPrefill ? 1 : 0;
         p.exactWeights = c->exactWeights;
         int launches = 0;
+        if (pam::prefillFp8StagingApplies(p)) {
+            // FP8 KV: the pages this launch can see are dequantised to float16 scratch pools
+            // (the reference's all-half chain), which the tensor-core kernel then reads
+            // through a table of scratch block numbers.
+            int maxCount = 0;
+            for (int i = 0; i < n; ++i) {
+                const int lo = meta[static_cast<size_t>(4) * n + i] / l.block_size;
+                const int hi = (meta[i] + l.block_size - 1) / l.block_size;
+                maxCount = std::max(maxCount, hi - lo);
+            }
+            const size_t poolBytes = static_cast<size_t>(n) * maxCount * l.num_kv_heads * l.block_size * l.head_dim * 2;
+            if (maxCount > 0 && poolBytes <= (size_t(1) << 30)) {
+                const size_t tableBytes = static_cast<size_t>(n) * maxNumBlocks * sizeof(int32_t);
+                void* kOut = c->arena.take(poolBytes);
+                void* vOut = c->arena.take(poolBytes);
+                int32_t* staged = static_cast<int32_t*>(c->arena.take(tableBytes));
+                const int32_t* dm = static_cast<const int32_t*>(st.upload(meta.data(), meta.size() * sizeof(int32_t)));
+                if (!kOut || !vOut || !staged || !st.ok()) return cudaErrorMemoryAllocation;
+                cudaError_t se = cudaMemsetAsync(staged, 0, tableBytes, c->stream);
+                if (se == cudaSuccess)
+                    se = pam::launchFp8StagePages(p, dm, dm + static_cast<size_t>(4) * n, maxCount, kOut, vOut, staged, c->stream, &launches);
+                if (se != cudaSuccess) return se;
+                p.dtype = PAM_DTYPE_F16;
+                p.kPool = kOut; p.vPool = vOut; p.tables = staged;
+                p.kScale = nullptr; p.vScale = nullptr;
+                p.poolBlocks = n * maxCount;
+            }
+        }
         cudaError_t e = pam::launchPrefill(p, c->smCount, c->stream, &launches, &tensorPath);
         c->launches += launches;
         if (e == cudaSuccess && tensorPath) {

@@ -173,6 +173,63 @@ cudaError_t launchGeneral(const PrefillParams& p, cudaStream_t stream, int* laun
     return cudaGetLastError();
 }
 
+// One CTA per (visible block of a sequence): codes -> float16 for all KV heads of the
+// block, K and V, 16 codes per thread and step.
+__global__ void __launch_bounds__(256)
+fp8StagePagesKernel(const uint8_t* __restrict__ kCodes, const uint8_t* __restrict__ vCodes, const __half* __restrict__ kScale,
+                    const __half* __restrict__ vScale, const int32_t* __restrict__ tables, const int32_t* __restrict__ seqLens,
+                    const int32_t* __restrict__ windowStarts, __half* __restrict__ kOut, __half* __restrict__ vOut,
+                    int32_t* __restrict__ stagedTables, int maxNumBlocks, int maxCount, int kvHeads, int blockSize, int headDim,
+                    int poolBlocks) {
+    const int seq = blockIdx.y, c = blockIdx.x;
+    const int lo = windowStarts[seq] / blockSize, hi = (seqLens[seq] + blockSize - 1) / blockSize;
+    const int b = lo + c;
+    if (b >= hi || b >= maxNumBlocks) return;
+    const int src = min(max(tables[static_cast<int64_t>(seq) * maxNumBlocks + b], 0), poolBlocks - 1);
+    const int dst = seq * maxCount + c;
+    if (threadIdx.x == 0) stagedTables[static_cast<int64_t>(seq) * maxNumBlocks + b] = dst;
+    const int perHead = blockSize * headDim;                 // elements of one (block, kv head)
+    const int chunks = kvHeads * perHead / 16;
+    for (int i = threadIdx.x; i < 2 * chunks; i += blockDim.x) {
+        const bool isV = i >= chunks;
+        const int ch = isV ? i - chunks : i;
+        const int kvh = ch * 16 / perHead;
+        const int64_t off = static_cast<int64_t>(src) * kvHeads * perHead + static_cast<int64_t>(ch) * 16;
+        const uint4 codes = *reinterpret_cast<const uint4*>((isV ? vCodes : kCodes) + off);
+        const __half scale = (isV ? vScale : kScale)[src * kvHeads + kvh];
+        const uint8_t* cb = reinterpret_cast<const uint8_t*>(&codes);
+        __align__(16) __half h[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) h[e] = __float2half_rn(dequantE4m3(cb[e], scale));   // exact: the value is a half
+        uint4* out = reinterpret_cast<uint4*>((isV ? vOut : kOut) + static_cast<int64_t>(dst) * kvHeads * perHead + static_cast<int64_t>(ch) * 16);
+        out[0] = *reinterpret_cast<const uint4*>(h);
+        out[1] = *reinterpret_cast<const uint4*>(h + 8);
+    }
+}
+
+}  // namespace
+
+bool prefillFp8StagingApplies(const PrefillParams& p) {
+    if (p.dtype != kFP8 || p.forceGeneral || !p.errFlag || !p.kScale || !p.vScale) return false;
+    PrefillParams f = p;
+    f.dtype = kF16;
+    return prefillTensorPathApplies(f) && (p.blockSize * p.headDim) % 16 == 0;
+}
+
+cudaError_t launchFp8StagePages(const PrefillParams& p, const int32_t* seqLens, const int32_t* windowStarts, int maxCount,
+                                void* kOut, void* vOut, int32_t* stagedTables, cudaStream_t stream, int* launches) {
+    if (maxCount <= 0 || p.numSeqs <= 0) return cudaSuccess;
+    dim3 grid(static_cast<unsigned>(maxCount), static_cast<unsigned>(p.numSeqs));
+    fp8StagePagesKernel<<<grid, 256, 0, stream>>>(static_cast<const uint8_t*>(p.kPool), static_cast<const uint8_t*>(p.vPool),
+                                                  static_cast<const __half*>(p.kScale), static_cast<const __half*>(p.vScale),
+                                                  p.tables, seqLens, windowStarts, static_cast<__half*>(kOut),
+                                                  static_cast<__half*>(vOut), stagedTables, p.maxNumBlocks, maxCount, p.kvHeads,
+                                                  p.blockSize, p.headDim, p.poolBlocks);
+    if (launches) *launches += 1;
+    return cudaGetLastError();
+}
+
+namespace {
 }  // namespace
 
 cudaError_t launchPrefill(const PrefillParams& p, int smCount, cudaStream_t stream, int* launches,

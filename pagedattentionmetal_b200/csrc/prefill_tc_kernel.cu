@@ -74,22 +74,14 @@ constexpr int kShortRowKeys = 256;
 constexpr long long kWaitCycles = 400000000LL;         // ~0.2 s
 
 #ifdef PAM_PREFILL_TRACE
-// Instrumented build only: CTA 0 leaves clock stamps [role][tile][event] in global memory.
-constexpr int kTraceRoles = 4, kTraceTiles = 32, kTraceEvents = 12;
-__device__ long long gTrace[kTraceRoles * kTraceTiles * kTraceEvents];
+// Instrumented build only (-DPAM_PREFILL_TRACE): every CTA leaves the wall-clock time and the
+// SM cycle count of its start and end in global memory, for the per-CTA cost model.
 __device__ unsigned long long gCtaTimes[4 * 256];      // start and end of every CTA: nanoseconds, then SM cycles
 __device__ __forceinline__ unsigned long long globalTimerNs() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-#define TRACE(role, tile, event)                                                                        \
-    do {                                                                                                \
-        if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (role) < kTraceRoles && (tile) < kTraceTiles) \
-            gTrace[((role) * kTraceTiles + (tile)) * kTraceEvents + (event)] = clock64();               \
-    } while (0)
-#else
-#define TRACE(role, tile, event)
 #endif
 
 struct Smem {
@@ -179,19 +171,10 @@ __device__ __forceinline__ void tmaStore3d(const CUtensorMap* map, const void* s
                  : "memory");
 }
 
-// Shared-memory matrix descriptor (128-byte swizzle, descriptor version 1).
-// lbo/sbo in bytes.  K-major operands: sbo = 1024 (eight 128-byte rows),
-// lbo unused (1).  MN-major operand (V): lbo = distance between 64-element
-// column blocks, sbo = 1024 (eight keys).
-__device__ __forceinline__ uint64_t makeDesc(uint32_t addr, uint32_t lboBytes, uint32_t sboBytes) {
-    uint64_t d = (addr & 0x3FFFFu) >> 4;
-    d |= static_cast<uint64_t>((lboBytes >> 4) & 0x3FFFu) << 16;
-    d |= static_cast<uint64_t>((sboBytes >> 4) & 0x3FFFu) << 32;
-    d |= 1ull << 46;       // version
-    d |= 2ull << 61;       // SWIZZLE_128B
-    return d;
-}
-
+// Shared-memory matrix descriptors (128-byte swizzle, descriptor version 1): start address,
+// leading and stride byte offsets in 16-byte units.  K-major operands: stride offset 1024
+// (eight 128-byte rows), leading offset unused.  MN-major operand (V): leading offset =
+// distance between 64-element column blocks, stride offset 1024 (eight keys).
 // The two halves of a descriptor: the high word is the same for every tile of a
 // layout, the low word is the start address (in 16-byte units) plus the LBO
 // field, so that stepping through a tile is one integer add on the low word.
@@ -283,22 +266,6 @@ __device__ __forceinline__ void tmemSt16(uint32_t taddr, const uint32_t (&r)[32]
           "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
         : "memory");
 }
-__device__ __forceinline__ uint32_t tmemLd1(uint32_t taddr) {
-    uint32_t v;
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(v) : "r"(taddr));
-    return v;
-}
-__device__ __forceinline__ void tmemSt1(uint32_t taddr, uint32_t v) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "r"(v) : "memory");
-}
-// A float as bfloat16 bits, rounded towards +infinity, and back.  Used for the reference
-// maximum of a row: any value at or a little above the true maximum serves, as long as the
-// four threads of the row use the same one.
-__device__ __forceinline__ unsigned short bf16Up(float x) {
-    const uint32_t b = __float_as_uint(x);
-    return static_cast<unsigned short>(((b >> 31) ? b : b + 0xFFFFu) >> 16);
-}
-__device__ __forceinline__ float bf16ToFloat(unsigned short h) { return __uint_as_float(static_cast<uint32_t>(h) << 16); }
 __device__ __forceinline__ void tmemStWait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 template <bool BF16>
@@ -849,7 +816,6 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             wNext = w + gridDim.x;
             haveNext = seekNext();
             if (haveNext && loader) prefetchQ(nextIt);
-            TRACE(((warp & 3) == 0 ? x : 99), items, 0);
             const MaskInfo mk(it.ws, it.seqLen, firstPos + t, p.causal);
             const bool useLo = BF16 && (x ? it.useLo[1] : it.useLo[0]);
             float mUsed = -INFINITY, l = 0.f;
@@ -859,9 +825,6 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 ok = mbarWait(&s->sFull[x], steps & 1, &s->dead, errFlag, 7);
                 if (!ok) break;
                 tcFenceAfter();
-                if (j == 0) TRACE(((warp & 3) == 0 ? x : 99), items, 1);
-                if (j == 1) TRACE(((warp & 3) == 0 ? x : 99), items, 6);
-                if (j == nT - 1) TRACE(((warp & 3) == 0 ? x : 99), items, 7);
                 // S of the item's last tile is there, so its query tile is no longer read
                 if (j == nT - 1 && haveNext && loader) loadQ(nextIt);
                 // ---- the whole row of scores into registers, then its maximum (the scale is positive)
@@ -947,13 +910,11 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 mbarArrive(&s->pFull[x]);
             }
             if (!ok) break;
-            TRACE(((warp & 3) == 0 ? x : 99), items, 2);
             // ---- output of the tile: O / l.  The last P V product: the one before it is known
             // complete (the last S product came behind it), so the phase parity is unambiguous.
             ok = mbarWait(&s->pvDone[x], (steps - 1) & 1, &s->dead, errFlag, 10);
             if (!ok) break;
             tcFenceAfter();
-            TRACE(((warp & 3) == 0 ? x : 99), items, 3);
             const float inv = l > 0.f ? 1.f / l : 0.f;
             const bool full = rowsValid == kRows;
             if (full && myTurn >= 1) {
@@ -963,7 +924,6 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 ok = mbarWait(&s->stageFree[(myTurn - 1) & 1], ((myTurn - 1) >> 1) & 1, &s->dead, errFlag, 17);
                 if (!ok) break;
             }
-            TRACE(((warp & 3) == 0 ? x : 99), items, 4);
             unsigned char* out = static_cast<unsigned char*>(p.out) + ((static_cast<int64_t>(rowBase) + t) * p.heads + it.head) * kHd * 2;
             {
                 uint32_t o0[32], o1[32], o2[32], o3[32];
@@ -1000,7 +960,6 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 mbarArrive(&s->oEmpty[x]);                  // the accumulator may be overwritten
                 if (full) mbarArrive(&s->oStaged);
             }
-            TRACE(((warp & 3) == 0 ? x : 99), items, 5);
             ++items;
         }
     }
@@ -1104,10 +1063,5 @@ extern "C" int pamc_debug_cta_times(unsigned long long* out) {
     cudaDeviceSynchronize();
     cudaMemcpyFromSymbol(out, pam::gCtaTimes, sizeof(unsigned long long) * 1024);
     return 1024;
-}
-extern "C" int pamc_debug_trace_read(long long* out) {
-    cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(out, pam::gTrace, sizeof(long long) * pam::kTraceRoles * pam::kTraceTiles * pam::kTraceEvents);
-    return pam::kTraceRoles * pam::kTraceTiles * pam::kTraceEvents;
 }
 #endif

@@ -181,3 +181,24 @@ def test_reference_cabi_prefill(engine):
     assert_close(out.astype(np.float32), ref, DT.float16)
     assert engine.lastStats.sequenceLength == S and engine.lastStats.numBlocks == 5
     cache.close()
+
+
+@pytest.mark.parametrize("seq_len,window,q_start,q_len", [(700, 0, 0, 0), (1000, 256, 0, 0), (900, 300, 512, 388), (520, 64, 0, 0)])
+def test_prefill_fp8_tensor_path(engine, seq_len, window, q_start, q_len):
+    """FP8 KV with head_dim 128 goes through the tensor-core kernel: the visible pages are
+    dequantised to float16 first (dequant_fp8, kernels.metal:553-562), so the result obeys
+    the FP8 bound against the oracle, which dequantises the same way."""
+    case = PrefillCase(41, seq_len, 8, 2, 128, 16, DT.float8)
+    ref = case.oracle(window=window, q_start=q_start, q_len=q_len or None)
+    out = case.run(engine, window=window, q_start=q_start, q_len=q_len)
+    assert engine.lastStats.operation == pam.Operation.prefillMMA
+    lo = max(0, max(0, seq_len - window) - q_start) if window > 0 else 0     # rows before the window: don't-care
+    assert_close(out[lo:], ref[lo:], DT.float8)
+    # and the general kernel gives the same within the bound
+    engine.setPrefillTensorPath(False)
+    try:
+        gen = case.run(engine, window=window, q_start=q_start, q_len=q_len)
+        assert engine.lastStats.operation != pam.Operation.prefillMMA
+    finally:
+        engine.setPrefillTensorPath(True)
+    assert_close(gen[lo:], ref[lo:], DT.float8)
