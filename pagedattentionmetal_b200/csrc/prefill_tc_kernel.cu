@@ -31,9 +31,9 @@
 //                        the PV instructions, because 8-bit weights alone miss
 //                        the 2e-3 bound there.  Thread 0 of a group fetches the
 //                        group's next query tile by TMA during the last key
-//                        tile of the current one.  O / l goes to a staging
-//                        buffer in the layout of a TMA box, the groups taking
-//                        turns.
+//                        tile of the current one.  At the end of an item the
+//                        thread leaves its row's sum in shared memory and goes
+//                        on with the next item.
 //   warp 8               TMA producer of K: per key tile 8 pages (each 16 rows x
 //                        256 B, fetched as two 128-byte-swizzled boxes, one page
 //                        per lane) into a ring; completion on mbarriers.
@@ -44,9 +44,14 @@
 //                        and right behind it S = Q K^T of the group's next key
 //                        tile (8 x tcgen05.mma 128x128x16, both operands from
 //                        shared memory); tcgen05.commit signals the mbarriers.
-//   warp 11              TMA store of the staged rows.
+//   warps 12-15          output: once the last P V product of a group's tile is
+//                        complete, O / l goes from tensor memory to a staging
+//                        buffer in the layout of a TMA box and out with a TMA
+//                        store, then the accumulator goes back to the MMA
+//                        issuer.  This keeps the output off the softmax warps,
+//                        which are the busiest.
 //
-// The service warps hand registers to the softmax warps (setmaxnreg).
+// The service and output warps hand registers to the softmax warps (setmaxnreg).
 //
 // Every wait on an mbarrier is bounded; a wait that runs out raises a flag the
 // host reads and the CTA falls through to the common exit, where the tensor
@@ -91,8 +96,8 @@ struct Smem {
     unsigned char v[kVStages][kTileBytes];
     unsigned char stage[kTileBytes];           // finished rows of one group on their way out (TMA box layout)
     unsigned long long qFull[2], kFull[kKStages], kEmpty[kKStages], vFull[kVStages], vEmpty[kVStages];
-    unsigned long long sFull[2], pFull[2], pvDone[2], oEmpty[2];   // one of each per softmax group
-    unsigned long long oStaged, stageFree[2];
+    unsigned long long sFull[2], pFull[2], oFull[2], oEmpty[2], lReady[2];   // one of each per softmax group
+    float rowL[2][kRows];                      // [group][row]: sum of the weights of the item just finished
     uint32_t tmemBase;
     int dead;
 };
@@ -373,8 +378,8 @@ __device__ __forceinline__ float weightsRange(const uint32_t (&r)[32], uint32_t 
 
 constexpr int kGroupThreads = 128;                     // one thread per query row
 constexpr int kSoftmaxWarps = 8;                       // two groups of four warps
-constexpr int kKProducerWarp = 8, kVProducerWarp = 9, kMmaWarp = 10, kStoreWarp = 11;
-constexpr int kThreads = (kSoftmaxWarps + 4) * 32;
+constexpr int kKProducerWarp = 8, kVProducerWarp = 9, kMmaWarp = 10, kIdleWarp = 11, kOutputWarp0 = 12;
+constexpr int kThreads = (kSoftmaxWarps + 8) * 32;     // softmax, service and output warpgroups
 
 // One unit of work: two consecutive tiles of 128 query rows of one head of one sequence.
 // Softmax group x owns tile x of the pair: its own query tile, S buffer and accumulator;
@@ -494,21 +499,19 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
 
     if (threadIdx.x == kKProducerWarp * 32) asm volatile("prefetch.tensormap [%0];" ::"l"(&mapK) : "memory");
     if (threadIdx.x == kVProducerWarp * 32) asm volatile("prefetch.tensormap [%0];" ::"l"(&mapV) : "memory");
-    if (threadIdx.x == kStoreWarp * 32) asm volatile("prefetch.tensormap [%0];" ::"l"(&mapO) : "memory");
+    if (threadIdx.x == kOutputWarp0 * 32) asm volatile("prefetch.tensormap [%0];" ::"l"(&mapO) : "memory");
     if (threadIdx.x == 0 || threadIdx.x == kGroupThreads) asm volatile("prefetch.tensormap [%0];" ::"l"(&mapQ) : "memory");
     if (threadIdx.x == 0) {
         for (int i = 0; i < 2; ++i) {
             mbarInit(&s->qFull[i], 1);
             mbarInit(&s->sFull[i], 1);
             mbarInit(&s->pFull[i], kGroupThreads);
-            mbarInit(&s->pvDone[i], 1);
-            mbarInit(&s->oEmpty[i], kGroupThreads / 32);
+            mbarInit(&s->oFull[i], 1);
+            mbarInit(&s->oEmpty[i], 1);
+            mbarInit(&s->lReady[i], kGroupThreads);
         }
         for (int i = 0; i < kKStages; ++i) { mbarInit(&s->kFull[i], 1); mbarInit(&s->kEmpty[i], 1); }
         for (int i = 0; i < kVStages; ++i) { mbarInit(&s->vFull[i], 1); mbarInit(&s->vEmpty[i], 1); }
-        mbarInit(&s->oStaged, kGroupThreads / 32);
-        mbarInit(&s->stageFree[0], 1);
-        mbarInit(&s->stageFree[1], 1);
         // an earlier CTA gave up: do not pile up waits
         s->dead = *reinterpret_cast<volatile int*>(errFlag) != 0 ? 1 : 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -536,13 +539,13 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         return (blk * p.kvHeads + it.kvh) * p.blockSize + (t16 % tilesPerPage) * 16;
     };
 
-    // Registers move from the four service warps to the softmax warps, which hold a whole row
-    // of scores: first statement of every role's branch, the same value in all four warps of
-    // a warpgroup (the instruction is defined per warpgroup).  384 x 168 registers at launch;
-    // 128 threads give up 64 each, 256 threads take 32 each.
+    // Registers move from the service and output warps to the softmax warps, which hold a whole
+    // row of scores: first statement of every role's branch, the same value in all four warps
+    // of a warpgroup (the instruction is defined per warpgroup).  512 x 128 registers at
+    // launch; the service warps give up 48 each, the output warps 64, the softmax warps take 56.
     if (warp == kKProducerWarp) {
         // ------------------------------------------------------------ K producer
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
         if (!live) goto done;
         Cursor c;
         c.init(p, total, numPairs);
@@ -563,7 +566,7 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         }
     } else if (warp == kVProducerWarp) {
         // ------------------------------------------------------------ V producer
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
         if (!live) goto done;
         Cursor c;
         c.init(p, total, numPairs);
@@ -593,7 +596,7 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         // All 32 lanes walk the loop, so that the descriptor arithmetic is uniform across the
         // warp (it then runs on the uniform datapath, where the tensor-core instructions take
         // their operands from); one elected lane issues the tensor-core instructions.
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
         if (!live) goto done;
         const bool leader = electOne();
         const uint32_t fmt = BF16 ? 1u : 0u;
@@ -694,7 +697,7 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                         for (int ks = 0; ks < kKeys / 16; ++ks)
                             ummaTs(dO, sCol + 32u * (ks >> 1) + 8u * (ks & 1) + 16u, dv[ks], idescO, 1u);
                     }
-                    ummaCommit(&s->pvDone[x]);
+                    if (c.j == c.it.nTg[x] - 1) ummaCommit(&s->oFull[x]);     // the tile's accumulator is final
                     if (lastUser) ummaCommit(&s->vEmpty[st]);
                 }
                 __syncwarp();
@@ -714,45 +717,89 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             (void)lastOfItem;
             c.nextTile(p, total, numPairs);
         }
-    } else if (warp == kStoreWarp) {
-        // ------------------------------------------------------------ output store
-        // The softmax groups leave the finished rows of a query tile in the staging buffer, in
-        // the swizzled layout of a TMA box, taking turns in stream order (group 0, then group 1
-        // of each item); one thread sends them to global memory and hands the buffer on once
-        // the copy has read it.  Tiles with fewer than 128 rows of the sequence are written by
-        // the softmax threads themselves (a box would run into the next sequence's rows) and
-        // take no turn.
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
+    } else if (warp == kIdleWarp) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");          // (the fourth warp of the service warpgroup)
+    } else if (warp >= kOutputWarp0) {
+        // ------------------------------------------------------------ output warps
+        // Thread t of the warpgroup owns row t of the tile being written.  Per item and group,
+        // in stream order: the row's sum from the softmax thread, the final accumulator from
+        // tensor memory (its barrier gets one commit per tile, so its phases are taken in
+        // order), O / l into the staging buffer in the layout of the two TMA boxes ([half]
+        // [row][8 chunks of 16 bytes, chunk index XOR row % 8]), one TMA store.  Tiles with
+        // fewer than 128 rows of the sequence go out with plain stores (a box would run into
+        // the next sequence's rows).
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
         if (!live) goto done;
-        int turn = 0;
-        bool ok = true;
+        const int t = (warp & 3) * 32 + lane;
+        const uint32_t laneBase = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const bool issuer = threadIdx.x == kOutputWarp0 * 32;
+        int cnt0 = 0, cnt1 = 0;           // tiles written per group (phase of lReady, oFull)
+        bool ok = true, storePending = false;
         for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
             Item it;
             if (!loadItem(p, w, numPairs, it)) continue;
 #pragma unroll
             for (int x = 0; x < 2; ++x) {
-                if (it.nTg[x] == 0 || it.rowsValid[x] < kRows || !ok) continue;
-                ok = mbarWait(&s->oStaged, turn & 1, &s->dead, errFlag, 16);
+                if (it.nTg[x] == 0 || it.rowsValid[x] == 0 || !ok) continue;
+                int& cnt = x ? cnt1 : cnt0;
+                ok = mbarWait(&s->lReady[x], cnt & 1, &s->dead, errFlag, 17);
+                if (ok) ok = mbarWait(&s->oFull[x], cnt & 1, &s->dead, errFlag, 10);
                 ok = __all_sync(0xFFFFFFFFu, ok);
                 if (!ok) break;
-                if (lane == 0) {
-                    tmaStore3d(&mapO, s->stage, 0, it.head, it.rowBase[x]);
-                    tmaStore3d(&mapO, s->stage + kHalfBytes, 64, it.head, it.rowBase[x]);
-                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-                    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-                    mbarArrive(&s->stageFree[turn & 1]);
+                tcFenceAfter();
+                const float l = s->rowL[x][t];
+                const float inv = l > 0.f ? 1.f / l : 0.f;
+                const bool full = it.rowsValid[x] == kRows;
+                if (full && storePending) {
+                    // the staging buffer is free once the store before has read it
+                    if (issuer) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    storePending = false;
                 }
-                ++turn;
+                unsigned char* out = static_cast<unsigned char*>(p.out) + ((static_cast<int64_t>(it.rowBase[x]) + t) * p.heads + it.head) * kHd * 2;
+                const uint32_t oAddr = tmemO(x) + laneBase;
+#pragma unroll 1
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t o[32];
+                    tmemLd32(oAddr + 32u * c, o);
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        uint32_t wv[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            wv[e] = pack16<BF16>(__uint_as_float(o[8 * q4 + 2 * e]) * inv, __uint_as_float(o[8 * q4 + 2 * e + 1]) * inv);
+                        const int chunk = c * 4 + q4;          // 16-byte chunk of the 256-byte row
+                        if (full)
+                            *reinterpret_cast<uint4*>(s->stage + (chunk >> 3) * kHalfBytes + t * 128 + (((chunk & 7) ^ (t & 7)) << 4)) =
+                                make_uint4(wv[0], wv[1], wv[2], wv[3]);
+                        else if (t < it.rowsValid[x])
+                            *reinterpret_cast<uint4*>(out + chunk * 16) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+                    }
+                }
+                tcFenceBefore();
+                // the buffer is next read (TMA store) by the asynchronous proxy
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (issuer) {
+                    mbarArrive(&s->oEmpty[x]);                  // the accumulator may be overwritten
+                    if (full) {
+                        tmaStore3d(&mapO, s->stage, 0, it.head, it.rowBase[x]);
+                        tmaStore3d(&mapO, s->stage + kHalfBytes, 64, it.head, it.rowBase[x]);
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+                }
+                if (full) storePending = true;
+                ++cnt;
             }
         }
-        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        if (issuer) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     } else {
         // ------------------------------------------------------------ softmax warps
         // Two groups of 128 threads; group x owns query tile x of every item, thread t of a
         // group owns row t of it: all 128 key columns of a tile in registers, no exchange
         // between threads.  While one group turns its S into P, the tensor pipe works for the
         // other.
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 184;");
         if (!live) goto done;
         const int x = warp >> 2, t = (warp & 3) * 32 + lane;
         const bool loader = t == 0;                     // fetches the group's query tiles
@@ -762,7 +809,6 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         int steps = 0;      // key tiles this group has done (phase of its barriers)
         int items = 0;      // items this group has taken part in
         int g0 = 0;         // key tiles of the stream before the current item
-        int turn = 0;       // staging turns of the stream before the current item
         // the next query tile is brought into L2 an item early, so that its fetch during the
         // last key tile of the item before it is short
         auto prefetchQ = [&](const Item& it) {
@@ -791,10 +837,6 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
             Item it;
             if (!loadItem(p, w, numPairs, it)) continue;
-            // staging turns of this item that come before this group's
-            const bool turn0 = it.nTg[0] > 0 && it.rowsValid[0] == kRows, turn1 = it.nTg[1] > 0 && it.rowsValid[1] == kRows;
-            const int myTurn = turn + (x == 1 && turn0 ? 1 : 0);
-            turn += (turn0 ? 1 : 0) + (turn1 ? 1 : 0);
             const int gBase = g0;
             g0 += it.nT;
             // this group's half of the item
@@ -910,56 +952,12 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 mbarArrive(&s->pFull[x]);
             }
             if (!ok) break;
-            // ---- output of the tile: O / l.  The last P V product: the one before it is known
-            // complete (the last S product came behind it), so the phase parity is unambiguous.
-            ok = mbarWait(&s->pvDone[x], (steps - 1) & 1, &s->dead, errFlag, 10);
-            if (!ok) break;
-            tcFenceAfter();
-            const float inv = l > 0.f ? 1.f / l : 0.f;
-            const bool full = rowsValid == kRows;
-            if (full && myTurn >= 1) {
-                // This group's turn at the staging buffer comes when the turn before it is
-                // complete.  (One barrier per turn parity; the turn three before is known
-                // complete, because the turn two before was staged before this group got here.)
-                ok = mbarWait(&s->stageFree[(myTurn - 1) & 1], ((myTurn - 1) >> 1) & 1, &s->dead, errFlag, 17);
-                if (!ok) break;
-            }
-            unsigned char* out = static_cast<unsigned char*>(p.out) + ((static_cast<int64_t>(rowBase) + t) * p.heads + it.head) * kHd * 2;
-            {
-                uint32_t o0[32], o1[32], o2[32], o3[32];
-                tmemLd32NoWait(oAddr, o0);
-                tmemLd32NoWait(oAddr + 32u, o1);
-                tmemLd32NoWait(oAddr + 64u, o2);
-                tmemLd32NoWait(oAddr + 96u, o3);
-                tmemLdWait();
-                auto put = [&](const uint32_t (&o)[32], int c) {
-#pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) {
-                        uint32_t wv[4];
-#pragma unroll
-                        for (int e = 0; e < 4; ++e)
-                            wv[e] = pack16<BF16>(__uint_as_float(o[8 * q4 + 2 * e]) * inv, __uint_as_float(o[8 * q4 + 2 * e + 1]) * inv);
-                        const int chunk = c * 4 + q4;          // 16-byte chunk of the 256-byte row
-                        if (full)
-                            *reinterpret_cast<uint4*>(s->stage + (chunk >> 3) * kHalfBytes + t * 128 + (((chunk & 7) ^ (t & 7)) << 4)) =
-                                make_uint4(wv[0], wv[1], wv[2], wv[3]);
-                        else if (t < rowsValid)
-                            *reinterpret_cast<uint4*>(out + chunk * 16) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
-                    }
-                };
-                put(o0, 0);
-                put(o1, 1);
-                put(o2, 2);
-                put(o3, 3);
-            }
-            tcFenceBefore();
-            // the buffer is next read (TMA store) by the asynchronous proxy
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) {
-                mbarArrive(&s->oEmpty[x]);                  // the accumulator may be overwritten
-                if (full) mbarArrive(&s->oStaged);
-            }
+            // The output warps write the tile once its last P V product is complete; this thread
+            // leaves them the sum of its row's weights and goes on.  (The next write to this
+            // slot comes at the end of the group's next item, whose first P V product waits for
+            // the accumulator to be handed back, which happens after the sum was read.)
+            s->rowL[x][t] = l;
+            mbarArrive(&s->lReady[x]);
             ++items;
         }
     }
