@@ -527,6 +527,112 @@ def run_prefill(args):
     engine.close()
 
 
+# ------------------------------------------------ KV append + FP8 quantisation + CoW copy (c1)
+
+C1_TOKENS, C1_BLOCKS, C1_COPIES = 4096, 4096, 512
+
+
+def run_append(args):
+    """`configs[1]`: 4096 new tokens (float16 K/V, 8 KV heads x 128) scattered by a slot
+    mapping of random distinct slots into a pool of 4096 blocks x 16, once as float16 and
+    once quantised to FP8 e4m3 with per-(block, kv_head) scales, plus the copy of 512
+    random blocks (copy-on-write).  A step is the three calls; the working set is smaller
+    than L2, so L2 is flushed (a 512 MB buffer is written) before every timed step and
+    every step is timed with its own pair of CUDA events.  Metric: algorithmic GB/s."""
+    import torch
+
+    import pagedattentionmetal_b200 as pam
+
+    DT = pam.PagedAttentionDataType
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    engine = pam.PagedAttentionEngine(0)
+    stream = torch.cuda.Stream(dev)
+    torch.cuda.set_stream(stream)
+    engine.setStream(stream.cuda_stream)
+    rng = np.random.default_rng(1001)
+    T, nblk = C1_TOKENS, C1_BLOCKS
+    k_h = rng.standard_normal((T, KV_HEADS, HEAD_DIM), dtype=np.float32).astype(np.float16)
+    v_h = rng.standard_normal((T, KV_HEADS, HEAD_DIM), dtype=np.float32).astype(np.float16)
+    slots_h = rng.choice(nblk * BLOCK, T, replace=False).astype(np.int64)
+    perm = rng.permutation(nblk)
+    src, dst = perm[:C1_COPIES].astype(np.int32), perm[C1_COPIES:2 * C1_COPIES].astype(np.int32)
+    k, v, slots = torch.from_numpy(k_h).to(dev), torch.from_numpy(v_h).to(dev), torch.from_numpy(slots_h).to(dev)
+    c16 = pam.KVCacheManager(engine, nblk, BLOCK, HEAD_DIM, KV_HEADS, DT.float16)
+    c8 = pam.KVCacheManager(engine, nblk, BLOCK, HEAD_DIM, KV_HEADS, DT.float8)
+
+    def step():
+        engine.reshapeAndCache(c16, k, v, slots, T)
+        engine.reshapeAndCache(c8, k, v, slots, T)
+        engine.copyBlocks(c16, src, dst)
+
+    # correctness guard: pools, codes and scales bit for bit against the oracle
+    step()
+    engine.synchronize()
+    from oracle import c_oracle as co
+    kp = np.zeros((nblk, KV_HEADS, BLOCK, HEAD_DIM), np.float16)
+    vp = np.zeros_like(kp)
+    co.reshape_and_cache(k_h, v_h, kp, vp, slots_h, BLOCK)
+    co.copy_blocks(kp, vp, src, dst)
+    gk, gv, _, _ = c16.readPools()
+    assert np.array_equal(gk, kp) and np.array_equal(gv, vp), "float16 append or block copy differs from the oracle"
+    kc = np.zeros((nblk, KV_HEADS, BLOCK, HEAD_DIM), np.uint8)
+    vc = np.zeros_like(kc)
+    ks = np.zeros((nblk, KV_HEADS), np.float16)
+    vs = np.zeros_like(ks)
+    co.reshape_and_cache_fp8(k_h, v_h, kc, vc, ks.view(np.uint16), vs.view(np.uint16), slots_h, BLOCK)
+    gk8, gv8, gks, gvs = c8.readPools()
+    assert np.array_equal(gk8, kc) and np.array_equal(gv8, vc), "FP8 codes differ from the oracle"
+    assert np.array_equal(gks, ks) and np.array_equal(gvs, vs), "FP8 scales differ from the oracle"
+
+    engine.setAsync(True)
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+    sampler = ClockSampler(0)
+    sampler.start()
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
+        step()
+    torch.cuda.synchronize(dev)
+    launches0 = engine.kernelLaunches
+    total_ms = 0.0
+    for _ in range(args.steps):
+        flush.fill_(1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        step()
+        e1.record(stream)
+        torch.cuda.synchronize(dev)
+        total_ms += e0.elapsed_time(e1)
+    engine.synchronize()
+    ms_step = total_ms / args.steps
+    launches = engine.kernelLaunches - launches0
+    clocks = sampler.stop()
+    row = KV_HEADS * HEAD_DIM
+    block16 = KV_HEADS * BLOCK * HEAD_DIM * 2
+    bytes_f16 = 2 * (T * row * 2) * 2                         # K and V: read + write
+    bytes_fp8 = 2 * (T * row * 2) + 2 * (T * row) + 2 * 2 * T * KV_HEADS * 2   # read f16, write codes, scales (upper bound)
+    bytes_cow = 2 * C1_COPIES * block16 * 2                   # K and V blocks: read + write
+    total = bytes_f16 + bytes_fp8 + bytes_cow + T * 8 * 2
+    peak, kind = measured_hbm_peak()
+    achieved = total / (ms_step * 1e-3) / 1e9
+    line = {"metric": "KV append GB/s", "value": achieved, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": warm,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f16 -> f16 / fp8-e4m3", "data": "synthetic",
+            "config": {"workload": "append_c1: 4096 tokens x 8 kv heads x 128 scattered to random distinct slots of a "
+                                   "4096-block pool as float16 and as FP8 e4m3 with (block, kv_head) scales, plus a copy of "
+                                   "512 random blocks", "seed": 1001, "l2": "flushed before every timed step (512 MB written)"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_source": f"{kind} copy bandwidth",
+                         "kernel": "reshapeAndCacheKernel, fp8AbsmaxKernel + fp8QuantizeKernel, copyBlocksKernel",
+                         "algorithmic_bytes_per_launch": total, "traffic": None,
+                         "note": "126 MB per step in 4 short kernels: launch latency, not HBM, bounds it"},
+            "tokens_per_s": T / (ms_step * 1e-3), "gpu_launches": int(launches), "clocks": clocks}
+    print(json.dumps(line))
+    c16.close()
+    c8.close()
+    engine.close()
+
+
 # ------------------------------------------- long-context FP8 decode (c4)
 
 C4_SEQS, C4_LO, C4_HI, C4_WINDOW, C4_HEADS, C4_CHUNK = 64, 32768, 131072, 4096, 64, 2048
@@ -728,7 +834,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=BATCH,
                     help="number of sequences (default: the workload's 256; smaller values are for profiler captures)")
-    ap.add_argument("--workload", default="decode_c2", choices=["decode_c2", "prefill_c3", "decode_c4", "step_c4"],
+    ap.add_argument("--workload", default="decode_c2", choices=["decode_c2", "prefill_c3", "decode_c4", "step_c4", "append_c1"],
                     help="decode_c2 is the headline workload; prefill_c3 reports prefill TFLOP/s (1 GPU)")
     ap.add_argument("--profile", action="store_true",
                     help="profiler run: no clock-settling loop, no end-to-end leg, no CPU baseline")
@@ -738,6 +844,8 @@ def main():
         globals()["PF_SEQS"] = args.batch
     if args.workload == "prefill_c3" and args.impl == "ours":
         run_prefill(args)
+    elif args.workload == "append_c1" and args.impl == "ours":
+        run_append(args)
     elif args.workload in ("decode_c4", "step_c4") and args.impl == "ours":
         run_decode_fp8(args)
     elif args.impl == "reference":
