@@ -202,3 +202,41 @@ def test_prefill_fp8_tensor_path(engine, seq_len, window, q_start, q_len):
     finally:
         engine.setPrefillTensorPath(True)
     assert_close(gen[lo:], ref[lo:], DT.float8)
+
+
+@pytest.mark.parametrize("dtype", [DT.bfloat16, DT.float16])
+def test_prefill_batch_many_items_per_cta(engine, dtype):
+    """A ragged batch with far more work items than multiprocessors (each CTA of the
+    tensor-core kernel walks several items, of very different lengths, with chunks that
+    start inside a tile): every row of every sequence against the oracle."""
+    rng = np.random.default_rng(37)
+    H, KVH, D, bs = 32, 8, 128, 16
+    seq_lens = [1500, 700, 1029, 130, 2048, 333, 1, 900]
+    q_starts = [1000, 0, 517, 0, 1536, 300, 0, 128]
+    q_lens = [500, 700, 512, 130, 512, 33, 1, 700]
+    n_seq = len(seq_lens)
+    max_nb = (max(seq_lens) + bs - 1) // bs
+    n_pool = sum((L + bs - 1) // bs for L in seq_lens) + 8
+    perm = rng.permutation(n_pool).astype(np.int32)
+    tables = np.zeros((n_seq, max_nb), np.int32)
+    o = 0
+    for s, L in enumerate(seq_lens):
+        nb = (L + bs - 1) // bs
+        tables[s, :nb] = perm[o:o + nb]
+        o += nb
+    shape = (n_pool, KVH, bs, D)
+    k_pool = to_storage(rng.standard_normal(shape, dtype=np.float32), dtype)
+    v_pool = to_storage(rng.standard_normal(shape, dtype=np.float32), dtype)
+    qs = [to_storage(rng.standard_normal((q_lens[s], H, D), dtype=np.float32), dtype) for s in range(n_seq)]
+    q_cat = np.concatenate(qs)
+    kp, vp = engine.makeBufferFrom(k_pool), engine.makeBufferFrom(v_pool)
+    out_buf = engine.makeBuffer(q_cat.nbytes)
+    engine.prefillBatch(engine.makeBufferFrom(q_cat), kp, vp, engine.makeBufferFrom(tables), out_buf, seq_lens, q_starts,
+                        q_lens, max_nb, pam.PagedLayerSpec(D, H, KVH, bs, dtype))
+    assert engine.lastStats.operation == pam.Operation.prefillMMA
+    out = out_buf.download(io_numpy_dtype(dtype), q_cat.shape)
+    o = 0
+    for s in range(n_seq):
+        ref = co.prefill(qs[s], k_pool, v_pool, tables[s], seq_lens[s], KVH, bs, int(dtype), q_start=q_starts[s])
+        assert_close(from_io(out[o:o + q_lens[s]], dtype), ref, dtype)
+        o += q_lens[s]
