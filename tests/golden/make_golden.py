@@ -84,7 +84,9 @@ def fill_pools(rng, n_pool, kvh, bs, hd, tables, lens, dtype=po.DT_F32):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py <checkout of the reference project>")
+    ref_root = sys.argv[1]
     sim = load_sim(ref_root)
 
     # 1. The reference's own self-check case (sim:143-176): seed 42, S=8,
