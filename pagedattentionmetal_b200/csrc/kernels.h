@@ -95,6 +95,11 @@ struct PrefillParams {
     int inlineMeta;
     int32_t meta[5][kPrefillInlineSeqs];
     int exactWeights;             // bfloat16 tensor path: 0 = 8-bit weights, 1 = 16-bit on short rows, 2 = 16-bit always
+    // Filled by the tensor-core launcher: reciprocals for the work-item arithmetic (an item
+    // index is split by numSeqs * heads, heads and heads / kvHeads; valid while the item
+    // count stays below 2^22, else fastItems is 0 and the kernel divides).
+    int fastItems;
+    float invPer, invHeads, invGroup;
 };
 // Tensor-core path (prefill_tc_kernel.cu): bf16/f16, head_dim 128, block size multiple of 16.
 bool prefillTensorPathApplies(const PrefillParams& p);

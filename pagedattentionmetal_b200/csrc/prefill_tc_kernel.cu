@@ -399,15 +399,40 @@ struct Item {
 // first and the head running fastest, so that the CTAs working side by side share the keys
 // of one KV head through L2 and the short items fill the end of the launch.  Returns false
 // when the sequence has no rows in that pair.
+// n / d and n % d for 0 <= n < 2^22, 0 < d, through the float reciprocal of d (a division
+// by a run-time value is some twenty instructions, and the roles of the kernel split item
+// indices at every item boundary on their critical paths).
+__device__ __forceinline__ int fastDivMod(int n, int d, float inv, int& rem) {
+    int q = __float2int_rz(__int2float_rn(n) * inv);
+    int r = n - q * d;
+    if (r < 0) {
+        --q;
+        r += d;
+    } else if (r >= d) {
+        ++q;
+        r -= d;
+    }
+    rem = r;
+    return q;
+}
+
 __device__ __forceinline__ bool loadItem(const PrefillParams& p, int w, int numPairs, Item& it) {
-    const int per = p.numSeqs * p.heads;
-    const int pair = numPairs - 1 - w / per;
-    const int rem = w % per;
-    it.seq = rem / p.heads;
-    it.head = rem % p.heads;
+    const int per = p.numSeqs * p.heads, group = p.heads / p.kvHeads;
+    int pairFromEnd, rem, unused;
+    if (p.fastItems) {
+        pairFromEnd = fastDivMod(w, per, p.invPer, rem);
+        it.seq = fastDivMod(rem, p.heads, p.invHeads, it.head);
+        it.kvh = fastDivMod(it.head, group, p.invGroup, unused);
+    } else {
+        pairFromEnd = w / per;
+        rem = w % per;
+        it.seq = rem / p.heads;
+        it.head = rem % p.heads;
+        it.kvh = it.head / group;
+    }
+    const int pair = numPairs - 1 - pairFromEnd;
     const int qLen = prefillMeta(p, 2, it.seq);
     if (pair * 2 * kRows >= qLen) return false;
-    it.kvh = it.head / (p.heads / p.kvHeads);
     const int qStart = prefillMeta(p, 1, it.seq), rowOff = prefillMeta(p, 3, it.seq);
     it.seqLen = prefillMeta(p, 0, it.seq);
     it.ws = prefillMeta(p, 4, it.seq);
@@ -1040,15 +1065,20 @@ cudaError_t launchPrefillTensor(const PrefillParams& p, int totalRows, int* errF
     if (e != cudaSuccess) return e;
     const long long items = static_cast<long long>(((p.maxQLen + kRows - 1) / kRows + 1) / 2) * p.heads * p.numSeqs;
     if (items <= 0 || items > 0x7FFFFFFF) return cudaErrorInvalidValue;
+    PrefillParams pk = p;
+    pk.fastItems = items < (1 << 22) ? 1 : 0;
+    pk.invPer = 1.0f / static_cast<float>(p.numSeqs * p.heads);
+    pk.invHeads = 1.0f / static_cast<float>(p.heads);
+    pk.invGroup = 1.0f / static_cast<float>(p.heads / p.kvHeads);
     dim3 grid(static_cast<unsigned>(items < sms ? items : sms));
     if (p.dtype == kBF16) {
         e = cudaFuncSetAttribute(prefillTcKernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (e != cudaSuccess) return e;
-        prefillTcKernel<true><<<grid, kThreads, smem, stream>>>(mapQ, mapK, mapV, mapO, p, scaleLog2, errFlag);
+        prefillTcKernel<true><<<grid, kThreads, smem, stream>>>(mapQ, mapK, mapV, mapO, pk, scaleLog2, errFlag);
     } else {
         e = cudaFuncSetAttribute(prefillTcKernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (e != cudaSuccess) return e;
-        prefillTcKernel<false><<<grid, kThreads, smem, stream>>>(mapQ, mapK, mapV, mapO, p, scaleLog2, errFlag);
+        prefillTcKernel<false><<<grid, kThreads, smem, stream>>>(mapQ, mapK, mapV, mapO, pk, scaleLog2, errFlag);
     }
     if (launches) *launches += 1;
     return cudaGetLastError();
