@@ -99,6 +99,7 @@ struct PrefillParams {
     // index is split by numSeqs * heads, heads and heads / kvHeads; valid while the item
     // count stays below 2^22, else fastItems is 0 and the kernel divides).
     int fastItems;
+    int pairHeads;   // set by launchPrefillTensor: the two row groups of a CTA take two heads of one KV head
     float invPer, invHeads, invGroup;
 };
 // Tensor-core path (prefill_tc_kernel.cu): bf16/f16, head_dim 128, block size multiple of 16.

@@ -8,10 +8,12 @@
 // PagedAttentionEngine.swift:740-756).
 //
 // The kernel is persistent: one CTA per multiprocessor walks the work items
-// round robin, longest items first.  An item is a pair of consecutive tiles of
-// 128 query rows of one head of one sequence; it walks the key tiles (128 keys
-// each) its rows can see, and every key and value tile is fetched once for
-// both query tiles.  Each query tile belongs to one of two softmax groups, with
+// round robin, longest items first.  An item is a pair of tiles of 128 query
+// rows of one sequence that share a KV head: the same rows of two neighbouring
+// query heads when the number of query heads per KV head is even (both tiles
+// then see the same keys), else two consecutive tiles of one head.  It walks the
+// key tiles (128 keys each) its rows can see, and every key and value tile is
+// fetched once for both query tiles.  Each query tile belongs to one of two softmax groups, with
 // its own S buffer and accumulator O in tensor memory (4 x 128 columns): while
 // one group turns its S into the weights P, the tensor pipe works for the
 // other.
@@ -381,11 +383,13 @@ constexpr int kSoftmaxWarps = 8;                       // two groups of four war
 constexpr int kKProducerWarp = 8, kVProducerWarp = 9, kMmaWarp = 10, kIdleWarp = 11, kOutputWarp0 = 12;
 constexpr int kThreads = (kSoftmaxWarps + 8) * 32;     // softmax, service and output warpgroups
 
-// One unit of work: two consecutive tiles of 128 query rows of one head of one sequence.
+// One unit of work: two tiles of 128 query rows of one sequence under one KV head (the same
+// rows of two heads, or two consecutive tiles of one head: see loadItem).
 // Softmax group x owns tile x of the pair: its own query tile, S buffer and accumulator;
 // the key and value tiles are fetched once for both.
 struct Item {
-    int head, seq, kvh;
+    int head, headStep, seq, kvh; // group x works on head + x * headStep
+    __device__ __forceinline__ int headOf(int x) const { return head + x * headStep; }
     int tileLo, nT;              // key tiles tileLo .. tileLo + nT - 1 hold every key a row of the pair may see
     int nTg[2];                  // ... a row of group x may see (0: the group has no rows, or they see nothing)
     int rowBase[2], rowsValid[2];// first row in q/out, rows that exist
@@ -417,22 +421,28 @@ __device__ __forceinline__ int fastDivMod(int n, int d, float inv, int& rem) {
 }
 
 __device__ __forceinline__ bool loadItem(const PrefillParams& p, int w, int numPairs, Item& it) {
-    const int per = p.numSeqs * p.heads, group = p.heads / p.kvHeads;
-    int pairFromEnd, rem, unused;
+    // pairHeads: the two groups take the same query tile of two neighbouring heads of one KV
+    // head (equal work for both); else two consecutive query tiles of one head
+    const int heads = p.pairHeads ? p.heads / 2 : p.heads;
+    const int per = p.numSeqs * heads, group = heads / p.kvHeads;
+    int pairFromEnd, rem, unused, h;
     if (p.fastItems) {
         pairFromEnd = fastDivMod(w, per, p.invPer, rem);
-        it.seq = fastDivMod(rem, p.heads, p.invHeads, it.head);
-        it.kvh = fastDivMod(it.head, group, p.invGroup, unused);
+        it.seq = fastDivMod(rem, heads, p.invHeads, h);
+        it.kvh = fastDivMod(h, group, p.invGroup, unused);
     } else {
         pairFromEnd = w / per;
         rem = w % per;
-        it.seq = rem / p.heads;
-        it.head = rem % p.heads;
-        it.kvh = it.head / group;
+        it.seq = rem / heads;
+        h = rem % heads;
+        it.kvh = h / group;
     }
+    it.head = p.pairHeads ? 2 * h : h;
+    it.headStep = p.pairHeads ? 1 : 0;
+    const int tilesPer = p.pairHeads ? 1 : 2, tileStep = p.pairHeads ? 0 : 1;
     const int pair = numPairs - 1 - pairFromEnd;
     const int qLen = prefillMeta(p, 2, it.seq);
-    if (pair * 2 * kRows >= qLen) return false;
+    if (pair * tilesPer * kRows >= qLen) return false;
     const int qStart = prefillMeta(p, 1, it.seq), rowOff = prefillMeta(p, 3, it.seq);
     it.seqLen = prefillMeta(p, 0, it.seq);
     it.ws = prefillMeta(p, 4, it.seq);
@@ -440,7 +450,7 @@ __device__ __forceinline__ bool loadItem(const PrefillParams& p, int w, int numP
     it.nT = 0;
 #pragma unroll
     for (int x = 0; x < 2; ++x) {
-        const int first = (pair * 2 + x) * kRows;                 // first row of the tile within the launch's rows
+        const int first = (pair * tilesPer + x * tileStep) * kRows;  // first row of the tile within the launch's rows
         const int rows = min(kRows, qLen - first);
         it.rowsValid[x] = max(rows, 0);
         it.rowBase[x] = rowOff + first;
@@ -519,8 +529,9 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     }
 #endif
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int numPairs = ((p.maxQLen + kRows - 1) / kRows + 1) / 2;
-    const int total = numPairs * p.numSeqs * p.heads;
+    const int numTiles = (p.maxQLen + kRows - 1) / kRows;
+    const int numPairs = p.pairHeads ? numTiles : (numTiles + 1) / 2;      // item rows of the launch
+    const int total = numPairs * p.numSeqs * (p.pairHeads ? p.heads / 2 : p.heads);
 
     if (threadIdx.x == kKProducerWarp * 32) asm volatile("prefetch.tensormap [%0];" ::"l"(&mapK) : "memory");
     if (threadIdx.x == kVProducerWarp * 32) asm volatile("prefetch.tensormap [%0];" ::"l"(&mapV) : "memory");
@@ -781,7 +792,7 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                     asm volatile("bar.sync 1, 128;" ::: "memory");
                     storePending = false;
                 }
-                unsigned char* out = static_cast<unsigned char*>(p.out) + ((static_cast<int64_t>(it.rowBase[x]) + t) * p.heads + it.head) * kHd * 2;
+                unsigned char* out = static_cast<unsigned char*>(p.out) + ((static_cast<int64_t>(it.rowBase[x]) + t) * p.heads + it.headOf(x)) * kHd * 2;
                 const uint32_t oAddr = tmemO(x) + laneBase;
 #pragma unroll 1
                 for (int c = 0; c < 4; ++c) {
@@ -808,8 +819,8 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 if (issuer) {
                     mbarArrive(&s->oEmpty[x]);                  // the accumulator may be overwritten
                     if (full) {
-                        tmaStore3d(&mapO, s->stage, 0, it.head, it.rowBase[x]);
-                        tmaStore3d(&mapO, s->stage + kHalfBytes, 64, it.head, it.rowBase[x]);
+                        tmaStore3d(&mapO, s->stage, 0, it.headOf(x), it.rowBase[x]);
+                        tmaStore3d(&mapO, s->stage + kHalfBytes, 64, it.headOf(x), it.rowBase[x]);
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                     }
                 }
@@ -838,14 +849,14 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         // last key tile of the item before it is short
         auto prefetchQ = [&](const Item& it) {
             const int rowBase = x ? it.rowBase[1] : it.rowBase[0];
-            asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(&mapQ), "r"(0), "r"(it.head), "r"(rowBase) : "memory");
-            asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(&mapQ), "r"(64), "r"(it.head), "r"(rowBase) : "memory");
+            asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(&mapQ), "r"(0), "r"(it.headOf(x)), "r"(rowBase) : "memory");
+            asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(&mapQ), "r"(64), "r"(it.headOf(x)), "r"(rowBase) : "memory");
         };
         auto loadQ = [&](const Item& it) {
             const int rowBase = x ? it.rowBase[1] : it.rowBase[0];
             mbarExpectTx(&s->qFull[x], kTileBytes);
-            tmaLoad3d(s->q[x], &mapQ, &s->qFull[x], 0, it.head, rowBase);
-            tmaLoad3d(s->q[x] + kHalfBytes, &mapQ, &s->qFull[x], 64, it.head, rowBase);
+            tmaLoad3d(s->q[x], &mapQ, &s->qFull[x], 0, it.headOf(x), rowBase);
+            tmaLoad3d(s->q[x] + kHalfBytes, &mapQ, &s->qFull[x], 64, it.headOf(x), rowBase);
         };
         // the first item the group takes part in: its query tile is fetched right away
         int wNext = blockIdx.x;
@@ -872,7 +883,7 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 // rows that see no key at all: zeros (no other role takes part)
                 if (t < rowsValid) {
                     uint4* out = reinterpret_cast<uint4*>(static_cast<unsigned char*>(p.out) +
-                                                          ((static_cast<int64_t>(rowBase) + t) * p.heads + it.head) * kHd * 2);
+                                                          ((static_cast<int64_t>(rowBase) + t) * p.heads + it.headOf(x)) * kHd * 2);
 #pragma unroll
                     for (int i = 0; i < 16; ++i) out[i] = make_uint4(0u, 0u, 0u, 0u);
                 }
@@ -1063,13 +1074,19 @@ cudaError_t launchPrefillTensor(const PrefillParams& p, int totalRows, int* errF
     cudaError_t e = cudaGetDevice(&dev);
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return e;
-    const long long items = static_cast<long long>(((p.maxQLen + kRows - 1) / kRows + 1) / 2) * p.heads * p.numSeqs;
+    // An even number of query heads per KV head: an item is one query tile of two heads,
+    // so both softmax groups have the same key tiles; else two query tiles of one head.
+    const int numTiles = (p.maxQLen + kRows - 1) / kRows;
+    const bool pairHeads = (p.heads / p.kvHeads) % 2 == 0;
+    const int itemHeads = pairHeads ? p.heads / 2 : p.heads;
+    const long long items = static_cast<long long>(pairHeads ? numTiles : (numTiles + 1) / 2) * itemHeads * p.numSeqs;
     if (items <= 0 || items > 0x7FFFFFFF) return cudaErrorInvalidValue;
     PrefillParams pk = p;
+    pk.pairHeads = pairHeads ? 1 : 0;
     pk.fastItems = items < (1 << 22) ? 1 : 0;
-    pk.invPer = 1.0f / static_cast<float>(p.numSeqs * p.heads);
-    pk.invHeads = 1.0f / static_cast<float>(p.heads);
-    pk.invGroup = 1.0f / static_cast<float>(p.heads / p.kvHeads);
+    pk.invPer = 1.0f / static_cast<float>(p.numSeqs * itemHeads);
+    pk.invHeads = 1.0f / static_cast<float>(itemHeads);
+    pk.invGroup = 1.0f / static_cast<float>(itemHeads / p.kvHeads);
     dim3 grid(static_cast<unsigned>(items < sms ? items : sms));
     if (p.dtype == kBF16) {
         e = cudaFuncSetAttribute(prefillTcKernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
