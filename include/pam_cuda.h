@@ -368,6 +368,23 @@ typedef struct PamBatchPrefillRequest {
 } PamBatchPrefillRequest;
 int32_t pamc_prefill_batch(void *ctx, const PamBatchPrefillRequest *request);
 
+/* PagedAttentionFusedPrefillRequest (PagedAttentionTypes.swift:367-421): the raw
+ * keys and values of tokens [0, seq_len) are written to the pages of block_table
+ * and the prefill of the same seq_len rows runs over them. */
+typedef struct PamFusedPrefillRequest {
+    PamBuffer q, raw_k, raw_v, block_table, k_pool, v_pool, output;
+    int32_t seq_len;
+    PamLayerSpec layer;
+    int32_t causal;
+    PamBuffer k_scale, v_scale;
+} PamFusedPrefillRequest;
+/* PagedAttentionEngine.fusedPrefill (PagedAttentionEngine.swift:633-710).  Pools
+ * and output equal those of pamc_append_to_cache (token_offset 0) followed by
+ * pamc_prefill, which is what the reference's own test of this call checks.
+ * cache: the handle that owns the pools; required for FP8 (absmax scratch and
+ * scale rows), may be NULL otherwise. */
+int32_t pamc_fused_prefill(void *ctx, const PamFusedPrefillRequest *request, void *cache);
+
 /* ------------------------------------------------------------------------
  * Scheduler (Scheduler.swift)
  * ---------------------------------------------------------------------- */

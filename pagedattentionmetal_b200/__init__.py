@@ -11,6 +11,7 @@ import importlib
 _API = {
     "api_types": ["BlockEvictionPolicy", "KVCacheError", "KVCacheMemoryStats", "LogicalSequence", "Operation",
                   "PagedAttentionDataType", "PagedAttentionDecodeRequest", "PagedAttentionError",
+                  "PagedAttentionFusedPrefillRequest",
                   "PagedAttentionPrefillRequest", "PagedAttentionStats", "PagedKVAppendRequest", "PagedLayerSpec",
                   "SchedulerSequence", "SequenceStatus"],
     "engine": ["BatchKVCacheManager", "ContinuousBatchingScheduler", "DeviceBuffer", "KVCacheManager",

@@ -74,6 +74,12 @@ class PamBatchPrefillRequest(C.Structure):
                 ("layer", PamLayerSpec), ("causal", c_int32), ("k_scale", PamBuffer), ("v_scale", PamBuffer)]
 
 
+class PamFusedPrefillRequest(C.Structure):
+    _fields_ = [("q", PamBuffer), ("raw_k", PamBuffer), ("raw_v", PamBuffer), ("block_table", PamBuffer),
+                ("k_pool", PamBuffer), ("v_pool", PamBuffer), ("output", PamBuffer), ("seq_len", c_int32),
+                ("layer", PamLayerSpec), ("causal", c_int32), ("k_scale", PamBuffer), ("v_scale", PamBuffer)]
+
+
 class PamSchedSequence(C.Structure):
     _fields_ = [("id", c_int64), ("status", c_int32), ("num_generated_tokens", c_int32),
                 ("max_new_tokens", c_int32), ("prompt_length", c_int32), ("arrival_order", c_int32)]
@@ -142,6 +148,7 @@ SIGNATURES = {
     "pamc_decode_noalloc": (c_int32, [c_void_p, C.POINTER(PamDecodeRequest)]),
     "pamc_prefill": (c_int32, [c_void_p, C.POINTER(PamPrefillRequest), c_int32]),
     "pamc_prefill_batch": (c_int32, [c_void_p, C.POINTER(PamBatchPrefillRequest)]),
+    "pamc_fused_prefill": (c_int32, [c_void_p, C.POINTER(PamFusedPrefillRequest), c_void_p]),
     # scheduler
     "pamc_sched_create": (c_void_p, [c_int32, c_int32]),
     "pamc_sched_destroy": (None, [c_void_p]),

@@ -175,6 +175,23 @@ class PagedAttentionPrefillRequest:
 
 
 @dataclass
+class PagedAttentionFusedPrefillRequest:
+    """PagedAttentionTypes.swift:367-421"""
+    q: Any
+    rawK: Any
+    rawV: Any
+    blockTable: Any
+    kPool: Any
+    vPool: Any
+    output: Any
+    seqLen: int
+    layer: PagedLayerSpec
+    causal: bool = True
+    kScaleBuffer: Optional[Any] = None
+    vScaleBuffer: Optional[Any] = None
+
+
+@dataclass
 class PagedAttentionDecodeRequest:
     """PagedAttentionTypes.swift:259-315"""
     q: Any

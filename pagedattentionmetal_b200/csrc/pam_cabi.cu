@@ -1318,6 +1318,48 @@ int32_t pamc_prefill_batch(void* ctx, const PamBatchPrefillRequest* request) {
     return rc;
 }
 
+int32_t pamc_fused_prefill(void* ctx, const PamFusedPrefillRequest* request, void* cache) {
+    // PagedAttentionEngine.swift:633-710.  The reference's kernels (kernels.metal:1963-2340)
+    // have every threadgroup rewrite the whole sequence into the pools before its own
+    // attention rows; here the rows are written once by the append kernels and the
+    // prefill kernel follows on the same stream.
+    if (!ctx || !request) return -1;
+    Context* c = asCtx(ctx);
+    std::lock_guard<std::mutex> g(c->mu);
+    DeviceGuard dg(c->device);
+    if (c->device < 0) return noGpu(c);
+    const PamFusedPrefillRequest& rq = *request;
+    if (!validateLayer(c, rq.layer)) return -1;
+    if (rq.seq_len <= 0) return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("seqLen must be positive."));
+    const PamLayerSpec& l = rq.layer;
+    const size_t numBlocks = (static_cast<size_t>(rq.seq_len) + l.block_size - 1) / l.block_size;
+    if (!requireBuffer(c, rq.block_table, "blockTable", numBlocks * sizeof(int32_t))) return -1;
+    if (!requireBuffer(c, rq.output, "output", static_cast<size_t>(rq.seq_len) * qBytesPerToken(l))) return -1;
+    Cache* k = cache ? asCache(cache) : nullptr;
+    if (l.data_type == PAM_DTYPE_FP8 && !k)
+        return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("FP8 fused prefill needs the cache handle that owns the scale buffers."));
+    const double t0 = nowMs();
+    PamAppendRequest ap{};
+    ap.keys = rq.raw_k; ap.values = rq.raw_v;
+    ap.k_pool = rq.k_pool; ap.v_pool = rq.v_pool;
+    ap.block_table = rq.block_table;
+    ap.token_offset = 0; ap.num_new_tokens = rq.seq_len;
+    ap.layer = l;
+    ap.k_scale = rq.k_scale; ap.v_scale = rq.v_scale;
+    int32_t rc = appendImpl(c, ap, k, nullptr);
+    if (rc != 0) return rc;
+    const int maxNumBlocks = rq.block_table.bytes != kUnknownBytes
+                                 ? static_cast<int>(std::min<size_t>(rq.block_table.bytes / sizeof(int32_t), 1u << 30))
+                                 : static_cast<int>(numBlocks);
+    rc = prefillImpl(c, l, rq.q, rq.k_pool, rq.v_pool, rq.block_table, rq.output, rq.k_scale, rq.v_scale,
+                     {PrefillSeq{rq.seq_len, 0, rq.seq_len}}, maxNumBlocks, rq.causal != 0, "blockTable");
+    if (rc != 0) return rc;
+    // the reference reports the fused call as a single pass over the sequence (:697-706)
+    c->stats = PamStats{PAM_OP_PREFILL_SINGLE_PASS, 1, rq.seq_len, static_cast<int32_t>(numBlocks), 0, 0, nowMs() - t0};
+    c->clearError();
+    return 0;
+}
+
 int32_t pam_prefill(void* ctx, void* cache, int64_t id, void* q, void* out, int32_t seq_len, int32_t num_heads,
                     bool causal) {
     if (!ctx || !cache || !q || !out) return -1;                 // CABI.swift:257-262

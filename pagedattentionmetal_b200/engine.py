@@ -18,7 +18,8 @@ from . import _cabi
 from ._cabi import lib
 from .api_types import (BlockEvictionPolicy, KVCacheError, KVCacheMemoryStats, LogicalSequence,
                         Operation, PagedAttentionDataType, PagedAttentionDecodeRequest,
-                        PagedAttentionError, PagedAttentionPrefillRequest, PagedAttentionStats,
+                        PagedAttentionError, PagedAttentionFusedPrefillRequest, PagedAttentionPrefillRequest,
+                        PagedAttentionStats,
                         PagedKVAppendRequest, PagedLayerSpec, SchedulerSequence, SequenceStatus)
 
 
@@ -204,6 +205,17 @@ class PagedAttentionEngine:
                                     _buf(request.kScaleBuffer), _buf(request.vScaleBuffer),
                                     request.qStart, request.qLen)
         _check(self._ctx, lib.pamc_prefill(self._ctx, C.byref(r), chunkSize))
+
+    def fusedPrefill(self, request: PagedAttentionFusedPrefillRequest, cache: Optional["KVCacheManager"] = None) -> None:
+        """PagedAttentionEngine.swift:633-710: the raw keys and values of tokens
+        [0, seqLen) go into the pages and the prefill of the same rows runs over
+        them.  cache is the manager that owns the pools (required for FP8)."""
+        r = _cabi.PamFusedPrefillRequest(_buf(request.q), _buf(request.rawK), _buf(request.rawV),
+                                         _buf(request.blockTable), _buf(request.kPool), _buf(request.vPool),
+                                         _buf(request.output), request.seqLen, _layer(request.layer),
+                                         1 if request.causal else 0, _buf(request.kScaleBuffer),
+                                         _buf(request.vScaleBuffer))
+        _check(self._ctx, lib.pamc_fused_prefill(self._ctx, C.byref(r), cache._h if cache is not None else None))
 
     def prefillBatch(self, q, kPool, vPool, blockTables, output, seqLens: Sequence[int], qStarts: Sequence[int],
                      qLens: Sequence[int], maxNumBlocks: int, layer: PagedLayerSpec, causal: bool = True,

@@ -240,3 +240,87 @@ def test_prefill_batch_many_items_per_cta(engine, dtype):
         ref = co.prefill(qs[s], k_pool, v_pool, tables[s], seq_lens[s], KVH, bs, int(dtype), q_start=q_starts[s])
         assert_close(from_io(out[o:o + q_lens[s]], dtype), ref, dtype)
         o += q_lens[s]
+
+
+@pytest.mark.parametrize("dtype", [DT.float32, DT.float16, DT.bfloat16, DT.float8])
+@pytest.mark.parametrize("seq_len,window", [(128, 0), (301, 0), (640, 256)])
+def test_fused_prefill_equals_append_then_prefill(engine, dtype, seq_len, window):
+    """PagedAttentionEngine.fusedPrefill (PagedAttentionEngine.swift:633-710): the reference's
+    own test of the call (PagedAttentionMetalTests.swift:927-1037) compares the output and
+    both pools with a separate append followed by prefill; here they must be identical bit
+    for bit (FP8 codes and scales included), and the output must meet the oracle's bound
+    over the pools the oracle's append produces."""
+    rng = np.random.default_rng(70 + seq_len)
+    H, KVH, D, bs = 8, 2, 128, 16
+    n_pool = (seq_len + bs - 1) // bs + 3
+    layer = pam.PagedLayerSpec(D, H, KVH, bs, dtype, window)
+    io = DT.float16 if dtype == DT.float8 else dtype                       # FP8 pools take float16 rows
+    q = to_storage(rng.standard_normal((seq_len, H, D), dtype=np.float32), io)
+    k = to_storage(rng.standard_normal((seq_len, KVH, D), dtype=np.float32), io)
+    v = to_storage(rng.standard_normal((seq_len, KVH, D), dtype=np.float32), io)
+
+    def run(fused):
+        cache = pam.KVCacheManager(engine, n_pool, bs, D, KVH, dtype)
+        cache.allocateSequence(1)
+        cache.appendTokens(1, seq_len)
+        table = np.asarray(cache.getBlockTable(1), dtype=np.int32)
+        out = np.zeros_like(q)
+        if fused:
+            engine.fusedPrefill(pam.PagedAttentionFusedPrefillRequest(
+                q, k, v, table, cache.kPoolBuffer, cache.vPoolBuffer, out, seq_len, layer, True,
+                cache.kScaleBuffer, cache.vScaleBuffer), cache)
+            assert engine.lastStats.operation == pam.Operation.prefillSinglePass
+            assert engine.lastStats.sequenceLength == seq_len
+        else:
+            engine.appendKV(cache, 1, k, v, 0, seq_len, H)
+            engine.prefill(pam.PagedAttentionPrefillRequest(q, cache.kPoolBuffer, cache.vPoolBuffer, table, out,
+                                                            seq_len, layer, True, cache.kScaleBuffer,
+                                                            cache.vScaleBuffer))
+        pools = cache.readPools()
+        cache.close()
+        return out, pools, table
+
+    out_f, pools_f, table = run(True)
+    out_s, pools_s, table_s = run(False)
+    assert np.array_equal(table, table_s)
+    for a, b in zip(pools_f, pools_s):
+        assert (a is None) == (b is None)
+        if a is not None:
+            assert np.array_equal(a.view(np.uint8), b.view(np.uint8))
+    assert np.array_equal(out_f.view(np.uint8), out_s.view(np.uint8))
+    # against the oracle, over the pools the oracle's own append makes
+    ws = max(0, seq_len - window) if window > 0 else 0
+    kp, vp, ks, vs = pools_f
+    ref = co.prefill(q, kp, vp, table, seq_len, KVH, bs, int(dtype), causal=True, window_start=ws, q_start=0,
+                     k_scale=None if ks is None else ks.view(np.uint16),
+                     v_scale=None if vs is None else vs.view(np.uint16))
+    assert_close(from_io(out_f, dtype)[ws:], ref[ws:], dtype)
+    if dtype == DT.float8:
+        okp, ovp = np.zeros_like(kp), np.zeros_like(vp)
+        oks, ovs = np.zeros(ks.shape, np.uint16), np.zeros(vs.shape, np.uint16)
+        co.reshape_and_cache_fp8(k, v, okp, ovp, oks, ovs, po.slot_mapping(table, 0, seq_len, bs), bs)
+        assert np.array_equal(okp, kp) and np.array_equal(ovp, vp)
+        assert np.array_equal(oks, ks.view(np.uint16)) and np.array_equal(ovs, vs.view(np.uint16))
+
+
+def test_fused_prefill_errors(engine):
+    """seqLen and buffer checks in the reference's order (PagedAttentionEngine.swift:634-640)."""
+    D, H, KVH, bs = 128, 4, 2, 16
+    layer = pam.PagedLayerSpec(D, H, KVH, bs, DT.float16)
+    cache = pam.KVCacheManager(engine, 4, bs, D, KVH, DT.float16)
+    q = np.zeros((20, H, D), np.float16)
+    kv = np.zeros((20, KVH, D), np.float16)
+    table = np.array([0, 1], np.int32)
+    mk = lambda seq_len, tbl, out: pam.PagedAttentionFusedPrefillRequest(
+        q, kv, kv, tbl, cache.kPoolBuffer, cache.vPoolBuffer, out, seq_len, layer)
+    with pytest.raises(pam.PagedAttentionError, match="seqLen must be positive"):
+        engine.fusedPrefill(mk(0, table, np.zeros_like(q)))
+    with pytest.raises(pam.PagedAttentionError, match="blockTable"):
+        engine.fusedPrefill(mk(20, table[:1], np.zeros_like(q)))
+    with pytest.raises(pam.PagedAttentionError, match="output"):
+        engine.fusedPrefill(mk(20, table, np.zeros((10, H, D), np.float16)))
+    fp8 = pam.PagedLayerSpec(D, H, KVH, bs, DT.float8)
+    with pytest.raises(pam.PagedAttentionError, match="cache handle"):
+        engine.fusedPrefill(pam.PagedAttentionFusedPrefillRequest(
+            q, kv, kv, table, cache.kPoolBuffer, cache.vPoolBuffer, np.zeros_like(q), 20, fp8))
+    cache.close()
