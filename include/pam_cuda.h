@@ -385,6 +385,18 @@ typedef struct PamFusedPrefillRequest {
  * scale rows), may be NULL otherwise. */
 int32_t pamc_fused_prefill(void *ctx, const PamFusedPrefillRequest *request, void *cache);
 
+/* The batched-layer calls (PagedAttentionEngine.swift:1433-1895: prefillLayers,
+ * decodeLayers, appendLayers): one request per layer, enqueued back to back on
+ * the context's stream and waited for once.  The reference hands every layer
+ * the same pools; here each request names its own, so one pool per layer works
+ * too.  caches[i] (append only) is the handle that owns layer i's pools; it is
+ * required for FP8 layers, caches may be NULL otherwise.  num_layers <= 0 is
+ * the reference's "buffer/layer count mismatch". */
+int32_t pamc_decode_layers(void *ctx, const PamDecodeRequest *requests, int32_t num_layers);
+int32_t pamc_prefill_layers(void *ctx, const PamPrefillRequest *requests, int32_t num_layers);
+int32_t pamc_append_layers(void *ctx, const PamAppendRequest *requests, int32_t num_layers,
+                           void *const *caches);
+
 /* ------------------------------------------------------------------------
  * Scheduler (Scheduler.swift)
  * ---------------------------------------------------------------------- */

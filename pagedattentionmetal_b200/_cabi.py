@@ -148,6 +148,9 @@ SIGNATURES = {
     "pamc_decode_noalloc": (c_int32, [c_void_p, C.POINTER(PamDecodeRequest)]),
     "pamc_prefill": (c_int32, [c_void_p, C.POINTER(PamPrefillRequest), c_int32]),
     "pamc_prefill_batch": (c_int32, [c_void_p, C.POINTER(PamBatchPrefillRequest)]),
+    "pamc_decode_layers": (c_int32, [c_void_p, C.POINTER(PamDecodeRequest), c_int32]),
+    "pamc_prefill_layers": (c_int32, [c_void_p, C.POINTER(PamPrefillRequest), c_int32]),
+    "pamc_append_layers": (c_int32, [c_void_p, C.POINTER(PamAppendRequest), c_int32, C.POINTER(c_void_p)]),
     "pamc_fused_prefill": (c_int32, [c_void_p, C.POINTER(PamFusedPrefillRequest), c_void_p]),
     # scheduler
     "pamc_sched_create": (c_void_p, [c_int32, c_int32]),

@@ -699,6 +699,52 @@ Cache* createCache(Context* c, int32_t maxBlocks, int32_t blockSize, int32_t hea
     return k;
 }
 
+int32_t syncContext(Context* c) {
+    cudaError_t e = cudaSuccess;
+    if (c->errPending) e = cudaMemcpyAsync(c->hostErr, c->devErr, sizeof(int), cudaMemcpyDeviceToHost, c->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+    if (e != cudaSuccess) { cudaGetLastError(); return c->fail(PAM_ERR_COMMAND_EXECUTION, commandExecutionFailed(cudaGetErrorString(e))); }
+    if (c->errPending) {
+        c->errPending = false;
+        if (*c->hostErr != 0) {
+            const int site = *c->hostErr;
+            *c->hostErr = 0;
+            cudaMemsetAsync(c->devErr, 0, sizeof(int), c->stream);
+            return c->fail(PAM_ERR_COMMAND_EXECUTION, commandExecutionFailed("a kernel's bounded wait ran out (site " + std::to_string(site) + ")"));
+        }
+    }
+    return 0;
+}
+
+// The *Layers calls (PagedAttentionEngine.swift:1433-1895) run the same operation once per
+// layer and wait once at the end.  Here each layer's request is enqueued on the context's
+// stream without a wait in between, and the stream is waited for once (unless the context
+// is in async mode, where the caller waits).
+template <class Rq, class F>
+int32_t runLayers(void* ctx, const Rq* requests, int32_t numLayers, F one) {
+    if (!ctx) return -1;
+    Context* c = asCtx(ctx);
+    std::lock_guard<std::mutex> g(c->mu);
+    DeviceGuard dg(c->device);
+    if (c->device < 0) return noGpu(c);
+    if (!requests || numLayers <= 0) return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("buffer/layer count mismatch"));
+    const bool wasAsync = c->async;
+    c->async = true;
+    int32_t rc = 0;
+    const double t0 = nowMs();
+    for (int i = 0; i < numLayers && rc == 0; ++i) rc = one(c, requests[i], i);
+    c->async = wasAsync;
+    if (!wasAsync) {
+        const int32_t src = syncContext(c);
+        if (rc == 0) rc = src;
+    }
+    if (rc == 0) {
+        c->stats.elapsed_ms = nowMs() - t0;
+        c->clearError();
+    }
+    return rc;
+}
+
 }  // namespace
 
 // ======================================================================= C ABI
@@ -1021,20 +1067,7 @@ int32_t pamc_synchronize(void* ctx) {
     Context* c = asCtx(ctx);
     DeviceGuard dg(c->device);
     if (c->device < 0) return noGpu(c);
-    cudaError_t e = cudaSuccess;
-    if (c->errPending) e = cudaMemcpyAsync(c->hostErr, c->devErr, sizeof(int), cudaMemcpyDeviceToHost, c->stream);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
-    if (e != cudaSuccess) { cudaGetLastError(); return c->fail(PAM_ERR_COMMAND_EXECUTION, commandExecutionFailed(cudaGetErrorString(e))); }
-    if (c->errPending) {
-        c->errPending = false;
-        if (*c->hostErr != 0) {
-            const int site = *c->hostErr;
-            *c->hostErr = 0;
-            cudaMemsetAsync(c->devErr, 0, sizeof(int), c->stream);
-            return c->fail(PAM_ERR_COMMAND_EXECUTION, commandExecutionFailed("a kernel's bounded wait ran out (site " + std::to_string(site) + ")"));
-        }
-    }
-    return 0;
+    return syncContext(c);
 }
 int32_t pamc_set_max_retries(void* ctx, int32_t n) { if (!ctx || n < 0) return -1; asCtx(ctx)->maxRetries = n; return 0; }
 int32_t pamc_set_graceful_degradation(void* ctx, int32_t on) { if (!ctx) return -1; asCtx(ctx)->graceful = on != 0; return 0; }
@@ -1358,6 +1391,33 @@ int32_t pamc_fused_prefill(void* ctx, const PamFusedPrefillRequest* request, voi
     c->stats = PamStats{PAM_OP_PREFILL_SINGLE_PASS, 1, rq.seq_len, static_cast<int32_t>(numBlocks), 0, 0, nowMs() - t0};
     c->clearError();
     return 0;
+}
+
+int32_t pamc_decode_layers(void* ctx, const PamDecodeRequest* requests, int32_t num_layers) {
+    return runLayers(ctx, requests, num_layers, [](Context* c, const PamDecodeRequest& rq, int) { return decodeImpl(c, rq, 0); });
+}
+
+int32_t pamc_prefill_layers(void* ctx, const PamPrefillRequest* requests, int32_t num_layers) {
+    return runLayers(ctx, requests, num_layers, [](Context* c, const PamPrefillRequest& rq, int) -> int32_t {
+        if (rq.seq_len <= 0) return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("seqLen must be positive."));
+        const int qLen = rq.q_len > 0 ? rq.q_len : rq.seq_len;
+        const int qStart = rq.q_len > 0 ? rq.q_start : 0;
+        const int bs = std::max(rq.layer.block_size, 1);
+        const int maxNumBlocks = rq.block_table.bytes != kUnknownBytes
+                                     ? static_cast<int>(std::min<size_t>(rq.block_table.bytes / sizeof(int32_t), 1u << 30))
+                                     : (rq.seq_len + bs - 1) / bs;
+        return prefillImpl(c, rq.layer, rq.q, rq.k_pool, rq.v_pool, rq.block_table, rq.output, rq.k_scale, rq.v_scale,
+                           {PrefillSeq{rq.seq_len, qStart, qLen}}, maxNumBlocks, rq.causal != 0, "blockTable");
+    });
+}
+
+int32_t pamc_append_layers(void* ctx, const PamAppendRequest* requests, int32_t num_layers, void* const* caches) {
+    return runLayers(ctx, requests, num_layers, [caches](Context* c, const PamAppendRequest& rq, int i) -> int32_t {
+        Cache* k = caches && caches[i] ? asCache(caches[i]) : nullptr;
+        if (rq.layer.data_type == PAM_DTYPE_FP8 && !k)
+            return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("FP8 append needs the cache handle that owns the scale buffers."));
+        return appendImpl(c, rq, k, nullptr);
+    });
 }
 
 int32_t pam_prefill(void* ctx, void* cache, int64_t id, void* q, void* out, int32_t seq_len, int32_t num_heads,

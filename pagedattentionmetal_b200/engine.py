@@ -256,6 +256,74 @@ class PagedAttentionEngine:
                                    _buf(request.vScaleBuffer))
         _check(self._ctx, lib.pamc_append_to_cache(self._ctx, C.byref(r)))
 
+    # -- batched-layer calls (PagedAttentionEngine.swift:1433-1895) --
+    @staticmethod
+    def _perLayer(x, n: int, what: str) -> list:
+        """A buffer shared by all layers (the reference's kPool / vPool) or one per layer."""
+        if isinstance(x, (list, tuple)):
+            if len(x) != n:
+                raise PagedAttentionError(4, f"Invalid paged attention configuration: {what} count must match layers count")
+            return list(x)
+        return [x] * n
+
+    @staticmethod
+    def _layerCounts(n: int, *lists) -> None:
+        if n == 0 or any(len(x) != n for x in lists):       # :1445-1447, :1652-1654, :1757-1759
+            raise PagedAttentionError(4, "Invalid paged attention configuration: buffer/layer count mismatch")
+
+    def prefillLayers(self, qBuffers, kPool, vPool, blockTable, outputBuffers, seqLen: int,
+                      layers: Sequence[PagedLayerSpec], causal: bool = True, windowSize: int = 0,
+                      kScaleBuffers=None, vScaleBuffers=None) -> None:
+        """PagedAttentionEngine.swift:1433-1639: the prefill of every layer, one wait."""
+        n = len(layers)
+        self._layerCounts(n, qBuffers, outputBuffers)
+        kp, vp = self._perLayer(kPool, n, "kPool"), self._perLayer(vPool, n, "vPool")
+        ks, vs = self._perLayer(kScaleBuffers, n, "kScaleBuffers"), self._perLayer(vScaleBuffers, n, "vScaleBuffers")
+        arr = (_cabi.PamPrefillRequest * n)()
+        for i, spec in enumerate(layers):
+            arr[i] = _cabi.PamPrefillRequest(_buf(qBuffers[i]), _buf(kp[i]), _buf(vp[i]), _buf(blockTable),
+                                             _buf(outputBuffers[i]), seqLen, _layer(self._windowed(spec, windowSize)),
+                                             1 if causal else 0, _buf(ks[i]), _buf(vs[i]), 0, 0)
+        _check(self._ctx, lib.pamc_prefill_layers(self._ctx, arr, n))
+
+    def decodeLayers(self, qBuffers, kPool, vPool, blockTables, seqLengths, outputBuffers, batchSize: int,
+                     maxNumBlocks: int, layers: Sequence[PagedLayerSpec], windowSize: int = 0,
+                     kScaleBuffers=None, vScaleBuffers=None) -> None:
+        """PagedAttentionEngine.swift:1641-1742: the decode of every layer, one wait."""
+        n = len(layers)
+        self._layerCounts(n, qBuffers, outputBuffers)
+        kp, vp = self._perLayer(kPool, n, "kPool"), self._perLayer(vPool, n, "vPool")
+        ks, vs = self._perLayer(kScaleBuffers, n, "kScaleBuffers"), self._perLayer(vScaleBuffers, n, "vScaleBuffers")
+        arr = (_cabi.PamDecodeRequest * n)()
+        for i, spec in enumerate(layers):
+            arr[i] = _cabi.PamDecodeRequest(_buf(qBuffers[i]), _buf(kp[i]), _buf(vp[i]), _buf(blockTables),
+                                            _buf(seqLengths), _buf(outputBuffers[i]), batchSize, maxNumBlocks,
+                                            _layer(self._windowed(spec, windowSize)), _buf(ks[i]), _buf(vs[i]))
+        _check(self._ctx, lib.pamc_decode_layers(self._ctx, arr, n))
+
+    def appendLayers(self, keys, values, kPool, vPool, blockTable, tokenOffset: int, numNewTokens: int,
+                     layers: Sequence[PagedLayerSpec], kScaleBuffers=None, vScaleBuffers=None, caches=None) -> None:
+        """PagedAttentionEngine.swift:1744-1895: the append of every layer, one wait.
+        caches: the managers that own the pools, one per layer (required for FP8 layers)."""
+        n = len(layers)
+        self._layerCounts(n, keys, values)
+        kp, vp = self._perLayer(kPool, n, "kPool"), self._perLayer(vPool, n, "vPool")
+        ks, vs = self._perLayer(kScaleBuffers, n, "kScaleBuffers"), self._perLayer(vScaleBuffers, n, "vScaleBuffers")
+        cs = self._perLayer(caches, n, "caches")
+        arr = (_cabi.PamAppendRequest * n)()
+        for i, spec in enumerate(layers):
+            arr[i] = _cabi.PamAppendRequest(_buf(keys[i]), _buf(values[i]), _buf(kp[i]), _buf(vp[i]), _buf(blockTable),
+                                            tokenOffset, numNewTokens, _layer(spec), _buf(ks[i]), _buf(vs[i]))
+        handles = (C.c_void_p * n)(*[c._h if c is not None else None for c in cs])
+        _check(self._ctx, lib.pamc_append_layers(self._ctx, arr, n, handles))
+
+    @staticmethod
+    def _windowed(spec: PagedLayerSpec, windowSize: int) -> PagedLayerSpec:
+        """An explicit window wins over the layer's own (PagedAttentionEngine.swift:1466, 1673)."""
+        if windowSize > 0 and windowSize != spec.windowSize:
+            return PagedLayerSpec(spec.headDim, spec.numHeads, spec.numKVHeads, spec.blockSize, spec.dataType, windowSize)
+        return spec
+
     # -- cache-handle forms (the reference's C ABI, PagedAttentionCABI.swift:203-337) --
     def appendKV(self, cache: "KVCacheManager", sequenceId: int, keys, values, tokenOffset: int,
                  numNewTokens: int, numHeads: int) -> None:
