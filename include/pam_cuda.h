@@ -432,6 +432,41 @@ typedef struct PamSchedSequence {
 } PamSchedSequence;
 int32_t pamc_sched_get(void *sched, int64_t id, PamSchedSequence *out);
 
+/* ------------------------------------------------------------------------
+ * Inference orchestration (PagedAttentionInference.swift:7-299)
+ * ---------------------------------------------------------------------- */
+
+/* PagedAttentionInference.init (:47-90): a cache shaped by the first layer spec
+ * and a scheduler, owned by the handle; the engine is the given context.  NULL
+ * on error (message in the context). */
+void *pamc_infer_create(void *ctx, int32_t max_blocks, int32_t block_size, const PamLayerSpec *layers,
+                        int32_t num_layers, int32_t max_batch_size, int32_t max_sequences);
+void pamc_infer_destroy(void *infer);
+/* the handle's cache and scheduler (borrowed; valid for pam_* / pamc_cache_* and pamc_sched_*) */
+void *pamc_infer_cache(void *infer);
+void *pamc_infer_scheduler(void *infer);
+/* addRequest (:103-105), completeSequence (:108-114) */
+int64_t pamc_infer_add_request(void *infer, int32_t prompt_token_count, int32_t max_new_tokens);
+void pamc_infer_complete_sequence(void *infer, int64_t id);
+/* step (:119-148): prefill of the batch's sequences that are not prefilled yet
+ * (one prefillLayers each), one decodeLayers for the others, one token appended
+ * to each decoded sequence, finished sequences completed.  Returns the batch
+ * size (ids of the batch in out_ids, up to capacity), or -1 on error. */
+int32_t pamc_infer_step(void *infer, int64_t *out_ids, int32_t capacity);
+/* runAll (:151-156) */
+int32_t pamc_infer_run_all(void *infer);
+/* totalTokensGenerated (:166-170; prompt tokens count at prefill, :216), stepCount (:34) */
+int64_t pamc_infer_total_tokens(void *infer);
+int32_t pamc_infer_step_count(void *infer);
+/* onTokenGenerated (:27): called with (sequence id, token id = 0) per decoded token */
+typedef void (*pamc_token_fn)(void *user, int64_t sequence_id, int32_t token_id);
+void pamc_infer_set_token_callback(void *infer, pamc_token_fn fn, void *user);
+/* Under memory pressure the reference pauses every running sequence, because
+ * the free count it hands to handleMemoryPressure does not change while the
+ * victims are chosen (:280-299, Scheduler.swift:134-152).  on != 0: pause and
+ * free one victim at a time until enough blocks are free.  Default off. */
+void pamc_infer_set_incremental_preemption(void *infer, int32_t on);
+
 #ifdef __cplusplus
 }
 #endif

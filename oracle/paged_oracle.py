@@ -10,6 +10,7 @@ the reference project root):
 
 * ``KVCM``  = Sources/PagedAttentionMetal/KVCacheManager.swift
 * ``Sched`` = Sources/PagedAttentionMetal/Scheduler.swift
+* ``Infer`` = Sources/PagedAttentionMetal/PagedAttentionInference.swift
 * ``metal`` = Sources/PagedAttentionMetal/kernels.metal
 * ``tests`` = Tests/PagedAttentionMetalTests/PagedAttentionMetalTests.swift
 * ``sim``   = Reference/paged_attention_sim.py
@@ -321,6 +322,107 @@ class OracleScheduler:
 
     def count(self, status: int) -> int:  # Sched:154-170
         return sum(1 for s in self.seqs.values() if s["status"] == status)
+
+
+class OracleInference:
+    """The bookkeeping of ``PagedAttentionInference`` (Infer:7-299) without the
+    attention launches: which sequences a step prefills and decodes, the block
+    tables, lengths and counters it leaves.  ``launches`` records, per step,
+    ("prefill", id, seq_len, table) and ("decode", ids, lens, tables) in order."""
+
+    def __init__(self, max_blocks: int, block_size: int, max_batch_size: int = 16, max_sequences: int = 128,
+                 incremental_preemption: bool = False):
+        self.cache = OracleKVCacheManager(max_blocks, block_size)
+        self.sched = OracleScheduler(max_batch_size, max_sequences)
+        self.block_size = block_size
+        self.prefilled: set[int] = set()
+        self.total_tokens = 0
+        self.step_count = 0
+        self.tokens: list[tuple[int, int]] = []        # onTokenGenerated calls
+        self.launches: list[tuple] = []
+        self.incremental = incremental_preemption
+
+    def add_request(self, prompt_tokens: int, max_new_tokens: int) -> int:  # Infer:103-105
+        return self.sched.add_request(prompt_tokens, max_new_tokens)
+
+    def complete_sequence(self, sid: int) -> None:  # Infer:108-114
+        self.sched.complete_sequence(sid)
+        self.cache.free_sequence(sid)
+        self.prefilled.discard(sid)
+
+    def _ensure_blocks(self, needed: int) -> None:  # Infer:280-299
+        if self.cache.available_blocks >= needed:
+            return
+        if not self.incremental:
+            avail = self.cache.available_blocks       # read once: the victims are freed afterwards
+            for pid in self.sched.handle_memory_pressure(needed, lambda: avail):
+                self.cache.free_sequence(pid)
+                self.prefilled.discard(pid)
+        else:
+            while self.cache.available_blocks < needed:
+                calls = [0]
+
+                def available():
+                    calls[0] += 1
+                    return self.cache.available_blocks if calls[0] == 1 else needed
+
+                victims = self.sched.handle_memory_pressure(needed, available)
+                if not victims:
+                    break
+                for pid in victims:
+                    self.cache.free_sequence(pid)
+                    self.prefilled.discard(pid)
+        if self.cache.available_blocks < needed:
+            raise OutOfMemory()
+
+    def step(self) -> list[int]:  # Infer:119-148
+        batch = self.sched.step()
+        if not batch:
+            return []
+        prefill = [i for i in batch if i not in self.prefilled]
+        decode = [i for i in batch if i in self.prefilled]
+        bs = self.block_size
+        for sid in prefill:  # Infer:169-220
+            prompt = self.sched.seqs[sid]["prompt"]
+            self._ensure_blocks((prompt + bs - 1) // bs)
+            try:
+                self.cache.allocate_sequence(sid)
+            except SequenceAlreadyExists:
+                self.cache.free_sequence(sid)
+                self.cache.allocate_sequence(sid)
+            self.cache.append_tokens(sid, prompt)
+            self.launches.append(("prefill", sid, prompt, list(self.cache.block_table(sid))))
+            self.sched.mark_prefilled(sid)
+            self.prefilled.add(sid)
+            self.total_tokens += prompt
+        if decode:  # Infer:222-278
+            extras = 0
+            for sid in decode:
+                try:
+                    cur = self.cache.sequence_length(sid)
+                except SequenceNotFound:
+                    cur = self.sched.seqs[sid]["prompt"]
+                extras += max(0, (cur + 1 + bs - 1) // bs - (cur + bs - 1) // bs)
+            if extras > 0:
+                self._ensure_blocks(extras)
+            tables = [list(self.cache.block_table(sid)) for sid in decode]      # raises if a victim was in the batch
+            lens = [self.cache.sequence_length(sid) for sid in decode]
+            self.launches.append(("decode", list(decode), lens, tables))
+            for sid in decode:
+                self.cache.append_tokens(sid, 1)
+                self.sched.mark_decoded(sid)
+                self.total_tokens += 1
+                self.tokens.append((sid, 0))
+                sq = self.sched.seqs[sid]
+                if sq["gen"] >= sq["max_new"]:
+                    self.complete_sequence(sid)
+        self.step_count += 1
+        return batch
+
+    def run_all(self) -> None:  # Infer:151-156
+        while self.sched.count(WAITING) > 0 or self.sched.count(RUNNING) > 0:
+            if not self.step():
+                break
 
 
 # --------------------------------------------------------------------------

@@ -15,7 +15,7 @@ _API = {
                   "PagedAttentionPrefillRequest", "PagedAttentionStats", "PagedKVAppendRequest", "PagedLayerSpec",
                   "SchedulerSequence", "SequenceStatus"],
     "engine": ["BatchKVCacheManager", "ContinuousBatchingScheduler", "DeviceBuffer", "KVCacheManager",
-               "PagedAttentionEngine"],
+               "PagedAttentionEngine", "PagedAttentionInference"],
 }
 _WHERE = {name: mod for mod, names in _API.items() for name in names}
 __all__ = sorted(_WHERE)

@@ -86,6 +86,7 @@ class PamSchedSequence(C.Structure):
 
 
 AVAILABLE_FN = C.CFUNCTYPE(c_int32, c_void_p)
+TOKEN_FN = C.CFUNCTYPE(None, c_void_p, c_int64, c_int32)
 
 # name -> (restype, argtypes); every symbol include/pam_cuda.h declares.
 SIGNATURES = {
@@ -164,6 +165,19 @@ SIGNATURES = {
     "pamc_sched_handle_memory_pressure": (c_int32, [c_void_p, c_int32, AVAILABLE_FN, c_void_p, C.POINTER(c_int64), c_int32]),
     "pamc_sched_count": (c_int32, [c_void_p, c_int32]),
     "pamc_sched_total": (c_int32, [c_void_p]),
+    # inference orchestration
+    "pamc_infer_create": (c_void_p, [c_void_p, c_int32, c_int32, C.POINTER(PamLayerSpec), c_int32, c_int32, c_int32]),
+    "pamc_infer_destroy": (None, [c_void_p]),
+    "pamc_infer_cache": (c_void_p, [c_void_p]),
+    "pamc_infer_scheduler": (c_void_p, [c_void_p]),
+    "pamc_infer_add_request": (c_int64, [c_void_p, c_int32, c_int32]),
+    "pamc_infer_complete_sequence": (None, [c_void_p, c_int64]),
+    "pamc_infer_step": (c_int32, [c_void_p, C.POINTER(c_int64), c_int32]),
+    "pamc_infer_run_all": (c_int32, [c_void_p]),
+    "pamc_infer_total_tokens": (c_int64, [c_void_p]),
+    "pamc_infer_step_count": (c_int32, [c_void_p]),
+    "pamc_infer_set_token_callback": (None, [c_void_p, TOKEN_FN, c_void_p]),
+    "pamc_infer_set_incremental_preemption": (None, [c_void_p, c_int32]),
     "pamc_sched_get": (c_int32, [c_void_p, c_int64, C.POINTER(PamSchedSequence)]),
 }
 

@@ -13,6 +13,7 @@
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <set>
 #include <string>
 #include <unordered_set>
 #include <vector>
@@ -1475,6 +1476,296 @@ int32_t pamc_sched_get(void* s, int64_t id, PamSchedSequence* out) {
     out->id = q.id; out->status = q.status; out->num_generated_tokens = q.numGeneratedTokens;
     out->max_new_tokens = q.maxNewTokens; out->prompt_length = q.promptLength; out->arrival_order = q.arrivalOrder;
     return 0;
+}
+
+// ------------------------------------------------------------------ inference orchestration
+// PagedAttentionInference (PagedAttentionInference.swift:7-299): scheduler + cache + engine
+// driven step by step.  Like the reference it has no model: the queries are zeroed buffers
+// and nothing is appended to the pools; what it exercises is the scheduling, the block
+// bookkeeping and the batched-layer attention launches.
+
+struct Inference {
+    Context* c = nullptr;
+    Cache* cache = nullptr;
+    Sched* sched = nullptr;
+    std::vector<PamLayerSpec> layers;
+    int maxBatch = 0;
+    bool incrementalPreemption = false;
+    std::set<int64_t> prefilled;                      // :29
+    long long totalTokens = 0;                        // :31
+    int stepCount = 0;                                // :34
+    pamc_token_fn onToken = nullptr;                  // :27
+    void* onTokenUser = nullptr;
+    std::mutex mu;
+    std::vector<void*> q, out;                        // per layer, grown on demand
+    std::vector<size_t> cap;
+    ~Inference() {
+        if (c && c->device >= 0) {
+            cudaSetDevice(c->device);
+            cudaStreamSynchronize(c->stream);
+            for (void* p : q) cudaFree(p);
+            for (void* p : out) cudaFree(p);
+        }
+        delete sched;
+        delete cache;
+    }
+};
+
+static int32_t inferFail(Inference* inf, int code, const std::string& m) {
+    std::lock_guard<std::mutex> g(inf->c->mu);
+    return inf->c->fail(code, m);
+}
+static int32_t inferKvFail(Inference* inf, const KVResult& r) {
+    std::lock_guard<std::mutex> g(inf->c->mu);
+    return kvFail(inf->c, r);
+}
+
+// zeroed query rows and an output buffer per layer (the reference makes fresh shared
+// buffers every step, PagedAttentionInference.swift:190-202, 241-253)
+static int32_t inferBuffers(Inference* inf, size_t rows) {
+    Context* c = inf->c;
+    DeviceGuard dg(c->device);
+    for (size_t l = 0; l < inf->layers.size(); ++l) {
+        const size_t need = std::max<size_t>(rows * qBytesPerToken(inf->layers[l]), 16);
+        if (inf->cap[l] < need) {
+            cudaStreamSynchronize(c->stream);
+            cudaFree(inf->q[l]); cudaFree(inf->out[l]);
+            inf->q[l] = inf->out[l] = nullptr; inf->cap[l] = 0;
+            cudaError_t e = cudaMalloc(&inf->q[l], need);
+            if (e == cudaSuccess) e = cudaMalloc(&inf->out[l], need);
+            if (e != cudaSuccess) {
+                cudaGetLastError();
+                return inferFail(inf, PAM_ERR_COMMAND_ENCODING, "Failed to encode Metal command: unable to allocate attention buffers");
+            }
+            inf->cap[l] = need;
+        }
+        if (cudaMemsetAsync(inf->q[l], 0, need, c->stream) != cudaSuccess) {
+            cudaGetLastError();
+            return inferFail(inf, PAM_ERR_COMMAND_EXECUTION, commandExecutionFailed("memset of the query buffer failed"));
+        }
+    }
+    return 0;
+}
+
+static void inferForget(Inference* inf, int64_t id) {
+    inf->cache->mgr.freeSequence(id);
+    inf->prefilled.erase(id);
+}
+
+// ensureBlocksAvailable (PagedAttentionInference.swift:280-299).  The reference reads the
+// free count once per call of handleMemoryPressure while the victims' blocks are only
+// freed afterwards, so under pressure every running sequence is paused; with
+// incrementalPreemption one victim is paused and freed at a time.
+static int32_t inferEnsureBlocks(Inference* inf, int needed) {
+    BlockManager& mgr = inf->cache->mgr;
+    if (mgr.availableBlocks() >= needed) return 0;
+    if (!inf->incrementalPreemption) {
+        const int avail = mgr.availableBlocks();
+        for (int64_t id : inf->sched->s.handleMemoryPressure(needed, [&]() { return avail; })) inferForget(inf, id);
+    } else {
+        while (mgr.availableBlocks() < needed) {
+            bool first = true;
+            std::vector<int64_t> v = inf->sched->s.handleMemoryPressure(needed, [&]() {
+                const int a = first ? mgr.availableBlocks() : needed;
+                first = false;
+                return a;
+            });
+            if (v.empty()) break;
+            for (int64_t id : v) inferForget(inf, id);
+        }
+    }
+    if (mgr.availableBlocks() < needed) return inferKvFail(inf, KVResult{KVStatus::outOfMemory, ""});
+    return 0;
+}
+
+static void inferComplete(Inference* inf, int64_t id) {     // :108-114
+    inf->sched->s.complete(id);
+    inferForget(inf, id);
+}
+
+static int32_t inferPrefill(Inference* inf, const pam::SchedulerSequence& seq) {     // :169-220
+    Cache* k = inf->cache;
+    const int needed = (seq.promptLength + k->blockSize - 1) / k->blockSize;
+    if (int32_t rc = inferEnsureBlocks(inf, needed)) return rc;
+    KVResult r = k->mgr.allocateSequence(seq.id);
+    if (r.status == KVStatus::sequenceAlreadyExists) {
+        k->mgr.freeSequence(seq.id);
+        r = k->mgr.allocateSequence(seq.id);
+    }
+    if (!r.ok()) return inferKvFail(inf, r);
+    r = k->mgr.appendTokens(seq.id, seq.promptLength, nullptr, 0, nullptr);
+    if (!r.ok()) return inferKvFail(inf, r);
+    std::vector<int32_t> table;
+    r = k->mgr.blockTable(seq.id, &table);
+    if (!r.ok()) return inferKvFail(inf, r);
+    if (table.empty()) table.push_back(0);
+    if (int32_t rc = inferBuffers(inf, static_cast<size_t>(std::max(seq.promptLength, 0)))) return rc;
+    std::vector<PamPrefillRequest> rq(inf->layers.size());
+    for (size_t l = 0; l < rq.size(); ++l) {
+        const size_t bytes = static_cast<size_t>(std::max(seq.promptLength, 0)) * qBytesPerToken(inf->layers[l]);
+        rq[l] = PamPrefillRequest{};
+        rq[l].q = buf(inf->q[l], bytes); rq[l].output = buf(inf->out[l], bytes);
+        rq[l].k_pool = buf(k->kPool, k->poolBytes); rq[l].v_pool = buf(k->vPool, k->poolBytes);
+        rq[l].block_table = buf(table.data(), table.size() * sizeof(int32_t));
+        rq[l].seq_len = seq.promptLength; rq[l].layer = inf->layers[l]; rq[l].causal = 1;
+        rq[l].k_scale = buf(k->kScale, k->scaleBytes); rq[l].v_scale = buf(k->vScale, k->scaleBytes);
+    }
+    if (int32_t rc = pamc_prefill_layers(inf->c, rq.data(), static_cast<int32_t>(rq.size()))) return rc;
+    inf->sched->s.markPrefilled(seq.id);
+    inf->prefilled.insert(seq.id);
+    inf->totalTokens += seq.promptLength;
+    return 0;
+}
+
+static int32_t inferDecode(Inference* inf, const std::vector<pam::SchedulerSequence>& seqs) {   // :222-278
+    Cache* k = inf->cache;
+    const int n = static_cast<int>(seqs.size());
+    std::vector<int64_t> ids;
+    int totalExtras = 0;
+    for (auto& sq : seqs) {
+        ids.push_back(sq.id);
+        int64_t len = 0;
+        if (!k->mgr.sequenceLength(sq.id, &len).ok()) len = sq.promptLength;
+        const int64_t now = (len + k->blockSize - 1) / k->blockSize, after = (len + 1 + k->blockSize - 1) / k->blockSize;
+        totalExtras += static_cast<int>(std::max<int64_t>(0, after - now));
+    }
+    if (totalExtras > 0)
+        if (int32_t rc = inferEnsureBlocks(inf, totalExtras)) return rc;
+    // The reference's table rows are maxSequenceBlocks (= maxBlocks) wide (:75, 238); the
+    // widest table of the batch gives the same result with a smaller upload.
+    int maxNumBlocks = 1;
+    std::vector<int32_t> t;
+    for (int64_t id : ids) {
+        KVResult r = k->mgr.blockTable(id, &t);
+        if (!r.ok()) return inferKvFail(inf, r);
+        maxNumBlocks = std::max(maxNumBlocks, static_cast<int>(t.size()));
+    }
+    std::vector<int32_t> tables;
+    std::vector<uint32_t> lens;
+    {
+        std::lock_guard<std::mutex> g(inf->c->mu);
+        if (buildBatchTables(inf->c, k, ids.data(), n, maxNumBlocks, &tables, &lens, nullptr) != 0) return -1;
+    }
+    if (int32_t rc = inferBuffers(inf, static_cast<size_t>(n))) return rc;
+    std::vector<PamDecodeRequest> rq(inf->layers.size());
+    for (size_t l = 0; l < rq.size(); ++l) {
+        const size_t bytes = static_cast<size_t>(n) * qBytesPerToken(inf->layers[l]);
+        rq[l] = PamDecodeRequest{};
+        rq[l].q = buf(inf->q[l], bytes); rq[l].output = buf(inf->out[l], bytes);
+        rq[l].k_pool = buf(k->kPool, k->poolBytes); rq[l].v_pool = buf(k->vPool, k->poolBytes);
+        rq[l].block_tables = buf(tables.data(), tables.size() * sizeof(int32_t));
+        rq[l].seq_lengths = buf(lens.data(), lens.size() * sizeof(uint32_t));
+        rq[l].batch_size = n; rq[l].max_num_blocks = maxNumBlocks; rq[l].layer = inf->layers[l];
+        rq[l].k_scale = buf(k->kScale, k->scaleBytes); rq[l].v_scale = buf(k->vScale, k->scaleBytes);
+    }
+    if (int32_t rc = pamc_decode_layers(inf->c, rq.data(), static_cast<int32_t>(rq.size()))) return rc;
+    for (auto& sq : seqs) {
+        KVResult r = k->mgr.appendTokens(sq.id, 1, nullptr, 0, nullptr);
+        if (!r.ok()) return inferKvFail(inf, r);
+        inf->sched->s.markDecoded(sq.id);
+        inf->totalTokens += 1;
+        if (inf->onToken) inf->onToken(inf->onTokenUser, sq.id, 0);
+        pam::SchedulerSequence now;
+        if (inf->sched->s.get(sq.id, &now) && now.isDone()) inferComplete(inf, sq.id);
+    }
+    return 0;
+}
+
+static int32_t inferStep(Inference* inf, std::vector<int64_t>* batch) {      // :119-148
+    *batch = inf->sched->s.step();
+    if (batch->empty()) return 0;
+    std::vector<pam::SchedulerSequence> prefill, decode;
+    for (int64_t id : *batch) {
+        pam::SchedulerSequence sq;
+        if (!inf->sched->s.get(id, &sq)) continue;
+        (inf->prefilled.count(id) ? decode : prefill).push_back(sq);
+    }
+    for (auto& sq : prefill)
+        if (int32_t rc = inferPrefill(inf, sq)) return rc;
+    if (!decode.empty())
+        if (int32_t rc = inferDecode(inf, decode)) return rc;
+    inf->stepCount += 1;
+    return 0;
+}
+
+void* pamc_infer_create(void* ctx, int32_t max_blocks, int32_t block_size, const PamLayerSpec* layers, int32_t num_layers,
+                        int32_t max_batch_size, int32_t max_sequences) {
+    if (!ctx) return nullptr;
+    Context* c = asCtx(ctx);
+    if (!layers || num_layers <= 0) {                              // :55-57
+        std::lock_guard<std::mutex> g(c->mu);
+        c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("at least one layer spec required"));
+        return nullptr;
+    }
+    // pools are shaped by the first layer (:59-62, 76-85)
+    void* cache = pam_create_cache(ctx, max_blocks, block_size, layers[0].head_dim, layers[0].num_kv_heads, layers[0].data_type);
+    if (!cache) return nullptr;
+    Inference* inf = new Inference();
+    inf->c = c;
+    inf->cache = asCache(cache);
+    inf->sched = new Sched(max_batch_size, max_sequences);
+    inf->layers.assign(layers, layers + num_layers);
+    inf->maxBatch = max_batch_size;
+    inf->q.assign(static_cast<size_t>(num_layers), nullptr);
+    inf->out.assign(static_cast<size_t>(num_layers), nullptr);
+    inf->cap.assign(static_cast<size_t>(num_layers), 0);
+    return inf;
+}
+void pamc_infer_destroy(void* infer) { delete static_cast<Inference*>(infer); }
+void* pamc_infer_cache(void* infer) { return infer ? static_cast<Inference*>(infer)->cache : nullptr; }
+void* pamc_infer_scheduler(void* infer) { return infer ? static_cast<Inference*>(infer)->sched : nullptr; }
+int64_t pamc_infer_add_request(void* infer, int32_t prompt_token_count, int32_t max_new_tokens) {     // :103-105
+    return infer ? static_cast<Inference*>(infer)->sched->s.addRequest(prompt_token_count, max_new_tokens) : -1;
+}
+void pamc_infer_complete_sequence(void* infer, int64_t id) {
+    if (!infer) return;
+    Inference* inf = static_cast<Inference*>(infer);
+    std::lock_guard<std::mutex> g(inf->mu);
+    inferComplete(inf, id);
+}
+int32_t pamc_infer_step(void* infer, int64_t* out_ids, int32_t capacity) {
+    if (!infer) return -1;
+    Inference* inf = static_cast<Inference*>(infer);
+    std::lock_guard<std::mutex> g(inf->mu);
+    std::vector<int64_t> batch;
+    if (inferStep(inf, &batch) != 0) return -1;
+    for (int i = 0; out_ids && i < capacity && i < static_cast<int>(batch.size()); ++i) out_ids[i] = batch[static_cast<size_t>(i)];
+    return static_cast<int32_t>(batch.size());
+}
+int32_t pamc_infer_run_all(void* infer) {                          // :151-156
+    if (!infer) return -1;
+    Inference* inf = static_cast<Inference*>(infer);
+    std::lock_guard<std::mutex> g(inf->mu);
+    while (inf->sched->s.count(pam::waiting) > 0 || inf->sched->s.count(pam::running) > 0) {
+        std::vector<int64_t> batch;
+        if (inferStep(inf, &batch) != 0) return -1;
+        if (batch.empty()) break;
+    }
+    return 0;
+}
+int64_t pamc_infer_total_tokens(void* infer) {
+    if (!infer) return -1;
+    Inference* inf = static_cast<Inference*>(infer);
+    std::lock_guard<std::mutex> g(inf->mu);
+    return inf->totalTokens;
+}
+int32_t pamc_infer_step_count(void* infer) {
+    if (!infer) return -1;
+    Inference* inf = static_cast<Inference*>(infer);
+    std::lock_guard<std::mutex> g(inf->mu);
+    return inf->stepCount;
+}
+void pamc_infer_set_token_callback(void* infer, pamc_token_fn fn, void* user) {
+    if (!infer) return;
+    Inference* inf = static_cast<Inference*>(infer);
+    std::lock_guard<std::mutex> g(inf->mu);
+    inf->onToken = fn; inf->onTokenUser = user;
+}
+void pamc_infer_set_incremental_preemption(void* infer, int32_t on) {
+    if (!infer) return;
+    Inference* inf = static_cast<Inference*>(infer);
+    std::lock_guard<std::mutex> g(inf->mu);
+    inf->incrementalPreemption = on != 0;
 }
 
 }  // extern "C"

@@ -665,3 +665,111 @@ class ContinuousBatchingScheduler:
     @property
     def totalSequencesProcessed(self) -> int:                                       # Scheduler.swift:172-176
         return lib.pamc_sched_total(self._h)
+
+
+class PagedAttentionInference:
+    """PagedAttentionInference (PagedAttentionInference.swift:7-299): engine,
+    cache and scheduler driven step by step.  The state machine lives in the
+    library (pamc_infer_*); ``cache`` and ``scheduler`` are views of the handles
+    it owns."""
+
+    def __init__(self, maxBlocks: int, blockSize: int = 16, layerSpecs: Sequence[PagedLayerSpec] = (),
+                 maxBatchSize: int = 16, maxSequences: int = 128, engine: Optional[PagedAttentionEngine] = None):
+        self.engine = engine if engine is not None else PagedAttentionEngine()
+        self.layerSpecs = list(layerSpecs)
+        self.maxBatchSize, self.numLayers = maxBatchSize, len(self.layerSpecs)
+        specs = (_cabi.PamLayerSpec * max(self.numLayers, 1))(*[_layer(s) for s in self.layerSpecs])
+        self._h = lib.pamc_infer_create(self.engine._ctx, maxBlocks, blockSize, specs, self.numLayers, maxBatchSize,
+                                        maxSequences)
+        if not self._h:
+            _raise(self.engine._ctx)
+        first = self.layerSpecs[0]
+        # views of the handles the library object owns (never destroyed from here)
+        cache = object.__new__(BatchKVCacheManager)
+        cache.engine, cache._ctx, cache._ownCtx = self.engine, self.engine._ctx, None
+        cache.maxBlocks, cache.blockSize, cache.headDim, cache.numKVHeads = maxBlocks, blockSize, first.headDim, first.numKVHeads
+        cache.dataType = PagedAttentionDataType(first.dataType)
+        cache._policy = BlockEvictionPolicy.fifo
+        cache.maxBatchSize, cache.maxSequenceBlocks = maxBatchSize, maxBlocks            # :75
+        cache._h = lib.pamc_infer_cache(self._h)
+        cache.close = lambda: None
+        cache.blockTablesSlab = cache.seqLengthsSlab = None
+        self.cache = cache
+        self.scheduler = _BorrowedScheduler(lib.pamc_infer_scheduler(self._h), maxBatchSize, maxSequences)
+        self._callback = None
+        self._onTokenGenerated = None
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self.cache._h = None
+            lib.pamc_infer_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def onTokenGenerated(self):
+        return self._onTokenGenerated
+
+    @onTokenGenerated.setter
+    def onTokenGenerated(self, fn) -> None:                                  # :27
+        self._onTokenGenerated = fn
+        self._callback = _cabi.TOKEN_FN(lambda user, seq, tok: fn(int(seq), int(tok))) if fn else _cabi.TOKEN_FN(0)
+        lib.pamc_infer_set_token_callback(self._h, self._callback, None)
+
+    def setIncrementalPreemption(self, on: bool) -> None:
+        """Pause one victim at a time under memory pressure instead of every
+        running sequence (see pamc_infer_set_incremental_preemption)."""
+        lib.pamc_infer_set_incremental_preemption(self._h, 1 if on else 0)
+
+    def addRequest(self, promptTokenCount: int, maxNewTokens: int) -> int:   # :103-105
+        return int(lib.pamc_infer_add_request(self._h, promptTokenCount, maxNewTokens))
+
+    def completeSequence(self, id: int) -> None:                             # :108-114
+        lib.pamc_infer_complete_sequence(self._h, id)
+
+    def step(self) -> list:                                                  # :119-148
+        cap = max(self.maxBatchSize, 1)
+        out = (C.c_int64 * cap)()
+        n = lib.pamc_infer_step(self._h, out, cap)
+        if n < 0:
+            _raise(self.engine._ctx)
+        return [self.scheduler._get(out[i]) for i in range(min(n, cap))]
+
+    def runAll(self) -> None:                                                # :151-156
+        _check(self.engine._ctx, lib.pamc_infer_run_all(self._h))
+
+    @property
+    def waitingCount(self) -> int:
+        return self.scheduler.waitingCount
+
+    @property
+    def runningCount(self) -> int:
+        return self.scheduler.runningCount
+
+    @property
+    def completedCount(self) -> int:
+        return self.scheduler.completedCount
+
+    @property
+    def totalTokensGenerated(self) -> int:                                   # :166-170
+        return int(lib.pamc_infer_total_tokens(self._h))
+
+    @property
+    def stepCount(self) -> int:                                              # :34
+        return int(lib.pamc_infer_step_count(self._h))
+
+
+class _BorrowedScheduler(ContinuousBatchingScheduler):
+    """The scheduler a PagedAttentionInference owns: same methods, not destroyed here."""
+
+    def __init__(self, handle, maxBatchSize: int, maxSequences: int):
+        self.maxBatchSize, self.maxSequences = maxBatchSize, maxSequences
+        self._h = handle
+
+    def __del__(self):
+        self._h = None

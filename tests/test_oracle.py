@@ -203,3 +203,51 @@ def test_copy_blocks_np_vs_c():
     co.copy_blocks(k2, v2, src, dst)
     assert np.array_equal(k, k2) and np.array_equal(v, v2)
     assert np.array_equal(k[0], k[1]) and np.array_equal(v[11], v[7])
+
+
+def test_inference_state_machine_hand_checked():
+    """OracleInference (PagedAttentionInference.swift:119-299).  The reference has no test
+    of this class, so the restatement is checked against a run worked out by hand from the
+    source: batch of 3, prompts (40, 3 new), (17, 1), (100, 5), (5, 2), (64, 4)."""
+    ora = po.OracleInference(64, 16, 3)
+    for prompt, new in ((40, 3), (17, 1), (100, 5), (5, 2), (64, 4)):
+        ora.add_request(prompt, new)
+    # step 1: the first three waiting sequences are prefilled (3 + 2 + 7 blocks), nothing decodes
+    assert ora.step() == [0, 1, 2]
+    assert [l[0] for l in ora.launches] == ["prefill"] * 3
+    assert ora.cache.available_blocks == 64 - 12 and ora.total_tokens == 157 and ora.tokens == []
+    # step 2: waiting sequences come first (Scheduler.swift:90-95), one running one fits
+    assert ora.step() == [3, 4, 0]
+    assert ora.launches[-1] == ("decode", [0], [40], [ora.cache.block_table(0)])
+    assert ora.cache.sequence_length(0) == 41 and ora.tokens == [(0, 0)]
+    # step 3: all five are running, the first three by arrival decode; sequence 1 is done
+    assert ora.step() == [0, 1, 2]
+    assert ora.sched.seqs[1]["status"] == po.COMPLETED and 1 not in ora.cache.sequences
+    ora.run_all()
+    assert ora.step_count == 8 and ora.total_tokens == 226 + 15 and len(ora.tokens) == 15
+    assert ora.cache.available_blocks == 64 and ora.sched.count(po.COMPLETED) == 5
+
+
+def test_inference_memory_pressure_policies():
+    """ensureBlocksAvailable (PagedAttentionInference.swift:280-299): the free count handed to
+    handleMemoryPressure is read once, so every running sequence is paused; the incremental
+    option pauses one at a time (newest first, the sequence being prefilled included, since
+    the scheduler's step has already promoted it)."""
+    for incremental, paused, new_one in ((False, [0, 1, 2], po.RUNNING), (True, [2], po.PAUSED)):
+        ora = po.OracleInference(14, 16, 4, 128, incremental)
+        for _ in range(3):
+            ora.add_request(48, 8)
+        assert ora.step() == [0, 1, 2] and ora.step() == [0, 1, 2]
+        assert ora.cache.available_blocks == 2
+        ora.add_request(90, 2)
+        with pytest.raises(po.SequenceNotFound):       # a victim was part of the same batch
+            ora.step()
+        assert [i for i in range(3) if ora.sched.seqs[i]["status"] == po.PAUSED] == paused
+        # incremental: the decode of the same step needs one more block for the sequence whose
+        # pages are gone (its length falls back to the prompt's, :226-231), and the newest
+        # running sequence, the one just prefilled, pays for it
+        assert ora.sched.seqs[3]["status"] == new_one and (3 in ora.prefilled) == (new_one == po.RUNNING)
+    ora = po.OracleInference(4, 16, 2)
+    ora.add_request(200, 1)
+    with pytest.raises(po.OutOfMemory):
+        ora.step()
