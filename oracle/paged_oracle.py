@@ -20,7 +20,9 @@ reference's own numpy implementation) stored under tests/golden/, and the
 allocator against the integer facts asserted by the reference's tests
 (tests:599-604, 758-770, 799-807, 739-749).  The FP8 codec and the sliding
 window have no golden vectors in the reference ("parity unpinned" for those
-two): they follow the shader source text line by line.
+two): they follow the shader source text line by line.  ``OracleInference``
+is likewise unpinned (the reference has no test of ``Infer``); it follows the
+source and a run worked out by hand.
 
 KV pool layout used here is the build's layout, ``[block][kv_head][slot][dim]``;
 the reference stores ``[block][slot][kv_head][dim]`` (metal:1829-1832).  The two
