@@ -796,6 +796,35 @@ def run_decode_fp8(args):
         torch.cuda.synchronize(dev)
         engine.synchronize()
         ms_decode = d0.elapsed_time(d1) / args.steps
+    # The same decode launches replayed from a CUDA graph: the device time of the kernels
+    # without the host's per-call work (request checks, launch calls), which is of the same
+    # order as this short step.
+    ms_graph = None
+    try:
+        if args.profile:
+            raise RuntimeError("skipped under --profile")
+        graph = torch.cuda.CUDAGraph()
+        cap = torch.cuda.Stream(dev)
+        cap.wait_stream(stream)
+        engine.setStream(cap.cuda_stream)
+        with torch.cuda.graph(graph, stream=cap):
+            for _ in range(args.steps):
+                engine.decode(req)
+        engine.setStream(stream.cuda_stream)
+        stream.wait_stream(cap)
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize(dev)
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record(stream)
+        graph.replay()
+        g1.record(stream)
+        torch.cuda.synchronize(dev)
+        engine.synchronize()
+        ms_graph = g0.elapsed_time(g1) / args.steps
+    except Exception as exc:           # capture refused: the eager figures stand alone
+        engine.setStream(stream.cuda_stream)
+        print(f"graph replay not measured: {exc}", file=sys.stderr)
     clocks = sampler.stop()
     # visible tokens per sequence: tokens in blocks >= floor((L - W) / 16); K and V codes, scales, q, out, tables
     nvis = np.array([int(l) - ((int(l) - C4_WINDOW) // BLOCK) * BLOCK for l in lens])
@@ -816,6 +845,9 @@ def run_decode_fp8(args):
                          "peak_source": f"{kind} copy bandwidth", "kernel": "decodeSplitFp8Kernel (+ decodeMergeKernel)",
                          "algorithmic_bytes_per_launch": bytes_step, "traffic": None},
             "gpu_launches": int(launches), "clocks": clocks}
+    if ms_graph is not None:
+        line["graph_replay"] = {"decode_ms_per_step": ms_graph, "kv_read_gbs": bytes_step / (ms_graph * 1e-3) / 1e9,
+                                "frac": bytes_step / (ms_graph * 1e-3) / 1e9 / peak}
     if whole:
         pf_flops = C4_HEADS * (C4_CHUNK * (C4_CHUNK + 1) // 2) * 4 * HEAD_DIM
         line["step_parts"] = {"decode_ms": ms_decode, "append_and_prefill_ms": ms_step - ms_decode,
