@@ -324,3 +324,75 @@ def test_fused_prefill_errors(engine):
         engine.fusedPrefill(pam.PagedAttentionFusedPrefillRequest(
             q, kv, kv, table, cache.kPoolBuffer, cache.vPoolBuffer, np.zeros_like(q), 20, fp8))
     cache.close()
+
+
+def test_prefill_shared_prefix_with_copy_on_write(engine):
+    """The prefill configuration with a shared prefix that ends inside a block: 2048-token
+    bfloat16 sequences of 32 query / 8 KV heads in chunks of 512, the first 1032 tokens (65
+    block hashes, the last block half full) shared.  Every follower's first own append
+    copies that block (KVCacheManager.swift:134-140, 176-194).  Block tables and the
+    copy-on-write log must equal the oracle manager's, the pools the oracle's scatter and
+    block copies bit for bit, and chunk rows on both sides of the copied block the oracle's
+    attention."""
+    rng = np.random.default_rng(1003)
+    n_seq, prefix, total, chunk, H, KVH, D, bs = 4, 1032, 2048, 512, 32, 8, 128, 16
+    dtype = DT.bfloat16
+    n_hash = (prefix + bs - 1) // bs                                        # 65
+    n_pool = 128 + (n_seq - 1) * 64 + 8
+    cache = pam.KVCacheManager(engine, n_pool, bs, D, KVH, dtype)
+    ora = po.OracleKVCacheManager(n_pool, bs)
+    ok_pool = np.zeros((n_pool, KVH, bs, D), np.uint16)
+    ov_pool = np.zeros_like(ok_pool)
+    shared_k = rng.standard_normal((prefix, KVH, D), dtype=np.float32)
+    shared_v = rng.standard_normal((prefix, KVH, D), dtype=np.float32)
+    ks, vs, qs = [], [], []
+    cow_log = []
+    for s in range(n_seq):
+        k = to_storage(np.concatenate([shared_k, rng.standard_normal((total - prefix, KVH, D), dtype=np.float32)]), dtype)
+        v = to_storage(np.concatenate([shared_v, rng.standard_normal((total - prefix, KVH, D), dtype=np.float32)]), dtype)
+        ks.append(k); vs.append(v)
+        qs.append(to_storage(rng.standard_normal((total, H, D), dtype=np.float32), dtype))
+        cache.allocateSequence(s); ora.allocate_sequence(s)
+        cache.appendTokens(s, prefix, list(range(n_hash))); ora.append_tokens(s, prefix, list(range(n_hash)))
+        if s == 0:
+            engine.appendKV(cache, 0, k[:prefix], v[:prefix], 0, prefix, H)           # the prefix is written once
+            po.reshape_and_cache(ok_pool, ov_pool, k[:prefix], v[:prefix], po.slot_mapping(ora.block_table(0), 0, prefix, bs), bs)
+        before = list(ora.block_table(s))
+        cache.appendTokens(s, total - prefix); ora.append_tokens(s, total - prefix)
+        after = list(ora.block_table(s))
+        assert cache.getBlockTable(s) == after
+        log = cache.drainCopyOnWriteLog()
+        if s == 0:
+            assert log == [] and after[:n_hash] == before
+        else:
+            # block 64 was shared and half full: it is replaced by a private copy before the append
+            assert after[:n_hash - 1] == before[:n_hash - 1] and after[n_hash - 1] != before[n_hash - 1]
+            assert log == [(before[n_hash - 1], after[n_hash - 1])]
+            po.copy_blocks([ok_pool, ov_pool], [before[n_hash - 1]], [after[n_hash - 1]])
+            cow_log += log
+        engine.appendKV(cache, s, k[prefix:], v[prefix:], prefix, total - prefix, H)
+        po.reshape_and_cache(ok_pool, ov_pool, k[prefix:], v[prefix:], po.slot_mapping(after, prefix, total - prefix, bs), bs)
+    assert len(cow_log) == n_seq - 1
+    stats = cache.memoryStats()
+    want = ora.memory_stats()
+    assert stats.sharedBlocks == want["sharedBlocks"] == n_hash - 1
+    assert stats.prefixCacheHits == want["prefixCacheHits"] == (n_seq - 1) * n_hash
+    assert cache.availableBlocks == ora.available_blocks
+    gk, gv, _, _ = cache.readPools()
+    assert np.array_equal(gk, ok_pool) and np.array_equal(gv, ov_pool)
+    # the chunk loop of the configuration: four launches, all sequences in each
+    tables, _ = cache.batchTables(list(range(n_seq)), total // bs)
+    layer = pam.PagedLayerSpec(D, H, KVH, bs, dtype)
+    for c in range(total // chunk):
+        q_cat = np.concatenate([qs[s][c * chunk:(c + 1) * chunk] for s in range(n_seq)])
+        out = np.zeros(q_cat.shape, dtype=np.uint16)
+        engine.prefillBatch(q_cat, cache.kPoolBuffer, cache.vPoolBuffer, tables, out, [(c + 1) * chunk] * n_seq,
+                            [c * chunk] * n_seq, [chunk] * n_seq, total // bs, layer)
+        assert engine.lastStats.operation == pam.Operation.prefillMMA
+        # rows checked: around the copied block in chunk 2 (tokens 1024 .. 1055), else the chunk's last 16
+        r0, nr = (0, 32) if c == 2 else (chunk - 16, 16)
+        for s in range(n_seq):
+            ref = co.prefill(qs[s][c * chunk + r0:c * chunk + r0 + nr], gk, gv, tables[s], (c + 1) * chunk, KVH, bs,
+                             int(dtype), q_start=c * chunk + r0)
+            assert_close(from_io(out[s * chunk + r0:s * chunk + r0 + nr], dtype), ref, dtype)
+    cache.close()
