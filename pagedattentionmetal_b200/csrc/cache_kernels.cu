@@ -191,6 +191,141 @@ __global__ void fp8QuantizeKernel(const __half* __restrict__ keys, const __half*
     }
 }
 
+// ---- FP8, 16-byte pieces ----------------------------------------------------
+// The same two passes with one thread per 16-byte piece (8 values) of a (token, kv_head)
+// row and 32-bit index arithmetic: every lane of a warp works, consecutive lanes read
+// consecutive pieces, and a row of head_dim / 8 = 2^k <= 32 pieces is reduced inside its
+// group of lanes.  Used when the row splits that way and the launch has fewer than 2^31
+// pieces; results are those of the row-per-warp kernels above, bit for bit.
+
+// quantize_fp8 (kernels.metal:564-601) without the division.  `inv` is the reciprocal of
+// the scale, rounded to nearest, times (1 + 2^-20).  The code of a quotient only depends
+// on comparisons with thresholds of at most five significant bits (the rounding points of
+// the 3-bit mantissa, the sub-normal steps k/512 + 1/1024, 2^-6 and 448).  Value and scale
+// are float16 numbers (11 significant bits), so value / scale either equals such a
+// threshold or is at least 2^-17 away from it in relative terms: a product that lies
+// between value / scale and value / scale * (1 + 2^-19) falls on the same side of every
+// threshold as the correctly rounded quotient, and on the threshold's upper side when
+// they are equal, which is where round-half-away puts it.
+__device__ __forceinline__ uint32_t quantizeE4m3Scaled(float value, float inv) {
+    const float q = value * inv;
+    const float a = fminf(fabsf(q), 448.0f);                                  // :566
+    // exponent and mantissa rounded to 3 bits, half up; a carry moves into the exponent (:580-592)
+    const uint32_t normal = min(((__float_as_uint(a) + 0x80000u) >> 20) - 960u, 0x7Eu);   // :585-586, :593-598
+    // round(a * 512), at most 7 (:573-578); also yields 0 for a == 0 (:571)
+    const uint32_t sub = min(static_cast<uint32_t>(__float2int_rz(fmaf(a, 512.0f, 0.5f))), 7u);
+    return (a < 0x1p-6f ? sub : normal) | (q < 0.0f ? 0x80u : 0u);            // :568 (-0.0 is not < 0)
+}
+
+__device__ __forceinline__ float absmax8(const uint4& x) {
+    // |x| of eight float16 values: clear the sign bits, then compare as float16 pairs
+    const uint32_t w[4] = {x.x & 0x7FFF7FFFu, x.y & 0x7FFF7FFFu, x.z & 0x7FFF7FFFu, x.w & 0x7FFF7FFFu};
+    __half2 m = __hmax2(__hmax2(*reinterpret_cast<const __half2*>(&w[0]), *reinterpret_cast<const __half2*>(&w[1])),
+                        __hmax2(*reinterpret_cast<const __half2*>(&w[2]), *reinterpret_cast<const __half2*>(&w[3])));
+    return fmaxf(__low2float(m), __high2float(m));
+}
+
+struct PieceIndex {
+    uint32_t t, kvh, c;
+};
+__device__ __forceinline__ PieceIndex pieceIndex(uint32_t i, int pieceShift, uint32_t kvHeads) {
+    PieceIndex p;
+    const uint32_t row = i >> pieceShift;
+    p.c = i & ((1u << pieceShift) - 1u);
+    p.t = row / kvHeads;
+    p.kvh = row - p.t * kvHeads;
+    return p;
+}
+// block and offset of a slot; block sizes are powers of two in practice
+__device__ __forceinline__ void splitSlot(int64_t slot, int blockSize, int64_t& blk, int& off) {
+    if ((blockSize & (blockSize - 1)) == 0) {
+        blk = slot >> (__ffs(blockSize) - 1);
+        off = static_cast<int>(slot & (blockSize - 1));
+    } else {
+        blk = slot / blockSize;
+        off = static_cast<int>(slot - blk * blockSize);
+    }
+}
+
+__global__ void __launch_bounds__(256)
+fp8AbsmaxPiecesKernel(const uint4* __restrict__ keys, const uint4* __restrict__ values, SlotSource src,
+                      uint32_t pieces, int pieceShift, int kvHeads, int blockSize,
+                      unsigned long long* __restrict__ amax, uint32_t epoch) {
+    const uint32_t rowLanes = 1u << pieceShift;
+    const uint32_t rounded = (pieces + 31u) & ~31u;               // whole warps stay in the loop for the shuffles
+    const uint32_t stride = gridDim.x * blockDim.x;
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < rounded; i += stride) {
+        const bool valid = i < pieces;
+        float ka = 0.f, va = 0.f;
+        if (valid) {
+            const uint4 kk = keys[i], vv = values[i];
+            ka = absmax8(kk);
+            va = absmax8(vv);
+        }
+        for (uint32_t o = rowLanes >> 1; o > 0; o >>= 1) {
+            ka = fmaxf(ka, __shfl_xor_sync(0xFFFFFFFFu, ka, o));
+            va = fmaxf(va, __shfl_xor_sync(0xFFFFFFFFu, va, o));
+        }
+        if (valid && (i & (rowLanes - 1u)) == 0u) {
+            const PieceIndex p = pieceIndex(i, pieceShift, static_cast<uint32_t>(kvHeads));
+            const int64_t slot = slotOf(src, static_cast<int>(p.t), blockSize);
+            if (slot >= 0) {
+                int64_t blk;
+                int off;
+                splitSlot(slot, blockSize, blk, off);
+                unsigned long long* w = amax + (blk * kvHeads + p.kvh) * 2;
+                const unsigned long long tag = static_cast<unsigned long long>(epoch) << 32;
+                atomicMax(w + 0, tag | __float_as_uint(ka));
+                atomicMax(w + 1, tag | __float_as_uint(va));
+            }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256)
+fp8QuantizePiecesKernel(const uint4* __restrict__ keys, const uint4* __restrict__ values,
+                        uint8_t* __restrict__ kCodes, uint8_t* __restrict__ vCodes, __half* kScale, __half* vScale,
+                        SlotSource src, uint32_t pieces, int pieceShift, int kvHeads, int blockSize,
+                        const unsigned long long* __restrict__ amax) {
+    const uint32_t stride = gridDim.x * blockDim.x;
+    const int headDim = 8 << pieceShift;
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < pieces; i += stride) {
+        const uint4 kk = keys[i], vv = values[i];
+        const PieceIndex p = pieceIndex(i, pieceShift, static_cast<uint32_t>(kvHeads));
+        const int64_t slot = slotOf(src, static_cast<int>(p.t), blockSize);
+        if (slot < 0) continue;
+        int64_t blk;
+        int off;
+        splitSlot(slot, blockSize, blk, off);
+        const int64_t group = blk * kvHeads + p.kvh;
+        // the group's scale, derived by every thread of the row (kernels.metal:1942-1960)
+        const float ka = __uint_as_float(static_cast<uint32_t>(amax[group * 2 + 0]));
+        const float va = __uint_as_float(static_cast<uint32_t>(amax[group * 2 + 1]));
+        const float km = fmaxf(ka, __half2float(*(volatile __half*)(kScale + group)) * 448.0f);
+        const float vm = fmaxf(va, __half2float(*(volatile __half*)(vScale + group)) * 448.0f);
+        const __half kh = km > 0.f ? __float2half_rn(__fdiv_rn(km, 448.0f)) : __float2half_rn(1.0f);
+        const __half vh = vm > 0.f ? __float2half_rn(__fdiv_rn(vm, 448.0f)) : __float2half_rn(1.0f);
+        if (p.c == 0) { kScale[group] = kh; vScale[group] = vh; }
+        const float kInv = __frcp_rn(__half2float(kh)) * 1.00000095367431640625f;
+        const float vInv = __frcp_rn(__half2float(vh)) * 1.00000095367431640625f;
+        const __half2* k2 = reinterpret_cast<const __half2*>(&kk);
+        const __half2* v2 = reinterpret_cast<const __half2*>(&vv);
+        uint2 ko = make_uint2(0u, 0u), vo = make_uint2(0u, 0u);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const float2 a = __half22float2(k2[j]), b = __half22float2(k2[j + 2]);
+            const float2 c = __half22float2(v2[j]), d = __half22float2(v2[j + 2]);
+            ko.x |= (quantizeE4m3Scaled(a.x, kInv) | (quantizeE4m3Scaled(a.y, kInv) << 8)) << (16 * j);
+            ko.y |= (quantizeE4m3Scaled(b.x, kInv) | (quantizeE4m3Scaled(b.y, kInv) << 8)) << (16 * j);
+            vo.x |= (quantizeE4m3Scaled(c.x, vInv) | (quantizeE4m3Scaled(c.y, vInv) << 8)) << (16 * j);
+            vo.y |= (quantizeE4m3Scaled(d.x, vInv) | (quantizeE4m3Scaled(d.y, vInv) << 8)) << (16 * j);
+        }
+        const int64_t dst = ((blk * kvHeads + p.kvh) * blockSize + off) * headDim + static_cast<int64_t>(p.c) * 8;
+        *reinterpret_cast<uint2*>(kCodes + dst) = ko;
+        *reinterpret_cast<uint2*>(vCodes + dst) = vo;
+    }
+}
+
 // ---- copy-on-write block copies -------------------------------------------
 
 // grid.x = pair, grid.y = slice of the block; 16-byte vectors, K and V.
@@ -263,6 +398,26 @@ cudaError_t launchReshapeAndCacheFp8(const void* keysF16, const void* valuesF16,
         (!aligned16(keysF16) || !aligned16(valuesF16) ||
          ((reinterpret_cast<uintptr_t>(kCodes) | reinterpret_cast<uintptr_t>(vCodes)) & 7u) != 0))
         return cudaErrorMisalignedAddress;
+    const int rowPieces = headDim / 8;
+    const int64_t pieces = rows * rowPieces;
+    if (headDim % 8 == 0 && rowPieces <= 32 && (rowPieces & (rowPieces - 1)) == 0 && pieces < (int64_t(1) << 31)) {
+        int pieceShift = 0;
+        while ((1 << pieceShift) < rowPieces) ++pieceShift;
+        int64_t grid = (pieces + threads - 1) / threads;
+        if (grid > 148 * 32) grid = 148 * 32;                      // grid-stride beyond four waves of eight CTAs per SM
+        fp8AbsmaxPiecesKernel<<<static_cast<unsigned>(grid), threads, 0, stream>>>(
+            static_cast<const uint4*>(keysF16), static_cast<const uint4*>(valuesF16), src, static_cast<uint32_t>(pieces),
+            pieceShift, kvHeads, blockSize, amaxScratch, epoch);
+        cudaError_t pe = cudaGetLastError();
+        if (pe != cudaSuccess) return pe;
+        if (launches) *launches += 1;
+        fp8QuantizePiecesKernel<<<static_cast<unsigned>(grid), threads, 0, stream>>>(
+            static_cast<const uint4*>(keysF16), static_cast<const uint4*>(valuesF16), static_cast<uint8_t*>(kCodes),
+            static_cast<uint8_t*>(vCodes), static_cast<__half*>(kScale), static_cast<__half*>(vScale), src,
+            static_cast<uint32_t>(pieces), pieceShift, kvHeads, blockSize, amaxScratch);
+        if (launches) *launches += 1;
+        return cudaGetLastError();
+    }
     fp8AbsmaxKernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(
         static_cast<const __half*>(keysF16), static_cast<const __half*>(valuesF16), src, numTokens,
         kvHeads, blockSize, headDim, amaxScratch, epoch);

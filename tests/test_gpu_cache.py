@@ -232,3 +232,51 @@ def test_config_append_fp8_cow_full_size(engine):
     assert np.array_equal(gk, kc) and np.array_equal(gv, vc)
     assert np.array_equal(gks, ks) and np.array_equal(gvs, vs)
     cache.close()
+
+
+def test_fp8_codes_of_every_float16_value(engine):
+    """quantize_fp8 (kernels.metal:564-601) over every finite float16 value, against group
+    scales from 2^-20 to 146: powers of two (where thousands of quotients sit exactly on a
+    rounding point of the 3-bit mantissa or of the sub-normal steps) and scales with full
+    mantissas.  Each (block, kv_head) group holds 2048 of the 65 536 bit patterns plus the
+    value that fixes its absmax; a second append with smaller values then reuses the stored
+    scales (max(absmax, scale * 448), kernels.metal:1945-1951).  Codes and scales bit for
+    bit against the oracle."""
+    kvh, bs, D = 8, 16, 128
+    caps = [448.0 * 2.0 ** k for k in (-20, -17, -14, -11, -8, -5, -2, 0, 1, 4, 7)]
+    caps += [65504.0, 1000.5, 3.140625, 1.0, 0.333251953125, 6.103515625e-05, 0.00123596191]
+    caps = np.asarray(caps, dtype=np.float16)
+    patterns = np.arange(65536, dtype=np.uint16).view(np.float16)
+    n_sets = len(caps)
+    n_blocks = 4 * n_sets                                            # 4 blocks x 8 kv heads = 32 groups of 2048 values
+    T = n_blocks * bs
+    rng = np.random.default_rng(26)
+
+    def build(order, shrink):
+        rows = np.zeros((T, kvh, D), np.float16)
+        for s, cap in enumerate(caps):
+            vals = patterns[order].copy()
+            limit = np.float16(float(cap) * shrink)
+            vals[~np.isfinite(vals) | (np.abs(vals.astype(np.float32)) > float(limit))] = np.float16(0)
+            groups = vals.reshape(4, kvh, bs, D)                     # [block][kv_head][slot][dim]
+            groups[:, :, 0, 0] = limit if s % 2 == 0 else -limit     # the group's absmax
+            rows[4 * s * bs:4 * (s + 1) * bs] = np.transpose(groups, (0, 2, 1, 3)).reshape(4 * bs, kvh, D)
+        return rows
+
+    k1, v1 = build(np.arange(65536), 1.0), build(rng.permutation(65536), 1.0)
+    k2, v2 = build(rng.permutation(65536), 0.5), build(rng.permutation(65536), 0.25)   # below the stored scales
+    slots = np.arange(T, dtype=np.int64)
+    cache = pam.KVCacheManager(engine, n_blocks, bs, D, kvh, DT.float8)
+    kc = np.zeros((n_blocks, kvh, bs, D), np.uint8)
+    vc = np.zeros_like(kc)
+    ks = np.zeros((n_blocks, kvh), np.uint16)
+    vs = np.zeros_like(ks)
+    for k, v in ((k1, v1), (k2, v2)):
+        engine.reshapeAndCache(cache, k, v, slots, T)
+        co.reshape_and_cache_fp8(k, v, kc, vc, ks, vs, slots, bs)
+        gk, gv, gks, gvs = cache.readPools()
+        assert np.array_equal(gks.view(np.uint16), ks) and np.array_equal(gvs.view(np.uint16), vs)
+        assert np.array_equal(gk, kc), f"{np.count_nonzero(gk != kc)} K codes differ"
+        assert np.array_equal(gv, vc), f"{np.count_nonzero(gv != vc)} V codes differ"
+    assert len(np.unique(ks)) >= n_sets - 1 and np.all(ks != 0)
+    cache.close()
