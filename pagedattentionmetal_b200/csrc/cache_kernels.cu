@@ -254,29 +254,35 @@ fp8AbsmaxPiecesKernel(const uint4* __restrict__ keys, const uint4* __restrict__ 
     const uint32_t rowLanes = 1u << pieceShift;
     const uint32_t rounded = (pieces + 31u) & ~31u;               // whole warps stay in the loop for the shuffles
     const uint32_t stride = gridDim.x * blockDim.x;
-    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < rounded; i += stride) {
-        const bool valid = i < pieces;
-        float ka = 0.f, va = 0.f;
-        if (valid) {
-            const uint4 kk = keys[i], vv = values[i];
-            ka = absmax8(kk);
-            va = absmax8(vv);
+    const unsigned long long tag = static_cast<unsigned long long>(epoch) << 32;
+    // two pieces per thread and trip, a grid apart: four 16-byte loads in flight per thread
+    for (uint32_t i0 = blockIdx.x * blockDim.x + threadIdx.x; i0 < rounded; i0 += 2u * stride) {
+        const uint32_t idx[2] = {i0, i0 + stride};
+        uint4 kk[2], vv[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            kk[u] = vv[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (idx[u] < pieces) { kk[u] = keys[idx[u]]; vv[u] = values[idx[u]]; }
         }
-        for (uint32_t o = rowLanes >> 1; o > 0; o >>= 1) {
-            ka = fmaxf(ka, __shfl_xor_sync(0xFFFFFFFFu, ka, o));
-            va = fmaxf(va, __shfl_xor_sync(0xFFFFFFFFu, va, o));
-        }
-        if (valid && (i & (rowLanes - 1u)) == 0u) {
-            const PieceIndex p = pieceIndex(i, pieceShift, static_cast<uint32_t>(kvHeads));
-            const int64_t slot = slotOf(src, static_cast<int>(p.t), blockSize);
-            if (slot >= 0) {
-                int64_t blk;
-                int off;
-                splitSlot(slot, blockSize, blk, off);
-                unsigned long long* w = amax + (blk * kvHeads + p.kvh) * 2;
-                const unsigned long long tag = static_cast<unsigned long long>(epoch) << 32;
-                atomicMax(w + 0, tag | __float_as_uint(ka));
-                atomicMax(w + 1, tag | __float_as_uint(va));
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            if (idx[u] >= rounded) continue;                       // the same for the whole warp
+            float ka = absmax8(kk[u]), va = absmax8(vv[u]);
+            for (uint32_t o = rowLanes >> 1; o > 0; o >>= 1) {
+                ka = fmaxf(ka, __shfl_xor_sync(0xFFFFFFFFu, ka, o));
+                va = fmaxf(va, __shfl_xor_sync(0xFFFFFFFFu, va, o));
+            }
+            if (idx[u] < pieces && (idx[u] & (rowLanes - 1u)) == 0u) {
+                const PieceIndex p = pieceIndex(idx[u], pieceShift, static_cast<uint32_t>(kvHeads));
+                const int64_t slot = slotOf(src, static_cast<int>(p.t), blockSize);
+                if (slot >= 0) {
+                    int64_t blk;
+                    int off;
+                    splitSlot(slot, blockSize, blk, off);
+                    unsigned long long* w = amax + (blk * kvHeads + p.kvh) * 2;
+                    atomicMax(w + 0, tag | __float_as_uint(ka));
+                    atomicMax(w + 1, tag | __float_as_uint(va));
+                }
             }
         }
     }
