@@ -173,37 +173,65 @@ cudaError_t launchGeneral(const PrefillParams& p, cudaStream_t stream, int* laun
     return cudaGetLastError();
 }
 
-// One CTA per (visible block of a sequence): codes -> float16 for all KV heads of the
-// block, K and V, 16 codes per thread and step.
+// Two codes (the low two bytes of `c2`) to two float16 values by the reference's chain
+// (dequant_fp8, kernels.metal:553-562: every product rounded to half) for normal codes:
+// (+-scale) * (1 + m/8), then * 2^(e-7), as two half2 products.  1 + m/8 and 2^(e-7) are
+// built from their float16 bit patterns.  `anySpecial` is set when one of the two codes
+// has a zero exponent field (zero or sub-normal), for which the caller takes the scalar
+// function.
+__device__ __forceinline__ uint32_t dequantPairNormal(uint32_t c2, uint32_t scale2, bool& anySpecial) {
+    const uint32_t lanes = __byte_perm(c2, 0u, 0x4140);                      // code 0 and code 1, one per 16-bit lane
+    const uint32_t e = (lanes >> 3) & 0x000F000Fu;
+    anySpecial = (e & 0x0000FFFFu) == 0u || (e >> 16) == 0u;
+    const uint32_t onePlus = 0x3C003C00u | ((lanes & 0x00070007u) << 7);     // 1 + m/8
+    const uint32_t pow2 = (e + 0x00080008u) << 10;                           // 2^(e-7): exponent field e - 7 + 15
+    const uint32_t signedScale = scale2 ^ ((lanes & 0x00800080u) << 8);
+    const __half2 t = __hmul2(*reinterpret_cast<const __half2*>(&signedScale), *reinterpret_cast<const __half2*>(&onePlus));
+    const __half2 r = __hmul2(t, *reinterpret_cast<const __half2*>(&pow2));
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+
+// One CTA per (visible block of a sequence, KV head): codes -> float16, K and V, 16 codes
+// per thread and step.
 __global__ void __launch_bounds__(256)
 fp8StagePagesKernel(const uint8_t* __restrict__ kCodes, const uint8_t* __restrict__ vCodes, const __half* __restrict__ kScale,
                     const __half* __restrict__ vScale, const int32_t* __restrict__ tables, const int32_t* __restrict__ seqLens,
                     const int32_t* __restrict__ windowStarts, __half* __restrict__ kOut, __half* __restrict__ vOut,
                     int32_t* __restrict__ stagedTables, int maxNumBlocks, int maxCount, int kvHeads, int blockSize, int headDim,
                     int poolBlocks) {
-    const int seq = blockIdx.y, c = blockIdx.x;
+    const int seq = blockIdx.y, c = blockIdx.x, kvh = blockIdx.z;
     const int lo = windowStarts[seq] / blockSize, hi = (seqLens[seq] + blockSize - 1) / blockSize;
     const int b = lo + c;
     if (b >= hi || b >= maxNumBlocks) return;
     const int src = min(max(tables[static_cast<int64_t>(seq) * maxNumBlocks + b], 0), poolBlocks - 1);
     const int dst = seq * maxCount + c;
-    if (threadIdx.x == 0) stagedTables[static_cast<int64_t>(seq) * maxNumBlocks + b] = dst;
+    if (threadIdx.x == 0 && kvh == 0) stagedTables[static_cast<int64_t>(seq) * maxNumBlocks + b] = dst;
     const int perHead = blockSize * headDim;                 // elements of one (block, kv head)
-    const int chunks = kvHeads * perHead / 16;
+    const int chunks = perHead / 16;
+    const __half ksc = kScale[src * kvHeads + kvh], vsc = vScale[src * kvHeads + kvh];
     for (int i = threadIdx.x; i < 2 * chunks; i += blockDim.x) {
         const bool isV = i >= chunks;
         const int ch = isV ? i - chunks : i;
-        const int kvh = ch * 16 / perHead;
-        const int64_t off = static_cast<int64_t>(src) * kvHeads * perHead + static_cast<int64_t>(ch) * 16;
-        const uint4 codes = *reinterpret_cast<const uint4*>((isV ? vCodes : kCodes) + off);
-        const __half scale = (isV ? vScale : kScale)[src * kvHeads + kvh];
-        const uint8_t* cb = reinterpret_cast<const uint8_t*>(&codes);
-        __align__(16) __half h[16];
+        const int64_t inHead = static_cast<int64_t>(kvh) * perHead + static_cast<int64_t>(ch) * 16;
+        const uint4 codes = *reinterpret_cast<const uint4*>((isV ? vCodes : kCodes) + static_cast<int64_t>(src) * kvHeads * perHead + inHead);
+        const __half scale = isV ? vsc : ksc;
+        const uint32_t scale2 = static_cast<uint32_t>(__half_as_ushort(scale)) * 0x00010001u;
+        const uint32_t w[4] = {codes.x, codes.y, codes.z, codes.w};
+        uint32_t h[8];
 #pragma unroll
-        for (int e = 0; e < 16; ++e) h[e] = __float2half_rn(dequantE4m3(cb[e], scale));   // exact: the value is a half
-        uint4* out = reinterpret_cast<uint4*>((isV ? vOut : kOut) + static_cast<int64_t>(dst) * kvHeads * perHead + static_cast<int64_t>(ch) * 16);
-        out[0] = *reinterpret_cast<const uint4*>(h);
-        out[1] = *reinterpret_cast<const uint4*>(h + 8);
+        for (int e = 0; e < 8; ++e) {
+            const uint32_t c2 = (w[e >> 1] >> (16 * (e & 1))) & 0xFFFFu;
+            bool special;
+            h[e] = dequantPairNormal(c2, scale2, special);
+            if (special) {
+                const __half a = __float2half_rn(dequantE4m3(static_cast<uint8_t>(c2 & 0xFFu), scale));   // exact: the value is a half
+                const __half bb = __float2half_rn(dequantE4m3(static_cast<uint8_t>(c2 >> 8), scale));
+                h[e] = static_cast<uint32_t>(__half_as_ushort(a)) | (static_cast<uint32_t>(__half_as_ushort(bb)) << 16);
+            }
+        }
+        uint4* out = reinterpret_cast<uint4*>((isV ? vOut : kOut) + static_cast<int64_t>(dst) * kvHeads * perHead + inHead);
+        out[0] = make_uint4(h[0], h[1], h[2], h[3]);
+        out[1] = make_uint4(h[4], h[5], h[6], h[7]);
     }
 }
 
@@ -219,7 +247,7 @@ bool prefillFp8StagingApplies(const PrefillParams& p) {
 cudaError_t launchFp8StagePages(const PrefillParams& p, const int32_t* seqLens, const int32_t* windowStarts, int maxCount,
                                 void* kOut, void* vOut, int32_t* stagedTables, cudaStream_t stream, int* launches) {
     if (maxCount <= 0 || p.numSeqs <= 0) return cudaSuccess;
-    dim3 grid(static_cast<unsigned>(maxCount), static_cast<unsigned>(p.numSeqs));
+    dim3 grid(static_cast<unsigned>(maxCount), static_cast<unsigned>(p.numSeqs), static_cast<unsigned>(p.kvHeads));
     fp8StagePagesKernel<<<grid, 256, 0, stream>>>(static_cast<const uint8_t*>(p.kPool), static_cast<const uint8_t*>(p.vPool),
                                                   static_cast<const __half*>(p.kScale), static_cast<const __half*>(p.vScale),
                                                   p.tables, seqLens, windowStarts, static_cast<__half*>(kOut),

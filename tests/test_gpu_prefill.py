@@ -396,3 +396,31 @@ def test_prefill_shared_prefix_with_copy_on_write(engine):
                              int(dtype), q_start=c * chunk + r0)
             assert_close(from_io(out[s * chunk + r0:s * chunk + r0 + nr], dtype), ref, dtype)
     cache.close()
+
+
+def test_fp8_staged_pages_follow_the_reference_dequant_chain(engine):
+    """The float16 pages the tensor-core prefill reads for FP8 KV must be dequant_fp8's
+    all-half chain (kernels.metal:553-562) exactly.  One token per sequence: the only weight
+    is 1, so a head's output row is the value row of its KV head after dequantisation — every
+    code against scales over sixteen binades, zero, sub-normal and 0x7F/0xFF codes included."""
+    rng = np.random.default_rng(43)
+    n_seq, H, KVH, D, bs = 512, 8, 8, 128, 16
+    shape = (n_seq, KVH, bs, D)
+    k_codes = rng.integers(0, 256, size=shape, dtype=np.uint8)
+    v_codes = rng.integers(0, 256, size=shape, dtype=np.uint8)
+    v_codes[:, :, 0, :] = (np.arange(n_seq * KVH * D, dtype=np.int64) * 37 % 256).reshape(n_seq, KVH, D).astype(np.uint8)
+    mant = 1.0 + rng.integers(0, 1024, size=(n_seq, KVH)) / 1024.0
+    v_scale = (mant * 2.0 ** rng.integers(-12, 4, size=(n_seq, KVH))).astype(np.float16)
+    k_scale = np.full((n_seq, KVH), 0.01, np.float16)
+    q = rng.standard_normal((n_seq, H, D)).astype(np.float16)
+    tables = np.arange(n_seq, dtype=np.int32).reshape(n_seq, 1)
+    out = np.zeros_like(q)
+    engine.prefillBatch(q, engine.makeBufferFrom(k_codes), engine.makeBufferFrom(v_codes), tables, out, [1] * n_seq,
+                        [0] * n_seq, [1] * n_seq, 1, pam.PagedLayerSpec(D, H, KVH, bs, DT.float8), True,
+                        engine.makeBufferFrom(k_scale), engine.makeBufferFrom(v_scale))
+    assert engine.lastStats.operation == pam.Operation.prefillMMA
+    want = po.dequant_fp8(v_codes[:, :, 0, :], v_scale[:, :, None])           # [seq][kv head = head][dim]
+    finite = np.isfinite(want)
+    assert finite.mean() > 0.99
+    assert np.array_equal(out[finite], want[finite])
+    assert len(np.unique(v_codes[:, :, 0, :])) == 256
