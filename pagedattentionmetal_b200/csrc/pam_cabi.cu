@@ -93,6 +93,8 @@ struct Context {
     bool errPending = false;
     bool forceGeneralPrefill = false;
     int exactWeights = 1;
+    void* pinned = nullptr;   // page-locked scratch for host arrays the library builds itself (batch tables)
+    size_t pinnedCap = 0;
 
     int32_t fail(int code, const std::string& msg) {            // CABI.swift:18-30
         lastError = msg;
@@ -139,6 +141,27 @@ bool isDevicePointer(const void* p) {
 // Operations that need the GPU fail like a missing device (PagedAttentionTypes.swift:36-37).
 int32_t noGpu(Context* c) {
     return c->fail(PAM_ERR_DEVICE_INIT, "Metal device or command queue could not be initialized.");
+}
+
+// Page-locked scratch of at least `bytes` (nullptr when it cannot be had: the caller then
+// copies from its pageable array).  A copy from page-locked memory runs at the link's speed
+// and does not hold the host; one block is reused by every call, so the caller must have
+// the stream drained before the next call writes it (the synchronous mode does, and the
+// cache-handle calls drain it themselves in async mode).
+void* pinnedScratch(Context* c, size_t bytes) {
+    if (bytes <= c->pinnedCap) return c->pinned;
+    cudaStreamSynchronize(c->stream);
+    if (c->pinned) cudaFreeHost(c->pinned);
+    c->pinned = nullptr;
+    c->pinnedCap = 0;
+    const size_t cap = std::max<size_t>(bytes + bytes / 2, size_t(1) << 20);
+    if (cudaHostAlloc(&c->pinned, cap, cudaHostAllocDefault) != cudaSuccess) {
+        cudaGetLastError();
+        c->pinned = nullptr;
+        return nullptr;
+    }
+    c->pinnedCap = cap;
+    return c->pinned;
 }
 
 int32_t kvFail(Context* c, const KVResult& r) {
@@ -807,6 +830,7 @@ void pam_destroy_context(void* ctx) {
     c->arena.release();
     if (c->devErr) cudaFree(c->devErr);
     if (c->hostErr) cudaFreeHost(c->hostErr);
+    if (c->pinned) cudaFreeHost(c->pinned);
     if (c->ownStream) cudaStreamDestroy(c->ownStream);
     delete c;
 }
@@ -1286,6 +1310,15 @@ int32_t pam_decode(void* ctx, void* cache, const int64_t* batch_ids, int32_t bat
     rq.k_pool = buf(k->kPool, k->poolBytes); rq.v_pool = buf(k->vPool, k->poolBytes);
     rq.block_tables = buf(tables.data(), tables.size() * sizeof(int32_t));
     rq.seq_lengths = buf(lens.data(), lens.size() * sizeof(uint32_t));
+    // tables and lengths go up from page-locked memory
+    const size_t tableBytes = tables.size() * sizeof(int32_t), lenBytes = lens.size() * sizeof(uint32_t);
+    const size_t lenOff = (tableBytes + 255) & ~static_cast<size_t>(255);
+    if (unsigned char* pin = static_cast<unsigned char*>(pinnedScratch(c, lenOff + lenBytes))) {
+        std::memcpy(pin, tables.data(), tableBytes);
+        std::memcpy(pin + lenOff, lens.data(), lenBytes);
+        rq.block_tables = buf(pin, tableBytes);
+        rq.seq_lengths = buf(pin + lenOff, lenBytes);
+    }
     rq.batch_size = batch_size; rq.max_num_blocks = maxNumBlocks;
     rq.layer = layerOf(k, num_heads);
     rq.k_scale = buf(k->kScale, k->scaleBytes); rq.v_scale = buf(k->vScale, k->scaleBytes);
