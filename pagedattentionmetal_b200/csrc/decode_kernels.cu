@@ -385,6 +385,14 @@ decodeSplitKernel(const T* __restrict__ q, const T* __restrict__ kPool, const T*
 
 // ------------------------------------------------------------ FP8 split kernel
 
+// 2^x by the special-function unit alone (exp2f adds a range fix-up for results below the
+// normal range, which a softmax weight does not need); 2^-inf = 0.
+__device__ __forceinline__ float ex2Fast(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // Two e4m3 codes (low 16 bits of `v`) to two float16 values; exact, every e4m3
 // value is a float16 value.
 __device__ __forceinline__ uint32_t e4m3x2ToHalf2(uint32_t v) {
@@ -557,28 +565,28 @@ decodeSplitFp8Kernel(const __half* __restrict__ q, const uint8_t* __restrict__ k
         tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xFFFFFFFFu, tmax0, 1));
         tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xFFFFFFFFu, tmax0, 2));
         const float mn0 = fmaxf(m0, tmax0);
-        const float c0 = exp2f(m0 - mn0);
+        const float c0 = ex2Fast(m0 - mn0);
         m0 = mn0;
         float c1 = 1.f;
         if (UPPER) {
             tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xFFFFFFFFu, tmax1, 1));
             tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xFFFFFFFFu, tmax1, 2));
             const float mn1 = fmaxf(m1, tmax1);
-            c1 = exp2f(m1 - mn1);
+            c1 = ex2Fast(m1 - mn1);
             m1 = mn1;
         }
         // weights; those that enter the product carry V's group scale relative to vRef
         const float vw = vs_ * invVRef;
         uint32_t pa[4];
         {
-            const float p00 = exp2f(s[0][0] - m0), p01 = exp2f(s[0][1] - m0);
-            const float p10 = exp2f(s[1][0] - m0), p11 = exp2f(s[1][1] - m0);
+            const float p00 = ex2Fast(s[0][0] - m0), p01 = ex2Fast(s[0][1] - m0);
+            const float p10 = ex2Fast(s[1][0] - m0), p11 = ex2Fast(s[1][1] - m0);
             l0 = l0 * c0 + (p00 + p01 + p10 + p11);
             pa[0] = pack2<__half>(p00 * vw, p01 * vw);
             pa[2] = pack2<__half>(p10 * vw, p11 * vw);
             if (UPPER) {
-                const float q00 = exp2f(s[0][2] - m1), q01 = exp2f(s[0][3] - m1);
-                const float q10 = exp2f(s[1][2] - m1), q11 = exp2f(s[1][3] - m1);
+                const float q00 = ex2Fast(s[0][2] - m1), q01 = ex2Fast(s[0][3] - m1);
+                const float q10 = ex2Fast(s[1][2] - m1), q11 = ex2Fast(s[1][3] - m1);
                 l1 = l1 * c1 + (q00 + q01 + q10 + q11);
                 pa[1] = pack2<__half>(q00 * vw, q01 * vw);
                 pa[3] = pack2<__half>(q10 * vw, q11 * vw);
