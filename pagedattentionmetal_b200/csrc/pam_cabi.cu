@@ -95,6 +95,8 @@ struct Context {
     int exactWeights = 1;
     void* pinned = nullptr;   // page-locked scratch for host arrays the library builds itself (batch tables)
     size_t pinnedCap = 0;
+    void* qStage = nullptr;   // device copy of a host query of pam_decode, sent before the tables are built
+    size_t qStageCap = 0;
 
     int32_t fail(int code, const std::string& msg) {            // CABI.swift:18-30
         lastError = msg;
@@ -831,6 +833,7 @@ void pam_destroy_context(void* ctx) {
     if (c->devErr) cudaFree(c->devErr);
     if (c->hostErr) cudaFreeHost(c->hostErr);
     if (c->pinned) cudaFreeHost(c->pinned);
+    if (c->qStage) cudaFree(c->qStage);
     if (c->ownStream) cudaStreamDestroy(c->ownStream);
     delete c;
 }
@@ -1294,41 +1297,80 @@ int32_t pam_decode(void* ctx, void* cache, const int64_t* batch_ids, int32_t bat
     if (c->device < 0) return noGpu(c);
     if (k->bookkeeping) return c->fail(PAM_ERR_INVALID_STATE, "Invalid engine state: cache has no pools");
     if (batch_size <= 0) return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("batchSize must be positive."));
+    // A host query goes up first, so that its copy runs while the tables are put together.
+    const PamLayerSpec layer = layerOf(k, num_heads);
+    const void* qDev = nullptr;
+    bool qInFlight = false;
+    if (num_heads > 0 && !isDevicePointer(q)) {
+        const size_t qBytes = static_cast<size_t>(batch_size) * qBytesPerToken(layer);
+        if (qBytes > c->qStageCap) {
+            cudaStreamSynchronize(c->stream);
+            if (c->qStage) cudaFree(c->qStage);
+            c->qStage = nullptr;
+            c->qStageCap = 0;
+            if (cudaMalloc(&c->qStage, qBytes) == cudaSuccess) c->qStageCap = qBytes;
+            else cudaGetLastError();
+        }
+        if (c->qStage && cudaMemcpyAsync(c->qStage, q, qBytes, cudaMemcpyHostToDevice, c->stream) == cudaSuccess) {
+            qDev = c->qStage;
+            qInFlight = true;
+        } else {
+            cudaGetLastError();
+        }
+    }
+    // every return below leaves no copy from the caller's memory behind
+    auto failed = [&](int32_t rc) {
+        if (qInFlight) cudaStreamSynchronize(c->stream);
+        return rc;
+    };
+    // block tables of the batch, each read once from the manager (CABI.swift:306-330, 339-372)
     int maxNumBlocks = 1;                                         // CABI.swift:308
-    std::vector<int32_t> t;
+    std::vector<int32_t> flat, t;
+    std::vector<size_t> start(static_cast<size_t>(batch_size) + 1, 0);
     for (int i = 0; i < batch_size; ++i) {
         KVResult r = k->mgr.blockTable(batch_ids[i], &t);
-        if (!r.ok()) return kvFail(c, r);
+        if (!r.ok()) return failed(kvFail(c, r));
+        flat.insert(flat.end(), t.begin(), t.end());
+        start[static_cast<size_t>(i) + 1] = flat.size();
         maxNumBlocks = std::max(maxNumBlocks, static_cast<int>(t.size()));
     }
-    std::vector<int32_t> tables;
-    std::vector<uint32_t> lens;
-    int maxLen = 0;
-    if (buildBatchTables(c, k, batch_ids, batch_size, maxNumBlocks, &tables, &lens, &maxLen) != 0) return -1;
-    PamDecodeRequest rq{};
-    rq.q = buf(q); rq.output = buf(out);
-    rq.k_pool = buf(k->kPool, k->poolBytes); rq.v_pool = buf(k->vPool, k->poolBytes);
-    rq.block_tables = buf(tables.data(), tables.size() * sizeof(int32_t));
-    rq.seq_lengths = buf(lens.data(), lens.size() * sizeof(uint32_t));
-    // tables and lengths go up from page-locked memory
-    const size_t tableBytes = tables.size() * sizeof(int32_t), lenBytes = lens.size() * sizeof(uint32_t);
+    const size_t tableBytes = static_cast<size_t>(batch_size) * maxNumBlocks * sizeof(int32_t);
+    const size_t lenBytes = static_cast<size_t>(batch_size) * sizeof(uint32_t);
     const size_t lenOff = (tableBytes + 255) & ~static_cast<size_t>(255);
-    if (unsigned char* pin = static_cast<unsigned char*>(pinnedScratch(c, lenOff + lenBytes))) {
-        std::memcpy(pin, tables.data(), tableBytes);
-        std::memcpy(pin + lenOff, lens.data(), lenBytes);
-        rq.block_tables = buf(pin, tableBytes);
-        rq.seq_lengths = buf(pin + lenOff, lenBytes);
+    // tables and lengths go up from page-locked memory (pageable vectors when that cannot be had)
+    std::vector<unsigned char> pageable;
+    unsigned char* host = static_cast<unsigned char*>(pinnedScratch(c, lenOff + lenBytes));
+    if (!host) {
+        pageable.resize(lenOff + lenBytes);
+        host = pageable.data();
     }
+    int32_t* tables = reinterpret_cast<int32_t*>(host);
+    uint32_t* lens = reinterpret_cast<uint32_t*>(host + lenOff);
+    std::memset(tables, 0, tableBytes);                           // zero padding, CABI.swift:360-363
+    int maxLen = 0;
+    for (int i = 0; i < batch_size; ++i) {
+        const size_t n = start[static_cast<size_t>(i) + 1] - start[static_cast<size_t>(i)];
+        std::memcpy(tables + static_cast<size_t>(i) * maxNumBlocks, flat.data() + start[static_cast<size_t>(i)], n * sizeof(int32_t));
+        int64_t len = 0;
+        k->mgr.sequenceLength(batch_ids[i], &len);
+        lens[i] = static_cast<uint32_t>(len);
+        maxLen = std::max(maxLen, static_cast<int>(len));
+    }
+    PamDecodeRequest rq{};
+    rq.q = qDev ? buf(qDev, static_cast<size_t>(batch_size) * qBytesPerToken(layer)) : buf(q);
+    rq.output = buf(out);
+    rq.k_pool = buf(k->kPool, k->poolBytes); rq.v_pool = buf(k->vPool, k->poolBytes);
+    rq.block_tables = buf(tables, tableBytes);
+    rq.seq_lengths = buf(lens, lenBytes);
     rq.batch_size = batch_size; rq.max_num_blocks = maxNumBlocks;
-    rq.layer = layerOf(k, num_heads);
+    rq.layer = layer;
     rq.k_scale = buf(k->kScale, k->scaleBytes); rq.v_scale = buf(k->vScale, k->scaleBytes);
     // validateDecode's pool bound uses maxNumBlocks (a lower bound, PagedAttentionEngine.swift:1931)
     int32_t rc = decodeImpl(c, rq, std::max(maxLen, 1));
-    if (rc == 0) {
-        // tables/lens are host vectors read by async copies: they must be consumed before they die
-        if (c->async) cudaStreamSynchronize(c->stream);
-        c->clearError();
-    }
+    // the tables, the lengths and a host query are read by async copies: they must be consumed
+    // before this call returns (the synchronous mode has waited already)
+    if (c->async || rc != 0) cudaStreamSynchronize(c->stream);
+    if (rc == 0) c->clearError();
     return rc;
 }
 
