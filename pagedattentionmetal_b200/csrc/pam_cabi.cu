@@ -1302,7 +1302,7 @@ int32_t pam_decode(void* ctx, void* cache, const int64_t* batch_ids, int32_t bat
     const void* qDev = nullptr;
     bool qInFlight = false;
     if (num_heads > 0 && !isDevicePointer(q)) {
-        const size_t qBytes = static_cast<size_t>(batch_size) * qBytesPerToken(layer);
+        const size_t qBytes = static_cast<size_t>(batch_size) * ioBytesPerToken(layer);
         if (qBytes > c->qStageCap) {
             cudaStreamSynchronize(c->stream);
             if (c->qStage) cudaFree(c->qStage);
@@ -1357,7 +1357,7 @@ int32_t pam_decode(void* ctx, void* cache, const int64_t* batch_ids, int32_t bat
         maxLen = std::max(maxLen, static_cast<int>(len));
     }
     PamDecodeRequest rq{};
-    rq.q = qDev ? buf(qDev, static_cast<size_t>(batch_size) * qBytesPerToken(layer)) : buf(q);
+    rq.q = qDev ? buf(qDev, static_cast<size_t>(batch_size) * ioBytesPerToken(layer)) : buf(q);
     rq.output = buf(out);
     rq.k_pool = buf(k->kPool, k->poolBytes); rq.v_pool = buf(k->vPool, k->poolBytes);
     rq.block_tables = buf(tables, tableBytes);
@@ -1596,12 +1596,14 @@ static int32_t inferKvFail(Inference* inf, const KVResult& r) {
 }
 
 // zeroed query rows and an output buffer per layer (the reference makes fresh shared
-// buffers every step, PagedAttentionInference.swift:190-202, 241-253)
+// buffers every step, PagedAttentionInference.swift:190-202, 241-253).  Sized by the type
+// the queries really have: float16 for an FP8 layer, where the reference's
+// qBytesPerToken counts one byte per element.
 static int32_t inferBuffers(Inference* inf, size_t rows) {
     Context* c = inf->c;
     DeviceGuard dg(c->device);
     for (size_t l = 0; l < inf->layers.size(); ++l) {
-        const size_t need = std::max<size_t>(rows * qBytesPerToken(inf->layers[l]), 16);
+        const size_t need = std::max<size_t>(rows * ioBytesPerToken(inf->layers[l]), 16);
         if (inf->cap[l] < need) {
             cudaStreamSynchronize(c->stream);
             cudaFree(inf->q[l]); cudaFree(inf->out[l]);
@@ -1677,7 +1679,7 @@ static int32_t inferPrefill(Inference* inf, const pam::SchedulerSequence& seq) {
     if (int32_t rc = inferBuffers(inf, static_cast<size_t>(std::max(seq.promptLength, 0)))) return rc;
     std::vector<PamPrefillRequest> rq(inf->layers.size());
     for (size_t l = 0; l < rq.size(); ++l) {
-        const size_t bytes = static_cast<size_t>(std::max(seq.promptLength, 0)) * qBytesPerToken(inf->layers[l]);
+        const size_t bytes = static_cast<size_t>(std::max(seq.promptLength, 0)) * ioBytesPerToken(inf->layers[l]);
         rq[l] = PamPrefillRequest{};
         rq[l].q = buf(inf->q[l], bytes); rq[l].output = buf(inf->out[l], bytes);
         rq[l].k_pool = buf(k->kPool, k->poolBytes); rq[l].v_pool = buf(k->vPool, k->poolBytes);
@@ -1724,7 +1726,7 @@ static int32_t inferDecode(Inference* inf, const std::vector<pam::SchedulerSeque
     if (int32_t rc = inferBuffers(inf, static_cast<size_t>(n))) return rc;
     std::vector<PamDecodeRequest> rq(inf->layers.size());
     for (size_t l = 0; l < rq.size(); ++l) {
-        const size_t bytes = static_cast<size_t>(n) * qBytesPerToken(inf->layers[l]);
+        const size_t bytes = static_cast<size_t>(n) * ioBytesPerToken(inf->layers[l]);
         rq[l] = PamDecodeRequest{};
         rq[l].q = buf(inf->q[l], bytes); rq[l].output = buf(inf->out[l], bytes);
         rq[l].k_pool = buf(k->kPool, k->poolBytes); rq[l].v_pool = buf(k->vPool, k->poolBytes);

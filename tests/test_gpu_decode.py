@@ -128,13 +128,15 @@ def test_host_buffers_are_staged(engine):
     assert_close(out, case.oracle(), DT.float16)
 
 
-def test_reference_cabi_decode_end_to_end(engine):
+@pytest.mark.parametrize("dtype", [DT.float16, DT.float8])
+def test_reference_cabi_decode_end_to_end(engine, dtype):
     """pam_reserve_sequence / pam_append_tokens / pam_append_kv / pam_decode with
-    host buffers, the call sequence of the reference's C ABI."""
+    host buffers, the call sequence of the reference's C ABI (FP8: float16 rows in,
+    codes and scales in the pools, float16 queries)."""
     rng = np.random.default_rng(19)
     H, KVH, D, bs = 8, 2, 128, 16
-    cache = pam.KVCacheManager(engine, 64, bs, D, KVH, DT.float16)
-    lens = [37, 5, 80]
+    cache = pam.KVCacheManager(engine, 64, bs, D, KVH, dtype)
+    lens = [37, 5, 80, 1, 130]
     ks, vs = {}, {}
     for sid, L in enumerate(lens):
         cache.allocateSequence(sid)
@@ -146,21 +148,23 @@ def test_reference_cabi_decode_end_to_end(engine):
         if cut:
             engine.appendKV(cache, sid, ks[sid][:cut], vs[sid][:cut], 0, cut, H)
         engine.appendKV(cache, sid, ks[sid][cut:], vs[sid][cut:], cut, L - cut, H)
-    q = rng.standard_normal((3, H, D)).astype(np.float16)
-    out = np.zeros_like(q)
-    engine.decodeBatch(cache, [2, 0, 1], q, out, H)
-    # oracle on its own pools, filled by its own scatter
-    kp = np.zeros((64, KVH, bs, D), np.float16)
-    vp = np.zeros_like(kp)
-    tabs = []
-    for sid, L in enumerate(lens):
-        t = cache.getBlockTable(sid)
-        tabs.append(t)
-        po.reshape_and_cache(kp, vp, ks[sid], vs[sid], po.slot_mapping(t, 0, L, bs), bs)
-    gk, gv, _, _ = cache.readPools()
-    assert np.array_equal(gk, kp) and np.array_equal(gv, vp)
-    tables, l = cache.batchTables([2, 0, 1], 5)
+    ids = [2, 0, 4, 3, 1]
+    gk, gv, gks, gvs = cache.readPools()
+    if dtype == DT.float16:
+        # oracle on its own pools, filled by its own scatter
+        kp = np.zeros((64, KVH, bs, D), np.float16)
+        vp = np.zeros_like(kp)
+        for sid, L in enumerate(lens):
+            po.reshape_and_cache(kp, vp, ks[sid], vs[sid], po.slot_mapping(cache.getBlockTable(sid), 0, L, bs), bs)
+        assert np.array_equal(gk, kp) and np.array_equal(gv, vp)
     from oracle import c_oracle as co
-    ref = co.decode(q, kp, vp, tables, l, KVH, bs, 1)
-    assert_close(out.astype(np.float32), ref, DT.float16)
+    for _ in range(2):                                   # the second call reuses the context's staging buffers
+        q = rng.standard_normal((len(ids), H, D)).astype(np.float16)
+        out = np.zeros_like(q)
+        engine.decodeBatch(cache, ids, q, out, H)
+        tables, l = cache.batchTables(ids, 9)
+        ref = co.decode(q, gk, gv, tables, l, KVH, bs, int(dtype),
+                        k_scale=None if gks is None else gks.view(np.uint16),
+                        v_scale=None if gvs is None else gvs.view(np.uint16))
+        assert_close(out.astype(np.float32), ref, dtype)
     cache.close()
