@@ -173,6 +173,16 @@ int32_t pamc_set_prefill_exact_weights(void *ctx, int32_t mode);
 int32_t pamc_inject_launch_failures(void *ctx, int32_t n);
 /* Number of this library's kernels launched on the context since creation. */
 int64_t pamc_kernel_launches(void *ctx);
+/* Every wait inside the tensor-core prefill kernel is bounded; a wait that runs out makes
+ * the kernel return early and the call fail with "a kernel's bounded wait ran out (site n)"
+ * (retried and degraded like any failed launch, PagedAttentionEngine.swift:375-414).
+ * sm_cycles is that bound in SM clock cycles; 0 restores the default (about 0.2 s). */
+int32_t pamc_set_wait_limit(void *ctx, int64_t sm_cycles);
+/* Test switch for that path: in each of the next `launches` tensor-core prefill launches
+ * no CTA fetches its first value tile, so the wait for it runs out after the wait limit and
+ * the kernel returns through its error exit.  Nothing spins or faults; set a short limit
+ * first.  The host-side counterpart of pamc_inject_launch_failures. */
+int32_t pamc_test_starve_prefill(void *ctx, int32_t launches);
 
 /* PagedAttentionStats (PagedAttentionTypes.swift:169-207). */
 typedef struct PamStats {
@@ -232,6 +242,22 @@ int32_t pamc_cache_num_blocks(void *ctx, void *cache, int64_t sequence_id);
 int32_t pamc_cache_active_sequences(void *cache);
 /* KVCacheManager.evictionPolicy didSet (KVCacheManager.swift:65-67, 267-283) */
 int32_t pamc_cache_set_eviction_policy(void *cache, int32_t policy);
+
+/* Two fixes of reference behaviour for servers, off by default so that block tables, free
+ * counts and hit counts stay bit-exact with the reference.  on != 0:
+ *  - a prefix-cache hash is forgotten when its block's reference count reaches zero (the
+ *    reference keeps it, KVCacheManager.swift:216-239, and a later appendTokens with that
+ *    hash is handed a block that meanwhile holds other tokens, :150-158);
+ *  - an appendTokens that runs out of blocks changes nothing (the reference has by then
+ *    copied a shared last block, :134-146, leaking the fresh block and dropping a
+ *    reference the sequence still uses). */
+int32_t pamc_cache_set_hygiene(void *cache, int32_t on);
+/* Content hashes for appendTokens' blockHashes (the reference takes caller-supplied
+ * UInt64s, KVCacheManager.swift:115): hash j covers the token ids of blocks 0..j (64-bit
+ * FNV-1a, chained), so equal hashes mean equal prefixes.  Writes up to capacity hashes of
+ * the num_tokens / block_size full blocks to out (may be NULL) and returns their number. */
+int32_t pamc_block_hashes(const int32_t *token_ids, int32_t num_tokens, int32_t block_size, uint64_t seed,
+                          uint64_t *out, int32_t capacity);
 
 /* KVCacheMemoryStats (KVCacheManager.swift:19-32). */
 typedef struct PamMemoryStats {
@@ -306,8 +332,15 @@ typedef struct PamDecodeRequest {
     PamLayerSpec layer;
     PamBuffer k_scale, v_scale;
 } PamDecodeRequest;
-/* PagedAttentionEngine.decode (PagedAttentionEngine.swift:533-580) */
+/* PagedAttentionEngine.decode (PagedAttentionEngine.swift:533-580).  When seq_lengths is
+ * host memory (the reference's buffer is host-visible) the launch is planned from the real
+ * lengths: equal ranges per sequence, longest first, no idle CTAs. */
 int32_t pamc_decode(void *ctx, const PamDecodeRequest *request);
+/* Which kernel a decode request would run on, without launching anything: 1 = the split-K
+ * kernels (float16 / bfloat16 / FP8 KV, head_dim 128 or 64, block size a multiple of 16, at
+ * most 16 query heads per KV head, pools 16-byte aligned, queries 4-byte aligned, 8-byte for
+ * FP8), 0 = the general kernel, -1 = bad request.  Only pointers, types and shapes are read. */
+int32_t pamc_decode_path(const PamDecodeRequest *request);
 
 /* Decode without any allocation.  No counterpart in the reference.
  *
@@ -331,6 +364,9 @@ int32_t pamc_decode(void *ctx, const PamDecodeRequest *request);
  *  - The first call on each GPU looks up the array's device address (once per
  *    device, with that device current).  Make that first call before starting
  *    any stream capture.
+ *  - While the context's stream is being captured the call only records its
+ *    launches: it does not wait for the stream and does not run the retry loop
+ *    (an eager call does both unless pamc_set_async is on).
  *  - All calls on one GPU share the array and it keeps whatever the previous
  *    call left there.  Nothing in it has to start at zero: every word a call
  *    reads was written earlier by that same call.  Two such decodes that
@@ -396,6 +432,29 @@ int32_t pamc_decode_layers(void *ctx, const PamDecodeRequest *requests, int32_t 
 int32_t pamc_prefill_layers(void *ctx, const PamPrefillRequest *requests, int32_t num_layers);
 int32_t pamc_append_layers(void *ctx, const PamAppendRequest *requests, int32_t num_layers,
                            void *const *caches);
+
+/* ------------------------------------------------------------------------
+ * Outputs of a cache sharded by KV head over several GPUs
+ * ---------------------------------------------------------------------- */
+
+/* No counterpart in the reference (one device: PagedAttentionEngine.swift:249,
+ * PagedAttentionCABI.swift:104).  With N GPUs, GPU r owns KV heads [r*KVH/N, (r+1)*KVH/N)
+ * and the query heads that map to them; attention needs no exchange.  A caller that wants
+ * the whole [rows][heads][head_dim] output on every GPU gathers it with these calls
+ * (ncclAllGather over NVLink, then one kernel that interleaves the head slices).  NCCL is
+ * loaded at run time; without it pamc_comm_unique_id and pamc_comm_create fail.
+ *
+ * One process per GPU: rank 0 makes the id, the caller carries its 128 bytes to the other
+ * ranks by any means, every rank creates its communicator (a collective call). */
+int32_t pamc_comm_unique_id(void *out_128_bytes);
+void *pamc_comm_create(void *ctx, const void *unique_id_128_bytes, int32_t rank, int32_t num_ranks);
+void pamc_comm_destroy(void *comm);
+/* local: this GPU's [rows][heads_local][head_dim]; full: [rows][heads_local * num_ranks][head_dim],
+ * both device memory of the context's GPU, elements of the query type of data_type
+ * (PAM_DTYPE_*).  heads_local * head_dim * element size must be a multiple of 16 bytes.
+ * Collective: every rank calls it with the same shape, on its context's stream. */
+int32_t pamc_allgather_heads(void *ctx, void *comm, const void *local, void *full, int32_t rows,
+                             int32_t heads_local, int32_t head_dim, int32_t data_type);
 
 /* ------------------------------------------------------------------------
  * Scheduler (Scheduler.swift)
@@ -466,6 +525,17 @@ void pamc_infer_set_token_callback(void *infer, pamc_token_fn fn, void *user);
  * victims are chosen (:280-299, Scheduler.swift:134-152).  on != 0: pause and
  * free one victim at a time until enough blocks are free.  Default off. */
 void pamc_infer_set_incremental_preemption(void *infer, int32_t on);
+/* The reference prefills one sequence per dispatch (:172-219).  on != 0: the prompts of a
+ * step go through the same block bookkeeping in the same order, but their attention rows
+ * are issued together, one launch per layer.  token_budget > 0 also bounds the prompt rows
+ * of a step: a longer prompt is prefilled in chunks over several steps and prompts that do
+ * not fit wait for the next step (they decode only once their whole prompt is done).
+ * Default off; with on != 0 and token_budget 0 every step leaves the same state as the
+ * reference's. */
+void pamc_infer_set_batched_prefill(void *infer, int32_t on, int32_t token_budget);
+/* Prefill launch sets issued so far (one per sequence in the reference's mode, one per
+ * step with batched prefill). */
+int64_t pamc_infer_prefill_launch_sets(void *infer);
 
 #ifdef __cplusplus
 }

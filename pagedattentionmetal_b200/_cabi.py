@@ -179,6 +179,18 @@ SIGNATURES = {
     "pamc_infer_set_token_callback": (None, [c_void_p, TOKEN_FN, c_void_p]),
     "pamc_infer_set_incremental_preemption": (None, [c_void_p, c_int32]),
     "pamc_sched_get": (c_int32, [c_void_p, c_int64, C.POINTER(PamSchedSequence)]),
+    "pamc_infer_set_batched_prefill": (None, [c_void_p, c_int32, c_int32]),
+    "pamc_infer_prefill_launch_sets": (c_int64, [c_void_p]),
+    # additions without a reference counterpart
+    "pamc_set_wait_limit": (c_int32, [c_void_p, c_int64]),
+    "pamc_test_starve_prefill": (c_int32, [c_void_p, c_int32]),
+    "pamc_cache_set_hygiene": (c_int32, [c_void_p, c_int32]),
+    "pamc_block_hashes": (c_int32, [C.POINTER(c_int32), c_int32, c_int32, C.c_uint64, C.POINTER(C.c_uint64), c_int32]),
+    "pamc_decode_path": (c_int32, [C.POINTER(PamDecodeRequest)]),
+    "pamc_comm_unique_id": (c_int32, [c_void_p]),
+    "pamc_comm_create": (c_void_p, [c_void_p, c_void_p, c_int32, c_int32]),
+    "pamc_comm_destroy": (None, [c_void_p]),
+    "pamc_allgather_heads": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32]),
 }
 
 for _name, (_res, _args) in SIGNATURES.items():

@@ -20,7 +20,7 @@ LIB = os.path.join(HERE, "libpam_cuda.so")
 INCLUDE = os.path.join(HERE, "..", "include")
 
 SOURCES = ["cache_kernels.cu", "decode_kernels.cu", "prefill_kernels.cu", "prefill_tc_kernel.cu", "pam_cabi.cu",
-           "block_manager.cpp"]
+           "comm.cu", "block_manager.cpp"]
 HEADERS = ["kernels.h", "block_manager.h", os.path.join(INCLUDE, "pam_cuda.h")]
 
 NVCC_FLAGS = [

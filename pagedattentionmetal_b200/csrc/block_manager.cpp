@@ -17,7 +17,9 @@ BlockManager::BlockManager(int maxBlocks, int blockSize)
 KVResult BlockManager::allocateSequence(int64_t id) {          // KVCacheManager.swift:106-113
     std::lock_guard<std::mutex> g(mu_);
     if (sequences_.count(id)) return {KVStatus::sequenceAlreadyExists, "sequenceAlreadyExists"};
-    sequences_[id] = LogicalSequence{};
+    LogicalSequence fresh;
+    fresh.rewriteVersion = ++versionCounter_;
+    sequences_[id] = std::move(fresh);
     return {};
 }
 
@@ -51,6 +53,7 @@ KVResult BlockManager::copyOnWriteLocked(int32_t block, size_t index, LogicalSeq
     refcounts_[static_cast<size_t>(block)] -= 1;
     refcounts_[static_cast<size_t>(fresh)] = 1;
     seq.blockTable[index] = fresh;
+    seq.rewriteVersion = ++versionCounter_;
     return {};
 }
 
@@ -69,6 +72,13 @@ KVResult BlockManager::appendTokens(int64_t id, int64_t count, const uint64_t* h
     const int64_t now = (cur + bs - 1) / bs, after = (newLen + bs - 1) / bs;
     const int64_t additional = after - now;
 
+    if (hygiene_) {
+        // nothing is changed by an append that cannot be completed
+        const bool needsCopy = now > 0 && cur % bs != 0 &&
+                               refcounts_[static_cast<size_t>(seq.blockTable[static_cast<size_t>(now - 1)])] > 1;
+        if (static_cast<int64_t>(free_.size()) < additional + (needsCopy ? 1 : 0))
+            return {KVStatus::outOfMemory, "outOfMemory"};
+    }
     if (now > 0 && cur % bs != 0) {                            // :134-140
         int32_t last = seq.blockTable[static_cast<size_t>(now - 1)];
         if (refcounts_[static_cast<size_t>(last)] > 1) {
@@ -93,7 +103,10 @@ KVResult BlockManager::appendTokens(int64_t id, int64_t count, const uint64_t* h
             int32_t b = allocateBlockLocked();                 // :161-168
             seq.blockTable.push_back(b);
             refcounts_[static_cast<size_t>(b)] = 1;
-            if (hashed) prefix_[hashes[i]] = b;
+            if (hashed) {
+                prefix_[hashes[i]] = b;
+                if (hygiene_) hashesOfBlock_[b].push_back(hashes[i]);
+            }
         }
     }
     seq.sequenceLength = newLen;
@@ -122,6 +135,20 @@ KVResult BlockManager::ensureExclusiveAccess(int64_t id, int64_t logicalBlock,
 void BlockManager::registerBlockHash(uint64_t hash, int32_t block) {   // KVCacheManager.swift:196-198
     std::lock_guard<std::mutex> g(mu_);   // the reference takes no lock here; taking one changes no result
     prefix_[hash] = block;
+    if (hygiene_) hashesOfBlock_[block].push_back(hash);
+}
+
+void BlockManager::setHygiene(bool on) {
+    std::lock_guard<std::mutex> g(mu_);
+    hygiene_ = on;
+    hashesOfBlock_.clear();
+    // entries registered before the switch are tracked from now on
+    if (on) for (auto& kv : prefix_) hashesOfBlock_[kv.second].push_back(kv.first);
+}
+
+bool BlockManager::hygiene() const {
+    std::lock_guard<std::mutex> g(mu_);
+    return hygiene_;
 }
 
 void BlockManager::freeSequence(int64_t id) {                  // KVCacheManager.swift:216-239
@@ -138,6 +165,17 @@ void BlockManager::freeSequence(int64_t id) {                  // KVCacheManager
         int32_t& rc = refcounts_[static_cast<size_t>(b)];
         rc -= 1;
         if (rc <= 0) {
+            if (hygiene_) {
+                // the block goes back to the free list: nobody may reach it through a hash any more
+                auto h = hashesOfBlock_.find(b);
+                if (h != hashesOfBlock_.end()) {
+                    for (uint64_t hash : h->second) {
+                        auto e = prefix_.find(hash);
+                        if (e != prefix_.end() && e->second == b) prefix_.erase(e);
+                    }
+                    hashesOfBlock_.erase(h);
+                }
+            }
             switch (policy_) {
                 case fifo: free_.push_front(b); break;
                 case lifo: free_.push_back(b); break;

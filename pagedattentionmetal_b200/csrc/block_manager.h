@@ -28,6 +28,19 @@ struct KVResult {
 struct LogicalSequence {            // KVCacheManager.swift:34-44
     std::vector<int32_t> blockTable;
     int64_t sequenceLength = 0;
+    // Not in the reference: changes whenever an entry that already exists is replaced
+    // (copy-on-write) and when the id is allocated again after a free; growing the table
+    // leaves it alone.  A holder of a copy of the first n entries needs no more than the
+    // entries from n on while this number stays the same.
+    uint64_t rewriteVersion = 0;
+};
+
+// One sequence as seen under the manager's lock (BlockManager::visit).
+struct SequenceView {
+    const int32_t* table;
+    int32_t numBlocks;
+    int64_t length;
+    uint64_t rewriteVersion;
 };
 
 struct MemoryStats {                // KVCacheManager.swift:19-32 (byte fields filled by the owner)
@@ -54,6 +67,19 @@ public:
     void registerBlockHash(uint64_t hash, int32_t block);
     void freeSequence(int64_t id);
     void setPolicy(int policy);
+    // Two fixes of reference behaviour, both off by default so that block tables, free
+    // counts and hit counts stay bit-exact with the reference:
+    //  * a prefix-cache entry is dropped when its block's reference count reaches zero
+    //    (the reference keeps the hash and later hands the recycled block to whoever
+    //    presents it, KVCacheManager.swift:150-158, 216-239);
+    //  * an append that runs out of blocks changes nothing (the reference has already
+    //    done the copy-on-write of a shared last block by then, KVCacheManager.swift:134-146,
+    //    which leaks the fresh block and drops a reference the sequence still uses).
+    void setHygiene(bool on);
+    bool hygiene() const;
+    // fn(i, view) for ids[0 .. n) in order under one lock; stops at the first unknown id
+    // and reports it.
+    template <class F> KVResult visit(const int64_t* ids, int n, F fn) const;
 
     KVResult blockTable(int64_t id, std::vector<int32_t>* out) const;
     KVResult sequenceLength(int64_t id, int64_t* out) const;
@@ -77,7 +103,22 @@ private:
     std::unordered_map<uint64_t, int32_t> prefix_;
     std::vector<int32_t> refcounts_;
     int64_t prefixHits_ = 0;
+    uint64_t versionCounter_ = 0;
+    bool hygiene_ = false;
+    std::unordered_map<int32_t, std::vector<uint64_t>> hashesOfBlock_;   // hygiene only
 };
+
+template <class F>
+KVResult BlockManager::visit(const int64_t* ids, int n, F fn) const {
+    std::lock_guard<std::mutex> g(mu_);
+    for (int i = 0; i < n; ++i) {
+        auto it = sequences_.find(ids[i]);
+        if (it == sequences_.end()) return {KVStatus::sequenceNotFound, "sequenceNotFound"};
+        const LogicalSequence& q = it->second;
+        fn(i, SequenceView{q.blockTable.data(), static_cast<int32_t>(q.blockTable.size()), q.sequenceLength, q.rewriteVersion});
+    }
+    return {};
+}
 
 enum SeqStatus { waiting = 0, running = 1, paused = 2, completed = 3 };   // Scheduler.swift:5-10
 

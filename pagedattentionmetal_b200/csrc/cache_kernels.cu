@@ -456,4 +456,19 @@ cudaError_t launchCopyBlocks(void* kPool, void* vPool, void* kScale, void* vScal
     return cudaGetLastError();
 }
 
+// Block-table entries that changed since the device copy was made.
+__global__ void patchTablesKernel(int32_t* __restrict__ tables, int stride, const int32_t* __restrict__ patches, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int row = patches[3 * i], col = patches[3 * i + 1];
+    tables[static_cast<int64_t>(row) * stride + col] = patches[3 * i + 2];
+}
+
+cudaError_t launchPatchTables(int32_t* tables, int stride, const int32_t* patches, int n, cudaStream_t stream, int* launches) {
+    if (n <= 0) return cudaSuccess;
+    patchTablesKernel<<<(n + 255) / 256, 256, 0, stream>>>(tables, stride, patches, n);
+    if (launches) *launches += 1;
+    return cudaGetLastError();
+}
+
 }  // namespace pam

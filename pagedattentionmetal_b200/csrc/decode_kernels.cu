@@ -28,7 +28,11 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <atomic>
 #include <cmath>
+#include <cstdlib>
+#include <cstring>
+#include <vector>
 
 #include "kernels.h"
 
@@ -129,6 +133,120 @@ __device__ __forceinline__ SplitInfo splitInfo(uint32_t len, int window, int max
     return s;
 }
 
+// The tiles of a sequence are divided evenly over its splits (sizes differ by at most one
+// tile, none is empty): split k of n covers tiles [begin, end) counted from the first
+// visible tile.
+__host__ __device__ __forceinline__ int splitCount(int numTiles, int chunkTiles) {
+    const int n = (numTiles + chunkTiles - 1) / chunkTiles;
+    return n < 1 ? 1 : n;
+}
+__host__ __device__ __forceinline__ void splitRange(int numTiles, int numSplits, int split, int& begin, int& end) {
+    const int base = numTiles / numSplits, rem = numTiles - base * numSplits;
+    begin = split * base + (split < rem ? split : rem);
+    end = begin + base + (split < rem ? 1 : 0);
+}
+
+// The running maximum of a row is only raised when a tile exceeds it by more than this
+// (log2 domain): the result is the same either way because the final division uses the
+// same reference, and the accumulator is then rescaled a few times per split instead of
+// once per tile.  Weights reach at most 2^kLazyMax, well inside float16 and bfloat16.
+constexpr float kLazyMax = 6.0f;
+
+// What a CTA of the split kernels works on.  Two launch shapes:
+//  * grid (maxSplits, kv_heads, batch): the range follows from the sequence's length;
+//  * grid (items, kv_heads) with a work list built on the host from the lengths (longest
+//    ranges first, so that the short ones fill the end of the launch): item = (sequence,
+//    first tile, end tile, split | splits << 16).
+struct SplitWork {
+    int b, kvh, split, numSplits, tileBegin, tileEnd;
+    SplitInfo si;
+    uint32_t len;
+};
+__device__ __forceinline__ SplitWork splitWork(const int4* __restrict__ items, const uint32_t* __restrict__ lens,
+                                               int window, int maxTokens, int chunkTiles) {
+    SplitWork w;
+    if (items) {
+        const int4 it = items[blockIdx.x];
+        w.b = it.x; w.kvh = blockIdx.y;
+        w.len = lens[w.b];
+        w.si = splitInfo(w.len, window, maxTokens);
+        w.split = it.w & 0xFFFF; w.numSplits = it.w >> 16;
+        w.tileBegin = it.y; w.tileEnd = it.z;
+    } else {
+        w.b = blockIdx.z; w.kvh = blockIdx.y; w.split = blockIdx.x;
+        w.len = lens[w.b];
+        w.si = splitInfo(w.len, window, maxTokens);
+        w.numSplits = splitCount(w.si.numTiles, chunkTiles);
+        int begin = 0, end = 0;
+        if (w.si.numTiles > 0 && w.split < w.numSplits) splitRange(w.si.numTiles, w.numSplits, w.split, begin, end);
+        w.tileBegin = w.si.firstTile + begin;
+        w.tileEnd = w.si.firstTile + end;
+    }
+    return w;
+}
+
+// End of a split: the warps' partial results (m, l, O per query head, in `red`,
+// [NW][G][HD + 2]) are combined; a sequence with one split gets its output, else the
+// partial goes to the workspace.  With `counters` (one zeroed word per (sequence, kv head))
+// the CTA that finishes a (sequence, kv head) last combines its splits right away and puts
+// the word back to zero; without, decodeMergeKernel does that in a launch of its own.
+template <typename T, int HD, int NW>
+__device__ __forceinline__ void finishSplit(const float* red, int G, const SplitWork& w, int heads, int kvHeads,
+                                            int maxSplits, T* __restrict__ out, float* __restrict__ workspace,
+                                            int* __restrict__ counters) {
+    constexpr int RS = HD + 2;
+    __shared__ int sIsLast;
+    for (int idx = threadIdx.x; idx < G * HD; idx += NW * 32) {
+        const int g = idx / HD, d = idx - g * HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int x = 0; x < NW; ++x) M = fmaxf(M, red[(x * G + g) * RS + HD]);
+        float acc = 0.f, lsum = 0.f;
+#pragma unroll
+        for (int x = 0; x < NW; ++x) {
+            const float wgt = exp2f(red[(x * G + g) * RS + HD] - M);   // idle warps: exp2(-inf) = 0
+            acc += wgt * red[(x * G + g) * RS + d];
+            lsum += wgt * red[(x * G + g) * RS + HD + 1];
+        }
+        const int head = w.kvh * G + g;
+        if (w.numSplits == 1) {
+            out[(static_cast<int64_t>(w.b) * heads + head) * HD + d] = fromFloat<T>(acc / lsum);
+        } else {
+            float* part = workspace + ((static_cast<int64_t>(w.b) * heads + head) * maxSplits + w.split) * RS;
+            part[d] = acc;
+            if (d == 0) { part[HD] = M; part[HD + 1] = lsum; }
+        }
+    }
+    if (w.numSplits == 1 || !counters) return;
+    // The partial is published before the arrival is counted; the last arrival reads the
+    // others' partials from L2.
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int* cnt = counters + static_cast<int64_t>(w.b) * kvHeads + w.kvh;
+        const int before = atomicAdd(cnt, 1);
+        sIsLast = before == w.numSplits - 1 ? 1 : 0;
+        if (sIsLast) *cnt = 0;                      // ready for the next launch
+    }
+    __syncthreads();
+    if (!sIsLast) return;
+    __threadfence();
+    for (int idx = threadIdx.x; idx < G * HD; idx += NW * 32) {
+        const int g = idx / HD, d = idx - g * HD;
+        const int head = w.kvh * G + g;
+        const float* part = workspace + (static_cast<int64_t>(w.b) * heads + head) * maxSplits * RS;
+        float M = -INFINITY;
+        for (int sp = 0; sp < w.numSplits; ++sp) M = fmaxf(M, __ldcg(part + sp * RS + HD));
+        float acc = 0.f, lsum = 0.f;
+        for (int sp = 0; sp < w.numSplits; ++sp) {
+            const float wgt = exp2f(__ldcg(part + sp * RS + HD) - M);
+            acc += wgt * __ldcg(part + sp * RS + d);
+            lsum += wgt * __ldcg(part + sp * RS + HD + 1);
+        }
+        out[(static_cast<int64_t>(w.b) * heads + head) * HD + d] = fromFloat<T>(acc / lsum);
+    }
+}
+
 // ------------------------------------------------------------ fast split kernel
 
 template <typename T, int HD, int NW, int NS, bool UPPER>
@@ -137,7 +255,7 @@ decodeSplitKernel(const T* __restrict__ q, const T* __restrict__ kPool, const T*
                   const int32_t* __restrict__ tables, const uint32_t* __restrict__ lens,
                   T* __restrict__ out, float* __restrict__ workspace, int heads, int kvHeads,
                   int blockSize, int maxNumBlocks, int window, int chunkTiles, int maxSplits,
-                  float scaleLog2, int poolBlocks) {
+                  float scaleLog2, int poolBlocks, const int4* __restrict__ items, int* __restrict__ counters) {
     constexpr int ROWB = HD * 2;                 // bytes per token row
     constexpr int CPR = ROWB / 16;               // 16-byte chunks per row
     constexpr int TILEB = kTileTokens * ROWB;    // bytes per K (or V) tile
@@ -147,25 +265,24 @@ decodeSplitKernel(const T* __restrict__ q, const T* __restrict__ kPool, const T*
 
     extern __shared__ __align__(128) unsigned char smem[];
 
-    const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const SplitWork work = splitWork(items, lens, window, maxNumBlocks * blockSize, chunkTiles);
+    const int kvh = work.kvh, b = work.b;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = heads / kvHeads;
     const int r = lane >> 2, j = lane & 3;
 
-    const uint32_t len = lens[b];
-    const SplitInfo si = splitInfo(len, window, maxNumBlocks * blockSize);
-    const int numSplits = (si.numTiles + chunkTiles - 1) / chunkTiles;
+    const uint32_t len = work.len;
+    const SplitInfo si = work.si;
     if (si.numTiles <= 0) {
         // Empty context (the reference divides 0 by 0 here): write zeros.
-        if (split == 0)
+        if (work.split == 0)
             for (int i = threadIdx.x; i < G * HD; i += NW * 32)
                 out[(static_cast<int64_t>(b) * heads + kvh * G) * HD + i] = fromFloat<T>(0.f);
         return;
     }
-    if (split >= numSplits) return;
+    if (work.split >= work.numSplits) return;
 
-    const int tileBegin = si.firstTile + split * chunkTiles;
-    const int tileEnd = min(tileBegin + chunkTiles, si.firstTile + si.numTiles);
+    const int tileBegin = work.tileBegin, tileEnd = work.tileEnd;
     // warp w takes tiles tileBegin + w, + NW, ...
     const int myTiles = (tileEnd - tileBegin - warp + NW - 1) / NW;
     const int tilesPerPage = blockSize / kTileTokens;
@@ -272,42 +389,43 @@ decodeSplitKernel(const T* __restrict__ q, const T* __restrict__ kPool, const T*
         }
         tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xFFFFFFFFu, tmax0, 1));
         tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xFFFFFFFFu, tmax0, 2));
-        const float mn0 = fmaxf(m0, tmax0);
-        const float c0 = exp2f(m0 - mn0);          // m0 = -inf gives 0
-        m0 = mn0;
-        float c1 = 1.f;
+        bool raise = tmax0 > m0 + kLazyMax;        // m0 = -inf: the first tile always raises
+        float c0 = 1.f, c1 = 1.f;
+        if (raise) { c0 = exp2f(m0 - tmax0); m0 = tmax0; }   // m0 = -inf gives 0
         if (UPPER) {
             tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xFFFFFFFFu, tmax1, 1));
             tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xFFFFFFFFu, tmax1, 2));
-            const float mn1 = fmaxf(m1, tmax1);
-            c1 = exp2f(m1 - mn1);
-            m1 = mn1;
+            if (tmax1 > m1 + kLazyMax) { c1 = exp2f(m1 - tmax1); m1 = tmax1; raise = true; }
+        }
+        if (__any_sync(0xFFFFFFFFu, raise)) {
+            l0 *= c0;
+            if (UPPER) l1 *= c1;
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                o[n][0] *= c0;
+                o[n][1] *= c0;
+                if (UPPER) {
+                    o[n][2] *= c1;
+                    o[n][3] *= c1;
+                }
+            }
         }
         uint32_t pa[4];
         {
             const float p00 = exp2f(s[0][0] - m0), p01 = exp2f(s[0][1] - m0);
             const float p10 = exp2f(s[1][0] - m0), p11 = exp2f(s[1][1] - m0);
-            l0 = l0 * c0 + (p00 + p01 + p10 + p11);
+            l0 += (p00 + p01) + (p10 + p11);
             pa[0] = pack2<T>(p00, p01);
             pa[2] = pack2<T>(p10, p11);
             if (UPPER) {
                 const float q00 = exp2f(s[0][2] - m1), q01 = exp2f(s[0][3] - m1);
                 const float q10 = exp2f(s[1][2] - m1), q11 = exp2f(s[1][3] - m1);
-                l1 = l1 * c1 + (q00 + q01 + q10 + q11);
+                l1 += (q00 + q01) + (q10 + q11);
                 pa[1] = pack2<T>(q00, q01);
                 pa[3] = pack2<T>(q10, q11);
             } else {
                 pa[1] = 0u;
                 pa[3] = 0u;
-            }
-        }
-#pragma unroll
-        for (int n = 0; n < NT; ++n) {
-            o[n][0] *= c0;
-            o[n][1] *= c0;
-            if (UPPER) {
-                o[n][2] *= c1;
-                o[n][3] *= c1;
             }
         }
 
@@ -360,27 +478,7 @@ decodeSplitKernel(const T* __restrict__ q, const T* __restrict__ kPool, const T*
         }
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < G * HD; idx += NW * 32) {
-        const int g = idx / HD, d = idx - g * HD;
-        float M = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < NW; ++w) M = fmaxf(M, red[(w * G + g) * RS + HD]);
-        float acc = 0.f, lsum = 0.f;
-#pragma unroll
-        for (int w = 0; w < NW; ++w) {
-            const float wgt = exp2f(red[(w * G + g) * RS + HD] - M);   // idle warps: exp2(-inf) = 0
-            acc += wgt * red[(w * G + g) * RS + d];
-            lsum += wgt * red[(w * G + g) * RS + HD + 1];
-        }
-        const int head = kvh * G + g;
-        if (numSplits == 1) {
-            out[(static_cast<int64_t>(b) * heads + head) * HD + d] = fromFloat<T>(acc / lsum);
-        } else {
-            float* part = workspace + ((static_cast<int64_t>(b) * heads + head) * maxSplits + split) * RS;
-            part[d] = acc;
-            if (d == 0) { part[HD] = M; part[HD + 1] = lsum; }
-        }
-    }
+    finishSplit<T, HD, NW>(red, G, work, heads, kvHeads, maxSplits, out, workspace, counters);
 }
 
 // ------------------------------------------------------------ FP8 split kernel
@@ -423,7 +521,7 @@ decodeSplitFp8Kernel(const __half* __restrict__ q, const uint8_t* __restrict__ k
                      const int32_t* __restrict__ tables, const uint32_t* __restrict__ lens,
                      __half* __restrict__ out, float* __restrict__ workspace, int heads, int kvHeads,
                      int blockSize, int maxNumBlocks, int window, int chunkTiles, int maxSplits,
-                     float scaleLog2, int poolBlocks) {
+                     float scaleLog2, int poolBlocks, const int4* __restrict__ items, int* __restrict__ counters) {
     constexpr int HD = 128;
     constexpr int ROWB = HD;                     // bytes per token row
     constexpr int TILEB = kTileTokens * ROWB;    // 2 KB per K (or V) tile
@@ -434,24 +532,23 @@ decodeSplitFp8Kernel(const __half* __restrict__ q, const uint8_t* __restrict__ k
 
     extern __shared__ __align__(128) unsigned char smem[];
 
-    const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const SplitWork work = splitWork(items, lens, window, maxNumBlocks * blockSize, chunkTiles);
+    const int kvh = work.kvh, b = work.b;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = heads / kvHeads;
     const int r = lane >> 2, j = lane & 3;
 
-    const uint32_t len = lens[b];
-    const SplitInfo si = splitInfo(len, window, maxNumBlocks * blockSize);
-    const int numSplits = (si.numTiles + chunkTiles - 1) / chunkTiles;
+    const uint32_t len = work.len;
+    const SplitInfo si = work.si;
     if (si.numTiles <= 0) {
-        if (split == 0)
+        if (work.split == 0)
             for (int i = threadIdx.x; i < G * HD; i += NW * 32)
                 out[(static_cast<int64_t>(b) * heads + kvh * G) * HD + i] = __float2half_rn(0.f);
         return;
     }
-    if (split >= numSplits) return;
+    if (work.split >= work.numSplits) return;
 
-    const int tileBegin = si.firstTile + split * chunkTiles;
-    const int tileEnd = min(tileBegin + chunkTiles, si.firstTile + si.numTiles);
+    const int tileBegin = work.tileBegin, tileEnd = work.tileEnd;
     const int myTiles = (tileEnd - tileBegin - warp + NW - 1) / NW;
     const int tilesPerPage = blockSize / kTileTokens;
     const int32_t* table = tables + static_cast<int64_t>(b) * maxNumBlocks;
@@ -564,16 +661,26 @@ decodeSplitFp8Kernel(const __half* __restrict__ q, const uint8_t* __restrict__ k
         }
         tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xFFFFFFFFu, tmax0, 1));
         tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xFFFFFFFFu, tmax0, 2));
-        const float mn0 = fmaxf(m0, tmax0);
-        const float c0 = ex2Fast(m0 - mn0);
-        m0 = mn0;
-        float c1 = 1.f;
+        bool raise = tmax0 > m0 + kLazyMax;        // m0 = -inf: the first tile always raises
+        float c0 = 1.f, c1 = 1.f;
+        if (raise) { c0 = ex2Fast(m0 - tmax0); m0 = tmax0; }
         if (UPPER) {
             tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xFFFFFFFFu, tmax1, 1));
             tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xFFFFFFFFu, tmax1, 2));
-            const float mn1 = fmaxf(m1, tmax1);
-            c1 = ex2Fast(m1 - mn1);
-            m1 = mn1;
+            if (tmax1 > m1 + kLazyMax) { c1 = ex2Fast(m1 - tmax1); m1 = tmax1; raise = true; }
+        }
+        if (__any_sync(0xFFFFFFFFu, raise)) {
+            l0 *= c0;
+            if (UPPER) l1 *= c1;
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                o[n][0] *= c0;
+                o[n][1] *= c0;
+                if (UPPER) {
+                    o[n][2] *= c1;
+                    o[n][3] *= c1;
+                }
+            }
         }
         // weights; those that enter the product carry V's group scale relative to vRef
         const float vw = vs_ * invVRef;
@@ -581,27 +688,18 @@ decodeSplitFp8Kernel(const __half* __restrict__ q, const uint8_t* __restrict__ k
         {
             const float p00 = ex2Fast(s[0][0] - m0), p01 = ex2Fast(s[0][1] - m0);
             const float p10 = ex2Fast(s[1][0] - m0), p11 = ex2Fast(s[1][1] - m0);
-            l0 = l0 * c0 + (p00 + p01 + p10 + p11);
+            l0 += (p00 + p01) + (p10 + p11);
             pa[0] = pack2<__half>(p00 * vw, p01 * vw);
             pa[2] = pack2<__half>(p10 * vw, p11 * vw);
             if (UPPER) {
                 const float q00 = ex2Fast(s[0][2] - m1), q01 = ex2Fast(s[0][3] - m1);
                 const float q10 = ex2Fast(s[1][2] - m1), q11 = ex2Fast(s[1][3] - m1);
-                l1 = l1 * c1 + (q00 + q01 + q10 + q11);
+                l1 += (q00 + q01) + (q10 + q11);
                 pa[1] = pack2<__half>(q00 * vw, q01 * vw);
                 pa[3] = pack2<__half>(q10 * vw, q11 * vw);
             } else {
                 pa[1] = 0u;
                 pa[3] = 0u;
-            }
-        }
-#pragma unroll
-        for (int n = 0; n < NT; ++n) {
-            o[n][0] *= c0;
-            o[n][1] *= c0;
-            if (UPPER) {
-                o[n][2] *= c1;
-                o[n][3] *= c1;
             }
         }
 
@@ -670,27 +768,7 @@ decodeSplitFp8Kernel(const __half* __restrict__ q, const uint8_t* __restrict__ k
         }
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < G * HD; idx += NW * 32) {
-        const int g = idx / HD, d = idx - g * HD;
-        float M = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < NW; ++w) M = fmaxf(M, red[(w * G + g) * RS + HD]);
-        float acc = 0.f, lsum = 0.f;
-#pragma unroll
-        for (int w = 0; w < NW; ++w) {
-            const float wgt = exp2f(red[(w * G + g) * RS + HD] - M);
-            acc += wgt * red[(w * G + g) * RS + d];
-            lsum += wgt * red[(w * G + g) * RS + HD + 1];
-        }
-        const int head = kvh * G + g;
-        if (numSplits == 1) {
-            out[(static_cast<int64_t>(b) * heads + head) * HD + d] = __float2half_rn(acc / lsum);
-        } else {
-            float* part = workspace + ((static_cast<int64_t>(b) * heads + head) * maxSplits + split) * RS;
-            part[d] = acc;
-            if (d == 0) { part[HD] = M; part[HD + 1] = lsum; }
-        }
-    }
+    finishSplit<__half, HD, NW>(red, G, work, heads, kvHeads, maxSplits, out, workspace, counters);
 }
 
 // Combine the splits of one (sequence, head): out = sum_s 2^(m_s - M) O_s / sum_s 2^(m_s - M) l_s.
@@ -701,7 +779,7 @@ __global__ void decodeMergeKernel(const float* __restrict__ workspace, const uin
     constexpr int RS = HD + 2;
     const int head = blockIdx.x, b = blockIdx.y;
     const SplitInfo si = splitInfo(lens[b], window, maxNumBlocks * blockSize);
-    const int numSplits = (si.numTiles + chunkTiles - 1) / chunkTiles;
+    const int numSplits = si.numTiles > 0 ? splitCount(si.numTiles, chunkTiles) : 0;
     if (numSplits <= 1) return;                       // written by the decode kernel itself
     const float* part = workspace + (static_cast<int64_t>(b) * heads + head) * maxSplits * RS;
     float M = -INFINITY;
@@ -844,22 +922,44 @@ decodeGeneralKernel(const QT* __restrict__ q, const KT* __restrict__ kPool, cons
 struct SplitPlan {
     bool fast;
     int chunkTiles, maxSplits;
+    const int4* items;      // work list on the device (host-planned launches), else null
+    int numItems;
 };
 
-constexpr int kWarps = 4, kStages = 3;
+constexpr int kWarps = 4, kStages = 3, kStagesFp8 = 4;
 
-SplitPlan planSplits(const DecodeParams& p, int smCount) {
-    SplitPlan plan{false, 0, 1};
+bool fastPathApplies(const DecodeParams& p) {
     const int G = p.kvHeads > 0 ? p.heads / p.kvHeads : 0;
-    plan.fast = ((p.dtype == kF16 || p.dtype == kBF16) && (p.headDim == 128 || p.headDim == 64) &&
-                 p.blockSize % kTileTokens == 0 && G >= 1 && G <= 16) ||
-                (p.dtype == kFP8 && p.headDim == 128 && p.blockSize % kTileTokens == 0 && G >= 1 && G <= 16 &&
-                 p.kScale && p.vScale);
-    if (!plan.fast) return plan;
+    const bool shape = p.headDim > 0 && p.blockSize % kTileTokens == 0 && G >= 1 && G <= 16;
+    // the split kernels copy pages with 16-byte cp.async and read the query rows as 4-byte
+    // (FP8: 8-byte) words; anything less aligned goes to the general kernel
+    const auto aligned = [](const void* ptr, uintptr_t a) { return (reinterpret_cast<uintptr_t>(ptr) & (a - 1)) == 0; };
+    if (!shape || !aligned(p.kPool, 16) || !aligned(p.vPool, 16) || !aligned(p.out, 2)) return false;
+    if (p.dtype == kF16 || p.dtype == kBF16) return (p.headDim == 128 || p.headDim == 64) && aligned(p.q, 4);
+    if (p.dtype == kFP8) return p.headDim == 128 && p.kScale && p.vScale && aligned(p.q, 8) && aligned(p.kScale, 2) && aligned(p.vScale, 2);
+    return false;
+}
+
+// CTAs of the split kernel an SM holds at once (bounded by shared memory).
+int residentCtas(const DecodeParams& p) {
+    if (p.dtype == kFP8) return 3;
+    return p.headDim == 64 ? 4 : 2;
+}
+
+int maxTilesOf(const DecodeParams& p) {
     int maxTokens = p.maxNumBlocks * p.blockSize;
     if (p.maxContext > 0 && p.maxContext < maxTokens) maxTokens = p.maxContext;
     if (p.window > 0 && p.window + kTileTokens < maxTokens) maxTokens = p.window + kTileTokens;
-    const int maxTiles = (maxTokens + kTileTokens - 1) / kTileTokens;
+    return (maxTokens + kTileTokens - 1) / kTileTokens;
+}
+
+// Lengths unknown on the host: one chunk size for the whole batch from the longest
+// context the tables can hold.
+SplitPlan planSplits(const DecodeParams& p, int smCount) {
+    SplitPlan plan{false, 0, 1, nullptr, 0};
+    plan.fast = fastPathApplies(p);
+    if (!plan.fast) return plan;
+    const int maxTiles = maxTilesOf(p);
     // Enough CTAs to fill the machine several times over, but no chunk shorter
     // than two tiles per warp.
     const int64_t pairs = static_cast<int64_t>(p.batch) * p.kvHeads;
@@ -872,66 +972,246 @@ SplitPlan planSplits(const DecodeParams& p, int smCount) {
     return plan;
 }
 
+}  // namespace
+
+// Work list of a decode whose lengths the host knows, kept between calls: most decode
+// steps leave every sequence's tile count as it was, and the list on the device is then
+// used again without any upload.
+struct DecodePlanCache {
+    static constexpr int kRing = 4;
+    int device = -1;
+    // what the list was built from
+    std::vector<int> geometry;            // (first tile, tiles) per sequence
+    int kvHeads = 0, slots = 0, waves = 0;
+    // the list
+    int chunkTiles = 0, maxSplits = 1, numItems = 0;
+    std::vector<int4> host;
+    int4* dev = nullptr;
+    size_t devCap = 0;
+    // page-locked staging, one slot per upload in flight
+    int4* pinned[kRing] = {};
+    size_t pinnedCap[kRing] = {};
+    cudaEvent_t ev[kRing] = {};
+    int next = 0;
+    ~DecodePlanCache() {
+        if (device < 0) return;
+        int prev = -1;
+        cudaGetDevice(&prev);
+        cudaSetDevice(device);
+        if (dev) cudaFree(dev);
+        for (int i = 0; i < kRing; ++i) {
+            if (pinned[i]) cudaFreeHost(pinned[i]);
+            if (ev[i]) cudaEventDestroy(ev[i]);
+        }
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+};
+
+DecodePlanCache* createDecodePlanCache() { return new DecodePlanCache(); }
+void destroyDecodePlanCache(DecodePlanCache* c) { delete c; }
+
+namespace {
+
+int planWaves() {
+    // CTAs per resident slot the work list aims at (PAM_DECODE_WAVES overrides, for tuning runs)
+    static const int waves = [] {
+        const char* e = std::getenv("PAM_DECODE_WAVES");
+        const int v = e ? std::atoi(e) : 0;
+        return v > 0 ? v : 12;
+    }();
+    return waves;
+}
+
+// Builds (or finds unchanged) the work list for `p` from the host copy of the lengths and
+// makes sure it is on the device.  The upload is ordered on `stream` before the launch.
+cudaError_t planFromLengths(const DecodeParams& p, int smCount, cudaStream_t stream, SplitPlan& plan) {
+    DecodePlanCache& c = *p.planCache;
+    plan = SplitPlan{true, 0, 1, nullptr, 0};
+    const int maxTokens = p.maxNumBlocks * p.blockSize;
+    const int slots = smCount * residentCtas(p), waves = planWaves();
+    std::vector<int> geometry(static_cast<size_t>(p.batch) * 2);
+    int64_t totalTiles = 0;
+    for (int b = 0; b < p.batch; ++b) {
+        const uint32_t len = p.hostLens[b];
+        uint32_t L = len < static_cast<uint32_t>(maxTokens) ? len : static_cast<uint32_t>(maxTokens);
+        int ws = (p.window > 0 && len > static_cast<uint32_t>(p.window)) ? static_cast<int>(len) - p.window : 0;
+        if (ws > static_cast<int>(L)) ws = static_cast<int>(L);
+        const int first = ws / kTileTokens;
+        const int tiles = (static_cast<int>(L) + kTileTokens - 1) / kTileTokens - first;
+        geometry[2 * b] = first;
+        geometry[2 * b + 1] = tiles;
+        totalTiles += tiles > 0 ? tiles : 0;
+    }
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    const bool same = c.device == dev && c.kvHeads == p.kvHeads && c.slots == slots && c.waves == waves &&
+                      c.geometry == geometry && c.dev != nullptr;
+    if (!same) {
+        if (c.device >= 0 && c.device != dev) return cudaErrorInvalidDevice;   // one cache belongs to one GPU
+        c.device = dev;
+        // chunk: about `waves` CTAs per resident slot, between two tiles per warp and 1024 tokens
+        int64_t chunk = totalTiles * p.kvHeads / (static_cast<int64_t>(slots) * waves);
+        if (chunk < 2 * kWarps) chunk = 2 * kWarps;
+        if (chunk > 64) chunk = 64;
+        c.chunkTiles = static_cast<int>(chunk);
+        c.maxSplits = 1;
+        // ranges by decreasing size (counting sort; a range has at most `chunk` tiles)
+        std::vector<int> count(static_cast<size_t>(chunk) + 2, 0);
+        int items = 0;
+        for (int b = 0; b < p.batch; ++b) {
+            const int tiles = geometry[2 * b + 1];
+            const int n = tiles > 0 ? splitCount(tiles, c.chunkTiles) : 1;
+            if (n > c.maxSplits) c.maxSplits = n;
+            if (n > 0x7FFF) return cudaErrorInvalidValue;
+            for (int k = 0; k < n; ++k) {
+                int begin = 0, end = 0;
+                if (tiles > 0) splitRange(tiles, n, k, begin, end);
+                count[static_cast<size_t>(end - begin)] += 1;
+                ++items;
+            }
+        }
+        std::vector<int> start(count.size(), 0);
+        for (int sz = static_cast<int>(chunk); sz >= 0; --sz) start[static_cast<size_t>(sz)] = start[static_cast<size_t>(sz) + 1] + count[static_cast<size_t>(sz) + 1];
+        c.host.assign(static_cast<size_t>(items), int4{0, 0, 0, 0});
+        for (int b = 0; b < p.batch; ++b) {
+            const int first = geometry[2 * b], tiles = geometry[2 * b + 1];
+            const int n = tiles > 0 ? splitCount(tiles, c.chunkTiles) : 1;
+            for (int k = 0; k < n; ++k) {
+                int begin = 0, end = 0;
+                if (tiles > 0) splitRange(tiles, n, k, begin, end);
+                c.host[static_cast<size_t>(start[static_cast<size_t>(end - begin)]++)] = int4{b, first + begin, first + end, k | (n << 16)};
+            }
+        }
+        c.numItems = items;
+        if (static_cast<size_t>(items) > c.devCap) {
+            if (c.dev) { cudaStreamSynchronize(stream); cudaFree(c.dev); c.dev = nullptr; c.devCap = 0; }
+            const size_t cap = static_cast<size_t>(items) + static_cast<size_t>(items) / 2 + 64;
+            e = cudaMalloc(reinterpret_cast<void**>(&c.dev), cap * sizeof(int4));
+            if (e != cudaSuccess) { c.dev = nullptr; return e; }
+            c.devCap = cap;
+        }
+        const int slot = c.next;
+        c.next = (c.next + 1) % DecodePlanCache::kRing;
+        if (!c.ev[slot]) {
+            e = cudaEventCreateWithFlags(&c.ev[slot], cudaEventDisableTiming);
+            if (e != cudaSuccess) return e;
+        } else {
+            e = cudaEventSynchronize(c.ev[slot]);           // the upload that last used this slot has been read
+            if (e != cudaSuccess) return e;
+        }
+        if (static_cast<size_t>(items) > c.pinnedCap[slot]) {
+            if (c.pinned[slot]) cudaFreeHost(c.pinned[slot]);
+            c.pinned[slot] = nullptr;
+            c.pinnedCap[slot] = 0;
+            e = cudaHostAlloc(reinterpret_cast<void**>(&c.pinned[slot]), c.devCap * sizeof(int4), cudaHostAllocDefault);
+            if (e != cudaSuccess) { c.pinned[slot] = nullptr; return e; }
+            c.pinnedCap[slot] = c.devCap;
+        }
+        std::memcpy(c.pinned[slot], c.host.data(), static_cast<size_t>(items) * sizeof(int4));
+        e = cudaMemcpyAsync(c.dev, c.pinned[slot], static_cast<size_t>(items) * sizeof(int4), cudaMemcpyHostToDevice, stream);
+        if (e == cudaSuccess) e = cudaEventRecord(c.ev[slot], stream);
+        if (e != cudaSuccess) { c.geometry.clear(); return e; }
+        c.geometry.swap(geometry);
+        c.kvHeads = p.kvHeads; c.slots = slots; c.waves = waves;
+    }
+    plan.chunkTiles = c.chunkTiles;
+    plan.maxSplits = c.maxSplits;
+    plan.items = c.dev;
+    plan.numItems = c.numItems;
+    return cudaSuccess;
+}
+
+// Bytes of split-K partials of a plan.
+size_t partialBytes(const DecodeParams& p, const SplitPlan& plan) {
+    if (!plan.fast || plan.maxSplits <= 1) return 0;
+    return static_cast<size_t>(p.batch) * p.heads * plan.maxSplits * (p.headDim + 2) * sizeof(float);
+}
+
+// The dynamic shared memory limit of a kernel is raised once per device, not per launch.
+template <class K>
+cudaError_t allowSharedMemory(K kernel, size_t bytes, std::atomic<size_t>* granted) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (granted[dev].load(std::memory_order_acquire) >= bytes) return cudaSuccess;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
+    if (e == cudaSuccess) granted[dev].store(bytes, std::memory_order_release);
+    return e;
+}
+
+dim3 splitGrid(const DecodeParams& p, const SplitPlan& plan) {
+    if (plan.items) return dim3(static_cast<unsigned>(plan.numItems), static_cast<unsigned>(p.kvHeads));
+    return dim3(static_cast<unsigned>(plan.maxSplits), static_cast<unsigned>(p.kvHeads), static_cast<unsigned>(p.batch));
+}
+
+// The last CTA of a (sequence, kv head) merges its splits when the caller gave counters
+// for every such pair; else the merge kernel follows.
+bool mergeInKernel(const DecodeParams& p, const SplitPlan& plan) {
+    return plan.maxSplits > 1 && p.counters && static_cast<int64_t>(p.batch) * p.kvHeads <= p.countersCap;
+}
+
+template <typename T, int HD>
+cudaError_t launchMerge(const DecodeParams& p, const SplitPlan& plan, cudaStream_t stream, int* launches) {
+    dim3 mgrid(static_cast<unsigned>(p.heads), static_cast<unsigned>(p.batch));
+    decodeMergeKernel<T, HD><<<mgrid, HD, 0, stream>>>(p.workspace, p.lens, static_cast<T*>(p.out), p.heads,
+                                                      p.blockSize, p.maxNumBlocks, p.window, plan.chunkTiles,
+                                                      plan.maxSplits);
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess && launches) *launches += 1;
+    return e;
+}
+
 template <typename T, int HD, bool UPPER>
 cudaError_t launchFast(const DecodeParams& p, const SplitPlan& plan, cudaStream_t stream, int* launches) {
     constexpr int NW = kWarps, NS = kStages;
+    static std::atomic<size_t> granted[64];
     const int G = p.heads / p.kvHeads;
     size_t ring = static_cast<size_t>(NW) * NS * 2 * kTileTokens * HD * 2;
     size_t red = static_cast<size_t>(NW) * G * (HD + 2) * sizeof(float);
     size_t smem = ring > red ? ring : red;
     auto kernel = decodeSplitKernel<T, HD, NW, NS, UPPER>;
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    cudaError_t e = allowSharedMemory(kernel, smem, granted);
     if (e != cudaSuccess) return e;
-    dim3 grid(static_cast<unsigned>(plan.maxSplits), static_cast<unsigned>(p.kvHeads), static_cast<unsigned>(p.batch));
+    const bool fused = mergeInKernel(p, plan);
     const float scaleLog2 = (1.0f / sqrtf(static_cast<float>(p.headDim))) * kLog2e;
-    kernel<<<grid, NW * 32, smem, stream>>>(static_cast<const T*>(p.q), static_cast<const T*>(p.kPool),
-                                            static_cast<const T*>(p.vPool), p.tables, p.lens,
-                                            static_cast<T*>(p.out), p.workspace, p.heads, p.kvHeads,
-                                            p.blockSize, p.maxNumBlocks, p.window, plan.chunkTiles,
-                                            plan.maxSplits, scaleLog2, p.poolBlocks);
+    kernel<<<splitGrid(p, plan), NW * 32, smem, stream>>>(static_cast<const T*>(p.q), static_cast<const T*>(p.kPool),
+                                                          static_cast<const T*>(p.vPool), p.tables, p.lens,
+                                                          static_cast<T*>(p.out), p.workspace, p.heads, p.kvHeads,
+                                                          p.blockSize, p.maxNumBlocks, p.window, plan.chunkTiles,
+                                                          plan.maxSplits, scaleLog2, p.poolBlocks, plan.items,
+                                                          fused ? p.counters : nullptr);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     if (launches) *launches += 1;
-    if (plan.maxSplits > 1) {
-        dim3 mgrid(static_cast<unsigned>(p.heads), static_cast<unsigned>(p.batch));
-        decodeMergeKernel<T, HD><<<mgrid, HD, 0, stream>>>(p.workspace, p.lens, static_cast<T*>(p.out), p.heads,
-                                                          p.blockSize, p.maxNumBlocks, p.window,
-                                                          plan.chunkTiles, plan.maxSplits);
-        e = cudaGetLastError();
-        if (e == cudaSuccess && launches) *launches += 1;
-    }
+    if (plan.maxSplits > 1 && !fused) e = launchMerge<T, HD>(p, plan, stream, launches);
     return e;
 }
 
 template <bool UPPER>
 cudaError_t launchFastFp8(const DecodeParams& p, const SplitPlan& plan, cudaStream_t stream, int* launches) {
-    constexpr int NW = kWarps, NS = 4, HD = 128;
+    constexpr int NW = kWarps, NS = kStagesFp8, HD = 128;
+    static std::atomic<size_t> granted[64];
     const int G = p.heads / p.kvHeads;
     size_t ring = static_cast<size_t>(NW) * NS * (2 * kTileTokens * HD + 16);
     size_t red = static_cast<size_t>(NW) * G * (HD + 2) * sizeof(float);
     size_t smem = ring > red ? ring : red;
     auto kernel = decodeSplitFp8Kernel<NW, NS, UPPER>;
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    cudaError_t e = allowSharedMemory(kernel, smem, granted);
     if (e != cudaSuccess) return e;
-    dim3 grid(static_cast<unsigned>(plan.maxSplits), static_cast<unsigned>(p.kvHeads), static_cast<unsigned>(p.batch));
+    const bool fused = mergeInKernel(p, plan);
     const float scaleLog2 = (1.0f / sqrtf(static_cast<float>(p.headDim))) * kLog2e;
-    kernel<<<grid, NW * 32, smem, stream>>>(static_cast<const __half*>(p.q), static_cast<const uint8_t*>(p.kPool),
-                                            static_cast<const uint8_t*>(p.vPool), static_cast<const __half*>(p.kScale),
-                                            static_cast<const __half*>(p.vScale), p.tables, p.lens,
-                                            static_cast<__half*>(p.out), p.workspace, p.heads, p.kvHeads, p.blockSize,
-                                            p.maxNumBlocks, p.window, plan.chunkTiles, plan.maxSplits, scaleLog2,
-                                            p.poolBlocks);
+    kernel<<<splitGrid(p, plan), NW * 32, smem, stream>>>(static_cast<const __half*>(p.q), static_cast<const uint8_t*>(p.kPool),
+                                                          static_cast<const uint8_t*>(p.vPool), static_cast<const __half*>(p.kScale),
+                                                          static_cast<const __half*>(p.vScale), p.tables, p.lens,
+                                                          static_cast<__half*>(p.out), p.workspace, p.heads, p.kvHeads, p.blockSize,
+                                                          p.maxNumBlocks, p.window, plan.chunkTiles, plan.maxSplits, scaleLog2,
+                                                          p.poolBlocks, plan.items, fused ? p.counters : nullptr);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     if (launches) *launches += 1;
-    if (plan.maxSplits > 1) {
-        dim3 mgrid(static_cast<unsigned>(p.heads), static_cast<unsigned>(p.batch));
-        decodeMergeKernel<__half, HD><<<mgrid, HD, 0, stream>>>(p.workspace, p.lens, static_cast<__half*>(p.out), p.heads,
-                                                               p.blockSize, p.maxNumBlocks, p.window, plan.chunkTiles,
-                                                               plan.maxSplits);
-        e = cudaGetLastError();
-        if (e == cudaSuccess && launches) *launches += 1;
-    }
+    if (plan.maxSplits > 1 && !fused) e = launchMerge<__half, HD>(p, plan, stream, launches);
     return e;
 }
 
@@ -947,9 +1227,10 @@ cudaError_t launchFastT(const DecodeParams& p, const SplitPlan& plan, cudaStream
 
 template <typename QT, typename KT>
 cudaError_t launchGeneral(const DecodeParams& p, cudaStream_t stream, int* launches) {
+    static std::atomic<size_t> granted[64];
     const size_t smem = (static_cast<size_t>(8 + 2 * 16) * p.headDim + 8 * 16 + 3 * 8) * sizeof(float);
     auto kernel = decodeGeneralKernel<QT, KT>;
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    cudaError_t e = allowSharedMemory(kernel, smem, granted);
     if (e != cudaSuccess) return e;
     dim3 grid(static_cast<unsigned>(p.kvHeads), static_cast<unsigned>(p.batch));
     kernel<<<grid, 128, smem, stream>>>(static_cast<const QT*>(p.q), static_cast<const KT*>(p.kPool),
@@ -961,21 +1242,30 @@ cudaError_t launchGeneral(const DecodeParams& p, cudaStream_t stream, int* launc
     return cudaGetLastError();
 }
 
+cudaError_t makePlan(const DecodeParams& p, int smCount, cudaStream_t stream, SplitPlan& plan) {
+    if (p.hostLens && p.planCache && fastPathApplies(p)) return planFromLengths(p, smCount, stream, plan);
+    plan = planSplits(p, smCount);
+    return cudaSuccess;
+}
+
 }  // namespace
 
-size_t decodeWorkspaceBytes(const DecodeParams& p, int smCount) {
-    const SplitPlan plan = planSplits(p, smCount);
-    if (!plan.fast || plan.maxSplits <= 1) return 0;
-    return static_cast<size_t>(p.batch) * p.heads * plan.maxSplits * (p.headDim + 2) * sizeof(float);
+bool decodeTakesSplitPath(const DecodeParams& p) { return fastPathApplies(p); }
+
+size_t decodeWorkspaceBytes(const DecodeParams& p, int smCount, cudaStream_t stream) {
+    SplitPlan plan{};
+    if (makePlan(p, smCount, stream, plan) != cudaSuccess) { cudaGetLastError(); return 0; }
+    return partialBytes(p, plan);
 }
 
 cudaError_t launchDecode(const DecodeParams& p, int smCount, cudaStream_t stream, int* launches) {
     if (p.batch <= 0) return cudaSuccess;
     if (p.headDim > 256 || p.poolBlocks <= 0) return cudaErrorInvalidValue;
-    const SplitPlan plan = planSplits(p, smCount);
+    SplitPlan plan{};
+    cudaError_t pe = makePlan(p, smCount, stream, plan);
+    if (pe != cudaSuccess) return pe;
     if (plan.fast) {
-        if (plan.maxSplits > 1 &&
-            (!p.workspace || p.workspaceBytes < decodeWorkspaceBytes(p, smCount)))
+        if (plan.maxSplits > 1 && (!p.workspace || p.workspaceBytes < partialBytes(p, plan)))
             return cudaErrorInvalidValue;
         if (p.dtype == kFP8)
             return p.heads / p.kvHeads > 8 ? launchFastFp8<true>(p, plan, stream, launches)
@@ -997,21 +1287,28 @@ size_t decodeStaticScratchBytes() { return kStaticScratchBytes; }
 cudaError_t launchDecodeStatic(const DecodeParams& p, int smCount, cudaStream_t stream, int* launches) {
     // In host code the array's name is only a handle; the kernels need its
     // device address, which differs per GPU.  It is looked up once per device,
-    // with that device current (the caller has made it so).
-    static float* addressOnDevice[64] = {};
+    // with that device current (the caller has made it so).  Two host threads may
+    // get here together for the same GPU: both then store the same address.
+    static std::atomic<float*> addressOnDevice[64];
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
-    if (!addressOnDevice[dev]) {
+    float* scratch = addressOnDevice[dev].load(std::memory_order_acquire);
+    if (!scratch) {
         void* ptr = nullptr;
         e = cudaGetSymbolAddress(&ptr, gStaticDecodeScratch);
         if (e != cudaSuccess) return e;
-        addressOnDevice[dev] = static_cast<float*>(ptr);
+        scratch = static_cast<float*>(ptr);
+        addressOnDevice[dev].store(scratch, std::memory_order_release);
     }
-    if (decodeWorkspaceBytes(p, smCount) > kStaticScratchBytes) return cudaErrorInvalidValue;
     DecodeParams q = p;
-    q.workspace = addressOnDevice[dev];
+    q.hostLens = nullptr;      // the plan of this variant never depends on a cache that may allocate
+    q.planCache = nullptr;
+    q.counters = nullptr;
+    q.countersCap = 0;
+    if (decodeWorkspaceBytes(q, smCount, stream) > kStaticScratchBytes) return cudaErrorInvalidValue;
+    q.workspace = scratch;
     q.workspaceBytes = kStaticScratchBytes;
     return launchDecode(q, smCount, stream, launches);
 }

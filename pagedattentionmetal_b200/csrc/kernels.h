@@ -7,6 +7,7 @@
 
 #include <cstddef>
 #include <cstdint>
+#include <string>
 
 namespace pam {
 
@@ -41,6 +42,11 @@ cudaError_t launchCopyBlocks(void* kPool, void* vPool, void* kScale, void* vScal
                              const int32_t* pairs, int n, size_t blockBytes, int kvHeads,
                              cudaStream_t stream, int* launches);
 
+// patches: [n][3] (row, column, block) written into tables[row * stride + column]: the
+// entries of a resident batch of block tables that changed since it was uploaded.
+cudaError_t launchPatchTables(int32_t* tables, int stride, const int32_t* patches, int n, cudaStream_t stream,
+                              int* launches);
+
 // ---- decode (decode_kernels.cu) ----
 struct DecodeParams {
     const void* q;            // [batch][heads][dim], io type
@@ -56,9 +62,25 @@ struct DecodeParams {
     int poolBlocks;           // blocks in the pools; table entries are clamped into [0, poolBlocks)
     float* workspace;         // split-K partials, decodeWorkspaceBytes() bytes
     size_t workspaceBytes;
+    // Optional.  With a host copy of `lens` and a plan cache the launch is planned from the
+    // real lengths: ranges of equal size per sequence, longest first, exactly as many CTAs
+    // as there is work.  With `counters` (device words, all zero between launches, one per
+    // (sequence, kv head)) the splits are merged by the CTA that finishes last instead of
+    // by a second kernel.
+    const uint32_t* hostLens;
+    struct DecodePlanCache* planCache;
+    int* counters;
+    int64_t countersCap;
 };
-// Bytes of split-K workspace the launch of `p` needs (0 when it runs unsplit).
-size_t decodeWorkspaceBytes(const DecodeParams& p, int smCount);
+// State of the host-planned launches of one context (work list on the device, staging).
+struct DecodePlanCache;
+DecodePlanCache* createDecodePlanCache();
+void destroyDecodePlanCache(DecodePlanCache* cache);
+// True when `p` runs on the split kernels (type, shape and pointer alignment allow it).
+bool decodeTakesSplitPath(const DecodeParams& p);
+// Bytes of split-K workspace the launch of `p` needs (0 when it runs unsplit).  With host
+// lengths this builds the plan (and may enqueue its upload on `stream`).
+size_t decodeWorkspaceBytes(const DecodeParams& p, int smCount, cudaStream_t stream);
 cudaError_t launchDecode(const DecodeParams& p, int smCount, cudaStream_t stream, int* launches);
 // Same decode with the split-K workspace taken from a fixed array inside the
 // library (decodeStaticScratchBytes() bytes per GPU) instead of p.workspace.
@@ -95,6 +117,8 @@ struct PrefillParams {
     int inlineMeta;
     int32_t meta[5][kPrefillInlineSeqs];
     int exactWeights;             // bfloat16 tensor path: 0 = 8-bit weights, 1 = 16-bit on short rows, 2 = 16-bit always
+    long long waitCycles;         // tensor path: bound of every wait on a barrier in SM cycles; 0 = the default (about 0.2 s)
+    int starveV;                  // tensor path, test launches: the CTA's first value tile is not fetched (its wait runs out)
     // Filled by the tensor-core launcher: reciprocals for the work-item arithmetic (an item
     // index is split by numSeqs * heads, heads and heads / kvHeads; valid while the item
     // count stays below 2^22, else fastItems is 0 and the kernel divides).
@@ -125,5 +149,18 @@ cudaError_t launchPrefill(const PrefillParams& p, int smCount, cudaStream_t stre
 bool prefillFp8StagingApplies(const PrefillParams& p);
 cudaError_t launchFp8StagePages(const PrefillParams& p, const int32_t* seqLens, const int32_t* windowStarts, int maxCount,
                                 void* kOut, void* vOut, int32_t* stagedTables, cudaStream_t stream, int* launches);
+
+// ---- all-gather of head-sharded outputs (comm.cu) ----
+// local: [rows][slice] on this GPU (slice = heads/N * dim * element bytes, a multiple of 16);
+// staging: N * rows * slice bytes of scratch; full: [rows][N][slice] on every GPU.
+struct HeadComm;
+bool commAvailable();
+int commUniqueId(void* out128);
+HeadComm* commCreate(const void* id128, int rank, int size, int device, std::string* error);
+void commDestroy(HeadComm* comm);
+int commRank(const HeadComm* comm);
+int commSize(const HeadComm* comm);
+cudaError_t launchAllGatherHeads(HeadComm* comm, const void* local, void* staging, void* full, int rows, size_t sliceBytes,
+                                 cudaStream_t stream, int* launches, std::string* error);
 
 }  // namespace pam

@@ -9,6 +9,7 @@
 #include <algorithm>
 #include <chrono>
 #include <climits>
+#include <map>
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
@@ -97,6 +98,13 @@ struct Context {
     size_t pinnedCap = 0;
     void* qStage = nullptr;   // device copy of a host query of pam_decode, sent before the tables are built
     size_t qStageCap = 0;
+    void* outStage = nullptr; // device side of a pageable host output of pam_decode
+    size_t outStageCap = 0;
+    pam::DecodePlanCache* planCache = nullptr;   // work lists of decodes whose lengths the host knows
+    int* mergeCounters = nullptr;                // zero between launches: split arrivals per (sequence, kv head)
+    int64_t mergeCountersCap = 0;
+    long long waitLimitCycles = 0;               // 0: the prefill kernel's default bound on its waits
+    int dropFirstVTile = 0;                      // test switch, see pamc_test_starve_prefill
 
     int32_t fail(int code, const std::string& msg) {            // CABI.swift:18-30
         lastError = msg;
@@ -117,11 +125,29 @@ struct Cache {
     size_t poolBytes = 0, scaleBytes = 0;
     std::mutex mu;
     std::vector<std::pair<int32_t, int32_t>> cowLog;
+    // The block tables of the batch pam_decode last ran, kept on the device: a decode step
+    // changes at most one entry per sequence, so only what changed is sent again.
+    struct Resident {
+        int32_t* tables = nullptr;         // [rows][stride]
+        uint32_t* upload = nullptr;        // lengths, then (row, column, block) patches
+        int rows = 0, stride = 0;
+        size_t uploadCap = 0;              // bytes
+        std::vector<int64_t> ids;          // per row: what the device copy holds
+        std::vector<uint64_t> versions;
+        std::vector<int32_t> counts;
+        unsigned char* pinned = nullptr;   // staging of `upload`
+        size_t pinnedCap = 0;
+        cudaEvent_t consumed = nullptr;    // the last upload has left `pinned`
+    } res;
     Cache(int maxBlocks_, int blockSize_) : mgr(maxBlocks_, blockSize_), blockSize(blockSize_), maxBlocks(maxBlocks_) {}
     ~Cache() {
         if (bookkeeping) return;
         cudaSetDevice(device);
+        cudaDeviceSynchronize();
         cudaFree(kPool); cudaFree(vPool); cudaFree(kScale); cudaFree(vScale); cudaFree(amax);
+        cudaFree(res.tables); cudaFree(res.upload);
+        if (res.pinned) cudaFreeHost(res.pinned);
+        if (res.consumed) cudaEventDestroy(res.consumed);
     }
     size_t blockBytes() const { return static_cast<size_t>(blockSize) * kvHeads * headDim * pam::elemBytes(dtype); }
 };
@@ -138,6 +164,23 @@ bool isDevicePointer(const void* p) {
     cudaPointerAttributes a{};
     if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return false; }
     return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
+}
+
+// Where a buffer argument lives, asked once per call.  `device` is the address a kernel
+// may use: the pointer itself for device memory, the device-side alias for page-locked
+// host memory, null for pageable host memory (which has to be staged).
+struct Placement {
+    bool onDevice = false;
+    void* device = nullptr;
+};
+Placement placementOf(const void* p) {
+    Placement r;
+    cudaPointerAttributes a{};
+    if (!p || cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return r; }
+    r.onDevice = a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
+    if (r.onDevice) r.device = const_cast<void*>(p);
+    else if (a.type == cudaMemoryTypeHost) r.device = a.devicePointer;
+    return r;
 }
 
 // Operations that need the GPU fail like a missing device (PagedAttentionTypes.swift:36-37).
@@ -215,6 +258,14 @@ bool requireBuffer(Context* c, const PamBuffer& b, const char* name, size_t expe
         return false;
     }
     return true;
+}
+
+// Query, output and new K/V rows of an FP8 layer are float16: the reference's
+// qBytesPerToken / kvBytesPerToken count the cache's one byte per element there
+// (PagedAttentionTypes.swift:149-151), half of what the kernels read and write.  A buffer
+// of known length must hold what is really accessed.
+bool requireIoBuffer(Context* c, const PamBuffer& b, const char* name, size_t referenceBytes, size_t accessedBytes) {
+    return requireBuffer(c, b, name, std::max(referenceBytes, accessedBytes));
 }
 
 size_t qBytesPerToken(const PamLayerSpec& l) {                  // PagedAttentionTypes.swift:149
@@ -382,8 +433,8 @@ int32_t appendImpl(Context* c, const PamAppendRequest& rq, Cache* cacheForScratc
     const size_t finalLen = static_cast<size_t>(rq.token_offset) + T;
     const size_t numBlocks = (finalLen + l.block_size - 1) / l.block_size;
     const size_t newBytes = static_cast<size_t>(T) * l.num_kv_heads * l.head_dim * pam::ioBytes(l.data_type);
-    if (!requireBuffer(c, rq.keys, "new keys", static_cast<size_t>(T) * kvBytesPerToken(l))) return -1;
-    if (!requireBuffer(c, rq.values, "new values", static_cast<size_t>(T) * kvBytesPerToken(l))) return -1;
+    if (!requireIoBuffer(c, rq.keys, "new keys", static_cast<size_t>(T) * kvBytesPerToken(l), newBytes)) return -1;
+    if (!requireIoBuffer(c, rq.values, "new values", static_cast<size_t>(T) * kvBytesPerToken(l), newBytes)) return -1;
     if (!hostSlots && !deviceSlots && !requireBuffer(c, rq.block_table, "blockTable", numBlocks * sizeof(int32_t))) return -1;
     if (!requireBuffer(c, rq.k_pool, "K pool", numBlocks * l.block_size * kvBytesPerToken(l))) return -1;
     if (!requireBuffer(c, rq.v_pool, "V pool", numBlocks * l.block_size * kvBytesPerToken(l))) return -1;
@@ -444,8 +495,9 @@ int32_t appendImpl(Context* c, const PamAppendRequest& rq, Cache* cacheForScratc
     return 0;
 }
 
-int32_t decodeImpl(Context* c, const PamDecodeRequest& rq, int maxContext) {
-    // PagedAttentionEngine.swift:533-580; validateDecode :1916-1933
+// validateDecode (PagedAttentionEngine.swift:1916-1933) and the checks of decodeFlat's
+// arguments; host work only, done before anything that needs the GPU.
+int32_t validateDecode(Context* c, const PamDecodeRequest& rq) {
     if (!validateLayer(c, rq.layer)) return -1;
     if (rq.batch_size <= 0) return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("batchSize must be positive."));
     if (rq.max_num_blocks <= 0) return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("maxNumBlocks must be positive."));
@@ -453,16 +505,25 @@ int32_t decodeImpl(Context* c, const PamDecodeRequest& rq, int maxContext) {
     const size_t B = static_cast<size_t>(rq.batch_size), NB = static_cast<size_t>(rq.max_num_blocks);
     if (rq.block_tables.bytes != kUnknownBytes && NB > rq.block_tables.bytes / (B * sizeof(int32_t)))
         return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("maxNumBlocks exceeds blockTables buffer capacity"));
-    if (!requireBuffer(c, rq.q, "Q", B * qBytesPerToken(l))) return -1;
+    if (!requireIoBuffer(c, rq.q, "Q", B * qBytesPerToken(l), B * ioBytesPerToken(l))) return -1;
     if (!requireBuffer(c, rq.block_tables, "blockTables", B * NB * sizeof(int32_t))) return -1;
     if (!requireBuffer(c, rq.seq_lengths, "seqLengths", B * sizeof(uint32_t))) return -1;
-    if (!requireBuffer(c, rq.output, "output", B * qBytesPerToken(l))) return -1;
+    if (!requireIoBuffer(c, rq.output, "output", B * qBytesPerToken(l), B * ioBytesPerToken(l))) return -1;
     if (!requireBuffer(c, rq.k_pool, "K pool", NB * l.block_size * kvBytesPerToken(l))) return -1;
     if (!requireBuffer(c, rq.v_pool, "V pool", NB * l.block_size * kvBytesPerToken(l))) return -1;
     if (l.data_type == PAM_DTYPE_FP8 && (!rq.k_scale.ptr || !rq.v_scale.ptr))
         return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("FP8 decode needs kScaleBuffer and vScaleBuffer."));
     if (l.head_dim > 256)
         return c->fail(PAM_ERR_UNSUPPORTED, "Unsupported paged attention path: headDim above 256.");
+    return 0;
+}
+
+int32_t decodeImpl(Context* c, const PamDecodeRequest& rq, int maxContext) {
+    // PagedAttentionEngine.swift:533-580
+    if (validateDecode(c, rq) != 0) return -1;
+    if (c->device < 0) return noGpu(c);
+    const PamLayerSpec& l = rq.layer;
+    const size_t B = static_cast<size_t>(rq.batch_size), NB = static_cast<size_t>(rq.max_num_blocks);
     if (!isDevicePointer(rq.k_pool.ptr) || !isDevicePointer(rq.v_pool.ptr))
         return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("KV pools must be device memory."));
 
@@ -486,7 +547,14 @@ int32_t decodeImpl(Context* c, const PamDecodeRequest& rq, int maxContext) {
         p.blockSize = l.block_size; p.maxNumBlocks = rq.max_num_blocks; p.window = window; p.dtype = l.data_type;
         p.maxContext = maxContext;
         p.poolBlocks = poolBlocksOf(rq.k_pool, rq.v_pool, l);
-        tempBytes = pam::decodeWorkspaceBytes(p, c->smCount);
+        // lengths the host can read (the reference's seqLengths buffer is host-visible) let the
+        // launch be planned from the real lengths
+        p.hostLens = p.lens != rq.seq_lengths.ptr ? static_cast<const uint32_t*>(rq.seq_lengths.ptr) : nullptr;
+        p.planCache = c->planCache;
+        p.counters = c->mergeCounters;
+        p.countersCap = c->mergeCountersCap;
+        if (!st.ok()) return cudaErrorMemoryAllocation;
+        tempBytes = pam::decodeWorkspaceBytes(p, c->smCount, c->stream);
         if (tempBytes) {
             p.workspace = static_cast<float*>(c->arena.take(tempBytes));
             p.workspaceBytes = tempBytes;
@@ -500,6 +568,8 @@ int32_t decodeImpl(Context* c, const PamDecodeRequest& rq, int maxContext) {
         return e;
     });
     if (rc != 0) {
+        // a launch that did not finish may have left arrivals counted
+        if (c->mergeCounters) cudaMemsetAsync(c->mergeCounters, 0, static_cast<size_t>(c->mergeCountersCap) * sizeof(int), c->stream);
         if (!c->graceful) return rc;
         st.zeroOutputs(rq.output.ptr, rq.output.bytes != kUnknownBytes ? rq.output.bytes : ioBytes);   // :536-542
         c->clearError();
@@ -514,23 +584,10 @@ int32_t decodeImpl(Context* c, const PamDecodeRequest& rq, int maxContext) {
 // memory), the context's arena is left alone, and split-K partials go to the
 // library's fixed scratch array.
 int32_t decodeNoAllocImpl(Context* c, const PamDecodeRequest& rq) {
-    if (!validateLayer(c, rq.layer)) return -1;
-    if (rq.batch_size <= 0) return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("batchSize must be positive."));
-    if (rq.max_num_blocks <= 0) return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("maxNumBlocks must be positive."));
+    if (validateDecode(c, rq) != 0) return -1;
+    if (c->device < 0) return noGpu(c);
     const PamLayerSpec& l = rq.layer;
-    const size_t B = static_cast<size_t>(rq.batch_size), NB = static_cast<size_t>(rq.max_num_blocks);
-    if (rq.block_tables.bytes != kUnknownBytes && NB > rq.block_tables.bytes / (B * sizeof(int32_t)))
-        return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("maxNumBlocks exceeds blockTables buffer capacity"));
-    if (!requireBuffer(c, rq.q, "Q", B * qBytesPerToken(l))) return -1;
-    if (!requireBuffer(c, rq.block_tables, "blockTables", B * NB * sizeof(int32_t))) return -1;
-    if (!requireBuffer(c, rq.seq_lengths, "seqLengths", B * sizeof(uint32_t))) return -1;
-    if (!requireBuffer(c, rq.output, "output", B * qBytesPerToken(l))) return -1;
-    if (!requireBuffer(c, rq.k_pool, "K pool", NB * l.block_size * kvBytesPerToken(l))) return -1;
-    if (!requireBuffer(c, rq.v_pool, "V pool", NB * l.block_size * kvBytesPerToken(l))) return -1;
-    if (l.data_type == PAM_DTYPE_FP8 && (!rq.k_scale.ptr || !rq.v_scale.ptr))
-        return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("FP8 decode needs kScaleBuffer and vScaleBuffer."));
-    if (l.head_dim > 256)
-        return c->fail(PAM_ERR_UNSUPPORTED, "Unsupported paged attention path: headDim above 256.");
+    const size_t B = static_cast<size_t>(rq.batch_size);
     const void* mustBeDevice[] = {rq.q.ptr, rq.k_pool.ptr, rq.v_pool.ptr, rq.block_tables.ptr, rq.seq_lengths.ptr, rq.output.ptr};
     for (const void* p : mustBeDevice)
         if (!isDevicePointer(p))
@@ -546,7 +603,8 @@ int32_t decodeNoAllocImpl(Context* c, const PamDecodeRequest& rq) {
     p.window = l.window_size > 0 ? l.window_size : c->defaultWindow;
     p.dtype = l.data_type; p.maxContext = 0;
     p.poolBlocks = poolBlocksOf(rq.k_pool, rq.v_pool, l);
-    const size_t need = pam::decodeWorkspaceBytes(p, c->smCount);
+    p.hostLens = nullptr; p.planCache = nullptr; p.counters = nullptr; p.countersCap = 0;
+    const size_t need = pam::decodeWorkspaceBytes(p, c->smCount, c->stream);
     if (need > pam::decodeStaticScratchBytes())
         return c->fail(PAM_ERR_RESOURCE_EXHAUSTED,
                        "GPU resource exhausted: this decode needs " + std::to_string(need) +
@@ -554,12 +612,27 @@ int32_t decodeNoAllocImpl(Context* c, const PamDecodeRequest& rq) {
                            std::to_string(pam::decodeStaticScratchBytes()) +
                            "; use pamc_decode, or a smaller batch, fewer heads or shorter tables.");
     const double t0 = nowMs();
-    int32_t rc = withRetry(c, "decodeFlat", [&]() -> cudaError_t {
+    // While the stream is being captured nothing may wait on it and nothing runs yet: the
+    // launch is recorded once, without the wait and the retry loop of the eager call.
+    cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(c->stream, &capture) != cudaSuccess) { cudaGetLastError(); capture = cudaStreamCaptureStatusNone; }
+    int32_t rc = 0;
+    if (capture != cudaStreamCaptureStatusNone) {
         int launches = 0;
         cudaError_t e = pam::launchDecodeStatic(p, c->smCount, c->stream, &launches);
         c->launches += launches;
-        return e;
-    });
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            return c->fail(PAM_ERR_COMMAND_EXECUTION, commandExecutionFailed(cudaGetErrorString(e)));
+        }
+    } else {
+        rc = withRetry(c, "decodeFlat", [&]() -> cudaError_t {
+            int launches = 0;
+            cudaError_t e = pam::launchDecodeStatic(p, c->smCount, c->stream, &launches);
+            c->launches += launches;
+            return e;
+        });
+    }
     if (rc != 0) {
         if (!c->graceful) return rc;
         cudaMemsetAsync(rq.output.ptr, 0, rq.output.bytes != kUnknownBytes ? rq.output.bytes : B * ioBytesPerToken(l), c->stream);
@@ -589,9 +662,9 @@ int32_t prefillImpl(Context* c, const PamLayerSpec& l, const PamBuffer& q, const
     const size_t numBlocks = (static_cast<size_t>(maxSeqLen) + l.block_size - 1) / l.block_size;
     if (static_cast<size_t>(maxNumBlocks) < numBlocks)
         return c->fail(PAM_ERR_BUFFER_TOO_SMALL, bufferTooSmall(tableName, numBlocks * sizeof(int32_t), static_cast<size_t>(maxNumBlocks) * sizeof(int32_t)));
-    if (!requireBuffer(c, q, "Q", static_cast<size_t>(totalRows) * qBytesPerToken(l))) return -1;
+    if (!requireIoBuffer(c, q, "Q", static_cast<size_t>(totalRows) * qBytesPerToken(l), static_cast<size_t>(totalRows) * ioBytesPerToken(l))) return -1;
     if (!requireBuffer(c, tables, tableName, seqs.size() * static_cast<size_t>(maxNumBlocks) * sizeof(int32_t))) return -1;
-    if (!requireBuffer(c, output, "output", static_cast<size_t>(totalRows) * qBytesPerToken(l))) return -1;
+    if (!requireIoBuffer(c, output, "output", static_cast<size_t>(totalRows) * qBytesPerToken(l), static_cast<size_t>(totalRows) * ioBytesPerToken(l))) return -1;
     if (!requireBuffer(c, kPool, "K pool", numBlocks * l.block_size * kvBytesPerToken(l))) return -1;
     if (!requireBuffer(c, vPool, "V pool", numBlocks * l.block_size * kvBytesPerToken(l))) return -1;
     if (l.data_type == PAM_DTYPE_FP8 && (!kScale.ptr || !vScale.ptr))
@@ -642,6 +715,9 @@ int32_t prefillImpl(Context* c, const PamLayerSpec& l, const PamBuffer& q, const
         p.errFlag = c->devErr;
         p.forceGeneral = c->forceGeneralPrefill ? 1 : 0;
         p.exactWeights = c->exactWeights;
+        p.waitCycles = c->waitLimitCycles;
+        p.starveV = 0;
+        if (c->dropFirstVTile > 0) { c->dropFirstVTile -= 1; p.starveV = 1; }
         int launches = 0;
         if (pam::prefillFp8StagingApplies(p)) {
             // FP8 KV: the pages this launch can see are dequantised to float16 scratch pools
@@ -807,6 +883,17 @@ void* pamc_create_context_on(int32_t device) {
         return nullptr;
     }
     *c->hostErr = 0;
+    c->planCache = pam::createDecodePlanCache();
+    constexpr int64_t kCounters = 1 << 16;
+    if (cudaMalloc(reinterpret_cast<void**>(&c->mergeCounters), kCounters * sizeof(int)) == cudaSuccess &&
+        cudaMemset(c->mergeCounters, 0, kCounters * sizeof(int)) == cudaSuccess) {
+        c->mergeCountersCap = kCounters;
+    } else {
+        // without them the splits are merged by a kernel of its own
+        cudaGetLastError();
+        if (c->mergeCounters) cudaFree(c->mergeCounters);
+        c->mergeCounters = nullptr;
+    }
     return c;
 }
 
@@ -834,6 +921,9 @@ void pam_destroy_context(void* ctx) {
     if (c->hostErr) cudaFreeHost(c->hostErr);
     if (c->pinned) cudaFreeHost(c->pinned);
     if (c->qStage) cudaFree(c->qStage);
+    if (c->outStage) cudaFree(c->outStage);
+    if (c->mergeCounters) cudaFree(c->mergeCounters);
+    pam::destroyDecodePlanCache(c->planCache);
     if (c->ownStream) cudaStreamDestroy(c->ownStream);
     delete c;
 }
@@ -880,6 +970,17 @@ int32_t pam_reserve_sequence(void* ctx, void* cache, int64_t id) {
     return 0;
 }
 
+// The log of copy-on-write pairs is for callers that mirror the copies elsewhere (another
+// GPU's pools, a test); one that never drains it must not grow without bound: beyond this
+// many pairs the oldest are dropped.
+constexpr size_t kCowLogLimit = size_t(1) << 16;
+static void logCopies(Cache* k, const std::vector<std::pair<int32_t, int32_t>>& cow) {
+    if (cow.empty()) return;
+    std::lock_guard<std::mutex> gk(k->mu);
+    k->cowLog.insert(k->cowLog.end(), cow.begin(), cow.end());
+    if (k->cowLog.size() > kCowLogLimit) k->cowLog.erase(k->cowLog.begin(), k->cowLog.end() - static_cast<std::ptrdiff_t>(kCowLogLimit));
+}
+
 int32_t pamc_cache_append_tokens(void* ctx, void* cache, int64_t id, int32_t count, const uint64_t* hashes,
                                  int32_t num_hashes) {
     if (!ctx || !cache) return -1;
@@ -888,11 +989,11 @@ int32_t pamc_cache_append_tokens(void* ctx, void* cache, int64_t id, int32_t cou
     std::lock_guard<std::mutex> g(c->mu);
     std::vector<std::pair<int32_t, int32_t>> cow;
     KVResult r = k->mgr.appendTokens(id, count, hashes, hashes ? num_hashes : 0, &cow);
-    {
-        std::lock_guard<std::mutex> gk(k->mu);
-        k->cowLog.insert(k->cowLog.end(), cow.begin(), cow.end());
-    }
-    if (!cow.empty() && !k->bookkeeping) {
+    logCopies(k, cow);
+    // An append that failed after its copy-on-write (the reference's order,
+    // KVCacheManager.swift:134-146) has left the sequence's table as it was: the fresh
+    // block is in no table, so there is nothing to copy into it.
+    if (r.ok() && !cow.empty() && !k->bookkeeping) {
         DeviceGuard dg(c->device);
         if (c->device < 0) return noGpu(c);
         c->arena.reset(c->stream);
@@ -914,11 +1015,8 @@ int32_t pamc_cache_ensure_exclusive(void* ctx, void* cache, int64_t id, int32_t 
     std::lock_guard<std::mutex> g(c->mu);
     std::vector<std::pair<int32_t, int32_t>> cow;
     KVResult r = k->mgr.ensureExclusiveAccess(id, logical_block, &cow);
-    {
-        std::lock_guard<std::mutex> gk(k->mu);
-        k->cowLog.insert(k->cowLog.end(), cow.begin(), cow.end());
-    }
-    if (!cow.empty() && !k->bookkeeping) {
+    logCopies(k, cow);
+    if (r.ok() && !cow.empty() && !k->bookkeeping) {
         DeviceGuard dg(c->device);
         if (c->device < 0) return noGpu(c);
         c->arena.reset(c->stream);
@@ -972,6 +1070,34 @@ int32_t pamc_cache_set_eviction_policy(void* cache, int32_t policy) {
     if (!cache || policy < 0 || policy > 2) return -1;
     asCache(cache)->mgr.setPolicy(policy);
     return 0;
+}
+
+int32_t pamc_cache_set_hygiene(void* cache, int32_t on) {
+    if (!cache) return -1;
+    asCache(cache)->mgr.setHygiene(on != 0);
+    return 0;
+}
+
+// Chained content hash of the full blocks of a token sequence: hash j covers the ids of
+// blocks 0 .. j (64-bit FNV-1a over the ids, continued from the hash of the block before),
+// so equal hashes mean equal prefixes up to a 64-bit collision.
+int32_t pamc_block_hashes(const int32_t* token_ids, int32_t num_tokens, int32_t block_size, uint64_t seed, uint64_t* out,
+                          int32_t capacity) {
+    if (!token_ids || num_tokens < 0 || block_size <= 0) return -1;
+    const int full = num_tokens / block_size;
+    uint64_t h = 0xcbf29ce484222325ull ^ seed;
+    for (int j = 0; j < full; ++j) {
+        for (int t = 0; t < block_size; ++t) {
+            uint32_t v = static_cast<uint32_t>(token_ids[static_cast<size_t>(j) * block_size + t]);
+            for (int byte = 0; byte < 4; ++byte) {
+                h ^= v & 0xFFu;
+                h *= 0x100000001b3ull;
+                v >>= 8;
+            }
+        }
+        if (out && j < capacity) out[j] = h;
+    }
+    return full;
 }
 
 int32_t pamc_cache_memory_stats(void* cache, PamMemoryStats* out) {
@@ -1106,6 +1232,8 @@ int32_t pamc_set_default_window(void* ctx, int32_t t) { if (!ctx || t < 0) retur
 int32_t pamc_set_default_chunk(void* ctx, int32_t t) { if (!ctx || t < 0) return -1; asCtx(ctx)->defaultChunk = t; return 0; }
 int32_t pamc_inject_launch_failures(void* ctx, int32_t n) { if (!ctx || n < 0) return -1; asCtx(ctx)->injectFailures = n; return 0; }
 int64_t pamc_kernel_launches(void* ctx) { return ctx ? asCtx(ctx)->launches : -1; }
+int32_t pamc_set_wait_limit(void* ctx, int64_t sm_cycles) { if (!ctx || sm_cycles < 0) return -1; asCtx(ctx)->waitLimitCycles = sm_cycles; return 0; }
+int32_t pamc_test_starve_prefill(void* ctx, int32_t launches) { if (!ctx || launches < 0) return -1; asCtx(ctx)->dropFirstVTile = launches; return 0; }
 
 int32_t pamc_last_stats(void* ctx, PamStats* out) {
     if (!ctx || !out) return -1;
@@ -1270,10 +1398,21 @@ int32_t pamc_decode(void* ctx, const PamDecodeRequest* request) {
     Context* c = asCtx(ctx);
     std::lock_guard<std::mutex> g(c->mu);
     DeviceGuard dg(c->device);
-    if (c->device < 0) return noGpu(c);
     int32_t rc = decodeImpl(c, *request, 0);
     if (rc == 0) c->clearError();
     return rc;
+}
+
+int32_t pamc_decode_path(const PamDecodeRequest* request) {
+    if (!request) return -1;
+    const PamDecodeRequest& rq = *request;
+    pam::DecodeParams p{};
+    p.q = rq.q.ptr; p.kPool = rq.k_pool.ptr; p.vPool = rq.v_pool.ptr; p.out = rq.output.ptr;
+    p.kScale = rq.k_scale.ptr; p.vScale = rq.v_scale.ptr;
+    p.heads = rq.layer.num_heads; p.kvHeads = rq.layer.num_kv_heads; p.headDim = rq.layer.head_dim;
+    p.blockSize = rq.layer.block_size; p.dtype = rq.layer.data_type;
+    if (p.kvHeads <= 0 || p.heads <= 0 || p.blockSize <= 0) return -1;
+    return pam::decodeTakesSplitPath(p) ? 1 : 0;
 }
 
 int32_t pamc_decode_noalloc(void* ctx, const PamDecodeRequest* request) {
@@ -1281,10 +1420,118 @@ int32_t pamc_decode_noalloc(void* ctx, const PamDecodeRequest* request) {
     Context* c = asCtx(ctx);
     std::lock_guard<std::mutex> g(c->mu);
     DeviceGuard dg(c->device);
-    if (c->device < 0) return noGpu(c);
     int32_t rc = decodeNoAllocImpl(c, *request);
     if (rc == 0) c->clearError();
     return rc;
+}
+
+// Brings the device copy of the batch's block tables and lengths up to date
+// (CABI.swift:306-330, 339-372 build and upload all of it on every call).  Row i of the copy
+// belongs to batch_ids[i]; a row is sent again in full when it holds another sequence, or
+// one whose existing entries were replaced (copy-on-write, free and re-allocation), and only
+// from its old end on when the table merely grew.  The lengths go up every time.  Returns
+// the host copy of the lengths (page-locked, valid until the next call on this cache).
+static int32_t refreshResidentTables(Context* c, Cache* k, const int64_t* ids, int B, int* maxNumBlocks, int* maxLen,
+                                     const uint32_t** hostLens, size_t* uploadedBytes) {
+    Cache::Resident& r = k->res;
+    std::lock_guard<std::mutex> gk(k->mu);
+    auto fail = [&](cudaError_t e) {
+        cudaGetLastError();
+        r.ids.clear(); r.versions.clear(); r.counts.clear();
+        return c->fail(PAM_ERR_COMMAND_EXECUTION, commandExecutionFailed(cudaGetErrorString(e)));
+    };
+    cudaError_t e = cudaSuccess;
+    if (!r.consumed) {
+        e = cudaEventCreateWithFlags(&r.consumed, cudaEventDisableTiming);
+        if (e != cudaSuccess) return fail(e);
+    } else {
+        e = cudaEventSynchronize(r.consumed);        // the staging block is about to be rewritten
+        if (e != cudaSuccess) return fail(e);
+    }
+    std::vector<int32_t> patches;
+    std::vector<uint32_t> lens(static_cast<size_t>(B));
+    for (int attempt = 0; attempt < 2; ++attempt) {
+        patches.clear();
+        if (static_cast<int>(r.ids.size()) < B) {
+            r.ids.resize(static_cast<size_t>(B), INT64_MIN);
+            r.versions.resize(static_cast<size_t>(B), 0);
+            r.counts.resize(static_cast<size_t>(B), 0);
+        }
+        int widest = 1, longest = 0;                  // CABI.swift:308
+        KVResult kr = k->mgr.visit(ids, B, [&](int i, const pam::SequenceView& v) {
+            const size_t si = static_cast<size_t>(i);
+            const bool keep = r.ids[si] == ids[i] && r.versions[si] == v.rewriteVersion && r.counts[si] <= v.numBlocks;
+            for (int col = keep ? r.counts[si] : 0; col < v.numBlocks; ++col) {
+                patches.push_back(i); patches.push_back(col); patches.push_back(v.table[col]);
+            }
+            r.ids[si] = ids[i]; r.versions[si] = v.rewriteVersion; r.counts[si] = v.numBlocks;
+            lens[si] = static_cast<uint32_t>(v.length);
+            widest = std::max(widest, static_cast<int>(v.numBlocks));
+            longest = std::max(longest, static_cast<int>(v.length));
+        });
+        if (!kr.ok()) {
+            r.ids.clear(); r.versions.clear(); r.counts.clear();   // rows up to the unknown id were marked as sent
+            return kvFail(c, kr);
+        }
+        *maxNumBlocks = widest;
+        *maxLen = longest;
+        if (widest <= r.stride && B <= r.rows) break;
+        // a wider or taller table: new device block, every row goes up again
+        cudaStreamSynchronize(c->stream);
+        cudaFree(r.tables);
+        r.tables = nullptr;
+        r.rows = std::max(B, r.rows);
+        r.stride = std::max((widest + widest / 4 + 63) / 64 * 64, r.stride);
+        e = cudaMalloc(reinterpret_cast<void**>(&r.tables), static_cast<size_t>(r.rows) * r.stride * sizeof(int32_t));
+        if (e != cudaSuccess) { r.rows = r.stride = 0; return fail(e); }
+        r.ids.assign(static_cast<size_t>(r.rows), INT64_MIN);
+    }
+    const size_t lenBytes = (static_cast<size_t>(B) * sizeof(uint32_t) + 15) & ~static_cast<size_t>(15);
+    const size_t numPatches = patches.size() / 3;
+    const size_t tableBytes = static_cast<size_t>(B) * r.stride * sizeof(int32_t);
+    // many changes (a new batch): the rows go up whole, zero padded, which is fewer bytes
+    const bool whole = patches.size() * sizeof(int32_t) > tableBytes;
+    const size_t need = lenBytes + (whole ? tableBytes : patches.size() * sizeof(int32_t));
+    if (need > r.pinnedCap) {
+        if (r.pinned) cudaFreeHost(r.pinned);
+        r.pinned = nullptr; r.pinnedCap = 0;
+        const size_t cap = need + need / 2 + 4096;
+        e = cudaHostAlloc(reinterpret_cast<void**>(&r.pinned), cap, cudaHostAllocDefault);
+        if (e != cudaSuccess) return fail(e);
+        r.pinnedCap = cap;
+    }
+    const size_t devNeed = lenBytes + (whole ? 0 : patches.size() * sizeof(int32_t));
+    if (devNeed > r.uploadCap) {
+        cudaStreamSynchronize(c->stream);
+        cudaFree(r.upload);
+        r.upload = nullptr; r.uploadCap = 0;
+        const size_t cap = devNeed + devNeed / 2 + 4096;
+        e = cudaMalloc(reinterpret_cast<void**>(&r.upload), cap);
+        if (e != cudaSuccess) return fail(e);
+        r.uploadCap = cap;
+    }
+    std::memcpy(r.pinned, lens.data(), static_cast<size_t>(B) * sizeof(uint32_t));
+    int32_t* staged = reinterpret_cast<int32_t*>(r.pinned + lenBytes);
+    if (whole) {
+        std::memset(staged, 0, tableBytes);                       // zero padding, CABI.swift:360-363
+        for (size_t t = 0; t < numPatches; ++t)
+            staged[static_cast<size_t>(patches[3 * t]) * r.stride + patches[3 * t + 1]] = patches[3 * t + 2];
+        e = cudaMemcpyAsync(r.upload, r.pinned, lenBytes, cudaMemcpyHostToDevice, c->stream);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(r.tables, staged, tableBytes, cudaMemcpyHostToDevice, c->stream);
+    } else {
+        if (numPatches) std::memcpy(staged, patches.data(), patches.size() * sizeof(int32_t));
+        e = cudaMemcpyAsync(r.upload, r.pinned, need, cudaMemcpyHostToDevice, c->stream);
+        int launches = 0;
+        if (e == cudaSuccess)
+            e = pam::launchPatchTables(r.tables, r.stride, reinterpret_cast<const int32_t*>(reinterpret_cast<unsigned char*>(r.upload) + lenBytes),
+                                       static_cast<int>(numPatches), c->stream, &launches);
+        c->launches += launches;
+    }
+    if (e == cudaSuccess) e = cudaEventRecord(r.consumed, c->stream);
+    if (e != cudaSuccess) return fail(e);
+    *hostLens = reinterpret_cast<const uint32_t*>(r.pinned);
+    *uploadedBytes = need;
+    return 0;
 }
 
 int32_t pam_decode(void* ctx, void* cache, const int64_t* batch_ids, int32_t batch_size, void* q, void* out,
@@ -1296,82 +1543,102 @@ int32_t pam_decode(void* ctx, void* cache, const int64_t* batch_ids, int32_t bat
     DeviceGuard dg(c->device);
     if (c->device < 0) return noGpu(c);
     if (k->bookkeeping) return c->fail(PAM_ERR_INVALID_STATE, "Invalid engine state: cache has no pools");
-    if (batch_size <= 0) return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("batchSize must be positive."));
-    // A host query goes up first, so that its copy runs while the tables are put together.
     const PamLayerSpec layer = layerOf(k, num_heads);
-    const void* qDev = nullptr;
-    bool qInFlight = false;
-    if (num_heads > 0 && !isDevicePointer(q)) {
-        const size_t qBytes = static_cast<size_t>(batch_size) * ioBytesPerToken(layer);
-        if (qBytes > c->qStageCap) {
-            cudaStreamSynchronize(c->stream);
-            if (c->qStage) cudaFree(c->qStage);
-            c->qStage = nullptr;
-            c->qStageCap = 0;
-            if (cudaMalloc(&c->qStage, qBytes) == cudaSuccess) c->qStageCap = qBytes;
-            else cudaGetLastError();
-        }
-        if (c->qStage && cudaMemcpyAsync(c->qStage, q, qBytes, cudaMemcpyHostToDevice, c->stream) == cudaSuccess) {
-            qDev = c->qStage;
-            qInFlight = true;
-        } else {
-            cudaGetLastError();
-        }
-    }
-    // every return below leaves no copy from the caller's memory behind
+    // PagedAttentionEngine.swift:533-580; validateDecode :1916-1933
+    if (!validateLayer(c, layer)) return -1;
+    if (batch_size <= 0) return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("batchSize must be positive."));
+    if (layer.head_dim > 256) return c->fail(PAM_ERR_UNSUPPORTED, "Unsupported paged attention path: headDim above 256.");
+    const double t0 = nowMs();
+    const size_t ioBytes = static_cast<size_t>(batch_size) * ioBytesPerToken(layer);
+    // each argument is looked at once: device memory is used in place; a page-locked host
+    // output is written by the kernels themselves through its device-side address; a host
+    // query, and a pageable host output, go through a device block the context keeps
+    const Placement qAt = placementOf(q), outAt = placementOf(out);
+    auto deviceBlock = [&](void*& block, size_t& cap) -> bool {
+        if (ioBytes <= cap) return true;
+        cudaStreamSynchronize(c->stream);
+        if (block) cudaFree(block);
+        block = nullptr; cap = 0;
+        if (cudaMalloc(&block, ioBytes) != cudaSuccess) { cudaGetLastError(); block = nullptr; return false; }
+        cap = ioBytes;
+        return true;
+    };
+    bool callerMemoryInFlight = false;
+    // every return below leaves no copy from or to the caller's memory behind
     auto failed = [&](int32_t rc) {
-        if (qInFlight) cudaStreamSynchronize(c->stream);
+        if (callerMemoryInFlight) cudaStreamSynchronize(c->stream);
         return rc;
     };
-    // block tables of the batch, each read once from the manager (CABI.swift:306-330, 339-372)
-    int maxNumBlocks = 1;                                         // CABI.swift:308
-    std::vector<int32_t> flat, t;
-    std::vector<size_t> start(static_cast<size_t>(batch_size) + 1, 0);
-    for (int i = 0; i < batch_size; ++i) {
-        KVResult r = k->mgr.blockTable(batch_ids[i], &t);
-        if (!r.ok()) return failed(kvFail(c, r));
-        flat.insert(flat.end(), t.begin(), t.end());
-        start[static_cast<size_t>(i) + 1] = flat.size();
-        maxNumBlocks = std::max(maxNumBlocks, static_cast<int>(t.size()));
+    const void* qDev = q;
+    if (!qAt.onDevice) {
+        // the query goes up first, so that its copy runs while the tables are put together
+        if (!deviceBlock(c->qStage, c->qStageCap)) return c->fail(PAM_ERR_RESOURCE_EXHAUSTED, "GPU resource exhausted: query staging block");
+        cudaError_t e = cudaMemcpyAsync(c->qStage, q, ioBytes, cudaMemcpyHostToDevice, c->stream);
+        if (e != cudaSuccess) { cudaGetLastError(); return c->fail(PAM_ERR_COMMAND_EXECUTION, commandExecutionFailed(cudaGetErrorString(e))); }
+        qDev = c->qStage;
+        callerMemoryInFlight = true;
     }
-    const size_t tableBytes = static_cast<size_t>(batch_size) * maxNumBlocks * sizeof(int32_t);
-    const size_t lenBytes = static_cast<size_t>(batch_size) * sizeof(uint32_t);
-    const size_t lenOff = (tableBytes + 255) & ~static_cast<size_t>(255);
-    // tables and lengths go up from page-locked memory (pageable vectors when that cannot be had)
-    std::vector<unsigned char> pageable;
-    unsigned char* host = static_cast<unsigned char*>(pinnedScratch(c, lenOff + lenBytes));
-    if (!host) {
-        pageable.resize(lenOff + lenBytes);
-        host = pageable.data();
+    void* outDev = outAt.device;
+    if (!outDev) {
+        if (!deviceBlock(c->outStage, c->outStageCap)) return failed(c->fail(PAM_ERR_RESOURCE_EXHAUSTED, "GPU resource exhausted: output staging block"));
+        outDev = c->outStage;
     }
-    int32_t* tables = reinterpret_cast<int32_t*>(host);
-    uint32_t* lens = reinterpret_cast<uint32_t*>(host + lenOff);
-    std::memset(tables, 0, tableBytes);                           // zero padding, CABI.swift:360-363
-    int maxLen = 0;
-    for (int i = 0; i < batch_size; ++i) {
-        const size_t n = start[static_cast<size_t>(i) + 1] - start[static_cast<size_t>(i)];
-        std::memcpy(tables + static_cast<size_t>(i) * maxNumBlocks, flat.data() + start[static_cast<size_t>(i)], n * sizeof(int32_t));
-        int64_t len = 0;
-        k->mgr.sequenceLength(batch_ids[i], &len);
-        lens[i] = static_cast<uint32_t>(len);
-        maxLen = std::max(maxLen, static_cast<int>(len));
-    }
-    PamDecodeRequest rq{};
-    rq.q = qDev ? buf(qDev, static_cast<size_t>(batch_size) * ioBytesPerToken(layer)) : buf(q);
-    rq.output = buf(out);
-    rq.k_pool = buf(k->kPool, k->poolBytes); rq.v_pool = buf(k->vPool, k->poolBytes);
-    rq.block_tables = buf(tables, tableBytes);
-    rq.seq_lengths = buf(lens, lenBytes);
-    rq.batch_size = batch_size; rq.max_num_blocks = maxNumBlocks;
-    rq.layer = layer;
-    rq.k_scale = buf(k->kScale, k->scaleBytes); rq.v_scale = buf(k->vScale, k->scaleBytes);
+    int maxNumBlocks = 1, maxLen = 0;
+    const uint32_t* hostLens = nullptr;
+    size_t uploaded = 0;
+    if (int32_t rc = refreshResidentTables(c, k, batch_ids, batch_size, &maxNumBlocks, &maxLen, &hostLens, &uploaded)) return failed(rc);
     // validateDecode's pool bound uses maxNumBlocks (a lower bound, PagedAttentionEngine.swift:1931)
-    int32_t rc = decodeImpl(c, rq, std::max(maxLen, 1));
-    // the tables, the lengths and a host query are read by async copies: they must be consumed
-    // before this call returns (the synchronous mode has waited already)
-    if (c->async || rc != 0) cudaStreamSynchronize(c->stream);
-    if (rc == 0) c->clearError();
-    return rc;
+    const size_t poolNeed = static_cast<size_t>(maxNumBlocks) * layer.block_size * kvBytesPerToken(layer);
+    if (k->poolBytes < poolNeed) return failed(c->fail(PAM_ERR_BUFFER_TOO_SMALL, bufferTooSmall("K pool", poolNeed, k->poolBytes)));
+
+    pam::DecodeParams p{};
+    p.q = qDev; p.kPool = k->kPool; p.vPool = k->vPool;
+    p.tables = k->res.tables;
+    p.lens = k->res.upload;
+    p.out = outDev;
+    p.kScale = k->kScale; p.vScale = k->vScale;
+    p.batch = batch_size; p.heads = num_heads; p.kvHeads = k->kvHeads; p.headDim = k->headDim;
+    p.blockSize = k->blockSize; p.maxNumBlocks = k->res.stride; p.window = c->defaultWindow; p.dtype = k->dtype;   // :1028
+    p.maxContext = std::max(maxLen, 1);
+    p.poolBlocks = k->maxBlocks;
+    p.hostLens = hostLens;
+    p.planCache = c->planCache;
+    p.counters = c->mergeCounters;
+    p.countersCap = c->mergeCountersCap;
+    c->arena.reset(c->stream);
+    size_t tempBytes = 0;
+    int32_t rc = withRetry(c, "decodeFlat", [&]() -> cudaError_t {
+        tempBytes = pam::decodeWorkspaceBytes(p, c->smCount, c->stream);
+        if (tempBytes) {
+            p.workspace = static_cast<float*>(c->arena.take(tempBytes));
+            p.workspaceBytes = tempBytes;
+            if (!p.workspace) return cudaErrorMemoryAllocation;
+        }
+        int launches = 0;
+        cudaError_t e = pam::launchDecode(p, c->smCount, c->stream, &launches);
+        c->launches += launches;
+        if (e == cudaSuccess && outDev == c->outStage) {
+            e = cudaMemcpyAsync(out, outDev, ioBytes, cudaMemcpyDeviceToHost, c->stream);
+            callerMemoryInFlight = true;
+        }
+        return e;
+    });
+    if (rc != 0) {
+        if (c->mergeCounters) cudaMemsetAsync(c->mergeCounters, 0, static_cast<size_t>(c->mergeCountersCap) * sizeof(int), c->stream);
+        cudaStreamSynchronize(c->stream);
+        callerMemoryInFlight = false;
+        if (!c->graceful) return rc;
+        if (outAt.onDevice) cudaMemsetAsync(out, 0, ioBytes, c->stream);       // :536-542
+        else std::memset(out, 0, ioBytes);
+        c->clearError();
+    }
+    // host memory of the caller's (the query on its way up, the output on its way down or
+    // being written by the kernels) must be settled before this call returns; the
+    // synchronous mode has waited already
+    if (c->async && (!qAt.onDevice || !outAt.onDevice)) cudaStreamSynchronize(c->stream);
+    c->stats = PamStats{PAM_OP_DECODE, batch_size, 0, maxNumBlocks, static_cast<int64_t>(tempBytes), 0, nowMs() - t0};   // :568-577
+    c->clearError();
+    return 0;
 }
 
 int32_t pamc_prefill(void* ctx, const PamPrefillRequest* request, int32_t chunk_size) {
@@ -1443,7 +1710,7 @@ int32_t pamc_fused_prefill(void* ctx, const PamFusedPrefillRequest* request, voi
     const PamLayerSpec& l = rq.layer;
     const size_t numBlocks = (static_cast<size_t>(rq.seq_len) + l.block_size - 1) / l.block_size;
     if (!requireBuffer(c, rq.block_table, "blockTable", numBlocks * sizeof(int32_t))) return -1;
-    if (!requireBuffer(c, rq.output, "output", static_cast<size_t>(rq.seq_len) * qBytesPerToken(l))) return -1;
+    if (!requireIoBuffer(c, rq.output, "output", static_cast<size_t>(rq.seq_len) * qBytesPerToken(l), static_cast<size_t>(rq.seq_len) * ioBytesPerToken(l))) return -1;
     Cache* k = cache ? asCache(cache) : nullptr;
     if (l.data_type == PAM_DTYPE_FP8 && !k)
         return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("FP8 fused prefill needs the cache handle that owns the scale buffers."));
@@ -1520,6 +1787,57 @@ int32_t pam_prefill(void* ctx, void* cache, int64_t id, void* q, void* out, int3
     return rc;
 }
 
+// ------------------------------------------------------------------ head-sharded outputs
+
+int32_t pamc_comm_unique_id(void* out_128_bytes) { return pam::commUniqueId(out_128_bytes) == 0 ? 0 : -1; }
+
+void* pamc_comm_create(void* ctx, const void* unique_id_128_bytes, int32_t rank, int32_t num_ranks) {
+    if (!ctx) return nullptr;
+    Context* c = asCtx(ctx);
+    std::lock_guard<std::mutex> g(c->mu);
+    DeviceGuard dg(c->device);
+    if (c->device < 0) { noGpu(c); return nullptr; }
+    std::string why;
+    pam::HeadComm* comm = pam::commCreate(unique_id_128_bytes, rank, num_ranks, c->device, &why);
+    if (!comm) { c->fail(PAM_ERR_DEVICE_INIT, "Metal device or command queue could not be initialized: " + why); return nullptr; }
+    c->clearError();
+    return comm;
+}
+
+void pamc_comm_destroy(void* comm) { pam::commDestroy(static_cast<pam::HeadComm*>(comm)); }
+
+int32_t pamc_allgather_heads(void* ctx, void* comm, const void* local, void* full, int32_t rows, int32_t heads_local,
+                             int32_t head_dim, int32_t data_type) {
+    if (!ctx || !comm || !local || !full) return -1;
+    Context* c = asCtx(ctx);
+    std::lock_guard<std::mutex> g(c->mu);
+    DeviceGuard dg(c->device);
+    if (c->device < 0) return noGpu(c);
+    if (rows <= 0 || heads_local <= 0 || head_dim <= 0 || !validDtype(data_type))
+        return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("rows, heads and headDim must be positive."));
+    pam::HeadComm* hc = static_cast<pam::HeadComm*>(comm);
+    const size_t slice = static_cast<size_t>(heads_local) * head_dim * pam::ioBytes(data_type);
+    if (slice % 16 != 0)
+        return c->fail(PAM_ERR_UNSUPPORTED, "Unsupported paged attention path: a GPU's head slice must be a multiple of 16 bytes.");
+    if (!isDevicePointer(local) || !isDevicePointer(full))
+        return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("the gathered tensors must be device memory."));
+    c->arena.reset(c->stream);
+    // A collective is not retried: the other ranks would not take part in the second attempt.
+    std::string why;
+    void* staging = pam::commSize(hc) > 1 ? c->arena.take(static_cast<size_t>(pam::commSize(hc)) * rows * slice) : const_cast<void*>(local);
+    if (!staging) return c->fail(PAM_ERR_RESOURCE_EXHAUSTED, "GPU resource exhausted: staging block of the all-gather");
+    int launches = 0;
+    cudaError_t e = pam::launchAllGatherHeads(hc, local, staging, full, rows, slice, c->stream, &launches, &why);
+    c->launches += launches;
+    if (e == cudaSuccess && !c->async) e = cudaStreamSynchronize(c->stream);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return c->fail(PAM_ERR_COMMAND_EXECUTION, commandExecutionFailed(why.empty() ? cudaGetErrorString(e) : why));
+    }
+    c->clearError();
+    return 0;
+}
+
 // ------------------------------------------------------------------ scheduler
 
 void* pamc_sched_create(int32_t max_batch_size, int32_t max_sequences) { return new Sched(max_batch_size, max_sequences); }
@@ -1566,6 +1884,10 @@ struct Inference {
     std::vector<PamLayerSpec> layers;
     int maxBatch = 0;
     bool incrementalPreemption = false;
+    bool batchedPrefill = false;                      // one prefill launch per layer and step (not in the reference)
+    int prefillTokenBudget = 0;                       // prompt rows per step with batchedPrefill; 0: no limit
+    std::map<int64_t, int> prefillProgress;           // rows done of a prompt that spans steps
+    long long prefillLaunchSets = 0;                  // prefill launch sets (one per layer set) issued so far
     std::set<int64_t> prefilled;                      // :29
     long long totalTokens = 0;                        // :31
     int stepCount = 0;                                // :34
@@ -1627,6 +1949,7 @@ static int32_t inferBuffers(Inference* inf, size_t rows) {
 static void inferForget(Inference* inf, int64_t id) {
     inf->cache->mgr.freeSequence(id);
     inf->prefilled.erase(id);
+    inf->prefillProgress.erase(id);
 }
 
 // ensureBlocksAvailable (PagedAttentionInference.swift:280-299).  The reference reads the
@@ -1660,7 +1983,9 @@ static void inferComplete(Inference* inf, int64_t id) {     // :108-114
     inferForget(inf, id);
 }
 
-static int32_t inferPrefill(Inference* inf, const pam::SchedulerSequence& seq) {     // :169-220
+// The block bookkeeping of a prompt (:172-186): room for its blocks, a fresh table, the
+// prompt's tokens appended.
+static int32_t inferReservePrompt(Inference* inf, const pam::SchedulerSequence& seq) {
     Cache* k = inf->cache;
     const int needed = (seq.promptLength + k->blockSize - 1) / k->blockSize;
     if (int32_t rc = inferEnsureBlocks(inf, needed)) return rc;
@@ -1672,6 +1997,113 @@ static int32_t inferPrefill(Inference* inf, const pam::SchedulerSequence& seq) {
     if (!r.ok()) return inferKvFail(inf, r);
     r = k->mgr.appendTokens(seq.id, seq.promptLength, nullptr, 0, nullptr);
     if (!r.ok()) return inferKvFail(inf, r);
+    return 0;
+}
+
+// With batchedPrefill: the prompts of a step that are not prefilled yet go through the same
+// bookkeeping as in the reference, one after the other in batch order (so block tables,
+// preemptions and errors are those of the reference), but their attention rows are issued
+// together, one launch per layer, instead of one launch set per sequence
+// (PagedAttentionInference.swift:172-219).  With a token budget a step takes at most that
+// many prompt rows: a long prompt is prefilled in chunks over several steps (rows
+// [done, done + n) against keys [0, done + n)), and prompts that do not fit wait.
+struct PendingPrefill { pam::SchedulerSequence seq; int start, rows; };
+
+static int32_t inferFlushPrefill(Inference* inf, std::vector<PendingPrefill>& pend) {
+    if (pend.empty()) return 0;
+    Cache* k = inf->cache;
+    const int n = static_cast<int>(pend.size());
+    size_t totalRows = 0;
+    int maxNumBlocks = 1;
+    std::vector<std::vector<int32_t>> rowsOf(static_cast<size_t>(n));
+    for (int i = 0; i < n; ++i) {
+        KVResult r = k->mgr.blockTable(pend[static_cast<size_t>(i)].seq.id, &rowsOf[static_cast<size_t>(i)]);
+        if (!r.ok()) return inferKvFail(inf, r);
+        maxNumBlocks = std::max(maxNumBlocks, static_cast<int>(rowsOf[static_cast<size_t>(i)].size()));
+        totalRows += static_cast<size_t>(pend[static_cast<size_t>(i)].rows);
+    }
+    std::vector<int32_t> tables(static_cast<size_t>(n) * maxNumBlocks, 0);
+    std::vector<PrefillSeq> seqs;
+    for (int i = 0; i < n; ++i) {
+        std::copy(rowsOf[static_cast<size_t>(i)].begin(), rowsOf[static_cast<size_t>(i)].end(), tables.begin() + static_cast<std::ptrdiff_t>(i) * maxNumBlocks);
+        const PendingPrefill& pp = pend[static_cast<size_t>(i)];
+        seqs.push_back(PrefillSeq{pp.start + pp.rows, pp.start, pp.rows});
+    }
+    if (int32_t rc = inferBuffers(inf, totalRows)) return rc;
+    Context* c = inf->c;
+    int32_t rc = 0;
+    {
+        std::lock_guard<std::mutex> g(c->mu);
+        DeviceGuard dg(c->device);
+        const bool wasAsync = c->async;
+        c->async = true;                                   // the layers are enqueued back to back, one wait at the end
+        for (size_t l = 0; l < inf->layers.size() && rc == 0; ++l) {
+            const size_t bytes = totalRows * ioBytesPerToken(inf->layers[l]);
+            rc = prefillImpl(c, inf->layers[l], buf(inf->q[l], bytes), buf(k->kPool, k->poolBytes), buf(k->vPool, k->poolBytes),
+                             buf(tables.data(), tables.size() * sizeof(int32_t)), buf(inf->out[l], bytes),
+                             buf(k->kScale, k->scaleBytes), buf(k->vScale, k->scaleBytes), seqs, maxNumBlocks, true, "blockTables");
+        }
+        c->async = wasAsync;
+        const int32_t src = syncContext(c);                // `tables` is read by async copies: wait in either mode
+        if (rc == 0) rc = src;
+        if (rc == 0) c->clearError();
+    }
+    if (rc != 0) return rc;
+    inf->prefillLaunchSets += 1;
+    for (const PendingPrefill& pp : pend) {
+        const int done = pp.start + pp.rows;
+        if (done >= pp.seq.promptLength) {
+            inf->prefillProgress.erase(pp.seq.id);
+            inf->sched->s.markPrefilled(pp.seq.id);
+            inf->prefilled.insert(pp.seq.id);
+            inf->totalTokens += pp.seq.promptLength;
+        } else {
+            inf->prefillProgress[pp.seq.id] = done;
+        }
+    }
+    pend.clear();
+    return 0;
+}
+
+static int32_t inferPrefillBatched(Inference* inf, const std::vector<pam::SchedulerSequence>& prefill) {
+    std::vector<PendingPrefill> pend;
+    int budget = inf->prefillTokenBudget > 0 ? inf->prefillTokenBudget : INT_MAX;
+    for (const auto& sq : prefill) {
+        if (budget <= 0) break;                            // the others wait for the next step
+        auto at = inf->prefillProgress.find(sq.id);
+        int done = at == inf->prefillProgress.end() ? -1 : at->second;
+        if (done < 0) {
+            if (int32_t rc = inferReservePrompt(inf, sq)) {
+                // what was prepared before the failing prompt is issued, as the reference
+                // would have done by then; the step still fails
+                inferFlushPrefill(inf, pend);
+                return rc;
+            }
+            // a preemption inside the reservation may have taken sequences of this step
+            pend.erase(std::remove_if(pend.begin(), pend.end(), [&](const PendingPrefill& pp) {
+                           int64_t len = 0;
+                           return !inf->cache->mgr.sequenceLength(pp.seq.id, &len).ok();
+                       }), pend.end());
+            done = 0;
+        }
+        const int rows = std::min(sq.promptLength - done, budget);
+        if (sq.promptLength <= 0) {
+            // the reference's prefill of an empty prompt fails its validation (seqLen must be positive)
+            inferFlushPrefill(inf, pend);
+            std::lock_guard<std::mutex> g(inf->c->mu);
+            return inf->c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("seqLen must be positive."));
+        }
+        pend.push_back(PendingPrefill{sq, done, rows});
+        inf->prefillProgress[sq.id] = done;
+        budget -= rows;
+    }
+    return inferFlushPrefill(inf, pend);
+}
+
+static int32_t inferPrefill(Inference* inf, const pam::SchedulerSequence& seq) {     // :169-220
+    Cache* k = inf->cache;
+    if (int32_t rc = inferReservePrompt(inf, seq)) return rc;
+    KVResult r;
     std::vector<int32_t> table;
     r = k->mgr.blockTable(seq.id, &table);
     if (!r.ok()) return inferKvFail(inf, r);
@@ -1688,6 +2120,7 @@ static int32_t inferPrefill(Inference* inf, const pam::SchedulerSequence& seq) {
         rq[l].k_scale = buf(k->kScale, k->scaleBytes); rq[l].v_scale = buf(k->vScale, k->scaleBytes);
     }
     if (int32_t rc = pamc_prefill_layers(inf->c, rq.data(), static_cast<int32_t>(rq.size()))) return rc;
+    inf->prefillLaunchSets += 1;
     inf->sched->s.markPrefilled(seq.id);
     inf->prefilled.insert(seq.id);
     inf->totalTokens += seq.promptLength;
@@ -1757,8 +2190,13 @@ static int32_t inferStep(Inference* inf, std::vector<int64_t>* batch) {      // 
         if (!inf->sched->s.get(id, &sq)) continue;
         (inf->prefilled.count(id) ? decode : prefill).push_back(sq);
     }
-    for (auto& sq : prefill)
-        if (int32_t rc = inferPrefill(inf, sq)) return rc;
+    if (inf->batchedPrefill) {
+        if (!prefill.empty())
+            if (int32_t rc = inferPrefillBatched(inf, prefill)) return rc;
+    } else {
+        for (auto& sq : prefill)
+            if (int32_t rc = inferPrefill(inf, sq)) return rc;
+    }
     if (!decode.empty())
         if (int32_t rc = inferDecode(inf, decode)) return rc;
     inf->stepCount += 1;
@@ -1837,6 +2275,19 @@ void pamc_infer_set_token_callback(void* infer, pamc_token_fn fn, void* user) {
     Inference* inf = static_cast<Inference*>(infer);
     std::lock_guard<std::mutex> g(inf->mu);
     inf->onToken = fn; inf->onTokenUser = user;
+}
+void pamc_infer_set_batched_prefill(void* infer, int32_t on, int32_t token_budget) {
+    if (!infer) return;
+    Inference* inf = static_cast<Inference*>(infer);
+    std::lock_guard<std::mutex> g(inf->mu);
+    inf->batchedPrefill = on != 0;
+    inf->prefillTokenBudget = std::max(token_budget, 0);
+}
+int64_t pamc_infer_prefill_launch_sets(void* infer) {
+    if (!infer) return -1;
+    Inference* inf = static_cast<Inference*>(infer);
+    std::lock_guard<std::mutex> g(inf->mu);
+    return inf->prefillLaunchSets;
 }
 void pamc_infer_set_incremental_preemption(void* infer, int32_t on) {
     if (!infer) return;

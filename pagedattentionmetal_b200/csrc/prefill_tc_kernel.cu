@@ -78,18 +78,7 @@ constexpr int kHalfBytes = kTileBytes / 2;             // one 64-column block
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;
 constexpr int kShortRowKeys = 256;
-constexpr long long kWaitCycles = 400000000LL;         // ~0.2 s
-
-#ifdef PAM_PREFILL_TRACE
-// Instrumented build only (-DPAM_PREFILL_TRACE): every CTA leaves the wall-clock time and the
-// SM cycle count of its start and end in global memory, for the per-CTA cost model.
-__device__ unsigned long long gCtaTimes[4 * 256];      // start and end of every CTA: nanoseconds, then SM cycles
-__device__ __forceinline__ unsigned long long globalTimerNs() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#endif
+constexpr long long kWaitCycles = 400000000LL;         // ~0.2 s: the bound of a wait unless the launch gives its own
 
 struct Smem {
     // tiles first: each 1024-byte aligned (swizzle atoms)
@@ -145,13 +134,13 @@ __device__ __forceinline__ bool mbarTrySleep(unsigned long long* bar, uint32_t p
 }
 // Bounded wait.  Returns false (and marks the CTA dead) when the barrier did
 // not complete in time or another thread of the CTA already gave up.
-__device__ __forceinline__ bool mbarWait(unsigned long long* bar, uint32_t parity, int* dead, int* errFlag, int where) {
+__device__ __forceinline__ bool mbarWait(unsigned long long* bar, uint32_t parity, int* dead, int* errFlag, long long limit, int where) {
     if (mbarTry(bar, parity)) return true;
     const long long t0 = clock64();
     while (true) {
         if (mbarTrySleep(bar, parity, 20000u)) return true;
         if (*reinterpret_cast<volatile int*>(dead)) return false;
-        if (clock64() - t0 > kWaitCycles) {
+        if (clock64() - t0 > limit) {
             *reinterpret_cast<volatile int*>(dead) = 1;
             atomicCAS(errFlag, 0, where);
             return false;
@@ -522,12 +511,6 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         return;
     }
 
-#ifdef PAM_PREFILL_TRACE
-    if (threadIdx.x == 0 && blockIdx.x < 256) {
-        gCtaTimes[4 * blockIdx.x] = globalTimerNs();
-        gCtaTimes[4 * blockIdx.x + 2] = clock64();
-    }
-#endif
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int numTiles = (p.maxQLen + kRows - 1) / kRows;
     const int numPairs = p.pairHeads ? numTiles : (numTiles + 1) / 2;      // item rows of the launch
@@ -564,6 +547,7 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     auto tmemS = [&](int grp) { return tmem + 128u * static_cast<uint32_t>(grp); };
     auto tmemO = [&](int grp) { return tmem + 256u + 128u * static_cast<uint32_t>(grp); };
     const bool live = *reinterpret_cast<volatile int*>(&s->dead) == 0;
+    const long long waitLimit = p.waitCycles > 0 ? p.waitCycles : kWaitCycles;
 
     // Row of the pool (block * kv_heads * block_size space) of the 16-token piece `lane`
     // of key tile j of an item; lanes 0-7 of a producer warp fetch one piece each.
@@ -589,7 +573,7 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         while (c.valid && ok) {
             const int st = c.g % kKStages;
             const int row = lane < kKeys / 16 ? pieceRow(c.it, c.j) : 0;
-            if (c.g >= kKStages) ok = mbarWait(&s->kEmpty[st], ((c.g / kKStages) - 1) & 1, &s->dead, errFlag, 1);
+            if (c.g >= kKStages) ok = mbarWait(&s->kEmpty[st], ((c.g / kKStages) - 1) & 1, &s->dead, errFlag, waitLimit, 1);
             ok = __all_sync(0xFFFFFFFFu, ok);
             if (!ok) break;
             if (lane == 0) mbarExpectTx(&s->kFull[st], kTileBytes);
@@ -610,12 +594,15 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         while (c.valid && ok) {
             const int st = c.g % kVStages;
             const int row = lane < kKeys / 16 ? pieceRow(c.it, c.j) : 0;
-            if (c.g >= kVStages) ok = mbarWait(&s->vEmpty[st], ((c.g / kVStages) - 1) & 1, &s->dead, errFlag, 13);
+            if (c.g >= kVStages) ok = mbarWait(&s->vEmpty[st], ((c.g / kVStages) - 1) & 1, &s->dead, errFlag, waitLimit, 13);
             ok = __all_sync(0xFFFFFFFFu, ok);
             if (!ok) break;
-            if (lane == 0) mbarExpectTx(&s->vFull[st], kTileBytes);
+            // (test launches only: the CTA's first value tile is never fetched, so that the wait
+            // for it runs out; see pamc_test_starve_prefill)
+            const bool starved = p.starveV != 0 && c.g == 0;
+            if (lane == 0 && !starved) mbarExpectTx(&s->vFull[st], kTileBytes);
             __syncwarp();
-            if (lane < kKeys / 16) {
+            if (lane < kKeys / 16 && !starved) {
                 tmaLoad2d(s->v[st] + lane * 2048, &mapV, &s->vFull[st], 0, row);
                 tmaLoad2d(s->v[st] + kHalfBytes + lane * 2048, &mapV, &s->vFull[st], 64, row);
             }
@@ -652,8 +639,8 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         // S = Q_x K^T for tile j (global tile gTile) of item `it`
         auto issueQK = [&](int x, const Item& it, int j, int gTile) {
             const int st = gTile % kKStages;
-            if (j == 0) ok = mbarWait(&s->qFull[x], (x ? items1 : items0) & 1, &s->dead, errFlag, 2);
-            if (ok) ok = mbarWait(&s->kFull[st], (gTile / kKStages) & 1, &s->dead, errFlag, 3);
+            if (j == 0) ok = mbarWait(&s->qFull[x], (x ? items1 : items0) & 1, &s->dead, errFlag, waitLimit, 2);
+            if (ok) ok = mbarWait(&s->kFull[st], (gTile / kKStages) & 1, &s->dead, errFlag, waitLimit, 3);
             ok = __all_sync(0xFFFFFFFFu, ok);
             if (!ok) return;
             tcFenceAfter();
@@ -706,11 +693,11 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             for (int x = 0; x < 2; ++x) {
                 if (!(c.j < c.it.nTg[x]) || !ok) continue;
                 int& steps = x ? steps1 : steps0;
-                ok = mbarWait(&s->pFull[x], steps & 1, &s->dead, errFlag, 5);
-                if (ok) ok = mbarWait(&s->vFull[st], (c.g / kVStages) & 1, &s->dead, errFlag, 6);
+                ok = mbarWait(&s->pFull[x], steps & 1, &s->dead, errFlag, waitLimit, 5);
+                if (ok) ok = mbarWait(&s->vFull[st], (c.g / kVStages) & 1, &s->dead, errFlag, waitLimit, 6);
                 // the accumulator is free once the output of the group's item before was read from it
                 const int itemsX = x ? items1 : items0;
-                if (ok && c.j == 0 && itemsX >= 2) ok = mbarWait(&s->oEmpty[x], (itemsX - 2) & 1, &s->dead, errFlag, 15);
+                if (ok && c.j == 0 && itemsX >= 2) ok = mbarWait(&s->oEmpty[x], (itemsX - 2) & 1, &s->dead, errFlag, waitLimit, 15);
                 ok = __all_sync(0xFFFFFFFFu, ok);
                 if (!ok) break;
                 tcFenceAfter();
@@ -778,8 +765,8 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             for (int x = 0; x < 2; ++x) {
                 if (it.nTg[x] == 0 || it.rowsValid[x] == 0 || !ok) continue;
                 int& cnt = x ? cnt1 : cnt0;
-                ok = mbarWait(&s->lReady[x], cnt & 1, &s->dead, errFlag, 17);
-                if (ok) ok = mbarWait(&s->oFull[x], cnt & 1, &s->dead, errFlag, 10);
+                ok = mbarWait(&s->lReady[x], cnt & 1, &s->dead, errFlag, waitLimit, 17);
+                if (ok) ok = mbarWait(&s->oFull[x], cnt & 1, &s->dead, errFlag, waitLimit, 10);
                 ok = __all_sync(0xFFFFFFFFu, ok);
                 if (!ok) break;
                 tcFenceAfter();
@@ -900,7 +887,7 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             for (int j = 0; j < nT && ok; ++j, ++steps) {
                 const int k0 = (it.tileLo + j) * kKeys;
                 const bool edge = k0 < it.ws || k0 + kKeys > it.seqLen || (p.causal && k0 + kKeys - 1 > firstPos);
-                ok = mbarWait(&s->sFull[x], steps & 1, &s->dead, errFlag, 7);
+                ok = mbarWait(&s->sFull[x], steps & 1, &s->dead, errFlag, waitLimit, 7);
                 if (!ok) break;
                 tcFenceAfter();
                 // S of the item's last tile is there, so its query tile is no longer read
@@ -974,7 +961,7 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                     // rows of V past the end of the sequence may hold anything: zero them (both
                     // groups may, with the same zeros)
                     const int gt = gBase + j, st = gt % kVStages;
-                    ok = mbarWait(&s->vFull[st], (gt / kVStages) & 1, &s->dead, errFlag, 9);
+                    ok = mbarWait(&s->vFull[st], (gt / kVStages) & 1, &s->dead, errFlag, waitLimit, 9);
                     if (!ok) break;
                     if (k0 + t >= it.seqLen) {
 #pragma unroll
@@ -1001,12 +988,6 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
 done:
     tcFenceBefore();
     __syncthreads();
-#ifdef PAM_PREFILL_TRACE
-    if (threadIdx.x == 0 && blockIdx.x < 256) {
-        gCtaTimes[4 * blockIdx.x + 1] = globalTimerNs();
-        gCtaTimes[4 * blockIdx.x + 3] = clock64();
-    }
-#endif
     if (warp == kMmaWarp) {
         tcFenceAfter();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
@@ -1102,11 +1083,3 @@ cudaError_t launchPrefillTensor(const PrefillParams& p, int totalRows, int* errF
 }
 
 }  // namespace pam
-
-#ifdef PAM_PREFILL_TRACE
-extern "C" int pamc_debug_cta_times(unsigned long long* out) {
-    cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(out, pam::gCtaTimes, sizeof(unsigned long long) * 1024);
-    return 1024;
-}
-#endif

@@ -196,6 +196,52 @@ class PagedAttentionEngine:
     def injectLaunchFailures(self, n: int) -> None:
         lib.pamc_inject_launch_failures(self._ctx, n)
 
+    def setWaitLimit(self, smCycles: int) -> None:
+        """Bound of every wait inside the tensor-core prefill kernel, in SM clock
+        cycles (0: the default, about 0.2 s); see pamc_set_wait_limit."""
+        _check(self._ctx, lib.pamc_set_wait_limit(self._ctx, int(smCycles)))
+
+    def testStarvePrefill(self, launches: int) -> None:
+        """The next `launches` tensor-core prefill launches never fetch their first
+        value tile, so the wait for it runs out (see pamc_test_starve_prefill)."""
+        _check(self._ctx, lib.pamc_test_starve_prefill(self._ctx, int(launches)))
+
+    @staticmethod
+    def decodePath(request: PagedAttentionDecodeRequest) -> int:
+        """1: the split-K kernels would run this request, 0: the general kernel
+        (pamc_decode_path; nothing is launched)."""
+        r = _cabi.PamDecodeRequest(_buf(request.q), _buf(request.kPool), _buf(request.vPool),
+                                   _buf(request.blockTables), _buf(request.seqLengths), _buf(request.output),
+                                   request.batchSize, request.maxNumBlocks, _layer(request.layer),
+                                   _buf(request.kScaleBuffer), _buf(request.vScaleBuffer))
+        return int(lib.pamc_decode_path(C.byref(r)))
+
+    # -- outputs of a cache sharded by KV head over several GPUs (no reference counterpart) --
+    @staticmethod
+    def makeCommId() -> bytes:
+        """128 bytes that rank 0 makes and every rank passes to joinComm."""
+        raw = C.create_string_buffer(128)
+        if lib.pamc_comm_unique_id(raw) != 0:
+            raise PagedAttentionError(1, "NCCL could not be loaded")
+        return raw.raw
+
+    def joinComm(self, commId: bytes, rank: int, numRanks: int):
+        raw = C.create_string_buffer(bytes(commId), 128)
+        h = lib.pamc_comm_create(self._ctx, raw, rank, numRanks)
+        if not h:
+            _raise(self._ctx)
+        return h
+
+    @staticmethod
+    def leaveComm(comm) -> None:
+        lib.pamc_comm_destroy(comm)
+
+    def allGatherHeads(self, comm, local, full, rows: int, headsLocal: int, headDim: int, dataType) -> None:
+        """[rows][headsLocal][headDim] of every rank into [rows][headsLocal * ranks][headDim]
+        on every rank (pamc_allgather_heads; a collective call)."""
+        _check(self._ctx, lib.pamc_allgather_heads(self._ctx, comm, _cabi.address(local), _cabi.address(full), rows,
+                                                    headsLocal, headDim, int(dataType)))
+
     # -- operations --
     def prefill(self, request: PagedAttentionPrefillRequest, chunkSize: int = 0) -> None:
         """PagedAttentionEngine.swift:405-418 (request form) and :713-768 (chunk loop)."""
@@ -527,6 +573,23 @@ class KVCacheManager:
                                   s.fragmentation_ratio, s.prefix_cache_hits, s.prefix_cache_entries,
                                   s.shared_blocks, BlockEvictionPolicy(s.eviction_policy))
 
+    def setHygiene(self, on: bool) -> None:
+        """Forget a block's prefix hashes when it is freed, and make an append that
+        runs out of blocks change nothing (see pamc_cache_set_hygiene).  Off by
+        default: the reference does neither."""
+        lib.pamc_cache_set_hygiene(self._h, 1 if on else 0)
+
+    @staticmethod
+    def blockHashes(tokenIds: Sequence[int], blockSize: int, seed: int = 0) -> list:
+        """Chained content hashes of the full blocks of a token sequence, usable as
+        appendTokens' blockHashes (see pamc_block_hashes)."""
+        n = len(tokenIds)
+        ids = (C.c_int32 * max(n, 1))(*[int(t) for t in tokenIds])
+        full = n // blockSize
+        out = (C.c_uint64 * max(full, 1))()
+        got = lib.pamc_block_hashes(ids, n, blockSize, seed, out, full)
+        return [int(out[i]) for i in range(got)]
+
     def drainCopyOnWriteLog(self) -> list:
         out = (C.c_int32 * 2048)()
         n = lib.pamc_cache_drain_cow_log(self._h, out, 1024)
@@ -725,6 +788,15 @@ class PagedAttentionInference:
         """Pause one victim at a time under memory pressure instead of every
         running sequence (see pamc_infer_set_incremental_preemption)."""
         lib.pamc_infer_set_incremental_preemption(self._h, 1 if on else 0)
+
+    def setBatchedPrefill(self, on: bool, tokenBudget: int = 0) -> None:
+        """One prefill launch per layer and step for all prompts of the step, with an
+        optional bound on the prompt rows per step (see pamc_infer_set_batched_prefill)."""
+        lib.pamc_infer_set_batched_prefill(self._h, 1 if on else 0, int(tokenBudget))
+
+    @property
+    def prefillLaunchSets(self) -> int:
+        return int(lib.pamc_infer_prefill_launch_sets(self._h))
 
     def addRequest(self, promptTokenCount: int, maxNewTokens: int) -> int:   # :103-105
         return int(lib.pamc_infer_add_request(self._h, promptTokenCount, maxNewTokens))

@@ -277,3 +277,94 @@ def test_scheduler_random_matches_oracle(seed):
 def lib_count(s, status):
     from pagedattentionmetal_b200._cabi import lib
     return lib.pamc_sched_count(s._h, status)
+
+
+# ---- the two fixes of reference behaviour behind pamc_cache_set_hygiene (default: off)
+
+def test_stale_prefix_hash_is_kept_by_default_and_dropped_with_hygiene():
+    # KVCacheManager.swift:216-239 frees blocks without touching the prefix map, so a later
+    # appendTokens with the same hash is handed a block that now belongs to someone else.
+    for hygiene in (False, True):
+        m = new_manager(4, 16)
+        m.setHygiene(hygiene)
+        m.allocateSequence(1)
+        m.appendTokens(1, 16, [111])
+        shared = m.getBlockTable(1)[0]
+        m.freeSequence(1)
+        assert m.memoryStats().prefixCacheEntries == (0 if hygiene else 1)
+        m.allocateSequence(2)
+        m.appendTokens(2, 64)                              # takes every block, the freed one included
+        assert shared in m.getBlockTable(2)
+        m.allocateSequence(3)
+        if hygiene:
+            with pytest.raises(pam.KVCacheError) as e:     # no hit: it needs a block and there is none
+                m.appendTokens(3, 16, [111])
+            assert e.value.case == "outOfMemory"
+        else:
+            # the reference's OOM check comes before the hit is looked up (:142-146)
+            with pytest.raises(pam.KVCacheError):
+                m.appendTokens(3, 16, [111])
+            m.freeSequence(2)
+            m.allocateSequence(4)
+            m.appendTokens(4, 16)                          # block `shared` may be handed out again ...
+            m.appendTokens(3, 16, [111])                   # ... and the stale hash still points at it
+            assert m.memoryStats().prefixCacheHits == 1
+
+
+def test_hygiene_keeps_hashes_of_blocks_that_are_still_referenced():
+    m = new_manager(8, 16)
+    m.setHygiene(True)
+    for sid in (1, 2):
+        m.allocateSequence(sid)
+        m.appendTokens(sid, 32, [5, 6])
+    assert m.getBlockTable(1) == m.getBlockTable(2) and m.memoryStats().prefixCacheHits == 2
+    m.freeSequence(1)                                      # sequence 2 still holds both blocks
+    assert m.memoryStats().prefixCacheEntries == 2
+    m.allocateSequence(3)
+    m.appendTokens(3, 32, [5, 6])
+    assert m.getBlockTable(3) == m.getBlockTable(2)
+    m.freeSequence(2)
+    m.freeSequence(3)
+    assert m.memoryStats().prefixCacheEntries == 0 and m.availableBlocks == 8
+
+
+def test_append_that_runs_out_of_blocks_after_copy_on_write():
+    # A shared, partly filled last block plus an append the pool cannot hold.  The reference
+    # copies the block first and fails afterwards (KVCacheManager.swift:134-146): the fresh
+    # block is lost and the shared block loses a reference.  With hygiene nothing changes.
+    for hygiene in (False, True):
+        m = new_manager(3, 16)
+        m.setHygiene(hygiene)
+        m.allocateSequence(1)
+        m.appendTokens(1, 8, [9])                          # block 0, half full, hashed
+        m.allocateSequence(2)
+        m.appendTokens(2, 8, [9])                          # shares block 0
+        assert m.memoryStats().sharedBlocks == 1 and m.availableBlocks == 2
+        with pytest.raises(pam.KVCacheError) as e:
+            m.appendTokens(2, 8 + 3 * 16)                  # copy of block 0 + three more blocks: too many
+        assert e.value.case == "outOfMemory"
+        assert m.getBlockTable(2) == [0] and m.getSequenceLength(2) == 8
+        if hygiene:
+            assert m.availableBlocks == 2 and m.memoryStats().sharedBlocks == 1
+            assert m.drainCopyOnWriteLog() == []
+        else:
+            assert m.availableBlocks == 1 and m.memoryStats().sharedBlocks == 0
+            assert m.drainCopyOnWriteLog() == [(0, 1)]
+
+
+def test_block_hashes_chain_over_the_prefix():
+    a = list(range(100, 164))
+    b = a[:32] + [7] + a[33:]
+    ha, hb = pam.KVCacheManager.blockHashes(a, 16), pam.KVCacheManager.blockHashes(b, 16)
+    assert len(ha) == 4 and len(set(ha)) == 4
+    assert ha[:2] == hb[:2] and ha[2] != hb[2] and ha[3] != hb[3]      # a change reaches every later block
+    assert pam.KVCacheManager.blockHashes(a[:47], 16) == ha[:2]        # only full blocks are hashed
+    assert pam.KVCacheManager.blockHashes(a, 16, seed=1)[0] != ha[0]
+    # usable as blockHashes: the second sequence shares the common prefix's blocks
+    m = new_manager(16, 16)
+    m.allocateSequence(1)
+    m.appendTokens(1, 64, ha)
+    m.allocateSequence(2)
+    m.appendTokens(2, 64, hb)
+    assert m.getBlockTable(1)[:2] == m.getBlockTable(2)[:2] and m.getBlockTable(1)[2:] != m.getBlockTable(2)[2:]
+    assert m.memoryStats().prefixCacheHits == 2
