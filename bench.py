@@ -1,24 +1,35 @@
 """Benchmark of the paged-KV hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--batch B] [--profile]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload NAME] [--blocks R] [--batch B] [--profile]
 
-Default workload `decode_c2`: large-batch paged decode with float16 KV -- 256
-sequences, context lengths uniform in [512, 8192], block size 16, head_dim 128,
-32 query / 8 KV heads, non-contiguous block tables, seeded synthetic N(0,1)
-data.  With N GPUs the KV heads are split into N groups, one per GPU; no
-collective runs on the attention path, so the total work is fixed (strong
-scaling).  A step is one decode of the whole batch (one new token per
-sequence); the metric is decode tokens per second of the whole job.
+With no --workload the line is the headline workload `decode_c2` -- large-batch paged
+decode with float16 KV: 256 sequences, context lengths uniform in [512, 8192], block size
+16, head_dim 128, 32 query / 8 KV heads, non-contiguous block tables, seeded synthetic
+N(0,1) data -- and its `also` object carries one entry per other workload of the metric
+(`prefill_c3`, `decode_c4`, `step_c4`, `append_c1`), each with its own time, roofline,
+clocks, end-to-end figure and bounded CPU baseline.  With --workload NAME the line is that
+workload alone.
 
-Prints ONE JSON line: `value` is measured with every input resident in HBM
-(CUDA events around exactly K steps on the launching stream, max over ranks);
-`e2e` is the same step through the reference-shaped C-ABI call `pam_decode`
-with queries and outputs in pinned host memory, copies inside the timed
-region; `roofline` relates the decode kernel's algorithmic bytes to the
-measured HBM copy bandwidth; `cpu_baseline` is the C oracle (a restatement of
-the reference's CPU path) timed on this host's cores on a bounded sample.
+With N GPUs (one process per GPU, torch.distributed.run) the KV heads are split into N
+groups, one per GPU; every GPU holds its heads' pages and an identical copy of the block
+tables, and no collective runs on the attention path, so the total work is fixed (strong
+scaling).  `value` is the whole job: the units of one step divided by the step time of the
+slowest rank.
 
-`--impl reference` times that CPU path alone (rank 0 only).
+Timing: W warm-up steps, a half-second settling loop (so that the clock sampler sees the
+clocks of the timed region), then R blocks (default 10) of exactly K steps, each block
+bracketed by a barrier and a device synchronisation and timed with CUDA events on the
+launching stream, maximum over ranks per block; `ms_per_step` is the median block,
+`ms_per_step_min` / `_max` the fastest and slowest.
+
+`e2e` is the same step through the reference-shaped C-ABI calls with queries, new K/V rows
+and outputs in page-locked host memory, copies inside the timed region.  `roofline` relates
+the dominant kernel's algorithmic bytes (or flops) to the measured peaks.  `cpu_baseline`
+is the C oracle (a restatement of the reference's CPU path) on this host's cores on a
+bounded sample (rank 0, N = 1 only).
+
+`--impl reference` times that CPU path alone (rank 0 only), for the same workloads.
 """
 from __future__ import annotations
 
@@ -37,36 +48,36 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-SEED = 1002
-BATCH, LEN_LO, LEN_HI = 256, 512, 8192
-HEADS, KV_HEADS, HEAD_DIM, BLOCK = 32, 8, 128, 16
-SPARE_BLOCKS = 1024
-CPU_SAMPLE_SEQS = 32
-FALLBACK_HBM_GBS = 6650.0
+HEAD_DIM, BLOCK, KV_HEADS = 128, 16, 8
+# decode_c2
+SEED, BATCH, LEN_LO, LEN_HI, HEADS, SPARE_BLOCKS, CPU_SAMPLE_SEQS = 1002, 256, 512, 8192, 32, 1024, 32
+# prefill_c3
+PF_SEQS, PF_LEN, PF_CHUNK, PF_PREFIX = 16, 2048, 512, 1024
+# append_c1
+C1_TOKENS, C1_BLOCKS, C1_COPIES = 4096, 4096, 512
+# decode_c4 / step_c4
+C4_SEQS, C4_LO, C4_HI, C4_WINDOW, C4_HEADS, C4_CHUNK = 64, 32768, 131072, 4096, 64, 2048
+
+FALLBACK = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+# DRAM bytes (read + written) of one decode launch relative to its algorithmic bytes, from an
+# ncu capture (dram__bytes_read.sum + dram__bytes_write.sum) of the split kernels on a
+# 64-sequence cut of the same workload; the traffic grows in proportion to the context tokens.
+DECODE_TRAFFIC_FACTOR = {"f16": 1.010, "fp8": 1.02}
+WORKLOADS = ("decode_c2", "prefill_c3", "decode_c4", "step_c4", "append_c1")
 
 
-def workload_lengths():
-    rng = np.random.default_rng(SEED)
-    return rng.integers(LEN_LO, LEN_HI + 1, size=BATCH).astype(np.int64)
-
-
-def measured_hbm_peak():
-    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+def peaks():
     try:
-        with open(path) as f:
-            return float(json.load(f)["hbm_gbs"]), "measured"
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            mp = json.load(f)
+        return {k: float(mp[k]) for k in FALLBACK}, "measured"
     except Exception:
-        return FALLBACK_HBM_GBS, "fallback"
+        return dict(FALLBACK), "fallback"
 
 
-def algorithmic_bytes(lens, heads, kv_heads):
-    """Bytes one decode step must move for `kv_heads` KV heads and `heads` query
-    heads: K and V of every context token once, queries, outputs, the touched
-    block-table entries and the lengths."""
-    kv = int(lens.sum()) * 2 * kv_heads * HEAD_DIM * 2
-    qo = 2 * len(lens) * heads * HEAD_DIM * 2
-    tables = int(((lens + BLOCK - 1) // BLOCK).sum()) * 4
-    return kv + qo + tables + len(lens) * 4
+def host_cores() -> int:
+    # all host cores this process may run on (a launcher may have set OMP_NUM_THREADS=1)
+    return len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
 
 
 class ClockSampler:
@@ -86,6 +97,7 @@ class ClockSampler:
             threading.Thread(target=self._read, daemon=True).start()
         except Exception:
             self.proc = None
+        return self
 
     def _read(self):
         for line in self.proc.stdout:
@@ -115,13 +127,20 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-# --------------------------------------------------------------------- CPU arm
+# ===================================================================== CPU arm
 
-def cpu_sample_inputs(lens, n_seqs):
-    """K/V pools, tables, lengths and queries for the first n_seqs sequences of
-    the workload (same lengths, same shapes, N(0,1) float16)."""
-    from oracle import paged_oracle as po
+def c2_lengths(batch=None):
+    rng = np.random.default_rng(SEED)
+    return rng.integers(LEN_LO, LEN_HI + 1, size=batch or BATCH).astype(np.int64)
 
+
+def cpu_decode_c2(steps, warmup, n_seqs=CPU_SAMPLE_SEQS):
+    """The reference's decode loop (restated in C, OpenMP over (sequence, kv head)) on all
+    host cores, on the first sequences of the workload; tokens/s over the sample."""
+    from oracle import c_oracle as co
+
+    lens = c2_lengths()
+    n_seqs = min(n_seqs, len(lens))
     sub = lens[:n_seqs]
     nblk = (sub + BLOCK - 1) // BLOCK
     n_pool = int(nblk.sum()) + 16
@@ -136,18 +155,8 @@ def cpu_sample_inputs(lens, n_seqs):
     k_pool = rng.standard_normal(shape, dtype=np.float32).astype(np.float16)
     v_pool = rng.standard_normal(shape, dtype=np.float32).astype(np.float16)
     q = rng.standard_normal((n_seqs, HEADS, HEAD_DIM), dtype=np.float32).astype(np.float16)
-    return q, k_pool, v_pool, tables, sub.astype(np.uint32)
-
-
-def time_cpu_path(lens, steps, warmup, n_seqs=CPU_SAMPLE_SEQS):
-    n_seqs = min(n_seqs, len(lens))
-    """The reference's CPU path (its decode loop restated in C, OpenMP over
-    (sequence, kv head)) on all host cores; tokens/s over the sample."""
-    from oracle import c_oracle as co
-
-    q, k_pool, v_pool, tables, l = cpu_sample_inputs(lens, n_seqs)
-    # all host cores this process may run on (a launcher may have set OMP_NUM_THREADS=1)
-    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    l = sub.astype(np.uint32)
+    cores = host_cores()
     for _ in range(max(warmup, 1)):
         co.decode(q, k_pool, v_pool, tables, l, KV_HEADS, BLOCK, 1, nthreads=cores)
     t0 = time.perf_counter()
@@ -155,40 +164,318 @@ def time_cpu_path(lens, steps, warmup, n_seqs=CPU_SAMPLE_SEQS):
         co.decode(q, k_pool, v_pool, tables, l, KV_HEADS, BLOCK, 1, nthreads=cores)
     dt = (time.perf_counter() - t0) / steps
     return {"value": n_seqs / dt, "unit": "tokens/s", "cores": cores, "kind": "port",
-            "sample": f"first {n_seqs} of {BATCH} sequences of the workload ({int(l.sum())} context tokens), "
-                      f"{steps} timed passes of {dt * 1e3:.1f} ms",
-            "ms_per_step_sample": dt * 1e3}
+            "sample": f"first {n_seqs} of {len(lens)} sequences of the workload ({int(l.sum())} context tokens), "
+                      f"{steps} timed passes of {dt * 1e3:.1f} ms (oracle/paged_oracle.c orc_decode)",
+            "ms_per_step_sample": dt * 1e3, "sample_fraction": n_seqs / len(lens)}
 
 
-def config_dict(n_gpus):
-    return {"workload": f"decode_c2: batch {BATCH}, context U[512,8192], block 16, head_dim 128, 32 q / 8 kv heads, "
-                        "float16 KV, random non-contiguous block tables",
-            "seed": SEED, "sharding": f"kv-head groups over {n_gpus} GPU(s), no collective on the attention path",
-            "l2": "inputs larger than L2 (KV read per step per GPU exceeds 126 MB); no flush needed"}
+def cpu_prefill_c3(budget_s=8.0):
+    """orc_prefill on every 8th row of one 2048-token sequence (256 rows x 32 heads, causal,
+    bf16), repeated for about budget_s seconds; TFLOP/s over the rows computed."""
+    from oracle import c_oracle as co
+    from oracle import paged_oracle as po
+
+    rng = np.random.default_rng(1003)
+    nb = PF_LEN // BLOCK
+    k_pool = po.to_bf16_bits(rng.standard_normal((nb, KV_HEADS, BLOCK, HEAD_DIM), dtype=np.float32))
+    v_pool = po.to_bf16_bits(rng.standard_normal((nb, KV_HEADS, BLOCK, HEAD_DIM), dtype=np.float32))
+    table = rng.permutation(nb).astype(np.int32)
+    rows = np.arange(0, PF_LEN, 8)
+    q = po.to_bf16_bits(rng.standard_normal((len(rows), HEADS, HEAD_DIM), dtype=np.float32))
+    cores = host_cores()
+
+    def one_pass():
+        # rows are not contiguous: one call per row (q_start selects the sequence position)
+        for i, r in enumerate(rows):
+            co.prefill(q[i:i + 1], k_pool, v_pool, table, PF_LEN, KV_HEADS, BLOCK, 3, q_start=int(r), nthreads=cores)
+
+    one_pass()
+    passes, t0 = 0, time.perf_counter()
+    while passes < 1 or time.perf_counter() - t0 < budget_s:
+        one_pass()
+        passes += 1
+    dt = (time.perf_counter() - t0) / passes
+    flops = int((rows + 1).sum()) * HEADS * 4 * HEAD_DIM
+    return {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+            "sample": f"every 8th row of one 2048-token sequence (256 rows x 32 heads, causal, {flops / 1e9:.2f} GFLOP), "
+                      f"{passes} timed passes of {dt * 1e3:.0f} ms (oracle/paged_oracle.c orc_prefill)",
+            "ms_per_step_sample": dt * 1e3, "sample_fraction": flops / c3_flops()}
+
+
+def cpu_decode_c4(budget_s=6.0, n_seqs=4):
+    """orc_decode with FP8 KV and the 4096-token window on the first sequences of the
+    workload (only the visible pages are materialised)."""
+    from oracle import c_oracle as co
+    from oracle import paged_oracle as po
+
+    lens = np.random.default_rng(1004).integers(C4_LO, C4_HI + 1, size=C4_SEQS).astype(np.int64)[:n_seqs]
+    rng = np.random.default_rng(1004 + 1)
+    vis_blocks = C4_WINDOW // BLOCK + 1
+    n_pool = n_seqs * vis_blocks
+    nblk = (lens + BLOCK - 1) // BLOCK
+    tables = np.zeros((n_seqs, int(nblk.max())), np.int32)
+    for i in range(n_seqs):
+        first = (int(lens[i]) - C4_WINDOW) // BLOCK
+        tables[i, first: nblk[i]] = i * vis_blocks + np.arange(int(nblk[i]) - first)
+    kc = rng.integers(0, 256, size=(n_pool, KV_HEADS, BLOCK, HEAD_DIM), dtype=np.uint8)
+    vc = rng.integers(0, 256, size=(n_pool, KV_HEADS, BLOCK, HEAD_DIM), dtype=np.uint8)
+    kc[(kc & 0x7F) == 0x7F] = 0x3C                      # no NaN codes
+    vc[(vc & 0x7F) == 0x7F] = 0x3C
+    scale = np.full((n_pool, KV_HEADS), 1.0 / 128, np.float16).view(np.uint16)
+    q = rng.standard_normal((n_seqs, C4_HEADS, HEAD_DIM), dtype=np.float32).astype(np.float16)
+    l = lens.astype(np.uint32)
+    cores = host_cores()
+    run = lambda: co.decode(q, kc, vc, tables, l, KV_HEADS, BLOCK, 2, window=C4_WINDOW, k_scale=scale, v_scale=scale,
+                            nthreads=cores)
+    run()
+    passes, t0 = 0, time.perf_counter()
+    while passes < 1 or time.perf_counter() - t0 < budget_s:
+        run()
+        passes += 1
+    dt = (time.perf_counter() - t0) / passes
+    _ = po
+    return {"value": n_seqs / dt, "unit": "tokens/s", "cores": cores, "kind": "port",
+            "sample": f"first {n_seqs} of {C4_SEQS} sequences, FP8 KV, window {C4_WINDOW}, 64 q / 8 kv heads, "
+                      f"{passes} timed passes of {dt * 1e3:.1f} ms (oracle/paged_oracle.c orc_decode)",
+            "ms_per_step_sample": dt * 1e3, "sample_fraction": n_seqs / C4_SEQS}
+
+
+def c1_inputs():
+    rng = np.random.default_rng(1001)
+    k = rng.standard_normal((C1_TOKENS, KV_HEADS, HEAD_DIM), dtype=np.float32).astype(np.float16)
+    v = rng.standard_normal((C1_TOKENS, KV_HEADS, HEAD_DIM), dtype=np.float32).astype(np.float16)
+    slots = rng.choice(C1_BLOCKS * BLOCK, C1_TOKENS, replace=False).astype(np.int64)
+    perm = rng.permutation(C1_BLOCKS)
+    return rng, k, v, slots, perm[:C1_COPIES].astype(np.int32), perm[C1_COPIES:2 * C1_COPIES].astype(np.int32)
+
+
+def c1_bytes(kv_heads, tokens=C1_TOKENS, copies=C1_COPIES):
+    row = kv_heads * HEAD_DIM
+    f16 = 2 * (tokens * row * 2) * 2                       # K and V: read + write
+    fp8 = 2 * (tokens * row * 2) + 2 * (tokens * row) + 2 * 2 * tokens * kv_heads * 2   # read once, codes, scales (upper bound)
+    cow = 2 * copies * kv_heads * BLOCK * HEAD_DIM * 2 * 2 # K and V blocks: read + write
+    return f16 + fp8 + cow + tokens * 8 * 2
+
+
+def cpu_append_c1(budget_s=5.0):
+    """The three parts of the step with the C oracle (scatter, FP8 scale + quantise with the
+    reference's software codec, block copies), one thread (the oracle's loops are scalar)."""
+    from oracle import c_oracle as co
+
+    _, k, v, slots, src, dst = c1_inputs()
+    kp = np.zeros((C1_BLOCKS, KV_HEADS, BLOCK, HEAD_DIM), np.float16)
+    vp = np.zeros_like(kp)
+    kc = np.zeros((C1_BLOCKS, KV_HEADS, BLOCK, HEAD_DIM), np.uint8)
+    vc = np.zeros_like(kc)
+    ks = np.zeros((C1_BLOCKS, KV_HEADS), np.uint16)
+    vs = np.zeros_like(ks)
+
+    def run():
+        co.reshape_and_cache(k, v, kp, vp, slots, BLOCK)
+        co.reshape_and_cache_fp8(k, v, kc, vc, ks, vs, slots, BLOCK)
+        co.copy_blocks(kp, vp, src, dst)
+
+    run()
+    passes, t0 = 0, time.perf_counter()
+    while passes < 1 or time.perf_counter() - t0 < budget_s:
+        run()
+        passes += 1
+    dt = (time.perf_counter() - t0) / passes
+    return {"value": c1_bytes(KV_HEADS) / dt / 1e9, "unit": "GB/s", "cores": 1, "kind": "port",
+            "sample": f"the whole step, {passes} timed passes of {dt * 1e3:.1f} ms (oracle/paged_oracle.c orc_reshape_and_cache, "
+                      "orc_reshape_and_cache_fp8, orc_copy_blocks)",
+            "ms_per_step_sample": dt * 1e3, "sample_fraction": 1.0}
+
+
+def c3_flops(heads=HEADS, seqs=None):
+    return (seqs or PF_SEQS) * heads * (PF_LEN * (PF_LEN + 1) // 2) * 4 * HEAD_DIM
+
+
+CPU_ARMS = {"decode_c2": lambda a: cpu_decode_c2(max(a.steps, 1), a.warmup), "prefill_c3": lambda a: cpu_prefill_c3(),
+            "decode_c4": lambda a: cpu_decode_c4(), "append_c1": lambda a: cpu_append_c1()}
+CPU_META = {
+    "decode_c2": ("paged decode tokens/s", "f16", lambda cb: BATCH),
+    "prefill_c3": ("prefill TFLOP/s", "bf16", None),
+    "decode_c4": ("paged decode tokens/s", "fp8-e4m3 KV, f16 q/out", lambda cb: C4_SEQS),
+    "append_c1": ("KV append GB/s", "f16 -> f16 / fp8-e4m3", None),
+}
+
+
+def reference_line(name, args):
+    """One JSON object of the CPU arm for workload `name` (step_c4 has no CPU restatement of
+    its own: its decode half is decode_c4)."""
+    key = "decode_c4" if name == "step_c4" else name
+    cb = CPU_ARMS[key](args)
+    metric, dtype, _ = CPU_META[key]
+    ms_full = cb["ms_per_step_sample"] / max(cb["sample_fraction"], 1e-12)
+    return {"impl": "reference", "metric": metric, "value": cb["value"], "unit": cb["unit"], "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_full,
+            "ms_per_step_note": "time of the sample divided by the fraction of the workload it covers (subsampled)",
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": dtype, "data": "synthetic",
+            "config": {"workload": CONFIG_TEXT[key], "sample": cb["sample"]}, "cpu_baseline": cb,
+            "e2e": {"value": cb["value"], "unit": cb["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
 
 
 def run_reference(args):
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+    if int(os.environ.get("RANK", "0")) != 0:
         return
-    lens = workload_lengths()
-    cb = time_cpu_path(lens, max(args.steps, 1), args.warmup)
-    line = {"impl": "reference", "metric": "paged decode tokens/s", "value": cb["value"], "unit": "tokens/s",
-            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": cb["ms_per_step_sample"] * BATCH / min(CPU_SAMPLE_SEQS, BATCH),
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
-            "data": "synthetic", "config": config_dict(args.gpus), "cpu_baseline": cb,
-            "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-            "gpu_launches": 0}
+    primary = args.workload or "decode_c2"
+    line = reference_line(primary, args)
+    if not args.workload:
+        line["also"] = {n: reference_line(n, args) for n in ("prefill_c3", "decode_c4", "append_c1")}
     print(json.dumps(line))
 
 
-# --------------------------------------------------------------------- GPU arm
+CONFIG_TEXT = {
+    "decode_c2": "decode_c2: batch 256, context U[512,8192], block 16, head_dim 128, 32 q / 8 kv heads, float16 KV, "
+                 "random non-contiguous block tables",
+    "prefill_c3": "prefill_c3: 16 seqs x 2048 tokens, chunks of 512, shared 1024-token prefix, bf16, 32 q / 8 kv heads, "
+                  "head_dim 128, block 16",
+    "decode_c4": "decode_c4: 64 seqs, context U[32768,131072], window 4096, FP8 e4m3 KV with (block, kv_head) scales, "
+                 "64 q / 8 kv heads, head_dim 128, block 16",
+    "step_c4": "step_c4: one scheduler step = append + prefill of a 2048-token chunk of a new sequence, and the 64 "
+               "windowed FP8 decodes of decode_c4",
+    "append_c1": "append_c1: 4096 tokens x 8 kv heads x 128 scattered to random distinct slots of a 4096-block pool as "
+                 "float16 and as FP8 e4m3 with (block, kv_head) scales, plus a copy of 512 random blocks",
+}
+
+
+# ===================================================================== GPU arm
+
+class Runtime:
+    """Process group, device, the stream shared with the library, and the timing rules."""
+
+    def __init__(self, args):
+        import torch
+        import torch.distributed as dist
+
+        import pagedattentionmetal_b200 as pam
+
+        self.torch, self.dist, self.pam, self.args = torch, dist, pam, args
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local = int(os.environ.get("LOCAL_RANK", "0"))
+        if self.world != args.gpus and self.world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run for --gpus > 1")
+        assert KV_HEADS % self.world == 0, "the KV heads must divide over the GPUs"
+        torch.cuda.set_device(self.local)
+        self.dev = torch.device("cuda", self.local)
+        if self.world > 1:
+            dist.init_process_group("nccl", device_id=self.dev)
+        self.engine = pam.PagedAttentionEngine(self.local)
+        # a stream of torch's that is not the legacy default stream, shared with the library so
+        # that torch's events time the library's kernels
+        self.stream = torch.cuda.Stream(self.dev)
+        torch.cuda.set_stream(self.stream)
+        self.engine.setStream(self.stream.cuda_stream)
+        # --shards M (single process only): this GPU takes KV-head group 0 of M, the share it
+        # would have in an M-GPU job, for profiling the small per-GPU steps of large N alone
+        self.shards = args.shards if (args.shards and self.world == 1) else self.world
+        assert KV_HEADS % self.shards == 0
+        self.kvh = KV_HEADS // self.shards
+        self.peaks, self.peak_kind = peaks()
+        self.comm = None
+
+    def heads(self, total):
+        return total // self.shards
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize(self.dev)
+
+    def max_over_ranks(self, x: float) -> float:
+        if self.world == 1:
+            return x
+        t = self.torch.tensor([x], device=self.dev, dtype=self.torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def settle(self, step, burst=10):
+        """Keep the GPU busy for about half a second, so that the clock sampler sees the
+        clocks the timed region runs at; returns the number of steps run."""
+        n, t0 = 0, time.perf_counter()
+        while not self.args.profile and time.perf_counter() - t0 < 0.5:
+            for _ in range(burst):
+                step()
+            self.torch.cuda.synchronize(self.dev)
+            n += burst
+        return n
+
+    def timed(self, step, flush=None):
+        """args.blocks blocks of exactly args.steps steps; per block the device time between
+        two events on the launching stream, maximum over ranks.  With `flush` every step is
+        timed with its own event pair and `flush()` runs before each (inputs smaller than
+        L2).  Returns per-step milliseconds: (median, min, max, all blocks)."""
+        torch, K = self.torch, self.args.steps
+        blocks = []
+        for _ in range(1 if self.args.profile else self.args.blocks):
+            self.barrier()
+            if flush is None:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(self.stream)
+                for _ in range(K):
+                    step()
+                e1.record(self.stream)
+                self.barrier()
+                ms = e0.elapsed_time(e1)
+            else:
+                ms = 0.0
+                for _ in range(K):
+                    flush()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record(self.stream)
+                    step()
+                    e1.record(self.stream)
+                    torch.cuda.synchronize(self.dev)
+                    ms += e0.elapsed_time(e1)
+                self.barrier()
+            blocks.append(self.max_over_ranks(ms) / K)
+        self.engine.synchronize()          # raises if a kernel of the timed region reported an error
+        return statistics.median(blocks), min(blocks), max(blocks), blocks
+
+    def timed_host(self, step):
+        """The same blocks for the end-to-end legs: synchronous calls with host buffers, wall
+        clock between barriers, maximum over ranks."""
+        K, blocks = self.args.steps, []
+        if self.args.profile:
+            return None, None, None
+        for _ in range(max(self.args.warmup, 3)):
+            step()
+        for _ in range(self.args.blocks):
+            self.barrier()
+            t0 = time.perf_counter()
+            for _ in range(K):
+                step()
+            self.barrier()
+            blocks.append(self.max_over_ranks((time.perf_counter() - t0) * 1e3) / K)
+        return statistics.median(blocks), min(blocks), max(blocks)
+
+    def base_line(self, name, metric, value, unit, ms, dtype, warm_steps, launches, clocks, extra_config=None):
+        med, lo, hi, blocks = ms
+        cfg = {"workload": CONFIG_TEXT[name], "sharding": f"kv-head groups over {self.world} GPU(s), no collective on the attention path",
+               "timed_blocks": len(blocks), "settle_steps": warm_steps}
+        cfg.update(extra_config or {})
+        if self.shards != self.world:
+            cfg["sharding"] = f"KV-head group 0 of {self.shards} on one GPU (the per-GPU share of a {self.shards}-GPU job, run alone)"
+        return {"metric": metric, "value": value, "unit": unit, "n_gpus": self.world, "steps": self.args.steps,
+                "warmup": self.args.warmup, "ms_per_step": med, "ms_per_step_min": lo, "ms_per_step_max": hi,
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": dtype, "data": "synthetic",
+                "config": cfg, "gpu_launches": int(launches), "clocks": clocks}
+
+    def close(self):
+        if self.comm is not None:
+            self.pam.PagedAttentionEngine.leaveComm(self.comm)
+        self.engine.close()
+        if self.world > 1:
+            self.dist.destroy_process_group()
+
 
 def scramble_free_list(cache, n_blocks, rng):
-    """Make the allocator hand out blocks in a random order, as after a long
-    run of a server: take every block with one-block sequences, free them in a
-    random order (the fifo policy re-uses blocks in the order they were freed)."""
+    """Make the allocator hand out blocks in a random order, as after a long run of a server:
+    take every block with one-block sequences, free them in a random order (the fifo policy
+    re-uses blocks in the order they were freed)."""
     base = 1 << 40
     for i in range(n_blocks):
         cache.allocateSequence(base + i)
@@ -197,39 +484,68 @@ def scramble_free_list(cache, n_blocks, rng):
         cache.freeSequence(base + int(i))
 
 
-def run_ours(args):
-    import torch
-    import torch.distributed as dist
+def fetch_pages(rt, cache, blocks, elem_bytes, with_scales):
+    """Pages `blocks` of this rank's device pools as a compact host pool (guards only)."""
+    from pagedattentionmetal_b200._cabi import lib
 
-    import pagedattentionmetal_b200 as pam
+    kvh = rt.kvh
+    page = kvh * BLOCK * HEAD_DIM * elem_bytes
+    dt = np.uint8 if elem_bytes == 1 else np.float16
+    k = np.empty((len(blocks), kvh, BLOCK, HEAD_DIM), dt)
+    v = np.empty_like(k)
+    ks = np.empty((len(blocks), kvh), np.float16) if with_scales else None
+    vs = np.empty_like(ks) if with_scales else None
+    ctx = rt.engine._ctx
+    for i, b in enumerate(blocks):
+        lib.pamc_memcpy(ctx, k[i].ctypes.data, cache.kPoolBuffer.ptr + int(b) * page, page, 1)
+        lib.pamc_memcpy(ctx, v[i].ctypes.data, cache.vPoolBuffer.ptr + int(b) * page, page, 1)
+        if with_scales:
+            lib.pamc_memcpy(ctx, ks[i].ctypes.data, cache.kScaleBuffer.ptr + int(b) * kvh * 2, kvh * 2, 1)
+            lib.pamc_memcpy(ctx, vs[i].ctypes.data, cache.vScaleBuffer.ptr + int(b) * kvh * 2, kvh * 2, 1)
+    return k, v, ks, vs
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus:
-        if world == 1 and args.gpus > 1:
-            raise SystemExit("launch with torch.distributed.run for --gpus > 1")
-    assert KV_HEADS % world == 0, "the KV heads must divide over the GPUs"
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    dev = torch.device("cuda", local)
-    kvh = KV_HEADS // world
-    heads = HEADS // world
+
+def guard_decode(rt, cache, sample, tables, lens, q_host, out_host, dtype, tol, window=0):
+    """Correctness guard: the sequences `sample` against the oracle on this rank's heads."""
+    from oracle import c_oracle as co
+
+    first = [((int(lens[i]) - window) // BLOCK if window and lens[i] > window else 0) for i in sample]
+    last = [(int(lens[i]) + BLOCK - 1) // BLOCK for i in sample]
+    used = np.unique(np.concatenate([tables[i, f:l] for i, f, l in zip(sample, first, last)]))
+    remap = np.zeros(int(tables.max()) + 1, np.int32)
+    remap[used] = np.arange(len(used), dtype=np.int32)
+    fp8 = dtype == 2
+    k, v, ks, vs = fetch_pages(rt, cache, used, 1 if fp8 else 2, fp8)
+    ref = co.decode(np.ascontiguousarray(q_host[sample]), k, v, remap[tables[sample]], lens[sample].astype(np.uint32), rt.kvh,
+                    BLOCK, dtype, window=window, k_scale=None if ks is None else ks.view(np.uint16),
+                    v_scale=None if vs is None else vs.view(np.uint16))
+    err = float(np.abs(out_host[sample].astype(np.float32) - ref).max())
+    assert err <= tol, f"decode differs from the oracle by {err}"
+
+
+# ------------------------------------------------------------------ decode_c2
+
+def algorithmic_bytes_c2(lens, heads, kv_heads):
+    """Bytes one decode step must move for `kv_heads` KV heads and `heads` query heads: K and V
+    of every context token once, queries, outputs, the touched block-table entries and the
+    lengths."""
+    kv = int(lens.sum()) * 2 * kv_heads * HEAD_DIM * 2
+    qo = 2 * len(lens) * heads * HEAD_DIM * 2
+    tables = int(((lens + BLOCK - 1) // BLOCK).sum()) * 4
+    return kv + qo + tables + len(lens) * 4
+
+
+def run_decode_c2(rt, with_cpu):
+    torch, pam, engine, dev, args = rt.torch, rt.pam, rt.engine, rt.dev, rt.args
     DT = pam.PagedAttentionDataType
-
-    lens = workload_lengths()
+    kvh, heads, rank = rt.kvh, rt.heads(HEADS), rt.rank
+    lens = c2_lengths(args.batch)
+    B = len(lens)
     nblk = (lens + BLOCK - 1) // BLOCK
     n_pool = int(nblk.sum()) + SPARE_BLOCKS
-    engine = pam.PagedAttentionEngine(local)
-    # a stream of torch's that is not the legacy default stream, shared with the
-    # library so that torch's events time the library's kernels
-    stream = torch.cuda.Stream(dev)
-    torch.cuda.set_stream(stream)
-    engine.setStream(stream.cuda_stream)
     cache = pam.KVCacheManager(engine, n_pool, BLOCK, HEAD_DIM, kvh, DT.float16)
     scramble_free_list(cache, n_pool, np.random.default_rng(SEED + 2))
-    ids = list(range(BATCH))
+    ids = list(range(B))
     gen = torch.Generator(device=dev)
     for sid in ids:
         L = int(lens[sid])
@@ -241,325 +557,244 @@ def run_ours(args):
         kv = kv[:, :, rank * kvh:(rank + 1) * kvh, :].to(torch.float16).contiguous()
         engine.appendKV(cache, sid, kv[0], kv[1], 0, L, heads)
     gen.manual_seed(SEED * 1000 + 999983)
-    q_full = torch.randn((BATCH, HEADS, HEAD_DIM), generator=gen, device=dev, dtype=torch.float32).to(torch.float16)
+    q_full = torch.randn((B, HEADS, HEAD_DIM), generator=gen, device=dev, dtype=torch.float32).to(torch.float16)
     q_dev = q_full[:, rank * heads:(rank + 1) * heads, :].contiguous()
     out_dev = torch.empty_like(q_dev)
     max_nb = int(nblk.max())
     tables_h, lens_h = cache.batchTables(ids, max_nb)
     assert np.array_equal(lens_h.astype(np.int64), lens)
     tables_dev = torch.from_numpy(tables_h).to(dev)
-    lens_dev = torch.from_numpy(lens_h.view(np.int32)).to(dev)
     layer = pam.PagedLayerSpec(HEAD_DIM, heads, kvh, BLOCK, DT.float16)
-    req = pam.PagedAttentionDecodeRequest(q_dev, cache.kPoolBuffer, cache.vPoolBuffer, tables_dev, lens_dev, out_dev,
-                                          BATCH, max_nb, layer)
-    q_pin = torch.empty((BATCH, heads, HEAD_DIM), dtype=torch.float16, pin_memory=True)
+    # K/V pools, queries, outputs and block tables resident in HBM; the lengths are a host
+    # array (as the reference's seqLengths buffer is host-visible): the library plans the
+    # launch from them and sends them up with the call
+    req = pam.PagedAttentionDecodeRequest(q_dev, cache.kPoolBuffer, cache.vPoolBuffer, tables_dev, lens_h, out_dev,
+                                          B, max_nb, layer)
+    q_pin = torch.empty((B, heads, HEAD_DIM), dtype=torch.float16, pin_memory=True)
     q_pin.copy_(q_dev)
     out_pin = torch.empty_like(q_pin, pin_memory=True)
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize(dev)
-
-    def max_over_ranks(x: float) -> float:
-        if world == 1:
-            return x
-        t = torch.tensor([x], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    # correctness guard on two sequences against the oracle (rank 0, its own heads)
     engine.decode(req)
-    if rank == 0:
-        from oracle import c_oracle as co
-        chk = [int(np.argmin(lens)), 3]
-        sub_tables, sub_lens = cache.batchTables(chk, max_nb)
-        # gather the pages of the two sequences into a small pool for the oracle
-        used = np.unique(np.concatenate([sub_tables[i, : (int(sub_lens[i]) + BLOCK - 1) // BLOCK] for i in range(2)]))
-        remap = {int(b): i for i, b in enumerate(used)}
-        pools = []
-        for pb in (cache.kPoolBuffer, cache.vPoolBuffer):
-            page_elems = kvh * BLOCK * HEAD_DIM
-            small = np.empty((len(used), kvh, BLOCK, HEAD_DIM), np.float16)
-            from pagedattentionmetal_b200._cabi import lib
-            for i, b in enumerate(used):
-                lib.pamc_memcpy(engine._ctx, small[i].ctypes.data, pb.ptr + int(b) * page_elems * 2, page_elems * 2, 1)
-            pools.append(small)
-        t2 = np.vectorize(lambda b: remap.get(int(b), 0))(sub_tables).astype(np.int32)
-        ref = co.decode(q_dev[chk].cpu().numpy(), pools[0], pools[1], t2, sub_lens, kvh, BLOCK, 1)
-        err = float(np.abs(out_dev[chk].float().cpu().numpy() - ref).max())
-        assert err <= 2e-3, f"decode differs from the oracle by {err}"
+    sample = [int(np.argmin(lens)), int(np.argmax(lens)), 3 % B]
+    guard_decode(rt, cache, sample, tables_h, lens_h, q_dev.cpu().numpy(), out_dev.cpu().numpy(), 1, 2e-3)
 
-    # ---- value: inputs resident in HBM, kernels only ----
+    # ---- value: inputs resident in HBM ----
     engine.setAsync(True)
-    sampler = ClockSampler(local)
-    sampler.start()
-    warm = max(args.warmup, 3)
-    for _ in range(warm):
-        engine.decode(req)
-    # keep the GPU busy for about half a second before timing, so that the
-    # clock sampler sees the clocks the timed region runs at
-    t_busy = time.perf_counter()
-    while not args.profile and time.perf_counter() - t_busy < 0.5:
-        for _ in range(10):
-            engine.decode(req)
-        torch.cuda.synchronize(dev)
-        warm += 10
-    barrier()
+    sampler = ClockSampler(rt.local).start()
+    step = lambda: engine.decode(req)
+    for _ in range(max(args.warmup, 3)):
+        step()
+    settled = rt.settle(step)
     launches0 = engine.kernelLaunches
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for _ in range(args.steps):
-        engine.decode(req)
-    e1.record(stream)
-    barrier()
-    engine.synchronize()        # raises if a kernel of the timed region reported an error
-    ms_total = max_over_ranks(e0.elapsed_time(e1))
-    ms_step = ms_total / args.steps
+    ms = rt.timed(step)
+    launches = engine.kernelLaunches - launches0
     engine.setAsync(False)
+    clocks = sampler.stop()
 
     # ---- e2e: the reference-shaped call with host buffers ----
-    e2e_steps = 0 if args.profile else args.steps
-    for _ in range(0 if args.profile else max(args.warmup, 3)):
-        engine.decodeBatch(cache, ids, q_pin.data_ptr(), out_pin.data_ptr(), heads)
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        engine.decodeBatch(cache, ids, q_pin.data_ptr(), out_pin.data_ptr(), heads)
-    barrier()
-    e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3) / max(e2e_steps, 1)
-    launches = engine.kernelLaunches - launches0
-    clocks = sampler.stop()
+    e2e_step = lambda: engine.decodeBatch(cache, ids, q_pin.data_ptr(), out_pin.data_ptr(), heads)
+    e2e = rt.timed_host(e2e_step)
     if not args.profile:
         assert torch.equal(out_pin.to(dev), out_dev), "host-buffer path and device path disagree"
 
+    # ---- all-gather of the head slices, for a caller that wants the whole output on every GPU ----
+    gather = None
+    if rt.world > 1 and not args.profile:
+        gather = gather_leg(rt, out_dev, B, heads)
+
+    line = None
     if rank == 0:
-        peak, peak_kind = measured_hbm_peak()
-        bytes_gpu = algorithmic_bytes(lens, heads, kvh)
-        achieved = bytes_gpu / (ms_step * 1e-3) / 1e9
-        cpu = time_cpu_path(lens, 90, 2) if world == 1 and not args.profile else None   # about 10 s of CPU work
-        io_bytes = BATCH * heads * HEAD_DIM * 2
-        line = {
-            "metric": "paged decode tokens/s", "value": BATCH / (ms_step * 1e-3), "unit": "tokens/s",
-            "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": ms_step,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": config_dict(world),
-            "kv_read_gbs_total": achieved * world,
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_source": f"{peak_kind} copy bandwidth", "per": "GPU",
-                         "kernel": "decodeSplitKernel (+ decodeMergeKernel, same timed step)",
-                         "algorithmic_bytes_per_launch": bytes_gpu,
-                         # DRAM read+write of one launch: 1.010 x algorithmic, from an ncu capture of the same
-                         # kernel on a 64-sequence case (profiles/decode_split_f16_b64_full.md), scaled by tokens
-                         "traffic": bytes_gpu * 1.010, "traffic_source": "ncu on batch 64, scaled by context tokens"},
-            "e2e": {"value": BATCH / (e2e_ms * 1e-3) if e2e_steps else None, "unit": "tokens/s", "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": io_bytes + tables_h.nbytes + lens_h.nbytes, "d2h_bytes_per_step": io_bytes,
-                    "call": "pam_decode with pinned host q/out; block tables rebuilt and uploaded per call"},
-            "gpu_launches": int(launches), "clocks": clocks,
-        }
-        if cpu:
-            line["cpu_baseline"] = cpu
-        print(json.dumps(line))
+        bytes_gpu = algorithmic_bytes_c2(lens, heads, kvh)
+        achieved = bytes_gpu / (ms[0] * 1e-3) / 1e9
+        peak = rt.peaks["hbm_gbs"]
+        io_bytes = B * heads * HEAD_DIM * 2
+        line = rt.base_line("decode_c2", "paged decode tokens/s", B / (ms[0] * 1e-3), "tokens/s", ms, "f16", settled,
+                            launches, clocks,
+                            {"seed": SEED, "l2": "inputs larger than L2 (KV read per step per GPU exceeds 126 MB); no flush needed",
+                             "lengths": "host array, uploaded by every call"})
+        line["kv_read_gbs_total"] = achieved * rt.world
+        line["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                            "peak_source": f"{rt.peak_kind} copy bandwidth", "per": "GPU",
+                            "kernel": "decodeSplitKernel (splits merged by the CTA that finishes a sequence last)",
+                            "algorithmic_bytes_per_launch": bytes_gpu,
+                            "traffic": bytes_gpu * DECODE_TRAFFIC_FACTOR["f16"],
+                            "traffic_source": "ncu on a 64-sequence cut, scaled by context tokens"}
+        line["e2e"] = {"value": B / (e2e[0] * 1e-3) if e2e[0] else None, "unit": "tokens/s", "ms_per_step": e2e[0],
+                       "ms_per_step_min": e2e[1], "ms_per_step_max": e2e[2],
+                       "h2d_bytes_per_step": io_bytes + lens_h.nbytes, "d2h_bytes_per_step": io_bytes,
+                       "call": "pam_decode with page-locked host q/out: block tables resident on the device (only changed "
+                               "entries are sent), lengths sent per call, output written by the kernels into the host buffer"}
+        if gather:
+            line["gather"] = gather
+        if with_cpu:
+            line["cpu_baseline"] = cpu_decode_c2(90, 2)        # about 10 s of CPU work
     cache.close()
-    engine.close()
-    if world > 1:
-        dist.destroy_process_group()
+    return line
 
 
-# ----------------------------------------------------- prefill workload (c3)
-
-PF_SEQS, PF_LEN, PF_CHUNK, PF_PREFIX = 16, 2048, 512, 1024
-
-
-def run_prefill(args):
-    """Chunked causal prefill with prefix caching (`configs[3]`): 16 sequences x
-    2048 prompt tokens in 512-token chunks, all sharing an identical 1024-token
-    prefix (its pages are shared through the manager's prefix cache and written
-    once), bf16, 32 q / 8 kv heads, head_dim 128, block 16.  A step is the four
-    chunk launches (one launch per chunk for all 16 sequences); the metric is
-    algorithmic TFLOP/s: 16 x 32 x (2048 x 2049 / 2) x 4 x 128 = 550.0 GFLOP per
-    step, masked pairs and softmax not counted.  Tensor-bound."""
-    import torch
-
-    import pagedattentionmetal_b200 as pam
-
+def gather_leg(rt, out_dev, rows, heads):
+    """pamc_allgather_heads on the decode output: checked against the ranks' outputs put side
+    by side (torch.distributed as the checker), then timed."""
+    torch, dist, engine, pam = rt.torch, rt.dist, rt.engine, rt.pam
+    if rt.comm is None:
+        raw = torch.zeros(128, dtype=torch.uint8, device=rt.dev)
+        if rt.rank == 0:
+            raw.copy_(torch.frombuffer(bytearray(pam.PagedAttentionEngine.makeCommId()), dtype=torch.uint8))
+        dist.broadcast(raw, 0)
+        rt.comm = engine.joinComm(bytes(raw.cpu().numpy().tobytes()), rt.rank, rt.world)
+    full = torch.empty((rows, heads * rt.world, HEAD_DIM), dtype=out_dev.dtype, device=rt.dev)
     DT = pam.PagedAttentionDataType
-    dev = torch.device("cuda", 0)
-    torch.cuda.set_device(dev)
-    engine = pam.PagedAttentionEngine(0)
-    stream = torch.cuda.Stream(dev)
-    torch.cuda.set_stream(stream)
-    engine.setStream(stream.cuda_stream)
+    call = lambda: engine.allGatherHeads(rt.comm, out_dev, full, rows, heads, HEAD_DIM, DT.float16)
+    call()
+    parts = [torch.empty_like(out_dev) for _ in range(rt.world)]
+    dist.all_gather(parts, out_dev)
+    assert torch.equal(full, torch.cat(parts, dim=1)), "gathered tensor differs from the ranks' outputs side by side"
+    engine.setAsync(True)
+    for _ in range(3):
+        call()
+    ms = rt.timed(call)
+    engine.setAsync(False)
+    bytes_moved = full.numel() * full.element_size()
+    return {"ms": ms[0], "ms_min": ms[1], "ms_max": ms[2], "bytes_gathered_per_gpu": bytes_moved,
+            "gbs_per_gpu": bytes_moved / (ms[0] * 1e-3) / 1e9,
+            "call": "pamc_allgather_heads: ncclAllGather over NVLink + one interleave kernel; verified against the ranks' slices"}
+
+
+# ------------------------------------------------------------------ prefill_c3
+
+def run_prefill_c3(rt, with_cpu):
+    """Chunked causal prefill with prefix caching (`configs[3]`): 16 sequences x 2048 prompt
+    tokens in 512-token chunks, all sharing an identical 1024-token prefix (its pages are
+    shared through the manager's prefix cache and written once), bf16.  A step is the four
+    chunk launches (one launch per chunk for all 16 sequences); the metric is algorithmic
+    TFLOP/s: 16 x 32 x (2048 x 2049 / 2) x 4 x 128 = 550.0 GFLOP per step, masked pairs and
+    softmax not counted.  Tensor-bound."""
+    torch, pam, engine, dev, args = rt.torch, rt.pam, rt.engine, rt.dev, rt.args
+    DT = pam.PagedAttentionDataType
+    kvh, heads, rank = rt.kvh, rt.heads(HEADS), rt.rank
+    seqs = PF_SEQS if args.batch is None or args.workload != "prefill_c3" else args.batch
     nblk_seq = PF_LEN // BLOCK
-    cache = pam.KVCacheManager(engine, PF_SEQS * nblk_seq + 64, BLOCK, HEAD_DIM, KV_HEADS, DT.bfloat16)
+    cache = pam.KVCacheManager(engine, seqs * nblk_seq + 64, BLOCK, HEAD_DIM, kvh, DT.bfloat16)
     gen = torch.Generator(device=dev)
     gen.manual_seed(1003)
+    ksl, qsl = slice(rank * kvh, (rank + 1) * kvh), slice(rank * heads, (rank + 1) * heads)
     prefix_kv = torch.randn((2, PF_PREFIX, KV_HEADS, HEAD_DIM), generator=gen, device=dev).to(torch.bfloat16)
-    prefix_q = torch.randn((PF_PREFIX, HEADS, HEAD_DIM), generator=gen, device=dev).to(torch.bfloat16)
+    prefix_q = torch.randn((PF_PREFIX, HEADS, HEAD_DIM), generator=gen, device=dev).to(torch.bfloat16)[:, qsl]
     qs = []
     hashes = list(range(PF_PREFIX // BLOCK))
-    for sid in range(PF_SEQS):
+    for sid in range(seqs):
         cache.allocateSequence(sid)
         cache.appendTokens(sid, PF_PREFIX, hashes)              # followers hit the leader's pages
         if sid == 0:
-            engine.appendKV(cache, 0, prefix_kv[0].contiguous(), prefix_kv[1].contiguous(), 0, PF_PREFIX, HEADS)
+            engine.appendKV(cache, 0, prefix_kv[0][:, ksl].contiguous(), prefix_kv[1][:, ksl].contiguous(), 0, PF_PREFIX, heads)
         cache.appendTokens(sid, PF_LEN - PF_PREFIX)
         kv = torch.randn((2, PF_LEN - PF_PREFIX, KV_HEADS, HEAD_DIM), generator=gen, device=dev).to(torch.bfloat16)
-        engine.appendKV(cache, sid, kv[0].contiguous(), kv[1].contiguous(), PF_PREFIX, PF_LEN - PF_PREFIX, HEADS)
-        q_own = torch.randn((PF_LEN - PF_PREFIX, HEADS, HEAD_DIM), generator=gen, device=dev).to(torch.bfloat16)
-        qs.append(torch.cat([prefix_q, q_own]))
+        engine.appendKV(cache, sid, kv[0][:, ksl].contiguous(), kv[1][:, ksl].contiguous(), PF_PREFIX, PF_LEN - PF_PREFIX, heads)
+        q_own = torch.randn((PF_LEN - PF_PREFIX, HEADS, HEAD_DIM), generator=gen, device=dev).to(torch.bfloat16)[:, qsl]
+        qs.append(torch.cat([prefix_q, q_own]).contiguous())
     stats = cache.memoryStats()
-    assert stats.sharedBlocks == PF_PREFIX // BLOCK and stats.prefixCacheHits == (PF_SEQS - 1) * (PF_PREFIX // BLOCK)
-    tables_h, _ = cache.batchTables(list(range(PF_SEQS)), nblk_seq)
+    assert stats.sharedBlocks == (PF_PREFIX // BLOCK if seqs > 1 else 0)
+    assert stats.prefixCacheHits == (seqs - 1) * (PF_PREFIX // BLOCK)
+    tables_h, _ = cache.batchTables(list(range(seqs)), nblk_seq)
     tables = torch.from_numpy(tables_h).to(dev)
-    layer = pam.PagedLayerSpec(HEAD_DIM, HEADS, KV_HEADS, BLOCK, DT.bfloat16)
+    layer = pam.PagedLayerSpec(HEAD_DIM, heads, kvh, BLOCK, DT.bfloat16)
     n_chunks = PF_LEN // PF_CHUNK
-    q_chunks = [torch.cat([qs[s][c * PF_CHUNK:(c + 1) * PF_CHUNK] for s in range(PF_SEQS)]).contiguous() for c in range(n_chunks)]
+    q_chunks = [torch.cat([qs[s][c * PF_CHUNK:(c + 1) * PF_CHUNK] for s in range(seqs)]).contiguous() for c in range(n_chunks)]
     outs = [torch.empty_like(q_chunks[c]) for c in range(n_chunks)]
 
-    def step():
-        for c in range(n_chunks):
-            engine.prefillBatch(q_chunks[c], cache.kPoolBuffer, cache.vPoolBuffer, tables, outs[c],
-                                [(c + 1) * PF_CHUNK] * PF_SEQS, [c * PF_CHUNK] * PF_SEQS, [PF_CHUNK] * PF_SEQS,
-                                nblk_seq, layer, True)
+    def make_step(q_list, out_list):
+        def step():
+            for c in range(n_chunks):
+                engine.prefillBatch(q_list[c], cache.kPoolBuffer, cache.vPoolBuffer, tables, out_list[c],
+                                    [(c + 1) * PF_CHUNK] * seqs, [c * PF_CHUNK] * seqs, [PF_CHUNK] * seqs,
+                                    nblk_seq, layer, True)
+        return step
 
+    step = make_step(q_chunks, outs)
     # correctness guard: a few rows of one follower sequence against the oracle
     step()
     engine.synchronize()
     from oracle import c_oracle as co
     from oracle import paged_oracle as po
-    gk, gv, _, _ = cache.readPools()
-    sid, c, r0, n = min(5, PF_SEQS - 1), 2, 100, 8
-    ref = co.prefill(qs[sid][c * PF_CHUNK + r0: c * PF_CHUNK + r0 + n].view(torch.uint16).cpu().numpy(), gk, gv,
-                     tables_h[sid], (c + 1) * PF_CHUNK, KV_HEADS, BLOCK, 3, q_start=c * PF_CHUNK + r0)
+    tensor_path = engine.lastStats.operation == pam.Operation.prefillMMA
+    sid, c, r0, n = min(5, seqs - 1), 2, 100, 8
+    used = tables_h[sid]
+    k, v, _, _ = fetch_pages(rt, cache, used, 2, False)
+    ref = co.prefill(qs[sid][c * PF_CHUNK + r0: c * PF_CHUNK + r0 + n].view(torch.uint16).cpu().numpy(), k.view(np.uint16),
+                     v.view(np.uint16), np.arange(len(used), dtype=np.int32), (c + 1) * PF_CHUNK, kvh, BLOCK, 3,
+                     q_start=c * PF_CHUNK + r0)
     got = po.from_bf16_bits(outs[c][sid * PF_CHUNK + r0: sid * PF_CHUNK + r0 + n].view(torch.uint16).cpu().numpy())
     err = float(np.abs(got - ref).max())
     assert err <= 2e-3 + 2.0 ** -8, f"prefill differs from the oracle by {err}"
-    tensor_path = engine.lastStats.operation == pam.Operation.prefillMMA
 
     engine.setAsync(True)
-    sampler = ClockSampler(0)
-    sampler.start()
-    warm = max(args.warmup, 3)
-    for _ in range(warm):
+    sampler = ClockSampler(rt.local).start()
+    for _ in range(max(args.warmup, 3)):
         step()
-    t_busy = time.perf_counter()
-    while not args.profile and time.perf_counter() - t_busy < 0.5:
-        step()
-        torch.cuda.synchronize(dev)
-        warm += 1
-    torch.cuda.synchronize(dev)
+    settled = rt.settle(step, burst=2)
     launches0 = engine.kernelLaunches
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for _ in range(args.steps):
-        step()
-    e1.record(stream)
-    torch.cuda.synchronize(dev)
-    engine.synchronize()        # raises if a kernel of the timed region reported an error
-    ms_step = e0.elapsed_time(e1) / args.steps
+    ms = rt.timed(step)
     launches = engine.kernelLaunches - launches0
-    clocks = sampler.stop()
-    flops = PF_SEQS * HEADS * (PF_LEN * (PF_LEN + 1) // 2) * 4 * HEAD_DIM
-    tflops = flops / (ms_step * 1e-3) / 1e12
-
-    # ---- e2e: the same four chunk calls with q and the output in pinned host memory ----
     engine.setAsync(False)
-    q_pin = [q.cpu().pin_memory() for q in q_chunks]
-    out_pin = [torch.empty_like(q).pin_memory() for q in q_pin]
+    clocks = sampler.stop()
 
-    def step_host():
-        for c in range(n_chunks):
-            engine.prefillBatch(q_pin[c], cache.kPoolBuffer, cache.vPoolBuffer, tables, out_pin[c],
-                                [(c + 1) * PF_CHUNK] * PF_SEQS, [c * PF_CHUNK] * PF_SEQS, [PF_CHUNK] * PF_SEQS,
-                                nblk_seq, layer, True)
-
-    e2e_ms, e2e_steps = None, 0 if args.profile else args.steps
-    if e2e_steps:
-        for _ in range(3):
-            step_host()
-        torch.cuda.synchronize(dev)
-        t0 = time.perf_counter()
-        for _ in range(e2e_steps):
-            step_host()
-        torch.cuda.synchronize(dev)
-        e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
-        assert torch.equal(out_pin[n_chunks - 1].to(dev), outs[n_chunks - 1]), "host-buffer path and device path disagree"
-    io_bytes = sum(q.numel() * 2 for q in q_pin)
-
-    # ---- CPU baseline: the C oracle's prefill over the whole step (every row of all 16 sequences) ----
-    cpu = None
+    # ---- e2e: the same four chunk calls with q and the output in page-locked host memory ----
+    e2e = (None, None, None)
+    io_bytes = sum(q.numel() * 2 for q in q_chunks)
     if not args.profile:
-        t0 = time.perf_counter()
-        for s_i in range(PF_SEQS):
-            co.prefill(qs[s_i].view(torch.uint16).cpu().numpy(), gk, gv, tables_h[s_i], PF_LEN, KV_HEADS, BLOCK, 3, q_start=0)
-        dt = time.perf_counter() - t0
-        cpu = {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": co.max_threads(), "kind": "port",
-               "sample": f"the whole step once: 16 sequences x 2048 rows x 32 heads, causal ({dt:.1f} s): "
-                         "oracle/paged_oracle.c orc_prefill, OpenMP over (row, head)"}
-    try:
-        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
-            mp = json.load(f)
-            peak, kind = float(mp["bf16_tflops"]), "measured cuBLAS bf16 burst"
-            sustained = float(mp.get("bf16_tflops_sustained", 0)) or None
-    except Exception:
-        peak, kind, sustained = 1590.0, "fallback", 1400.0
-    line = {"metric": "prefill TFLOP/s", "value": tflops, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
-            "warmup": warm, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "prefill_c3: 16 seqs x 2048 tokens, chunks of 512, shared 1024-token prefix, bf16, "
-                                   "32 q / 8 kv heads, head_dim 128, block 16", "seed": 1003},
-            "tokens_per_s": PF_SEQS * PF_LEN / (ms_step * 1e-3),
-            "roofline": {"bound": "tensor", "achieved": tflops, "peak": peak, "unit": "TFLOP/s", "frac": tflops / peak,
-                         "peak_source": kind, "kernel": "prefillTcKernel" if tensor_path else "prefillGeneralKernel",
-                         "algorithmic_flops_per_step": flops, "traffic": None,
-                         # the step is timed inside a half-second loop of back-to-back steps: the fraction of the
-                         # sustained cuBLAS figure is given beside the fraction of its burst figure
-                         "frac_of_sustained": tflops / sustained if sustained else None, "peak_sustained": sustained},
-            "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12 if e2e_ms else None, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": io_bytes, "d2h_bytes_per_step": io_bytes,
-                    "call": "pamc_prefill_batch per chunk with pinned host q/out (block tables resident)"},
-            "gpu_launches": int(launches), "clocks": clocks}
-    if cpu:
-        line["cpu_baseline"] = cpu
-    print(json.dumps(line))
+        q_pin = [q.cpu().pin_memory() for q in q_chunks]
+        out_pin = [torch.empty_like(q).pin_memory() for q in q_pin]
+        e2e = rt.timed_host(make_step(q_pin, out_pin))
+        assert torch.equal(out_pin[n_chunks - 1].to(dev), outs[n_chunks - 1]), "host-buffer path and device path disagree"
+
+    line = None
+    if rank == 0:
+        flops = c3_flops(HEADS, seqs)                      # whole job, all GPUs
+        tflops = flops / (ms[0] * 1e-3) / 1e12
+        flops = flops * rt.world // rt.shards              # (with --shards: the share that ran)
+        tflops = flops / (ms[0] * 1e-3) / 1e12
+        per_gpu = tflops / rt.world
+        peak, sustained = rt.peaks["bf16_tflops"], rt.peaks["bf16_tflops_sustained"]
+        line = rt.base_line("prefill_c3", "prefill TFLOP/s", tflops, "TFLOP/s", ms, "bf16", settled, launches, clocks,
+                            {"seed": 1003, "l2": "K/V of a step (16 x 2048 tokens x 8 kv heads) is re-read from L2 by design; "
+                                                 "q and out stream through HBM"})
+        line["tokens_per_s"] = seqs * PF_LEN / (ms[0] * 1e-3)
+        line["roofline"] = {"bound": "tensor", "achieved": per_gpu, "peak": peak, "unit": "TFLOP/s", "frac": per_gpu / peak,
+                            "peak_source": f"{rt.peak_kind} cuBLAS bf16 burst", "per": "GPU",
+                            "kernel": "prefillTcKernel" if tensor_path else "prefillGeneralKernel",
+                            "algorithmic_flops_per_step": flops // rt.world, "traffic": None,
+                            # the step is timed inside a loop of back-to-back steps: the fraction of the sustained
+                            # cuBLAS figure is given beside the fraction of its burst figure
+                            "frac_of_sustained": per_gpu / sustained if sustained else None, "peak_sustained": sustained}
+        line["e2e"] = {"value": flops / (e2e[0] * 1e-3) / 1e12 if e2e[0] else None, "unit": "TFLOP/s", "ms_per_step": e2e[0],
+                       "ms_per_step_min": e2e[1], "ms_per_step_max": e2e[2],
+                       "h2d_bytes_per_step": io_bytes, "d2h_bytes_per_step": io_bytes,
+                       "call": "pamc_prefill_batch per chunk with page-locked host q/out (block tables resident)"}
+        if with_cpu:
+            line["cpu_baseline"] = cpu_prefill_c3()
     cache.close()
-    engine.close()
+    return line
 
 
-# ------------------------------------------------ KV append + FP8 quantisation + CoW copy (c1)
+# ------------------------------------------------------------------ append_c1
 
-C1_TOKENS, C1_BLOCKS, C1_COPIES = 4096, 4096, 512
-
-
-def run_append(args):
-    """`configs[1]`: 4096 new tokens (float16 K/V, 8 KV heads x 128) scattered by a slot
-    mapping of random distinct slots into a pool of 4096 blocks x 16, once as float16 and
-    once quantised to FP8 e4m3 with per-(block, kv_head) scales, plus the copy of 512
-    random blocks (copy-on-write).  A step is the three calls; the working set is smaller
-    than L2, so L2 is flushed (a 512 MB buffer is written) before every timed step and
-    every step is timed with its own pair of CUDA events.  Metric: algorithmic GB/s."""
-    import torch
-
-    import pagedattentionmetal_b200 as pam
-
+def run_append_c1(rt, with_cpu):
+    """`configs[1]`: 4096 new tokens (float16 K/V) scattered by a slot mapping of random
+    distinct slots into a pool of 4096 blocks x 16, once as float16 and once quantised to FP8
+    e4m3 with per-(block, kv_head) scales, plus the copy of 512 random blocks (copy-on-write).
+    A step is the three calls; the working set is smaller than L2, so L2 is flushed (a 512 MB
+    buffer is written) before every timed step and every step is timed with its own pair of
+    CUDA events.  Metric: algorithmic GB/s (this GPU's KV heads)."""
+    torch, pam, engine, dev, args = rt.torch, rt.pam, rt.engine, rt.dev, rt.args
     DT = pam.PagedAttentionDataType
-    dev = torch.device("cuda", 0)
-    torch.cuda.set_device(dev)
-    engine = pam.PagedAttentionEngine(0)
-    stream = torch.cuda.Stream(dev)
-    torch.cuda.set_stream(stream)
-    engine.setStream(stream.cuda_stream)
-    rng = np.random.default_rng(1001)
+    kvh, rank = rt.kvh, rt.rank
     T, nblk = C1_TOKENS, C1_BLOCKS
-    k_h = rng.standard_normal((T, KV_HEADS, HEAD_DIM), dtype=np.float32).astype(np.float16)
-    v_h = rng.standard_normal((T, KV_HEADS, HEAD_DIM), dtype=np.float32).astype(np.float16)
-    slots_h = rng.choice(nblk * BLOCK, T, replace=False).astype(np.int64)
-    perm = rng.permutation(nblk)
-    src, dst = perm[:C1_COPIES].astype(np.int32), perm[C1_COPIES:2 * C1_COPIES].astype(np.int32)
+    rng, k_full, v_full, slots_h, src, dst = c1_inputs()
+    k_h = np.ascontiguousarray(k_full[:, rank * kvh:(rank + 1) * kvh])
+    v_h = np.ascontiguousarray(v_full[:, rank * kvh:(rank + 1) * kvh])
     k, v, slots = torch.from_numpy(k_h).to(dev), torch.from_numpy(v_h).to(dev), torch.from_numpy(slots_h).to(dev)
-    c16 = pam.KVCacheManager(engine, nblk, BLOCK, HEAD_DIM, KV_HEADS, DT.float16)
-    c8 = pam.KVCacheManager(engine, nblk, BLOCK, HEAD_DIM, KV_HEADS, DT.float8)
+    c16 = pam.KVCacheManager(engine, nblk, BLOCK, HEAD_DIM, kvh, DT.float16)
+    c8 = pam.KVCacheManager(engine, nblk, BLOCK, HEAD_DIM, kvh, DT.float8)
 
     def step():
         engine.reshapeAndCache(c16, k, v, slots, T)
@@ -570,15 +805,15 @@ def run_append(args):
     step()
     engine.synchronize()
     from oracle import c_oracle as co
-    kp = np.zeros((nblk, KV_HEADS, BLOCK, HEAD_DIM), np.float16)
+    kp = np.zeros((nblk, kvh, BLOCK, HEAD_DIM), np.float16)
     vp = np.zeros_like(kp)
     co.reshape_and_cache(k_h, v_h, kp, vp, slots_h, BLOCK)
     co.copy_blocks(kp, vp, src, dst)
     gk, gv, _, _ = c16.readPools()
     assert np.array_equal(gk, kp) and np.array_equal(gv, vp), "float16 append or block copy differs from the oracle"
-    kc = np.zeros((nblk, KV_HEADS, BLOCK, HEAD_DIM), np.uint8)
+    kc = np.zeros((nblk, kvh, BLOCK, HEAD_DIM), np.uint8)
     vc = np.zeros_like(kc)
-    ks = np.zeros((nblk, KV_HEADS), np.float16)
+    ks = np.zeros((nblk, kvh), np.float16)
     vs = np.zeros_like(ks)
     co.reshape_and_cache_fp8(k_h, v_h, kc, vc, ks.view(np.uint16), vs.view(np.uint16), slots_h, BLOCK)
     gk8, gv8, gks, gvs = c8.readPools()
@@ -586,36 +821,24 @@ def run_append(args):
     assert np.array_equal(gks, ks) and np.array_equal(gvs, vs), "FP8 scales differ from the oracle"
 
     engine.setAsync(True)
-    flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
-    sampler = ClockSampler(0)
-    sampler.start()
-    warm = max(args.warmup, 3)
-    for _ in range(warm):
+    flush_buf = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+    flush = lambda: flush_buf.fill_(1)
+    sampler = ClockSampler(rt.local).start()
+    for _ in range(max(args.warmup, 3)):
         step()
     torch.cuda.synchronize(dev)
     launches0 = engine.kernelLaunches
-    total_ms = 0.0
-    for _ in range(args.steps):
-        flush.fill_(1)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        step()
-        e1.record(stream)
-        torch.cuda.synchronize(dev)
-        total_ms += e0.elapsed_time(e1)
-    engine.synchronize()
-    ms_step = total_ms / args.steps
+    ms = rt.timed(step, flush=flush)
     launches = engine.kernelLaunches - launches0
     clocks = sampler.stop()
-    row = KV_HEADS * HEAD_DIM
 
     # ---- the same scatters with 16 times the tokens: 65 536 tokens that fill every slot of the
     # pool (a permutation of all slots), where the kernels run long enough for HBM to bound them
     x16 = None
     if not args.profile:
         T16 = nblk * BLOCK
-        k16_h = rng.standard_normal((T16, KV_HEADS, HEAD_DIM), dtype=np.float32).astype(np.float16)
-        v16_h = rng.standard_normal((T16, KV_HEADS, HEAD_DIM), dtype=np.float32).astype(np.float16)
+        k16_h = rng.standard_normal((T16, kvh, HEAD_DIM), dtype=np.float32).astype(np.float16)
+        v16_h = rng.standard_normal((T16, kvh, HEAD_DIM), dtype=np.float32).astype(np.float16)
         slots16_h = rng.permutation(T16).astype(np.int64)
         k16, v16 = torch.from_numpy(k16_h).to(dev), torch.from_numpy(v16_h).to(dev)
         slots16 = torch.from_numpy(slots16_h).to(dev)
@@ -626,287 +849,271 @@ def run_append(args):
 
         step16()
         engine.synchronize()
-        kp16 = np.zeros((nblk, KV_HEADS, BLOCK, HEAD_DIM), np.float16)
+        kp16 = np.zeros((nblk, kvh, BLOCK, HEAD_DIM), np.float16)
         vp16 = np.zeros_like(kp16)
         co.reshape_and_cache(k16_h, v16_h, kp16, vp16, slots16_h, BLOCK)
         gk, gv, _, _ = c16.readPools()
         assert np.array_equal(gk, kp16) and np.array_equal(gv, vp16), "x16 float16 append differs from the oracle"
-        # the FP8 pool already holds codes and scales of the steps before: the oracle replays them
-        for _ in range(warm + args.steps):
-            co.reshape_and_cache_fp8(k_h, v_h, kc, vc, ks.view(np.uint16), vs.view(np.uint16), slots_h, BLOCK)
+        # the FP8 pool already holds codes and scales of the steps before (same tokens to the same
+        # slots: a second pass of the oracle leaves what every later pass leaves)
+        co.reshape_and_cache_fp8(k_h, v_h, kc, vc, ks.view(np.uint16), vs.view(np.uint16), slots_h, BLOCK)
         co.reshape_and_cache_fp8(k16_h, v16_h, kc, vc, ks.view(np.uint16), vs.view(np.uint16), slots16_h, BLOCK)
         gk8, gv8, gks, gvs = c8.readPools()
         assert np.array_equal(gk8, kc) and np.array_equal(gv8, vc), "x16 FP8 codes differ from the oracle"
         assert np.array_equal(gks, ks) and np.array_equal(gvs, vs), "x16 FP8 scales differ from the oracle"
         for _ in range(3):
             step16()
-        torch.cuda.synchronize(dev)
-        t16 = 0.0
-        for _ in range(args.steps):
-            flush.fill_(1)
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(stream)
-            step16()
-            e1.record(stream)
-            torch.cuda.synchronize(dev)
-            t16 += e0.elapsed_time(e1)
-        engine.synchronize()
-        ms16 = t16 / args.steps
-        bytes16 = 2 * (T16 * row * 2) * 2 + 2 * (T16 * row * 2) + 2 * (T16 * row) + 2 * 2 * nblk * KV_HEADS * 2 + T16 * 8 * 2
-        peak16, _ = measured_hbm_peak()
-        x16 = {"tokens": T16, "ms_per_step": ms16, "algorithmic_bytes": bytes16,
-               "gbs": bytes16 / (ms16 * 1e-3) / 1e9, "frac": bytes16 / (ms16 * 1e-3) / 1e9 / peak16,
+        ms16 = rt.timed(step16, flush=flush)
+        row = kvh * HEAD_DIM
+        bytes16 = 2 * (T16 * row * 2) * 2 + 2 * (T16 * row * 2) + 2 * (T16 * row) + 2 * 2 * nblk * kvh * 2 + T16 * 8 * 2
+        x16 = {"tokens": T16, "ms_per_step": ms16[0], "ms_per_step_min": ms16[1], "ms_per_step_max": ms16[2],
+               "algorithmic_bytes": bytes16, "gbs": bytes16 / (ms16[0] * 1e-3) / 1e9,
+               "frac": bytes16 / (ms16[0] * 1e-3) / 1e9 / rt.peaks["hbm_gbs"],
                "what": "float16 scatter + FP8 scatter of 65 536 tokens over all slots of the pool, no block copies"}
-    block16 = KV_HEADS * BLOCK * HEAD_DIM * 2
-    bytes_f16 = 2 * (T * row * 2) * 2                         # K and V: read + write
-    bytes_fp8 = 2 * (T * row * 2) + 2 * (T * row) + 2 * 2 * T * KV_HEADS * 2   # read f16, write codes, scales (upper bound)
-    bytes_cow = 2 * C1_COPIES * block16 * 2                   # K and V blocks: read + write
-    total = bytes_f16 + bytes_fp8 + bytes_cow + T * 8 * 2
-    peak, kind = measured_hbm_peak()
-    achieved = total / (ms_step * 1e-3) / 1e9
-    line = {"metric": "KV append GB/s", "value": achieved, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": warm,
-            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "f16 -> f16 / fp8-e4m3", "data": "synthetic",
-            "config": {"workload": "append_c1: 4096 tokens x 8 kv heads x 128 scattered to random distinct slots of a "
-                                   "4096-block pool as float16 and as FP8 e4m3 with (block, kv_head) scales, plus a copy of "
-                                   "512 random blocks", "seed": 1001, "l2": "flushed before every timed step (512 MB written)"},
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_source": f"{kind} copy bandwidth",
-                         "kernel": "reshapeAndCacheKernel, fp8AbsmaxKernel + fp8QuantizeKernel, copyBlocksKernel",
-                         "algorithmic_bytes_per_launch": total, "traffic": None,
-                         "note": "126 MB per step in 4 short kernels: launch latency, not HBM, bounds it"},
-            "tokens_per_s": T / (ms_step * 1e-3), "gpu_launches": int(launches), "clocks": clocks}
-    if x16 is not None:
-        line["x16"] = x16
-    print(json.dumps(line))
+    engine.setAsync(False)
+
+    # ---- e2e: new K/V rows in page-locked host memory through pamc_reshape_and_cache ----
+    e2e = (None, None, None)
+    if not args.profile:
+        k_pin, v_pin = torch.from_numpy(k_h).pin_memory(), torch.from_numpy(v_h).pin_memory()
+
+        def step_host():
+            engine.reshapeAndCache(c16, k_pin, v_pin, slots_h, T)
+            engine.reshapeAndCache(c8, k_pin, v_pin, slots_h, T)
+            engine.copyBlocks(c16, src, dst)
+
+        e2e = rt.timed_host(step_host)
+
+    line = None
+    if rank == 0:
+        total = c1_bytes(kvh)
+        peak = rt.peaks["hbm_gbs"]
+        achieved = total / (ms[0] * 1e-3) / 1e9
+        line = rt.base_line("append_c1", "KV append GB/s", achieved * rt.world, "GB/s", ms, "f16 -> f16 / fp8-e4m3", 0, launches,
+                            clocks, {"seed": 1001, "l2": "flushed before every timed step (512 MB written)"})
+        line["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                            "peak_source": f"{rt.peak_kind} copy bandwidth", "per": "GPU",
+                            "kernel": "reshapeAndCacheKernel, fp8AbsmaxPiecesKernel + fp8QuantizePiecesKernel, copyBlocksKernel",
+                            "algorithmic_bytes_per_launch": total, "traffic": None,
+                            "note": "four short kernels per step: launch latency, not HBM, bounds this size; see x16"}
+        line["tokens_per_s"] = T / (ms[0] * 1e-3)
+        io = 2 * 2 * T * kvh * HEAD_DIM * 2 + 2 * T * 8 + 2 * C1_COPIES * 4
+        line["e2e"] = {"value": total * rt.world / (e2e[0] * 1e-3) / 1e9 if e2e[0] else None, "unit": "GB/s", "ms_per_step": e2e[0],
+                       "ms_per_step_min": e2e[1], "ms_per_step_max": e2e[2], "h2d_bytes_per_step": io, "d2h_bytes_per_step": 0,
+                       "call": "pamc_reshape_and_cache (float16 and FP8 cache) with page-locked host K/V rows and a host slot "
+                               "list, pamc_copy_blocks with host block lists"}
+        if x16 is not None:
+            line["x16"] = x16
+        if with_cpu:
+            line["cpu_baseline"] = cpu_append_c1()
     c16.close()
     c8.close()
-    engine.close()
+    return line
 
 
-# ------------------------------------------- long-context FP8 decode (c4)
+# ------------------------------------------- long-context FP8 decode and step (c4)
 
-C4_SEQS, C4_LO, C4_HI, C4_WINDOW, C4_HEADS, C4_CHUNK = 64, 32768, 131072, 4096, 64, 2048
-
-
-def run_decode_fp8(args):
-    """Decode part of `configs[4]`: 64 sequences with contexts uniform in
-    [32768, 131072], sliding window 4096, FP8 e4m3 KV with per-(block, kv_head)
-    scales, 64 query / 8 KV heads, head_dim 128, block 16.  Every block of every
-    context is allocated through the manager (the pool holds all tokens, about
-    10.7 GB, as the reference never frees out-of-window blocks); K/V is written
-    (quantised by the append kernel) only for the tokens a decode can see, the
-    rest of the pool is never read.  Metric: decode tokens/s; roofline: bytes of
-    the visible window."""
-    import torch
-
-    import pagedattentionmetal_b200 as pam
-
+def run_c4(rt, with_cpu, want=("decode_c4", "step_c4")):
+    """`configs[4]`: 64 sequences with contexts uniform in [32768, 131072], sliding window
+    4096, FP8 e4m3 KV with per-(block, kv_head) scales, 64 query / 8 KV heads.  Every block of
+    every context is allocated through the manager (the pool holds all tokens, about 10.7 GB
+    over all GPUs, as the reference never frees out-of-window blocks); K/V is written
+    (quantised by the append kernel) only for the tokens a decode can see, the rest of the
+    pool is never read.  `decode_c4` is the 64 decodes; `step_c4` adds the waiting sequence of
+    the scheduler's batch: its first 2048-token chunk is appended (quantised) and prefilled
+    in the same step.  Returns {name: line}."""
+    torch, pam, engine, dev, args = rt.torch, rt.pam, rt.engine, rt.dev, rt.args
     DT = pam.PagedAttentionDataType
-    dev = torch.device("cuda", 0)
-    torch.cuda.set_device(dev)
-    engine = pam.PagedAttentionEngine(0)
-    stream = torch.cuda.Stream(dev)
-    torch.cuda.set_stream(stream)
-    engine.setStream(stream.cuda_stream)
+    kvh, heads, rank = rt.kvh, rt.heads(C4_HEADS), rt.rank
+    ksl, qsl = slice(rank * kvh, (rank + 1) * kvh), slice(rank * heads, (rank + 1) * heads)
     rng = np.random.default_rng(1004)
-    n_seq = min(C4_SEQS, args.batch) if args.batch != 256 else C4_SEQS
-    lens = rng.integers(C4_LO, C4_HI + 1, size=n_seq).astype(np.int64)
+    n_seq = C4_SEQS if args.batch is None or args.workload not in ("decode_c4", "step_c4") else min(C4_SEQS, args.batch)
+    lens = rng.integers(C4_LO, C4_HI + 1, size=C4_SEQS).astype(np.int64)[:n_seq]
     nblk = (lens + BLOCK - 1) // BLOCK
-    cache = pam.KVCacheManager(engine, int(nblk.sum()) + 256 + C4_CHUNK // BLOCK, BLOCK, HEAD_DIM, KV_HEADS, DT.float8)
+    cache = pam.KVCacheManager(engine, int(nblk.sum()) + 256 + C4_CHUNK // BLOCK, BLOCK, HEAD_DIM, kvh, DT.float8)
     gen = torch.Generator(device=dev)
-    visible = 0
     for sid in range(n_seq):
         L = int(lens[sid])
         cache.allocateSequence(sid)
         cache.appendTokens(sid, L)
         first = ((L - C4_WINDOW) // BLOCK) * BLOCK                      # first token of the first visible block
-        n = L - first
-        visible += n
         gen.manual_seed(1004 * 1000 + sid)
-        kv = torch.randn((2, n, KV_HEADS, HEAD_DIM), generator=gen, device=dev).to(torch.float16)
-        engine.appendKV(cache, sid, kv[0].contiguous(), kv[1].contiguous(), first, n, C4_HEADS)
+        kv = torch.randn((2, L - first, KV_HEADS, HEAD_DIM), generator=gen, device=dev).to(torch.float16)
+        engine.appendKV(cache, sid, kv[0][:, ksl].contiguous(), kv[1][:, ksl].contiguous(), first, L - first, heads)
+    ids = list(range(n_seq))
     max_nb = int(nblk.max())
-    tables_h, lens_h = cache.batchTables(list(range(n_seq)), max_nb)
+    tables_h, lens_h = cache.batchTables(ids, max_nb)
     tables = torch.from_numpy(tables_h).to(dev)
-    lens_dev = torch.from_numpy(lens_h.view(np.int32)).to(dev)
-    q = torch.randn((n_seq, C4_HEADS, HEAD_DIM), device=dev).to(torch.float16)
+    gen.manual_seed(1004 * 1000 + 999983)
+    q = torch.randn((n_seq, C4_HEADS, HEAD_DIM), generator=gen, device=dev).to(torch.float16)[:, qsl].contiguous()
     out = torch.empty_like(q)
-    layer = pam.PagedLayerSpec(HEAD_DIM, C4_HEADS, KV_HEADS, BLOCK, DT.float8, C4_WINDOW)
-    req = pam.PagedAttentionDecodeRequest(q, cache.kPoolBuffer, cache.vPoolBuffer, tables, lens_dev, out, n_seq, max_nb,
+    layer = pam.PagedLayerSpec(HEAD_DIM, heads, kvh, BLOCK, DT.float8, C4_WINDOW)
+    req = pam.PagedAttentionDecodeRequest(q, cache.kPoolBuffer, cache.vPoolBuffer, tables, lens_h, out, n_seq, max_nb,
                                           layer, cache.kScaleBuffer, cache.vScaleBuffer)
-    engine.decode(req)
-    # correctness guard: one sequence against the oracle (its visible pages only)
-    from oracle import c_oracle as co
-    from pagedattentionmetal_b200._cabi import lib
-    sid = int(np.argmin(lens))
-    L = int(lens[sid])
-    first_blk = (L - C4_WINDOW) // BLOCK
-    used = tables_h[sid, first_blk: (L + BLOCK - 1) // BLOCK]
-    page = KV_HEADS * BLOCK * HEAD_DIM
-    kc = np.zeros((len(used), KV_HEADS, BLOCK, HEAD_DIM), np.uint8)
-    vc = np.zeros_like(kc)
-    ks = np.zeros((len(used), KV_HEADS), np.float16)
-    vs = np.zeros_like(ks)
-    kp, vp, ksp, vsp = cache.kPoolBuffer.ptr, cache.vPoolBuffer.ptr, cache.kScaleBuffer.ptr, cache.vScaleBuffer.ptr
-    for i, b in enumerate(used):
-        lib.pamc_memcpy(engine._ctx, kc[i].ctypes.data, kp + int(b) * page, page, 1)
-        lib.pamc_memcpy(engine._ctx, vc[i].ctypes.data, vp + int(b) * page, page, 1)
-        lib.pamc_memcpy(engine._ctx, ks[i].ctypes.data, ksp + int(b) * KV_HEADS * 2, KV_HEADS * 2, 1)
-        lib.pamc_memcpy(engine._ctx, vs[i].ctypes.data, vsp + int(b) * KV_HEADS * 2, KV_HEADS * 2, 1)
-    t2 = np.zeros((1, (L + BLOCK - 1) // BLOCK), np.int32)
-    t2[0, first_blk:] = np.arange(len(used))
-    ref = co.decode(q[sid:sid + 1].cpu().numpy(), kc, vc, t2, np.array([L], np.uint32), KV_HEADS, BLOCK, 2,
-                    window=C4_WINDOW, k_scale=ks.view(np.uint16), v_scale=vs.view(np.uint16))
-    err = float(np.abs(out[sid:sid + 1].float().cpu().numpy() - ref).max())
-    assert err <= 1e-2, f"FP8 decode differs from the oracle by {err}"
+    decode = lambda: engine.decode(req)
+    decode()
+    guard_decode(rt, cache, [int(np.argmin(lens)), int(np.argmax(lens))], tables_h, lens_h, q.cpu().numpy(), out.cpu().numpy(),
+                 2, 1e-2, window=C4_WINDOW)
+    q_pin = q.cpu().pin_memory()
+    out_pin = torch.empty_like(q_pin).pin_memory()
+    engine.defaultWindowSize = C4_WINDOW                       # pam_decode takes the engine's default window
+    decode_host = lambda: engine.decodeBatch(cache, ids, q_pin.data_ptr(), out_pin.data_ptr(), heads)
+    # visible tokens per sequence: tokens in blocks >= floor((L - W) / 16); K and V codes, scales, q, out, tables
+    nvis = np.array([int(l) - ((int(l) - C4_WINDOW) // BLOCK) * BLOCK for l in lens])
+    bytes_decode = int(nvis.sum()) * 2 * kvh * HEAD_DIM + int(((nvis + BLOCK - 1) // BLOCK).sum()) * (kvh * 4 + 4) \
+        + 2 * n_seq * heads * HEAD_DIM * 2 + n_seq * 4
+    peak = rt.peaks["hbm_gbs"]
+    io_decode = n_seq * heads * HEAD_DIM * 2
+    lines = {}
 
-    # ---- the waiting sequence of the whole step (`step_c4`): its first 2048-token chunk is
-    # appended (quantised to FP8) and prefilled in the same step as the 64 decodes
-    whole = args.workload == "step_c4"
-    step_tokens = n_seq
-    decode_only = lambda: engine.decode(req)
-    step = decode_only
-    if whole:
+    def decode_roofline(ms_decode):
+        achieved = bytes_decode / (ms_decode * 1e-3) / 1e9
+        return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "peak_source": f"{rt.peak_kind} copy bandwidth", "per": "GPU",
+                "kernel": "decodeSplitFp8Kernel (splits merged by the CTA that finishes a sequence last)",
+                "algorithmic_bytes_per_launch": bytes_decode, "traffic": bytes_decode * DECODE_TRAFFIC_FACTOR["fp8"],
+                "traffic_source": "ncu on a 16-sequence cut, scaled by visible tokens"}
+
+    l2_note = {"seed": 1004, "l2": "window bytes per step (0.54 GB over all GPUs) exceed L2 up to 4 GPUs; at 8 GPUs a GPU's 67 MB "
+                                   "share fits L2 and L2 is flushed between timed steps",
+               "lengths": "host array, uploaded by every call"}
+    small = bytes_decode < 126e6
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if small else None
+    flush = (lambda: flush_buf.fill_(1)) if small else None
+
+    if "decode_c4" in want:
+        engine.setAsync(True)
+        sampler = ClockSampler(rt.local).start()
+        for _ in range(max(args.warmup, 3)):
+            decode()
+        settled = rt.settle(decode)
+        launches0 = engine.kernelLaunches
+        ms = rt.timed(decode, flush=flush)
+        launches = engine.kernelLaunches - launches0
+        engine.setAsync(False)
+        clocks = sampler.stop()
+        e2e = rt.timed_host(decode_host)
+        if not args.profile:
+            assert torch.equal(out_pin.to(dev), out), "host-buffer path and device path disagree"
+        if rank == 0:
+            line = rt.base_line("decode_c4", "paged decode tokens/s", n_seq / (ms[0] * 1e-3), "tokens/s", ms,
+                                "fp8-e4m3 KV, f16 q/out", settled, launches, clocks, l2_note)
+            line["roofline"] = decode_roofline(ms[0])
+            line["kv_read_gbs_total"] = line["roofline"]["achieved"] * rt.world
+            line["e2e"] = {"value": n_seq / (e2e[0] * 1e-3) if e2e[0] else None, "unit": "tokens/s", "ms_per_step": e2e[0],
+                           "ms_per_step_min": e2e[1], "ms_per_step_max": e2e[2],
+                           "h2d_bytes_per_step": io_decode + lens_h.nbytes, "d2h_bytes_per_step": io_decode,
+                           "call": "pam_decode (engine default window 4096) with page-locked host q/out"}
+            if with_cpu:
+                line["cpu_baseline"] = cpu_decode_c4()
+            lines["decode_c4"] = line
+
+    if "step_c4" in want:
         new_id = n_seq
         sched = pam.ContinuousBatchingScheduler(n_seq + 1, n_seq + 1)
-        ids = [sched.addRequest(int(l), 1) for l in lens]
+        sids = [sched.addRequest(int(l), 1) for l in lens]
         for q_s in sched.step():
             sched.markPrefilled(q_s.id)
         wid = sched.addRequest(8192, 1)
         batch = [q_s.id for q_s in sched.step()]              # Scheduler.swift:78-114: waiting first, then running
-        assert batch == [wid] + ids and sched.waitingCount == 0, "scheduler batch order"
+        assert batch == [wid] + sids and sched.waitingCount == 0, "scheduler batch order"
         cache.allocateSequence(new_id)
         cache.appendTokens(new_id, C4_CHUNK)
         gen.manual_seed(1004 * 1000 + new_id)
         kv_new = torch.randn((2, C4_CHUNK, KV_HEADS, HEAD_DIM), generator=gen, device=dev).to(torch.float16)
-        k_new, v_new = kv_new[0].contiguous(), kv_new[1].contiguous()
-        q_new = torch.randn((C4_CHUNK, C4_HEADS, HEAD_DIM), generator=gen, device=dev).to(torch.float16)
+        k_new, v_new = kv_new[0][:, ksl].contiguous(), kv_new[1][:, ksl].contiguous()
+        q_new = torch.randn((C4_CHUNK, C4_HEADS, HEAD_DIM), generator=gen, device=dev).to(torch.float16)[:, qsl].contiguous()
         o_new = torch.empty_like(q_new)
         t_new_h, _ = cache.batchTables([new_id], C4_CHUNK // BLOCK)
         t_new = torch.from_numpy(t_new_h).to(dev)
 
-        def step():
-            engine.appendKV(cache, new_id, k_new, v_new, 0, C4_CHUNK, C4_HEADS)
-            engine.prefillBatch(q_new, cache.kPoolBuffer, cache.vPoolBuffer, t_new, o_new, [C4_CHUNK], [0], [C4_CHUNK],
-                                C4_CHUNK // BLOCK, layer, True, cache.kScaleBuffer, cache.vScaleBuffer)
-            engine.decode(req)
+        def make_step(kk, vv, qq, oo, dec):
+            def step():
+                engine.appendKV(cache, new_id, kk, vv, 0, C4_CHUNK, heads)
+                engine.prefillBatch(qq, cache.kPoolBuffer, cache.vPoolBuffer, t_new, oo, [C4_CHUNK], [0], [C4_CHUNK],
+                                    C4_CHUNK // BLOCK, layer, True, cache.kScaleBuffer, cache.vScaleBuffer)
+                dec()
+            return step
 
+        step = make_step(k_new, v_new, q_new, o_new, decode)
         step()
         engine.synchronize()
-        prefill_tensor = None
         # correctness guard for the chunk: a few rows against the oracle on the quantised pages
-        used_n = t_new_h[0]
-        kc2 = np.zeros((len(used_n), KV_HEADS, BLOCK, HEAD_DIM), np.uint8)
-        vc2 = np.zeros_like(kc2)
-        ks2 = np.zeros((len(used_n), KV_HEADS), np.float16)
-        vs2 = np.zeros_like(ks2)
-        for i, b in enumerate(used_n):
-            lib.pamc_memcpy(engine._ctx, kc2[i].ctypes.data, kp + int(b) * page, page, 1)
-            lib.pamc_memcpy(engine._ctx, vc2[i].ctypes.data, vp + int(b) * page, page, 1)
-            lib.pamc_memcpy(engine._ctx, ks2[i].ctypes.data, ksp + int(b) * KV_HEADS * 2, KV_HEADS * 2, 1)
-            lib.pamc_memcpy(engine._ctx, vs2[i].ctypes.data, vsp + int(b) * KV_HEADS * 2, KV_HEADS * 2, 1)
+        from oracle import c_oracle as co
+        kc2, vc2, ks2, vs2 = fetch_pages(rt, cache, t_new_h[0], 1, True)
         r0, nr = C4_CHUNK - 8, 8
-        refp = co.prefill(q_new[r0:r0 + nr].cpu().numpy(), kc2, vc2, np.arange(len(used_n), dtype=np.int32), C4_CHUNK,
-                          KV_HEADS, BLOCK, 2, q_start=r0, k_scale=ks2.view(np.uint16), v_scale=vs2.view(np.uint16))
+        refp = co.prefill(q_new[r0:r0 + nr].cpu().numpy(), kc2, vc2, np.arange(len(t_new_h[0]), dtype=np.int32), C4_CHUNK,
+                          kvh, BLOCK, 2, q_start=r0, k_scale=ks2.view(np.uint16), v_scale=vs2.view(np.uint16))
         errp = float(np.abs(o_new[r0:r0 + nr].float().cpu().numpy() - refp).max())
         assert errp <= 1e-2, f"FP8 prefill chunk differs from the oracle by {errp}"
-        step_tokens = n_seq + C4_CHUNK
 
-    engine.setAsync(True)
-    sampler = ClockSampler(0)
-    sampler.start()
-    warm = max(args.warmup, 3)
-    for _ in range(warm):
-        step()
-    t_busy = time.perf_counter()
-    while not args.profile and time.perf_counter() - t_busy < 0.5:
-        for _ in range(10):
+        engine.setAsync(True)
+        sampler = ClockSampler(rt.local).start()
+        for _ in range(max(args.warmup, 3)):
             step()
-        torch.cuda.synchronize(dev)
-        warm += 10
-    torch.cuda.synchronize(dev)
-    launches0 = engine.kernelLaunches
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for _ in range(args.steps):
-        step()
-    e1.record(stream)
-    torch.cuda.synchronize(dev)
-    engine.synchronize()        # raises if a kernel of the timed region reported an error
-    ms_step = e0.elapsed_time(e1) / args.steps
-    launches = engine.kernelLaunches - launches0
-    ms_decode = ms_step
-    if whole:
-        # the decode launches alone, for the roofline of the HBM-bound kernel of the step
-        d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        d0.record(stream)
-        for _ in range(args.steps):
-            engine.decode(req)
-        d1.record(stream)
-        torch.cuda.synchronize(dev)
-        engine.synchronize()
-        ms_decode = d0.elapsed_time(d1) / args.steps
-    # The same decode launches replayed from a CUDA graph: the device time of the kernels
-    # without the host's per-call work (request checks, launch calls), which is of the same
-    # order as this short step.
-    ms_graph = None
-    try:
-        if args.profile:
-            raise RuntimeError("skipped under --profile")
-        graph = torch.cuda.CUDAGraph()
-        cap = torch.cuda.Stream(dev)
-        cap.wait_stream(stream)
-        engine.setStream(cap.cuda_stream)
-        with torch.cuda.graph(graph, stream=cap):
-            for _ in range(args.steps):
-                engine.decode(req)
-        engine.setStream(stream.cuda_stream)
-        stream.wait_stream(cap)
-        for _ in range(3):
-            graph.replay()
-        torch.cuda.synchronize(dev)
-        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        g0.record(stream)
-        graph.replay()
-        g1.record(stream)
-        torch.cuda.synchronize(dev)
-        engine.synchronize()
-        ms_graph = g0.elapsed_time(g1) / args.steps
-    except Exception as exc:           # capture refused: the eager figures stand alone
-        engine.setStream(stream.cuda_stream)
-        print(f"graph replay not measured: {exc}", file=sys.stderr)
-    clocks = sampler.stop()
-    # visible tokens per sequence: tokens in blocks >= floor((L - W) / 16); K and V codes, scales, q, out, tables
-    nvis = np.array([int(l) - ((int(l) - C4_WINDOW) // BLOCK) * BLOCK for l in lens])
-    bytes_step = int(nvis.sum()) * 2 * KV_HEADS * HEAD_DIM + int(((nvis + BLOCK - 1) // BLOCK).sum()) * (KV_HEADS * 4 + 4) \
-        + 2 * n_seq * C4_HEADS * HEAD_DIM * 2 + n_seq * 4
-    peak, kind = measured_hbm_peak()
-    achieved = bytes_step / (ms_decode * 1e-3) / 1e9
-    line = {"metric": "step tokens/s" if whole else "paged decode tokens/s", "value": step_tokens / (ms_step * 1e-3),
-            "unit": "tokens/s", "n_gpus": 1,
-            "steps": args.steps, "warmup": warm, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "fp8-e4m3 KV, f16 q/out", "data": "synthetic",
-            "config": {"workload": ("step_c4: one scheduler step = append + prefill of a 2048-token chunk of a new "
-                                    "sequence, and " if whole else "decode_c4: ") +
-                                   f"{n_seq} seqs, context U[32768,131072], window 4096, FP8 e4m3 KV with "
-                                   "(block, kv_head) scales, 64 q / 8 kv heads, head_dim 128, block 16", "seed": 1004,
-                       "l2": "window bytes per step (0.54 GB) exceed L2; contexts are resident, only the window is read"},
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_source": f"{kind} copy bandwidth", "kernel": "decodeSplitFp8Kernel (+ decodeMergeKernel)",
-                         "algorithmic_bytes_per_launch": bytes_step, "traffic": None},
-            "gpu_launches": int(launches), "clocks": clocks}
-    if ms_graph is not None:
-        line["graph_replay"] = {"decode_ms_per_step": ms_graph, "kv_read_gbs": bytes_step / (ms_graph * 1e-3) / 1e9,
-                                "frac": bytes_step / (ms_graph * 1e-3) / 1e9 / peak}
-    if whole:
-        pf_flops = C4_HEADS * (C4_CHUNK * (C4_CHUNK + 1) // 2) * 4 * HEAD_DIM
-        line["step_parts"] = {"decode_ms": ms_decode, "append_and_prefill_ms": ms_step - ms_decode,
-                              "prefill_chunk_gflop": pf_flops / 1e9,
-                              "prefill_path": "FP8 pages dequantised to float16 scratch, then prefillTcKernel"}
-    print(json.dumps(line))
+        settled = rt.settle(step)
+        launches0 = engine.kernelLaunches
+        ms = rt.timed(step, flush=flush)
+        launches = engine.kernelLaunches - launches0
+        ms_dec = rt.timed(decode, flush=flush)              # the decode launches alone, for the roofline of the HBM-bound part
+        engine.setAsync(False)
+        clocks = sampler.stop()
+        e2e = (None, None, None)
+        io_new = C4_CHUNK * heads * HEAD_DIM * 2
+        kv_new_bytes = 2 * C4_CHUNK * kvh * HEAD_DIM * 2
+        if not args.profile:
+            pins = [t.cpu().pin_memory() for t in (k_new, v_new, q_new)]
+            o_pin = torch.empty_like(pins[2]).pin_memory()
+            e2e = rt.timed_host(make_step(pins[0], pins[1], pins[2], o_pin, decode_host))
+            assert torch.equal(o_pin.to(dev), o_new), "host-buffer path and device path disagree"
+        if rank == 0:
+            tokens = n_seq + C4_CHUNK
+            line = rt.base_line("step_c4", "step tokens/s", tokens / (ms[0] * 1e-3), "tokens/s", ms, "fp8-e4m3 KV, f16 q/out",
+                                settled, launches, clocks, l2_note)
+            line["roofline"] = decode_roofline(ms_dec[0])
+            pf_flops = C4_HEADS * (C4_CHUNK * (C4_CHUNK + 1) // 2) * 4 * HEAD_DIM
+            rest = ms[0] - ms_dec[0]
+            line["step_parts"] = {"decode_ms": ms_dec[0], "append_and_prefill_ms": rest,
+                                  "prefill_chunk_gflop": pf_flops / 1e9,
+                                  "prefill_chunk_tflops_lower_bound": pf_flops / (rest * 1e-3) / 1e12 if rest > 0 else None,
+                                  "prefill_path": "FP8 pages dequantised to float16 scratch, then prefillTcKernel"}
+            line["e2e"] = {"value": tokens / (e2e[0] * 1e-3) if e2e[0] else None, "unit": "tokens/s", "ms_per_step": e2e[0],
+                           "ms_per_step_min": e2e[1], "ms_per_step_max": e2e[2],
+                           "h2d_bytes_per_step": io_decode + lens_h.nbytes + io_new + kv_new_bytes,
+                           "d2h_bytes_per_step": io_decode + io_new,
+                           "call": "pam_append_kv + pamc_prefill_batch + pam_decode with page-locked host K/V rows, q and out"}
+            lines["step_c4"] = line
+    engine.defaultWindowSize = 0
     cache.close()
-    engine.close()
+    return lines
+
+
+def run_ours(args):
+    rt = Runtime(args)
+    with_cpu = rt.world == 1 and not args.profile
+    names = [args.workload] if args.workload else list(WORKLOADS)
+    results = {}
+    for name in names:
+        if name in results:
+            continue
+        if name == "decode_c2":
+            results[name] = run_decode_c2(rt, with_cpu)
+        elif name == "prefill_c3":
+            results[name] = run_prefill_c3(rt, with_cpu)
+        elif name == "append_c1":
+            results[name] = run_append_c1(rt, with_cpu)
+        else:
+            want = [n for n in names if n in ("decode_c4", "step_c4")]
+            out = run_c4(rt, with_cpu, want)
+            for n in want:
+                results[n] = out.get(n)
+        rt.torch.cuda.empty_cache()
+    if rt.rank == 0:
+        line = results[names[0]]
+        if len(names) > 1:
+            line["also"] = {n: results[n] for n in names[1:]}
+        print(json.dumps(line))
+    rt.close()
 
 
 def main():
@@ -914,24 +1121,18 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--blocks", type=int, default=10, help="timed blocks of --steps steps each; the median block is reported")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--batch", type=int, default=BATCH,
-                    help="number of sequences (default: the workload's 256; smaller values are for profiler captures)")
-    ap.add_argument("--workload", default="decode_c2", choices=["decode_c2", "prefill_c3", "decode_c4", "step_c4", "append_c1"],
-                    help="decode_c2 is the headline workload; prefill_c3 reports prefill TFLOP/s (1 GPU)")
+    ap.add_argument("--batch", type=int, default=None,
+                    help="number of sequences of the chosen workload (smaller values are for profiler captures)")
+    ap.add_argument("--workload", default=None, choices=list(WORKLOADS),
+                    help="one workload alone; default: decode_c2 with the others under `also`")
+    ap.add_argument("--shards", type=int, default=None,
+                    help="single process only: run KV-head group 0 of this many (the per-GPU share of a larger job)")
     ap.add_argument("--profile", action="store_true",
-                    help="profiler run: no clock-settling loop, no end-to-end leg, no CPU baseline")
+                    help="profiler run: one timed block, no clock-settling loop, no end-to-end leg, no CPU baseline")
     args = ap.parse_args()
-    globals()["BATCH"] = args.batch
-    if args.workload == "prefill_c3" and args.batch != 256:
-        globals()["PF_SEQS"] = args.batch
-    if args.workload == "prefill_c3" and args.impl == "ours":
-        run_prefill(args)
-    elif args.workload == "append_c1" and args.impl == "ours":
-        run_append(args)
-    elif args.workload in ("decode_c4", "step_c4") and args.impl == "ours":
-        run_decode_fp8(args)
-    elif args.impl == "reference":
+    if args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

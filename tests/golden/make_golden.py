@@ -145,6 +145,64 @@ def main():
             caus[i, h] = sim_call(sim, qs, kp, vp, table[: (n + bs - 1) // bs], bs, hd)[0]
     np.savez(os.path.join(HERE, "prefill_small.npz"), q=q, k_pool=k_pool, v_pool=v_pool,
              table=table, out_full=full, out_causal=caus)
+    # 5. Sliding-window decode (kernels.metal:1442, 1464: keys [L - W, L) when L > W).  The
+    #    reference function has no window argument; the same arithmetic over the same token
+    #    set is obtained by re-packing tokens [ws, L) of a sequence into fresh blocks and
+    #    calling it on those.  Windows that do and do not start on a block boundary.
+    rng, lens, tables, n_pool = po.make_decode_case(21, batch=6, len_lo=20, len_hi=200, heads=8,
+                                                    kv_heads=2, head_dim=32, block_size=16,
+                                                    spare_blocks=2)
+    k_pool, v_pool = fill_pools(rng, n_pool, 2, 16, 32, tables, lens)
+    q = rng.standard_normal((6, 8, 32), dtype=np.float32)
+    windows = np.array([48, 50, 1, 16, 500], dtype=np.int32)
+    outs = np.zeros((len(windows), 6, 8, 32), dtype=np.float64)
+    for wi, W in enumerate(windows):
+        for b in range(6):
+            L = int(lens[b])
+            ws = L - int(W) if L > int(W) else 0
+            n = L - ws
+            slots = po.slot_mapping(tables[b], ws, n, 16)
+            # tokens [ws, L) of every KV head, in order, into blocks 0, 1, ... of a fresh pool
+            nb = (n + 15) // 16
+            kp = np.zeros((nb, 2, 16, 32), dtype=np.float32)
+            vp = np.zeros_like(kp)
+            for t, slot in enumerate(slots):
+                kp[t // 16, :, t % 16] = k_pool[slot // 16, :, slot % 16]
+                vp[t // 16, :, t % 16] = v_pool[slot // 16, :, slot % 16]
+            outs[wi, b] = sim_decode(sim, q[b:b + 1], kp, vp, np.arange(nb, dtype=np.int32)[None, :],
+                                     np.array([n]), 2, 16)[0]
+    np.savez(os.path.join(HERE, "decode_window.npz"), q=q, k_pool=k_pool, v_pool=v_pool, tables=tables,
+             lens=lens, windows=windows, out=outs)
+
+    # 6. Prefill with a window that starts on a block boundary (the only case in which the
+    #    reference's loop reads the keys it labels, kernels.metal:734-746): S = 64, block 8,
+    #    window 40, so window_start = 24.  Non-causal rows see keys [24, 64); causal row
+    #    i >= 24 sees keys [24, i]; causal rows below 24 see nothing (0/0 in the reference),
+    #    stored as NaN.
+    rng = np.random.default_rng(23)
+    S, bs, hd, H, KVH, W = 64, 8, 16, 4, 2, 40
+    ws = S - W
+    nb = S // bs
+    table = rng.permutation(10)[:nb].astype(np.int32)
+    k_pool = rng.standard_normal((10, KVH, bs, hd), dtype=np.float32)
+    v_pool = rng.standard_normal((10, KVH, bs, hd), dtype=np.float32)
+    q = rng.standard_normal((S, H, hd), dtype=np.float32)
+    inv = np.float32(1.0) / np.sqrt(np.float32(hd))
+    wtable = table[ws // bs:]                      # the pages of tokens [ws, S), already block aligned
+    full = np.zeros((S, H, hd))
+    caus = np.full((S, H, hd), np.nan)
+    for h in range(H):
+        kvh = h // (H // KVH)
+        kp, vp = np.ascontiguousarray(k_pool[:, kvh]), np.ascontiguousarray(v_pool[:, kvh])
+        for i in range(S):
+            qs = np.tile((q[i, h] * inv)[None, :], (W, 1))
+            full[i, h] = sim_call(sim, qs, kp, vp, wtable, bs, hd)[0]
+            if i >= ws:
+                n = i + 1 - ws
+                qs = np.tile((q[i, h] * inv)[None, :], (n, 1))
+                caus[i, h] = sim_call(sim, qs, kp, vp, wtable[: (n + bs - 1) // bs], bs, hd)[0]
+    np.savez(os.path.join(HERE, "prefill_window.npz"), q=q, k_pool=k_pool, v_pool=v_pool, table=table,
+             window=np.array(W), out_full=full, out_causal=caus)
     print("golden vectors written to", HERE)
 
 

@@ -168,3 +168,161 @@ def test_reference_cabi_decode_end_to_end(engine, dtype):
                         v_scale=None if gvs is None else gvs.view(np.uint16))
         assert_close(out.astype(np.float32), ref, dtype)
     cache.close()
+
+
+def test_golden_decode_window(engine, golden_dir):
+    """Sliding-window decode against the reference's numpy implementation run over the
+    window's tokens (tests/golden/make_golden.py, case 5): float32 through the general
+    kernel, and the same data as float16 through the split-K kernels (head_dim 64 copy)."""
+    g = np.load(os.path.join(golden_dir, "decode_window.npz"))
+    for wi, w in enumerate(g["windows"]):
+        out = _flat_decode_f32(engine, g["q"], g["k_pool"], g["v_pool"], g["tables"], g["lens"], 2, 16, window=int(w))
+        assert max_abs(out, g["out"][wi]) < 1e-4
+
+
+@pytest.mark.parametrize("dtype", [DT.float16, DT.bfloat16, DT.float8])
+@pytest.mark.parametrize("window", [0, 700])
+def test_host_planned_launch_matches_oracle(engine, dtype, window):
+    """Lengths in host memory: the launch is planned from them (a work list of equal
+    ranges, longest first, splits merged by the CTA that finishes last).  Lengths from 0 to
+    several thousand tokens in one batch, twice (the second call finds the list unchanged),
+    then with other lengths (the list is rebuilt)."""
+    lens = [0, 1, 15, 16, 17, 300, 1024, 1025, 2500, 4000, 6000, 33, 512, 4096, 5, 7000]
+    case = DecodeCase(31, len(lens), 1, 1, 8, 2, 128, 16, dtype, lens=lens)
+    kp, vp = engine.makeBufferFrom(case.k_pool), engine.makeBufferFrom(case.v_pool)
+    ks = engine.makeBufferFrom(case.k_scale) if case.k_scale is not None else None
+    vs = engine.makeBufferFrom(case.v_scale) if case.v_scale is not None else None
+    q, tables = engine.makeBufferFrom(case.q), engine.makeBufferFrom(case.tables)
+    ref = case.oracle(window=window)
+
+    def run(lens_arg):
+        out = engine.makeBuffer(case.q.nbytes)
+        engine.decode(pam.PagedAttentionDecodeRequest(q, kp, vp, tables, lens_arg, out, len(lens), case.tables.shape[1],
+                                                      case.layer(window), ks, vs))
+        return from_io(out.download(case.q.dtype, case.q.shape), dtype)
+
+    host = run(case.lens)
+    assert np.all(host[0] == 0)
+    assert_close(host[1:], ref[1:], dtype)
+    assert_close(run(case.lens)[1:], ref[1:], dtype)
+    device = run(engine.makeBufferFrom(case.lens))           # planned on the device side of the same kernels
+    assert_close(device[1:], ref[1:], dtype)
+    shorter = np.maximum(case.lens // 3, 1).astype(np.uint32)
+    case.lens = shorter
+    assert_close(run(shorter), case.oracle(window=window), dtype)
+
+
+def test_misaligned_query_takes_the_general_kernel(engine):
+    """A query pointer the split kernels' word loads cannot take: the general kernel
+    runs instead and the result is the same."""
+    case = DecodeCase(32, 3, 10, 300, 8, 2, 128, 16, DT.float16)
+    kp, vp = engine.makeBufferFrom(case.k_pool), engine.makeBufferFrom(case.v_pool)
+    raw = engine.makeBuffer(case.q.nbytes + 16)
+    raw.upload(case.q, offset=2)
+    out = engine.makeBuffer(case.q.nbytes)
+    req = pam.PagedAttentionDecodeRequest(raw.data_ptr() + 2, kp, vp, case.tables, case.lens, out, 3, case.tables.shape[1],
+                                          case.layer())
+    assert pam.PagedAttentionEngine.decodePath(req) == 0
+    engine.decode(req)
+    assert_close(from_io(out.download(np.float16, case.q.shape), DT.float16), case.oracle(), DT.float16)
+
+
+def _oracle_of_cache(cache, ids, q, kvh, bs, dtype, window=0):
+    from oracle import c_oracle as co
+    gk, gv, gks, gvs = cache.readPools()
+    tables, l = cache.batchTables(ids, max(max(cache.getNumBlocks(i) for i in ids), 1))
+    return co.decode(q, gk, gv, tables, l, kvh, bs, int(dtype), window=window,
+                     k_scale=None if gks is None else gks.view(np.uint16),
+                     v_scale=None if gvs is None else gvs.view(np.uint16))
+
+
+def test_pam_decode_follows_table_changes(engine):
+    """pam_decode keeps the batch's block tables on the device and sends only what changed.
+    Every kind of change between two calls must reach the kernels: tokens appended inside a
+    block and across a block boundary, a block replaced by copy-on-write, a sequence freed
+    and allocated again under the same id, the id list reordered, shortened and extended."""
+    rng = np.random.default_rng(33)
+    H, KVH, D, bs = 8, 2, 128, 16
+    cache = pam.KVCacheManager(engine, 256, bs, D, KVH, DT.float16)
+    lens = {}
+
+    def grow(sid, n, hashes=None):
+        if sid not in lens:
+            cache.allocateSequence(sid)
+            lens[sid] = 0
+        cache.appendTokens(sid, n, hashes)
+        k = rng.standard_normal((n, KVH, D)).astype(np.float16)
+        v = rng.standard_normal((n, KVH, D)).astype(np.float16)
+        engine.appendKV(cache, sid, k, v, lens[sid], n, H)
+        lens[sid] += n
+
+    def check(ids):
+        q = rng.standard_normal((len(ids), H, D)).astype(np.float16)
+        out = np.zeros_like(q)
+        engine.decodeBatch(cache, ids, q, out, H)
+        assert_close(out.astype(np.float32), _oracle_of_cache(cache, ids, q, KVH, bs, DT.float16), DT.float16)
+
+    for sid, n in enumerate((37, 5, 80, 1, 130, 600)):
+        grow(sid, n)
+    ids = [2, 0, 4, 3, 1, 5]
+    check(ids)
+    check(ids)                                   # nothing changed: only the lengths go up again
+    for sid in ids:
+        grow(sid, 1)                             # one decode step: sequence 2 crosses a block boundary (80 -> 81)
+    check(ids)
+    grow(0, 40)
+    grow(5, 500)                                 # many new blocks in one row
+    check(ids)
+    check([5, 1, 0])                             # reordered and shorter
+    check(ids + [3, 3])                          # longer, with a repeated id
+    # free + allocate under the same id: other pages, possibly fewer of them
+    cache.freeSequence(4)
+    del lens[4]
+    grow(4, 20)
+    check(ids)
+    # copy-on-write replaces a table entry without changing the table's length
+    grow(10, 24, [901, 902])
+    grow(11, 24, [901, 902])                     # shares block 0 and the half-full block 1
+    check([10, 11, 2])
+    before = cache.getBlockTable(11)
+    grow(11, 3)                                  # the shared last block is copied first
+    after = cache.getBlockTable(11)
+    assert before[0] == after[0] and before[1] != after[1] and len(after) == 2
+    check([10, 11, 2])
+    cache.ensureExclusiveAccess(11, 0)
+    assert cache.getBlockTable(11)[0] != after[0]
+    check([10, 11, 2])
+    # an unknown id fails like the reference's and leaves the cache usable
+    with pytest.raises(pam.KVCacheError) as e:
+        check([2, 999])
+    assert e.value.case == "sequenceNotFound"
+    check(ids)
+    cache.close()
+
+
+def test_pam_decode_host_memory_kinds(engine):
+    """Query and output in pageable host memory (staged), in page-locked host memory (the
+    output is written by the kernels through its device-side address) and in device memory
+    give the same bits."""
+    torch = pytest.importorskip("torch")
+    rng = np.random.default_rng(34)
+    H, KVH, D, bs = 16, 2, 128, 16
+    cache = pam.KVCacheManager(engine, 512, bs, D, KVH, DT.float16)
+    ids = list(range(5))
+    for sid, L in zip(ids, (900, 3000, 17, 1500, 260)):
+        cache.allocateSequence(sid)
+        cache.appendTokens(sid, L)
+        engine.appendKV(cache, sid, rng.standard_normal((L, KVH, D)).astype(np.float16),
+                        rng.standard_normal((L, KVH, D)).astype(np.float16), 0, L, H)
+    q = rng.standard_normal((5, H, D)).astype(np.float16)
+    pageable = np.zeros_like(q)
+    engine.decodeBatch(cache, ids, q, pageable, H)
+    assert_close(pageable.astype(np.float32), _oracle_of_cache(cache, ids, q, KVH, bs, DT.float16), DT.float16)
+    q_pin = torch.from_numpy(q).pin_memory()
+    out_pin = torch.zeros_like(q_pin).pin_memory()
+    engine.decodeBatch(cache, ids, q_pin.data_ptr(), out_pin.data_ptr(), H)
+    assert np.array_equal(out_pin.numpy().view(np.uint16), pageable.view(np.uint16))
+    q_dev, out_dev = engine.makeBufferFrom(q), engine.makeBuffer(q.nbytes)
+    engine.decodeBatch(cache, ids, q_dev.data_ptr(), out_dev.data_ptr(), H)
+    assert np.array_equal(out_dev.download(np.float16, q.shape).view(np.uint16), pageable.view(np.uint16))
+    cache.close()

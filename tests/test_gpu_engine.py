@@ -159,3 +159,58 @@ def test_batch_manager_slabs(engine):
     with pytest.raises(pam.KVCacheError):
         m.getBatchBlockTableBuffer([1, 2, 1, 2, 1])                          # more than maxBatchSize (KVCM:664-666)
     m.close()
+
+
+def test_bounded_wait_runs_out_and_the_context_stays_usable():
+    """Every wait inside the tensor-core prefill kernel is bounded.  With the wait limit set
+    to about a millisecond and the test switch that keeps each CTA's first value tile from
+    being fetched, the wait for that tile runs out: the kernel returns through its error exit
+    (nothing spins, nothing faults), the call fails with the site of the wait, the retry loop
+    and the zero fill of graceful degradation take over as for any failed launch, and the
+    next prefill on the same context is correct."""
+    from test_gpu_prefill import PrefillCase
+    from gpu_helpers import assert_close
+    engine = pam.PagedAttentionEngine()
+    case = PrefillCase(61, 300, 8, 2, 128, 16, DT.float16)
+    ref = case.oracle()
+    engine.setWaitLimit(2_000_000)                       # about 1 ms of SM clock cycles
+    # one starved launch: the first attempt fails, the retry succeeds (PagedAttentionEngine.swift:375-400)
+    engine.testStarvePrefill(1)
+    before = engine.kernelLaunches
+    assert_close(case.run(engine), ref, DT.float16)
+    assert engine.lastStats.operation == pam.Operation.prefillMMA and engine.kernelLaunches - before == 2
+    # every attempt starved, errors reported: the message names the wait that gave up
+    engine.enableGracefulDegradation = False
+    engine.testStarvePrefill(3)
+    with pytest.raises(pam.PagedAttentionError) as e:
+        case.run(engine)
+    assert e.value.case == "commandExecutionFailed"
+    assert "a kernel's bounded wait ran out (site " in str(e.value)
+    assert engine.lastError == str(e.value)
+    # the same with graceful degradation: no error, the output is zero-filled (:408-414)
+    engine.enableGracefulDegradation = True
+    engine.testStarvePrefill(3)
+    assert np.all(case.run(engine) == 0)
+    assert engine.lastError is None
+    # and the context works as before, with the default limit as well
+    assert_close(case.run(engine), ref, DT.float16)
+    engine.setWaitLimit(0)
+    assert_close(case.run(engine, q_start=100, q_len=150), case.oracle(q_start=100, q_len=150), DT.float16)
+    engine.close()
+
+
+def test_allgather_heads_single_rank(engine):
+    """One rank: the gathered tensor is the local one (the NCCL path needs a GPU per rank
+    and is exercised by the multi-GPU benchmark)."""
+    try:
+        comm = engine.joinComm(pam.PagedAttentionEngine.makeCommId(), 0, 1)
+    except pam.PagedAttentionError:
+        pytest.skip("NCCL is not loadable here")
+    local = np.random.default_rng(62).standard_normal((5, 4, 128)).astype(np.float16)
+    src, dst = engine.makeBufferFrom(local), engine.makeBuffer(local.nbytes)
+    engine.allGatherHeads(comm, src, dst, 5, 4, 128, DT.float16)
+    assert np.array_equal(dst.download(np.float16, local.shape), local)
+    with pytest.raises(pam.PagedAttentionError) as e:
+        engine.allGatherHeads(comm, src, dst, 5, 1, 4, DT.float16)       # an 8-byte slice
+    assert e.value.case == "unsupported" and "multiple of 16" in str(e.value)
+    pam.PagedAttentionEngine.leaveComm(comm)

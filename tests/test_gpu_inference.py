@@ -149,3 +149,84 @@ def test_fp8_layers(engine):
     _same_state(inf, ora, range(2))
     assert inf.completedCount == 2
     inf.close()
+
+
+def _run_pair(inf, ora, ids, steps=120):
+    for _ in range(steps):
+        err = None
+        try:
+            want = ora.step()
+        except po.SequenceNotFound:
+            err = "sequenceNotFound"
+        except po.OutOfMemory:
+            err = "outOfMemory"
+        if err:
+            with pytest.raises(pam.KVCacheError) as e:
+                inf.step()
+            assert e.value.case == err
+        else:
+            assert [s.id for s in inf.step()] == want
+        _same_state(inf, ora, ids)
+        if not err and not want:
+            return
+    raise AssertionError("did not finish")
+
+
+@pytest.mark.parametrize("blocks", [64, 14])
+def test_batched_prefill_leaves_the_reference_state(engine, blocks):
+    """With pamc_infer_set_batched_prefill the prompts of a step are prefilled by one launch
+    per layer; batches, block tables, lengths, statuses and counters stay those of the
+    reference's one-sequence-per-dispatch loop, step by step, under memory pressure too."""
+    inf, ora = _pair(engine, blocks, 4)
+    inf.setBatchedPrefill(True)
+    plain, _ = _pair(engine, blocks, 4)
+    requests = ((40, 3), (17, 1), (48, 5), (5, 2)) if blocks == 64 else ((48, 8), (48, 8), (48, 8))
+    for prompt, new in requests:
+        assert inf.addRequest(prompt, new) == ora.add_request(prompt, new)
+        plain.addRequest(prompt, new)
+    ids = list(range(len(requests)))
+    assert [s.id for s in inf.step()] == ora.step()
+    plain.step()
+    _same_state(inf, ora, ids)
+    # one launch set for the whole step instead of one per prompt
+    assert inf.prefillLaunchSets == 1 and plain.prefillLaunchSets == len(requests)
+    if blocks == 14:
+        assert [s.id for s in inf.step()] == ora.step()
+        inf.addRequest(90, 2), ora.add_request(90, 2)
+        ids.append(3)
+    _run_pair(inf, ora, ids)
+    inf.close()
+    plain.close()
+
+
+def test_prefill_token_budget_spreads_prompts_over_steps(engine):
+    """A budget of 64 prompt rows per step: a 150-token prompt takes three steps, the prompts
+    behind it wait, nothing decodes before its whole prompt is done, and the run ends with
+    the same totals as without a budget."""
+    inf, _ = _pair(engine, 64, 8)
+    inf.setBatchedPrefill(True, 64)
+    prompts = ((150, 2), (20, 3), (70, 1), (10, 2))
+    for prompt, new in prompts:
+        inf.addRequest(prompt, new)
+    tokens = []
+    inf.onTokenGenerated = lambda sid, tok: tokens.append(sid)
+    seen_first_token_at = {}
+    for step in range(40):
+        before, decoded = inf.totalTokensGenerated, len(tokens)
+        batch = inf.step()
+        if not batch:
+            break
+        for sid in tokens:
+            seen_first_token_at.setdefault(sid, step)
+        # prompt tokens are counted when a prompt completes (:216): the prompts completed in
+        # one step are the ones whose last chunk fitted the budget of 64 rows
+        completed_prompt_tokens = inf.totalTokensGenerated - before - (len(tokens) - decoded)
+        assert completed_prompt_tokens in (0, 150, 20, 70, 10, 20 + 10, 70 + 10, 20 + 70)
+    assert inf.completedCount == 4 and inf.cache.availableBlocks == 64
+    assert inf.totalTokensGenerated == sum(p + n for p, n in prompts)
+    # 150 rows at 64 per step: the first sequence cannot decode before the fourth step
+    assert seen_first_token_at[0] >= 3
+    # prompts 1 and 2 share the budget left over behind it, in arrival order
+    assert seen_first_token_at[1] <= seen_first_token_at[2] <= seen_first_token_at[3] + 1
+    assert inf.prefillLaunchSets >= 4
+    inf.close()

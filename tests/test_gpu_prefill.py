@@ -424,3 +424,19 @@ def test_fp8_staged_pages_follow_the_reference_dequant_chain(engine):
     assert finite.mean() > 0.99
     assert np.array_equal(out[finite], want[finite])
     assert len(np.unique(v_codes[:, :, 0, :])) == 256
+
+
+def test_golden_prefill_window(engine, golden_dir):
+    """Prefill with a block-aligned window start against the reference's numpy
+    implementation run over the window's tokens (tests/golden/make_golden.py, case 6); causal
+    rows below the window start see no key (0/0 in the reference) and come back as zeros."""
+    g = np.load(os.path.join(golden_dir, "prefill_window.npz"))
+    S, W = g["q"].shape[0], int(g["window"])
+    kp, vp = engine.makeBufferFrom(g["k_pool"]), engine.makeBufferFrom(g["v_pool"])
+    for causal, key in ((False, "out_full"), (True, "out_causal")):
+        out = np.full_like(g["q"], 7.0)
+        engine.prefill(pam.PagedAttentionPrefillRequest(g["q"], kp, vp, g["table"], out, S,
+                                                        pam.PagedLayerSpec(16, 4, 2, 8, DT.float32, W), causal))
+        seen = ~np.isnan(g[key])
+        assert max_abs(out[seen], g[key][seen]) < 1e-4
+        assert np.all(out[~seen] == 0)

@@ -80,6 +80,39 @@ def test_prefill_small_vs_sim(golden_dir):
     assert np.abs(chunk - g["out_causal"][8:24]).max() < 1e-5
 
 
+def test_window_decode_vs_sim(golden_dir):
+    """Sliding-window decode against the reference's numpy implementation run over tokens
+    [L - W, L) re-packed into fresh blocks (tests/golden/make_golden.py, case 5)."""
+    g = _load(golden_dir, "decode_window.npz")
+    for wi, w in enumerate(g["windows"]):
+        args = (g["q"], g["k_pool"], g["v_pool"], g["tables"], g["lens"], 2, 16)
+        assert np.abs(co.decode(*args, po.DT_F32, window=int(w)) - g["out"][wi]).max() < 1e-5
+        for online in (False, True):
+            assert np.abs(po.paged_decode(*args, window=int(w), online=online) - g["out"][wi]).max() < 1e-5
+    # the windows really cut: the unwindowed result differs
+    full = co.decode(g["q"], g["k_pool"], g["v_pool"], g["tables"], g["lens"], 2, 16, po.DT_F32)
+    assert np.abs(full - g["out"][0]).max() > 1e-2
+
+
+def test_window_prefill_vs_sim(golden_dir):
+    """Prefill with a block-aligned window start against the same (case 6): rows below the
+    window start see no key when causal (0/0 in the reference) and are not compared."""
+    g = _load(golden_dir, "prefill_window.npz")
+    S, W = g["q"].shape[0], int(g["window"])
+    ws = S - W
+    args = (g["q"], g["k_pool"], g["v_pool"], g["table"], S, 2, 8)
+    seen = ~np.isnan(g["out_causal"])
+    assert seen[ws:].all() and not seen[:ws].any()
+    for causal, want in ((False, g["out_full"]), (True, g["out_causal"])):
+        for got in (po.paged_prefill(*args, causal=causal, window_start=ws),
+                    co.prefill(*args, po.DT_F32, causal=causal, window_start=ws)):
+            mask = ~np.isnan(want)
+            assert np.abs(got[mask] - want[mask]).max() < 1e-5
+    chunk = co.prefill(g["q"][40:56], g["k_pool"], g["v_pool"], g["table"], S, 2, 8, po.DT_F32, causal=True,
+                       window_start=ws, q_start=40)
+    assert np.abs(chunk - g["out_causal"][40:56]).max() < 1e-5
+
+
 def test_window_decode_np_vs_c():
     rng, lens, tables, n_pool = po.make_decode_case(3, 4, 30, 90, 4, 2, head_dim=16, block_size=8, spare_blocks=2)
     k_pool = rng.standard_normal((n_pool, 2, 8, 16), dtype=np.float32)

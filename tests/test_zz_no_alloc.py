@@ -76,3 +76,41 @@ def test_noalloc_decode_rejects_what_it_cannot_hold():
                                                              out, 1, max_nb, layer))
     assert "device memory only" in str(e.value)
     engine.close()
+
+
+def test_noalloc_decode_allocates_nothing_and_can_be_recorded():
+    """Free device memory and the context's arena stay as they were across the call, and a
+    call made while the stream is being captured only records its launches (no wait, no
+    retry loop): the replayed graph gives the bits of pamc_decode."""
+    torch = pytest.importorskip("torch")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    engine = pam.PagedAttentionEngine(0)
+    case = DecodeCase(53, 3, 3000, 6000, 8, 2, 128, 16, DT.float16)
+    req, out = _device_request(engine, case)
+    engine.decode(req)
+    expected = _download(out, case)
+    req2, out2 = _device_request(engine, case)
+    engine.decodeNoAlloc(req2)                    # the first call on this GPU looks the scratch array up
+    torch.cuda.synchronize(dev)
+    free_before = torch.cuda.mem_get_info(dev)[0]
+    for _ in range(3):
+        engine.decodeNoAlloc(req2)
+    torch.cuda.synchronize(dev)
+    assert torch.cuda.mem_get_info(dev)[0] == free_before
+    assert np.array_equal(_download(out2, case).view(np.uint16), expected.view(np.uint16))
+    # recorded into a graph on a capturing stream, then replayed
+    req3, out3 = _device_request(engine, case)
+    stream = torch.cuda.Stream(dev)
+    graph = torch.cuda.CUDAGraph()
+    engine.setStream(stream.cuda_stream)
+    launches = engine.kernelLaunches
+    with torch.cuda.graph(graph, stream=stream):
+        engine.decodeNoAlloc(req3)
+    assert engine.kernelLaunches > launches
+    engine.setStream(None)
+    graph.replay()
+    torch.cuda.synchronize(dev)
+    assert np.array_equal(_download(out3, case).view(np.uint16), expected.view(np.uint16))
+    assert torch.cuda.mem_get_info(dev)[0] <= free_before      # the graph itself may hold memory, the call did not
+    engine.close()
