@@ -42,11 +42,6 @@ namespace {
 constexpr int kTileTokens = 16;
 constexpr float kLog2e = 1.4426950408889634f;
 
-// Split-K workspace for launchDecodeStatic(): device memory that belongs to the
-// library image itself, so that a decode can run without any allocation call.
-// Every GPU that loads the library holds these 8 MiB until the process exits.
-constexpr size_t kStaticScratchBytes = size_t(8) << 20;
-static __device__ __align__(256) float gStaticDecodeScratch[kStaticScratchBytes / sizeof(float)];
 
 // ---------------------------------------------------------------- PTX helpers
 
@@ -104,6 +99,17 @@ __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// The two 16-bit halves of a packed pair, widened.
+template <typename T> __device__ __forceinline__ float lowHalf(uint32_t v);
+template <typename T> __device__ __forceinline__ float highHalf(uint32_t v);
+template <> __device__ __forceinline__ float lowHalf<__nv_bfloat16>(uint32_t v) { return __uint_as_float(v << 16); }
+template <> __device__ __forceinline__ float highHalf<__nv_bfloat16>(uint32_t v) { return __uint_as_float(v & 0xFFFF0000u); }
+template <> __device__ __forceinline__ float lowHalf<__half>(uint32_t v) { return __half2float(__ushort_as_half(static_cast<unsigned short>(v & 0xFFFFu))); }
+template <> __device__ __forceinline__ float highHalf<__half>(uint32_t v) { return __half2float(__ushort_as_half(static_cast<unsigned short>(v >> 16))); }
+template <typename T> __device__ __forceinline__ constexpr bool isHalf() { return false; }
+template <> __device__ __forceinline__ constexpr bool isHalf<__half>() { return true; }
+constexpr int kShortContextKeys = 256;
+
 template <typename T>
 __device__ __forceinline__ T fromFloat(float v);
 template <>
@@ -151,6 +157,12 @@ __host__ __device__ __forceinline__ void splitRange(int numTiles, int numSplits,
 // same reference, and the accumulator is then rescaled a few times per split instead of
 // once per tile.  Weights reach at most 2^kLazyMax, well inside float16 and bfloat16.
 constexpr float kLazyMax = 6.0f;
+// bfloat16 weights keep 8 significant bits: only with the exact maximum as the reference is
+// the largest weight of a row exactly 1, and a row that one key dominates stays within the
+// 2e-3 bound.  There the maximum is followed exactly (the accumulator is still only
+// rescaled on the tiles that raise it); float16 weights (11 bits) take the lazy form.
+template <typename T> __device__ __forceinline__ constexpr float lazyMaxOf() { return kLazyMax; }
+template <> __device__ __forceinline__ constexpr float lazyMaxOf<__nv_bfloat16>() { return 0.f; }
 
 // What a CTA of the split kernels works on.  Two launch shapes:
 //  * grid (maxSplits, kv_heads, batch): the range follows from the sequence's length;
@@ -231,19 +243,56 @@ __device__ __forceinline__ void finishSplit(const float* red, int G, const Split
     __syncthreads();
     if (!sIsLast) return;
     __threadfence();
+    // The weights of the splits first (one thread per (head, split), all loads in flight
+    // together), into the shared memory the warps' partials no longer need; then one thread
+    // per output element sums over the splits with eight loads in flight.
+    float* wgtOf = const_cast<float*>(red);                 // [G][maxSplits] weights, then [G] 1 / sum
+    __syncthreads();
+    for (int g = 0; g < G; ++g) {
+        const float* part = workspace + (static_cast<int64_t>(w.b) * heads + w.kvh * G + g) * maxSplits * RS;
+        float M = -INFINITY;
+        for (int sp = threadIdx.x; sp < w.numSplits; sp += NW * 32) M = fmaxf(M, __ldcg(part + sp * RS + HD));
+        // block maximum through the warps
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xFFFFFFFFu, M, o));
+        __shared__ float sM[NW], sL[NW];
+        if ((threadIdx.x & 31) == 0) sM[threadIdx.x >> 5] = M;
+        __syncthreads();
+        M = sM[0];
+#pragma unroll
+        for (int x = 1; x < NW; ++x) M = fmaxf(M, sM[x]);
+        float lsum = 0.f;
+        for (int sp = threadIdx.x; sp < w.numSplits; sp += NW * 32) {
+            const float wgt = exp2f(__ldcg(part + sp * RS + HD) - M);
+            wgtOf[g * maxSplits + sp] = wgt;
+            lsum += wgt * __ldcg(part + sp * RS + HD + 1);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) lsum += __shfl_xor_sync(0xFFFFFFFFu, lsum, o);
+        if ((threadIdx.x & 31) == 0) sL[threadIdx.x >> 5] = lsum;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float total = 0.f;
+#pragma unroll
+            for (int x = 0; x < NW; ++x) total += sL[x];
+            wgtOf[G * maxSplits + g] = 1.f / total;
+        }
+        __syncthreads();
+    }
     for (int idx = threadIdx.x; idx < G * HD; idx += NW * 32) {
         const int g = idx / HD, d = idx - g * HD;
         const int head = w.kvh * G + g;
-        const float* part = workspace + (static_cast<int64_t>(w.b) * heads + head) * maxSplits * RS;
-        float M = -INFINITY;
-        for (int sp = 0; sp < w.numSplits; ++sp) M = fmaxf(M, __ldcg(part + sp * RS + HD));
-        float acc = 0.f, lsum = 0.f;
-        for (int sp = 0; sp < w.numSplits; ++sp) {
-            const float wgt = exp2f(__ldcg(part + sp * RS + HD) - M);
-            acc += wgt * __ldcg(part + sp * RS + d);
-            lsum += wgt * __ldcg(part + sp * RS + HD + 1);
+        const float* part = workspace + (static_cast<int64_t>(w.b) * heads + head) * maxSplits * RS + d;
+        const float* wg = wgtOf + g * maxSplits;
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        int sp = 0;
+        for (; sp + 8 <= w.numSplits; sp += 8) {
+#pragma unroll
+            for (int u = 0; u < 8; ++u) acc[u] += wg[sp + u] * __ldcg(part + (sp + u) * RS);
         }
-        out[(static_cast<int64_t>(w.b) * heads + head) * HD + d] = fromFloat<T>(acc / lsum);
+        for (; sp < w.numSplits; ++sp) acc[0] += wg[sp] * __ldcg(part + sp * RS);
+        const float total = ((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7]));
+        out[(static_cast<int64_t>(w.b) * heads + head) * HD + d] = fromFloat<T>(total * wgtOf[G * maxSplits + g]);
     }
 }
 
@@ -283,6 +332,11 @@ decodeSplitKernel(const T* __restrict__ q, const T* __restrict__ kPool, const T*
     if (work.split >= work.numSplits) return;
 
     const int tileBegin = work.tileBegin, tileEnd = work.tileEnd;
+    // A bfloat16 weight keeps 8 significant bits.  A sequence with few visible keys has large
+    // weights, and 8 bits alone can then miss the 2e-3 bound on unit-variance values: such
+    // sequences carry every weight as two bfloat16 operands (16 bits) into a second product.
+    // With hundreds of keys the weights are small enough for 8 bits.
+    const bool twoPartWeights = sizeof(T) == 2 && !isHalf<T>() && static_cast<int>(len) - si.windowStart < kShortContextKeys;
     // warp w takes tiles tileBegin + w, + NW, ...
     const int myTiles = (tileEnd - tileBegin - warp + NW - 1) / NW;
     const int tilesPerPage = blockSize / kTileTokens;
@@ -389,13 +443,13 @@ decodeSplitKernel(const T* __restrict__ q, const T* __restrict__ kPool, const T*
         }
         tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xFFFFFFFFu, tmax0, 1));
         tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xFFFFFFFFu, tmax0, 2));
-        bool raise = tmax0 > m0 + kLazyMax;        // m0 = -inf: the first tile always raises
+        bool raise = tmax0 > m0 + lazyMaxOf<T>();  // m0 = -inf: the first tile always raises
         float c0 = 1.f, c1 = 1.f;
         if (raise) { c0 = exp2f(m0 - tmax0); m0 = tmax0; }   // m0 = -inf gives 0
         if (UPPER) {
             tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xFFFFFFFFu, tmax1, 1));
             tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xFFFFFFFFu, tmax1, 2));
-            if (tmax1 > m1 + kLazyMax) { c1 = exp2f(m1 - tmax1); m1 = tmax1; raise = true; }
+            if (tmax1 > m1 + lazyMaxOf<T>()) { c1 = exp2f(m1 - tmax1); m1 = tmax1; raise = true; }
         }
         if (__any_sync(0xFFFFFFFFu, raise)) {
             l0 *= c0;
@@ -410,19 +464,27 @@ decodeSplitKernel(const T* __restrict__ q, const T* __restrict__ kPool, const T*
                 }
             }
         }
-        uint32_t pa[4];
+        uint32_t pa[4], pl[4] = {0u, 0u, 0u, 0u};
         {
             const float p00 = exp2f(s[0][0] - m0), p01 = exp2f(s[0][1] - m0);
             const float p10 = exp2f(s[1][0] - m0), p11 = exp2f(s[1][1] - m0);
             l0 += (p00 + p01) + (p10 + p11);
             pa[0] = pack2<T>(p00, p01);
             pa[2] = pack2<T>(p10, p11);
+            if (twoPartWeights) {
+                pl[0] = pack2<T>(p00 - lowHalf<T>(pa[0]), p01 - highHalf<T>(pa[0]));
+                pl[2] = pack2<T>(p10 - lowHalf<T>(pa[2]), p11 - highHalf<T>(pa[2]));
+            }
             if (UPPER) {
                 const float q00 = exp2f(s[0][2] - m1), q01 = exp2f(s[0][3] - m1);
                 const float q10 = exp2f(s[1][2] - m1), q11 = exp2f(s[1][3] - m1);
                 l1 += (q00 + q01) + (q10 + q11);
                 pa[1] = pack2<T>(q00, q01);
                 pa[3] = pack2<T>(q10, q11);
+                if (twoPartWeights) {
+                    pl[1] = pack2<T>(q00 - lowHalf<T>(pa[1]), q01 - highHalf<T>(pa[1]));
+                    pl[3] = pack2<T>(q10 - lowHalf<T>(pa[3]), q11 - highHalf<T>(pa[3]));
+                }
             } else {
                 pa[1] = 0u;
                 pa[3] = 0u;
@@ -438,6 +500,10 @@ decodeSplitKernel(const T* __restrict__ q, const T* __restrict__ kPool, const T*
             ldmatrixX4Trans(vb, sv + row * ROWB + ((chunk ^ (row & 7)) << 4));
             mma16816<T>(o[2 * cp], pa, vb[0], vb[1]);
             mma16816<T>(o[2 * cp + 1], pa, vb[2], vb[3]);
+            if (twoPartWeights) {
+                mma16816<T>(o[2 * cp], pl, vb[0], vb[1]);
+                mma16816<T>(o[2 * cp + 1], pl, vb[2], vb[3]);
+            }
         }
 
         __syncwarp();
@@ -1017,7 +1083,7 @@ int planWaves() {
     static const int waves = [] {
         const char* e = std::getenv("PAM_DECODE_WAVES");
         const int v = e ? std::atoi(e) : 0;
-        return v > 0 ? v : 12;
+        return v > 0 ? v : 2;
     }();
     return waves;
 }
@@ -1149,7 +1215,10 @@ dim3 splitGrid(const DecodeParams& p, const SplitPlan& plan) {
 // The last CTA of a (sequence, kv head) merges its splits when the caller gave counters
 // for every such pair; else the merge kernel follows.
 bool mergeInKernel(const DecodeParams& p, const SplitPlan& plan) {
-    return plan.maxSplits > 1 && p.counters && static_cast<int64_t>(p.batch) * p.kvHeads <= p.countersCap;
+    // (the merging CTA keeps one weight per (head, split) in its shared memory: 48 KB of the ring's space)
+    const int64_t G = p.heads / p.kvHeads;
+    return plan.maxSplits > 1 && p.counters && static_cast<int64_t>(p.batch) * p.kvHeads <= p.countersCap &&
+           (G * plan.maxSplits + G) * static_cast<int64_t>(sizeof(float)) <= 48 * 1024;
 }
 
 template <typename T, int HD>
@@ -1250,9 +1319,22 @@ cudaError_t makePlan(const DecodeParams& p, int smCount, cudaStream_t stream, Sp
 
 }  // namespace
 
-bool decodeTakesSplitPath(const DecodeParams& p) { return fastPathApplies(p); }
+namespace {
+// (tuning runs only: PAM_DECODE_STREAM=0 takes the grid-per-split kernels instead of the stream kernel)
+bool streamEnabled() {
+    static const bool on = [] {
+        const char* e = std::getenv("PAM_DECODE_STREAM");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+bool takesStream(const DecodeParams& p) { return streamEnabled() && decodeStreamApplies(p); }
+}  // namespace
+
+bool decodeTakesSplitPath(const DecodeParams& p) { return decodeStreamApplies(p) || fastPathApplies(p); }
 
 size_t decodeWorkspaceBytes(const DecodeParams& p, int smCount, cudaStream_t stream) {
+    if (takesStream(p)) return decodeStreamWorkspaceBytes(p, smCount);
     SplitPlan plan{};
     if (makePlan(p, smCount, stream, plan) != cudaSuccess) { cudaGetLastError(); return 0; }
     return partialBytes(p, plan);
@@ -1261,6 +1343,8 @@ size_t decodeWorkspaceBytes(const DecodeParams& p, int smCount, cudaStream_t str
 cudaError_t launchDecode(const DecodeParams& p, int smCount, cudaStream_t stream, int* launches) {
     if (p.batch <= 0) return cudaSuccess;
     if (p.headDim > 256 || p.poolBlocks <= 0) return cudaErrorInvalidValue;
+    if (takesStream(p) && p.workspace && p.counters && static_cast<int64_t>(p.batch) * p.kvHeads <= p.countersCap)
+        return launchDecodeStream(p, smCount, stream, launches);
     SplitPlan plan{};
     cudaError_t pe = makePlan(p, smCount, stream, plan);
     if (pe != cudaSuccess) return pe;
@@ -1282,34 +1366,29 @@ cudaError_t launchDecode(const DecodeParams& p, int smCount, cudaStream_t stream
     return cudaErrorInvalidValue;
 }
 
-size_t decodeStaticScratchBytes() { return kStaticScratchBytes; }
-
 cudaError_t launchDecodeStatic(const DecodeParams& p, int smCount, cudaStream_t stream, int* launches) {
-    // In host code the array's name is only a handle; the kernels need its
-    // device address, which differs per GPU.  It is looked up once per device,
-    // with that device current (the caller has made it so).  Two host threads may
-    // get here together for the same GPU: both then store the same address.
-    static std::atomic<float*> addressOnDevice[64];
-    int dev = -1;
-    cudaError_t e = cudaGetDevice(&dev);
+    // The scratch array and the arrival words are part of the library image on every GPU;
+    // their device addresses are looked up once per device (decodeStaticScratch).
+    float* scratch = nullptr;
+    int* counters = nullptr;
+    int64_t countersCap = 0;
+    cudaError_t e = decodeStaticScratch(&scratch, &counters, &countersCap);
     if (e != cudaSuccess) return e;
-    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
-    float* scratch = addressOnDevice[dev].load(std::memory_order_acquire);
-    if (!scratch) {
-        void* ptr = nullptr;
-        e = cudaGetSymbolAddress(&ptr, gStaticDecodeScratch);
-        if (e != cudaSuccess) return e;
-        scratch = static_cast<float*>(ptr);
-        addressOnDevice[dev].store(scratch, std::memory_order_release);
-    }
     DecodeParams q = p;
-    q.hostLens = nullptr;      // the plan of this variant never depends on a cache that may allocate
+    q.hostLens = nullptr;      // nothing here may depend on a cache that allocates
     q.planCache = nullptr;
+    q.workspace = scratch;
+    q.workspaceBytes = decodeStaticScratchBytes();
+    q.counters = counters;
+    q.countersCap = countersCap;
+    if (takesStream(q)) {
+        // the stream kernel sizes its grid to the scratch it is given; the arrival words bound the batch
+        if (static_cast<int64_t>(q.batch) * q.kvHeads > countersCap) return cudaErrorInvalidValue;
+        return launchDecodeStream(q, smCount, stream, launches);
+    }
     q.counters = nullptr;
     q.countersCap = 0;
-    if (decodeWorkspaceBytes(q, smCount, stream) > kStaticScratchBytes) return cudaErrorInvalidValue;
-    q.workspace = scratch;
-    q.workspaceBytes = kStaticScratchBytes;
+    if (decodeWorkspaceBytes(q, smCount, stream) > decodeStaticScratchBytes()) return cudaErrorInvalidValue;
     return launchDecode(q, smCount, stream, launches);
 }
 

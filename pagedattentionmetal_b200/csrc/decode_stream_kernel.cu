@@ -1,0 +1,985 @@
+// Batched paged decode as one persistent stream of key/value tiles.
+//
+// Semantics: paged_decode_single / _f16 / _fp8 (kernels.metal:1417-1620): per (sequence,
+// query head) softmax(q.K^T / sqrt(dim)) V over tokens [window_start, L) reached through the
+// block table, float32 accumulation.  Pools are [block][kv_head][block_size][head_dim].
+//
+// The work of a launch is the list of 16-token tiles of all (sequence, kv head) pairs, laid
+// end to end: sequence after sequence, kv head after kv head, tile after tile.  Every warp of
+// the grid (one CTA per resident slot, four warps each) takes one contiguous piece of that
+// list, all pieces the same length, found from a prefix sum of the sequences' tile counts
+// that each CTA builds in shared memory from the lengths.  A warp streams its piece through
+// its own cp.async ring (K tile + V tile per stage, XOR-swizzled 16-byte chunks) without a
+// pause at the borders between sequences: the loads run ahead of the arithmetic across
+// them.  Nothing in the kernel waits for another warp.
+//
+// A (sequence, kv head) pair that lies inside one warp's piece gets its output from that
+// warp.  A pair that several warps share gets one partial result (m, l, O per query head)
+// from each of them in a workspace; every warp counts its arrival on the pair's word, and
+// the warp that arrives last combines the partials with a log-sum-exp reduction and puts
+// the word back to zero.  A warp has at most two shared pairs, the first and the last of
+// its piece, so the workspace is two partials per warp, whatever the lengths are.
+//
+// Arithmetic per tile: mma.sync m16n8k16 with the query heads of the GQA group as rows (every
+// K/V byte is read once for the whole group), online softmax in registers in the log2
+// domain; FP8 e4m3 codes become float16 in registers and the (block, kv_head) scales are
+// applied outside the products.  The kernel is bound by HBM bandwidth.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <atomic>
+#include <cmath>
+#include <type_traits>
+
+#include "kernels.h"
+
+namespace pam {
+namespace {
+
+constexpr int kTileTokens = 16;
+constexpr int kWarps = 4;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr int kShortContextKeys = 256;
+// The running maximum of a row is only raised when a tile exceeds it by more than this
+// (log2 domain): the result is the same either way because the final division uses the
+// same reference, and the accumulator is then rescaled a few times per sequence instead of
+// once per tile.  Weights reach at most 2^kLazyMax, well inside float16.
+constexpr float kLazyMax = 6.0f;
+
+// Split-K partials and arrival words for launchDecodeStatic(): device memory that belongs
+// to the library image itself, so that a decode can run without any allocation call.  Every
+// GPU that loads the library holds them until the process exits.
+constexpr size_t kStaticScratchBytes = size_t(8) << 20;
+constexpr int kStaticCounters = 1 << 16;
+static __device__ __align__(256) float gStaticDecodeScratch[kStaticScratchBytes / sizeof(float)];
+static __device__ __align__(256) int gStaticDecodeCounters[kStaticCounters];
+
+// ---------------------------------------------------------------- PTX helpers
+
+__device__ __forceinline__ uint32_t smemAddr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void cpAsync16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src));
+}
+__device__ __forceinline__ void cpAsync4(uint32_t dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst), "l"(src));
+}
+__device__ __forceinline__ void cpAsyncCommit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cpAsyncWait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrixX4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrixX4Trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+template <typename T>
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1);
+template <>
+__device__ __forceinline__ void mma16816<__half>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <>
+__device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+// The two 16-bit halves of a packed bfloat16 pair, widened.
+__device__ __forceinline__ float bf16Low(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf16High(uint32_t v) { return __uint_as_float(v & 0xFFFF0000u); }
+
+template <typename T> __device__ __forceinline__ T fromFloat(float v);
+template <> __device__ __forceinline__ __half fromFloat<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 fromFloat<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// 2^x by the special-function unit alone (exp2f adds a range fix-up for results below the
+// normal range, which a softmax weight does not need); 2^-inf = 0.
+__device__ __forceinline__ float ex2Fast(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// Two e4m3 codes (low or high 16 bits of `v`) to two float16 values; exact, every e4m3 value
+// is a float16 value.
+__device__ __forceinline__ uint32_t e4m3x2ToHalf2(uint32_t v) {
+    uint32_t r;
+    asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %1;\n\tcvt.rn.f16x2.e4m3x2 %0, lo;\n\t}" : "=r"(r) : "r"(v));
+    return r;
+}
+__device__ __forceinline__ uint32_t e4m3x2HiToHalf2(uint32_t v) {
+    uint32_t r;
+    asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %1;\n\tcvt.rn.f16x2.e4m3x2 %0, hi;\n\t}" : "=r"(r) : "r"(v));
+    return r;
+}
+
+// Visible tiles of a sequence.
+struct Visible {
+    int firstTile;   // first 16-token tile that holds a visible token
+    int numTiles;    // tiles from there to the end of the sequence
+    int windowStart; // first visible token
+};
+__device__ __forceinline__ Visible visibleOf(uint32_t len, int window, int maxTokens) {
+    Visible s;
+    uint32_t L = len < static_cast<uint32_t>(maxTokens) ? len : static_cast<uint32_t>(maxTokens);
+    s.windowStart = (window > 0 && len > static_cast<uint32_t>(window)) ? static_cast<int>(len) - window : 0;   // kernels.metal:1442
+    if (s.windowStart > static_cast<int>(L)) s.windowStart = static_cast<int>(L);
+    s.firstTile = s.windowStart / kTileTokens;
+    s.numTiles = (static_cast<int>(L) + kTileTokens - 1) / kTileTokens - s.firstTile;
+    if (s.numTiles < 0) s.numTiles = 0;
+    return s;
+}
+
+struct StreamArgs {
+    const void* q;
+    const void* kPool;
+    const void* vPool;
+    const void* kScale;
+    const void* vScale;
+    const int32_t* tables;
+    const uint32_t* lens;
+    void* out;
+    float* workspace;     // [warps of the grid][2][G][HD + 4]
+    int* counters;        // [batch][kvHeads], zero between launches
+    int batch, heads, kvHeads, blockSize, maxNumBlocks, window, poolBlocks;
+    float scaleLog2;
+};
+
+// ------------------------------------------------------------ tile arithmetic
+//
+// A policy says how one kind of pool is streamed and multiplied: the bytes of a ring stage,
+// how a tile is fetched, how the query rows sit in registers, what one tile does to the
+// running (m, l, O), and how the result leaves the registers.
+
+// float16 / bfloat16 pools, head_dim 64 or 128.
+template <typename T, int HD_, bool UPPER>
+struct HalfTiles {
+    using Out = T;
+    static constexpr int HD = HD_, NS = 3;
+    static constexpr int ROWB = HD * 2, CPR = ROWB / 16, TILEB = kTileTokens * ROWB, CHUNKS = TILEB / 16;
+    static constexpr int STAGEB = 2 * TILEB, KSTEPS = HD / 16, NT = HD / 8;
+    static constexpr bool kBf16 = sizeof(T) == 2 && !std::is_same<T, __half>::value;
+    struct Query { uint32_t a[KSTEPS][4]; };
+    struct Acc {
+        float o[NT][4];
+        float m0, m1, l0, l1;
+        bool twoPart;        // bfloat16, few visible keys: weights as two operands (16 bits)
+    };
+
+    static __device__ __forceinline__ void issue(uint32_t stage, unsigned char*, const StreamArgs& a, int64_t blk, int kvh,
+                                                 int within, int lane) {
+        const int64_t off = ((blk * a.kvHeads + kvh) * a.blockSize + within * kTileTokens) * static_cast<int64_t>(ROWB);
+        const unsigned char* gk = static_cast<const unsigned char*>(a.kPool) + off;
+        const unsigned char* gv = static_cast<const unsigned char*>(a.vPool) + off;
+#pragma unroll
+        for (int i = 0; i < CHUNKS / 32; ++i) {
+            const int idx = lane + 32 * i;
+            const int row = idx / CPR, c = idx % CPR;
+            const uint32_t dst = row * ROWB + ((c ^ (row & 7)) << 4);
+            cpAsync16(stage + dst, gk + idx * 16);
+            cpAsync16(stage + TILEB + dst, gv + idx * 16);
+        }
+    }
+
+    // Query rows of a GQA group as A fragments (rows >= G are zero).
+    static __device__ __forceinline__ void loadQuery(Query& q, const StreamArgs& a, int64_t row0, int G, int lane) {
+        const int r = lane >> 2, j = lane & 3;
+        const T* qb = static_cast<const T*>(a.q) + row0 * HD;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+            const int d0 = ks * 16 + 2 * j;
+            q.a[ks][0] = r < G ? *reinterpret_cast<const uint32_t*>(qb + r * HD + d0) : 0u;
+            q.a[ks][2] = r < G ? *reinterpret_cast<const uint32_t*>(qb + r * HD + d0 + 8) : 0u;
+            q.a[ks][1] = (UPPER && r + 8 < G) ? *reinterpret_cast<const uint32_t*>(qb + (r + 8) * HD + d0) : 0u;
+            q.a[ks][3] = (UPPER && r + 8 < G) ? *reinterpret_cast<const uint32_t*>(qb + (r + 8) * HD + d0 + 8) : 0u;
+        }
+    }
+
+    static __device__ __forceinline__ void reset(Acc& c, int visibleTokens) {
+#pragma unroll
+        for (int n = 0; n < NT; ++n) c.o[n][0] = c.o[n][1] = c.o[n][2] = c.o[n][3] = 0.f;
+        c.m0 = c.m1 = -INFINITY;
+        c.l0 = c.l1 = 0.f;
+        // A bfloat16 weight keeps 8 significant bits.  A sequence with few visible keys has
+        // large weights, and 8 bits alone can then miss the 2e-3 bound on unit-variance
+        // values: such sequences carry every weight as two bfloat16 operands into a second
+        // product.  With hundreds of keys the weights are small enough for 8 bits.
+        c.twoPart = kBf16 && visibleTokens < kShortContextKeys;
+    }
+
+    static __device__ __forceinline__ void tile(Acc& c, const Query& q, unsigned char* stagePtr, uint32_t stage, int tokBase,
+                                                int windowStart, int len, float scaleLog2, int lane) {
+        const int j = lane & 3;
+        const uint32_t sk = stage, sv = stage + TILEB;
+        const bool partial = tokBase < windowStart || tokBase + kTileTokens > len;
+        if (partial) {
+            // Rows outside [window_start, L) may hold anything; zero their V so that a zero
+            // probability times that row stays zero.
+            unsigned char* vt = stagePtr + TILEB;
+            for (int idx = lane; idx < CHUNKS; idx += 32) {
+                const int tok = tokBase + idx / CPR;
+                if (tok < windowStart || tok >= len) *reinterpret_cast<uint4*>(vt + idx * 16) = make_uint4(0u, 0u, 0u, 0u);
+            }
+            __syncwarp();
+        }
+        // S = Q K^T for the 16 tokens of the tile (two n-tiles of 8 tokens).
+        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+            const int mi = lane >> 3, rowIn = lane & 7;
+            const int row = 8 * (mi >> 1) + rowIn, chunk = 2 * ks + (mi & 1);
+            uint32_t kb[4];
+            ldmatrixX4(kb, sk + row * ROWB + ((chunk ^ (row & 7)) << 4));
+            mma16816<T>(s[0], q.a[ks], kb[0], kb[1]);
+            mma16816<T>(s[1], q.a[ks], kb[2], kb[3]);
+        }
+        // Online softmax in the log2 domain.
+        float tmax0 = -INFINITY, tmax1 = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int tok = tokBase + 8 * nt + 2 * j + e;
+                const bool ok = !partial || (tok >= windowStart && tok < len);
+                s[nt][e] = ok ? s[nt][e] * scaleLog2 : -INFINITY;
+                tmax0 = fmaxf(tmax0, s[nt][e]);
+                if (UPPER) {
+                    s[nt][e + 2] = ok ? s[nt][e + 2] * scaleLog2 : -INFINITY;
+                    tmax1 = fmaxf(tmax1, s[nt][e + 2]);
+                }
+            }
+        }
+        // With bfloat16 weights the maximum is followed exactly: only then is the largest
+        // weight of a row exactly 1, which a row that one key dominates needs for the bound.
+        constexpr float lazy = kBf16 ? 0.f : kLazyMax;
+        tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xFFFFFFFFu, tmax0, 1));
+        tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xFFFFFFFFu, tmax0, 2));
+        bool raise = tmax0 > c.m0 + lazy;              // m0 = -inf: the first tile always raises
+        float c0 = 1.f, c1 = 1.f;
+        if (raise) { c0 = exp2f(c.m0 - tmax0); c.m0 = tmax0; }   // m0 = -inf gives 0
+        if (UPPER) {
+            tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xFFFFFFFFu, tmax1, 1));
+            tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xFFFFFFFFu, tmax1, 2));
+            if (tmax1 > c.m1 + lazy) { c1 = exp2f(c.m1 - tmax1); c.m1 = tmax1; raise = true; }
+        }
+        if (__any_sync(0xFFFFFFFFu, raise)) {
+            c.l0 *= c0;
+            if (UPPER) c.l1 *= c1;
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                c.o[n][0] *= c0;
+                c.o[n][1] *= c0;
+                if (UPPER) {
+                    c.o[n][2] *= c1;
+                    c.o[n][3] *= c1;
+                }
+            }
+        }
+        uint32_t pa[4], pl[4] = {0u, 0u, 0u, 0u};
+        {
+            const float p00 = exp2f(s[0][0] - c.m0), p01 = exp2f(s[0][1] - c.m0);
+            const float p10 = exp2f(s[1][0] - c.m0), p11 = exp2f(s[1][1] - c.m0);
+            c.l0 += (p00 + p01) + (p10 + p11);
+            pa[0] = pack2<T>(p00, p01);
+            pa[2] = pack2<T>(p10, p11);
+            if (kBf16 && c.twoPart) {
+                pl[0] = pack2<T>(p00 - bf16Low(pa[0]), p01 - bf16High(pa[0]));
+                pl[2] = pack2<T>(p10 - bf16Low(pa[2]), p11 - bf16High(pa[2]));
+            }
+            if (UPPER) {
+                const float q00 = exp2f(s[0][2] - c.m1), q01 = exp2f(s[0][3] - c.m1);
+                const float q10 = exp2f(s[1][2] - c.m1), q11 = exp2f(s[1][3] - c.m1);
+                c.l1 += (q00 + q01) + (q10 + q11);
+                pa[1] = pack2<T>(q00, q01);
+                pa[3] = pack2<T>(q10, q11);
+                if (kBf16 && c.twoPart) {
+                    pl[1] = pack2<T>(q00 - bf16Low(pa[1]), q01 - bf16High(pa[1]));
+                    pl[3] = pack2<T>(q10 - bf16Low(pa[3]), q11 - bf16High(pa[3]));
+                }
+            } else {
+                pa[1] = 0u;
+                pa[3] = 0u;
+            }
+        }
+        // O += P V
+#pragma unroll
+        for (int cp = 0; cp < NT / 2; ++cp) {
+            const int mi = lane >> 3, rowIn = lane & 7;
+            const int row = (mi & 1) * 8 + rowIn, chunk = 2 * cp + (mi >> 1);
+            uint32_t vb[4];
+            ldmatrixX4Trans(vb, sv + row * ROWB + ((chunk ^ (row & 7)) << 4));
+            mma16816<T>(c.o[2 * cp], pa, vb[0], vb[1]);
+            mma16816<T>(c.o[2 * cp + 1], pa, vb[2], vb[3]);
+            if (kBf16 && c.twoPart) {
+                mma16816<T>(c.o[2 * cp], pl, vb[0], vb[1]);
+                mma16816<T>(c.o[2 * cp + 1], pl, vb[2], vb[3]);
+            }
+        }
+    }
+
+    // Row sums live spread over the four lanes of a quad.
+    static __device__ __forceinline__ void finish(Acc& c) {
+        c.l0 += __shfl_xor_sync(0xFFFFFFFFu, c.l0, 1);
+        c.l0 += __shfl_xor_sync(0xFFFFFFFFu, c.l0, 2);
+        if (UPPER) {
+            c.l1 += __shfl_xor_sync(0xFFFFFFFFu, c.l1, 1);
+            c.l1 += __shfl_xor_sync(0xFFFFFFFFu, c.l1, 2);
+        }
+    }
+
+    // f(row g, column d, value) for every accumulator element this lane holds, and
+    // g(row, m, l) once per row.
+    template <class F, class Gf>
+    static __device__ __forceinline__ void each(const Acc& c, int G, int lane, F f, Gf g) {
+        const int r = lane >> 2, j = lane & 3;
+        if (r < G) {
+#pragma unroll
+            for (int n = 0; n < NT; ++n) f(r, 8 * n + 2 * j, c.o[n][0], c.o[n][1]);
+            if (j == 0) g(r, c.m0, c.l0);
+        }
+        if (UPPER && r + 8 < G) {
+#pragma unroll
+            for (int n = 0; n < NT; ++n) f(r + 8, 8 * n + 2 * j, c.o[n][2], c.o[n][3]);
+            if (j == 0) g(r + 8, c.m1, c.l1);
+        }
+    }
+    static constexpr int kPairStride = 1;     // the two values handed to f are columns d and d + 1
+    static __device__ __forceinline__ float rowSum(const Acc& c, bool upper) { return upper ? c.l1 : c.l0; }
+};
+
+// FP8 e4m3 pools with float16 (block, kv_head) scales, head_dim 128, float16 queries and
+// outputs.  A 16-token tile is 2 KB of K codes and 2 KB of V codes.  Codes become float16 in
+// registers (exactly) and feed mma.sync.m16n8k16.f16; the group scales are applied outside
+// the products: K's on the scores, V's on the weights (relative to the scale of the first
+// tile of the sequence this warp sees, so that the weights stay in float16's normal range).
+// The fragments are loaded with 16-byte shared-memory reads: the K-dimension of QK^T and
+// the N-dimension of PV are permuted so that every thread reads contiguous codes, which no
+// result depends on.
+template <bool UPPER>
+struct Fp8Tiles {
+    using Out = __half;
+    static constexpr int HD = 128, NS = 4;
+    static constexpr int ROWB = HD, TILEB = kTileTokens * ROWB, CHUNKS = TILEB / 16;
+    static constexpr int STAGEB = 2 * TILEB + 16;   // + the words that hold the tile's two group scales
+    static constexpr int KSTEPS = HD / 16, NT = HD / 8;
+    struct Query { uint32_t a[KSTEPS][4]; };
+    struct Acc {
+        float o[NT][4];
+        float m0, m1, l0, l1;
+        float vRef, invVRef;     // V scale of the first tile
+        bool first;
+    };
+
+    static __device__ __forceinline__ void issue(uint32_t stage, unsigned char* stagePtr, const StreamArgs& a, int64_t blk,
+                                                 int kvh, int within, int lane) {
+        const int64_t off = ((blk * a.kvHeads + kvh) * a.blockSize + within * kTileTokens) * static_cast<int64_t>(ROWB);
+        const unsigned char* gk = static_cast<const unsigned char*>(a.kPool) + off;
+        const unsigned char* gv = static_cast<const unsigned char*>(a.vPool) + off;
+#pragma unroll
+        for (int i = 0; i < CHUNKS / 32; ++i) {
+            const int idx = lane + 32 * i;
+            const int row = idx >> 3, c = idx & 7;
+            const uint32_t dst = row * ROWB + ((c ^ (row & 7)) << 4);
+            cpAsync16(stage + dst, gk + idx * 16);
+            cpAsync16(stage + TILEB + dst, gv + idx * 16);
+        }
+        // the aligned words that hold the two float16 scales travel with the tile; which half
+        // of a word is the scale follows from the parity of its index
+        if (lane < 2) {
+            const int64_t si = blk * a.kvHeads + kvh;
+            const unsigned char* base = static_cast<const unsigned char*>(lane == 0 ? a.kScale : a.vScale);
+            cpAsync4(stage + 2 * TILEB + 4 * lane, base + ((si * 2) & ~static_cast<int64_t>(3)));
+            if (lane == 0) stagePtr[2 * TILEB + 8] = static_cast<unsigned char>(si & 1);
+        }
+    }
+
+    // Query rows as A fragments with the permuted K order: step ks of thread (r, j) covers
+    // dims 32j + 4ks + {0,1} (first half) and + {2,3} (second half).
+    static __device__ __forceinline__ void loadQuery(Query& q, const StreamArgs& a, int64_t row0, int G, int lane) {
+        const int r = lane >> 2, j = lane & 3;
+        const __half* qb = static_cast<const __half*>(a.q) + row0 * HD;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+            const int d0 = 32 * j + 4 * ks;
+            uint2 lo = make_uint2(0u, 0u), hi = make_uint2(0u, 0u);
+            if (r < G) lo = *reinterpret_cast<const uint2*>(qb + r * HD + d0);
+            if (UPPER && r + 8 < G) hi = *reinterpret_cast<const uint2*>(qb + (r + 8) * HD + d0);
+            q.a[ks][0] = lo.x; q.a[ks][2] = lo.y;
+            q.a[ks][1] = hi.x; q.a[ks][3] = hi.y;
+        }
+    }
+
+    static __device__ __forceinline__ void reset(Acc& c, int) {
+#pragma unroll
+        for (int n = 0; n < NT; ++n) c.o[n][0] = c.o[n][1] = c.o[n][2] = c.o[n][3] = 0.f;
+        c.m0 = c.m1 = -INFINITY;
+        c.l0 = c.l1 = 0.f;
+        c.vRef = 1.f; c.invVRef = 1.f;
+        c.first = true;
+    }
+
+    static __device__ __forceinline__ void tile(Acc& c, const Query& q, unsigned char* stagePtr, uint32_t, int tokBase,
+                                                int windowStart, int len, float scaleLog2, int lane) {
+        const int r = lane >> 2, j = lane & 3;
+        const __half* sc = reinterpret_cast<const __half*>(stagePtr + 2 * TILEB);
+        const int odd = stagePtr[2 * TILEB + 8];
+        const float ks_ = __half2float(sc[odd]), vs_ = __half2float(sc[2 + odd]);
+        if (c.first) { c.vRef = vs_ > 0.f ? vs_ : 1.f; c.invVRef = 1.f / c.vRef; c.first = false; }
+        const bool partial = tokBase < windowStart || tokBase + kTileTokens > len;
+        if (partial) {
+            // rows outside [window_start, L): zero codes, so that a zero weight times that row is zero
+            unsigned char* vt = stagePtr + TILEB;
+            for (int idx = lane; idx < CHUNKS; idx += 32) {
+                const int tok = tokBase + (idx >> 3);
+                if (tok < windowStart || tok >= len) *reinterpret_cast<uint4*>(vt + idx * 16) = make_uint4(0u, 0u, 0u, 0u);
+            }
+            __syncwarp();
+        }
+        // S = Q K^T on the codes; the group scale and 1/sqrt(d) follow.
+        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            const int row = 8 * nt + r;
+            const uint4 w0 = *reinterpret_cast<const uint4*>(stagePtr + row * ROWB + (((2 * j) ^ (row & 7)) << 4));
+            const uint4 w1 = *reinterpret_cast<const uint4*>(stagePtr + row * ROWB + (((2 * j + 1) ^ (row & 7)) << 4));
+            const uint32_t w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ++ks) mma16816<__half>(s[nt], q.a[ks], e4m3x2ToHalf2(w[ks]), e4m3x2HiToHalf2(w[ks]));
+        }
+        const float sScale = ks_ * scaleLog2;
+        float tmax0 = -INFINITY, tmax1 = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int tok = tokBase + 8 * nt + 2 * j + e;
+                const bool ok = !partial || (tok >= windowStart && tok < len);
+                s[nt][e] = ok ? s[nt][e] * sScale : -INFINITY;
+                tmax0 = fmaxf(tmax0, s[nt][e]);
+                if (UPPER) {
+                    s[nt][e + 2] = ok ? s[nt][e + 2] * sScale : -INFINITY;
+                    tmax1 = fmaxf(tmax1, s[nt][e + 2]);
+                }
+            }
+        }
+        tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xFFFFFFFFu, tmax0, 1));
+        tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xFFFFFFFFu, tmax0, 2));
+        bool raise = tmax0 > c.m0 + kLazyMax;          // m0 = -inf: the first tile always raises
+        float c0 = 1.f, c1 = 1.f;
+        if (raise) { c0 = ex2Fast(c.m0 - tmax0); c.m0 = tmax0; }
+        if (UPPER) {
+            tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xFFFFFFFFu, tmax1, 1));
+            tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xFFFFFFFFu, tmax1, 2));
+            if (tmax1 > c.m1 + kLazyMax) { c1 = ex2Fast(c.m1 - tmax1); c.m1 = tmax1; raise = true; }
+        }
+        if (__any_sync(0xFFFFFFFFu, raise)) {
+            c.l0 *= c0;
+            if (UPPER) c.l1 *= c1;
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                c.o[n][0] *= c0;
+                c.o[n][1] *= c0;
+                if (UPPER) {
+                    c.o[n][2] *= c1;
+                    c.o[n][3] *= c1;
+                }
+            }
+        }
+        // weights; those that enter the product carry V's group scale relative to vRef
+        const float vw = vs_ * c.invVRef;
+        uint32_t pa[4];
+        {
+            const float p00 = ex2Fast(s[0][0] - c.m0), p01 = ex2Fast(s[0][1] - c.m0);
+            const float p10 = ex2Fast(s[1][0] - c.m0), p11 = ex2Fast(s[1][1] - c.m0);
+            c.l0 += (p00 + p01) + (p10 + p11);
+            pa[0] = pack2<__half>(p00 * vw, p01 * vw);
+            pa[2] = pack2<__half>(p10 * vw, p11 * vw);
+            if (UPPER) {
+                const float q00 = ex2Fast(s[0][2] - c.m1), q01 = ex2Fast(s[0][3] - c.m1);
+                const float q10 = ex2Fast(s[1][2] - c.m1), q11 = ex2Fast(s[1][3] - c.m1);
+                c.l1 += (q00 + q01) + (q10 + q11);
+                pa[1] = pack2<__half>(q00 * vw, q01 * vw);
+                pa[3] = pack2<__half>(q10 * vw, q11 * vw);
+            } else {
+                pa[1] = 0u;
+                pa[3] = 0u;
+            }
+        }
+        // O += P V.  Thread (r, j) reads chunk r (dims 16r .. 16r+15) of the token rows
+        // 2j, 2j+1, 2j+8, 2j+9; n-tile c takes byte c of each: output column n of n-tile c
+        // is dim 16n + c.
+        {
+            const unsigned char* vt = stagePtr + TILEB;
+            uint4 x[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int row = 2 * j + (i & 1) + 8 * (i >> 1);
+                x[i] = *reinterpret_cast<const uint4*>(vt + row * ROWB + ((r ^ (row & 7)) << 4));
+            }
+            const uint32_t* x0 = reinterpret_cast<const uint32_t*>(&x[0]);
+            const uint32_t* x1 = reinterpret_cast<const uint32_t*>(&x[1]);
+            const uint32_t* x2 = reinterpret_cast<const uint32_t*>(&x[2]);
+            const uint32_t* x3 = reinterpret_cast<const uint32_t*>(&x[3]);
+#pragma unroll
+            for (int wi = 0; wi < 4; ++wi) {
+                const uint32_t a01 = __byte_perm(x0[wi], x1[wi], 0x5140);   // bytes 0,1 of both tokens, interleaved
+                const uint32_t a23 = __byte_perm(x0[wi], x1[wi], 0x7362);
+                const uint32_t b01 = __byte_perm(x2[wi], x3[wi], 0x5140);
+                const uint32_t b23 = __byte_perm(x2[wi], x3[wi], 0x7362);
+                mma16816<__half>(c.o[4 * wi + 0], pa, e4m3x2ToHalf2(a01), e4m3x2ToHalf2(b01));
+                mma16816<__half>(c.o[4 * wi + 1], pa, e4m3x2HiToHalf2(a01), e4m3x2HiToHalf2(b01));
+                mma16816<__half>(c.o[4 * wi + 2], pa, e4m3x2ToHalf2(a23), e4m3x2ToHalf2(b23));
+                mma16816<__half>(c.o[4 * wi + 3], pa, e4m3x2HiToHalf2(a23), e4m3x2HiToHalf2(b23));
+            }
+        }
+    }
+
+    static __device__ __forceinline__ void finish(Acc& c) {
+        c.l0 += __shfl_xor_sync(0xFFFFFFFFu, c.l0, 1);
+        c.l0 += __shfl_xor_sync(0xFFFFFFFFu, c.l0, 2);
+        if (UPPER) {
+            c.l1 += __shfl_xor_sync(0xFFFFFFFFu, c.l1, 1);
+            c.l1 += __shfl_xor_sync(0xFFFFFFFFu, c.l1, 2);
+        }
+    }
+
+    // accumulator element n of a thread is dim 16 * (2j) + n (first value) and 16 * (2j + 1) + n
+    template <class F, class Gf>
+    static __device__ __forceinline__ void each(const Acc& c, int G, int lane, F f, Gf g) {
+        const int r = lane >> 2, j = lane & 3;
+        if (r < G) {
+#pragma unroll
+            for (int n = 0; n < NT; ++n) f(r, 16 * (2 * j) + n, c.o[n][0] * c.vRef, c.o[n][1] * c.vRef);
+            if (j == 0) g(r, c.m0, c.l0);
+        }
+        if (UPPER && r + 8 < G) {
+#pragma unroll
+            for (int n = 0; n < NT; ++n) f(r + 8, 16 * (2 * j) + n, c.o[n][2] * c.vRef, c.o[n][3] * c.vRef);
+            if (j == 0) g(r + 8, c.m1, c.l1);
+        }
+    }
+    static constexpr int kPairStride = 16;    // the two values handed to f are columns d and d + 16
+    static __device__ __forceinline__ float rowSum(const Acc& c, bool upper) { return upper ? c.l1 : c.l0; }
+};
+
+// ------------------------------------------------------------ the stream
+
+// Tile counts of the sequences as a prefix sum in shared memory: prefix[b] = tiles of all
+// (sequence, kv head) pairs before sequence b, first[b] = the sequence's first visible tile.
+__device__ __forceinline__ void buildPrefix(int* prefix, int* first, const StreamArgs& a) {
+    const int tid = threadIdx.x, nt = blockDim.x, lane = tid & 31, warp = tid >> 5;
+    const int per = (a.batch + nt - 1) / nt;
+    const int b0 = min(tid * per, a.batch), b1 = min(b0 + per, a.batch);
+    const int maxTokens = a.maxNumBlocks * a.blockSize;
+    int sum = 0;
+    for (int b = b0; b < b1; ++b) {
+        const Visible v = visibleOf(a.lens[b], a.window, maxTokens);
+        first[b] = v.firstTile;
+        prefix[b + 1] = v.numTiles * a.kvHeads;
+        sum += v.numTiles * a.kvHeads;
+    }
+    __shared__ int warpSums[kWarps];
+    int incl = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int n = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+        if (lane >= o) incl += n;
+    }
+    if (lane == 31) warpSums[warp] = incl;
+    __syncthreads();
+    int run = incl - sum;
+    for (int w = 0; w < warp; ++w) run += warpSums[w];
+    for (int b = b0; b < b1; ++b) {
+        run += prefix[b + 1];
+        prefix[b + 1] = run;
+    }
+    if (tid == 0) prefix[0] = 0;
+    __syncthreads();
+}
+
+// Position in the list of tiles.
+struct Cursor {
+    int b, kvh, tile;        // sequence, kv head, tile counted from the sequence's first visible tile
+    int tilesB, firstTile;   // tiles of a (sequence, kv head) pair of this sequence, its first visible tile
+};
+__device__ __forceinline__ void locate(Cursor& c, int unit, const int* prefix, const int* first, int batch, int kvHeads) {
+    int lo = 0, hi = batch - 1;
+    while (lo < hi) {                       // the sequence with prefix[b] <= unit < prefix[b + 1]
+        const int mid = (lo + hi) >> 1;
+        if (prefix[mid + 1] <= unit) lo = mid + 1; else hi = mid;
+    }
+    c.b = lo;
+    c.tilesB = (prefix[lo + 1] - prefix[lo]) / kvHeads;
+    const int local = unit - prefix[lo];
+    c.kvh = local / c.tilesB;
+    c.tile = local - c.kvh * c.tilesB;
+    c.firstTile = first[lo];
+}
+__device__ __forceinline__ void advance(Cursor& c, const int* prefix, const int* first, int batch, int kvHeads) {
+    if (++c.tile < c.tilesB) return;
+    c.tile = 0;
+    if (++c.kvh < kvHeads) return;
+    c.kvh = 0;
+    do { ++c.b; } while (c.b < batch && prefix[c.b + 1] == prefix[c.b]);    // sequences without visible tiles
+    if (c.b < batch) {
+        c.tilesB = (prefix[c.b + 1] - prefix[c.b]) / kvHeads;
+        c.firstTile = first[c.b];
+    }
+}
+
+constexpr int kPartialPad = 4;      // a partial row is head_dim + 4 floats: O, then m and l (16-byte rows)
+
+// Combination of the partials of one (sequence, kv head) pair by the warp that arrived last.
+// The contributions come from warps wf .. wl of the grid, each in its first slot, except that
+// warp wf holds it in its second slot when the pair begins inside its piece.
+template <class P>
+__device__ __forceinline__ void combine(const StreamArgs& a, int b, int kvh, int G, int wf, int wl, bool firstInSecondSlot,
+                                        int lane) {
+    constexpr int HD = P::HD, RS = HD + kPartialPad;
+    using Out = typename P::Out;
+    const int n = wl - wf + 1;
+    for (int g = 0; g < G; ++g) {
+        auto row = [&](int i) {
+            const int slot = (i == 0 && firstInSecondSlot) ? 1 : 0;
+            return a.workspace + ((static_cast<int64_t>(wf + i) * 2 + slot) * G + g) * RS;
+        };
+        float M = -INFINITY;
+        for (int i = lane; i < n; i += 32) M = fmaxf(M, __ldcg(row(i) + HD));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xFFFFFFFFu, M, o));
+        float lsum = 0.f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int base = 0; base < n; base += 32) {
+            // 32 contributions at a time: lane i weighs contribution base + i, every lane then sums
+            // four columns over them
+            const int mine = base + lane;
+            float wgt = 0.f;
+            if (mine < n) {
+                wgt = exp2f(__ldcg(row(mine) + HD) - M);
+                lsum += wgt * __ldcg(row(mine) + HD + 1);
+            }
+            const int cnt = min(32, n - base);
+            const bool holds = lane * 4 < HD;              // head_dim 64: half the lanes hold columns
+#pragma unroll 4
+            for (int i = 0; i < cnt; ++i) {
+                const float w = __shfl_sync(0xFFFFFFFFu, wgt, i);
+                if (holds) {
+                    const float4 v = __ldcg(reinterpret_cast<const float4*>(row(base + i)) + lane);
+                    acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w;
+                }
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) lsum += __shfl_xor_sync(0xFFFFFFFFu, lsum, o);
+        if (lane * 4 < HD) {
+            const float inv = 1.f / lsum;
+            Out* dst = static_cast<Out*>(a.out) + (static_cast<int64_t>(b) * a.heads + kvh * G + g) * HD + lane * 4;
+            dst[0] = fromFloat<Out>(acc.x * inv);
+            dst[1] = fromFloat<Out>(acc.y * inv);
+            dst[2] = fromFloat<Out>(acc.z * inv);
+            dst[3] = fromFloat<Out>(acc.w * inv);
+        }
+    }
+}
+
+template <class P>
+__global__ void __launch_bounds__(kWarps * 32)
+decodeStreamKernel(const StreamArgs a) {
+    constexpr int NS = P::NS, STAGEB = P::STAGEB, HD = P::HD, RS = HD + kPartialPad;
+    using Out = typename P::Out;
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int G = a.heads / a.kvHeads;
+    const int maxTokens = a.maxNumBlocks * a.blockSize;
+    constexpr int kRingBytes = (kWarps * NS * STAGEB + 15) / 16 * 16;
+    int* prefix = reinterpret_cast<int*>(smem + kRingBytes);     // [batch + 1]
+    int* first = prefix + a.batch + 1;                           // [batch]
+    buildPrefix(prefix, first, a);
+
+    // An empty context (the reference divides 0 by 0 there) gets zeros.
+    for (int b = blockIdx.x; b < a.batch; b += gridDim.x) {
+        if (prefix[b + 1] != prefix[b]) continue;
+        Out* dst = static_cast<Out*>(a.out) + static_cast<int64_t>(b) * a.heads * HD;
+        for (int i = threadIdx.x; i < a.heads * HD; i += kWarps * 32) dst[i] = fromFloat<Out>(0.f);
+    }
+
+    // this warp's piece of the list
+    const int total = prefix[a.batch];
+    const int warpsInGrid = gridDim.x * kWarps, wid = blockIdx.x * kWarps + warp;
+    const int quota = (total + warpsInGrid - 1) / warpsInGrid;
+    const int begin = min(wid * quota, total), end = min(begin + quota, total);
+    if (begin >= end) return;
+    const int count = end - begin;
+    const int tilesPerPage = a.blockSize / kTileTokens;
+
+    unsigned char* ring = smem + static_cast<size_t>(warp) * NS * STAGEB;
+    const uint32_t ringAddr = smemAddr(ring);
+
+    Cursor ahead, cur;                       // where the loads are, where the arithmetic is
+    locate(ahead, begin, prefix, first, a.batch, a.kvHeads);
+    cur = ahead;
+    auto issueNext = [&](int slot) {
+        const int tile = ahead.firstTile + ahead.tile;
+        const int page = tile / tilesPerPage, within = tile - page * tilesPerPage;
+        const int32_t* table = a.tables + static_cast<int64_t>(ahead.b) * a.maxNumBlocks;
+        const int64_t blk = min(max(table[page], 0), a.poolBlocks - 1);     // never read outside the pool
+        P::issue(ringAddr + slot * STAGEB, ring + slot * STAGEB, a, blk, ahead.kvh, within, lane);
+        advance(ahead, prefix, first, a.batch, a.kvHeads);
+    };
+    int issued = 0;
+#pragma unroll
+    for (int s = 0; s < NS; ++s) {
+        if (issued < count) { issueNext(s); ++issued; }
+        cpAsyncCommit();
+    }
+
+    typename P::Query q;
+    typename P::Acc acc;
+    int len = 0, windowStart = 0, pairBegin = 0;
+    bool fresh = true;
+    for (int it = 0; it < count; ++it) {
+        if (fresh) {
+            // a new (sequence, kv head) pair starts in this warp
+            const uint32_t L = a.lens[cur.b];
+            const Visible v = visibleOf(L, a.window, maxTokens);
+            len = static_cast<int>(L < static_cast<uint32_t>(maxTokens) ? L : static_cast<uint32_t>(maxTokens));
+            windowStart = v.windowStart;
+            pairBegin = prefix[cur.b] + cur.kvh * cur.tilesB;
+            P::loadQuery(q, a, static_cast<int64_t>(cur.b) * a.heads + cur.kvh * G, G, lane);
+            P::reset(acc, len - windowStart);
+            fresh = false;
+        }
+        cpAsyncWait<NS - 1>();
+        __syncwarp();
+        const int slot = it % NS;
+        P::tile(acc, q, ring + slot * STAGEB, ringAddr + slot * STAGEB, (cur.firstTile + cur.tile) * kTileTokens, windowStart,
+                len, a.scaleLog2, lane);
+        __syncwarp();
+        if (issued < count) { issueNext(slot); ++issued; }
+        cpAsyncCommit();
+
+        const bool pairEnds = cur.tile + 1 == cur.tilesB;
+        if (pairEnds || it + 1 == count) {
+            P::finish(acc);
+            const int pairEnd = pairBegin + cur.tilesB;
+            const int64_t outRow = static_cast<int64_t>(cur.b) * a.heads + cur.kvh * G;
+            if (pairBegin >= begin && pairEnd <= end) {
+                // the whole pair was this warp's: its output
+                Out* dst = static_cast<Out*>(a.out) + outRow * HD;
+                P::each(acc, G, lane,
+                        [&](int g, int d, float v0, float v1) {
+                            const float inv = 1.f / P::rowSum(acc, g >= 8);
+                            if (P::kPairStride == 1) {
+                                *reinterpret_cast<uint32_t*>(dst + g * HD + d) = pack2<Out>(v0 * inv, v1 * inv);
+                            } else {
+                                dst[g * HD + d] = fromFloat<Out>(v0 * inv);
+                                dst[g * HD + d + P::kPairStride] = fromFloat<Out>(v1 * inv);
+                            }
+                        },
+                        [](int, float, float) {});
+            } else {
+                const int slot2 = pairBegin > begin ? 1 : 0;      // the first pair of the piece, or its last
+                float* part = a.workspace + ((static_cast<int64_t>(wid) * 2 + slot2) * G) * RS;
+                P::each(acc, G, lane,
+                        [&](int g, int d, float v0, float v1) {
+                            part[g * RS + d] = v0;
+                            part[g * RS + d + P::kPairStride] = v1;
+                        },
+                        [&](int g, float m, float l) {
+                            part[g * RS + HD] = m;
+                            part[g * RS + HD + 1] = l;
+                        });
+                // the partial is published before the arrival is counted; the last arrival
+                // reads the others' partials from L2
+                __threadfence();
+                __syncwarp();
+                const int wf = pairBegin / quota, wl = (pairEnd - 1) / quota;
+                int last = 0;
+                if (lane == 0) {
+                    int* word = a.counters + static_cast<int64_t>(cur.b) * a.kvHeads + cur.kvh;
+                    last = atomicAdd(word, 1) == wl - wf ? 1 : 0;
+                    if (last) *word = 0;                           // ready for the next launch
+                }
+                last = __shfl_sync(0xFFFFFFFFu, last, 0);
+                if (last) {
+                    __threadfence();
+                    combine<P>(a, cur.b, cur.kvh, G, wf, wl, pairBegin > wf * quota, lane);
+                }
+            }
+            fresh = true;
+        }
+        advance(cur, prefix, first, a.batch, a.kvHeads);
+    }
+    cpAsyncWait<0>();
+}
+
+// ---------------------------------------------------------------- launch
+
+// The dynamic shared memory limit of a kernel is raised once per device, not per launch.
+template <class K>
+cudaError_t allowSharedMemory(K kernel, size_t bytes, std::atomic<size_t>* granted, int dev) {
+    if (granted[dev].load(std::memory_order_acquire) >= bytes) return cudaSuccess;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
+    if (e == cudaSuccess) granted[dev].store(bytes, std::memory_order_release);
+    return e;
+}
+
+template <class P>
+size_t streamSharedBytes(int batch) {
+    const size_t ring = (static_cast<size_t>(kWarps) * P::NS * P::STAGEB + 15) / 16 * 16;
+    return ring + (static_cast<size_t>(2) * batch + 1) * sizeof(int);
+}
+
+// CTAs of the launch: every resident slot of the GPU, fewer when the workspace is small.
+template <class P>
+cudaError_t streamGrid(int batch, int smCount, int* grid) {
+    static std::atomic<int> perSm[64][4];      // by device and by shared-memory class of the batch
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    const int cls = batch <= 256 ? 0 : batch <= 512 ? 1 : batch <= 1024 ? 2 : 3;
+    const int classBatch = cls == 0 ? 256 : cls == 1 ? 512 : cls == 2 ? 1024 : kDecodeStreamMaxBatch;
+    int n = perSm[dev][cls].load(std::memory_order_acquire);
+    if (n == 0) {
+        static std::atomic<size_t> granted[64];
+        const size_t smem = streamSharedBytes<P>(kDecodeStreamMaxBatch);
+        e = allowSharedMemory(decodeStreamKernel<P>, smem, granted, dev);
+        if (e != cudaSuccess) return e;
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, decodeStreamKernel<P>, kWarps * 32, streamSharedBytes<P>(classBatch));
+        if (e != cudaSuccess) return e;
+        if (n < 1) n = 1;
+        perSm[dev][cls].store(n, std::memory_order_release);
+    }
+    *grid = smCount * n;
+    return cudaSuccess;
+}
+
+template <class P>
+cudaError_t launchStreamT(const DecodeParams& p, int smCount, cudaStream_t stream, int* launches) {
+    int grid = 0;
+    cudaError_t e = streamGrid<P>(p.batch, smCount, &grid);
+    if (e != cudaSuccess) return e;
+    const int G = p.heads / p.kvHeads;
+    const size_t perWarp = static_cast<size_t>(2) * G * (P::HD + kPartialPad) * sizeof(float);
+    // a smaller workspace (the fixed array of the no-allocation call) holds fewer warps' partials
+    const size_t holds = p.workspaceBytes / perWarp / kWarps;
+    if (holds < 1) return cudaErrorInvalidValue;
+    if (static_cast<size_t>(grid) > holds) grid = static_cast<int>(holds);
+    StreamArgs a{};
+    a.q = p.q; a.kPool = p.kPool; a.vPool = p.vPool; a.kScale = p.kScale; a.vScale = p.vScale;
+    a.tables = p.tables; a.lens = p.lens; a.out = p.out; a.workspace = p.workspace; a.counters = p.counters;
+    a.batch = p.batch; a.heads = p.heads; a.kvHeads = p.kvHeads; a.blockSize = p.blockSize; a.maxNumBlocks = p.maxNumBlocks;
+    a.window = p.window; a.poolBlocks = p.poolBlocks;
+    a.scaleLog2 = (1.0f / sqrtf(static_cast<float>(p.headDim))) * kLog2e;
+    decodeStreamKernel<P><<<grid, kWarps * 32, streamSharedBytes<P>(p.batch), stream>>>(a);
+    e = cudaGetLastError();
+    if (e == cudaSuccess && launches) *launches += 1;
+    return e;
+}
+
+template <class F>
+auto dispatch(const DecodeParams& p, F f) {
+    const bool upper = p.heads / p.kvHeads > 8;
+    if (p.dtype == kFP8) return upper ? f(Fp8Tiles<true>{}) : f(Fp8Tiles<false>{});
+    if (p.dtype == kF16) {
+        if (p.headDim == 128) return upper ? f(HalfTiles<__half, 128, true>{}) : f(HalfTiles<__half, 128, false>{});
+        return upper ? f(HalfTiles<__half, 64, true>{}) : f(HalfTiles<__half, 64, false>{});
+    }
+    if (p.headDim == 128) return upper ? f(HalfTiles<__nv_bfloat16, 128, true>{}) : f(HalfTiles<__nv_bfloat16, 128, false>{});
+    return upper ? f(HalfTiles<__nv_bfloat16, 64, true>{}) : f(HalfTiles<__nv_bfloat16, 64, false>{});
+}
+
+}  // namespace
+
+bool decodeStreamApplies(const DecodeParams& p) {
+    const int G = p.kvHeads > 0 ? p.heads / p.kvHeads : 0;
+    const bool shape = p.headDim > 0 && p.blockSize > 0 && p.blockSize % kTileTokens == 0 && G >= 1 && G <= 16 && p.batch >= 1;
+    // the kernel copies pages with 16-byte cp.async and reads the query rows as 4-byte (FP8:
+    // 8-byte) words; anything less aligned goes to the general kernel
+    const auto aligned = [](const void* ptr, uintptr_t a) { return (reinterpret_cast<uintptr_t>(ptr) & (a - 1)) == 0; };
+    if (!shape || !aligned(p.kPool, 16) || !aligned(p.vPool, 16)) return false;
+    // the list of tiles is indexed with 32-bit integers
+    if (static_cast<int64_t>(p.maxNumBlocks) * p.blockSize / kTileTokens * p.kvHeads * static_cast<int64_t>(kDecodeStreamMaxBatch) >= (int64_t(1) << 31))
+        return false;
+    if (p.dtype == kF16 || p.dtype == kBF16) return (p.headDim == 128 || p.headDim == 64) && aligned(p.q, 4) && aligned(p.out, 4);
+    if (p.dtype == kFP8)
+        return p.headDim == 128 && p.kScale && p.vScale && aligned(p.q, 8) && aligned(p.out, 2) && aligned(p.kScale, 4) &&
+               aligned(p.vScale, 4);
+    return false;
+}
+
+size_t decodeStreamWorkspaceBytes(const DecodeParams& p, int smCount) {
+    int grid = 0;
+    const cudaError_t e = dispatch(p, [&](auto tiles) { return streamGrid<decltype(tiles)>(p.batch < kDecodeStreamMaxBatch ? p.batch : kDecodeStreamMaxBatch, smCount, &grid); });
+    if (e != cudaSuccess) { cudaGetLastError(); return 0; }
+    const int G = p.heads / p.kvHeads;
+    return static_cast<size_t>(grid) * kWarps * 2 * G * (p.headDim + kPartialPad) * sizeof(float);
+}
+
+cudaError_t launchDecodeStream(const DecodeParams& p, int smCount, cudaStream_t stream, int* launches) {
+    if (!p.workspace || !p.counters || static_cast<int64_t>(p.batch) * p.kvHeads > p.countersCap) return cudaErrorInvalidValue;
+    // batches beyond what the prefix sum in shared memory holds go in slices
+    for (int b0 = 0; b0 < p.batch; b0 += kDecodeStreamMaxBatch) {
+        DecodeParams s = p;
+        s.batch = p.batch - b0 < kDecodeStreamMaxBatch ? p.batch - b0 : kDecodeStreamMaxBatch;
+        const size_t io = static_cast<size_t>(p.heads) * p.headDim * ioBytes(p.dtype);
+        s.q = static_cast<const char*>(p.q) + b0 * io;
+        s.out = static_cast<char*>(p.out) + b0 * io;
+        s.tables = p.tables + static_cast<int64_t>(b0) * p.maxNumBlocks;
+        s.lens = p.lens + b0;
+        s.counters = p.counters + static_cast<int64_t>(b0) * p.kvHeads;
+        const cudaError_t e = dispatch(s, [&](auto tiles) { return launchStreamT<decltype(tiles)>(s, smCount, stream, launches); });
+        if (e != cudaSuccess) return e;
+    }
+    return cudaSuccess;
+}
+
+size_t decodeStaticScratchBytes() { return kStaticScratchBytes; }
+
+cudaError_t decodeStaticScratch(float** scratch, int** counters, int64_t* countersCap) {
+    // In host code the arrays' names are only handles; the kernels need their device
+    // addresses, which differ per GPU.  They are looked up once per device, with that device
+    // current (the caller has made it so).  Two host threads may get here together for the
+    // same GPU: both then store the same addresses.
+    static std::atomic<float*> scratchOn[64];
+    static std::atomic<int*> countersOn[64];
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    float* s = scratchOn[dev].load(std::memory_order_acquire);
+    int* c = countersOn[dev].load(std::memory_order_acquire);
+    if (!s || !c) {
+        void* ps = nullptr;
+        void* pc = nullptr;
+        e = cudaGetSymbolAddress(&ps, gStaticDecodeScratch);
+        if (e == cudaSuccess) e = cudaGetSymbolAddress(&pc, gStaticDecodeCounters);
+        if (e != cudaSuccess) return e;
+        s = static_cast<float*>(ps);
+        c = static_cast<int*>(pc);
+        scratchOn[dev].store(s, std::memory_order_release);
+        countersOn[dev].store(c, std::memory_order_release);
+    }
+    *scratch = s;
+    *counters = c;
+    *countersCap = kStaticCounters;
+    return cudaSuccess;
+}
+
+}  // namespace pam

@@ -82,6 +82,18 @@ bool decodeTakesSplitPath(const DecodeParams& p);
 // lengths this builds the plan (and may enqueue its upload on `stream`).
 size_t decodeWorkspaceBytes(const DecodeParams& p, int smCount, cudaStream_t stream);
 cudaError_t launchDecode(const DecodeParams& p, int smCount, cudaStream_t stream, int* launches);
+// The persistent stream kernel (decode_stream_kernel.cu): float16 / bfloat16 / FP8 pools,
+// head_dim 128 (64 for 16-bit pools), block size a multiple of 16, at most 16 query heads
+// per KV head, aligned pointers.  It needs `workspace` (decodeStreamWorkspaceBytes) and
+// `counters` (zero between launches, batch * kvHeads words).  Batches beyond
+// kDecodeStreamMaxBatch run as several launches.
+constexpr int kDecodeStreamMaxBatch = 2048;
+bool decodeStreamApplies(const DecodeParams& p);
+size_t decodeStreamWorkspaceBytes(const DecodeParams& p, int smCount);
+cudaError_t launchDecodeStream(const DecodeParams& p, int smCount, cudaStream_t stream, int* launches);
+// Device addresses of the fixed scratch array and arrival words inside the library image.
+cudaError_t decodeStaticScratch(float** scratch, int** counters, int64_t* countersCap);
+
 // Same decode with the split-K workspace taken from a fixed array inside the
 // library (decodeStaticScratchBytes() bytes per GPU) instead of p.workspace.
 // Allocates nothing; fails with cudaErrorInvalidValue when the launch would

@@ -604,13 +604,22 @@ int32_t decodeNoAllocImpl(Context* c, const PamDecodeRequest& rq) {
     p.dtype = l.data_type; p.maxContext = 0;
     p.poolBlocks = poolBlocksOf(rq.k_pool, rq.v_pool, l);
     p.hostLens = nullptr; p.planCache = nullptr; p.counters = nullptr; p.countersCap = 0;
-    const size_t need = pam::decodeWorkspaceBytes(p, c->smCount, c->stream);
-    if (need > pam::decodeStaticScratchBytes())
+    // What the call needs of the built-in arrays: one arrival word per (sequence, kv head)
+    // pair (65 536 words) and, per warp of the launch, two partial results of the GQA group
+    // (8 MiB; the launch takes fewer warps when that is all the array holds, but at least
+    // one CTA's worth).
+    const size_t pairs = B * static_cast<size_t>(l.num_kv_heads);
+    const size_t perCta = static_cast<size_t>(4) * 2 * (l.num_heads / l.num_kv_heads) * (static_cast<size_t>(l.head_dim) + 4) * sizeof(float);
+    size_t need = std::min(pam::decodeWorkspaceBytes(p, c->smCount, c->stream), pam::decodeStaticScratchBytes());
+    if (pam::decodeStreamApplies(p)) need = std::max(std::min(need, pam::decodeStaticScratchBytes()), perCta);
+    else need = pam::decodeWorkspaceBytes(p, c->smCount, c->stream);
+    if (need > pam::decodeStaticScratchBytes() || (pam::decodeStreamApplies(p) && pairs > (size_t(1) << 16)))
         return c->fail(PAM_ERR_RESOURCE_EXHAUSTED,
                        "GPU resource exhausted: this decode needs " + std::to_string(need) +
-                           " bytes of split-K scratch, the built-in scratch holds " +
+                           " bytes of split-K scratch and " + std::to_string(pairs) +
+                           " arrival words, the built-in scratch holds " +
                            std::to_string(pam::decodeStaticScratchBytes()) +
-                           "; use pamc_decode, or a smaller batch, fewer heads or shorter tables.");
+                           " bytes and 65536 words; use pamc_decode, or a smaller batch or fewer heads.");
     const double t0 = nowMs();
     // While the stream is being captured nothing may wait on it and nothing runs yet: the
     // launch is recorded once, without the wait and the retry loop of the eager call.
@@ -2073,6 +2082,12 @@ static int32_t inferPrefillBatched(Inference* inf, const std::vector<pam::Schedu
         auto at = inf->prefillProgress.find(sq.id);
         int done = at == inf->prefillProgress.end() ? -1 : at->second;
         if (done < 0) {
+            // A reservation that has to pause sequences may take one that this step has already
+            // prepared; the reference has by then issued and counted that sequence's prefill
+            // (one dispatch per sequence), so what is prepared goes out first.
+            const int needed = (sq.promptLength + inf->cache->blockSize - 1) / inf->cache->blockSize;
+            if (!pend.empty() && inf->cache->mgr.availableBlocks() < needed)
+                if (int32_t rc = inferFlushPrefill(inf, pend)) return rc;
             if (int32_t rc = inferReservePrompt(inf, sq)) {
                 // what was prepared before the failing prompt is issued, as the reference
                 // would have done by then; the step still fails

@@ -10,6 +10,7 @@ torch CUDA tensors, or raw device addresses.
 from __future__ import annotations
 
 import ctypes as C
+import weakref
 from typing import Iterable, Optional, Sequence
 
 import numpy as np
@@ -105,8 +106,11 @@ class PagedAttentionEngine:
             raise PagedAttentionError(1, "Metal device or command queue could not be initialized.")
         self._splitThreshold, self._defaultWindowSize, self._defaultChunkSize = 1024, 0, 0
         self._maxRetries, self._graceful = 3, True
+        self._dependents = weakref.WeakSet()      # objects whose native side refers to this context
 
     def close(self) -> None:
+        for d in list(getattr(self, "_dependents", ())):
+            d.close()                             # they must go before the context they point at
         if getattr(self, "_ctx", None):
             lib.pam_destroy_context(self._ctx)
             self._ctx = None
@@ -761,6 +765,7 @@ class PagedAttentionInference:
         self.scheduler = _BorrowedScheduler(lib.pamc_infer_scheduler(self._h), maxBatchSize, maxSequences)
         self._callback = None
         self._onTokenGenerated = None
+        self.engine._dependents.add(self)         # closed before the engine's context goes away
 
     def close(self) -> None:
         if getattr(self, "_h", None):
