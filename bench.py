@@ -565,10 +565,9 @@ def run_decode_c2(rt, with_cpu):
     assert np.array_equal(lens_h.astype(np.int64), lens)
     tables_dev = torch.from_numpy(tables_h).to(dev)
     layer = pam.PagedLayerSpec(HEAD_DIM, heads, kvh, BLOCK, DT.float16)
-    # K/V pools, queries, outputs and block tables resident in HBM; the lengths are a host
-    # array (as the reference's seqLengths buffer is host-visible): the library plans the
-    # launch from them and sends them up with the call
-    req = pam.PagedAttentionDecodeRequest(q_dev, cache.kPoolBuffer, cache.vPoolBuffer, tables_dev, lens_h, out_dev,
+    # K/V pools, queries, outputs, block tables and lengths resident in HBM
+    lens_dev = torch.from_numpy(lens_h.view(np.int32)).to(dev)
+    req = pam.PagedAttentionDecodeRequest(q_dev, cache.kPoolBuffer, cache.vPoolBuffer, tables_dev, lens_dev, out_dev,
                                           B, max_nb, layer)
     q_pin = torch.empty((B, heads, HEAD_DIM), dtype=torch.float16, pin_memory=True)
     q_pin.copy_(q_dev)
@@ -611,11 +610,11 @@ def run_decode_c2(rt, with_cpu):
         line = rt.base_line("decode_c2", "paged decode tokens/s", B / (ms[0] * 1e-3), "tokens/s", ms, "f16", settled,
                             launches, clocks,
                             {"seed": SEED, "l2": "inputs larger than L2 (KV read per step per GPU exceeds 126 MB); no flush needed",
-                             "lengths": "host array, uploaded by every call"})
+                             })
         line["kv_read_gbs_total"] = achieved * rt.world
         line["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                             "peak_source": f"{rt.peak_kind} copy bandwidth", "per": "GPU",
-                            "kernel": "decodeSplitKernel (splits merged by the CTA that finishes a sequence last)",
+                            "kernel": "decodeStreamKernel (float16 tiles)",
                             "algorithmic_bytes_per_launch": bytes_gpu,
                             "traffic": bytes_gpu * DECODE_TRAFFIC_FACTOR["f16"],
                             "traffic_source": "ncu on a 64-sequence cut, scaled by context tokens"}
@@ -948,7 +947,8 @@ def run_c4(rt, with_cpu, want=("decode_c4", "step_c4")):
     q = torch.randn((n_seq, C4_HEADS, HEAD_DIM), generator=gen, device=dev).to(torch.float16)[:, qsl].contiguous()
     out = torch.empty_like(q)
     layer = pam.PagedLayerSpec(HEAD_DIM, heads, kvh, BLOCK, DT.float8, C4_WINDOW)
-    req = pam.PagedAttentionDecodeRequest(q, cache.kPoolBuffer, cache.vPoolBuffer, tables, lens_h, out, n_seq, max_nb,
+    lens_dev = torch.from_numpy(lens_h.view(np.int32)).to(dev)
+    req = pam.PagedAttentionDecodeRequest(q, cache.kPoolBuffer, cache.vPoolBuffer, tables, lens_dev, out, n_seq, max_nb,
                                           layer, cache.kScaleBuffer, cache.vScaleBuffer)
     decode = lambda: engine.decode(req)
     decode()
@@ -970,13 +970,12 @@ def run_c4(rt, with_cpu, want=("decode_c4", "step_c4")):
         achieved = bytes_decode / (ms_decode * 1e-3) / 1e9
         return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "peak_source": f"{rt.peak_kind} copy bandwidth", "per": "GPU",
-                "kernel": "decodeSplitFp8Kernel (splits merged by the CTA that finishes a sequence last)",
+                "kernel": "decodeStreamKernel (FP8 tiles)",
                 "algorithmic_bytes_per_launch": bytes_decode, "traffic": bytes_decode * DECODE_TRAFFIC_FACTOR["fp8"],
                 "traffic_source": "ncu on a 16-sequence cut, scaled by visible tokens"}
 
     l2_note = {"seed": 1004, "l2": "window bytes per step (0.54 GB over all GPUs) exceed L2 up to 4 GPUs; at 8 GPUs a GPU's 67 MB "
-                                   "share fits L2 and L2 is flushed between timed steps",
-               "lengths": "host array, uploaded by every call"}
+                                   "share fits L2 and L2 is flushed between timed steps"}
     small = bytes_decode < 126e6
     flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if small else None
     flush = (lambda: flush_buf.fill_(1)) if small else None

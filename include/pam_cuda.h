@@ -332,14 +332,13 @@ typedef struct PamDecodeRequest {
     PamLayerSpec layer;
     PamBuffer k_scale, v_scale;
 } PamDecodeRequest;
-/* PagedAttentionEngine.decode (PagedAttentionEngine.swift:533-580).  When seq_lengths is
- * host memory (the reference's buffer is host-visible) the launch is planned from the real
- * lengths: equal ranges per sequence, longest first, no idle CTAs. */
+/* PagedAttentionEngine.decode (PagedAttentionEngine.swift:533-580). */
 int32_t pamc_decode(void *ctx, const PamDecodeRequest *request);
-/* Which kernel a decode request would run on, without launching anything: 1 = the split-K
- * kernels (float16 / bfloat16 / FP8 KV, head_dim 128 or 64, block size a multiple of 16, at
- * most 16 query heads per KV head, pools 16-byte aligned, queries 4-byte aligned, 8-byte for
- * FP8), 0 = the general kernel, -1 = bad request.  Only pointers, types and shapes are read. */
+/* Which kernel a decode request would run on, without launching anything: 1 = the stream
+ * kernel (float16 / bfloat16 / FP8 KV, head_dim 128 or 64 (FP8: 128), block size a multiple
+ * of 16, at most 16 query heads per KV head, pools 16-byte aligned, queries and outputs 4-byte
+ * aligned, queries 8-byte for FP8), 0 = the general kernel, -1 = bad request.  Only pointers,
+ * types and shapes are read. */
 int32_t pamc_decode_path(const PamDecodeRequest *request);
 
 /* Decode without any allocation.  No counterpart in the reference.
@@ -348,30 +347,34 @@ int32_t pamc_decode_path(const PamDecodeRequest *request);
  * is recording work to replay later, a serving loop that has handed all free
  * memory to the KV pools, or a host that only ever gets pointers from another
  * runtime's allocator and cannot reach cudaMalloc itself.  pamc_decode may grow
- * the context's arena (for staged host buffers and for the split-K partial
- * results); this entry point never does.  It calls no cudaMalloc, cudaFree or
+ * the context's arena (for staged host buffers and for the partial results of
+ * shared sequences); this entry point never does.  It calls no cudaMalloc, cudaFree or
  * other allocating routine.
  *
  * Same request, checks, kernels and results as pamc_decode, with these limits:
  *  - q, output, pools, block tables and lengths must all be device memory
  *    (nothing is staged);
- *  - the split-K partial results live in an 8 MiB array that is part of the
- *    library image on every GPU that loads it (held until the process exits).
- *    A request needs batch * heads * splits * (head_dim + 2) * 4 bytes of it,
- *    where splits is what the library's split plan yields for the batch and
- *    max_num_blocks; a request that needs more fails with
- *    PAM_ERR_RESOURCE_EXHAUSTED and a message that states both numbers.
+ *  - the partial results of sequences that several warps share live in an 8 MiB
+ *    array, and the kernel counts on 65 536 words; both are part of the library
+ *    image on every GPU that loads it (held until the process exits).  A request
+ *    needs one word per (sequence, kv head) pair and, of the array, one record of
+ *    (heads / kv_heads) * (head_dim + 4) * 4 bytes per pair of a launch (a launch
+ *    takes at most 2048 sequences) and one per warp; the launch takes fewer warps
+ *    when the array holds no more, but at least four.  A request that needs more
+ *    fails with PAM_ERR_RESOURCE_EXHAUSTED and a message that states the numbers.
+ *    Requests that run on the general kernel (pamc_decode_path() == 0) need neither.
  *  - The first call on each GPU looks up the array's device address (once per
  *    device, with that device current).  Make that first call before starting
  *    any stream capture.
  *  - While the context's stream is being captured the call only records its
  *    launches: it does not wait for the stream and does not run the retry loop
  *    (an eager call does both unless pamc_set_async is on).
- *  - All calls on one GPU share the array and it keeps whatever the previous
- *    call left there.  Nothing in it has to start at zero: every word a call
- *    reads was written earlier by that same call.  Two such decodes that
- *    overlap on one GPU (different streams or contexts) race on the array and
- *    give wrong results; keep them ordered. */
+ *  - All calls on one GPU share the arrays.  The counting words are zero when
+ *    the library is loaded and every call leaves them zero (the warp that
+ *    completes a pair's count puts its word back); of the records a call reads
+ *    only what it has written itself.  Two such decodes that overlap on one GPU
+ *    (different streams or contexts) race on both and give wrong results; keep
+ *    them ordered. */
 int32_t pamc_decode_noalloc(void *ctx, const PamDecodeRequest *request);
 
 /* PagedAttentionPrefillRequest (PagedAttentionTypes.swift:210-256) plus the row

@@ -15,10 +15,13 @@
 //
 // A (sequence, kv head) pair that lies inside one warp's piece gets its output from that
 // warp.  A pair that several warps share gets one partial result (m, l, O per query head)
-// from each of them in a workspace; every warp counts its arrival on the pair's word, and
-// the warp that arrives last combines the partials with a log-sum-exp reduction and puts
-// the word back to zero.  A warp has at most two shared pairs, the first and the last of
-// its piece, so the workspace is two partials per warp, whatever the lengths are.
+// from each of them in a workspace, at a place fixed by the piece's number; every warp adds
+// its tiles of the pair to the pair's counting word, and the warp that completes the count
+// combines the partials, in the order of the pieces, with a log-sum-exp reduction and puts
+// the word back to zero.  Equal inputs therefore give equal bits, whatever the timing.
+// (A variant in which a warp that is through takes the rest of another warp's piece was
+// measured and dropped: the warps finish apart because they share the memory system
+// unevenly, not because their pieces differ, and taking work did not shorten a launch.)
 //
 // Arithmetic per tile: mma.sync m16n8k16 with the query heads of the GQA group as rows (every
 // K/V byte is read once for the whole group), online softmax in registers in the log2
@@ -154,8 +157,8 @@ struct StreamArgs {
     const int32_t* tables;
     const uint32_t* lens;
     void* out;
-    float* workspace;     // [warps of the grid][2][G][HD + 4]
-    int* counters;        // [batch][kvHeads], zero between launches
+    float* records;       // partial results, G x (HD + 4) floats each
+    int* counters;        // [batch][kvHeads]: tiles of the pair whose partial result is in; zero between launches
     int batch, heads, kvHeads, blockSize, maxNumBlocks, window, poolBlocks;
     float scaleLog2;
 };
@@ -644,55 +647,94 @@ __device__ __forceinline__ void advance(Cursor& c, const int* prefix, const int*
 
 constexpr int kPartialPad = 4;      // a partial row is head_dim + 4 floats: O, then m and l (16-byte rows)
 
-// Combination of the partials of one (sequence, kv head) pair by the warp that arrived last.
-// The contributions come from warps wf .. wl of the grid, each in its first slot, except that
-// warp wf holds it in its second slot when the pair begins inside its piece.
+// Where the partial results of a pair go.  Piece w of the list (warp w's) covers tiles
+// [w * quota, (w + 1) * quota).  A pair that begins in piece wf and is the i-th pair of the
+// launch owns the records from wf + i on, one per piece it overlaps, in the order of the
+// pieces: the pair before it ends in piece wf or earlier and owns records up to wf + i - 1.
+__device__ __forceinline__ int64_t recordBase(int pairBegin, int pairIndex, int quota) {
+    return static_cast<int64_t>(pairBegin / quota) + pairIndex;
+}
+
+// Combination of the partials of one (sequence, kv head) pair by the warp whose tiles
+// completed it: records first .. first + n - 1, always in that order, so that equal inputs
+// give equal bits.  Two heads at a time; the (m, l) of all contributions are read by the
+// lanes in parallel, the columns with sixteen loads in flight per lane (each lane four
+// columns of eight records of both heads): the pairs of a launch tend to complete together
+// at its end, where nothing else hides the latency of these reads.
 template <class P>
-__device__ __forceinline__ void combine(const StreamArgs& a, int b, int kvh, int G, int wf, int wl, bool firstInSecondSlot,
-                                        int lane) {
-    constexpr int HD = P::HD, RS = HD + kPartialPad;
+__device__ __forceinline__ void combine(const float* __restrict__ records, typename P::Out* __restrict__ out, int heads, int b,
+                                        int kvh, int G, int64_t first, int n, int lane) {
+    constexpr int HD = P::HD, RS = HD + kPartialPad, U = 8;
     using Out = typename P::Out;
-    const int n = wl - wf + 1;
-    for (int g = 0; g < G; ++g) {
-        auto row = [&](int i) {
-            const int slot = (i == 0 && firstInSecondSlot) ? 1 : 0;
-            return a.workspace + ((static_cast<int64_t>(wf + i) * 2 + slot) * G + g) * RS;
-        };
-        float M = -INFINITY;
-        for (int i = lane; i < n; i += 32) M = fmaxf(M, __ldcg(row(i) + HD));
+    const bool holds = lane * 4 < HD;                    // head_dim 64: half the lanes hold columns
+    const int64_t step = static_cast<int64_t>(G) * RS;   // from one contribution to the next
+    for (int g = 0; g < G; g += 2) {
+        const bool two = g + 1 < G;
+        const float* base0 = records + (first * G + g) * RS;
+        const float* base1 = base0 + (two ? RS : 0);
+        float M0 = -INFINITY, M1 = -INFINITY;
+        for (int i = lane; i < n; i += 32) {
+            M0 = fmaxf(M0, __ldcg(base0 + i * step + HD));
+            M1 = fmaxf(M1, __ldcg(base1 + i * step + HD));
+        }
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xFFFFFFFFu, M, o));
-        float lsum = 0.f;
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int base = 0; base < n; base += 32) {
-            // 32 contributions at a time: lane i weighs contribution base + i, every lane then sums
-            // four columns over them
-            const int mine = base + lane;
-            float wgt = 0.f;
+        for (int o = 16; o > 0; o >>= 1) {
+            M0 = fmaxf(M0, __shfl_xor_sync(0xFFFFFFFFu, M0, o));
+            M1 = fmaxf(M1, __shfl_xor_sync(0xFFFFFFFFu, M1, o));
+        }
+        float l0 = 0.f, l1 = 0.f;
+        float4 acc0 = make_float4(0.f, 0.f, 0.f, 0.f), acc1 = acc0;
+        for (int c0 = 0; c0 < n; c0 += 32) {
+            const int mine = c0 + lane;
+            float w0 = 0.f, w1 = 0.f;
             if (mine < n) {
-                wgt = exp2f(__ldcg(row(mine) + HD) - M);
-                lsum += wgt * __ldcg(row(mine) + HD + 1);
+                const float2 ml0 = __ldcg(reinterpret_cast<const float2*>(base0 + mine * step + HD));
+                const float2 ml1 = __ldcg(reinterpret_cast<const float2*>(base1 + mine * step + HD));
+                w0 = exp2f(ml0.x - M0);
+                w1 = exp2f(ml1.x - M1);
+                l0 += w0 * ml0.y;
+                l1 += w1 * ml1.y;
             }
-            const int cnt = min(32, n - base);
-            const bool holds = lane * 4 < HD;              // head_dim 64: half the lanes hold columns
-#pragma unroll 4
-            for (int i = 0; i < cnt; ++i) {
-                const float w = __shfl_sync(0xFFFFFFFFu, wgt, i);
-                if (holds) {
-                    const float4 v = __ldcg(reinterpret_cast<const float4*>(row(base + i)) + lane);
-                    acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w;
+            const int cnt = min(32, n - c0);
+            for (int i0 = 0; i0 < cnt; i0 += U) {
+                float4 v0[U], v1[U];
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    v0[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    v1[u] = v0[u];
+                    if (holds && i0 + u < cnt) {
+                        v0[u] = __ldcg(reinterpret_cast<const float4*>(base0 + (c0 + i0 + u) * step) + lane);
+                        if (two) v1[u] = __ldcg(reinterpret_cast<const float4*>(base1 + (c0 + i0 + u) * step) + lane);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const float a0 = __shfl_sync(0xFFFFFFFFu, w0, (i0 + u) & 31);     // (zero beyond cnt)
+                    const float a1 = __shfl_sync(0xFFFFFFFFu, w1, (i0 + u) & 31);
+                    acc0.x += a0 * v0[u].x; acc0.y += a0 * v0[u].y; acc0.z += a0 * v0[u].z; acc0.w += a0 * v0[u].w;
+                    acc1.x += a1 * v1[u].x; acc1.y += a1 * v1[u].y; acc1.z += a1 * v1[u].z; acc1.w += a1 * v1[u].w;
                 }
             }
         }
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) lsum += __shfl_xor_sync(0xFFFFFFFFu, lsum, o);
-        if (lane * 4 < HD) {
-            const float inv = 1.f / lsum;
-            Out* dst = static_cast<Out*>(a.out) + (static_cast<int64_t>(b) * a.heads + kvh * G + g) * HD + lane * 4;
-            dst[0] = fromFloat<Out>(acc.x * inv);
-            dst[1] = fromFloat<Out>(acc.y * inv);
-            dst[2] = fromFloat<Out>(acc.z * inv);
-            dst[3] = fromFloat<Out>(acc.w * inv);
+        for (int o = 16; o > 0; o >>= 1) {
+            l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, o);
+            l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, o);
+        }
+        if (holds) {
+            Out* dst = out + (static_cast<int64_t>(b) * heads + kvh * G + g) * HD + lane * 4;
+            const float inv0 = 1.f / l0;
+            dst[0] = fromFloat<Out>(acc0.x * inv0);
+            dst[1] = fromFloat<Out>(acc0.y * inv0);
+            dst[2] = fromFloat<Out>(acc0.z * inv0);
+            dst[3] = fromFloat<Out>(acc0.w * inv0);
+            if (two) {
+                const float inv1 = 1.f / l1;
+                dst[HD + 0] = fromFloat<Out>(acc1.x * inv1);
+                dst[HD + 1] = fromFloat<Out>(acc1.y * inv1);
+                dst[HD + 2] = fromFloat<Out>(acc1.z * inv1);
+                dst[HD + 3] = fromFloat<Out>(acc1.w * inv1);
+            }
         }
     }
 }
@@ -709,6 +751,7 @@ decodeStreamKernel(const StreamArgs a) {
     constexpr int kRingBytes = (kWarps * NS * STAGEB + 15) / 16 * 16;
     int* prefix = reinterpret_cast<int*>(smem + kRingBytes);     // [batch + 1]
     int* first = prefix + a.batch + 1;                           // [batch]
+    const int warpsInGrid = gridDim.x * kWarps, wid = blockIdx.x * kWarps + warp;
     buildPrefix(prefix, first, a);
 
     // An empty context (the reference divides 0 by 0 there) gets zeros.
@@ -718,41 +761,40 @@ decodeStreamKernel(const StreamArgs a) {
         for (int i = threadIdx.x; i < a.heads * HD; i += kWarps * 32) dst[i] = fromFloat<Out>(0.f);
     }
 
-    // this warp's piece of the list
+    // This warp's piece of the list.
     const int total = prefix[a.batch];
-    const int warpsInGrid = gridDim.x * kWarps, wid = blockIdx.x * kWarps + warp;
-    const int quota = (total + warpsInGrid - 1) / warpsInGrid;
+    const int quota = max((total + warpsInGrid - 1) / warpsInGrid, 1);
     const int begin = min(wid * quota, total), end = min(begin + quota, total);
-    if (begin >= end) return;
-    const int count = end - begin;
+    if (begin >= end) return;                        // (no barrier below this line)
     const int tilesPerPage = a.blockSize / kTileTokens;
-
     unsigned char* ring = smem + static_cast<size_t>(warp) * NS * STAGEB;
     const uint32_t ringAddr = smemAddr(ring);
 
     Cursor ahead, cur;                       // where the loads are, where the arithmetic is
     locate(ahead, begin, prefix, first, a.batch, a.kvHeads);
     cur = ahead;
+    int issued = begin;
     auto issueNext = [&](int slot) {
+        if (issued >= end) return;
         const int tile = ahead.firstTile + ahead.tile;
         const int page = tile / tilesPerPage, within = tile - page * tilesPerPage;
         const int32_t* table = a.tables + static_cast<int64_t>(ahead.b) * a.maxNumBlocks;
         const int64_t blk = min(max(table[page], 0), a.poolBlocks - 1);     // never read outside the pool
         P::issue(ringAddr + slot * STAGEB, ring + slot * STAGEB, a, blk, ahead.kvh, within, lane);
         advance(ahead, prefix, first, a.batch, a.kvHeads);
+        ++issued;
     };
-    int issued = 0;
 #pragma unroll
     for (int s = 0; s < NS; ++s) {
-        if (issued < count) { issueNext(s); ++issued; }
+        issueNext(s);
         cpAsyncCommit();
     }
 
     typename P::Query q;
     typename P::Acc acc;
-    int len = 0, windowStart = 0, pairBegin = 0;
+    int len = 0, windowStart = 0, pairBegin = 0, pairTiles = 0;
     bool fresh = true;
-    for (int it = 0; it < count; ++it) {
+    for (int done = begin; done < end;) {
         if (fresh) {
             // a new (sequence, kv head) pair starts in this warp
             const uint32_t L = a.lens[cur.b];
@@ -760,26 +802,28 @@ decodeStreamKernel(const StreamArgs a) {
             len = static_cast<int>(L < static_cast<uint32_t>(maxTokens) ? L : static_cast<uint32_t>(maxTokens));
             windowStart = v.windowStart;
             pairBegin = prefix[cur.b] + cur.kvh * cur.tilesB;
+            pairTiles = 0;
             P::loadQuery(q, a, static_cast<int64_t>(cur.b) * a.heads + cur.kvh * G, G, lane);
             P::reset(acc, len - windowStart);
             fresh = false;
         }
         cpAsyncWait<NS - 1>();
         __syncwarp();
-        const int slot = it % NS;
+        const int slot = (done - begin) % NS;
         P::tile(acc, q, ring + slot * STAGEB, ringAddr + slot * STAGEB, (cur.firstTile + cur.tile) * kTileTokens, windowStart,
                 len, a.scaleLog2, lane);
         __syncwarp();
-        if (issued < count) { issueNext(slot); ++issued; }
+        ++done;
+        ++pairTiles;
+        issueNext(slot);
         cpAsyncCommit();
 
-        const bool pairEnds = cur.tile + 1 == cur.tilesB;
-        if (pairEnds || it + 1 == count) {
+        if (cur.tile + 1 == cur.tilesB || done == end) {
+            // the pair ends here, or the piece does
             P::finish(acc);
-            const int pairEnd = pairBegin + cur.tilesB;
             const int64_t outRow = static_cast<int64_t>(cur.b) * a.heads + cur.kvh * G;
-            if (pairBegin >= begin && pairEnd <= end) {
-                // the whole pair was this warp's: its output
+            if (pairTiles == cur.tilesB) {
+                // every tile of the pair was this warp's: its output
                 Out* dst = static_cast<Out*>(a.out) + outRow * HD;
                 P::each(acc, G, lane,
                         [&](int g, int d, float v0, float v1) {
@@ -793,8 +837,12 @@ decodeStreamKernel(const StreamArgs a) {
                         },
                         [](int, float, float) {});
             } else {
-                const int slot2 = pairBegin > begin ? 1 : 0;      // the first pair of the piece, or its last
-                float* part = a.workspace + ((static_cast<int64_t>(wid) * 2 + slot2) * G) * RS;
+                // one record per piece the pair overlaps, in the order of the pieces; the tiles
+                // counted so far decide who combines
+                const int pairIndex = cur.b * a.kvHeads + cur.kvh;
+                const int firstPiece = pairBegin / quota;
+                const int64_t base = recordBase(pairBegin, pairIndex, quota);
+                float* part = a.records + ((base + (wid - firstPiece)) * G) * RS;
                 P::each(acc, G, lane,
                         [&](int g, int d, float v0, float v1) {
                             part[g * RS + d] = v0;
@@ -804,21 +852,20 @@ decodeStreamKernel(const StreamArgs a) {
                             part[g * RS + HD] = m;
                             part[g * RS + HD + 1] = l;
                         });
-                // the partial is published before the arrival is counted; the last arrival
-                // reads the others' partials from L2
+                // the record is published before its tiles are counted; whoever completes the
+                // count reads the others' records from L2
                 __threadfence();
                 __syncwarp();
-                const int wf = pairBegin / quota, wl = (pairEnd - 1) / quota;
-                int last = 0;
+                int* tilesDone = a.counters + pairIndex;
+                bool last = false;
                 if (lane == 0) {
-                    int* word = a.counters + static_cast<int64_t>(cur.b) * a.kvHeads + cur.kvh;
-                    last = atomicAdd(word, 1) == wl - wf ? 1 : 0;
-                    if (last) *word = 0;                           // ready for the next launch
+                    last = atomicAdd(tilesDone, pairTiles) + pairTiles == cur.tilesB;
+                    if (last) *tilesDone = 0;                   // ready for the next launch
                 }
-                last = __shfl_sync(0xFFFFFFFFu, last, 0);
-                if (last) {
+                if (__shfl_sync(0xFFFFFFFFu, last ? 1 : 0, 0)) {
                     __threadfence();
-                    combine<P>(a, cur.b, cur.kvh, G, wf, wl, pairBegin > wf * quota, lane);
+                    const int n = (pairBegin + cur.tilesB - 1) / quota - firstPiece + 1;
+                    combine<P>(a.records, static_cast<Out*>(a.out), a.heads, cur.b, cur.kvh, G, base, n, lane);
                 }
             }
             fresh = true;
@@ -845,7 +892,7 @@ size_t streamSharedBytes(int batch) {
     return ring + (static_cast<size_t>(2) * batch + 1) * sizeof(int);
 }
 
-// CTAs of the launch: every resident slot of the GPU, fewer when the workspace is small.
+// CTAs of the launch: every resident slot of the GPU.
 template <class P>
 cudaError_t streamGrid(int batch, int smCount, int* grid) {
     static std::atomic<int> perSm[64][4];      // by device and by shared-memory class of the batch
@@ -870,20 +917,23 @@ cudaError_t streamGrid(int batch, int smCount, int* grid) {
     return cudaSuccess;
 }
 
+// One record per piece and per pair bounds what recordBase() hands out.
+size_t recordBytes(int grid, int pairs, int G, int headDim) {
+    return (static_cast<size_t>(grid) * kWarps + static_cast<size_t>(pairs)) * G * (headDim + kPartialPad) * sizeof(float);
+}
+
 template <class P>
 cudaError_t launchStreamT(const DecodeParams& p, int smCount, cudaStream_t stream, int* launches) {
     int grid = 0;
     cudaError_t e = streamGrid<P>(p.batch, smCount, &grid);
     if (e != cudaSuccess) return e;
-    const int G = p.heads / p.kvHeads;
-    const size_t perWarp = static_cast<size_t>(2) * G * (P::HD + kPartialPad) * sizeof(float);
-    // a smaller workspace (the fixed array of the no-allocation call) holds fewer warps' partials
-    const size_t holds = p.workspaceBytes / perWarp / kWarps;
-    if (holds < 1) return cudaErrorInvalidValue;
-    if (static_cast<size_t>(grid) > holds) grid = static_cast<int>(holds);
+    const int G = p.heads / p.kvHeads, pairs = p.batch * p.kvHeads;
+    // a smaller workspace (the fixed array of the no-allocation call) holds fewer warps' records
+    while (grid > 1 && recordBytes(grid, pairs, G, P::HD) > p.workspaceBytes) grid = grid * 3 / 4;
+    if (recordBytes(grid, pairs, G, P::HD) > p.workspaceBytes) return cudaErrorInvalidValue;
     StreamArgs a{};
     a.q = p.q; a.kPool = p.kPool; a.vPool = p.vPool; a.kScale = p.kScale; a.vScale = p.vScale;
-    a.tables = p.tables; a.lens = p.lens; a.out = p.out; a.workspace = p.workspace; a.counters = p.counters;
+    a.tables = p.tables; a.lens = p.lens; a.out = p.out; a.records = p.workspace; a.counters = p.counters;
     a.batch = p.batch; a.heads = p.heads; a.kvHeads = p.kvHeads; a.blockSize = p.blockSize; a.maxNumBlocks = p.maxNumBlocks;
     a.window = p.window; a.poolBlocks = p.poolBlocks;
     a.scaleLog2 = (1.0f / sqrtf(static_cast<float>(p.headDim))) * kLog2e;
@@ -914,9 +964,9 @@ bool decodeStreamApplies(const DecodeParams& p) {
     // 8-byte) words; anything less aligned goes to the general kernel
     const auto aligned = [](const void* ptr, uintptr_t a) { return (reinterpret_cast<uintptr_t>(ptr) & (a - 1)) == 0; };
     if (!shape || !aligned(p.kPool, 16) || !aligned(p.vPool, 16)) return false;
-    // the list of tiles is indexed with 32-bit integers
-    if (static_cast<int64_t>(p.maxNumBlocks) * p.blockSize / kTileTokens * p.kvHeads * static_cast<int64_t>(kDecodeStreamMaxBatch) >= (int64_t(1) << 31))
-        return false;
+    // positions in the list of tiles are ints
+    const int slice = p.batch < kDecodeStreamMaxBatch ? p.batch : kDecodeStreamMaxBatch;
+    if (static_cast<int64_t>(p.maxNumBlocks) * p.blockSize / kTileTokens * p.kvHeads * slice >= (int64_t(1) << 30)) return false;
     if (p.dtype == kF16 || p.dtype == kBF16) return (p.headDim == 128 || p.headDim == 64) && aligned(p.q, 4) && aligned(p.out, 4);
     if (p.dtype == kFP8)
         return p.headDim == 128 && p.kScale && p.vScale && aligned(p.q, 8) && aligned(p.out, 2) && aligned(p.kScale, 4) &&
@@ -924,12 +974,20 @@ bool decodeStreamApplies(const DecodeParams& p) {
     return false;
 }
 
-size_t decodeStreamWorkspaceBytes(const DecodeParams& p, int smCount) {
+int decodeStreamWarps(const DecodeParams& p, int smCount) {
     int grid = 0;
-    const cudaError_t e = dispatch(p, [&](auto tiles) { return streamGrid<decltype(tiles)>(p.batch < kDecodeStreamMaxBatch ? p.batch : kDecodeStreamMaxBatch, smCount, &grid); });
+    const int slice = p.batch < kDecodeStreamMaxBatch ? p.batch : kDecodeStreamMaxBatch;
+    const cudaError_t e = dispatch(p, [&](auto tiles) { return streamGrid<decltype(tiles)>(slice, smCount, &grid); });
     if (e != cudaSuccess) { cudaGetLastError(); return 0; }
-    const int G = p.heads / p.kvHeads;
-    return static_cast<size_t>(grid) * kWarps * 2 * G * (p.headDim + kPartialPad) * sizeof(float);
+    return grid * kWarps;
+}
+
+size_t decodeStreamWorkspaceBytes(const DecodeParams& p, int smCount) {
+    const int warps = decodeStreamWarps(p, smCount);
+    if (warps == 0) return 0;
+    const int slice = p.batch < kDecodeStreamMaxBatch ? p.batch : kDecodeStreamMaxBatch;
+    const int pairs = slice * p.kvHeads;
+    return recordBytes(warps / kWarps, pairs, p.heads / p.kvHeads, p.headDim);
 }
 
 cudaError_t launchDecodeStream(const DecodeParams& p, int smCount, cudaStream_t stream, int* launches) {

@@ -58,47 +58,37 @@ struct DecodeParams {
     const void* kScale;       // FP8: [block][kvHeads] float16
     const void* vScale;
     int batch, heads, kvHeads, headDim, blockSize, maxNumBlocks, window, dtype;
-    int maxContext;           // upper bound of any length in `lens` (for split sizing)
     int poolBlocks;           // blocks in the pools; table entries are clamped into [0, poolBlocks)
-    float* workspace;         // split-K partials, decodeWorkspaceBytes() bytes
+    float* workspace;         // partial results of the stream kernel, decodeWorkspaceBytes() bytes
     size_t workspaceBytes;
-    // Optional.  With a host copy of `lens` and a plan cache the launch is planned from the
-    // real lengths: ranges of equal size per sequence, longest first, exactly as many CTAs
-    // as there is work.  With `counters` (device words, all zero between launches, one per
-    // (sequence, kv head)) the splits are merged by the CTA that finishes last instead of
-    // by a second kernel.
-    const uint32_t* hostLens;
-    struct DecodePlanCache* planCache;
+    // Counting words of the stream kernel: device ints, all zero between launches, one per
+    // (sequence, kv head) pair, kept by the caller and written by nothing else.
     int* counters;
     int64_t countersCap;
 };
-// State of the host-planned launches of one context (work list on the device, staging).
-struct DecodePlanCache;
-DecodePlanCache* createDecodePlanCache();
-void destroyDecodePlanCache(DecodePlanCache* cache);
-// True when `p` runs on the split kernels (type, shape and pointer alignment allow it).
+// True when `p` runs on the stream kernel (type, shape and pointer alignment allow it).
 bool decodeTakesSplitPath(const DecodeParams& p);
-// Bytes of split-K workspace the launch of `p` needs (0 when it runs unsplit).  With host
-// lengths this builds the plan (and may enqueue its upload on `stream`).
-size_t decodeWorkspaceBytes(const DecodeParams& p, int smCount, cudaStream_t stream);
+// Bytes of workspace the launch of `p` needs (0 for the general kernel).
+size_t decodeWorkspaceBytes(const DecodeParams& p, int smCount);
 cudaError_t launchDecode(const DecodeParams& p, int smCount, cudaStream_t stream, int* launches);
 // The persistent stream kernel (decode_stream_kernel.cu): float16 / bfloat16 / FP8 pools,
 // head_dim 128 (64 for 16-bit pools), block size a multiple of 16, at most 16 query heads
-// per KV head, aligned pointers.  It needs `workspace` (decodeStreamWorkspaceBytes) and
-// `counters` (zero between launches, batch * kvHeads words).  Batches beyond
+// per KV head, aligned pointers.  It needs `workspace` (decodeStreamWorkspaceBytes; with less
+// it launches fewer warps) and `counters` (batch * kvHeads words).  Batches beyond
 // kDecodeStreamMaxBatch run as several launches.
 constexpr int kDecodeStreamMaxBatch = 2048;
 bool decodeStreamApplies(const DecodeParams& p);
+int decodeStreamWarps(const DecodeParams& p, int smCount);
 size_t decodeStreamWorkspaceBytes(const DecodeParams& p, int smCount);
 cudaError_t launchDecodeStream(const DecodeParams& p, int smCount, cudaStream_t stream, int* launches);
-// Device addresses of the fixed scratch array and arrival words inside the library image.
+// Device addresses of the fixed arrays inside the library image (workspace, counting words).
 cudaError_t decodeStaticScratch(float** scratch, int** counters, int64_t* countersCap);
 
-// Same decode with the split-K workspace taken from a fixed array inside the
-// library (decodeStaticScratchBytes() bytes per GPU) instead of p.workspace.
-// Allocates nothing; fails with cudaErrorInvalidValue when the launch would
-// need more workspace than the array holds.  The current device must be the
-// one the pointers in `p` live on.
+// Same decode with the workspace and the counting words taken from fixed arrays inside the
+// library (decodeStaticScratchBytes() bytes and 65 536 words per GPU) instead of
+// p.workspace and p.counters.  Allocates nothing; fails with cudaErrorInvalidValue when the
+// batch has more pairs than words or the array cannot hold one record per pair and a CTA's
+// worth of warps.  The current device must be the one the pointers in `p` live on.
 size_t decodeStaticScratchBytes();
 cudaError_t launchDecodeStatic(const DecodeParams& p, int smCount, cudaStream_t stream, int* launches);
 

@@ -12,6 +12,7 @@
 #include <map>
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <set>
@@ -100,8 +101,7 @@ struct Context {
     size_t qStageCap = 0;
     void* outStage = nullptr; // device side of a pageable host output of pam_decode
     size_t outStageCap = 0;
-    pam::DecodePlanCache* planCache = nullptr;   // work lists of decodes whose lengths the host knows
-    int* mergeCounters = nullptr;                // zero between launches: split arrivals per (sequence, kv head)
+    int* mergeCounters = nullptr;                // zero between launches: three counting words per (sequence, kv head)
     int64_t mergeCountersCap = 0;
     long long waitLimitCycles = 0;               // 0: the prefill kernel's default bound on its waits
     int dropFirstVTile = 0;                      // test switch, see pamc_test_starve_prefill
@@ -183,9 +183,31 @@ Placement placementOf(const void* p) {
     return r;
 }
 
+// One zeroed arrival word per (sequence, kv head) pair of the largest decode so far.
+struct Context;
+bool ensureMergeCounters(Context* c, int64_t pairs);
+
 // Operations that need the GPU fail like a missing device (PagedAttentionTypes.swift:36-37).
 int32_t noGpu(Context* c) {
     return c->fail(PAM_ERR_DEVICE_INIT, "Metal device or command queue could not be initialized.");
+}
+
+bool ensureMergeCounters(Context* c, int64_t pairs) {
+    if (pairs <= c->mergeCountersCap) return true;
+    cudaStreamSynchronize(c->stream);
+    if (c->mergeCounters) cudaFree(c->mergeCounters);
+    c->mergeCounters = nullptr;
+    c->mergeCountersCap = 0;
+    const int64_t cap = pairs + pairs / 2;
+    if (cudaMalloc(reinterpret_cast<void**>(&c->mergeCounters), static_cast<size_t>(cap) * sizeof(int)) != cudaSuccess ||
+        cudaMemsetAsync(c->mergeCounters, 0, static_cast<size_t>(cap) * sizeof(int), c->stream) != cudaSuccess) {
+        cudaGetLastError();
+        if (c->mergeCounters) cudaFree(c->mergeCounters);
+        c->mergeCounters = nullptr;
+        return false;
+    }
+    c->mergeCountersCap = cap;
+    return true;
 }
 
 // Page-locked scratch of at least `bytes` (nullptr when it cannot be had: the caller then
@@ -518,7 +540,7 @@ int32_t validateDecode(Context* c, const PamDecodeRequest& rq) {
     return 0;
 }
 
-int32_t decodeImpl(Context* c, const PamDecodeRequest& rq, int maxContext) {
+int32_t decodeImpl(Context* c, const PamDecodeRequest& rq) {
     // PagedAttentionEngine.swift:533-580
     if (validateDecode(c, rq) != 0) return -1;
     if (c->device < 0) return noGpu(c);
@@ -545,16 +567,12 @@ int32_t decodeImpl(Context* c, const PamDecodeRequest& rq, int maxContext) {
         p.vScale = rq.v_scale.ptr;
         p.batch = rq.batch_size; p.heads = l.num_heads; p.kvHeads = l.num_kv_heads; p.headDim = l.head_dim;
         p.blockSize = l.block_size; p.maxNumBlocks = rq.max_num_blocks; p.window = window; p.dtype = l.data_type;
-        p.maxContext = maxContext;
         p.poolBlocks = poolBlocksOf(rq.k_pool, rq.v_pool, l);
-        // lengths the host can read (the reference's seqLengths buffer is host-visible) let the
-        // launch be planned from the real lengths
-        p.hostLens = p.lens != rq.seq_lengths.ptr ? static_cast<const uint32_t*>(rq.seq_lengths.ptr) : nullptr;
-        p.planCache = c->planCache;
+        if (!ensureMergeCounters(c, static_cast<int64_t>(rq.batch_size) * l.num_kv_heads)) return cudaErrorMemoryAllocation;
         p.counters = c->mergeCounters;
         p.countersCap = c->mergeCountersCap;
         if (!st.ok()) return cudaErrorMemoryAllocation;
-        tempBytes = pam::decodeWorkspaceBytes(p, c->smCount, c->stream);
+        tempBytes = pam::decodeWorkspaceBytes(p, c->smCount);
         if (tempBytes) {
             p.workspace = static_cast<float*>(c->arena.take(tempBytes));
             p.workspaceBytes = tempBytes;
@@ -601,23 +619,22 @@ int32_t decodeNoAllocImpl(Context* c, const PamDecodeRequest& rq) {
     p.batch = rq.batch_size; p.heads = l.num_heads; p.kvHeads = l.num_kv_heads; p.headDim = l.head_dim;
     p.blockSize = l.block_size; p.maxNumBlocks = rq.max_num_blocks;
     p.window = l.window_size > 0 ? l.window_size : c->defaultWindow;
-    p.dtype = l.data_type; p.maxContext = 0;
+    p.dtype = l.data_type;
     p.poolBlocks = poolBlocksOf(rq.k_pool, rq.v_pool, l);
-    p.hostLens = nullptr; p.planCache = nullptr; p.counters = nullptr; p.countersCap = 0;
-    // What the call needs of the built-in arrays: one arrival word per (sequence, kv head)
-    // pair (65 536 words) and, per warp of the launch, two partial results of the GQA group
-    // (8 MiB; the launch takes fewer warps when that is all the array holds, but at least
-    // one CTA's worth).
-    const size_t pairs = B * static_cast<size_t>(l.num_kv_heads);
-    const size_t perCta = static_cast<size_t>(4) * 2 * (l.num_heads / l.num_kv_heads) * (static_cast<size_t>(l.head_dim) + 4) * sizeof(float);
-    size_t need = std::min(pam::decodeWorkspaceBytes(p, c->smCount, c->stream), pam::decodeStaticScratchBytes());
-    if (pam::decodeStreamApplies(p)) need = std::max(std::min(need, pam::decodeStaticScratchBytes()), perCta);
-    else need = pam::decodeWorkspaceBytes(p, c->smCount, c->stream);
-    if (need > pam::decodeStaticScratchBytes() || (pam::decodeStreamApplies(p) && pairs > (size_t(1) << 16)))
+    p.counters = nullptr; p.countersCap = 0;
+    // What the call needs of the built-in arrays: one counting word per (sequence, kv head)
+    // pair (65 536 words) and records for the partial results: one per warp of the launch and
+    // one per pair (8 MiB; the launch takes fewer warps when that is all the array holds, but
+    // at least one CTA's worth).  The general kernel needs neither.
+    const size_t pairs = std::min<size_t>(B, pam::kDecodeStreamMaxBatch) * static_cast<size_t>(l.num_kv_heads);
+    const size_t words = pam::decodeStreamApplies(p) ? B * static_cast<size_t>(l.num_kv_heads) : 0;
+    const size_t recordBytes = static_cast<size_t>(l.num_heads / l.num_kv_heads) * (static_cast<size_t>(l.head_dim) + 4) * sizeof(float);
+    const size_t need = pam::decodeStreamApplies(p) ? std::min(pam::decodeWorkspaceBytes(p, c->smCount), (4 + pairs) * recordBytes) : 0;
+    if (need > pam::decodeStaticScratchBytes() || words > (size_t(1) << 16))
         return c->fail(PAM_ERR_RESOURCE_EXHAUSTED,
                        "GPU resource exhausted: this decode needs " + std::to_string(need) +
-                           " bytes of split-K scratch and " + std::to_string(pairs) +
-                           " arrival words, the built-in scratch holds " +
+                           " bytes of scratch for partial results and " + std::to_string(words) +
+                           " counting words, the built-in arrays hold " +
                            std::to_string(pam::decodeStaticScratchBytes()) +
                            " bytes and 65536 words; use pamc_decode, or a smaller batch or fewer heads.");
     const double t0 = nowMs();
@@ -892,13 +909,12 @@ void* pamc_create_context_on(int32_t device) {
         return nullptr;
     }
     *c->hostErr = 0;
-    c->planCache = pam::createDecodePlanCache();
     constexpr int64_t kCounters = 1 << 16;
     if (cudaMalloc(reinterpret_cast<void**>(&c->mergeCounters), kCounters * sizeof(int)) == cudaSuccess &&
         cudaMemset(c->mergeCounters, 0, kCounters * sizeof(int)) == cudaSuccess) {
         c->mergeCountersCap = kCounters;
     } else {
-        // without them the splits are merged by a kernel of its own
+        // (asked for again by the first decode)
         cudaGetLastError();
         if (c->mergeCounters) cudaFree(c->mergeCounters);
         c->mergeCounters = nullptr;
@@ -932,7 +948,6 @@ void pam_destroy_context(void* ctx) {
     if (c->qStage) cudaFree(c->qStage);
     if (c->outStage) cudaFree(c->outStage);
     if (c->mergeCounters) cudaFree(c->mergeCounters);
-    pam::destroyDecodePlanCache(c->planCache);
     if (c->ownStream) cudaStreamDestroy(c->ownStream);
     delete c;
 }
@@ -1407,7 +1422,7 @@ int32_t pamc_decode(void* ctx, const PamDecodeRequest* request) {
     Context* c = asCtx(ctx);
     std::lock_guard<std::mutex> g(c->mu);
     DeviceGuard dg(c->device);
-    int32_t rc = decodeImpl(c, *request, 0);
+    int32_t rc = decodeImpl(c, *request);
     if (rc == 0) c->clearError();
     return rc;
 }
@@ -1420,6 +1435,8 @@ int32_t pamc_decode_path(const PamDecodeRequest* request) {
     p.kScale = rq.k_scale.ptr; p.vScale = rq.v_scale.ptr;
     p.heads = rq.layer.num_heads; p.kvHeads = rq.layer.num_kv_heads; p.headDim = rq.layer.head_dim;
     p.blockSize = rq.layer.block_size; p.dtype = rq.layer.data_type;
+    p.batch = rq.batch_size > 0 ? rq.batch_size : 1;
+    p.maxNumBlocks = rq.max_num_blocks > 0 ? rq.max_num_blocks : 1;
     if (p.kvHeads <= 0 || p.heads <= 0 || p.blockSize <= 0) return -1;
     return pam::decodeTakesSplitPath(p) ? 1 : 0;
 }
@@ -1438,10 +1455,9 @@ int32_t pamc_decode_noalloc(void* ctx, const PamDecodeRequest* request) {
 // (CABI.swift:306-330, 339-372 build and upload all of it on every call).  Row i of the copy
 // belongs to batch_ids[i]; a row is sent again in full when it holds another sequence, or
 // one whose existing entries were replaced (copy-on-write, free and re-allocation), and only
-// from its old end on when the table merely grew.  The lengths go up every time.  Returns
-// the host copy of the lengths (page-locked, valid until the next call on this cache).
+// from its old end on when the table merely grew.  The lengths go up every time.
 static int32_t refreshResidentTables(Context* c, Cache* k, const int64_t* ids, int B, int* maxNumBlocks, int* maxLen,
-                                     const uint32_t** hostLens, size_t* uploadedBytes) {
+                                     size_t* uploadedBytes) {
     Cache::Resident& r = k->res;
     std::lock_guard<std::mutex> gk(k->mu);
     auto fail = [&](cudaError_t e) {
@@ -1538,7 +1554,6 @@ static int32_t refreshResidentTables(Context* c, Cache* k, const int64_t* ids, i
     }
     if (e == cudaSuccess) e = cudaEventRecord(r.consumed, c->stream);
     if (e != cudaSuccess) return fail(e);
-    *hostLens = reinterpret_cast<const uint32_t*>(r.pinned);
     *uploadedBytes = need;
     return 0;
 }
@@ -1593,9 +1608,8 @@ int32_t pam_decode(void* ctx, void* cache, const int64_t* batch_ids, int32_t bat
         outDev = c->outStage;
     }
     int maxNumBlocks = 1, maxLen = 0;
-    const uint32_t* hostLens = nullptr;
     size_t uploaded = 0;
-    if (int32_t rc = refreshResidentTables(c, k, batch_ids, batch_size, &maxNumBlocks, &maxLen, &hostLens, &uploaded)) return failed(rc);
+    if (int32_t rc = refreshResidentTables(c, k, batch_ids, batch_size, &maxNumBlocks, &maxLen, &uploaded)) return failed(rc);
     // validateDecode's pool bound uses maxNumBlocks (a lower bound, PagedAttentionEngine.swift:1931)
     const size_t poolNeed = static_cast<size_t>(maxNumBlocks) * layer.block_size * kvBytesPerToken(layer);
     if (k->poolBytes < poolNeed) return failed(c->fail(PAM_ERR_BUFFER_TOO_SMALL, bufferTooSmall("K pool", poolNeed, k->poolBytes)));
@@ -1608,16 +1622,15 @@ int32_t pam_decode(void* ctx, void* cache, const int64_t* batch_ids, int32_t bat
     p.kScale = k->kScale; p.vScale = k->vScale;
     p.batch = batch_size; p.heads = num_heads; p.kvHeads = k->kvHeads; p.headDim = k->headDim;
     p.blockSize = k->blockSize; p.maxNumBlocks = k->res.stride; p.window = c->defaultWindow; p.dtype = k->dtype;   // :1028
-    p.maxContext = std::max(maxLen, 1);
     p.poolBlocks = k->maxBlocks;
-    p.hostLens = hostLens;
-    p.planCache = c->planCache;
+    if (!ensureMergeCounters(c, static_cast<int64_t>(batch_size) * k->kvHeads))
+        return failed(c->fail(PAM_ERR_RESOURCE_EXHAUSTED, "GPU resource exhausted: counting words of the decode kernel"));
     p.counters = c->mergeCounters;
     p.countersCap = c->mergeCountersCap;
     c->arena.reset(c->stream);
     size_t tempBytes = 0;
     int32_t rc = withRetry(c, "decodeFlat", [&]() -> cudaError_t {
-        tempBytes = pam::decodeWorkspaceBytes(p, c->smCount, c->stream);
+        tempBytes = pam::decodeWorkspaceBytes(p, c->smCount);
         if (tempBytes) {
             p.workspace = static_cast<float*>(c->arena.take(tempBytes));
             p.workspaceBytes = tempBytes;
@@ -1746,7 +1759,7 @@ int32_t pamc_fused_prefill(void* ctx, const PamFusedPrefillRequest* request, voi
 }
 
 int32_t pamc_decode_layers(void* ctx, const PamDecodeRequest* requests, int32_t num_layers) {
-    return runLayers(ctx, requests, num_layers, [](Context* c, const PamDecodeRequest& rq, int) { return decodeImpl(c, rq, 0); });
+    return runLayers(ctx, requests, num_layers, [](Context* c, const PamDecodeRequest& rq, int) { return decodeImpl(c, rq); });
 }
 
 int32_t pamc_prefill_layers(void* ctx, const PamPrefillRequest* requests, int32_t num_layers) {

@@ -667,15 +667,6 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             __syncwarp();
             if (j == 0) { if (x) ++items1; else ++items0; }
         };
-        Cursor nx = c;                       // first tile of the item after c's
-        bool nxKnown = false;
-        auto lookAhead = [&]() {
-            nx = c;
-            nx.g = c.g + (c.it.nT - 1 - c.j);          // last tile of this item
-            nx.j = c.it.nT - 1;
-            nx.nextTile(p, total, numPairs);           // first tile of the next item (or the end)
-            nxKnown = true;
-        };
         while (c.valid && ok) {
             // S products not issued ahead (start of the stream, or a group whose next item was
             // too far away when it finished the one before)
@@ -689,11 +680,15 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             }
             if (!ok) break;
             const int st = c.g % kVStages;
-            // the next item of the stream, for the groups that finish this one here (looked up
-            // at the start of the item, while the groups worked on its first key tile)
+            // the next item of the stream, for the groups that finish this one here
+            Cursor nx = c;
             const bool lastOfItem = c.j == c.it.nT - 1;
             const bool endsHere0 = c.j == c.it.nTg[0] - 1, endsHere1 = c.j == c.it.nTg[1] - 1;
-            if ((endsHere0 || endsHere1) && !nxKnown) lookAhead();
+            if (endsHere0 || endsHere1) {
+                nx.g = c.g + (c.it.nT - 1 - c.j);      // last tile of this item
+                nx.j = c.it.nT - 1;
+                nx.nextTile(p, total, numPairs);       // first tile of the next item (or the end)
+            }
 #pragma unroll
             for (int x = 0; x < 2; ++x) {
                 if (!(c.j < c.it.nTg[x]) || !ok) continue;
@@ -742,15 +737,8 @@ prefillTcKernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                     ahead = true;
                 }
             }
-            if (lastOfItem && nxKnown) {
-                c = nx;                                 // no index arithmetic between two items
-                nxKnown = false;
-            } else {
-                c.nextTile(p, total, numPairs);
-            }
-            // the look-up of the item after this one costs some hundred cycles of integer work:
-            // done here, where the issuer next waits for the groups' weights anyway
-            if (c.valid && c.j == 0) lookAhead();
+            (void)lastOfItem;
+            c.nextTile(p, total, numPairs);
         }
     } else if (warp == kIdleWarp) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");          // (the fourth warp of the service warpgroup)

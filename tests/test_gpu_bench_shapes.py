@@ -110,7 +110,7 @@ def test_headline_decode_shape_sampled_parity():
                                           tables.shape[1], layer)
     engine.decode(req)
     assert_close(out_dev.cpu().numpy()[sample].astype(np.float32), ref, DT.float16)
-    # ... and with the lengths on the device (the launch is then planned from the table width)
+    # ... and with the lengths on the device
     l_dev = torch.from_numpy(lens_u.view(np.int32)).to(dev)
     out_dev2 = torch.empty_like(q)
     engine.decode(pam.PagedAttentionDecodeRequest(q, cache.kPoolBuffer, cache.vPoolBuffer, t_dev, l_dev, out_dev2, B,

@@ -61,9 +61,10 @@ def test_noalloc_decode_matches_decode_on_two_calls_in_a_row():
 def test_noalloc_decode_rejects_what_it_cannot_hold():
     engine = pam.PagedAttentionEngine()
     engine.enableGracefulDegradation = False
-    # 64 sequences x 32 heads x 8 splits x 130 floats > 8 MiB; rejected before any launch,
-    # so a small pool that only satisfies the argument checks is enough
-    B, H, KVH, D, bs, max_nb = 64, 32, 8, 128, 16, 512
+    # The built-in arrays hold one arrival word per (sequence, kv head) pair, 65 536 of them:
+    # 70 000 single-head sequences are refused before any launch, so small buffers that only
+    # satisfy the argument checks are enough.
+    B, H, KVH, D, bs, max_nb = 70000, 1, 1, 128, 16, 1
     pool = engine.makeBuffer(max_nb * bs * KVH * D * 2)
     q = engine.makeBuffer(B * H * D * 2)
     out = engine.makeBuffer(B * H * D * 2)
@@ -73,7 +74,9 @@ def test_noalloc_decode_rejects_what_it_cannot_hold():
     with pytest.raises(pam.PagedAttentionError) as e:
         engine.decodeNoAlloc(pam.PagedAttentionDecodeRequest(q, pool, pool, tables, lens, out, B, max_nb, layer))
     assert e.value.case == "resourceExhausted"
-    assert str(8 << 20) in str(e.value) and "pamc_decode" in str(e.value)
+    assert str(8 << 20) in str(e.value) and "65536" in str(e.value) and "pamc_decode" in str(e.value)
+    # the same batch is fine for pamc_decode, which takes what it needs from the context
+    engine.decode(pam.PagedAttentionDecodeRequest(q, pool, pool, tables, lens, out, B, max_nb, layer))
     # host buffers would need staging memory: refused as well
     with pytest.raises(pam.PagedAttentionError) as e:
         engine.decodeNoAlloc(pam.PagedAttentionDecodeRequest(np.zeros((1, H, D), np.float16), pool, pool, tables, lens,
@@ -85,7 +88,7 @@ def test_noalloc_decode_rejects_what_it_cannot_hold():
 def test_noalloc_decode_allocates_nothing_and_can_be_recorded():
     """Free device memory and the context's arena stay as they were across the call, and a
     call made while the stream is being captured only records its launches (no wait, no
-    retry loop): the replayed graph gives the bits of pamc_decode."""
+    retry loop): the replayed graph gives the bits of the eager call, every time."""
     torch = pytest.importorskip("torch")
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
@@ -115,6 +118,10 @@ def test_noalloc_decode_allocates_nothing_and_can_be_recorded():
     assert engine.kernelLaunches > launches
     engine.setStream(None)
     graph.replay()
+    torch.cuda.synchronize(dev)
+    assert np.array_equal(_download(out3, case).view(np.uint16), eager.view(np.uint16))
+    for _ in range(5):
+        graph.replay()
     torch.cuda.synchronize(dev)
     assert np.array_equal(_download(out3, case).view(np.uint16), eager.view(np.uint16))
     engine.close()
