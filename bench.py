@@ -81,15 +81,55 @@ def host_cores() -> int:
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+    """SM clock and throttle reasons of one GPU while the timed region runs: NVML read every
+    20 ms by a thread of this process (the figures `nvidia-smi --query-gpu=clocks.sm,
+    clocks.max.sm,clocks_event_reasons.*` prints), with `nvidia-smi -lms 100` as the fallback
+    when the NVML binding is missing.  Nothing is set, only read."""
 
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASONS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
 
     def __init__(self, index: int):
         self.index, self.samples, self.proc = index, [], None
+        self.sm, self.mx, self.reasons = [], [], set()
+        self.stopping, self.thread = threading.Event(), None
+
+    def _nvml_handle(self):
+        import pynvml
+        pynvml.nvmlInit()
+        try:
+            import torch
+            pr = torch.cuda.get_device_properties(self.index)
+            bus = f"{pr.pci_domain_id:08x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+            return pynvml, pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode())
+        except Exception:
+            return pynvml, pynvml.nvmlDeviceGetHandleByIndex(self.index)
+
+    def _poll(self, nv, h):
+        mx = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+        while True:
+            try:
+                self.sm.append(float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)))
+                self.mx.append(float(mx))
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(h) if hasattr(nv, "nvmlDeviceGetCurrentClocksEventReasons") \
+                    else nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                for name, bit in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            if self.stopping.wait(0.02):
+                return
 
     def start(self):
+        try:
+            nv, h = self._nvml_handle()
+            self.thread = threading.Thread(target=self._poll, args=(nv, h), daemon=True)
+            self.thread.start()
+            return self
+        except Exception:
+            self.thread = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
                                           "--format=csv,noheader,nounits", "-lms", "100"],
@@ -104,6 +144,11 @@ class ClockSampler:
             self.samples.append(line.strip())
 
     def stop(self):
+        if self.thread:
+            self.stopping.set()
+            self.thread.join(timeout=2)
+            return {"sm_mhz": statistics.median(self.sm) if self.sm else None, "sm_max_mhz": max(self.mx) if self.mx else None,
+                    "reasons": sorted(self.reasons), "samples": len(self.sm), "source": "nvml"}
         if self.proc:
             self.proc.terminate()
             try:
@@ -124,7 +169,7 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(n)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "source": "nvidia-smi"}
 
 
 # ===================================================================== CPU arm
@@ -768,7 +813,8 @@ def run_prefill_c3(rt, with_cpu):
         line["e2e"] = {"value": flops / (e2e[0] * 1e-3) / 1e12 if e2e[0] else None, "unit": "TFLOP/s", "ms_per_step": e2e[0],
                        "ms_per_step_min": e2e[1], "ms_per_step_max": e2e[2],
                        "h2d_bytes_per_step": io_bytes, "d2h_bytes_per_step": io_bytes,
-                       "call": "pamc_prefill_batch per chunk with page-locked host q/out (block tables resident)"}
+                       "call": "pamc_prefill_batch per chunk with page-locked host q/out (copied to and from the device inside the call; "
+                               "block tables resident): 268 MB each way per step, bound by the host link"}
         if with_cpu:
             line["cpu_baseline"] = cpu_prefill_c3()
     cache.close()

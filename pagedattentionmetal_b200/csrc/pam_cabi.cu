@@ -719,6 +719,10 @@ int32_t prefillImpl(Context* c, const PamLayerSpec& l, const PamBuffer& q, const
     Stager st(c);
     int32_t rc = withRetry(c, "prefill", [&]() -> cudaError_t {
         pam::PrefillParams p{};
+        // (Host queries and outputs go through copies in the arena, page-locked ones too.  Letting
+        // the tensor-core kernel read and write page-locked host buffers in place through their
+        // device-side addresses worked on single calls and then stalled a call for minutes after
+        // some hundred calls in a row; it is not used.)
         p.q = st.in(q.ptr, ioBytes);
         p.kPool = kPool.ptr; p.vPool = vPool.ptr;
         p.tables = static_cast<const int32_t*>(st.in(tables.ptr, static_cast<size_t>(n) * maxNumBlocks * sizeof(int32_t)));

@@ -90,6 +90,26 @@ def test_prefill_shapes(engine, dtype, seq_len, heads, kv_heads, head_dim, block
     assert_close(out, case.oracle(), dtype)
 
 
+@pytest.mark.parametrize("dtype", [DT.float16, DT.float8])
+def test_prefill_host_memory_kinds(engine, dtype):
+    """Queries and outputs in device memory, in pageable host arrays and in page-locked host
+    memory give the same values (host buffers of either kind are staged)."""
+    torch = pytest.importorskip("torch")
+    case = PrefillCase(61, 700, 8, 2, 128, 16, dtype)
+    on_device = case.run(engine)                        # (float32 values of the output)
+    assert_close(on_device, case.oracle(), dtype)
+    assert np.array_equal(case.run(engine, host_io=True), on_device)
+    kp, vp = engine.makeBufferFrom(case.k_pool), engine.makeBufferFrom(case.v_pool)
+    ks = engine.makeBufferFrom(case.k_scale) if case.k_scale is not None else None
+    vs = engine.makeBufferFrom(case.v_scale) if case.v_scale is not None else None
+    q_pin = torch.from_numpy(np.ascontiguousarray(case.q).view(np.uint16).copy()).pin_memory()
+    out_pin = torch.zeros_like(q_pin).pin_memory()
+    engine.prefill(pam.PagedAttentionPrefillRequest(q_pin.data_ptr(), kp, vp, engine.makeBufferFrom(case.table), out_pin.data_ptr(),
+                                                    case.S, case.layer(), True, ks, vs, 0, 0))
+    got = from_io(out_pin.numpy().view(io_numpy_dtype(dtype)).reshape(case.q.shape), dtype)
+    assert np.array_equal(got, on_device)
+
+
 @pytest.mark.parametrize("dtype", [DT.float16, DT.bfloat16])
 def test_chunked_prefill_equals_full(engine, dtype):
     """Rows of a chunk equal the same rows of a full prefill
