@@ -59,10 +59,19 @@ C1_TOKENS, C1_BLOCKS, C1_COPIES = 4096, 4096, 512
 C4_SEQS, C4_LO, C4_HI, C4_WINDOW, C4_HEADS, C4_CHUNK = 64, 32768, 131072, 4096, 64, 2048
 
 FALLBACK = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
-# DRAM bytes (read + written) of one decode launch relative to its algorithmic bytes, from an
-# ncu capture (dram__bytes_read.sum + dram__bytes_write.sum) of the split kernels on a
-# 64-sequence cut of the same workload; the traffic grows in proportion to the context tokens.
-DECODE_TRAFFIC_FACTOR = {"f16": 1.010, "fp8": 1.02}
+# DRAM traffic of one decode launch from its algorithmic bytes, after ncu captures
+# (dram__bytes_read.sum, dram__bytes_write.sum) of decodeStreamKernel on cuts of the two
+# workloads (64 sequences of decode_c2, 16 of decode_c4): the bytes read grow in proportion to
+# the context tokens (factor), the bytes written are the outputs plus the records of the
+# pieces, whose number is that of the grid's warps whatever the batch (constant).
+DECODE_TRAFFIC = {"f16": (1.0032, 5.8e6), "fp8": (1.0043, 4.2e6)}
+
+
+def decode_traffic(kind, algorithmic_bytes):
+    factor, written = DECODE_TRAFFIC[kind]
+    return algorithmic_bytes * factor + written
+
+
 WORKLOADS = ("decode_c2", "prefill_c3", "decode_c4", "step_c4", "append_c1")
 
 
@@ -661,8 +670,8 @@ def run_decode_c2(rt, with_cpu):
                             "peak_source": f"{rt.peak_kind} copy bandwidth", "per": "GPU",
                             "kernel": "decodeStreamKernel (float16 tiles)",
                             "algorithmic_bytes_per_launch": bytes_gpu,
-                            "traffic": bytes_gpu * DECODE_TRAFFIC_FACTOR["f16"],
-                            "traffic_source": "ncu on a 64-sequence cut, scaled by context tokens"}
+                            "traffic": decode_traffic("f16", bytes_gpu),
+                            "traffic_source": "ncu on a 64-sequence cut: bytes read scaled by context tokens, bytes written constant"}
         line["e2e"] = {"value": B / (e2e[0] * 1e-3) if e2e[0] else None, "unit": "tokens/s", "ms_per_step": e2e[0],
                        "ms_per_step_min": e2e[1], "ms_per_step_max": e2e[2],
                        "h2d_bytes_per_step": io_bytes + lens_h.nbytes, "d2h_bytes_per_step": io_bytes,
@@ -1017,8 +1026,8 @@ def run_c4(rt, with_cpu, want=("decode_c4", "step_c4")):
         return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "peak_source": f"{rt.peak_kind} copy bandwidth", "per": "GPU",
                 "kernel": "decodeStreamKernel (FP8 tiles)",
-                "algorithmic_bytes_per_launch": bytes_decode, "traffic": bytes_decode * DECODE_TRAFFIC_FACTOR["fp8"],
-                "traffic_source": "ncu on a 16-sequence cut, scaled by visible tokens"}
+                "algorithmic_bytes_per_launch": bytes_decode, "traffic": decode_traffic("fp8", bytes_decode),
+                "traffic_source": "ncu on a 16-sequence cut: bytes read scaled by visible tokens, bytes written constant"}
 
     l2_note = {"seed": 1004, "l2": "window bytes per step (0.54 GB over all GPUs) exceed L2 up to 4 GPUs; at 8 GPUs a GPU's 67 MB "
                                    "share fits L2 and L2 is flushed between timed steps"}
