@@ -26,7 +26,9 @@
 // Arithmetic per tile: mma.sync m16n8k16 with the query heads of the GQA group as rows (every
 // K/V byte is read once for the whole group), online softmax in registers in the log2
 // domain; FP8 e4m3 codes become float16 in registers and the (block, kv_head) scales are
-// applied outside the products.  The kernel is bound by HBM bandwidth.
+// applied outside the products.  FP8 pools with at most 8 query heads per KV head take the
+// products transposed (tokens and dims as rows, heads as the 8 columns), which wastes no row
+// of a product on padding.  The kernel is bound by HBM bandwidth.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -362,7 +364,7 @@ struct HalfTiles {
         }
     }
     static constexpr int kPairStride = 1;     // the two values handed to f are columns d and d + 1
-    static __device__ __forceinline__ float rowSum(const Acc& c, bool upper) { return upper ? c.l1 : c.l0; }
+    static __device__ __forceinline__ float rowSum(const Acc& c, int g) { return g >= 8 ? c.l1 : c.l0; }
 };
 
 // FP8 e4m3 pools with float16 (block, kv_head) scales, head_dim 128, float16 queries and
@@ -577,7 +579,198 @@ struct Fp8Tiles {
         }
     }
     static constexpr int kPairStride = 16;    // the two values handed to f are columns d and d + 16
-    static __device__ __forceinline__ float rowSum(const Acc& c, bool upper) { return upper ? c.l1 : c.l0; }
+    static __device__ __forceinline__ float rowSum(const Acc& c, int g) { return g >= 8 ? c.l1 : c.l0; }
+};
+
+// The same pools with at most 8 query heads per KV head: the products are taken transposed,
+// S^T = K Q^T (16 tokens x 8 heads) and O^T = V^T P^T (dims x 8 heads), so that the 8-wide side
+// of mma.sync.m16n8k16 carries the heads and no row of a product is padding: half the
+// products, half the accumulator registers.  Thread (r, j) of a warp (r = lane / 4,
+// j = lane % 4) then holds the scores of tokens r and r + 8 for heads 2j and 2j + 1; the
+// weights go back to the token-major operand layout with two movmatrix transposes.
+__device__ __forceinline__ uint32_t movmatrixTrans(uint32_t v) {
+    uint32_t r;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(v));
+    return r;
+}
+
+struct Fp8TilesT {
+    using Base = Fp8Tiles<false>;
+    using Out = __half;
+    static constexpr int HD = 128, NS = Base::NS;
+    static constexpr int ROWB = Base::ROWB, TILEB = Base::TILEB, CHUNKS = Base::CHUNKS, STAGEB = Base::STAGEB;
+    static constexpr int KSTEPS = HD / 16, MT = HD / 16;
+    struct Query { uint32_t b[KSTEPS][2]; };
+    struct Acc {
+        float o[MT][4];          // m-tile t: (dim 16r + t, heads 2j, 2j+1), (dim 16r + 8 + t, heads 2j, 2j+1)
+        float m0, m1, l0, l1;    // running maximum and sum of heads 2j and 2j + 1 (the sums over this thread's tokens)
+        float vRef, invVRef;     // V scale of the first tile
+        bool first;
+    };
+
+    static __device__ __forceinline__ void issue(uint32_t stage, unsigned char* stagePtr, const StreamArgs& a, int64_t blk,
+                                                 int kvh, int within, int lane) {
+        Base::issue(stage, stagePtr, a, blk, kvh, within, lane);
+    }
+
+    // Query rows as B fragments with the permuted K order: step ks of thread (r, j) covers
+    // dims 32j + 4ks + {0,1} (first half) and + {2,3} (second half) of head r.
+    static __device__ __forceinline__ void loadQuery(Query& q, const StreamArgs& a, int64_t row0, int G, int lane) {
+        const int r = lane >> 2, j = lane & 3;
+        const __half* qb = static_cast<const __half*>(a.q) + row0 * HD;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+            uint2 w = make_uint2(0u, 0u);
+            if (r < G) w = *reinterpret_cast<const uint2*>(qb + r * HD + 32 * j + 4 * ks);
+            q.b[ks][0] = w.x;
+            q.b[ks][1] = w.y;
+        }
+    }
+
+    static __device__ __forceinline__ void reset(Acc& c, int) {
+#pragma unroll
+        for (int t = 0; t < MT; ++t) c.o[t][0] = c.o[t][1] = c.o[t][2] = c.o[t][3] = 0.f;
+        c.m0 = c.m1 = -INFINITY;
+        c.l0 = c.l1 = 0.f;
+        c.vRef = 1.f; c.invVRef = 1.f;
+        c.first = true;
+    }
+
+    static __device__ __forceinline__ void tile(Acc& c, const Query& q, unsigned char* stagePtr, uint32_t, int tokBase,
+                                                int windowStart, int len, float scaleLog2, int lane) {
+        const int r = lane >> 2, j = lane & 3;
+        const __half* sc = reinterpret_cast<const __half*>(stagePtr + 2 * TILEB);
+        const int odd = stagePtr[2 * TILEB + 8];
+        const float ks_ = __half2float(sc[odd]), vs_ = __half2float(sc[2 + odd]);
+        if (c.first) { c.vRef = vs_ > 0.f ? vs_ : 1.f; c.invVRef = 1.f / c.vRef; c.first = false; }
+        const bool partial = tokBase < windowStart || tokBase + kTileTokens > len;
+        if (partial) {
+            // rows outside [window_start, L): zero codes, so that a zero weight times that row is zero
+            unsigned char* vt = stagePtr + TILEB;
+            for (int idx = lane; idx < CHUNKS; idx += 32) {
+                const int tok = tokBase + (idx >> 3);
+                if (tok < windowStart || tok >= len) *reinterpret_cast<uint4*>(vt + idx * 16) = make_uint4(0u, 0u, 0u, 0u);
+            }
+            __syncwarp();
+        }
+        // S^T = K Q^T on the codes (two accumulators, so that the products do not form one
+        // chain); the group scale and 1/sqrt(d) follow.
+        float s[4] = {0.f, 0.f, 0.f, 0.f}, s2[4] = {0.f, 0.f, 0.f, 0.f};
+        {
+            const int rowA = r, rowB = r + 8;
+            const uint4 a0 = *reinterpret_cast<const uint4*>(stagePtr + rowA * ROWB + (((2 * j) ^ (rowA & 7)) << 4));
+            const uint4 a1 = *reinterpret_cast<const uint4*>(stagePtr + rowA * ROWB + (((2 * j + 1) ^ (rowA & 7)) << 4));
+            const uint4 b0 = *reinterpret_cast<const uint4*>(stagePtr + rowB * ROWB + (((2 * j) ^ (rowB & 7)) << 4));
+            const uint4 b1 = *reinterpret_cast<const uint4*>(stagePtr + rowB * ROWB + (((2 * j + 1) ^ (rowB & 7)) << 4));
+            const uint32_t wa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+            const uint32_t wb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ++ks) {
+                const uint32_t frag[4] = {e4m3x2ToHalf2(wa[ks]), e4m3x2ToHalf2(wb[ks]), e4m3x2HiToHalf2(wa[ks]), e4m3x2HiToHalf2(wb[ks])};
+                if (ks & 1) mma16816<__half>(s2, frag, q.b[ks][0], q.b[ks][1]);
+                else mma16816<__half>(s, frag, q.b[ks][0], q.b[ks][1]);
+            }
+        }
+        const float sScale = ks_ * scaleLog2;
+        const bool okA = !partial || (tokBase + r >= windowStart && tokBase + r < len);
+        const bool okB = !partial || (tokBase + r + 8 >= windowStart && tokBase + r + 8 < len);
+        s[0] = okA ? (s[0] + s2[0]) * sScale : -INFINITY;      // token r, head 2j
+        s[1] = okA ? (s[1] + s2[1]) * sScale : -INFINITY;      // token r, head 2j + 1
+        s[2] = okB ? (s[2] + s2[2]) * sScale : -INFINITY;      // token r + 8, head 2j
+        s[3] = okB ? (s[3] + s2[3]) * sScale : -INFINITY;      // token r + 8, head 2j + 1
+        float tmax0 = fmaxf(s[0], s[2]), tmax1 = fmaxf(s[1], s[3]);
+#pragma unroll
+        for (int o = 4; o <= 16; o <<= 1) {
+            tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xFFFFFFFFu, tmax0, o));
+            tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xFFFFFFFFu, tmax1, o));
+        }
+        bool raise = false;                              // m = -inf: the first tile always raises
+        float c0 = 1.f, c1 = 1.f;
+        if (tmax0 > c.m0 + kLazyMax) { c0 = ex2Fast(c.m0 - tmax0); c.m0 = tmax0; raise = true; }
+        if (tmax1 > c.m1 + kLazyMax) { c1 = ex2Fast(c.m1 - tmax1); c.m1 = tmax1; raise = true; }
+        if (__any_sync(0xFFFFFFFFu, raise)) {
+            c.l0 *= c0;
+            c.l1 *= c1;
+#pragma unroll
+            for (int t = 0; t < MT; ++t) {
+                c.o[t][0] *= c0;
+                c.o[t][1] *= c1;
+                c.o[t][2] *= c0;
+                c.o[t][3] *= c1;
+            }
+        }
+        // weights; those that enter the product carry V's group scale relative to vRef.  As the
+        // B operand they must be token-major per head: two 8 x 8 transposes.
+        const float vw = vs_ * c.invVRef;
+        uint32_t pb[2];
+        {
+            const float p0 = ex2Fast(s[0] - c.m0), p1 = ex2Fast(s[1] - c.m1);
+            const float p2 = ex2Fast(s[2] - c.m0), p3 = ex2Fast(s[3] - c.m1);
+            c.l0 += p0 + p2;
+            c.l1 += p1 + p3;
+            pb[0] = movmatrixTrans(pack2<__half>(p0 * vw, p1 * vw));      // (head r; tokens 2j, 2j + 1)
+            pb[1] = movmatrixTrans(pack2<__half>(p2 * vw, p3 * vw));      // (head r; tokens 2j + 8, 2j + 9)
+        }
+        // O^T += V^T P^T.  Thread (r, j) reads chunk r (dims 16r .. 16r+15) of the token rows
+        // 2j, 2j+1, 2j+8, 2j+9; m-tile t takes bytes t and 8 + t of each: its rows r and r + 8
+        // are dims 16r + t and 16r + 8 + t.
+        {
+            const unsigned char* vt = stagePtr + TILEB;
+            uint4 x[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int row = 2 * j + (i & 1) + 8 * (i >> 1);
+                x[i] = *reinterpret_cast<const uint4*>(vt + row * ROWB + ((r ^ (row & 7)) << 4));
+            }
+            const uint32_t* x0 = reinterpret_cast<const uint32_t*>(&x[0]);
+            const uint32_t* x1 = reinterpret_cast<const uint32_t*>(&x[1]);
+            const uint32_t* x2 = reinterpret_cast<const uint32_t*>(&x[2]);
+            const uint32_t* x3 = reinterpret_cast<const uint32_t*>(&x[3]);
+#pragma unroll
+            for (int wi = 0; wi < 2; ++wi) {
+                // words wi (dims 16r + 4wi ..) and wi + 2 (dims 16r + 8 + 4wi ..) of the four token rows
+                const uint32_t lo01 = __byte_perm(x0[wi], x1[wi], 0x5140), lo23 = __byte_perm(x0[wi], x1[wi], 0x7362);
+                const uint32_t hi01 = __byte_perm(x0[wi + 2], x1[wi + 2], 0x5140), hi23 = __byte_perm(x0[wi + 2], x1[wi + 2], 0x7362);
+                const uint32_t lp01 = __byte_perm(x2[wi], x3[wi], 0x5140), lp23 = __byte_perm(x2[wi], x3[wi], 0x7362);
+                const uint32_t hp01 = __byte_perm(x2[wi + 2], x3[wi + 2], 0x5140), hp23 = __byte_perm(x2[wi + 2], x3[wi + 2], 0x7362);
+                {
+                    const uint32_t f0[4] = {e4m3x2ToHalf2(lo01), e4m3x2ToHalf2(hi01), e4m3x2ToHalf2(lp01), e4m3x2ToHalf2(hp01)};
+                    mma16816<__half>(c.o[4 * wi + 0], f0, pb[0], pb[1]);
+                    const uint32_t f1[4] = {e4m3x2HiToHalf2(lo01), e4m3x2HiToHalf2(hi01), e4m3x2HiToHalf2(lp01), e4m3x2HiToHalf2(hp01)};
+                    mma16816<__half>(c.o[4 * wi + 1], f1, pb[0], pb[1]);
+                    const uint32_t f2[4] = {e4m3x2ToHalf2(lo23), e4m3x2ToHalf2(hi23), e4m3x2ToHalf2(lp23), e4m3x2ToHalf2(hp23)};
+                    mma16816<__half>(c.o[4 * wi + 2], f2, pb[0], pb[1]);
+                    const uint32_t f3[4] = {e4m3x2HiToHalf2(lo23), e4m3x2HiToHalf2(hi23), e4m3x2HiToHalf2(lp23), e4m3x2HiToHalf2(hp23)};
+                    mma16816<__half>(c.o[4 * wi + 3], f3, pb[0], pb[1]);
+                }
+            }
+        }
+    }
+
+    static __device__ __forceinline__ void finish(Acc& c) {
+#pragma unroll
+        for (int o = 4; o <= 16; o <<= 1) {
+            c.l0 += __shfl_xor_sync(0xFFFFFFFFu, c.l0, o);
+            c.l1 += __shfl_xor_sync(0xFFFFFFFFu, c.l1, o);
+        }
+    }
+
+    template <class F, class Gf>
+    static __device__ __forceinline__ void each(const Acc& c, int G, int lane, F f, Gf g) {
+        const int r = lane >> 2, j = lane & 3;
+        if (2 * j < G) {
+#pragma unroll
+            for (int t = 0; t < MT; ++t) f(2 * j, 16 * r + t, c.o[t][0] * c.vRef, c.o[t][2] * c.vRef);
+            if (r == 0) g(2 * j, c.m0, c.l0);
+        }
+        if (2 * j + 1 < G) {
+#pragma unroll
+            for (int t = 0; t < MT; ++t) f(2 * j + 1, 16 * r + t, c.o[t][1] * c.vRef, c.o[t][3] * c.vRef);
+            if (r == 0) g(2 * j + 1, c.m1, c.l1);
+        }
+    }
+    static constexpr int kPairStride = 8;     // the two values handed to f are columns d and d + 8
+    static __device__ __forceinline__ float rowSum(const Acc& c, int g) { return (g & 1) ? c.l1 : c.l0; }
 };
 
 // ------------------------------------------------------------ the stream
@@ -827,7 +1020,7 @@ decodeStreamKernel(const StreamArgs a) {
                 Out* dst = static_cast<Out*>(a.out) + outRow * HD;
                 P::each(acc, G, lane,
                         [&](int g, int d, float v0, float v1) {
-                            const float inv = 1.f / P::rowSum(acc, g >= 8);
+                            const float inv = 1.f / P::rowSum(acc, g);
                             if (P::kPairStride == 1) {
                                 *reinterpret_cast<uint32_t*>(dst + g * HD + d) = pack2<Out>(v0 * inv, v1 * inv);
                             } else {
@@ -946,7 +1139,7 @@ cudaError_t launchStreamT(const DecodeParams& p, int smCount, cudaStream_t strea
 template <class F>
 auto dispatch(const DecodeParams& p, F f) {
     const bool upper = p.heads / p.kvHeads > 8;
-    if (p.dtype == kFP8) return upper ? f(Fp8Tiles<true>{}) : f(Fp8Tiles<false>{});
+    if (p.dtype == kFP8) return upper ? f(Fp8Tiles<true>{}) : f(Fp8TilesT{});
     if (p.dtype == kF16) {
         if (p.headDim == 128) return upper ? f(HalfTiles<__half, 128, true>{}) : f(HalfTiles<__half, 128, false>{});
         return upper ? f(HalfTiles<__half, 64, true>{}) : f(HalfTiles<__half, 64, false>{});
