@@ -64,7 +64,7 @@ FALLBACK = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1
 # workloads (64 sequences of decode_c2, 16 of decode_c4): the bytes read grow in proportion to
 # the context tokens (factor), the bytes written are the outputs plus the records of the
 # pieces, whose number is that of the grid's warps whatever the batch (constant).
-DECODE_TRAFFIC = {"f16": (1.0032, 5.8e6), "fp8": (1.0043, 4.2e6)}
+DECODE_TRAFFIC = {"f16": (1.0032, 5.8e6), "fp8": (1.0042, 4.6e6)}
 
 
 def decode_traffic(kind, algorithmic_bytes):

@@ -92,10 +92,13 @@ def test_general_decode_matches_oracle(engine, dtype, heads, kv_heads, head_dim,
     assert_close(out, case.oracle(), dtype)
 
 
-@pytest.mark.parametrize("heads,kv_heads,block_size", [(8, 2, 16), (16, 2, 16), (32, 2, 32), (2, 2, 16), (64, 8, 16)])
+@pytest.mark.parametrize("heads,kv_heads,block_size", [(8, 2, 16), (16, 2, 16), (32, 2, 32), (2, 2, 16), (64, 8, 16),
+                                                        (6, 2, 16), (10, 2, 16), (14, 2, 16), (24, 2, 16)])
 def test_fp8_fast_decode_matches_oracle(engine, heads, kv_heads, block_size):
-    """FP8 KV through the tensor-core split-K kernel (head_dim 128), against the
-    oracle's half-precision dequantisation chain: max-abs <= 1e-2."""
+    """FP8 KV through the stream kernel (head_dim 128) with 1 to 16 query heads per KV head
+    (up to 8 the products are taken transposed, odd group sizes leave columns empty; above 8
+    both halves of the 16-row tile are used), against the oracle's half-precision
+    dequantisation chain: max-abs <= 1e-2."""
     case = DecodeCase(20, 6, 1, 400, heads, kv_heads, 128, block_size, DT.float8)
     out = case.run(engine)
     assert_close(out, case.oracle(), DT.float8)
