@@ -193,7 +193,7 @@ cudaError_t launchGeneral(const DecodeParams& p, cudaStream_t stream, int* launc
 
 }  // namespace
 
-bool decodeTakesSplitPath(const DecodeParams& p) { return decodeStreamApplies(p); }
+bool decodeTakesStreamPath(const DecodeParams& p) { return decodeStreamApplies(p); }
 
 size_t decodeWorkspaceBytes(const DecodeParams& p, int smCount) {
     return decodeStreamApplies(p) ? decodeStreamWorkspaceBytes(p, smCount) : 0;

@@ -51,7 +51,7 @@ constexpr int kShortContextKeys = 256;
 // once per tile.  Weights reach at most 2^kLazyMax, well inside float16.
 constexpr float kLazyMax = 6.0f;
 
-// Split-K partials and arrival words for launchDecodeStatic(): device memory that belongs
+// Records of shared pairs and counting words for launchDecodeStatic(): device memory that belongs
 // to the library image itself, so that a decode can run without any allocation call.  Every
 // GPU that loads the library holds them until the process exits.
 constexpr size_t kStaticScratchBytes = size_t(8) << 20;

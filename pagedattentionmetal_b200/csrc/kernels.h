@@ -67,7 +67,7 @@ struct DecodeParams {
     int64_t countersCap;
 };
 // True when `p` runs on the stream kernel (type, shape and pointer alignment allow it).
-bool decodeTakesSplitPath(const DecodeParams& p);
+bool decodeTakesStreamPath(const DecodeParams& p);
 // Bytes of workspace the launch of `p` needs (0 for the general kernel).
 size_t decodeWorkspaceBytes(const DecodeParams& p, int smCount);
 cudaError_t launchDecode(const DecodeParams& p, int smCount, cudaStream_t stream, int* launches);

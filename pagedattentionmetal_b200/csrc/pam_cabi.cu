@@ -35,7 +35,7 @@ constexpr size_t kUnknownBytes = static_cast<size_t>(-1);
 size_t alignUp(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // Device memory handed out in bump fashion for the duration of one call:
-// staging copies of host arguments, block tables, split-K partials.
+// staging copies of host arguments, block tables, the decode kernel's records.
 class Arena {
 public:
     ~Arena() { release(); }
@@ -599,7 +599,7 @@ int32_t decodeImpl(Context* c, const PamDecodeRequest& rq) {
 
 // Decode for callers that may not allocate: same checks and kernels as
 // decodeImpl, but nothing is staged (every buffer must already be device
-// memory), the context's arena is left alone, and split-K partials go to the
+// memory), the context's arena is left alone, and the records of shared pairs go to the
 // library's fixed scratch array.
 int32_t decodeNoAllocImpl(Context* c, const PamDecodeRequest& rq) {
     if (validateDecode(c, rq) != 0) return -1;
@@ -1442,7 +1442,7 @@ int32_t pamc_decode_path(const PamDecodeRequest* request) {
     p.batch = rq.batch_size > 0 ? rq.batch_size : 1;
     p.maxNumBlocks = rq.max_num_blocks > 0 ? rq.max_num_blocks : 1;
     if (p.kvHeads <= 0 || p.heads <= 0 || p.blockSize <= 0) return -1;
-    return pam::decodeTakesSplitPath(p) ? 1 : 0;
+    return pam::decodeTakesStreamPath(p) ? 1 : 0;
 }
 
 int32_t pamc_decode_noalloc(void* ctx, const PamDecodeRequest* request) {

@@ -212,7 +212,7 @@ class PagedAttentionEngine:
 
     @staticmethod
     def decodePath(request: PagedAttentionDecodeRequest) -> int:
-        """1: the split-K kernels would run this request, 0: the general kernel
+        """1: the stream kernel would run this request, 0: the general kernel
         (pamc_decode_path; nothing is launched)."""
         r = _cabi.PamDecodeRequest(_buf(request.q), _buf(request.kPool), _buf(request.vPool),
                                    _buf(request.blockTables), _buf(request.seqLengths), _buf(request.output),
@@ -291,7 +291,7 @@ class PagedAttentionEngine:
     def decodeNoAlloc(self, request: PagedAttentionDecodeRequest) -> None:
         """The same decode for callers that must not allocate device memory
         (see pamc_decode_noalloc in include/pam_cuda.h): device buffers only,
-        split-K partials in the library's fixed 8 MiB scratch array."""
+        partial results of shared sequences in the library's fixed 8 MiB array."""
         r = _cabi.PamDecodeRequest(_buf(request.q), _buf(request.kPool), _buf(request.vPool),
                                    _buf(request.blockTables), _buf(request.seqLengths), _buf(request.output),
                                    request.batchSize, request.maxNumBlocks, _layer(request.layer),

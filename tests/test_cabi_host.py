@@ -59,7 +59,7 @@ def test_decode_kernel_choice_follows_shape_type_and_alignment():
     assert path(decode_request(n, n, DT.float16, dim=96)) == 0
     assert path(decode_request(n, n, DT.float16, bs=8)) == 0
     assert path(decode_request(n, n, DT.float16, heads=64, kv_heads=2)) == 0        # 32 query heads per KV head
-    # pointers the split kernels' 16-byte copies and word loads cannot take: the general kernel runs
+    # pointers the stream kernel's 16-byte copies and word loads cannot take: the general kernel runs
     rq = decode_request(n, n, DT.float16)
     rq.k_pool.ptr += 8
     assert path(rq) == 0

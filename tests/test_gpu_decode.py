@@ -176,7 +176,7 @@ def test_reference_cabi_decode_end_to_end(engine, dtype):
 def test_golden_decode_window(engine, golden_dir):
     """Sliding-window decode against the reference's numpy implementation run over the
     window's tokens (tests/golden/make_golden.py, case 5): float32 through the general
-    kernel, and the same data as float16 through the split-K kernels (head_dim 64 copy)."""
+    kernel, and the same data as float16 through the stream kernel (head_dim 64 copy)."""
     g = np.load(os.path.join(golden_dir, "decode_window.npz"))
     for wi, w in enumerate(g["windows"]):
         out = _flat_decode_f32(engine, g["q"], g["k_pool"], g["v_pool"], g["tables"], g["lens"], 2, 16, window=int(w))
@@ -215,7 +215,7 @@ def test_ragged_batch_matches_oracle(engine, dtype, window):
 
 
 def test_misaligned_query_takes_the_general_kernel(engine):
-    """A query pointer the split kernels' word loads cannot take: the general kernel
+    """A query pointer the stream kernel's word loads cannot take: the general kernel
     runs instead and the result is the same."""
     case = DecodeCase(32, 3, 10, 300, 8, 2, 128, 16, DT.float16)
     kp, vp = engine.makeBufferFrom(case.k_pool), engine.makeBufferFrom(case.v_pool)

@@ -2,13 +2,14 @@
 memory (work being recorded for replay, a server that gave all free memory to
 the KV pools, a host that only receives pointers from another allocator).
 
-It must give what pamc_decode gives.  Both run the same split kernels on the
-same ranges; pamc_decode lets the last CTA of a sequence combine the splits,
-the no-allocation variant combines them in a kernel of its own, so the two sum
-in a different order and agree to rounding: the outputs are compared within
-the tolerance of the other decode tests (and with each other far inside it), on
-two calls in a row that share the library's fixed scratch array (the second
-with other data and another shape, so stale partial results of the first would
+It must give what pamc_decode gives.  Both run the same kernel; the no-allocation
+variant keeps the partial results of shared sequences in the library's fixed
+array, which can hold fewer records than the context's arena, so it may launch
+fewer warps: the list of tiles is then cut into other pieces, the two sum in a
+different order and agree to rounding.  The outputs are compared within the
+tolerance of the other decode tests (and with each other far inside it), on
+two calls in a row that share the fixed array (the second with other data and
+another shape, so stale partial results of the first would
 show).  Collected last on purpose.
 """
 import numpy as np
@@ -41,7 +42,7 @@ def test_noalloc_decode_matches_decode_on_two_calls_in_a_row():
     for case in cases:
         req, out = _device_request(engine, case)
         engine.decode(req)
-        assert engine.lastStats.temporaryBytes > 0, "the case must need split-K scratch"
+        assert engine.lastStats.temporaryBytes > 0, "the case must need records for shared sequences"
         expected = _download(out, case)
         req2, out2 = _device_request(engine, case)
         engine.decodeNoAlloc(req2)
