@@ -392,6 +392,8 @@ CONFIG_TEXT = {
                "windowed FP8 decodes of decode_c4",
     "append_c1": "append_c1: 4096 tokens x 8 kv heads x 128 scattered to random distinct slots of a 4096-block pool as "
                  "float16 and as FP8 e4m3 with (block, kv_head) scales, plus a copy of 512 random blocks",
+    "backward": "backward: gradients of one 2048-token sequence (no causal mask), 32 q / 8 kv heads, head_dim 128, float16, "
+                "block 16 (not a term of the headline metric; only with --workload backward)",
 }
 
 
@@ -965,6 +967,86 @@ def run_append_c1(rt, with_cpu):
     return line
 
 
+# ------------------------------------------------------------------ backward
+
+BW_LEN = 2048
+
+
+def run_backward(rt, with_cpu):
+    """PagedAttentionEngine.backward on one 2048-token float16 sequence: a step is one call
+    (row sums, the key-tile kernel, the store of dQ).  Algorithmic flops = five L x L x d
+    products per head (S, dP, dV, dK, dQ).  The guard compares dQ and the pool gradients with
+    automatic differentiation of the same attention in float32 torch."""
+    torch, pam, engine, dev, args = rt.torch, rt.pam, rt.engine, rt.dev, rt.args
+    DT = pam.PagedAttentionDataType
+    kvh, heads, rank = rt.kvh, rt.heads(HEADS), rt.rank
+    L, nb = BW_LEN, BW_LEN // BLOCK
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1005 * 1000 + rank)
+    table_h = np.random.default_rng(1005).permutation(nb + 8)[:nb].astype(np.int32)
+    table = torch.from_numpy(table_h).to(dev)
+    rnd = lambda *shape: torch.randn(shape, generator=gen, device=dev, dtype=torch.float32)
+    k_pool = rnd(nb + 8, kvh, BLOCK, HEAD_DIM).to(torch.float16)
+    v_pool = rnd(nb + 8, kvh, BLOCK, HEAD_DIM).to(torch.float16)
+    q = rnd(L, heads, HEAD_DIM).to(torch.float16)
+    d_out = (0.1 * rnd(L, heads, HEAD_DIM)).to(torch.float16)
+    dq = torch.empty_like(q)
+    dk_pool, dv_pool = torch.zeros_like(k_pool), torch.zeros_like(v_pool)
+    # the forward pass's row statistics and the float32 reference gradients
+    G = heads // kvh
+    idx = torch.from_numpy(table_h.astype(np.int64)).to(dev)
+    kd = k_pool[idx].permute(1, 0, 2, 3).reshape(kvh, L, HEAD_DIM).float().requires_grad_(True)
+    vd = v_pool[idx].permute(1, 0, 2, 3).reshape(kvh, L, HEAD_DIM).float().requires_grad_(True)
+    qf = q.float().permute(1, 0, 2).reshape(kvh, G, L, HEAD_DIM).requires_grad_(True)
+    sc = torch.einsum("kgid,kjd->kgij", qf, kd) / float(np.sqrt(np.float32(HEAD_DIM)))
+    m = sc.max(dim=-1).values
+    l = torch.exp(sc - m[..., None]).sum(dim=-1)
+    out = torch.einsum("kgij,kjd->kgid", torch.softmax(sc, dim=-1), vd)
+    (out * d_out.float().permute(1, 0, 2).reshape(kvh, G, L, HEAD_DIM)).sum().backward()
+    m_dev = m.detach().reshape(heads, L).t().contiguous()
+    l_dev = l.detach().reshape(heads, L).t().contiguous()
+    step = lambda: engine.backward(q, k_pool, v_pool, table, d_out, m_dev, l_dev, dq, dk_pool, dv_pool, L, HEAD_DIM, heads, kvh,
+                                   BLOCK, DT.float16, 0)
+    step()
+    engine.synchronize()
+    ref_dq = qf.grad.reshape(heads, L, HEAD_DIM).permute(1, 0, 2)
+    err_q = float((dq.float() - ref_dq).abs().max())
+    got_dk = dk_pool[idx].permute(1, 0, 2, 3).reshape(kvh, L, HEAD_DIM).float()
+    got_dv = dv_pool[idx].permute(1, 0, 2, 3).reshape(kvh, L, HEAD_DIM).float()
+    err_k, err_v = float((got_dk - kd.grad).abs().max()), float((got_dv - vd.grad).abs().max())
+    scale_k, scale_v = float(kd.grad.abs().max()), float(vd.grad.abs().max())
+    assert err_q <= 2e-3 and err_k <= 2e-3 + scale_k * 2 ** -10 and err_v <= 2e-3 + scale_v * 2 ** -10, \
+        f"backward differs from float32 autograd: dQ {err_q}, dK {err_k}, dV {err_v}"
+    del sc, out, qf, kd, vd
+
+    engine.setAsync(True)
+    sampler = ClockSampler(rt.local).start()
+    for _ in range(max(args.warmup, 3)):
+        step()
+    settled = rt.settle(step, burst=2)
+    launches0 = engine.kernelLaunches
+    ms = rt.timed(step)
+    launches = engine.kernelLaunches - launches0
+    engine.setAsync(False)
+    clocks = sampler.stop()
+    line = None
+    if rank == 0:
+        flops = 5 * 2 * L * L * HEAD_DIM * heads * rt.world           # whole job
+        tflops = flops / (ms[0] * 1e-3) / 1e12
+        line = rt.base_line("backward", "backward TFLOP/s", tflops, "TFLOP/s", ms, "f16 in, f32 arithmetic", settled, launches, clocks,
+                            {"seed": 1005, "l2": "the sequence's K/V and gradients (a few MB per KV head) stay in L2 by design"})
+        peak = rt.peaks["bf16_tflops"]
+        line["roofline"] = {"bound": "tensor", "achieved": tflops / rt.world, "peak": peak, "unit": "TFLOP/s",
+                            "frac": tflops / rt.world / peak, "peak_source": f"{rt.peak_kind} cuBLAS bf16 burst", "per": "GPU",
+                            "kernel": "backwardKeyTileKernel (+ backwardRowSumKernel, backwardStoreKernel)",
+                            "algorithmic_flops_per_step": flops // rt.world, "traffic": None,
+                            "note": "float32 products on the CUDA cores, as the reference's float32 arithmetic; the tensor "
+                                    "peak is given as the scale, not as the bound of this form"}
+        line["e2e"] = {"value": None, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                       "note": "not measured for this workload"}
+    return line
+
+
 # ------------------------------------------- long-context FP8 decode and step (c4)
 
 def run_c4(rt, with_cpu, want=("decode_c4", "step_c4")):
@@ -1156,6 +1238,8 @@ def run_ours(args):
             results[name] = run_prefill_c3(rt, with_cpu)
         elif name == "append_c1":
             results[name] = run_append_c1(rt, with_cpu)
+        elif name == "backward":
+            results[name] = run_backward(rt, with_cpu)
         else:
             want = [n for n in names if n in ("decode_c4", "step_c4")]
             out = run_c4(rt, with_cpu, want)
@@ -1179,7 +1263,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=None,
                     help="number of sequences of the chosen workload (smaller values are for profiler captures)")
-    ap.add_argument("--workload", default=None, choices=list(WORKLOADS),
+    ap.add_argument("--workload", default=None, choices=list(WORKLOADS) + ["backward"],
                     help="one workload alone; default: decode_c2 with the others under `also`")
     ap.add_argument("--shards", type=int, default=None,
                     help="single process only: run KV-head group 0 of this many (the per-GPU share of a larger job)")

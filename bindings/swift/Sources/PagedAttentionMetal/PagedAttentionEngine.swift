@@ -109,6 +109,20 @@ public final class PagedAttentionEngine: @unchecked Sendable {
         try check(ctx, pamc_fused_prefill(ctx, &c, cache?.handle))
     }
 
+    /// PagedAttentionEngine.swift:1341-1395: dQ is written, dKPool and dVPool are added to; m and l are
+    /// the float32 row maximum and row sum of the caller's forward pass, [seqLen][numHeads].
+    public func backward(q: PagedBuffer, kPool: PagedBuffer, vPool: PagedBuffer, blockTable: PagedBuffer, dO: PagedBuffer,
+                         m: PagedBuffer, l: PagedBuffer, dQ: PagedBuffer, dKPool: PagedBuffer, dVPool: PagedBuffer,
+                         seqLen: Int, headDim: Int, numHeads: Int, numKVHeads: Int, blockSize: Int,
+                         dataType: PagedAttentionDataType = .float32, windowSize: Int = 0) throws {
+        let layer = PagedLayerSpec(headDim: headDim, numHeads: numHeads, numKVHeads: numKVHeads, blockSize: blockSize,
+                                   dataType: dataType, windowSize: windowSize)
+        var c = PamBackwardRequest(q: q.c, k_pool: kPool.c, v_pool: vPool.c, block_table: blockTable.c, d_out: dO.c,
+                                   m: m.c, l: l.c, d_q: dQ.c, d_k_pool: dKPool.c, d_v_pool: dVPool.c,
+                                   seq_len: Int32(seqLen), layer: layer.c)
+        try check(ctx, pamc_backward(ctx, &c))
+    }
+
     // MARK: operations, flat form (PagedAttentionEngine.swift:713, 1012, 1167)
 
     public func prefill(q: PagedBuffer, kPool: PagedBuffer, vPool: PagedBuffer, blockTable: PagedBuffer, seqLen: Int,

@@ -424,6 +424,22 @@ typedef struct PamFusedPrefillRequest {
  * scale rows), may be NULL otherwise. */
 int32_t pamc_fused_prefill(void *ctx, const PamFusedPrefillRequest *request, void *cache);
 
+/* The arguments of PagedAttentionEngine.backward (PagedAttentionEngine.swift:1341-1359) as one
+ * struct: gradients of the attention of rows [0, seq_len) over the keys [window_start,
+ * seq_len) of one sequence (the kernels have no causal mask, kernels.metal:1217-1415) with
+ * respect to the queries and to the paged keys and values.  m and l are the float32 row
+ * maximum and row sum of exp(s - m) of the caller's forward pass, [seq_len][heads].  d_q is
+ * written; d_k_pool and d_v_pool (shaped and typed like the pools, device memory) are added
+ * to, as the reference's atomic adds do.  layer.window_size is the call's windowSize
+ * (window_start = max(0, seq_len - window_size) when it is positive); layer.data_type is
+ * float32 or float16 as in the reference, or bfloat16. */
+typedef struct PamBackwardRequest {
+    PamBuffer q, k_pool, v_pool, block_table, d_out, m, l, d_q, d_k_pool, d_v_pool;
+    int32_t seq_len;
+    PamLayerSpec layer;
+} PamBackwardRequest;
+int32_t pamc_backward(void *ctx, const PamBackwardRequest *request);
+
 /* The batched-layer calls (PagedAttentionEngine.swift:1433-1895: prefillLayers,
  * decodeLayers, appendLayers): one request per layer, enqueued back to back on
  * the context's stream and waited for once.  The reference hands every layer

@@ -663,6 +663,82 @@ def paged_prefill(q, k_pool, v_pool, block_table, seq_len: int, num_kv_heads: in
     return out
 
 
+def attention_stats(q, k_pool, block_table, seq_len: int, num_kv_heads: int, block_size: int,
+                    window_start: int = 0):
+    """The row maximum ``m`` and the row sum ``l`` of ``exp(s - m)`` over keys
+    ``[window_start, seq_len)`` (no causal mask), float32 ``[seq_len][heads]``: what the
+    backward kernel is handed beside the gradient (metal:1222-1223; the reference's
+    forward kernels keep them in private buffers, Engine.swift:811-816)."""
+    q = np.asarray(q)
+    H, D = q.shape[1], q.shape[2]
+    G = H // num_kv_heads
+    inv = np.float64(np.float32(1.0) / np.sqrt(np.float32(D)))
+    m = np.empty((seq_len, H), dtype=np.float32)
+    l = np.empty((seq_len, H), dtype=np.float32)
+    for kvh in range(num_kv_heads):
+        k = _gather_kv(k_pool, block_table, kvh, seq_len, block_size)[window_start:].astype(np.float64)
+        for g in range(G):
+            h = kvh * G + g
+            sc = (q[:seq_len, h].astype(np.float64) @ k.T) * inv
+            mx = sc.max(axis=1)
+            m[:, h] = mx
+            l[:, h] = np.exp(sc - m[:, h].astype(np.float64)[:, None]).sum(axis=1)
+    return m, l
+
+
+def paged_backward(q, k_pool, v_pool, block_table, d_out, m, l, seq_len: int, num_kv_heads: int,
+                   block_size: int, window_start: int = 0):
+    """Gradients of paged attention (metal:1217-1315; float16: metal:1317-1415).
+
+    Every row i of every head sees the keys ``[window_start, seq_len)`` (the kernel has no
+    causal mask).  With ``P_ij = exp(q_i . k_j / sqrt(d) - m_i) / l_i`` (metal:1283),
+    ``dP_ij = dO_i . v_j`` (metal:1284), ``rowsum_i = sum_j P_ij dP_ij`` (metal:1264) and
+    ``dS_ij = P_ij (dP_ij - rowsum_i)`` (metal:1285):
+
+        dQ_i  = sum_j dS_ij k_j / sqrt(d)                      (metal:1287, 1300)
+        dK_j += sum over rows and the heads of the KV head of dS_ij q_i / sqrt(d)   (metal:1289-1291)
+        dV_j += sum over rows and heads of P_ij dO_i           (metal:1293-1295)
+
+    Returns ``(dQ [seq_len][heads][dim], dK, dV)`` with dK, dV shaped like the pools
+    ``[blocks][kv_heads][block_size][dim]`` and holding only the contributions (the kernel
+    adds them to what the gradient pools hold), all float64.  The reference accumulates the
+    pool gradients with float (half) atomics in an order that is not defined; this is the
+    exact sum.
+    """
+    q = np.asarray(q)
+    d_out = np.asarray(d_out)
+    H, D = q.shape[1], q.shape[2]
+    G = H // num_kv_heads
+    inv = np.float64(np.float32(1.0) / np.sqrt(np.float32(D)))
+    dq = np.zeros((seq_len, H, D), dtype=np.float64)
+    dk = np.zeros(k_pool.shape, dtype=np.float64)
+    dv = np.zeros(v_pool.shape, dtype=np.float64)
+    nkeys = seq_len - window_start
+    toks = np.arange(window_start, seq_len)
+    blocks = np.asarray(block_table, dtype=np.int64)[toks // block_size]
+    slots = toks % block_size
+    for kvh in range(num_kv_heads):
+        k = _gather_kv(k_pool, block_table, kvh, seq_len, block_size)[window_start:].astype(np.float64)
+        v = _gather_kv(v_pool, block_table, kvh, seq_len, block_size)[window_start:].astype(np.float64)
+        dk_acc = np.zeros((nkeys, D))
+        dv_acc = np.zeros((nkeys, D))
+        for g in range(G):
+            h = kvh * G + g
+            qh = q[:seq_len, h].astype(np.float64)
+            doh = d_out[:seq_len, h].astype(np.float64)
+            sc = (qh @ k.T) * inv
+            p = np.exp(sc - m[:seq_len, h].astype(np.float64)[:, None]) / l[:seq_len, h].astype(np.float64)[:, None]
+            dp = doh @ v.T
+            rowsum = (p * dp).sum(axis=1, keepdims=True)
+            ds = p * (dp - rowsum)
+            dq[:, h] = (ds @ k) * inv
+            dk_acc += (ds.T @ qh) * inv
+            dv_acc += p.T @ doh
+        np.add.at(dk, (blocks, kvh, slots), dk_acc)
+        np.add.at(dv, (blocks, kvh, slots), dv_acc)
+    return dq, dk, dv
+
+
 # --------------------------------------------------------------------------
 # Seeded workload generators (shapes of the five benchmark configurations)
 # --------------------------------------------------------------------------

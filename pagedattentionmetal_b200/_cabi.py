@@ -80,6 +80,12 @@ class PamFusedPrefillRequest(C.Structure):
                 ("layer", PamLayerSpec), ("causal", c_int32), ("k_scale", PamBuffer), ("v_scale", PamBuffer)]
 
 
+class PamBackwardRequest(C.Structure):
+    _fields_ = [("q", PamBuffer), ("k_pool", PamBuffer), ("v_pool", PamBuffer), ("block_table", PamBuffer),
+                ("d_out", PamBuffer), ("m", PamBuffer), ("l", PamBuffer), ("d_q", PamBuffer),
+                ("d_k_pool", PamBuffer), ("d_v_pool", PamBuffer), ("seq_len", c_int32), ("layer", PamLayerSpec)]
+
+
 class PamSchedSequence(C.Structure):
     _fields_ = [("id", c_int64), ("status", c_int32), ("num_generated_tokens", c_int32),
                 ("max_new_tokens", c_int32), ("prompt_length", c_int32), ("arrival_order", c_int32)]
@@ -153,6 +159,7 @@ SIGNATURES = {
     "pamc_prefill_layers": (c_int32, [c_void_p, C.POINTER(PamPrefillRequest), c_int32]),
     "pamc_append_layers": (c_int32, [c_void_p, C.POINTER(PamAppendRequest), c_int32, C.POINTER(c_void_p)]),
     "pamc_fused_prefill": (c_int32, [c_void_p, C.POINTER(PamFusedPrefillRequest), c_void_p]),
+    "pamc_backward": (c_int32, [c_void_p, C.POINTER(PamBackwardRequest)]),
     # scheduler
     "pamc_sched_create": (c_void_p, [c_int32, c_int32]),
     "pamc_sched_destroy": (None, [c_void_p]),

@@ -92,6 +92,28 @@ cudaError_t decodeStaticScratch(float** scratch, int** counters, int64_t* counte
 size_t decodeStaticScratchBytes();
 cudaError_t launchDecodeStatic(const DecodeParams& p, int smCount, cudaStream_t stream, int* launches);
 
+// ---- backward (backward_kernels.cu) ----
+struct BackwardParams {
+    const void* q;            // [seqLen][heads][dim], io type
+    const void* kPool;        // [block][kvHeads][blockSize][dim], io type (float32 / float16 / bfloat16)
+    const void* vPool;
+    const int32_t* table;     // [maxNumBlocks]
+    const void* dO;           // [seqLen][heads][dim]
+    const float* m;           // [seqLen][heads]: row maximum of the forward pass
+    const float* l;           // [seqLen][heads]: row sum of exp(s - m)
+    void* dQ;                 // [seqLen][heads][dim], io type (written)
+    void* dKPool;             // like kPool (added to)
+    void* dVPool;
+    float* dQAcc;             // float32 [seqLen][heads][dim]: dQ itself for float32, else workspace
+    float* rowSum;            // float32 [seqLen][heads] workspace
+    int seqLen, heads, kvHeads, headDim, blockSize, windowStart, dtype;
+    int poolBlocks;           // blocks in the pools; table entries are clamped into [0, poolBlocks)
+    int maxNumBlocks;         // entries of the table
+};
+// Bytes of workspace (rowSum first, 256-byte aligned, then dQAcc for the 16-bit types).
+size_t backwardWorkspaceBytes(const BackwardParams& p);
+cudaError_t launchBackward(const BackwardParams& p, cudaStream_t stream, int* launches);
+
 // ---- prefill (prefill_kernels.cu) ----
 constexpr int kPrefillInlineSeqs = 32;
 struct PrefillParams {

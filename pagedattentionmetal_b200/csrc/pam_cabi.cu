@@ -1762,6 +1762,85 @@ int32_t pamc_fused_prefill(void* ctx, const PamFusedPrefillRequest* request, voi
     return 0;
 }
 
+int32_t pamc_backward(void* ctx, const PamBackwardRequest* request) {
+    // PagedAttentionEngine.backward (PagedAttentionEngine.swift:1341-1395); kernels.metal:1217-1415
+    if (!ctx || !request) return -1;
+    Context* c = asCtx(ctx);
+    std::lock_guard<std::mutex> g(c->mu);
+    DeviceGuard dg(c->device);
+    const PamBackwardRequest& rq = *request;
+    const PamLayerSpec& l = rq.layer;
+    if (!validateLayer(c, l)) return -1;
+    if (rq.seq_len <= 0) return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("seqLen must be positive."));
+    // the reference has a float32 and a float16 pipeline (:1366); bfloat16 is this library's addition
+    if (l.data_type == PAM_DTYPE_FP8)
+        return c->fail(PAM_ERR_UNSUPPORTED, "Unsupported paged attention path: backward over an FP8 cache.");
+    if (l.head_dim > 256) return c->fail(PAM_ERR_UNSUPPORTED, "Unsupported paged attention path: headDim above 256.");
+    const size_t rows = static_cast<size_t>(rq.seq_len);
+    const size_t numBlocks = (rows + l.block_size - 1) / l.block_size;
+    const size_t ioBytes = rows * ioBytesPerToken(l), statBytes = rows * l.num_heads * sizeof(float);
+    const size_t poolNeed = numBlocks * l.block_size * kvBytesPerToken(l);
+    if (!requireBuffer(c, rq.q, "Q", ioBytes)) return -1;
+    if (!requireBuffer(c, rq.d_out, "dO", ioBytes)) return -1;
+    if (!requireBuffer(c, rq.m, "m", statBytes)) return -1;
+    if (!requireBuffer(c, rq.l, "l", statBytes)) return -1;
+    if (!requireBuffer(c, rq.d_q, "dQ", ioBytes)) return -1;
+    if (!requireBuffer(c, rq.block_table, "blockTable", numBlocks * sizeof(int32_t))) return -1;
+    if (!requireBuffer(c, rq.k_pool, "K pool", poolNeed)) return -1;
+    if (!requireBuffer(c, rq.v_pool, "V pool", poolNeed)) return -1;
+    if (!requireBuffer(c, rq.d_k_pool, "dK pool", poolNeed)) return -1;
+    if (!requireBuffer(c, rq.d_v_pool, "dV pool", poolNeed)) return -1;
+    if (c->device < 0) return noGpu(c);
+    const void* pools[] = {rq.k_pool.ptr, rq.v_pool.ptr, rq.d_k_pool.ptr, rq.d_v_pool.ptr};
+    for (const void* ptr : pools)
+        if (!isDevicePointer(ptr))
+            return c->fail(PAM_ERR_INVALID_CONFIGURATION, invalidConfiguration("KV pools and their gradient pools must be device memory."));
+    const int window = l.window_size > 0 ? l.window_size : 0;                 // (the call's own windowSize, :1358; no engine default)
+    const int maxNumBlocks = rq.block_table.bytes != kUnknownBytes
+                                 ? static_cast<int>(std::min<size_t>(rq.block_table.bytes / sizeof(int32_t), 1u << 30))
+                                 : static_cast<int>(numBlocks);
+    const double t0 = nowMs();
+    c->arena.reset(c->stream);
+    Stager st(c);
+    size_t tempBytes = 0;
+    int32_t rc = withRetry(c, "backward", [&]() -> cudaError_t {
+        pam::BackwardParams p{};
+        p.q = st.in(rq.q.ptr, ioBytes);
+        p.dO = st.in(rq.d_out.ptr, ioBytes);
+        p.m = static_cast<const float*>(st.in(rq.m.ptr, statBytes));
+        p.l = static_cast<const float*>(st.in(rq.l.ptr, statBytes));
+        p.table = static_cast<const int32_t*>(st.in(rq.block_table.ptr, static_cast<size_t>(maxNumBlocks) * sizeof(int32_t)));
+        p.dQ = st.out(rq.d_q.ptr, ioBytes);
+        p.kPool = rq.k_pool.ptr; p.vPool = rq.v_pool.ptr; p.dKPool = rq.d_k_pool.ptr; p.dVPool = rq.d_v_pool.ptr;
+        p.seqLen = rq.seq_len; p.heads = l.num_heads; p.kvHeads = l.num_kv_heads; p.headDim = l.head_dim;
+        p.blockSize = l.block_size; p.dtype = l.data_type;
+        p.windowStart = window > 0 ? std::max(0, rq.seq_len - window) : 0;    // :1380
+        p.maxNumBlocks = maxNumBlocks;
+        const int kPoolBlocks = poolBlocksOf(rq.k_pool, rq.v_pool, l), dPoolBlocks = poolBlocksOf(rq.d_k_pool, rq.d_v_pool, l);
+        p.poolBlocks = std::min(kPoolBlocks, dPoolBlocks);
+        if (!st.ok()) return cudaErrorMemoryAllocation;
+        tempBytes = pam::backwardWorkspaceBytes(p);
+        unsigned char* ws = static_cast<unsigned char*>(c->arena.take(tempBytes));
+        if (!ws) return cudaErrorMemoryAllocation;
+        p.rowSum = reinterpret_cast<float*>(ws);
+        const size_t rowSumBytes = (statBytes + 255) / 256 * 256;
+        p.dQAcc = l.data_type == PAM_DTYPE_F32 ? static_cast<float*>(p.dQ) : reinterpret_cast<float*>(ws + rowSumBytes);
+        int launches = 0;
+        cudaError_t e = pam::launchBackward(p, c->stream, &launches);
+        c->launches += launches;
+        if (e == cudaSuccess) e = st.copyBack();
+        return e;
+    });
+    if (rc != 0) {
+        if (!c->graceful) return rc;
+        st.zeroOutputs(rq.d_q.ptr, rq.d_q.bytes != kUnknownBytes ? rq.d_q.bytes : ioBytes);
+        c->clearError();
+    }
+    if (c->async && st.hasOutputs()) cudaStreamSynchronize(c->stream);
+    c->stats = PamStats{PAM_OP_BACKWARD, 1, rq.seq_len, static_cast<int32_t>(numBlocks), static_cast<int64_t>(tempBytes), 0, nowMs() - t0};
+    return 0;
+}
+
 int32_t pamc_decode_layers(void* ctx, const PamDecodeRequest* requests, int32_t num_layers) {
     return runLayers(ctx, requests, num_layers, [](Context* c, const PamDecodeRequest& rq, int) { return decodeImpl(c, rq); });
 }

@@ -267,6 +267,18 @@ class PagedAttentionEngine:
                                          _buf(request.vScaleBuffer))
         _check(self._ctx, lib.pamc_fused_prefill(self._ctx, C.byref(r), cache._h if cache is not None else None))
 
+    def backward(self, q, kPool, vPool, blockTable, dO, m, l, dQ, dKPool, dVPool, seqLen: int, headDim: int,
+                 numHeads: int, numKVHeads: int, blockSize: int,
+                 dataType: PagedAttentionDataType = PagedAttentionDataType.float32, windowSize: int = 0) -> None:
+        """PagedAttentionEngine.swift:1341-1395: gradients with respect to the queries (dQ,
+        written) and the paged keys and values (dKPool, dVPool, added to) of the attention of
+        rows [0, seqLen) over keys [windowStart, seqLen), no causal mask; m and l are the row
+        maximum and row sum of the forward pass, float32 [seqLen][numHeads]."""
+        layer = _cabi.PamLayerSpec(headDim, numHeads, numKVHeads, blockSize, int(dataType), windowSize)
+        r = _cabi.PamBackwardRequest(_buf(q), _buf(kPool), _buf(vPool), _buf(blockTable), _buf(dO), _buf(m), _buf(l),
+                                     _buf(dQ), _buf(dKPool), _buf(dVPool), seqLen, layer)
+        _check(self._ctx, lib.pamc_backward(self._ctx, C.byref(r)))
+
     def prefillBatch(self, q, kPool, vPool, blockTables, output, seqLens: Sequence[int], qStarts: Sequence[int],
                      qLens: Sequence[int], maxNumBlocks: int, layer: PagedLayerSpec, causal: bool = True,
                      kScaleBuffer=None, vScaleBuffer=None) -> None:

@@ -284,3 +284,36 @@ def test_inference_memory_pressure_policies():
     ora.add_request(200, 1)
     with pytest.raises(po.OutOfMemory):
         ora.step()
+
+
+def test_backward_formulas_match_autograd():
+    """The backward restatement (kernels.metal:1217-1315 as dense algebra) against the gradient
+    that automatic differentiation of softmax(q k^T / sqrt(d)) v gives, in float64, over a
+    paged cache with a window: the reference has no test of its backward kernels, so this is
+    what pins the oracle's formulas (not the reference's arithmetic order)."""
+    torch = pytest.importorskip("torch")
+    rng = np.random.default_rng(5)
+    L, H, KVH, D, bs = 37, 4, 2, 16, 8
+    nb = (L + bs - 1) // bs
+    table = rng.permutation(nb + 3)[:nb].astype(np.int32)
+    kp = rng.standard_normal((nb + 3, KVH, bs, D)).astype(np.float32)
+    vp = rng.standard_normal((nb + 3, KVH, bs, D)).astype(np.float32)
+    q = rng.standard_normal((L, H, D)).astype(np.float32)
+    d_out = rng.standard_normal((L, H, D)).astype(np.float32)
+    for ws in (0, 10):
+        m, l = po.attention_stats(q, kp, table, L, KVH, bs, ws)
+        dq, dk, dv = po.paged_backward(q, kp, vp, table, d_out, m, l, L, KVH, bs, ws)
+        tq = torch.tensor(q, dtype=torch.float64, requires_grad=True)
+        tk = torch.tensor(kp, dtype=torch.float64, requires_grad=True)
+        tv = torch.tensor(vp, dtype=torch.float64, requires_grad=True)
+        toks = np.arange(ws, L)
+        blk, slot = torch.tensor(table[toks // bs].astype(np.int64)), torch.tensor(toks % bs)
+        heads = []
+        for h in range(H):
+            kvh = h // (H // KVH)
+            s = (tq[:, h] @ tk[blk, kvh, slot].T) / float(np.sqrt(np.float32(D)))
+            heads.append(torch.softmax(s, dim=1) @ tv[blk, kvh, slot])
+        (torch.stack(heads, dim=1) * torch.tensor(d_out, dtype=torch.float64)).sum().backward()
+        assert np.abs(dq - tq.grad.numpy()).max() < 1e-6
+        assert np.abs(dk - tk.grad.numpy()).max() < 1e-6
+        assert np.abs(dv - tv.grad.numpy()).max() < 1e-6
