@@ -1033,15 +1033,15 @@ def run_backward(rt, with_cpu):
     if rank == 0:
         flops = 5 * 2 * L * L * HEAD_DIM * heads * rt.world           # whole job
         tflops = flops / (ms[0] * 1e-3) / 1e12
-        line = rt.base_line("backward", "backward TFLOP/s", tflops, "TFLOP/s", ms, "f16 in, f32 arithmetic", settled, launches, clocks,
+        line = rt.base_line("backward", "backward TFLOP/s", tflops, "TFLOP/s", ms, "f16", settled, launches, clocks,
                             {"seed": 1005, "l2": "the sequence's K/V and gradients (a few MB per KV head) stay in L2 by design"})
         peak = rt.peaks["bf16_tflops"]
         line["roofline"] = {"bound": "tensor", "achieved": tflops / rt.world, "peak": peak, "unit": "TFLOP/s",
                             "frac": tflops / rt.world / peak, "peak_source": f"{rt.peak_kind} cuBLAS bf16 burst", "per": "GPU",
-                            "kernel": "backwardKeyTileKernel (+ backwardRowSumKernel, backwardStoreKernel)",
+                            "kernel": "backwardMmaKeyTileKernel (+ backwardMmaRowSumKernel, backwardMmaStoreKernel)",
                             "algorithmic_flops_per_step": flops // rt.world, "traffic": None,
-                            "note": "float32 products on the CUDA cores, as the reference's float32 arithmetic; the tensor "
-                                    "peak is given as the scale, not as the bound of this form"}
+                            "note": "mma.sync.m16n8k16 products (legacy tensor path) with float32 accumulation, seven products "
+                                    "of which five are counted (S and dP are computed twice)"}
         line["e2e"] = {"value": None, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
                        "note": "not measured for this workload"}
     return line

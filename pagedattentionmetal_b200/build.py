@@ -19,7 +19,7 @@ OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libpam_cuda.so")
 INCLUDE = os.path.join(HERE, "..", "include")
 
-SOURCES = ["cache_kernels.cu", "decode_kernels.cu", "decode_stream_kernel.cu", "prefill_kernels.cu", "prefill_tc_kernel.cu", "backward_kernels.cu", "pam_cabi.cu",
+SOURCES = ["cache_kernels.cu", "decode_kernels.cu", "decode_stream_kernel.cu", "prefill_kernels.cu", "prefill_tc_kernel.cu", "backward_kernels.cu", "backward_mma_kernels.cu", "pam_cabi.cu",
            "comm.cu", "block_manager.cpp"]
 HEADERS = ["kernels.h", "block_manager.h", os.path.join(INCLUDE, "pam_cuda.h")]
 

@@ -24,9 +24,11 @@
 //    into a float32 buffer with red.global.add.f32.
 //  * backwardStoreKernel -- float32 dQ to the output type (16-bit types only).
 //
-// The products run on the CUDA cores in float32 (4 x 4 register blocks out of shared memory):
-// the float32 path of the reference is float32 arithmetic, which tensor cores would only reach
-// through split operands.  Pools are [block][kv_head][block_size][head_dim] like everywhere here.
+// The products of this file run on the CUDA cores in float32 (4 x 4 register blocks out of
+// shared memory): the float32 path of the reference is float32 arithmetic, which tensor cores
+// would only reach through split operands.  float16 / bfloat16 with head_dim 64 or 128 take the
+// tensor-core form of backward_mma_kernels.cu instead.  Pools are
+// [block][kv_head][block_size][head_dim] like everywhere here.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -366,6 +368,7 @@ cudaError_t launchBackward(const BackwardParams& p, cudaStream_t stream, int* la
     if (p.headDim <= 0 || p.headDim > 256 || p.kvHeads <= 0 || p.heads % p.kvHeads != 0 || p.poolBlocks <= 0 || p.maxNumBlocks <= 0 ||
         p.windowStart < 0 || p.windowStart > p.seqLen)
         return cudaErrorInvalidValue;
+    if (backwardTensorPathApplies(p)) return launchBackwardTensor(p, stream, launches);
     switch (p.dtype) {
         case kF32: return launchByDim<float>(p, stream, launches);
         case kF16: return launchByDim<__half>(p, stream, launches);

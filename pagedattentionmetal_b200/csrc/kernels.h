@@ -113,6 +113,10 @@ struct BackwardParams {
 // Bytes of workspace (rowSum first, 256-byte aligned, then dQAcc for the 16-bit types).
 size_t backwardWorkspaceBytes(const BackwardParams& p);
 cudaError_t launchBackward(const BackwardParams& p, cudaStream_t stream, int* launches);
+// The tensor-core form (backward_mma_kernels.cu): float16 / bfloat16, head_dim 64 or 128,
+// 16-byte aligned buffers; launchBackward takes it when it applies.
+bool backwardTensorPathApplies(const BackwardParams& p);
+cudaError_t launchBackwardTensor(const BackwardParams& p, cudaStream_t stream, int* launches);
 
 // ---- prefill (prefill_kernels.cu) ----
 constexpr int kPrefillInlineSeqs = 32;
