@@ -96,16 +96,26 @@ struct Tiles {
 };
 
 // 64 rows of HD elements into a tile, 16 bytes per thread and step; `rowPtr(r)` gives the
-// global address of row r or null (zeros).
+// global address of row r or null (zeros).  The addresses (a block-table look-up each for
+// pool rows) are all taken first and the loads all issued before the first store, so that a
+// tile costs two memory round trips, not two per step.
 template <typename T, int HD, class F>
 __device__ __forceinline__ void loadTile(T* tile, F rowPtr) {
-    constexpr int CPR = HD * 2 / 16, RS = HD + 8;
-    for (int idx = threadIdx.x; idx < kTile * CPR; idx += kThreads) {
-        const int r = idx / CPR, c = idx - r * CPR;
-        const T* src = rowPtr(r);
-        uint4 val = make_uint4(0u, 0u, 0u, 0u);
-        if (src) val = *reinterpret_cast<const uint4*>(src + c * 8);
-        *reinterpret_cast<uint4*>(tile + r * RS + c * 8) = val;
+    constexpr int CPR = HD * 2 / 16, RS = HD + 8, N = kTile * CPR / kThreads;
+    static_assert(kTile * CPR % kThreads == 0, "a tile is a whole number of steps");
+    const T* src[N];
+    uint4 val[N];
+#pragma unroll
+    for (int i = 0; i < N; ++i) src[i] = rowPtr((threadIdx.x + kThreads * i) / CPR);
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+        val[i] = make_uint4(0u, 0u, 0u, 0u);
+        if (src[i]) val[i] = *reinterpret_cast<const uint4*>(src[i] + ((threadIdx.x + kThreads * i) % CPR) * 8);
+    }
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+        const int idx = threadIdx.x + kThreads * i;
+        *reinterpret_cast<uint4*>(tile + (idx / CPR) * RS + (idx % CPR) * 8) = val[i];
     }
 }
 
