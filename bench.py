@@ -341,17 +341,45 @@ def cpu_append_c1(budget_s=5.0):
             "ms_per_step_sample": dt * 1e3, "sample_fraction": 1.0}
 
 
+def cpu_backward(budget_s=5.0, rows=512):
+    """The backward restatement (numpy, float64 matrix products on the host's BLAS threads) on the
+    first `rows` tokens of a sequence of the workload's shape."""
+    from oracle import paged_oracle as po
+
+    rng = np.random.default_rng(1005)
+    nb = rows // BLOCK
+    table = rng.permutation(nb + 8)[:nb].astype(np.int32)
+    kp = rng.standard_normal((nb + 8, KV_HEADS, BLOCK, HEAD_DIM)).astype(np.float16)
+    vp = rng.standard_normal((nb + 8, KV_HEADS, BLOCK, HEAD_DIM)).astype(np.float16)
+    q = rng.standard_normal((rows, HEADS, HEAD_DIM)).astype(np.float16)
+    d_out = (0.1 * rng.standard_normal((rows, HEADS, HEAD_DIM))).astype(np.float16)
+    m, l = po.attention_stats(q, kp, table, rows, KV_HEADS, BLOCK)
+    run = lambda: po.paged_backward(q, kp, vp, table, d_out, m, l, rows, KV_HEADS, BLOCK)
+    run()
+    passes, t0 = 0, time.perf_counter()
+    while passes < 1 or time.perf_counter() - t0 < budget_s:
+        run()
+        passes += 1
+    dt = (time.perf_counter() - t0) / passes
+    flops = 5 * 2 * rows * rows * HEAD_DIM * HEADS
+    return {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
+            "sample": f"the first {rows} tokens of a sequence ({rows} x {rows} pairs per head, 32 q / 8 kv heads), {passes} timed "
+                      f"passes of {dt * 1e3:.1f} ms (oracle/paged_oracle.py paged_backward, numpy)",
+            "ms_per_step_sample": dt * 1e3, "sample_fraction": (rows / 2048.0) ** 2}
+
+
 def c3_flops(heads=HEADS, seqs=None):
     return (seqs or PF_SEQS) * heads * (PF_LEN * (PF_LEN + 1) // 2) * 4 * HEAD_DIM
 
 
 CPU_ARMS = {"decode_c2": lambda a: cpu_decode_c2(max(a.steps, 1), a.warmup), "prefill_c3": lambda a: cpu_prefill_c3(),
-            "decode_c4": lambda a: cpu_decode_c4(), "append_c1": lambda a: cpu_append_c1()}
+            "decode_c4": lambda a: cpu_decode_c4(), "append_c1": lambda a: cpu_append_c1(), "backward": lambda a: cpu_backward()}
 CPU_META = {
     "decode_c2": ("paged decode tokens/s", "f16", lambda cb: BATCH),
     "prefill_c3": ("prefill TFLOP/s", "bf16", None),
     "decode_c4": ("paged decode tokens/s", "fp8-e4m3 KV, f16 q/out", lambda cb: C4_SEQS),
     "append_c1": ("KV append GB/s", "f16 -> f16 / fp8-e4m3", None),
+    "backward": ("backward TFLOP/s", "f16", None),
 }
 
 
@@ -1044,6 +1072,8 @@ def run_backward(rt, with_cpu):
                                     "of which five are counted (S and dP are computed twice)"}
         line["e2e"] = {"value": None, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
                        "note": "not measured for this workload"}
+        if with_cpu:
+            line["cpu_baseline"] = cpu_backward()
     return line
 
 
