@@ -986,20 +986,19 @@ decodeStreamKernel(const StreamArgs a) {
     typename P::Query q;
     typename P::Acc acc;
     int len = 0, windowStart = 0, pairBegin = 0, pairTiles = 0;
-    bool fresh = true;
+    // The length and the query rows of the (sequence, kv head) pair at `c`.  At a border they are
+    // asked for before the finished pair's result leaves, so that they arrive meanwhile.
+    auto openPair = [&](const Cursor& c, int& newLen, int& newWindowStart, int& newPairBegin) {
+        const uint32_t L = a.lens[c.b];
+        const Visible v = visibleOf(L, a.window, maxTokens);
+        newLen = static_cast<int>(L < static_cast<uint32_t>(maxTokens) ? L : static_cast<uint32_t>(maxTokens));
+        newWindowStart = v.windowStart;
+        newPairBegin = prefix[c.b] + c.kvh * c.tilesB;
+        P::loadQuery(q, a, static_cast<int64_t>(c.b) * a.heads + c.kvh * G, G, lane);
+    };
+    openPair(cur, len, windowStart, pairBegin);
+    P::reset(acc, len - windowStart);
     for (int done = begin; done < end;) {
-        if (fresh) {
-            // a new (sequence, kv head) pair starts in this warp
-            const uint32_t L = a.lens[cur.b];
-            const Visible v = visibleOf(L, a.window, maxTokens);
-            len = static_cast<int>(L < static_cast<uint32_t>(maxTokens) ? L : static_cast<uint32_t>(maxTokens));
-            windowStart = v.windowStart;
-            pairBegin = prefix[cur.b] + cur.kvh * cur.tilesB;
-            pairTiles = 0;
-            P::loadQuery(q, a, static_cast<int64_t>(cur.b) * a.heads + cur.kvh * G, G, lane);
-            P::reset(acc, len - windowStart);
-            fresh = false;
-        }
         cpAsyncWait<NS - 1>();
         __syncwarp();
         const int slot = (done - begin) % NS;
@@ -1011,9 +1010,13 @@ decodeStreamKernel(const StreamArgs a) {
         issueNext(slot);
         cpAsyncCommit();
 
+        Cursor next = cur;
+        advance(next, prefix, first, a.batch, a.kvHeads);
         if (cur.tile + 1 == cur.tilesB || done == end) {
             // the pair ends here, or the piece does
             P::finish(acc);
+            int nextLen = 0, nextWindowStart = 0, nextPairBegin = 0;
+            if (done < end) openPair(next, nextLen, nextWindowStart, nextPairBegin);       // (the query registers are free: the last tile is done)
             const int64_t outRow = static_cast<int64_t>(cur.b) * a.heads + cur.kvh * G;
             if (pairTiles == cur.tilesB) {
                 // every tile of the pair was this warp's: its output
@@ -1061,9 +1064,13 @@ decodeStreamKernel(const StreamArgs a) {
                     combine<P>(a.records, static_cast<Out*>(a.out), a.heads, cur.b, cur.kvh, G, base, n, lane);
                 }
             }
-            fresh = true;
+            len = nextLen;
+            windowStart = nextWindowStart;
+            pairBegin = nextPairBegin;
+            pairTiles = 0;
+            P::reset(acc, len - windowStart);
         }
-        advance(cur, prefix, first, a.batch, a.kvHeads);
+        cur = next;
     }
     cpAsyncWait<0>();
 }
