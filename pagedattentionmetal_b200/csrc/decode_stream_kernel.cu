@@ -960,6 +960,9 @@ decodeStreamKernel(const StreamArgs a) {
     const int begin = min(wid * quota, total), end = min(begin + quota, total);
     if (begin >= end) return;                        // (no barrier below this line)
     const int tilesPerPage = a.blockSize / kTileTokens;
+    // (a division by a run-time value is some twenty instructions per tile; block sizes are
+    // powers of two in practice)
+    const int pageShift = (tilesPerPage & (tilesPerPage - 1)) == 0 ? __ffs(tilesPerPage) - 1 : -1;
     unsigned char* ring = smem + static_cast<size_t>(warp) * NS * STAGEB;
     const uint32_t ringAddr = smemAddr(ring);
 
@@ -970,7 +973,7 @@ decodeStreamKernel(const StreamArgs a) {
     auto issueNext = [&](int slot) {
         if (issued >= end) return;
         const int tile = ahead.firstTile + ahead.tile;
-        const int page = tile / tilesPerPage, within = tile - page * tilesPerPage;
+        const int page = pageShift >= 0 ? tile >> pageShift : tile / tilesPerPage, within = tile - page * tilesPerPage;
         const int32_t* table = a.tables + static_cast<int64_t>(ahead.b) * a.maxNumBlocks;
         const int64_t blk = min(max(table[page], 0), a.poolBlocks - 1);     // never read outside the pool
         P::issue(ringAddr + slot * STAGEB, ring + slot * STAGEB, a, blk, ahead.kvh, within, lane);
