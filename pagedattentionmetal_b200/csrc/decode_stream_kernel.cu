@@ -32,6 +32,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <algorithm>
 #include <atomic>
 #include <cmath>
 #include <type_traits>
@@ -1131,6 +1132,20 @@ cudaError_t launchStreamT(const DecodeParams& p, int smCount, cudaStream_t strea
     cudaError_t e = streamGrid<P>(p.batch, smCount, &grid);
     if (e != cudaSuccess) return e;
     const int G = p.heads / p.kvHeads, pairs = p.batch * p.kvHeads;
+    // Short lists get fewer warps.  With less than kMinTilesPerWarp tiles per warp (by the bound
+    // the table width and the window give; the lengths are on the device) a third CTA per SM
+    // costs more in records, combinations and starts than it hides latency: measured on one KV
+    // head of the long-context FP8 workload, 9 tiles per warp at three CTAs per SM took 0.063 ms
+    // against 0.048 ms at two (14 per warp), while 18 per warp at three beat 28 at two.
+    {
+        constexpr int64_t kMinTilesPerWarp = 14;
+        int64_t tokens = static_cast<int64_t>(p.maxNumBlocks) * p.blockSize;
+        if (p.window > 0) tokens = std::min<int64_t>(tokens, static_cast<int64_t>(p.window) + p.blockSize);
+        const int64_t tiles = (tokens + kTileTokens - 1) / kTileTokens * pairs;
+        int perSm = std::max(grid / std::max(smCount, 1), 1);
+        while (perSm > 2 && tiles < kMinTilesPerWarp * smCount * perSm * kWarps) --perSm;
+        grid = smCount * perSm;
+    }
     // a smaller workspace (the fixed array of the no-allocation call) holds fewer warps' records
     while (grid > 1 && recordBytes(grid, pairs, G, P::HD) > p.workspaceBytes) grid = grid * 3 / 4;
     if (recordBytes(grid, pairs, G, P::HD) > p.workspaceBytes) return cudaErrorInvalidValue;
