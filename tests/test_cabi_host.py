@@ -73,3 +73,38 @@ def test_decode_kernel_choice_follows_shape_type_and_alignment():
     rq.q.ptr += 4
     assert path(rq) == 1
     assert lib.pamc_decode_path(None) == -1
+
+
+def test_backward_validation_runs_before_the_device_is_needed():
+    """pamc_backward checks every buffer of known length against what the kernels touch and
+    refuses an FP8 cache, on a context without a GPU (the pointers are never dereferenced)."""
+    ctx = lib.pamc_create_host_context()
+    try:
+        L, H, KVH, D, bs = 40, 8, 2, 64, 16
+        nb = (L + bs - 1) // bs
+        io, stats, pool = L * H * D * 4, L * H * 4, nb * bs * KVH * D * 4
+        base = 1 << 22
+        b = lambda i, n: _cabi.PamBuffer(base + (i << 20), n)
+
+        def request(dtype=DT.float32, **short):
+            sizes = dict(q=io, k_pool=pool, v_pool=pool, block_table=nb * 4, d_out=io, m=stats, l=stats, d_q=io, d_k_pool=pool,
+                         d_v_pool=pool)
+            sizes.update(short)
+            order = ["q", "k_pool", "v_pool", "block_table", "d_out", "m", "l", "d_q", "d_k_pool", "d_v_pool"]
+            return _cabi.PamBackwardRequest(*[b(i, sizes[name]) for i, name in enumerate(order)], L,
+                                            _cabi.PamLayerSpec(D, H, KVH, bs, int(dtype), 0))
+
+        for name, text in (("d_q", "dQ"), ("m", "m"), ("d_out", "dO"), ("d_v_pool", "dV pool"), ("block_table", "blockTable")):
+            full = dict(q=io, m=stats, d_out=io, d_q=io, d_v_pool=pool, block_table=nb * 4)[name]
+            rq = request(**{name: full - 4})
+            assert lib.pamc_backward(ctx, C.byref(rq)) == -1
+            assert lib.pamc_last_error_code(ctx) == 5
+            assert lib.pam_last_error(ctx) == f"{text} buffer is too small: expected at least {full} bytes, got {full - 4}.".encode()
+        rq = request(DT.float8)
+        assert lib.pamc_backward(ctx, C.byref(rq)) == -1 and lib.pamc_last_error_code(ctx) == 8
+        # everything in order: only the missing GPU is left to complain about
+        rq = request()
+        assert lib.pamc_backward(ctx, C.byref(rq)) == -1 and lib.pamc_last_error_code(ctx) == 1
+        assert lib.pamc_backward(ctx, None) == -1
+    finally:
+        lib.pam_destroy_context(ctx)
